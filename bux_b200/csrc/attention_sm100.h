@@ -1,0 +1,28 @@
+// Host-visible types of the tcgen05 attention kernels (attention_sm100.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace bux {
+
+struct Status;
+
+// q, o, d_o, dq: [B, T, H, D] bf16.  k, v, dk, dv: [B, S, G, D] bf16 (H % G == 0).
+// lse, delta: [B, H, T] fp32.  sinks / dsinks: [H] fp32 or null.  D is 64 or 128.
+// Causal alignment is bottom-right (query t sees keys <= t + S - T); window > 0 keeps
+// keys in (t + S - T - window, t + S - T].
+struct AttnArgs {
+  const void* q = nullptr; const void* k = nullptr; const void* v = nullptr;
+  void* o = nullptr; float* lse = nullptr;
+  const void* d_o = nullptr; void* dq = nullptr; void* dk = nullptr; void* dv = nullptr;
+  float* delta = nullptr;
+  const float* sinks = nullptr; float* dsinks = nullptr;
+  int B = 0, T = 0, S = 0, H = 0, G = 0, D = 0;
+  float scale = 1.f; bool causal = true; int window = 0;
+  Status* status = nullptr;
+};
+
+const char* attn_fwd_launch(const AttnArgs& a, cudaStream_t stream);
+const char* attn_bwd_launch(const AttnArgs& a, cudaStream_t stream);
+
+}  // namespace bux

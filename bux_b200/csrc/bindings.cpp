@@ -1,0 +1,232 @@
+// torch.ops.bux_b200.* : thin tensor-checking wrappers around the CUDA launchers.
+// Registered with TORCH_LIBRARY so the shared object is loaded with
+// torch.ops.load_library and needs no Python headers.
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+
+#include "attention_sm100.h"
+#include "elementwise.h"
+#include "gemm_sm100.h"
+
+namespace {
+
+using at::Tensor;
+
+cudaStream_t stream_of(const Tensor& t) {
+  return at::cuda::getCurrentCUDAStream(t.device().index()).stream();
+}
+void check_cuda(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+}
+bux::Status* status_ptr(const c10::optional<Tensor>& st) {
+  if (!st.has_value()) return nullptr;
+  TORCH_CHECK(st->is_cuda() && st->scalar_type() == at::kInt && st->numel() >= 2, "status: int32[2] on the device");
+  return reinterpret_cast<bux::Status*>(st->data_ptr());
+}
+const float* opt_f32(const c10::optional<Tensor>& t) {
+  if (!t.has_value()) return nullptr;
+  TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat && t->is_contiguous(), "expected a contiguous fp32 CUDA tensor");
+  return t->data_ptr<float>();
+}
+const int* opt_i32(const c10::optional<Tensor>& t) {
+  if (!t.has_value()) return nullptr;
+  TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kInt && t->is_contiguous(), "expected a contiguous int32 CUDA tensor");
+  return t->data_ptr<int>();
+}
+
+// ------------------------------------------------------------------ GEMM
+// c (+)= a · b^T.  kind 0 = bf16, 1 = mxfp8 (a/b uint8 e4m3 bytes, sfa/sfb tiled scales).
+// a_mn / b_mn: operand stored transposed ([K, M] / [K, N]).  mode: 0 dense, 1 grouped rows
+// (b is [groups*N, K] or, MN-major, [groups*K, N]), 2 grouped contraction.
+void gemm(const Tensor& a, const Tensor& b, Tensor& c, const c10::optional<Tensor>& sfa,
+          const c10::optional<Tensor>& sfb, const c10::optional<Tensor>& group_offsets,
+          const c10::optional<Tensor>& status, int64_t kind, int64_t mode, int64_t M, int64_t N,
+          int64_t K, int64_t k_total, int64_t groups, bool a_mn, bool b_mn, int64_t out_kind,
+          int64_t bn, int64_t sms) {
+  check_cuda(a, "a"); check_cuda(b, "b"); check_cuda(c, "c");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "a and b are 2-D views");
+  c10::cuda::CUDAGuard guard(a.device());
+  bux::GemmArgs g;
+  g.kind = (int)kind; g.mode = (int)mode; g.bn = (int)bn; g.out_kind = (int)out_kind;
+  g.a_mn = a_mn; g.b_mn = b_mn;
+  const int elem = kind == bux::KIND_BF16 ? 2 : 1;
+  TORCH_CHECK((int)a.element_size() == elem && (int)b.element_size() == elem, "operand dtype does not match kind");
+  g.a = a.data_ptr(); g.a_outer = a.size(0); g.a_inner = a.size(1); g.lda_bytes = a.stride(0) * elem;
+  g.b = b.data_ptr(); g.b_outer = b.size(0); g.b_inner = b.size(1); g.ldb_bytes = b.stride(0) * elem;
+  if (kind == bux::KIND_MXFP8) {
+    TORCH_CHECK(sfa.has_value() && sfb.has_value(), "mxfp8 needs scale tensors");
+    g.sfa = reinterpret_cast<const uint8_t*>(sfa->data_ptr());
+    g.sfb = reinterpret_cast<const uint8_t*>(sfb->data_ptr());
+  }
+  g.c = c.data_ptr(); g.ldc = (int)c.stride(c.dim() - 2);
+  TORCH_CHECK(out_kind == bux::OUT_BF16 ? c.scalar_type() == at::kBFloat16 : c.scalar_type() == at::kFloat, "c dtype does not match out_kind");
+  g.M = (int)M; g.N = (int)N; g.K = (int)K; g.k_total = (int)k_total; g.groups = (int)groups;
+  g.group_offsets = opt_i32(group_offsets);
+  TORCH_CHECK(mode == bux::MODE_DENSE || g.group_offsets != nullptr, "grouped modes need group_offsets");
+  g.status = status_ptr(status);
+  g.sms = (int)sms;
+  const char* err = bux::gemm_launch(g, stream_of(a));
+  TORCH_CHECK(err == nullptr, "bux gemm: ", err);
+}
+
+// ------------------------------------------------------------------ norms
+void rmsnorm_fwd(const Tensor& x, const c10::optional<Tensor>& w, Tensor& y, Tensor& rstd, double eps) {
+  check_cuda(x, "x"); check_cuda(y, "y");
+  const int d = (int)x.size(-1);
+  TORCH_CHECK(d % 8 == 0 && x.scalar_type() == at::kBFloat16, "rmsnorm: bf16, width % 8 == 0");
+  c10::cuda::CUDAGuard guard(x.device());
+  bux::rmsnorm_fwd(x.data_ptr(), opt_f32(w), y.data_ptr(), rstd.data_ptr<float>(), x.numel() / d, d, (float)eps, stream_of(x));
+}
+void rmsnorm_bwd(const Tensor& x, const c10::optional<Tensor>& w, const Tensor& dy, const Tensor& rstd,
+                 Tensor& dx, const c10::optional<Tensor>& dw) {
+  check_cuda(x, "x"); check_cuda(dy, "dy"); check_cuda(dx, "dx");
+  const int d = (int)x.size(-1);
+  c10::cuda::CUDAGuard guard(x.device());
+  float* dwp = dw.has_value() ? dw->data_ptr<float>() : nullptr;
+  bux::rmsnorm_bwd(x.data_ptr(), opt_f32(w), dy.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(), dwp, x.numel() / d, d, stream_of(x));
+}
+// x viewed as [tokens, heads, D] with token stride stride_x (elements); y likewise.
+void norm_rope(bool bwd, const Tensor& x, const c10::optional<Tensor>& w, const Tensor& cos, const Tensor& sin,
+               Tensor& y, const c10::optional<Tensor>& rstd, const c10::optional<Tensor>& dy,
+               const c10::optional<Tensor>& dw, int64_t tokens, int64_t heads, int64_t D,
+               int64_t stride_x, int64_t stride_y, double eps) {
+  TORCH_CHECK(x.is_cuda() && y.is_cuda() && x.scalar_type() == at::kBFloat16, "norm_rope: bf16 CUDA tensors");
+  c10::cuda::CUDAGuard guard(x.device());
+  float* rs = rstd.has_value() ? rstd->data_ptr<float>() : nullptr;
+  float* dwp = dw.has_value() ? dw->data_ptr<float>() : nullptr;
+  const void* dyp = dy.has_value() ? dy->data_ptr() : nullptr;
+  const char* err = bux::norm_rope(bwd, x.data_ptr(), opt_f32(w), cos.data_ptr<float>(), sin.data_ptr<float>(), y.data_ptr(), rs, dyp, dwp,
+                                   tokens, (int)heads, (int)D, stride_x, stride_y, (float)eps, stream_of(x));
+  TORCH_CHECK(err == nullptr, err);
+}
+
+// ------------------------------------------------------------------ GLU
+void glu_fwd(const Tensor& h, Tensor& out, const c10::optional<Tensor>& row_scale, int64_t kind, double limit, double up_offset) {
+  check_cuda(h, "h"); check_cuda(out, "out");
+  const int f = (int)out.size(-1);
+  TORCH_CHECK(h.size(-1) == 2 * f && f % 8 == 0, "glu: h is [rows, 2f], f % 8 == 0");
+  c10::cuda::CUDAGuard guard(h.device());
+  bux::glu_fwd(h.data_ptr(), out.data_ptr(), opt_f32(row_scale), out.numel() / f, f, (int)kind, (float)limit, (float)up_offset, stream_of(h));
+}
+void glu_bwd(const Tensor& h, const Tensor& dout, Tensor& dh, const c10::optional<Tensor>& row_scale,
+             const c10::optional<Tensor>& d_row_scale, int64_t kind, double limit, double up_offset) {
+  check_cuda(h, "h"); check_cuda(dout, "dout"); check_cuda(dh, "dh");
+  const int f = (int)dout.size(-1);
+  c10::cuda::CUDAGuard guard(h.device());
+  float* drs = d_row_scale.has_value() ? d_row_scale->data_ptr<float>() : nullptr;
+  bux::glu_bwd(h.data_ptr(), dout.data_ptr(), dh.data_ptr(), opt_f32(row_scale), drs, dout.numel() / f, f, (int)kind, (float)limit, (float)up_offset, stream_of(h));
+}
+
+// ------------------------------------------------------------------ MXFP8 quantiser
+void quant_mxfp8(const Tensor& x, const c10::optional<Tensor>& row_index, const c10::optional<Tensor>& q_row,
+                 const c10::optional<Tensor>& sf_row, const c10::optional<Tensor>& q_col,
+                 const c10::optional<Tensor>& sf_col, int64_t rows, int64_t cols, int64_t ld_col) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.stride(-1) == 1, "quant: bf16 rows");
+  TORCH_CHECK(cols % 32 == 0, "quant: columns % 32 == 0");
+  c10::cuda::CUDAGuard guard(x.device());
+  uint8_t* qr = q_row.has_value() ? reinterpret_cast<uint8_t*>(q_row->data_ptr()) : nullptr;
+  uint8_t* sr = sf_row.has_value() ? reinterpret_cast<uint8_t*>(sf_row->data_ptr()) : nullptr;
+  uint8_t* qc = q_col.has_value() ? reinterpret_cast<uint8_t*>(q_col->data_ptr()) : nullptr;
+  uint8_t* sc = sf_col.has_value() ? reinterpret_cast<uint8_t*>(sf_col->data_ptr()) : nullptr;
+  TORCH_CHECK(qc == nullptr || ld_col % 32 == 0, "quant: transposed copy needs a row count padded to 32");
+  bux::quant_mxfp8(x.data_ptr(), x.stride(0), opt_i32(row_index), qr, sr, qc, sc, rows, (int)cols, ld_col, stream_of(x));
+}
+
+// ------------------------------------------------------------------ loss / optimiser / MoE rows
+void ce_fwd_bwd(Tensor& logits, const Tensor& targets, const c10::optional<Tensor>& mask, Tensor& loss,
+                const c10::optional<Tensor>& logz, double grad_scale, double z_weight, double softcap) {
+  check_cuda(logits, "logits");
+  TORCH_CHECK(logits.scalar_type() == at::kBFloat16 && logits.size(-1) % 8 == 0, "ce: bf16 logits, vocab % 8 == 0");
+  c10::cuda::CUDAGuard guard(logits.device());
+  float* lz = logz.has_value() ? logz->data_ptr<float>() : nullptr;
+  bux::ce_fwd_bwd(logits.data_ptr(), targets.data_ptr<int>(), opt_f32(mask), loss.data_ptr<float>(), lz,
+                  logits.size(0), (int)logits.size(1), logits.stride(0), (float)grad_scale, (float)z_weight, (float)softcap, stream_of(logits));
+}
+void adamw(Tensor& p, const Tensor& g, Tensor& m, Tensor& v, const c10::optional<Tensor>& m_sf,
+           const c10::optional<Tensor>& v_sf, const c10::optional<Tensor>& shadow,
+           const c10::optional<Tensor>& grad_scale, double lr, double b1, double b2, double eps,
+           double wd, double bc1, double bc2, double grad_scale_const) {
+  check_cuda(p, "p"); check_cuda(g, "g"); check_cuda(m, "m"); check_cuda(v, "v");
+  c10::cuda::CUDAGuard guard(p.device());
+  int mom = m.scalar_type() == at::kFloat ? bux::MOM_F32 : m.scalar_type() == at::kBFloat16 ? bux::MOM_BF16 : bux::MOM_FP8;
+  uint8_t* msf = m_sf.has_value() ? reinterpret_cast<uint8_t*>(m_sf->data_ptr()) : nullptr;
+  uint8_t* vsf = v_sf.has_value() ? reinterpret_cast<uint8_t*>(v_sf->data_ptr()) : nullptr;
+  TORCH_CHECK(mom != bux::MOM_FP8 || (msf && vsf), "8-bit moments need scale tensors");
+  void* sh = shadow.has_value() ? shadow->data_ptr() : nullptr;
+  const char* err = bux::adamw(p.data_ptr(), p.scalar_type() == at::kBFloat16, g.data_ptr(), g.scalar_type() == at::kBFloat16,
+                               m.data_ptr(), v.data_ptr(), msf, vsf, mom, sh, p.numel(), (float)lr, (float)b1, (float)b2,
+                               (float)eps, (float)wd, (float)bc1, (float)bc2, opt_f32(grad_scale), (float)grad_scale_const, stream_of(p));
+  TORCH_CHECK(err == nullptr, err);
+}
+void sumsq(const Tensor& g, Tensor& out) {
+  check_cuda(g, "g");
+  c10::cuda::CUDAGuard guard(g.device());
+  bux::sumsq(g.data_ptr(), g.scalar_type() == at::kBFloat16, g.numel(), out.data_ptr<float>(), stream_of(g));
+}
+void gather_rows(const Tensor& x, const Tensor& index, Tensor& out) {
+  check_cuda(x, "x"); check_cuda(out, "out");
+  c10::cuda::CUDAGuard guard(x.device());
+  bux::gather_rows(x.data_ptr(), index.data_ptr<int>(), out.data_ptr(), out.size(0), (int)out.size(1), stream_of(x));
+}
+void combine_rows(const Tensor& y, const Tensor& pos, const c10::optional<Tensor>& w, Tensor& out) {
+  check_cuda(y, "y"); check_cuda(out, "out");
+  c10::cuda::CUDAGuard guard(y.device());
+  bux::combine_rows(y.data_ptr(), pos.data_ptr<int>(), opt_f32(w), out.data_ptr(), out.size(0), (int)pos.size(1), (int)out.size(1), stream_of(y));
+}
+
+// ------------------------------------------------------------------ attention
+void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& o, Tensor& lse,
+              const c10::optional<Tensor>& sinks, const c10::optional<Tensor>& status,
+              double scale, bool causal, int64_t window) {
+  check_cuda(q, "q"); check_cuda(k, "k"); check_cuda(v, "v"); check_cuda(o, "o");
+  c10::cuda::CUDAGuard guard(q.device());
+  bux::AttnArgs a;
+  a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr(); a.o = o.data_ptr(); a.lse = lse.data_ptr<float>();
+  a.sinks = opt_f32(sinks);
+  a.B = (int)q.size(0); a.T = (int)q.size(1); a.H = (int)q.size(2); a.D = (int)q.size(3);
+  a.S = (int)k.size(1); a.G = (int)k.size(2);
+  a.scale = (float)scale; a.causal = causal; a.window = (int)window;
+  a.status = status_ptr(status);
+  const char* err = bux::attn_fwd_launch(a, stream_of(q));
+  TORCH_CHECK(err == nullptr, "bux attention: ", err);
+}
+void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& d_o,
+              const Tensor& lse, Tensor& dq, Tensor& dk, Tensor& dv, Tensor& delta,
+              const c10::optional<Tensor>& sinks, const c10::optional<Tensor>& dsinks,
+              const c10::optional<Tensor>& status, double scale, bool causal, int64_t window) {
+  check_cuda(q, "q"); check_cuda(d_o, "do");
+  c10::cuda::CUDAGuard guard(q.device());
+  bux::AttnArgs a;
+  a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr(); a.o = o.data_ptr(); a.lse = lse.data_ptr<float>();
+  a.d_o = d_o.data_ptr(); a.dq = dq.data_ptr(); a.dk = dk.data_ptr(); a.dv = dv.data_ptr(); a.delta = delta.data_ptr<float>();
+  a.sinks = opt_f32(sinks);
+  a.dsinks = dsinks.has_value() ? dsinks->data_ptr<float>() : nullptr;
+  a.B = (int)q.size(0); a.T = (int)q.size(1); a.H = (int)q.size(2); a.D = (int)q.size(3);
+  a.S = (int)k.size(1); a.G = (int)k.size(2);
+  a.scale = (float)scale; a.causal = causal; a.window = (int)window;
+  a.status = status_ptr(status);
+  const char* err = bux::attn_bwd_launch(a, stream_of(q));
+  TORCH_CHECK(err == nullptr, "bux attention backward: ", err);
+}
+
+}  // namespace
+
+TORCH_LIBRARY(bux_b200, m) {
+  m.def("gemm(Tensor a, Tensor b, Tensor(a!) c, Tensor? sfa, Tensor? sfb, Tensor? group_offsets, Tensor? status, int kind, int mode, int M, int N, int K, int k_total, int groups, bool a_mn, bool b_mn, int out_kind, int bn, int sms) -> ()", &gemm);
+  m.def("rmsnorm_fwd(Tensor x, Tensor? w, Tensor(a!) y, Tensor(b!) rstd, float eps) -> ()", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd(Tensor x, Tensor? w, Tensor dy, Tensor rstd, Tensor(a!) dx, Tensor? dw) -> ()", &rmsnorm_bwd);
+  m.def("norm_rope(bool bwd, Tensor x, Tensor? w, Tensor cos, Tensor sin, Tensor(a!) y, Tensor? rstd, Tensor? dy, Tensor? dw, int tokens, int heads, int D, int stride_x, int stride_y, float eps) -> ()", &norm_rope);
+  m.def("glu_fwd(Tensor h, Tensor(a!) out, Tensor? row_scale, int kind, float limit, float up_offset) -> ()", &glu_fwd);
+  m.def("glu_bwd(Tensor h, Tensor dout, Tensor(a!) dh, Tensor? row_scale, Tensor? d_row_scale, int kind, float limit, float up_offset) -> ()", &glu_bwd);
+  m.def("quant_mxfp8(Tensor x, Tensor? row_index, Tensor? q_row, Tensor? sf_row, Tensor? q_col, Tensor? sf_col, int rows, int cols, int ld_col) -> ()", &quant_mxfp8);
+  m.def("ce_fwd_bwd(Tensor(a!) logits, Tensor targets, Tensor? mask, Tensor(b!) loss, Tensor? logz, float grad_scale, float z_weight, float softcap) -> ()", &ce_fwd_bwd);
+  m.def("adamw(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor? m_sf, Tensor? v_sf, Tensor? shadow, Tensor? grad_scale, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2, float grad_scale_const) -> ()", &adamw);
+  m.def("sumsq(Tensor g, Tensor(a!) out) -> ()", &sumsq);
+  m.def("gather_rows(Tensor x, Tensor index, Tensor(a!) out) -> ()", &gather_rows);
+  m.def("combine_rows(Tensor y, Tensor pos, Tensor? w, Tensor(a!) out) -> ()", &combine_rows);
+  m.def("attn_fwd(Tensor q, Tensor k, Tensor v, Tensor(a!) o, Tensor(b!) lse, Tensor? sinks, Tensor? status, float scale, bool causal, int window) -> ()", &attn_fwd);
+  m.def("attn_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor d_o, Tensor lse, Tensor(a!) dq, Tensor(b!) dk, Tensor(c!) dv, Tensor(d!) delta, Tensor? sinks, Tensor? dsinks, Tensor? status, float scale, bool causal, int window) -> ()", &attn_bwd);
+}

@@ -1,0 +1,679 @@
+// Memory-bound kernels for sm_100a: RMSNorm (+ per-head QK-norm with RoPE), gated
+// activations, the dual-orientation MXFP8 quantiser, cross-entropy over a logits
+// chunk, flat AdamW (fp32 / bf16 / block-scaled 8-bit moments), and the MoE row
+// gather / weighted combine. All use 128-bit accesses and fp32 math; none allocates.
+//
+// Reference counterparts: norm_rope Pallas kernel (architecture/attention/norm_rope.py),
+// MXFP8 quantiser (architecture/precision/blockscaled.py:386-445), chunked
+// cross-entropy (architecture/logits.py:209-353), optax AdamW (train/optim.py:403),
+// token_rows / token_sums (architecture/experts/moe.py:992-1071).
+#include "common.cuh"
+#include "elementwise.h"
+
+namespace bux {
+
+// ---------------------------------------------------------------- RMSNorm
+// One warp per row. x, y: [rows, d] bf16; w: [d] fp32 or null; rstd: [rows] fp32 out.
+template <int VEC>
+__global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                                   __nv_bfloat16* __restrict__ y, float* __restrict__ rstd,
+                                   int rows, int d, float eps) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * d);
+  const int nvec = d / 8;
+  float ss = 0.f;
+  for (int i = lane; i < nvec; i += 32) {
+    uint4 v = xr[i];
+    float2 a = unpack_bf16(v.x), b = unpack_bf16(v.y), c = unpack_bf16(v.z), e = unpack_bf16(v.w);
+    ss += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y + c.x * c.x + c.y * c.y + e.x * e.x + e.y * e.y;
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / d + eps);
+  if (lane == 0 && rstd) rstd[row] = r;
+  uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * d);
+  for (int i = lane; i < nvec; i += 32) {
+    uint4 v = xr[i];
+    float f[8];
+    float2 t;
+    t = unpack_bf16(v.x); f[0] = t.x; f[1] = t.y;
+    t = unpack_bf16(v.y); f[2] = t.x; f[3] = t.y;
+    t = unpack_bf16(v.z); f[4] = t.x; f[5] = t.y;
+    t = unpack_bf16(v.w); f[6] = t.x; f[7] = t.y;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = f[j] * r * (w ? w[i * 8 + j] : 1.f);
+    uint4 o;
+    o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]);
+    o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
+    yr[i] = o;
+  }
+}
+
+// Backward: dx = r * (w*dy) - x * r^3 * mean(w*dy*x); dw += sum_rows dy * x * r.
+// Each block walks rows grid-stride, keeps its dw partial in shared memory (fp32) and
+// adds it to the global fp32 dw once at the end.
+__global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                                   const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd,
+                                   __nv_bfloat16* __restrict__ dx, float* __restrict__ dw,
+                                   int rows, int d) {
+  extern __shared__ float dw_part[];
+  for (int i = threadIdx.x; i < d; i += blockDim.x) dw_part[i] = 0.f;
+  __syncthreads();
+  const int warps_per_block = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = d / 8;
+  for (int row = blockIdx.x * warps_per_block + warp; row < rows; row += gridDim.x * warps_per_block) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * d);
+    const uint4* gr = reinterpret_cast<const uint4*>(dy + (size_t)row * d);
+    const float r = rstd[row];
+    float dot = 0.f;
+    for (int i = lane; i < nvec; i += 32) {
+      uint4 xv = xr[i], gv = gr[i];
+      const uint32_t* xu = &xv.x; const uint32_t* gu = &gv.x;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 a = unpack_bf16(xu[j]), g = unpack_bf16(gu[j]);
+        const float w0 = w ? w[i * 8 + 2 * j] : 1.f, w1 = w ? w[i * 8 + 2 * j + 1] : 1.f;
+        dot += a.x * g.x * w0 + a.y * g.y * w1;
+      }
+    }
+    dot = warp_sum(dot);
+    const float c = dot * r * r * r / d;
+    uint4* dxr = reinterpret_cast<uint4*>(dx + (size_t)row * d);
+    for (int i = lane; i < nvec; i += 32) {
+      uint4 xv = xr[i], gv = gr[i], o;
+      const uint32_t* xu = &xv.x; const uint32_t* gu = &gv.x; uint32_t* ou = &o.x;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 a = unpack_bf16(xu[j]), g = unpack_bf16(gu[j]);
+        const int col = i * 8 + 2 * j;
+        const float w0 = w ? w[col] : 1.f, w1 = w ? w[col + 1] : 1.f;
+        ou[j] = pack_bf16(r * w0 * g.x - a.x * c, r * w1 * g.y - a.y * c);
+        if (dw) {
+          atomicAdd(&dw_part[col], g.x * a.x * r);
+          atomicAdd(&dw_part[col + 1], g.y * a.y * r);
+        }
+      }
+      dxr[i] = o;
+    }
+  }
+  __syncthreads();
+  if (dw)
+    for (int i = threadIdx.x; i < d; i += blockDim.x) atomicAdd(&dw[i], dw_part[i]);
+}
+
+// ---------------------------------------------------------------- QK-norm + RoPE
+// x: [tokens, heads, D] bf16 (row stride `stride_tok` elements so it may be a slice of
+// a fused qkv buffer); cos/sin: [tokens, D/2] fp32; w: [D] fp32 or null (no norm).
+// One warp per (token, head): lane l holds D/32 consecutive elements; its rotation
+// partner (element i <-> i + D/2) lives in lane l ^ 16.
+template <int D, bool BWD>
+__global__ void norm_rope_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                                 const float* __restrict__ cs, const float* __restrict__ sn,
+                                 __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_io,
+                                 const __nv_bfloat16* __restrict__ dy, float* __restrict__ dw,
+                                 long tokens, int heads, long stride_tok_x, long stride_tok_y,
+                                 float eps) {
+  constexpr int E = D / 32;
+  __shared__ float dw_part[D];
+  if (BWD) {
+    for (int i = threadIdx.x; i < D; i += blockDim.x) dw_part[i] = 0.f;
+    __syncthreads();
+  }
+  const int lane = threadIdx.x & 31;
+  const long nwarps = (long)gridDim.x * (blockDim.x >> 5);
+  const long total = tokens * heads;
+  for (long item = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); item < total; item += nwarps) {
+    const long tok = item / heads;
+    const int head = (int)(item % heads);
+    const __nv_bfloat16* xp = x + tok * stride_tok_x + (long)head * D + lane * E;
+    float v[E];
+#pragma unroll
+    for (int j = 0; j < E; ++j) v[j] = __bfloat162float(xp[j]);
+    const bool upper = lane >= 16;
+    const int half_idx = (lane & 15) * E;  // index into cos/sin of my first element
+    float c[E], s[E];
+#pragma unroll
+    for (int j = 0; j < E; ++j) { c[j] = cs[tok * (D / 2) + half_idx + j]; s[j] = sn[tok * (D / 2) + half_idx + j]; }
+    if (!BWD) {
+      float r = 1.f;
+      if (w) {
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < E; ++j) ss += v[j] * v[j];
+        ss = warp_sum(ss);
+        r = rsqrtf(ss / D + eps);
+        if (lane == 0 && rstd_io) rstd_io[item] = r;
+#pragma unroll
+        for (int j = 0; j < E; ++j) v[j] = v[j] * r * w[lane * E + j];
+      }
+      __nv_bfloat16* yp = y + tok * stride_tok_y + (long)head * D + lane * E;
+#pragma unroll
+      for (int j = 0; j < E; ++j) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
+        // lower half: a*c - b*s ; upper half: a*s + b*c  (a = lower, b = upper element)
+        const float out = upper ? (other * s[j] + v[j] * c[j]) : (v[j] * c[j] - other * s[j]);
+        yp[j] = __float2bfloat16(out);
+      }
+    } else {
+      // dy -> d(normed) by the inverse rotation, then RMSNorm backward per head
+      const __nv_bfloat16* gp = dy + tok * stride_tok_y + (long)head * D + lane * E;
+      float g[E];
+#pragma unroll
+      for (int j = 0; j < E; ++j) g[j] = __bfloat162float(gp[j]);
+#pragma unroll
+      for (int j = 0; j < E; ++j) {
+        const float other = __shfl_xor_sync(0xffffffffu, g[j], 16);
+        // y_lo = a c - b s, y_hi = a s + b c  =>  da = g_lo c + g_hi s, db = -g_lo s + g_hi c
+        g[j] = upper ? (-other * s[j] + g[j] * c[j]) : (g[j] * c[j] + other * s[j]);
+      }
+      __nv_bfloat16* dxp = y + tok * stride_tok_x + (long)head * D + lane * E;  // y doubles as dx
+      if (w) {
+        const float r = rstd_io[item];
+        float dot = 0.f;
+#pragma unroll
+        for (int j = 0; j < E; ++j) dot += g[j] * w[lane * E + j] * v[j];
+        dot = warp_sum(dot);
+        const float cc = dot * r * r * r / D;
+#pragma unroll
+        for (int j = 0; j < E; ++j) {
+          atomicAdd(&dw_part[lane * E + j], g[j] * v[j] * r);
+          dxp[j] = __float2bfloat16(r * w[lane * E + j] * g[j] - v[j] * cc);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < E; ++j) dxp[j] = __float2bfloat16(g[j]);
+      }
+    }
+  }
+  if (BWD && dw) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < D; i += blockDim.x) atomicAdd(&dw[i], dw_part[i]);
+  }
+}
+
+// ---------------------------------------------------------------- gated activations
+__device__ __forceinline__ float act_fwd(float g, int kind) {
+  if (kind == ACT_SWISH) return g / (1.f + __expf(-g));
+  if (kind == ACT_QUICK_GELU) return g / (1.f + __expf(-1.702f * g));
+  if (kind == ACT_GELU_TANH) {
+    const float u = 0.7978845608f * (g + 0.044715f * g * g * g);
+    return 0.5f * g * (1.f + tanhf(u));
+  }
+  if (kind == ACT_RELU2) { const float r = fmaxf(g, 0.f); return r * r; }
+  return g;
+}
+__device__ __forceinline__ float act_grad(float g, int kind) {
+  if (kind == ACT_SWISH) { const float s = 1.f / (1.f + __expf(-g)); return s * (1.f + g * (1.f - s)); }
+  if (kind == ACT_QUICK_GELU) { const float s = 1.f / (1.f + __expf(-1.702f * g)); return s * (1.f + 1.702f * g * (1.f - s)); }
+  if (kind == ACT_GELU_TANH) {
+    const float u = 0.7978845608f * (g + 0.044715f * g * g * g);
+    const float t = tanhf(u);
+    return 0.5f * (1.f + t) + 0.5f * g * (1.f - t * t) * 0.7978845608f * (1.f + 3.f * 0.044715f * g * g);
+  }
+  if (kind == ACT_RELU2) return 2.f * fmaxf(g, 0.f);
+  return 1.f;
+}
+
+// h: [rows, 2f] (gate columns [0,f), up columns [f,2f)); out: [rows, f].
+// limit > 0 clamps gate from above and up to [-limit, limit] (gpt-oss); up_offset is
+// added to up after the clamp. Optional row scale (router weight) multiplies the output.
+__global__ void glu_fwd_kernel(const __nv_bfloat16* __restrict__ h, __nv_bfloat16* __restrict__ out,
+                               const float* __restrict__ row_scale, long rows, int f, int kind,
+                               float limit, float up_offset) {
+  const long total = rows * (long)(f / 8);
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long row = i / (f / 8);
+    const int c8 = (int)(i % (f / 8));
+    const uint4 gv = *reinterpret_cast<const uint4*>(h + row * 2 * f + c8 * 8);
+    const uint4 uv = *reinterpret_cast<const uint4*>(h + row * 2 * f + f + c8 * 8);
+    const float rs = row_scale ? row_scale[row] : 1.f;
+    uint4 o; uint32_t* ou = &o.x; const uint32_t* gu = &gv.x; const uint32_t* uu = &uv.x;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 g = unpack_bf16(gu[j]), u = unpack_bf16(uu[j]);
+      if (limit > 0.f) {
+        g.x = fminf(g.x, limit); g.y = fminf(g.y, limit);
+        u.x = fminf(fmaxf(u.x, -limit), limit); u.y = fminf(fmaxf(u.y, -limit), limit);
+      }
+      ou[j] = pack_bf16(act_fwd(g.x, kind) * (u.x + up_offset) * rs, act_fwd(g.y, kind) * (u.y + up_offset) * rs);
+    }
+    *reinterpret_cast<uint4*>(out + row * f + c8 * 8) = o;
+  }
+}
+
+// dh: [rows, 2f] from dout [rows, f]; with row_scale also emits d(row_scale) [rows]
+// (accumulated with atomics) = sum_cols dout * act(g) * (u + off).
+__global__ void glu_bwd_kernel(const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ dout,
+                               __nv_bfloat16* __restrict__ dh, const float* __restrict__ row_scale,
+                               float* __restrict__ d_row_scale, long rows, int f, int kind,
+                               float limit, float up_offset) {
+  const long total = rows * (long)(f / 8);
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long row = i / (f / 8);
+    const int c8 = (int)(i % (f / 8));
+    const uint4 gv = *reinterpret_cast<const uint4*>(h + row * 2 * f + c8 * 8);
+    const uint4 uv = *reinterpret_cast<const uint4*>(h + row * 2 * f + f + c8 * 8);
+    const uint4 dv = *reinterpret_cast<const uint4*>(dout + row * f + c8 * 8);
+    const float rs = row_scale ? row_scale[row] : 1.f;
+    uint4 og, ou4; uint32_t* ogu = &og.x; uint32_t* ouu = &ou4.x;
+    const uint32_t* gu = &gv.x; const uint32_t* uu = &uv.x; const uint32_t* du = &dv.x;
+    float ds = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 g = unpack_bf16(gu[j]), u = unpack_bf16(uu[j]), d = unpack_bf16(du[j]);
+      float gx[2] = {g.x, g.y}, ux[2] = {u.x, u.y}, dx[2] = {d.x, d.y}, rg[2], ru[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        bool g_pass = true, u_pass = true;
+        float gg = gx[e], uu_ = ux[e];
+        if (limit > 0.f) {
+          if (gg > limit) { gg = limit; g_pass = false; }
+          if (uu_ > limit) { uu_ = limit; u_pass = false; }
+          if (uu_ < -limit) { uu_ = -limit; u_pass = false; }
+        }
+        const float a = act_fwd(gg, kind);
+        ds += dx[e] * a * (uu_ + up_offset);
+        const float dsc = dx[e] * rs;
+        rg[e] = g_pass ? dsc * (uu_ + up_offset) * act_grad(gg, kind) : 0.f;
+        ru[e] = u_pass ? dsc * a : 0.f;
+      }
+      ogu[j] = pack_bf16(rg[0], rg[1]);
+      ouu[j] = pack_bf16(ru[0], ru[1]);
+    }
+    *reinterpret_cast<uint4*>(dh + row * 2 * f + c8 * 8) = og;
+    *reinterpret_cast<uint4*>(dh + row * 2 * f + f + c8 * 8) = ou4;
+    if (d_row_scale) atomicAdd(&d_row_scale[row], ds);
+  }
+}
+
+// ---------------------------------------------------------------- MXFP8 quantiser
+// E8M0 byte of 2^ceil(log2(amax / 448)), from the fp32 bit pattern (no log).
+__device__ __forceinline__ uint8_t e8m0_of(float amax) {
+  const float ratio = amax * (1.f / 448.f);
+  uint32_t bits = __float_as_uint(ratio);
+  int e = (int)((bits >> 23) & 0xff);
+  const uint32_t mant = bits & 0x7fffffu;
+  if (e == 0) return 0;            // zero / denormal ratio -> smallest scale (2^-127)
+  if (mant != 0) e += 1;           // round the exponent up
+  return (uint8_t)min(e, 254);
+}
+__device__ __forceinline__ float e8m0_inv(uint8_t e) {
+  // 1 / 2^(e-127) = 2^(127-e); e in [0,254] -> exponent field 254 - e (0 -> denormal ok)
+  const int ef = 254 - (int)e;
+  return ef > 0 ? __uint_as_float((uint32_t)ef << 23) : __uint_as_float(0x00400000u);
+}
+// byte offset of scale (row i, scale column j) in the tensor-core tile layout
+__device__ __forceinline__ size_t sf_offset(long i, int j, int sf_cols_padded) {
+  const long rb = i >> 7; const int ri = (int)(i & 127);
+  const int cb = j >> 2, cj = j & 3;
+  return ((size_t)rb * (sf_cols_padded >> 2) + cb) * 512 + (ri & 31) * 16 + (ri >> 5) * 4 + cj;
+}
+
+// Tile: 32 rows x 128 columns per block of 128 threads. Optional row gather
+// (`row_index[r]` = source row of output row r, negative = zero row) fuses the MoE
+// permute into the quantiser.
+//   q_row [R, C] e4m3, sf_row tiles over (R, C/32);  q_col [C, R_pad] e4m3 (R_pad = ld_col),
+//   sf_col tiles over (C, R_pad/32).
+__global__ void quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long ld_x,
+                                   const int* __restrict__ row_index,
+                                   uint8_t* __restrict__ q_row, uint8_t* __restrict__ sf_row,
+                                   uint8_t* __restrict__ q_col, uint8_t* __restrict__ sf_col,
+                                   long rows, int cols, long ld_col) {
+  __shared__ float tile[32][129];
+  const long r0 = (long)blockIdx.y * 32;
+  const int c0 = blockIdx.x * 128;
+  // load: 32 rows x 128 cols, 16 threads per row (8 elements each), 8 rows per pass
+  for (int pass = 0; pass < 4; ++pass) {
+    const int rr = pass * 8 + (threadIdx.x >> 4);
+    const int cc = (threadIdx.x & 15) * 8;
+    const long r = r0 + rr;
+    long src = r;
+    if (row_index && r < rows) src = row_index[r];
+    float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (r < rows && src >= 0 && c0 + cc < cols) {
+      const uint4 v = *reinterpret_cast<const uint4*>(x + src * ld_x + c0 + cc);
+      float2 t;
+      t = unpack_bf16(v.x); f[0] = t.x; f[1] = t.y;
+      t = unpack_bf16(v.y); f[2] = t.x; f[3] = t.y;
+      t = unpack_bf16(v.z); f[4] = t.x; f[5] = t.y;
+      t = unpack_bf16(v.w); f[6] = t.x; f[7] = t.y;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) tile[rr][cc + j] = f[j];
+  }
+  __syncthreads();
+  const int sf_cols_row = ((cols / 32) + 3) & ~3;
+  if (q_row) {
+    // thread -> (row = tid / 4, 32-column block = tid % 4)
+    const int rr = threadIdx.x >> 2, cb = threadIdx.x & 3;
+    const long r = r0 + rr;
+    if (r < rows && c0 + cb * 32 < cols) {
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(tile[rr][cb * 32 + j]));
+      const uint8_t e = e8m0_of(amax);
+      const float inv = e8m0_inv(e);
+      uint32_t packed[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float a = tile[rr][cb * 32 + 4 * j] * inv, b = tile[rr][cb * 32 + 4 * j + 1] * inv;
+        const float c = tile[rr][cb * 32 + 4 * j + 2] * inv, d = tile[rr][cb * 32 + 4 * j + 3] * inv;
+        const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+        const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+        packed[j] = (uint32_t)lo | ((uint32_t)hi << 16);
+      }
+      uint4* dst = reinterpret_cast<uint4*>(q_row + r * cols + c0 + cb * 32);
+      dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+      sf_row[sf_offset(r, (c0 >> 5) + cb, sf_cols_row)] = e;
+    }
+  }
+  if (q_col) {
+    // thread -> column; 32 rows of this tile form one scale block of the transposed copy
+    const int cc = threadIdx.x;
+    const int c = c0 + cc;
+    if (c < cols) {
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(tile[j][cc]));
+      const uint8_t e = e8m0_of(amax);
+      const float inv = e8m0_inv(e);
+      uint32_t packed[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(tile[4 * j][cc] * inv, tile[4 * j + 1][cc] * inv), __NV_SATFINITE, __NV_E4M3);
+        const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(tile[4 * j + 2][cc] * inv, tile[4 * j + 3][cc] * inv), __NV_SATFINITE, __NV_E4M3);
+        packed[j] = (uint32_t)lo | ((uint32_t)hi << 16);
+      }
+      uint4* dst = reinterpret_cast<uint4*>(q_col + (size_t)c * ld_col + r0);
+      dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+      const int sf_cols_col = (int)(((ld_col / 32) + 3) & ~3);
+      sf_col[sf_offset(c, (int)(r0 >> 5), sf_cols_col)] = e;
+    }
+  }
+}
+
+// ---------------------------------------------------------------- cross-entropy
+// One block per row of a logits chunk [rows, vocab] (bf16). Writes per-row loss and
+// logZ (fp32) and overwrites the logits with dlogits = (softmax - onehot) * grad_scale
+// * mask (+ z-loss term), ready for the dX / dW GEMMs.
+__global__ void ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, const int* __restrict__ targets,
+                                  const float* __restrict__ mask, float* __restrict__ loss,
+                                  float* __restrict__ logz_out, int vocab, long ld, float grad_scale,
+                                  float z_weight, float softcap) {
+  const long row = blockIdx.x;
+  __nv_bfloat16* lr = logits + row * ld;
+  __shared__ float red[32];
+  __shared__ float bcast[2];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  float mx = -INFINITY;
+  for (int i = threadIdx.x * 8; i < vocab; i += blockDim.x * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(lr + i);
+    const uint32_t* u = &v.x;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 t = unpack_bf16(u[j]);
+      if (softcap > 0.f) { t.x = softcap * tanhf(t.x / softcap); t.y = softcap * tanhf(t.y / softcap); }
+      mx = fmaxf(mx, fmaxf(t.x, t.y));
+    }
+  }
+  mx = warp_max(mx);
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  if (warp == 0) { float v = lane < nw ? red[lane] : -INFINITY; v = warp_max(v); if (lane == 0) bcast[0] = v; }
+  __syncthreads();
+  mx = bcast[0];
+  float sum = 0.f;
+  for (int i = threadIdx.x * 8; i < vocab; i += blockDim.x * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(lr + i);
+    const uint32_t* u = &v.x;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 t = unpack_bf16(u[j]);
+      if (softcap > 0.f) { t.x = softcap * tanhf(t.x / softcap); t.y = softcap * tanhf(t.y / softcap); }
+      sum += __expf(t.x - mx) + __expf(t.y - mx);
+    }
+  }
+  sum = warp_sum(sum);
+  __syncthreads();
+  if (lane == 0) red[warp] = sum;
+  __syncthreads();
+  if (warp == 0) { float v = lane < nw ? red[lane] : 0.f; v = warp_sum(v); if (lane == 0) bcast[1] = v; }
+  __syncthreads();
+  sum = bcast[1];
+  const float logz = mx + logf(sum);
+  const int tgt = targets[row];
+  const float m = mask ? mask[row] : 1.f;
+  if (threadIdx.x == 0) {
+    float t = __bfloat162float(lr[tgt]);
+    if (softcap > 0.f) t = softcap * tanhf(t / softcap);
+    loss[row] = (logz - t + z_weight * logz * logz) * m;
+    if (logz_out) logz_out[row] = logz;
+  }
+  __syncthreads();  // the target logit is read before it is overwritten below
+  const float gs = grad_scale * m;
+  const float zfac = 1.f + 2.f * z_weight * logz;
+  const float inv = 1.f / sum;
+  for (int i = threadIdx.x * 8; i < vocab; i += blockDim.x * 8) {
+    uint4 v = *reinterpret_cast<const uint4*>(lr + i);
+    uint32_t* u = &v.x;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 t = unpack_bf16(u[j]);
+      float dcap0 = 1.f, dcap1 = 1.f;
+      if (softcap > 0.f) {
+        const float a = tanhf(t.x / softcap), b = tanhf(t.y / softcap);
+        t.x = softcap * a; t.y = softcap * b; dcap0 = 1.f - a * a; dcap1 = 1.f - b * b;
+      }
+      float p0 = __expf(t.x - mx) * inv * zfac, p1 = __expf(t.y - mx) * inv * zfac;
+      if (i + 2 * j == tgt) p0 -= 1.f;
+      if (i + 2 * j + 1 == tgt) p1 -= 1.f;
+      u[j] = pack_bf16(p0 * gs * dcap0, p1 * gs * dcap1);
+    }
+    *reinterpret_cast<uint4*>(lr + i) = v;
+  }
+}
+
+// ---------------------------------------------------------------- AdamW over flat buffers
+// p: fp32 master (or bf16 master when MASTER_BF16), g: bf16 or fp32 grads, optional
+// bf16 shadow copy of the updated weights. Moments: fp32, bf16, or 8-bit block-scaled
+// (e4m3 values with one E8M0 scale per 32 elements; the second moment is stored as its
+// square root so that its dynamic range fits).
+template <typename PT, typename GT, int MOM>
+__global__ void adamw_kernel(PT* __restrict__ p, const GT* __restrict__ g, void* __restrict__ m_,
+                             void* __restrict__ v_, uint8_t* __restrict__ m_sf, uint8_t* __restrict__ v_sf,
+                             __nv_bfloat16* __restrict__ shadow, long n, float lr, float b1, float b2,
+                             float eps, float wd, float bc1, float bc2, const float* __restrict__ grad_scale_ptr,
+                             float grad_scale_const) {
+  const float gscale = grad_scale_ptr ? *grad_scale_ptr * grad_scale_const : grad_scale_const;
+  // each thread owns 32 consecutive elements (one 8-bit scale block)
+  const long blocks = (n + 31) / 32;
+  for (long b = (long)blockIdx.x * blockDim.x + threadIdx.x; b < blocks; b += (long)gridDim.x * blockDim.x) {
+    const long i0 = b * 32;
+    const int cnt = (int)min(32L, n - i0);
+    float pm[32], pv[32];
+    if (MOM == MOM_F32) {
+      for (int j = 0; j < cnt; ++j) { pm[j] = reinterpret_cast<float*>(m_)[i0 + j]; pv[j] = reinterpret_cast<float*>(v_)[i0 + j]; }
+    } else if (MOM == MOM_BF16) {
+      for (int j = 0; j < cnt; ++j) {
+        pm[j] = __bfloat162float(reinterpret_cast<__nv_bfloat16*>(m_)[i0 + j]);
+        pv[j] = __bfloat162float(reinterpret_cast<__nv_bfloat16*>(v_)[i0 + j]);
+      }
+    } else {
+      const float sm = __uint_as_float((uint32_t)max((int)m_sf[b], 1) << 23);
+      const float sv = __uint_as_float((uint32_t)max((int)v_sf[b], 1) << 23);
+      for (int j = 0; j < cnt; ++j) {
+        const __half_raw hm = __nv_cvt_fp8_to_halfraw(reinterpret_cast<uint8_t*>(m_)[i0 + j], __NV_E4M3);
+        const __half_raw hv = __nv_cvt_fp8_to_halfraw(reinterpret_cast<uint8_t*>(v_)[i0 + j], __NV_E4M3);
+        pm[j] = __half2float(__half(hm)) * sm;
+        const float rv = __half2float(__half(hv)) * sv;
+        pv[j] = rv * rv;
+      }
+    }
+    float am = 0.f, av = 0.f;
+    for (int j = 0; j < cnt; ++j) {
+      const float gr = (float)g[i0 + j] * gscale;
+      pm[j] = b1 * pm[j] + (1.f - b1) * gr;
+      pv[j] = b2 * pv[j] + (1.f - b2) * gr * gr;
+      const float w = (float)p[i0 + j];
+      const float upd = (pm[j] / bc1) / (sqrtf(pv[j] / bc2) + eps) + wd * w;
+      const float nw = w - lr * upd;
+      p[i0 + j] = (PT)nw;
+      if (shadow) shadow[i0 + j] = __float2bfloat16(nw);
+      am = fmaxf(am, fabsf(pm[j]));
+      av = fmaxf(av, sqrtf(pv[j]));
+    }
+    if (MOM == MOM_F32) {
+      for (int j = 0; j < cnt; ++j) { reinterpret_cast<float*>(m_)[i0 + j] = pm[j]; reinterpret_cast<float*>(v_)[i0 + j] = pv[j]; }
+    } else if (MOM == MOM_BF16) {
+      for (int j = 0; j < cnt; ++j) {
+        reinterpret_cast<__nv_bfloat16*>(m_)[i0 + j] = __float2bfloat16(pm[j]);
+        reinterpret_cast<__nv_bfloat16*>(v_)[i0 + j] = __float2bfloat16(pv[j]);
+      }
+    } else {
+      const uint8_t em = (uint8_t)max((int)e8m0_of(am), 1), ev = (uint8_t)max((int)e8m0_of(av), 1);
+      const float im = e8m0_inv(em), iv = e8m0_inv(ev);
+      m_sf[b] = em; v_sf[b] = ev;
+      for (int j = 0; j < cnt; ++j) {
+        reinterpret_cast<uint8_t*>(m_)[i0 + j] = __nv_cvt_float_to_fp8(pm[j] * im, __NV_SATFINITE, __NV_E4M3);
+        reinterpret_cast<uint8_t*>(v_)[i0 + j] = __nv_cvt_float_to_fp8(sqrtf(pv[j]) * iv, __NV_SATFINITE, __NV_E4M3);
+      }
+    }
+  }
+}
+
+// sum of squares of a flat buffer into out[0] (fp32 atomics), for the global grad norm
+template <typename GT>
+__global__ void sumsq_kernel(const GT* __restrict__ g, long n, float* __restrict__ out) {
+  float s = 0.f;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    const float v = (float)g[i];
+    s += v * v;
+  }
+  s = warp_sum(s);
+  __shared__ float red[32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) red[warp] = s;
+  __syncthreads();
+  if (warp == 0) {
+    float v = lane < (blockDim.x >> 5) ? red[lane] : 0.f;
+    v = warp_sum(v);
+    if (lane == 0) atomicAdd(out, v);
+  }
+}
+
+// ---------------------------------------------------------------- MoE gather / combine
+// out[r] = x[index[r]] (zero row when index[r] < 0); rows of d bf16, d % 8 == 0.
+__global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ index,
+                                   __nv_bfloat16* __restrict__ out, long rows, int d) {
+  const int vec = d / 8;
+  const long total = rows * vec;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long r = i / vec; const int c = (int)(i % vec);
+    const int src = index[r];
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (src >= 0) v = reinterpret_cast<const uint4*>(x + (long)src * d)[c];
+    reinterpret_cast<uint4*>(out + r * d)[c] = v;
+  }
+}
+// out[t] = sum_k w[t,k] * y[pos[t,k]]  (pos < 0 = dropped pick); w may be null (= 1).
+__global__ void combine_rows_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ pos,
+                                    const float* __restrict__ w, __nv_bfloat16* __restrict__ out,
+                                    long tokens, int k, int d) {
+  const int vec = d / 8;
+  const long total = tokens * vec;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long t = i / vec; const int c = (int)(i % vec);
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int j = 0; j < k; ++j) {
+      const int r = pos[t * k + j];
+      if (r < 0) continue;
+      const float ww = w ? w[t * k + j] : 1.f;
+      const uint4 v = reinterpret_cast<const uint4*>(y + (long)r * d)[c];
+      const uint32_t* u = &v.x;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) { const float2 f = unpack_bf16(u[q]); acc[2 * q] += ww * f.x; acc[2 * q + 1] += ww * f.y; }
+    }
+    uint4 o;
+    o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);
+    o.z = pack_bf16(acc[4], acc[5]); o.w = pack_bf16(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(out + t * d)[c] = o;
+  }
+}
+
+// ---------------------------------------------------------------- launchers
+static inline int grid_for(long work, int per_block, int cap = 148 * 16) {
+  long g = (work + per_block - 1) / per_block;
+  return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+void rmsnorm_fwd(const void* x, const float* w, void* y, float* rstd, long rows, int d, float eps, cudaStream_t s) {
+  const int wpb = 8;
+  rmsnorm_fwd_kernel<8><<<(int)((rows + wpb - 1) / wpb), wpb * 32, 0, s>>>(
+      (const __nv_bfloat16*)x, w, (__nv_bfloat16*)y, rstd, (int)rows, d, eps);
+}
+void rmsnorm_bwd(const void* x, const float* w, const void* dy, const float* rstd, void* dx, float* dw, long rows, int d, cudaStream_t s) {
+  const int wpb = 8;
+  int grid = (int)min((rows + wpb - 1) / wpb, 148L * 4);
+  rmsnorm_bwd_kernel<<<grid, wpb * 32, d * sizeof(float), s>>>(
+      (const __nv_bfloat16*)x, w, (const __nv_bfloat16*)dy, rstd, (__nv_bfloat16*)dx, dw, (int)rows, d);
+}
+const char* norm_rope(bool bwd, const void* x, const float* w, const float* cs, const float* sn, void* y,
+                      float* rstd, const void* dy, float* dw, long tokens, int heads, int D,
+                      long stride_x, long stride_y, float eps, cudaStream_t s) {
+  const int wpb = 8;
+  const long items = tokens * heads;
+  int grid = (int)min((items + wpb - 1) / wpb, 148L * 8);
+#define NR_CASE(D_) \
+  if (D == D_) { \
+    if (bwd) norm_rope_kernel<D_, true><<<grid, wpb * 32, 0, s>>>((const __nv_bfloat16*)x, w, cs, sn, (__nv_bfloat16*)y, rstd, (const __nv_bfloat16*)dy, dw, tokens, heads, stride_x, stride_y, eps); \
+    else     norm_rope_kernel<D_, false><<<grid, wpb * 32, 0, s>>>((const __nv_bfloat16*)x, w, cs, sn, (__nv_bfloat16*)y, rstd, nullptr, nullptr, tokens, heads, stride_x, stride_y, eps); \
+    return nullptr; }
+  NR_CASE(64) NR_CASE(128) NR_CASE(256)
+#undef NR_CASE
+  return "norm_rope: head_dim must be 64, 128 or 256";
+}
+void glu_fwd(const void* h, void* out, const float* row_scale, long rows, int f, int kind, float limit, float up_offset, cudaStream_t s) {
+  glu_fwd_kernel<<<grid_for(rows * (f / 8), 256), 256, 0, s>>>((const __nv_bfloat16*)h, (__nv_bfloat16*)out, row_scale, rows, f, kind, limit, up_offset);
+}
+void glu_bwd(const void* h, const void* dout, void* dh, const float* row_scale, float* d_row_scale, long rows, int f, int kind, float limit, float up_offset, cudaStream_t s) {
+  glu_bwd_kernel<<<grid_for(rows * (f / 8), 256), 256, 0, s>>>((const __nv_bfloat16*)h, (const __nv_bfloat16*)dout, (__nv_bfloat16*)dh, row_scale, d_row_scale, rows, f, kind, limit, up_offset);
+}
+void quant_mxfp8(const void* x, long ld_x, const int* row_index, uint8_t* q_row, uint8_t* sf_row, uint8_t* q_col, uint8_t* sf_col, long rows, int cols, long ld_col, cudaStream_t s) {
+  dim3 grid((cols + 127) / 128, (unsigned)((rows + 31) / 32));
+  quant_mxfp8_kernel<<<grid, 128, 0, s>>>((const __nv_bfloat16*)x, ld_x, row_index, q_row, sf_row, q_col, sf_col, rows, cols, ld_col);
+}
+void ce_fwd_bwd(void* logits, const int* targets, const float* mask, float* loss, float* logz, long rows, int vocab, long ld, float grad_scale, float z_weight, float softcap, cudaStream_t s) {
+  ce_fwd_bwd_kernel<<<(unsigned)rows, 512, 0, s>>>((__nv_bfloat16*)logits, targets, mask, loss, logz, vocab, ld, grad_scale, z_weight, softcap);
+}
+const char* adamw(void* p, bool p_bf16, const void* g, bool g_bf16, void* m, void* v, uint8_t* m_sf, uint8_t* v_sf, int mom,
+                  void* shadow, long n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
+                  const float* gscale_ptr, float gscale, cudaStream_t s) {
+  const int grid = grid_for((n + 31) / 32, 128);
+#define AW(PT, GT, MOM_) adamw_kernel<PT, GT, MOM_><<<grid, 128, 0, s>>>((PT*)p, (const GT*)g, m, v, m_sf, v_sf, (__nv_bfloat16*)shadow, n, lr, b1, b2, eps, wd, bc1, bc2, gscale_ptr, gscale)
+#define AW_MOM(PT, GT) { if (mom == MOM_F32) AW(PT, GT, MOM_F32); else if (mom == MOM_BF16) AW(PT, GT, MOM_BF16); else AW(PT, GT, MOM_FP8); return nullptr; }
+  if (!p_bf16 && g_bf16) AW_MOM(float, __nv_bfloat16)
+  if (!p_bf16 && !g_bf16) AW_MOM(float, float)
+  if (p_bf16 && g_bf16) AW_MOM(__nv_bfloat16, __nv_bfloat16)
+  if (p_bf16 && !g_bf16) AW_MOM(__nv_bfloat16, float)
+#undef AW_MOM
+#undef AW
+  return "adamw: unsupported dtypes";
+}
+void sumsq(const void* g, bool bf16, long n, float* out, cudaStream_t s) {
+  const int grid = grid_for(n, 256 * 8, 148 * 8);
+  if (bf16) sumsq_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)g, n, out);
+  else sumsq_kernel<float><<<grid, 256, 0, s>>>((const float*)g, n, out);
+}
+void gather_rows(const void* x, const int* index, void* out, long rows, int d, cudaStream_t s) {
+  gather_rows_kernel<<<grid_for(rows * (d / 8), 256), 256, 0, s>>>((const __nv_bfloat16*)x, index, (__nv_bfloat16*)out, rows, d);
+}
+void combine_rows(const void* y, const int* pos, const float* w, void* out, long tokens, int k, int d, cudaStream_t s) {
+  combine_rows_kernel<<<grid_for(tokens * (d / 8), 256), 256, 0, s>>>((const __nv_bfloat16*)y, pos, w, (__nv_bfloat16*)out, tokens, k, d);
+}
+
+}  // namespace bux

@@ -1,0 +1,254 @@
+"""Thin Python wrappers over ``torch.ops.bux_b200``: allocate outputs, pass shapes.
+
+No autograd here (see `functional`). Every function takes CUDA tensors and raises if
+the native library is missing: the GPU path never falls back to eager PyTorch.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _build
+
+KIND_BF16, KIND_MXFP8 = 0, 1
+MODE_DENSE, MODE_GROUPED_ROWS, MODE_GROUPED_K = 0, 1, 2
+OUT_BF16, OUT_F32, OUT_F32_ACC = 0, 1, 2
+ACT_KINDS = {"swish": 0, "quick_gelu": 1, "gelu_tanh": 2, "relu2": 3}
+
+_status: dict = {}
+launches = 0  # kernels launched through this module (bench.py reports it)
+
+
+def ops():
+    _build.load(required=True)
+    return torch.ops.bux_b200
+
+
+def _count(n: int = 1) -> None:
+    global launches
+    launches += n
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device int32[2] the kernels' bounded waits report into."""
+    key = torch.device(device).index or 0
+    if key not in _status:
+        _status[key] = torch.zeros(2, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status(device, what: str = "kernel") -> None:
+    """Raise if any bounded wait of a kernel on `device` ran out (synchronises)."""
+    st = status_word(device)
+    code, count = st.tolist()
+    if code:
+        st.zero_()
+        raise RuntimeError(
+            f"{what}: a bounded device wait ran out (kernel {code >> 24}, site {(code >> 16) & 0xff}, "
+            f"block {code & 0xffff}; {count} waits in total)")
+
+
+# ------------------------------------------------------------------ GEMM
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+              out: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16,
+              accumulate: bool = False, bn: int = 256, sms: int = 0) -> torch.Tensor:
+    """C = A · B^T. A is [M,K] (or stored [K,M] with a_mn), B is [N,K] (or [K,N] with b_mn)."""
+    m, k = (a.shape[1], a.shape[0]) if a_mn else a.shape
+    n = b.shape[1] if b_mn else b.shape[0]
+    if out is None:
+        out = torch.empty(m, n, dtype=out_dtype, device=a.device)
+    kind = OUT_BF16 if out.dtype == torch.bfloat16 else (OUT_F32_ACC if accumulate else OUT_F32)
+    ops().gemm(a, b, out, None, None, None, status_word(a.device), KIND_BF16, MODE_DENSE, m, n, k, k, 1,
+               a_mn, b_mn, kind, bn, sms)
+    _count()
+    return out
+
+
+def gemm_mxfp8(aq, asf, bq, bsf, m: int, n: int, k: int, *, out=None, out_dtype=torch.bfloat16,
+               accumulate: bool = False, bn: int = 128, sms: int = 0) -> torch.Tensor:
+    """C[m,n] = dequant(A)[m,k] · dequant(B)[n,k]^T; scales in the tiled layout."""
+    if out is None:
+        out = torch.empty(m, n, dtype=out_dtype, device=aq.device)
+    kind = OUT_BF16 if out.dtype == torch.bfloat16 else (OUT_F32_ACC if accumulate else OUT_F32)
+    ops().gemm(aq.view(torch.uint8), bq.view(torch.uint8), out, asf, bsf, None, status_word(aq.device),
+               KIND_MXFP8, MODE_DENSE, m, n, k, k, 1, False, False, kind, bn, sms)
+    _count()
+    return out
+
+
+def grouped_gemm(a, b, offsets: torch.Tensor, n: int, k: int, *, kind: int = KIND_BF16, asf=None,
+                 bsf=None, b_mn: bool = False, out=None, bn: int = 128, sms: int = 0) -> torch.Tensor:
+    """Rows of `a` ([R,k], sorted by group; offsets int32[G+1]) times group g's weight.
+    b: [G*n, k] (K-major) or [G*k, n] (b_mn). Returns [R, n] bf16."""
+    groups = offsets.numel() - 1
+    if out is None:
+        out = torch.empty(a.shape[0], n, dtype=torch.bfloat16, device=a.device)
+    if kind == KIND_MXFP8:
+        a, b = a.view(torch.uint8), b.view(torch.uint8)
+    ops().gemm(a, b, out, asf, bsf, offsets, status_word(a.device), kind, MODE_GROUPED_ROWS,
+               a.shape[0], n, k, k, groups, False, b_mn, OUT_BF16, bn, sms)
+    _count()
+    return out
+
+
+def grouped_gemm_k(a, b, offsets: torch.Tensor, m: int, n: int, *, kind: int = KIND_BF16, asf=None,
+                   bsf=None, a_mn: bool = False, b_mn: bool = False, out=None,
+                   accumulate: bool = False, bn: int = 128, sms: int = 0) -> torch.Tensor:
+    """out[g] (+)= A[:, kg] · B[:, kg]^T for each group's contraction range kg (weight
+    gradients of grouped experts). K-major: a [m, Ktot], b [n, Ktot]; MN-major: a [Ktot, m],
+    b [Ktot, n]. Returns fp32 [G, m, n]."""
+    groups = offsets.numel() - 1
+    ktot = a.shape[0] if a_mn else a.shape[1]
+    if out is None:
+        out = torch.empty(groups, m, n, dtype=torch.float32, device=a.device)
+        accumulate = False
+    if kind == KIND_MXFP8:
+        a, b = a.view(torch.uint8), b.view(torch.uint8)
+    okind = OUT_BF16 if out.dtype == torch.bfloat16 else (OUT_F32_ACC if accumulate else OUT_F32)
+    ops().gemm(a, b, out, asf, bsf, offsets, status_word(a.device), kind, MODE_GROUPED_K, m, n, ktot,
+               ktot, groups, a_mn, b_mn, okind, bn, sms)
+    _count()
+    return out
+
+
+# ------------------------------------------------------------------ MXFP8 quantiser
+def sf_bytes(rows: int, cols: int) -> int:
+    """Bytes of the tiled scale tensor of a [rows, cols] matrix quantised along cols."""
+    return (-(-rows // 128)) * (-(-(cols // 32) // 4)) * 512
+
+
+def quant_mxfp8(x: torch.Tensor, *, rowwise: bool = True, colwise: bool = False,
+                row_index: Optional[torch.Tensor] = None, rows: Optional[int] = None):
+    """Quantise bf16 x [R, C] along C (rowwise) and/or along R (colwise; a transposed
+    copy [C, R_pad]). With `row_index` (int32[rows]) output row r reads x[row_index[r]]
+    (negative: zeros). Returns (q_row, sf_row, q_col, sf_col); unused ones are None."""
+    x2 = x.reshape(-1, x.shape[-1])
+    c = x2.shape[1]
+    r = rows if rows is not None else (row_index.numel() if row_index is not None else x2.shape[0])
+    dev = x.device
+    q_row = sf_row = q_col = sf_col = None
+    if rowwise:
+        q_row = torch.empty(r, c, dtype=torch.float8_e4m3fn, device=dev)
+        sf_row = torch.full((sf_bytes(r, c),), 127, dtype=torch.uint8, device=dev)
+    r_pad = -(-r // 128) * 128
+    if colwise:
+        q_col = torch.zeros(c, r_pad, dtype=torch.float8_e4m3fn, device=dev)
+        sf_col = torch.full((sf_bytes(c, r_pad),), 127, dtype=torch.uint8, device=dev)
+    ops().quant_mxfp8(x2, row_index, None if q_row is None else q_row.view(torch.uint8), sf_row,
+                      None if q_col is None else q_col.view(torch.uint8), sf_col, r, c, r_pad)
+    _count()
+    return q_row, sf_row, q_col, sf_col
+
+
+# ------------------------------------------------------------------ norms / rope / glu
+def rmsnorm_fwd(x, w, eps: float):
+    y = torch.empty_like(x)
+    rstd = torch.empty(x.numel() // x.shape[-1], dtype=torch.float32, device=x.device)
+    ops().rmsnorm_fwd(x, w, y, rstd, eps)
+    _count()
+    return y, rstd
+
+
+def rmsnorm_bwd(x, w, dy, rstd, need_dw: bool = True):
+    dx = torch.empty_like(x)
+    dw = torch.zeros(x.shape[-1], dtype=torch.float32, device=x.device) if need_dw and w is not None else None
+    ops().rmsnorm_bwd(x, w, dy, rstd, dx, dw)
+    _count()
+    return dx, dw
+
+
+def norm_rope_fwd(x, w, cos, sin, eps: float):
+    """x: [..., T, H, D] contiguous; cos/sin: [tokens, D/2] fp32."""
+    d, h = x.shape[-1], x.shape[-2]
+    tokens = x.numel() // (h * d)
+    y = torch.empty_like(x)
+    rstd = torch.empty(tokens * h, dtype=torch.float32, device=x.device) if w is not None else None
+    ops().norm_rope(False, x, w, cos, sin, y, rstd, None, None, tokens, h, d, h * d, h * d, eps)
+    _count()
+    return y, rstd
+
+
+def norm_rope_bwd(x, w, cos, sin, rstd, dy, eps: float):
+    d, h = x.shape[-1], x.shape[-2]
+    tokens = x.numel() // (h * d)
+    dx = torch.empty_like(x)
+    dw = torch.zeros(d, dtype=torch.float32, device=x.device) if w is not None else None
+    ops().norm_rope(True, x, w, cos, sin, dx, rstd, dy, dw, tokens, h, d, h * d, h * d, eps)
+    _count()
+    return dx, dw
+
+
+def glu_fwd(h, kind: str = "swish", row_scale=None, limit: float = 0.0, up_offset: float = 0.0):
+    out = torch.empty(*h.shape[:-1], h.shape[-1] // 2, dtype=h.dtype, device=h.device)
+    ops().glu_fwd(h, out, row_scale, ACT_KINDS[kind], limit or 0.0, up_offset)
+    _count()
+    return out
+
+
+def glu_bwd(h, dout, kind: str = "swish", row_scale=None, limit: float = 0.0, up_offset: float = 0.0):
+    dh = torch.empty_like(h)
+    drs = torch.zeros_like(row_scale) if row_scale is not None else None
+    ops().glu_bwd(h, dout, dh, row_scale, drs, ACT_KINDS[kind], limit or 0.0, up_offset)
+    _count()
+    return dh, drs
+
+
+# ------------------------------------------------------------------ loss / optimiser / rows
+def ce_fwd_bwd(logits, targets, mask, grad_scale: float, z_weight: float = 0.0, softcap: float = 0.0):
+    """In place: logits become dlogits. Returns per-row loss (fp32)."""
+    loss = torch.empty(logits.shape[0], dtype=torch.float32, device=logits.device)
+    ops().ce_fwd_bwd(logits, targets, mask, loss, None, grad_scale, z_weight, softcap or 0.0)
+    _count()
+    return loss
+
+
+def adamw(p, g, m, v, *, lr, b1, b2, eps, wd, step: int, m_sf=None, v_sf=None, shadow=None,
+          grad_scale: Optional[torch.Tensor] = None, grad_scale_const: float = 1.0) -> None:
+    ops().adamw(p, g, m, v, m_sf, v_sf, shadow, grad_scale, lr, b1, b2, eps, wd,
+                1.0 - b1 ** step, 1.0 - b2 ** step, grad_scale_const)
+    _count()
+
+
+def sumsq(g, out) -> None:
+    ops().sumsq(g, out)
+    _count()
+
+
+def gather_rows(x, index, rows: int):
+    out = torch.empty(rows, x.shape[-1], dtype=x.dtype, device=x.device)
+    ops().gather_rows(x, index, out)
+    _count()
+    return out
+
+
+def combine_rows(y, pos, w, tokens: int):
+    out = torch.empty(tokens, y.shape[-1], dtype=y.dtype, device=y.device)
+    ops().combine_rows(y, pos, w, out)
+    _count()
+    return out
+
+
+# ------------------------------------------------------------------ attention
+def attn_fwd(q, k, v, *, causal=True, window=0, sinks=None, scale=None):
+    b, t, h, d = q.shape
+    o = torch.empty_like(q)
+    lse = torch.empty(b, h, t, dtype=torch.float32, device=q.device)
+    ops().attn_fwd(q, k, v, o, lse, sinks, status_word(q.device), scale if scale is not None else d ** -0.5,
+                   causal, window or 0)
+    _count()
+    return o, lse
+
+
+def attn_bwd(q, k, v, o, do, lse, *, causal=True, window=0, sinks=None, scale=None):
+    b, t, h, d = q.shape
+    dq = torch.zeros(b, t, h, d, dtype=torch.float32, device=q.device)
+    dk = torch.zeros(k.shape, dtype=torch.float32, device=q.device)
+    dv = torch.zeros(v.shape, dtype=torch.float32, device=q.device)
+    delta = torch.empty(b, h, t, dtype=torch.float32, device=q.device)
+    dsinks = torch.zeros_like(sinks) if sinks is not None else None
+    ops().attn_bwd(q, k, v, o, do, lse, dq, dk, dv, delta, sinks, dsinks, status_word(q.device),
+                   scale if scale is not None else d ** -0.5, causal, window or 0)
+    _count(3)
+    return dq, dk, dv, dsinks
