@@ -174,7 +174,7 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
     for (int t = 0; t < n_tiles && ok; ++t) {
       const int s = t & 1;
       const int kv0 = (j_lo + t) * KT;
-      ok = mbar_wait(&s_full[s], (t >> 1) & 1, abort_flag, st, KID_ATTN_FWD, 6);
+      ok = warp_all(mbar_wait(&s_full[s], (t >> 1) & 1, abort_flag, st, KID_ATTN_FWD, 6));
       if (!ok) break;
       tc_fence_after();
       // pass 1: row max
@@ -195,7 +195,7 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
       const float alpha = m == -INFINITY ? 0.f : exp2f(m - m_use);
       // fold the previous tile's P·V into the accumulator (it frees the P buffer too)
       if (t > 0) {
-        ok = mbar_wait(pv_full, (t - 1) & 1, abort_flag, st, KID_ATTN_FWD, 7);
+        ok = warp_all(mbar_wait(pv_full, (t - 1) & 1, abort_flag, st, KID_ATTN_FWD, 7));
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
@@ -246,7 +246,7 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
       mbar_arrive(p_ready);
     }
     if (ok && n_tiles > 0) {
-      ok = mbar_wait(pv_full, (n_tiles - 1) & 1, abort_flag, st, KID_ATTN_FWD, 8);
+      ok = warp_all(mbar_wait(pv_full, (n_tiles - 1) & 1, abort_flag, st, KID_ATTN_FWD, 8));
       if (ok) {
         tc_fence_after();
 #pragma unroll

@@ -105,6 +105,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
   return false;
 }
 
+// Warp-uniform verdict of a wait made by every lane: warp-collective instructions
+// (tcgen05.ld / st) that follow must be reached by all 32 lanes or by none.
+__device__ __forceinline__ bool warp_all(bool v) { return __all_sync(0xffffffffu, v); }
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

@@ -243,7 +243,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
     int acc = 0; uint32_t acc_phase = 0;
     bool ok = true;
     for (TileCoord c = walk.next(); c.valid && ok; c = walk.next()) {
-      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, st, KID_GEMM, 4)) { ok = false; break; }
+      if (!warp_all(mbar_wait(&acc_full[acc], acc_phase, abort_flag, st, KID_GEMM, 4))) { ok = false; break; }
       tc_fence_after();
       const int row = c.m0 + quad * 32 + lane;
       const bool row_ok = row < c.m_end;

@@ -244,11 +244,11 @@ def attn_fwd(q, k, v, *, causal=True, window=0, sinks=None, scale=None):
 def attn_bwd(q, k, v, o, do, lse, *, causal=True, window=0, sinks=None, scale=None):
     b, t, h, d = q.shape
     dq = torch.zeros(b, t, h, d, dtype=torch.float32, device=q.device)
-    dk = torch.zeros(k.shape, dtype=torch.float32, device=q.device)
-    dv = torch.zeros(v.shape, dtype=torch.float32, device=q.device)
+    dk = torch.empty_like(k)
+    dv = torch.empty_like(v)
     delta = torch.empty(b, h, t, dtype=torch.float32, device=q.device)
     dsinks = torch.zeros_like(sinks) if sinks is not None else None
     ops().attn_bwd(q, k, v, o, do, lse, dq, dk, dv, delta, sinks, dsinks, status_word(q.device),
                    scale if scale is not None else d ** -0.5, causal, window or 0)
-    _count(3)
+    _count(2)
     return dq, dk, dv, dsinks

@@ -238,3 +238,26 @@ def test_attention_fwd(cuda, d, h, g, t, window, sinks):
     got, lse = K.attn_fwd(q, k, v, causal=True, window=window, sinks=sk)
     assert rel_err(got, want) < 2e-2
     assert rel_err(lse, want_lse) < 1e-3
+
+
+@pytest.mark.parametrize("d,h,g", [(128, 4, 2), (64, 4, 1)])
+@pytest.mark.parametrize("t,window,sinks", [(256, 0, False), (300, 0, False), (384, 128, True)])
+def test_attention_bwd(cuda, d, h, g, t, window, sinks):
+    from bux_b200.ops import kernels as K
+
+    torch.manual_seed(12)
+    q = torch.randn(2, t, h, d, device=cuda).bfloat16().requires_grad_()
+    k = torch.randn(2, t, g, d, device=cuda).bfloat16().requires_grad_()
+    v = torch.randn(2, t, g, d, device=cuda).bfloat16().requires_grad_()
+    sk = torch.randn(h, device=cuda).requires_grad_() if sinks else None
+    want, _ = ref.attention(q, k, v, causal=True, window=window or None, sinks=sk)
+    do = torch.randn_like(q)
+    want.backward(do)
+    with torch.no_grad():
+        o, lse = K.attn_fwd(q, k, v, causal=True, window=window, sinks=sk)
+        dq, dk, dv, dsk = K.attn_bwd(q, k, v, o, do, lse, causal=True, window=window, sinks=sk)
+    assert rel_err(dv, v.grad) < 3e-2
+    assert rel_err(dk, k.grad) < 3e-2
+    assert rel_err(dq, q.grad) < 3e-2
+    if sinks:
+        assert rel_err(dsk, sk.grad) < 3e-2
