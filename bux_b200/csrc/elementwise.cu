@@ -321,8 +321,17 @@ __global__ void quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long ld_
                                    const int* __restrict__ row_index,
                                    uint8_t* __restrict__ q_row, uint8_t* __restrict__ sf_row,
                                    uint8_t* __restrict__ q_col, uint8_t* __restrict__ sf_col,
-                                   long rows, int cols, long ld_col) {
+                                   long rows, int cols, long ld_col, long x_batch_stride) {
   __shared__ float tile[32][129];
+  if (blockIdx.z > 0) {
+    // batched: matrix z of a stack, every output advanced by its own size
+    const long z = blockIdx.z;
+    const int sfc_row = ((cols / 32) + 3) & ~3;
+    const long sfc_col = ((ld_col / 32) + 3) & ~3L;
+    x += z * x_batch_stride;
+    if (q_row) { q_row += z * rows * cols; sf_row += z * ((rows + 127) / 128) * (sfc_row / 4) * 512; }
+    if (q_col) { q_col += z * (long)cols * ld_col; sf_col += z * ((cols + 127) / 128) * (sfc_col / 4) * 512; }
+  }
   const long r0 = (long)blockIdx.y * 32;
   const int c0 = blockIdx.x * 128;
   // load: 32 rows x 128 cols, 16 threads per row (8 elements each), 8 rows per pass
@@ -605,6 +614,44 @@ __global__ void combine_rows_kernel(const __nv_bfloat16* __restrict__ y, const i
   }
 }
 
+// Backward of the weighted combine, one warp per pick (t, j) with r = pos[t,j]:
+//   dy[r] = w[t,j] * dout[t]     dw[t,j] = <y[r], dout[t]>     (dropped picks: dw = 0)
+__global__ void combine_bwd_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ dout,
+                                   const int* __restrict__ pos, const float* __restrict__ w,
+                                   __nv_bfloat16* __restrict__ dy, float* __restrict__ dw,
+                                   long picks, int k, int d) {
+  const int lane = threadIdx.x & 31;
+  const int vec = d / 8;
+  for (long i = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < picks;
+       i += (long)gridDim.x * (blockDim.x >> 5)) {
+    const int r = pos[i];
+    if (r < 0) { if (lane == 0 && dw) dw[i] = 0.f; continue; }
+    const long t = i / k;
+    const float ww = w ? w[i] : 1.f;
+    float dot = 0.f;
+    for (int c = lane; c < vec; c += 32) {
+      const uint4 g = reinterpret_cast<const uint4*>(dout + t * d)[c];
+      const uint32_t* gu = &g.x;
+      uint4 o; uint32_t* ou = &o.x;
+      uint4 yv = make_uint4(0, 0, 0, 0);
+      if (dw) yv = reinterpret_cast<const uint4*>(y + (long)r * d)[c];
+      const uint32_t* yu = &yv.x;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 gf = unpack_bf16(gu[q]);
+        const float2 yf = unpack_bf16(yu[q]);
+        dot += gf.x * yf.x + gf.y * yf.y;
+        ou[q] = pack_bf16(gf.x * ww, gf.y * ww);
+      }
+      reinterpret_cast<uint4*>(dy + (long)r * d)[c] = o;
+    }
+    if (dw) {
+      dot = warp_sum(dot);
+      if (lane == 0) dw[i] = dot;
+    }
+  }
+}
+
 // ---------------------------------------------------------------- launchers
 static inline int grid_for(long work, int per_block, int cap = 148 * 16) {
   long g = (work + per_block - 1) / per_block;
@@ -643,9 +690,9 @@ void glu_fwd(const void* h, void* out, const float* row_scale, long rows, int f,
 void glu_bwd(const void* h, const void* dout, void* dh, const float* row_scale, float* d_row_scale, long rows, int f, int kind, float limit, float up_offset, cudaStream_t s) {
   glu_bwd_kernel<<<grid_for(rows * (f / 8), 256), 256, 0, s>>>((const __nv_bfloat16*)h, (const __nv_bfloat16*)dout, (__nv_bfloat16*)dh, row_scale, d_row_scale, rows, f, kind, limit, up_offset);
 }
-void quant_mxfp8(const void* x, long ld_x, const int* row_index, uint8_t* q_row, uint8_t* sf_row, uint8_t* q_col, uint8_t* sf_col, long rows, int cols, long ld_col, cudaStream_t s) {
-  dim3 grid((cols + 127) / 128, (unsigned)((rows + 31) / 32));
-  quant_mxfp8_kernel<<<grid, 128, 0, s>>>((const __nv_bfloat16*)x, ld_x, row_index, q_row, sf_row, q_col, sf_col, rows, cols, ld_col);
+void quant_mxfp8(const void* x, long ld_x, const int* row_index, uint8_t* q_row, uint8_t* sf_row, uint8_t* q_col, uint8_t* sf_col, long rows, int cols, long ld_col, int batch, long x_batch_stride, cudaStream_t s) {
+  dim3 grid((cols + 127) / 128, (unsigned)((rows + 31) / 32), batch);
+  quant_mxfp8_kernel<<<grid, 128, 0, s>>>((const __nv_bfloat16*)x, ld_x, row_index, q_row, sf_row, q_col, sf_col, rows, cols, ld_col, x_batch_stride);
 }
 void ce_fwd_bwd(void* logits, const int* targets, const float* mask, float* loss, float* logz, long rows, int vocab, long ld, float grad_scale, float z_weight, float softcap, cudaStream_t s) {
   ce_fwd_bwd_kernel<<<(unsigned)rows, 512, 0, s>>>((__nv_bfloat16*)logits, targets, mask, loss, logz, vocab, ld, grad_scale, z_weight, softcap);
@@ -671,6 +718,9 @@ void sumsq(const void* g, bool bf16, long n, float* out, cudaStream_t s) {
 }
 void gather_rows(const void* x, const int* index, void* out, long rows, int d, cudaStream_t s) {
   gather_rows_kernel<<<grid_for(rows * (d / 8), 256), 256, 0, s>>>((const __nv_bfloat16*)x, index, (__nv_bfloat16*)out, rows, d);
+}
+void combine_bwd(const void* y, const void* dout, const int* pos, const float* w, void* dy, float* dw, long picks, int k, int d, cudaStream_t s) {
+  combine_bwd_kernel<<<grid_for(picks, 8), 256, 0, s>>>((const __nv_bfloat16*)y, (const __nv_bfloat16*)dout, pos, w, (__nv_bfloat16*)dy, dw, picks, k, d);
 }
 void combine_rows(const void* y, const int* pos, const float* w, void* out, long tokens, int k, int d, cudaStream_t s) {
   combine_rows_kernel<<<grid_for(tokens * (d / 8), 256), 256, 0, s>>>((const __nv_bfloat16*)y, pos, w, (__nv_bfloat16*)out, tokens, k, d);

@@ -16,13 +16,14 @@ const char* norm_rope(bool bwd, const void* x, const float* w, const float* cs, 
                       long stride_x, long stride_y, float eps, cudaStream_t s);
 void glu_fwd(const void* h, void* out, const float* row_scale, long rows, int f, int kind, float limit, float up_offset, cudaStream_t s);
 void glu_bwd(const void* h, const void* dout, void* dh, const float* row_scale, float* d_row_scale, long rows, int f, int kind, float limit, float up_offset, cudaStream_t s);
-void quant_mxfp8(const void* x, long ld_x, const int* row_index, uint8_t* q_row, uint8_t* sf_row, uint8_t* q_col, uint8_t* sf_col, long rows, int cols, long ld_col, cudaStream_t s);
+void quant_mxfp8(const void* x, long ld_x, const int* row_index, uint8_t* q_row, uint8_t* sf_row, uint8_t* q_col, uint8_t* sf_col, long rows, int cols, long ld_col, int batch, long x_batch_stride, cudaStream_t s);
 void ce_fwd_bwd(void* logits, const int* targets, const float* mask, float* loss, float* logz, long rows, int vocab, long ld, float grad_scale, float z_weight, float softcap, cudaStream_t s);
 const char* adamw(void* p, bool p_bf16, const void* g, bool g_bf16, void* m, void* v, uint8_t* m_sf, uint8_t* v_sf, int mom,
                   void* shadow, long n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
                   const float* gscale_ptr, float gscale, cudaStream_t s);
 void sumsq(const void* g, bool bf16, long n, float* out, cudaStream_t s);
 void gather_rows(const void* x, const int* index, void* out, long rows, int d, cudaStream_t s);
+void combine_bwd(const void* y, const void* dout, const int* pos, const float* w, void* dy, float* dw, long picks, int k, int d, cudaStream_t s);
 void combine_rows(const void* y, const int* pos, const float* w, void* out, long tokens, int k, int d, cudaStream_t s);
 
 }  // namespace bux

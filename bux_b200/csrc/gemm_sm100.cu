@@ -19,6 +19,8 @@
 // (architecture/precision/blockscaled.py:204) and the Mosaic-GPU grouped kernel
 // (architecture/experts/grouped_mxfp8.py:416-740). Unlike the latter, no load here is
 // a cluster-multicast load.
+#include <cstdio>
+
 #include "common.cuh"
 #include "gemm_sm100.h"
 
@@ -345,6 +347,10 @@ const char* make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uin
                          uint32_t box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return "cuTensorMapEncodeTiled is not available from this driver";
+  // The driver call needs this thread's primary context bound; a thread that has made
+  // no runtime call yet (an autograd worker) has none until one is made.
+  static thread_local bool bound = false;
+  if (!bound) { cudaFree(nullptr); bound = true; }
   if (reinterpret_cast<uintptr_t>(base) % 16 != 0) return "tensor base is not 16-byte aligned";
   if (row_stride_bytes % 16 != 0) return "row stride is not a multiple of 16 bytes";
   CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
@@ -355,7 +361,12 @@ const char* make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uin
   CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? nullptr : "cuTensorMapEncodeTiled failed";
+  if (r == CUDA_SUCCESS) return nullptr;
+  static thread_local char msg[256];
+  snprintf(msg, sizeof(msg), "cuTensorMapEncodeTiled failed (code %d): base %p elem %d dims [%llu, %llu] stride %llu box [%u, %u]",
+           (int)r, base, elem_bytes, (unsigned long long)cols, (unsigned long long)rows,
+           (unsigned long long)row_stride_bytes, box_cols, box_rows);
+  return msg;
 }
 
 template <int KIND, int BN, bool A_MN, bool B_MN>

@@ -1,0 +1,242 @@
+"""Composite differentiable ops: the chunked LM-head cross-entropy and the sorted
+MoE expert stack (permute → grouped GLU GEMMs → weighted combine).
+
+Reference behaviour: ``architecture/logits.py:209-353`` (logits never materialised
+whole; head gradients computed in the forward) and ``architecture/experts/moe.py:634``
+(`run_sorted`) with ``token_rows`` / ``token_sums`` (``:992-1071``).
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import reference as ref
+from .functional import _K, _quant_weight, kernels_on
+
+CE_CHUNK_BYTES = 1 << 30  # logits held at once (bf16)
+
+
+# ------------------------------------------------------------------ LM head + loss
+class _CEHead(torch.autograd.Function):
+    """sum over kept tokens of CE(x·W^T, target). The forward walks token chunks:
+    logits chunk (tcgen05 GEMM) → loss + dlogits in place (one kernel) → dX chunk and
+    dW accumulation (two GEMMs). The backward only scales by the incoming gradient."""
+
+    @staticmethod
+    def forward(ctx, x, w, targets, mask, z_weight, softcap):
+        K = _K()
+        t, d = x.shape
+        v = w.shape[0]
+        rows = max(128, min(t, (CE_CHUNK_BYTES // (2 * v)) // 128 * 128))
+        need_dx, need_dw = x.requires_grad, w.requires_grad
+        dx = torch.empty_like(x) if need_dx else None
+        main = getattr(w, "main_grad", None)
+        dw = None
+        if need_dw:
+            dw = main if main is not None else torch.zeros(v, d, dtype=torch.float32, device=x.device)
+        loss = torch.zeros((), dtype=torch.float32, device=x.device)
+        tg = targets.to(torch.int32).contiguous()
+        mk = None if mask is None else mask.float().contiguous()
+        for s in range(0, t, rows):
+            e = min(t, s + rows)
+            xc = x[s:e]
+            logits = K.gemm_bf16(xc, w)
+            per_row = K.ce_fwd_bwd(logits, tg[s:e], None if mk is None else mk[s:e], 1.0, z_weight,
+                                   softcap or 0.0)
+            loss += per_row.sum()
+            if need_dx:
+                K.gemm_bf16(logits, w, b_mn=True, out=dx[s:e])
+            if need_dw:
+                K.gemm_bf16(logits, xc, a_mn=True, b_mn=True, out=dw, accumulate=True)
+        ctx.save_for_backward(dx, None if main is not None else dw)
+        ctx.main = main is not None
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        dx, dw = ctx.saved_tensors
+        gx = None if dx is None else (dx.float() * g).to(dx.dtype)
+        gw = None if dw is None else dw * g
+        return gx, gw, None, None, None, None
+
+
+def cross_entropy_head(x, w, targets, mask=None, *, bias=None, z_weight: float = 0.0,
+                       softcap: Optional[float] = None):
+    """(sum of per-token losses over kept positions, number kept). x [T,d], w [V,d]."""
+    count = (torch.tensor(float(targets.numel()), device=x.device) if mask is None
+             else mask.float().sum())
+    native = (kernels_on(x) and bias is None and w.dtype == torch.bfloat16
+              and w.shape[0] % 8 == 0 and x.shape[-1] % 8 == 0
+              and getattr(w, "main_grad", None) is None)
+    if native:
+        return _CEHead.apply(x.contiguous(), w, targets, mask, float(z_weight), softcap), count
+    # plain path, a chunk of tokens at a time so the fp32 logits stay bounded
+    t = x.shape[0]
+    rows = max(1, min(t, (1 << 28) // max(1, w.shape[0])))
+    total = x.new_zeros((), dtype=torch.float32)
+    for s in range(0, t, rows):
+        logits = F.linear(x[s:s + rows], w.to(x.dtype), None if bias is None else bias.to(x.dtype))
+        part, _ = ref.cross_entropy(logits, targets[s:s + rows],
+                                    None if mask is None else mask[s:s + rows], z_weight, softcap)
+        total = total + part
+    return total, count
+
+
+# ------------------------------------------------------------------ sorted MoE experts
+def sort_picks(experts: torch.Tensor, num_experts: int, align: int = 128):
+    """Expert-sorted, `align`-padded layout of the T·k picks, with static shapes.
+
+    Returns (row_index int32[R] = source token of each padded row or -1,
+    pos int32[T,k] = padded row of each pick, offsets int32[E+1]) where
+    R = T·k + E·(align-1) rounded up to `align` bounds the padded rows."""
+    t, k = experts.shape
+    dev = experts.device
+    flat = experts.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=num_experts)
+    padded = (counts + align - 1) // align * align
+    offsets = torch.zeros(num_experts + 1, dtype=torch.int64, device=dev)
+    offsets[1:] = padded.cumsum(0)
+    starts = counts.cumsum(0) - counts  # first sorted index of each expert
+    sorted_expert = flat[order]
+    rank = torch.arange(t * k, device=dev) - starts[sorted_expert]
+    dest = offsets[:-1][sorted_expert] + rank
+    r_max = -(-(t * k + num_experts * (align - 1)) // align) * align
+    row_index = torch.full((r_max,), -1, dtype=torch.int32, device=dev)
+    row_index[dest] = (order // k).to(torch.int32)
+    pos = torch.empty(t * k, dtype=torch.int32, device=dev)
+    pos[order] = dest.to(torch.int32)
+    return row_index, pos.view(t, k), offsets.to(torch.int32)
+
+
+class _SortedExperts(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w_gu, w_down, weights, experts, act, limit, up_offset, mx):
+        K = _K()
+        t, d = x.shape
+        e, f2, _ = w_gu.shape
+        f = f2 // 2
+        kind = K.KIND_MXFP8 if mx else K.KIND_BF16
+        row_index, pos, offsets = sort_picks(experts, e)
+        rows = row_index.numel()
+        wts = weights.float().contiguous()
+        if mx:
+            xq, xsf, _, _ = K.quant_mxfp8(x, row_index=row_index, rows=rows)
+            gq, gsf, _, _ = K.quant_mxfp8_batched(w_gu.detach(), rowwise=True)
+            h = K.grouped_gemm(xq, gq, offsets, f2, d, kind=kind, asf=xsf, bsf=gsf)
+            del gq, gsf
+        else:
+            xs = K.gather_rows(x, row_index, rows)
+            h = K.grouped_gemm(xs, w_gu.view(e * f2, d), offsets, f2, d)
+        a = K.glu_fwd(h, act, None, limit, up_offset)
+        if mx:
+            aq, asf, _, _ = K.quant_mxfp8(a)
+            dq, dsf, _, _ = K.quant_mxfp8_batched(w_down.detach(), rowwise=True)
+            y = K.grouped_gemm(aq, dq, offsets, d, f, kind=kind, asf=asf, bsf=dsf)
+            del aq, asf, dq, dsf
+        else:
+            y = K.grouped_gemm(a, w_down.view(e * d, f), offsets, d, f)
+        out = K.combine_rows(y, pos, wts, t)
+        ctx.save_for_backward(x, w_gu, w_down, wts, row_index, pos, offsets, h, y)
+        ctx.cfg = (act, limit, up_offset, mx)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        K = _K()
+        x, w_gu, w_down, wts, row_index, pos, offsets, h, y = ctx.saved_tensors
+        act, limit, up_offset, mx = ctx.cfg
+        t, d = x.shape
+        e, f2, _ = w_gu.shape
+        f = f2 // 2
+        rows = row_index.numel()
+        kind = K.KIND_MXFP8 if mx else K.KIND_BF16
+        dy, dwts = K.combine_bwd(y, dout.contiguous(), pos, wts, rows)
+        del y
+        a = K.glu_fwd(h, act, None, limit, up_offset)  # recomputed: cheaper than keeping it
+        g_gu = getattr(w_gu, "main_grad", None)
+        g_down = getattr(w_down, "main_grad", None)
+        if mx:
+            dyq, dysf, dytq, dytsf = K.quant_mxfp8(dy, rowwise=True, colwise=True)
+            _, _, atq, atsf = K.quant_mxfp8(a, rowwise=False, colwise=True)
+            # dW_down[e] = dy_e^T · a_e
+            dw_down = K.grouped_gemm_k(dytq, atq, offsets, d, f, kind=kind, asf=dytsf, bsf=atsf,
+                                       out=g_down, accumulate=g_down is not None)
+            del dytq, dytsf, atq, atsf
+            # da = dy · W_down  (per expert, contraction over d): B = W_down^T rows [f, d]
+            wdt = w_down.detach().transpose(1, 2).contiguous()
+            tq, tsf, _, _ = K.quant_mxfp8_batched(wdt, rowwise=True)
+            da = K.grouped_gemm(dyq, tq, offsets, f, d, kind=kind, asf=dysf, bsf=tsf)
+            del wdt, tq, tsf, dyq, dysf
+        else:
+            dw_down = K.grouped_gemm_k(dy, a, offsets, d, f, a_mn=True, b_mn=True, out=g_down,
+                                       accumulate=g_down is not None)
+            da = K.grouped_gemm(dy, w_down.view(e * d, f), offsets, f, d, b_mn=True)
+        del dy, a
+        dh, _ = K.glu_bwd(h, da, act, None, limit, up_offset)
+        del da
+        if mx:
+            hq, hsf, htq, htsf = K.quant_mxfp8(dh, rowwise=True, colwise=True)
+            _, _, xtq, xtsf = K.quant_mxfp8(x, rowwise=False, colwise=True, row_index=row_index, rows=rows)
+            dw_gu = K.grouped_gemm_k(htq, xtq, offsets, f2, d, kind=kind, asf=htsf, bsf=xtsf,
+                                     out=g_gu, accumulate=g_gu is not None)
+            del htq, htsf, xtq, xtsf
+            wgt = w_gu.detach().transpose(1, 2).contiguous()  # [E, d, 2f]
+            tq, tsf, _, _ = K.quant_mxfp8_batched(wgt, rowwise=True)
+            dxs = K.grouped_gemm(hq, tq, offsets, d, f2, kind=kind, asf=hsf, bsf=tsf)
+        else:
+            xs = K.gather_rows(x, row_index, rows)
+            dw_gu = K.grouped_gemm_k(dh, xs, offsets, f2, d, a_mn=True, b_mn=True, out=g_gu,
+                                     accumulate=g_gu is not None)
+            dxs = K.grouped_gemm(dh, w_gu.view(e * f2, d), offsets, d, f2, b_mn=True)
+        dx = K.combine_rows(dxs, pos, None, t)
+        gw_gu = None if g_gu is not None else dw_gu.to(w_gu.dtype)
+        gw_down = None if g_down is not None else dw_down.to(w_down.dtype)
+        return dx, gw_gu, gw_down, dwts.to(wts.dtype), None, None, None, None, None
+
+
+def moe_experts(x, w_gate_up, w_down, weights, experts, *, act: str = "swish",
+                limit: Optional[float] = None, up_offset: float = 0.0, fmt: str = "bf16"):
+    """Routed experts on x [T,d]: out[t] = Σ_j weights[t,j] · expert_{experts[t,j]}(x[t]).
+    w_gate_up [E, 2f, d] (gate rows first), w_down [E, d, f]."""
+    e, f2, d = w_gate_up.shape
+    f = f2 // 2
+    mx = fmt in ("mxfp8", "mxfp8_2d")
+    shapes_ok = d % 128 == 0 and f % 128 == 0 if mx else (d % 8 == 0 and f % 8 == 0)
+    if (kernels_on(x) and shapes_ok and act in ("swish", "quick_gelu", "gelu_tanh", "relu2")
+            and w_gate_up.dtype == torch.bfloat16):
+        return _SortedExperts.apply(x.contiguous(), w_gate_up, w_down, weights, experts, act,
+                                    float(limit or 0.0), float(up_offset), mx)
+    return moe_reference(x, w_gate_up, w_down, weights, experts, act, limit, up_offset)
+
+
+def moe_reference(x, w_gate_up, w_down, weights, experts, act="swish", limit=None, up_offset=0.0):
+    """Differentiable plain-PyTorch experts: sort picks, one matmul pair per expert."""
+    t, d = x.shape
+    e, f2, _ = w_gate_up.shape
+    f = f2 // 2
+    k = experts.shape[1]
+    flat = experts.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=e).tolist()
+    tok = order // k
+    xs = x[tok]
+    outs = []
+    start = 0
+    for ex in range(e):
+        n = counts[ex]
+        if n == 0:
+            continue
+        seg = xs[start:start + n]
+        h = seg @ w_gate_up[ex].to(seg.dtype).t()
+        a = ref.glu(h[:, :f], h[:, f:], act, limit, up_offset)
+        outs.append(a @ w_down[ex].to(seg.dtype).t())
+        start += n
+    ys = torch.cat(outs) if outs else xs.new_zeros(0, d)
+    wflat = weights.reshape(-1)[order].unsqueeze(-1)
+    out = torch.zeros(t, d, dtype=torch.float32, device=x.device)
+    out = out.index_add(0, tok, ys.float() * wflat.float())
+    return out.to(x.dtype)

@@ -119,6 +119,28 @@ def sf_bytes(rows: int, cols: int) -> int:
     return (-(-rows // 128)) * (-(-(cols // 32) // 4)) * 512
 
 
+def quant_mxfp8_batched(x: torch.Tensor, *, rowwise: bool = True, colwise: bool = False):
+    """Quantise every matrix of a stack x [E, R, C] (R % 128 == 0 when colwise).
+    Returns (q_row [E*R, C], sf_row, q_col [E*C, R], sf_col): the 2-D views a grouped
+    GEMM takes as its per-group operand."""
+    e, r, c = x.shape
+    dev = x.device
+    q_row = sf_row = q_col = sf_col = None
+    if rowwise:
+        assert r % 128 == 0 or e == 1, "rowwise scale tiles of a stack need R % 128 == 0"
+        q_row = torch.empty(e * r, c, dtype=torch.float8_e4m3fn, device=dev)
+        sf_row = torch.full((e * sf_bytes(r, c),), 127, dtype=torch.uint8, device=dev)
+    if colwise:
+        assert r % 128 == 0 and c % 128 == 0
+        q_col = torch.empty(e * c, r, dtype=torch.float8_e4m3fn, device=dev)
+        sf_col = torch.full((e * sf_bytes(c, r),), 127, dtype=torch.uint8, device=dev)
+    xc = x.contiguous()
+    ops().quant_mxfp8(xc, None, None if q_row is None else q_row.view(torch.uint8), sf_row,
+                      None if q_col is None else q_col.view(torch.uint8), sf_col, r, c, r, e, r * c)
+    _count()
+    return q_row, sf_row, q_col, sf_col
+
+
 def quant_mxfp8(x: torch.Tensor, *, rowwise: bool = True, colwise: bool = False,
                 row_index: Optional[torch.Tensor] = None, rows: Optional[int] = None):
     """Quantise bf16 x [R, C] along C (rowwise) and/or along R (colwise; a transposed
@@ -137,7 +159,7 @@ def quant_mxfp8(x: torch.Tensor, *, rowwise: bool = True, colwise: bool = False,
         q_col = torch.zeros(c, r_pad, dtype=torch.float8_e4m3fn, device=dev)
         sf_col = torch.full((sf_bytes(c, r_pad),), 127, dtype=torch.uint8, device=dev)
     ops().quant_mxfp8(x2, row_index, None if q_row is None else q_row.view(torch.uint8), sf_row,
-                      None if q_col is None else q_col.view(torch.uint8), sf_col, r, c, r_pad)
+                      None if q_col is None else q_col.view(torch.uint8), sf_col, r, c, r_pad, 1, 0)
     _count()
     return q_row, sf_row, q_col, sf_col
 
@@ -221,6 +243,16 @@ def gather_rows(x, index, rows: int):
     ops().gather_rows(x, index, out)
     _count()
     return out
+
+
+def combine_bwd(y, dout, pos, w, rows: int):
+    """Backward of `combine_rows`: dy [rows, d] (pad rows zero) and dw [T, k] (None
+    without y)."""
+    dy = torch.zeros(rows, dout.shape[-1], dtype=dout.dtype, device=dout.device)
+    dw = torch.empty(pos.shape, dtype=torch.float32, device=dout.device) if y is not None else None
+    ops().combine_bwd(y, dout, pos, w, dy, dw)
+    _count()
+    return dy, dw
 
 
 def combine_rows(y, pos, w, tokens: int):

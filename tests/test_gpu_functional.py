@@ -1,0 +1,100 @@
+"""Differentiable CUDA ops (kernels behind autograd) against plain PyTorch in fp32."""
+import pytest
+import torch
+
+from bux_b200 import ops
+from bux_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / b.norm().clamp_min(1e-12)).item()
+
+
+@pytest.fixture(autouse=True)
+def _status(cuda):
+    from bux_b200.ops import kernels as K
+
+    yield
+    torch.cuda.synchronize()
+    K.check_status(cuda)
+
+
+@pytest.mark.parametrize("fmt,tol", [("bf16", 2e-2), ("mxfp8", 8e-2)])
+def test_linear(cuda, fmt, tol):
+    torch.manual_seed(0)
+    x = torch.randn(4, 96, 256, device=cuda).bfloat16().requires_grad_()
+    w = (torch.randn(384, 256, device=cuda) * 0.05).bfloat16().requires_grad_()
+    y = ops.linear(x, w, fmt=fmt)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = xr @ wr.t()
+    yr.backward(dy.float())
+    assert rel_err(y, yr) < tol
+    assert rel_err(x.grad, xr.grad) < tol
+    assert rel_err(w.grad, wr.grad) < tol
+
+
+def test_cross_entropy_head(cuda):
+    torch.manual_seed(1)
+    x = torch.randn(300, 128, device=cuda).bfloat16().requires_grad_()
+    w = (torch.randn(1000, 128, device=cuda) * 0.1).bfloat16().requires_grad_()
+    tgt = torch.randint(0, 1000, (300,), device=cuda)
+    mask = (torch.rand(300, device=cuda) > 0.1).float()
+    total, count = ops.cross_entropy_head(x, w, tgt, mask, z_weight=1e-4)
+    (total / count).backward()
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    tr, cr = ref.cross_entropy(xr @ wr.t(), tgt, mask, 1e-4)
+    (tr / cr).backward()
+    assert abs(total.item() - tr.item()) / tr.item() < 5e-3
+    assert rel_err(x.grad, xr.grad) < 3e-2
+    assert rel_err(w.grad, wr.grad) < 3e-2
+
+
+@pytest.mark.parametrize("fmt,tol", [("bf16", 3e-2), ("mxfp8", 1e-1)])
+def test_moe_experts(cuda, fmt, tol):
+    torch.manual_seed(2)
+    t, d, f, e, k = 512, 256, 128, 8, 2
+    x = torch.randn(t, d, device=cuda).bfloat16().requires_grad_()
+    wgu = (torch.randn(e, 2 * f, d, device=cuda) * 0.06).bfloat16().requires_grad_()
+    wd = (torch.randn(e, d, f, device=cuda) * 0.06).bfloat16().requires_grad_()
+    logits = torch.randn(t, e, device=cuda)
+    logits[:, 3] = -100.0  # an expert nobody picks
+    wts, idx, _ = ref.router_topk(logits, k)
+    wts = wts.requires_grad_()
+    out = ops.moe_experts(x, wgu, wd, wts, idx, fmt=fmt)
+    dout = torch.randn_like(out)
+    out.backward(dout)
+    xr = x.detach().float().requires_grad_()
+    gr = wgu.detach().float().requires_grad_()
+    dr = wd.detach().float().requires_grad_()
+    wr = wts.detach().clone().requires_grad_()
+    want = ops.moe_reference(xr, gr, dr, wr, idx)
+    want.backward(dout.float())
+    assert rel_err(out, want) < tol
+    assert rel_err(x.grad, xr.grad) < tol
+    assert rel_err(wgu.grad, gr.grad) < tol
+    assert rel_err(wd.grad, dr.grad) < tol
+    assert rel_err(wts.grad, wr.grad) < tol
+
+
+def test_norm_glu_attention_autograd(cuda):
+    torch.manual_seed(3)
+    x = torch.randn(2, 64, 256, device=cuda).bfloat16().requires_grad_()
+    w = torch.ones(256, device=cuda).requires_grad_()
+    y = ops.rmsnorm(x, w, 1e-6)
+    h = ops.glu(y.view(2, 64, 256))
+    h.sum().backward()
+    assert torch.isfinite(x.grad).all() and torch.isfinite(w.grad).all()
+    q = torch.randn(1, 256, 4, 64, device=cuda).bfloat16().requires_grad_()
+    k = torch.randn(1, 256, 2, 64, device=cuda).bfloat16().requires_grad_()
+    v = torch.randn(1, 256, 2, 64, device=cuda).bfloat16().requires_grad_()
+    o = ops.attention(q, k, v)
+    o.float().square().sum().backward()
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    orf, _ = ref.attention(qr, kr, vr)
+    orf.square().sum().backward()
+    assert rel_err(q.grad, qr.grad) < 4e-2 and rel_err(k.grad, kr.grad) < 4e-2
