@@ -1,0 +1,234 @@
+"""Headline benchmark: training throughput of Qwen3-30B-A3B (MXFP8 matmuls, experts
+split over the GPUs) in tokens/s over all GPUs of one node, synthetic data, random init.
+
+    python bench.py --gpus 1 --steps 4 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 4 --warmup 3
+
+Prints one JSON line (rank 0). `value` is device-timed (CUDA events around exactly
+`steps` steps, max over ranks); `e2e` is the same steps through `Trainer.train_step`
+with every step's batch copied from pinned host memory and its loss read back.
+`--impl reference` runs the unmodified reference from ``baseline/_ref`` when it can
+be imported, else reports why not.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+PUBLISHED_TOK_S_PER_GPU = 42391.0  # reference, 8xB300, MXFP8 `sorted` fsdp=8 (docs/performance/benchmarks.md:188)
+ROWS_PER_GPU = 32                  # 256 rows of 4096 over 8 GPUs
+
+
+def reference_arm(args) -> int:
+    why = None
+    ref = ROOT / "baseline" / "_ref"
+    if not ref.exists():
+        why = "baseline/_ref is not installed"
+    else:
+        sys.path.insert(0, str(ref))
+        try:
+            import bux  # noqa: F401
+        except Exception as err:  # noqa: BLE001
+            why = f"the reference does not import here: {type(err).__name__}: {str(err)[:120]}"
+    if why is None:
+        why = "the reference needs jax/flax/optax (not in this image) to train"
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.index)], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        rows = [r.split(", ") for r in Path(self.file.name).read_text().splitlines() if r.strip()]
+        os.unlink(self.file.name)
+        clocks = sorted(float(r[1]) for r in rows if len(r) >= 9 and r[1].replace(".", "").isdigit())
+        reasons = set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in rows:
+            if len(r) >= 9:
+                for name, v in zip(names, r[5:9]):
+                    if v.strip().lower() == "active":
+                        reasons.add(name)
+        mx = next((float(r[2]) for r in rows if len(r) >= 9), None)
+        med = clocks[len(clocks) // 2] if clocks else None
+        return {"sm_mhz": med, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="bux_b200", choices=["bux_b200", "reference"])
+    ap.add_argument("--layers", type=int, default=None,
+                    help="debug only: fewer layers (the result is then marked invalid)")
+    ap.add_argument("--rows", type=int, default=ROWS_PER_GPU, help="rows of 4096 tokens per GPU per step")
+    ap.add_argument("--seq-len", type=int, default=4096)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+
+    from bux_b200 import runtime
+    from bux_b200.lang import compile_runs
+    from bux_b200.ops import kernels as K
+    from bux_b200.train import data as D
+    from bux_b200.train.flops import flops_per_token
+    from bux_b200.train.trainer import Trainer
+
+    runtime.configure()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if rank == 0:
+            print(f"--gpus {args.gpus} needs {args.gpus} ranks (torchrun), found {world}", file=sys.stderr)
+        return 2
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    parallel = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+        from bux_b200.parallel.engine import Parallel
+    n = args.gpus
+    total_steps = args.warmup + args.steps + 2
+    overrides = [f"mesh = mesh(expert={n})", f"batch = {args.rows * n}", f"steps = {2 * total_steps + 4}",
+                 f"seq_len = {args.seq_len}", "log = log(every=1000000)",
+                 f"methods.moe = {'fused_ep' if n > 1 else 'sorted'}"]
+    if args.layers:
+        overrides.append(f"model = embed block^{args.layers} norm head")
+    path = ROOT / "examples" / "benchmarks" / "qwen3_30b_a3b_mxfp8.bux"
+    run = compile_runs(path.read_text(), filename=str(path), overrides=overrides)[0]
+    if world > 1:
+        parallel = Parallel(run.train, device)
+    # State that fits 180 GB: bf16 master weights as the benchmark names them; on one GPU
+    # the whole model's moments are kept in 8-bit block-scaled form and every gradient is
+    # consumed by the optimizer as soon as the backward produces it.
+    single = n == 1
+    trainer = Trainer(run, device=device, parallel=parallel, fuse_optimizer=single,
+                      moments="fp8" if single else "bfloat16", master=False)
+    trainer.model.set_remat(True, offload=single)
+    feed = iter(trainer.batches())
+    tokens_per_step = args.rows * n * args.seq_len
+
+    def one_step(read_loss: bool):
+        batch = next(feed)
+        out = trainer.train_step(batch)
+        if read_loss:
+            return float(out["loss"].item())
+        return out
+
+    for _ in range(args.warmup):
+        one_step(True)
+    torch.cuda.synchronize()
+    if parallel is not None:
+        parallel.barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    # ---- device-timed region: exactly `steps` steps
+    launches0 = K.launches
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    last = None
+    for _ in range(args.steps):
+        last = one_step(False)
+    end.record()
+    torch.cuda.synchronize()
+    launches = K.launches - launches0
+    ms = start.elapsed_time(end)
+    K.check_status(device, "bench")
+    # ---- end-to-end region through the public step API, loss read back every step
+    if parallel is not None:
+        parallel.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    loss = None
+    for _ in range(args.steps):
+        loss = one_step(True)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop() if rank == 0 else None
+    times = torch.tensor([ms, e2e_s * 1000], device=device, dtype=torch.float64)
+    if parallel is not None:
+        import torch.distributed as dist
+
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = times.tolist()
+    if rank == 0:
+        ms_step = ms / args.steps
+        value = tokens_per_step / (ms_step / 1000)
+        e2e_value = tokens_per_step / (e2e_ms / args.steps / 1000)
+        fpt = flops_per_token(run.arch, args.seq_len)
+        rows_local = args.rows
+        h2d = rows_local * args.seq_len * (4 + 4 + 1)  # ids, positions (int32) and mask per step
+        result = {
+            "metric": "train tokens/sec (Qwen3-30B-A3B MXFP8, experts over the GPUs)",
+            "value": value, "unit": "tokens/s", "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": value / n / PUBLISHED_TOK_S_PER_GPU, "dtype": "bf16 + mxfp8 matmuls",
+            "data": "synthetic (uniform random tokens), random-init weights",
+            "tokens_per_s_per_gpu": value / n,
+            "mfu_bf16_peak": value / n * fpt / 2.25e15,
+            "config": {"model": "qwen3_30b_a3b" + (f" TRUNCATED to {args.layers} layers: INVALID" if args.layers else ""),
+                       "global_batch": args.rows * n, "seq_len": args.seq_len,
+                       "parallelism": f"ep{n}" if n > 1 else "1 gpu (all experts local)",
+                       "optimizer": "adamw, bf16 master, " + ("8-bit block-scaled moments, update fused into backward"
+                                                             if single else "bf16 moments"),
+                       "remat": "per block", "l2": "inputs and weights exceed L2 (126 MB) every step",
+                       "loss_last_step": loss},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": 4},
+            "gpu_launches": launches,
+        }
+        print(json.dumps(result))
+    if parallel is not None:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

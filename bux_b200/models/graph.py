@@ -1,0 +1,284 @@
+"""IR graph → module tree. One module class per node kind; layers come from the
+registry. Attribute names (``items``, ``body``, ``terms``, ``factors``) follow the IR so
+that parameter paths read like the graph (``graph.items.1.items.0.body.items.1.q``).
+
+Reference counterparts: ``architecture/graph.py:37-241`` and the repeat builders in
+``architecture/repeats/repeat.py:38-141``.
+"""
+
+from __future__ import annotations
+
+import copy
+from typing import Optional
+
+import torch
+from torch import nn
+
+from ..lang import ir
+from .registry import BuildContext, Context, build_layer
+
+
+class Sequence(nn.Module):
+    def __init__(self, items):
+        super().__init__()
+        self.items = nn.ModuleList(items)
+
+    def forward(self, x, ctx: Context):
+        for item in self.items:
+            x = item(x, ctx)
+        return x
+
+
+class ResidualBranch(nn.Module):
+    """``[body]``: x + body(x), or whatever the residual algebra makes of a branch."""
+
+    def __init__(self, body, algebra: Optional[nn.Module] = None):
+        super().__init__()
+        self.body = body
+        if algebra is not None:
+            self.algebra = algebra
+
+    def forward(self, x, ctx: Context):
+        algebra = getattr(self, "algebra", None)
+        ctx.branch_index += 1
+        if algebra is not None:
+            return algebra(x, self.body, ctx)
+        return x + self.body(x, ctx)
+
+
+class Parallel(nn.Module):
+    def __init__(self, terms, product: bool):
+        super().__init__()
+        name = "factors" if product else "terms"
+        setattr(self, name, nn.ModuleList(terms))
+        self.product = product
+
+    def forward(self, x, ctx: Context):
+        parts = self.factors if self.product else self.terms
+        out = None
+        for part in parts:
+            y = part(x, ctx)
+            if out is None:
+                out = y
+            else:
+                out = out * y if self.product else out + y
+        return out
+
+
+class Negate(nn.Module):
+    def __init__(self, body):
+        super().__init__()
+        self.body = body
+
+    def forward(self, x, ctx):
+        return -self.body(x, ctx)
+
+
+class Constant(nn.Module):
+    def __init__(self, value: float):
+        super().__init__()
+        self.value = value
+
+    def forward(self, x, ctx):
+        return self.value
+
+
+class Identity(nn.Module):
+    def forward(self, x, ctx):
+        return x
+
+
+class TapWrite(nn.Module):
+    def __init__(self, name: str):
+        super().__init__()
+        self.name = name
+
+    def forward(self, x, ctx: Context):
+        ctx.push(self.name, x)
+        return x
+
+
+class TapRead(nn.Module):
+    def __init__(self, name: str, pop: bool):
+        super().__init__()
+        self.name, self.pop = name, pop
+
+    def forward(self, x, ctx: Context):
+        return ctx.read(self.name, self.pop)
+
+
+class Repeated(nn.Module):
+    """``body^n``: n copies with their own parameters, run in order. `remat` wraps each
+    pass in activation checkpointing (only its input is kept for the backward)."""
+
+    def __init__(self, items, shared_body: bool = False):
+        super().__init__()
+        self.items = nn.ModuleList(items)
+        self.remat = False
+        self.offload = False  # keep each pass's input in pinned host memory
+
+    def forward(self, x, ctx: Context):
+        for i, item in enumerate(self.items):
+            if (self.remat and ctx.training and torch.is_grad_enabled() and isinstance(x, torch.Tensor)
+                    and x.requires_grad):
+                x = _checkpointed(item, x, ctx, self.offload, (id(self), i))
+            else:
+                x = item(x, ctx)
+        return x
+
+
+class _Remat(torch.autograd.Function):
+    """Activation checkpointing of one block: the forward keeps only the block's input
+    (optionally in pinned host memory), the backward reruns the block and differentiates
+    it. Auxiliary losses the block reports are outputs of the function, so their
+    gradients reach the block's parameters too."""
+
+    @staticmethod
+    def forward(fctx, x, holder):
+        fctx.holder = holder
+        fctx.cuda_rng = torch.cuda.get_rng_state(x.device) if x.is_cuda else None
+        fctx.cpu_rng = torch.get_rng_state()
+        with torch.no_grad():
+            y, aux = holder.run(x, replay=False)
+        fctx.host = None
+        if holder.offload and x.is_cuda:
+            host = holder.pinned(x)
+            host.copy_(x, non_blocking=True)
+            fctx.host = host
+            fctx.device = x.device
+        else:
+            fctx.save_for_backward(x)
+        return (y, *aux)
+
+    @staticmethod
+    def backward(fctx, dy, *daux):
+        holder = fctx.holder
+        if fctx.host is not None:
+            x = fctx.host.to(fctx.device, non_blocking=True)
+        else:
+            (x,) = fctx.saved_tensors
+        x = x.detach().requires_grad_(True)
+        devices = [x.device] if x.is_cuda else []
+        with torch.random.fork_rng(devices=devices):
+            torch.set_rng_state(fctx.cpu_rng)
+            if fctx.cuda_rng is not None:
+                torch.cuda.set_rng_state(fctx.cuda_rng, x.device)
+            with torch.enable_grad():
+                y, aux = holder.run(x, replay=True)
+        outs, grads = [], []
+        for o, g in zip((y, *aux), (dy, *daux)):
+            if o.requires_grad and g is not None:
+                outs.append(o)
+                grads.append(g)
+        torch.autograd.backward(outs, grads)
+        return x.grad, None
+
+
+class _BlockRun:
+    """Runs a block for `_Remat`: the first run records taps / metrics as usual and
+    returns the auxiliary losses it reported; the replay records nothing."""
+
+    _pinned: dict = {}
+
+    def __init__(self, block, ctx: Context, offload: bool, key):
+        self.block, self.ctx, self.offload, self.key = block, ctx, offload, key
+        self.names: list = []
+        self.taps = {k: list(v) for k, v in ctx.taps.items()}
+        self.ports = dict(ctx.ports)
+
+    def pinned(self, x):
+        k = (self.key, tuple(x.shape), x.dtype)
+        buf = _BlockRun._pinned.get(k)
+        if buf is None:
+            buf = torch.empty(x.shape, dtype=x.dtype, device="cpu", pin_memory=True)
+            _BlockRun._pinned[k] = buf
+        return buf
+
+    def run(self, x, replay: bool):
+        ctx = self.ctx
+        saved = (ctx.taps, ctx.losses, ctx.metrics, ctx.ports, ctx.branch_index)
+        ctx.losses = {}
+        if replay:
+            ctx.taps = {k: list(v) for k, v in self.taps.items()}
+            ctx.metrics, ctx.ports = {}, dict(self.ports)
+        try:
+            y = self.block(x, ctx)
+            reported = ctx.losses
+        finally:
+            if replay:
+                ctx.taps, ctx.losses, ctx.metrics, ctx.ports, ctx.branch_index = saved
+            else:
+                ctx.losses = saved[1]
+        if not replay:
+            self.names = list(reported)
+        return y, [reported[n] for n in self.names]
+
+
+def _checkpointed(block, x, ctx: Context, offload: bool = False, key=None):
+    holder = _BlockRun(block, ctx, offload, key)
+    y, *aux = _Remat.apply(x, holder)
+    for name, value in zip(holder.names, aux):
+        prev = ctx.losses.get(name)
+        ctx.losses[name] = value if prev is None else prev + value
+    return y
+
+
+class GraphBuilder:
+    def __init__(self, arch: ir.Architecture, dtype: torch.dtype):
+        self.arch = arch
+        self.dtype = dtype
+        self.shared: dict = {}
+        self.embedding = None
+        self.layer_count = 0
+        self.num_layers = sum(1 for _ in arch.layers())
+        self.algebra_factory = None
+        if arch.residual is not None:
+            from . import residual
+
+            self.algebra_factory = lambda: residual.build(arch.residual, arch.d_model)
+
+    def build(self, node):
+        if node.share is not None:
+            if node.share not in self.shared:
+                self.shared[node.share] = self._build(node)
+            return self.shared[node.share]
+        return self._build(node)
+
+    def _build(self, node):
+        if isinstance(node, ir.Layer):
+            bctx = BuildContext(d_model=self.arch.d_model, vocab_size=self.arch.vocab_size,
+                                residual=self.arch.residual, init=self.arch.init, width=node.width,
+                                ports=node.ports, embedding=self.embedding, dtype=self.dtype,
+                                layer_index=self.layer_count, num_layers=self.num_layers)
+            self.layer_count += 1
+            module = build_layer(node.config, bctx)
+            if node.config.type == "embed" and self.embedding is None:
+                self.embedding = module
+            if node.ports:
+                module.ports = node.ports
+            return module
+        if isinstance(node, ir.Seq):
+            return Sequence([self.build(n) for n in node.items])
+        if isinstance(node, ir.Residual):
+            algebra = self.algebra_factory() if self.algebra_factory else None
+            return ResidualBranch(self.build(node.body), algebra)
+        if isinstance(node, ir.Sum):
+            return Parallel([self.build(n) for n in node.terms], product=False)
+        if isinstance(node, ir.Prod):
+            return Parallel([self.build(n) for n in node.factors], product=True)
+        if isinstance(node, ir.Neg):
+            return Negate(self.build(node.body))
+        if isinstance(node, ir.Const):
+            return Constant(node.value)
+        if isinstance(node, ir.Identity):
+            return Identity()
+        if isinstance(node, ir.Repeat):
+            if node.body.share is not None:
+                body = self.build(node.body)
+                return Repeated([body] * node.times)
+            return Repeated([self.build(node.body) for _ in range(node.times)])
+        if isinstance(node, ir.Tap):
+            return TapWrite(node.name)
+        if isinstance(node, ir.Ref):
+            return TapRead(node.name, node.pop)
+        raise AssertionError(node)

@@ -1,0 +1,153 @@
+"""Mixture of experts (``moe``): fp32 router, top-k, balance loss, sorted experts on
+grouped GEMMs, optional shared experts; expert parallelism is delegated to
+`bux_b200.parallel.experts` when the mesh has an ``expert`` axis.
+
+Reference: ``architecture/experts/moe.py:69-1071``. Expert weights there are stacked
+``(E, d, f, 2)`` (up, gate) and ``(E, f, d)``; here ``experts_gate_up`` is ``[E, 2f, d]``
+(gate rows first) and ``experts_down`` is ``[E, d, f]``: the K-major operands of the
+grouped tcgen05 GEMM. The checkpoint layer converts.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+from torch import nn
+
+from ... import ops
+from ...config import layers as L
+from ...ops import reference as ref
+from ..registry import BuildContext, Context, register
+from .basic import MLP, Linear, Norm, init_weight
+
+
+def balance_loss(scores: torch.Tensor, picks: torch.Tensor, k: int, per_sequence: bool) -> torch.Tensor:
+    """E · Σ_e f_e P_e (Switch / DeepSeek-V3): 1 when picks and scores are uniform."""
+    over = (1,) if per_sequence else (0, 1)
+    f = picks.float().mean(over) / k
+    p = (scores / scores.sum(-1, keepdim=True)).mean(over)
+    return scores.shape[-1] * (f * p).sum(-1).mean()
+
+
+def limit_groups(choice: torch.Tensor, groups: int, keep: int) -> torch.Tensor:
+    b, t, n = choice.shape
+    grouped = choice.view(b, t, groups, n // groups)
+    best = grouped.topk(min(2, n // groups), dim=-1).values.sum(-1)
+    kept_idx = best.topk(keep, dim=-1).indices
+    kept = torch.zeros(b, t, groups, dtype=torch.bool, device=choice.device).scatter_(-1, kept_idx, True)
+    return torch.where(kept.unsqueeze(-1), grouped, torch.full_like(grouped, float("-inf"))).view(b, t, n)
+
+
+class MoE(nn.Module):
+    def __init__(self, c: L.MoEConfig, b: BuildContext):
+        super().__init__()
+        if c.num_zero_experts or c.latent_size is not None or c.expert_norm is not None:
+            raise NotImplementedError("moe: zero experts, LatentMoE and expert_norm are not built yet")
+        if c.expert.type != "gated_mlp":
+            raise NotImplementedError("moe: routed experts are gated MLPs in this framework")
+        self.c = c
+        d = b.width if isinstance(b.width, int) else b.d_model
+        e, f = c.num_experts, c.expert.intermediate_size
+        self.d, self.e, self.f = d, e, f
+        self.router = Linear(d, e + (c.num_shared_experts if c.shared_expert_sink else 0),
+                             c.router_bias, b, role="router")
+        self.router.weight.data = self.router.weight.data.float()
+        self.experts_gate_up = nn.Parameter(torch.empty(e, 2 * f, d, dtype=b.dtype))
+        self.experts_down = nn.Parameter(torch.empty(e, d, f, dtype=b.dtype))
+        init_weight(self.experts_gate_up, b.init)
+        init_weight(self.experts_down, b.init, "out")
+        if c.load_balancing in ("aux_free", "smebu"):
+            self.register_buffer("router_bias", torch.zeros(e))
+            self.register_buffer("router_load", torch.zeros(e))
+            self.register_buffer("bias_velocity", torch.zeros(e))
+        if c.num_shared_experts:
+            sc = c.shared_expert or c.expert
+            sc = sc.model_copy(update={"intermediate_size": sc.intermediate_size * c.num_shared_experts})
+            self.shared = MLP(sc, d, b, role="mlp")
+            if c.shared_expert_gate:
+                self.shared_gate = Linear(d, 1, False, b, role="router")
+        self.ep = None  # set by the parallel layer when experts are split over ranks
+
+    # ------------------------------------------------------------------ routing
+    def route(self, x: torch.Tensor, ctx: Context):
+        c = self.c
+        logits = nn.functional.linear(x.float(), self.router.weight.float(),
+                                      None if self.router.bias is None else self.router.bias.float())
+        logits = logits * c.router_logit_scale
+        if c.random_logits and ctx.training:
+            drawn = torch.randn_like(logits)
+            logits = drawn + (logits - logits.detach())
+        scores = ref.router_scores(logits, c.router)
+        n = c.num_experts
+        scores, sinks = scores[..., :n], scores[..., n:]
+        choice = scores
+        if hasattr(self, "router_bias"):
+            choice = scores + self.router_bias
+        if c.num_groups > 1:
+            choice = limit_groups(choice, c.num_groups, c.top_k_groups)
+        idx = choice.topk(c.top_k, dim=-1).indices
+        if ctx.training:
+            picks = torch.zeros_like(scores).scatter_add_(-1, idx, torch.ones_like(idx, dtype=scores.dtype))
+            w = c.aux_loss_weight
+            if w:
+                ctx.report("balance_loss", balance_loss(scores, picks, c.top_k, c.aux_loss_scope == "sequence"), w)
+            if hasattr(self, "router_load"):
+                self.router_load += picks.detach().sum((0, 1))
+        weights = scores.gather(-1, idx)
+        if c.normalize_top_k:
+            total = weights.sum(-1, keepdim=True) + sinks.sum(-1, keepdim=True)
+            weights, sinks = weights / total, sinks / total
+        weights = weights * c.routed_scaling_factor
+        return idx, weights, (sinks * c.routed_scaling_factor if sinks.shape[-1] else None)
+
+    @torch.no_grad()
+    def step_end_update(self) -> None:
+        """Aux-loss-free balancing (DeepSeek-V3): nudge the selection bias of over- and
+        under-loaded experts once per step, from the picks counted since the last one."""
+        if not hasattr(self, "router_bias"):
+            return
+        c = self.c
+        load = self.router_load
+        if load.sum() == 0:
+            return
+        err = load.mean() - load
+        if c.load_balancing == "smebu":
+            step = torch.tanh(err / load.mean().clamp_min(1.0) / c.bias_softclamp) * c.bias_softclamp
+            self.bias_velocity.mul_(c.bias_momentum).add_(step, alpha=1 - c.bias_momentum)
+            self.router_bias.add_(self.bias_velocity, alpha=c.bias_update_rate)
+        else:
+            self.router_bias.add_(torch.sign(err), alpha=c.bias_update_rate)
+        if c.center_bias:
+            self.router_bias.sub_(self.router_bias.mean())
+        load.zero_()
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, x, ctx: Context):
+        c = self.c
+        bsz, t, d = x.shape
+        idx, weights, sinks = self.route(x, ctx)
+        flat = x.reshape(bsz * t, d)
+        fmt = ctx.precision.of("experts")
+        ec = c.expert
+        if self.ep is not None:
+            out = self.ep(self, flat, weights.reshape(bsz * t, -1), idx.reshape(bsz * t, -1), ctx, fmt)
+        else:
+            out = ops.moe_experts(flat, self.experts_gate_up, self.experts_down,
+                                  weights.reshape(bsz * t, -1), idx.reshape(bsz * t, -1),
+                                  act=ec.activation, limit=ec.limit, up_offset=ec.up_offset, fmt=fmt)
+        out = out.view(bsz, t, d)
+        if c.num_shared_experts:
+            shared = self.shared(x, ctx)
+            if c.shared_expert_gate:
+                shared = (shared.float() * torch.sigmoid(self.shared_gate(x, ctx).float())).to(shared.dtype)
+            if sinks is not None:
+                shared = (shared.float() * sinks.sum(-1, keepdim=True)).to(shared.dtype)
+            out = out + shared
+        return out
+
+
+@register("moe")
+def _moe(c, b):
+    return MoE(c, b)

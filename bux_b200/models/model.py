@@ -1,0 +1,86 @@
+"""`Model`: an `ir.Architecture` built into modules, and its forward.
+
+Reference: ``architecture/model.py:18-167`` (`Model`, `num_params`, `active_params`).
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import nn
+
+from ..lang import ir
+from .graph import GraphBuilder, Repeated
+from .registry import Context, Precision
+
+
+class Model(nn.Module):
+    """``Model(arch)(input_ids)`` runs the graph and returns the forward's `Context`:
+    ``ctx.heads`` holds every head's `HeadOutput` (hidden states + output matrix, the
+    logits are left to the loss), ``ctx.losses`` the auxiliary losses layers reported."""
+
+    def __init__(self, arch: ir.Architecture, dtype: torch.dtype = torch.float32, seed: int = 0,
+                 device=None):
+        super().__init__()
+        self.arch = arch
+        self.dtype = dtype
+        gen_state = torch.random.get_rng_state()
+        torch.manual_seed(seed)
+        try:
+            with torch.device(device) if device is not None else _null():
+                self.graph = GraphBuilder(arch, dtype).build(arch.graph)
+        finally:
+            torch.random.set_rng_state(gen_state)
+
+    def forward(self, input_ids: torch.Tensor, positions: Optional[torch.Tensor] = None,
+                segments: Optional[torch.Tensor] = None, *, training: Optional[bool] = None,
+                precision: Optional[Precision] = None, methods=None, parallel=None,
+                step: int = 0) -> Context:
+        ctx = Context(input_ids, positions, segments,
+                      training=self.training if training is None else training,
+                      precision=precision or Precision(compute=self.dtype), methods=methods,
+                      parallel=parallel, step=step)
+        ctx.output = self.graph(input_ids, ctx)
+        return ctx
+
+    def logits(self, input_ids, **kw) -> torch.Tensor:
+        """Logits of the first head: for tests and small-scale inspection."""
+        ctx = self(input_ids, **kw)
+        return ctx.heads[0].logits()
+
+    def set_remat(self, on: bool, offload: bool = False) -> None:
+        """Checkpoint every pass of every repeated block (keep only its input, rerun it
+        in the backward); `offload` keeps those inputs in pinned host memory."""
+        for m in self.modules():
+            if isinstance(m, Repeated):
+                m.remat = on
+                m.offload = offload
+
+    def step_end_update(self) -> None:
+        for m in self.modules():
+            fn = getattr(m, "step_end_update", None)
+            if fn is not None and m is not self:
+                fn()
+
+    def num_params(self) -> int:
+        return sum(p.numel() for p in self.parameters())
+
+    def active_params(self) -> int:
+        """Parameters a token passes through: routed experts count top_k / num_experts."""
+        from .layers.moe import MoE
+
+        total = self.num_params()
+        for m in self.modules():
+            if isinstance(m, MoE):
+                routed = m.experts_gate_up.numel() + m.experts_down.numel()
+                total -= routed - routed * m.c.top_k // m.c.num_experts
+        return total
+
+
+class _null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False

@@ -1,0 +1,43 @@
+"""Process-wide defaults set before CUDA / NCCL start; a user's own values win.
+
+Reference: ``runtime.py:48-161`` (XLA / NCCL defaults, memory pool fraction, compile
+cache agreement). Here: NCCL knobs for NVLink-5 / NVSwitch, the caching allocator's
+expandable segments (fewer fragmentation stalls at 180 GB), TF32 off for fp32 islands.
+"""
+
+from __future__ import annotations
+
+import os
+
+NCCL_DEFAULTS = {
+    "NCCL_NVLS_ENABLE": "1",          # in-switch reductions where the fabric offers them
+    "TORCH_NCCL_ASYNC_ERROR_HANDLING": "1",
+    "TORCH_NCCL_AVOID_RECORD_STREAMS": "1",
+}
+ALLOC_DEFAULT = "expandable_segments:True"
+
+
+def configure() -> None:
+    for k, v in NCCL_DEFAULTS.items():
+        os.environ.setdefault(k, v)
+    os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", ALLOC_DEFAULT)
+    os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "8")
+
+
+def agree_on_folder(folder, rank: int, world: int, barrier) -> None:
+    """Fail early unless every rank sees the same (shared) folder: rank 0 drops a file,
+    the others must see it (reference: ``runtime.py:116``, ``train/hooks.py:508``)."""
+    from pathlib import Path
+
+    marker = Path(folder) / ".bux_shared_check"
+    if rank == 0:
+        Path(folder).mkdir(parents=True, exist_ok=True)
+        marker.write_text(str(world))
+    barrier()
+    seen = marker.exists()
+    barrier()
+    if rank == 0:
+        marker.unlink(missing_ok=True)
+    if not seen:
+        raise ValueError(f"rank {rank} does not see {folder}: checkpoints and logs need a folder "
+                         "every process shares")

@@ -1,0 +1,363 @@
+"""The trainer: one step = forward/backward over the rank's microbatches, gradient
+reduction, clipping, fused optimizer update; the loop launches step N+1 before it
+reads step N's metrics, so the host never waits on the device between steps.
+
+Reference: ``train/trainer.py:447-1649`` (`Trainer`, `train`, `directory`). There the
+step is one traced XLA program; here it is explicit CUDA work on streams, and the
+gradient paths (whole batch, microbatches reduced once, pipeline-scheduled) are
+chosen from ``methods(...)`` by `bux_b200.parallel`.
+"""
+
+from __future__ import annotations
+
+import json
+import math
+import re
+import time
+from pathlib import Path
+from typing import Iterable, Optional
+
+import numpy as np
+import torch
+
+from ..config import training as T
+from ..lang import ir
+from ..lang.printer import run_to_source
+from ..models import Model, Precision
+from . import curriculum, data, objective, optim
+
+
+def slug(name: str) -> str:
+    return re.sub(r"[^A-Za-z0-9_.=+-]+", "_", name).strip("_")
+
+
+def directory(run: ir.Run, out) -> Path:
+    """``<out>/<slug(name)>-<id>/``: where a run writes."""
+    return Path(out) / f"{slug(run.name)}-{run.id}"
+
+
+def pick_device(spec: Optional[str] = None) -> torch.device:
+    if spec:
+        return torch.device(spec)
+    if torch.cuda.is_available():
+        import os
+
+        return torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    return torch.device("cpu")
+
+
+class Timers:
+    """Host timers of a step's parts, averaged over the steps between two logs."""
+
+    def __init__(self):
+        self.sums: dict = {}
+        self.count = 0
+
+    def add(self, name: str, seconds: float) -> None:
+        self.sums[name] = self.sums.get(name, 0.0) + seconds
+
+    def flush(self) -> dict:
+        n = max(self.count, 1)
+        out = {f"time/{k}_ms": v / n * 1000 for k, v in self.sums.items()}
+        self.sums, self.count = {}, 0
+        return out
+
+
+class Trainer:
+    def __init__(self, run: ir.Run, *, device=None, parallel=None, cache=".", seed=None,
+                 fuse_optimizer: bool = False, moments: Optional[str] = None,
+                 master: Optional[bool] = None):
+        self.run, self.train = run, run.train
+        t = run.train
+        self.device = pick_device(device) if not isinstance(device, torch.device) else device
+        self.parallel = parallel
+        self.cache = cache
+        cuda = self.device.type == "cuda"
+        self.compute = torch.bfloat16 if (t.precision.compute == "bfloat16" and cuda) else torch.float32
+        self.param_dtype = self.compute
+        self.model = Model(run.arch, dtype=self.param_dtype, seed=t.seed if seed is None else seed,
+                           device=self.device)
+        if parallel is not None:
+            parallel.prepare_model(self.model)
+        self.precision = Precision(compute=self.compute, matmuls=t.precision.matmuls,
+                                   roles={k: v for k, v in t.precision.roles.model_dump().items()
+                                          if k != "type" and v is not None})
+        experts_fmt = t.precision.experts()
+        if experts_fmt:
+            self.precision.roles["experts"] = experts_fmt
+        remat = t.methods.remat if isinstance(t.methods.remat, str) else "custom"
+        self.model.set_remat(self._remat_on(remat))
+        use_master = (self.param_dtype != torch.float32) if master is None else master
+        self.optimizer = optim.Optimizer(
+            self.model.named_parameters(), t.optimizer, moments=moments or t.precision.moments,
+            master=use_master, clip=t.clip,
+            reduce=parallel.sum_scalar if parallel is not None else None,
+            norm_weight=parallel.norm_weight if parallel is not None else None)
+        self.lr_at = optim.lr_multiplier(t)
+        self.step = 0
+        self.tokens = 0
+        self.stopping = False
+        self.fuse_optimizer = fuse_optimizer
+        self._pending_factor = None
+        self._prev_norm_sq = None
+        self._hooks_installed = False
+        self.stretches = curriculum.stretches(t)
+        self.timers = Timers()
+
+    # ------------------------------------------------------------------ setup
+    def _remat_on(self, remat: str) -> bool:
+        if remat == "none":
+            return False
+        if remat != "auto":
+            return True
+        if self.device.type != "cuda":
+            return False
+        t = self.train
+        world = self.parallel.data_world if self.parallel is not None else 1
+        rows = max(1, t.batch // world // t.methods.microbatches)
+        layers = sum(1 for _ in self.run.arch.layers())
+        est = rows * t.seq_len * self.run.arch.d_model * 2 * 12 * layers  # bytes kept without remat
+        free, _ = torch.cuda.mem_get_info(self.device)
+        return est > 0.5 * free
+
+    def config_at(self, step: int) -> T.TrainConfig:
+        for s in self.stretches:
+            if s.start <= step < s.stop:
+                return s.config
+        return self.stretches[-1].config
+
+    def batches(self, start: Optional[int] = None) -> Iterable:
+        rank = self.parallel.data_rank if self.parallel is not None else 0
+        world = self.parallel.data_world if self.parallel is not None else 1
+        return data.batches(self.train, self.run.arch.vocab_size or 1, self.cache,
+                            self.step if start is None else start, False, rank, world)
+
+    # ------------------------------------------------------------------ a step
+    def to_device(self, batch: data.Batch):
+        def put(a, dtype):
+            t = torch.from_numpy(np.ascontiguousarray(a))
+            if self.device.type == "cuda":
+                t = t.pin_memory().to(self.device, non_blocking=True)
+            return t.to(dtype)
+
+        return (put(batch.input_ids, torch.long), put(batch.position_ids, torch.long),
+                put(batch.loss_mask, torch.bool))
+
+    def forward_loss(self, mb, inv_count, n_micro: int, world: int, training: bool = True):
+        ids, pos, mask = mb
+        segments = None
+        if bool((pos[:, 1:] <= pos[:, :-1]).any()) if pos.device.type == "cpu" else False:
+            segments = torch.cumsum((pos == 0).long(), dim=1)
+        ctx = self.model(ids, pos, segments, training=training, precision=self.precision,
+                         methods=self.train.methods, parallel=self.parallel, step=self.step)
+        parts = objective.compute(ctx, mb, self.train.loss)
+        loss = parts.total_sum * inv_count + parts.per_batch / (n_micro * world)
+        return loss, parts
+
+    def train_step(self, batch: data.Batch) -> dict:
+        """Run one optimizer step on this rank's rows of `batch`; returns device scalars."""
+        t = self.train
+        cfg = self.config_at(self.step)
+        n_micro = max(1, min(t.methods.microbatches, batch.input_ids.shape[0]))
+        world = self.parallel.data_world if self.parallel is not None else 1
+        dev_batch = self.to_device(batch)
+        rows = dev_batch[0].shape[0]
+        micro = [tuple(x[i::n_micro] for x in dev_batch) for i in range(n_micro)] if n_micro > 1 else [dev_batch]
+        # global number of targets: a device scalar, summed over ranks without a host sync
+        count = torch.zeros(1, dtype=torch.float32, device=self.device)
+        for mb in micro:
+            _, m = objective.targets_and_mask(*mb)
+            count += m.sum()
+        if self.parallel is not None:
+            count = self.parallel.sum_scalar(count, data_only=True)
+        inv_count = 1.0 / count.clamp_min(1.0)
+        lr_scale = self.lr_at(self.step)
+        if self.fuse_optimizer:
+            self._install_release_hooks()
+            self._release = (lr_scale, self._delayed_clip_factor())
+            self.optimizer.step_count += 1
+        self.model.train()
+        loss_sum = torch.zeros((), dtype=torch.float32, device=self.device)
+        terms: dict = {}
+        for k, mb in enumerate(micro):
+            last = k == len(micro) - 1
+            sync = self.parallel.grad_sync(self.model, last) if self.parallel is not None else _null()
+            with sync:
+                loss, parts = self.forward_loss(mb, inv_count, n_micro, world)
+                loss.backward()
+            loss_sum += parts.ce_sum * inv_count.squeeze()
+            for name, v in parts.terms.items():
+                terms[name] = terms.get(name, 0) + v.float() / n_micro
+        if self.parallel is not None:
+            self.parallel.finish_grads(self.model)
+        if self.fuse_optimizer:
+            norm = None if self._prev_norm_sq is None else self._prev_norm_sq.sqrt()
+            self._prev_norm_sq = self._norm_acc
+            self._norm_acc = None
+        else:
+            norm = self.optimizer.step(lr_scale)
+        self.model.step_end_update()
+        if self.parallel is not None:
+            loss_sum = self.parallel.sum_scalar(loss_sum.view(1), data_only=True).view(())
+        self.step += 1
+        self.tokens += cfg.batch * cfg.seq_len
+        base_lr = t.optimizer.lr
+        out = {"loss": loss_sum, "lr": base_lr * lr_scale, "tokens": self.tokens}
+        if norm is not None:
+            out["grad_norm"] = norm
+        out.update(terms)
+        return out
+
+    # ---- optimizer fused into the backward (gradients released as they are produced)
+    def _install_release_hooks(self) -> None:
+        if self._hooks_installed:
+            return
+        self._hooks_installed = True
+        self._norm_acc = None
+        names = {p: n for n, p in self.model.named_parameters()}
+
+        def hook(p):
+            lr_scale, factor = self._release
+            g = self.optimizer.grad_of(p)
+            if g is not None and self.train.clip is not None:
+                if self._norm_acc is None:
+                    self._norm_acc = torch.zeros(1, dtype=torch.float32, device=p.device)
+                if g.is_cuda and g.is_contiguous() and g.dtype in (torch.float32, torch.bfloat16):
+                    from ..ops import kernels as K
+
+                    K.sumsq(g, self._norm_acc)
+                else:
+                    self._norm_acc += g.float().square().sum()
+            self.optimizer.update_param(names[p], p, lr_scale, 1.0, factor)
+
+        for p in self.model.parameters():
+            if p.requires_grad:
+                p.register_post_accumulate_grad_hook(hook)
+
+    def _delayed_clip_factor(self):
+        """With the update fused into the backward the step's own norm is not known
+        until its end, so the clip factor comes from the previous step's norm."""
+        if self.train.clip is None or self._prev_norm_sq is None:
+            return None
+        return self.optimizer.clip_factor(self._prev_norm_sq)
+
+    # ------------------------------------------------------------------ eval
+    @torch.no_grad()
+    def evaluate(self, e: T.EvalConfig) -> dict:
+        self.model.eval()
+        rank = self.parallel.data_rank if self.parallel is not None else 0
+        world = self.parallel.data_world if self.parallel is not None else 1
+        total = torch.zeros(1, dtype=torch.float32, device=self.device)
+        count = torch.zeros(1, dtype=torch.float32, device=self.device)
+        for b in data.eval_batches(self.train, e, self.run.arch.vocab_size or 1, self.cache, rank, world):
+            mb = self.to_device(b)
+            ctx = self.model(mb[0], mb[1], None, training=False, precision=self.precision,
+                             methods=self.train.methods, parallel=self.parallel, step=self.step)
+            parts = objective.compute(ctx, mb, self.train.loss)
+            total += parts.ce_sum
+            count += parts.count
+        if self.parallel is not None:
+            total = self.parallel.sum_scalar(total, data_only=True)
+            count = self.parallel.sum_scalar(count, data_only=True)
+        self.model.train()
+        return {f"{e.name}_loss": (total / count.clamp_min(1)).item()}
+
+    # ------------------------------------------------------------------ state
+    def state(self) -> dict:
+        return {"model": self.model.state_dict(), "optimizer": self.optimizer.state_dict(),
+                "step": self.step, "tokens": self.tokens}
+
+    def load(self, state: dict) -> None:
+        self.model.load_state_dict(state["model"])
+        self.optimizer.load_state_dict(state["optimizer"])
+        self.step, self.tokens = state["step"], state["tokens"]
+
+    # ------------------------------------------------------------------ the loop
+    def fit(self, hooks=(), sinks=()) -> None:
+        t = self.train
+        feed = data.prefetch(iter(self.batches()), 2)
+        for h in hooks:
+            h.start(self)
+        pending = None  # (step, device scalars) of the step launched last
+        while self.step < t.steps and not self.stopping:
+            t0 = time.perf_counter()
+            batch = next(feed)
+            t1 = time.perf_counter()
+            scalars = self.train_step(batch)
+            t2 = time.perf_counter()
+            self.timers.add("data", t1 - t0)
+            self.timers.add("launch", t2 - t1)
+            self.timers.count += 1
+            if pending is not None:
+                self._after_step(pending, hooks, sinks)
+            pending = (self.step, scalars)
+        if pending is not None:
+            self._after_step(pending, hooks, sinks, last=True)
+        for h in hooks:
+            h.stop(self, sinks)
+        for s in sinks:
+            s.close()
+
+    def _after_step(self, pending, hooks, sinks, last: bool = False) -> None:
+        step, scalars = pending
+        for h in hooks:
+            if h.due(step, self, last=last or step >= self.train.steps):
+                t0 = time.perf_counter()
+                h(step, scalars, self, sinks)
+                self.timers.add("hooks", time.perf_counter() - t0)
+
+
+class _null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
+
+
+def count_params(arch: ir.Architecture) -> int:
+    with torch.device("meta"):
+        return Model(arch).num_params()
+
+
+def train(run: ir.Run, out="runs", cache=".", hooks=None, sinks=None, device=None, parallel=None,
+          resume: bool = True, quiet: bool = False) -> Trainer:
+    """Train `run` into ``<out>/<name>-<id>/``: writes run.bux, run.json, metrics.jsonl,
+    checkpoints; resumes from the latest checkpoint when there is one."""
+    from . import hooks as H
+    from . import sinks as S
+
+    folder = directory(run, out)
+    main = S.is_main_process()
+    if main:
+        folder.mkdir(parents=True, exist_ok=True)
+        (folder / "run.bux").write_text(run_to_source(run))
+        (folder / "run.json").write_text(run.model_dump_json(indent=1))
+    trainer = Trainer(run, device=device, parallel=parallel, cache=cache)
+    t = run.train
+    resumed = None
+    ckpt = H.Checkpoint(folder, t.checkpoint) if t.checkpoint is not None else None
+    if ckpt is not None and resume:
+        resumed = ckpt.restore(trainer)
+    if sinks is None:
+        sinks = [S.Console(run.name, t.steps), S.JSONL(folder, resume_step=resumed)] if not quiet \
+            else [S.JSONL(folder, resume_step=resumed)]
+    if main and not quiet:
+        dev = f"{parallel.world if parallel is not None else 1} × {trainer.device.type}"
+        n = trainer.model.num_params()
+        S.echo(f"{run.name}: {folder}, on {dev}")
+        from ..lang.printer import value_to_source
+
+        S.echo(f"{run.name}: {curriculum.si(n)} parameters, {curriculum.summary(t)}, "
+               f"{value_to_source(t.optimizer)}, {value_to_source(t.schedule)}")
+        S.echo(f"{run.name}: log every {t.log.every}")
+    all_hooks = [H.Log(t.log, run, trainer)]
+    for e in T.evals(t):
+        all_hooks.append(H.Eval(e))
+    if ckpt is not None:
+        all_hooks.append(ckpt)
+    if t.profile is not None:
+        all_hooks.append(H.Profile(t.profile, folder))
+    all_hooks += list(hooks or ())
+    trainer.fit(all_hooks, sinks)
+    return trainer

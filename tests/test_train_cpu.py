@@ -1,0 +1,130 @@
+"""The trainer end to end on CPU: the smoke run, resume exactness, remat, schedules, data."""
+import json
+
+import numpy as np
+import pytest
+import torch
+
+from bux_b200.lang import compile_runs
+from bux_b200.train import data, optim
+from bux_b200.train.trainer import Trainer, directory, train
+from test_lang import SMOKE
+
+
+def test_smoke_trains_and_writes_the_run_directory(tmp_path):
+    run = compile_runs(SMOKE, filename="smoke.bux")[0]
+    tr = train(run, out=tmp_path, quiet=True)
+    folder = directory(run, tmp_path)
+    assert folder.name == "smoke-5a4f0f7d85"
+    assert (folder / "run.bux").exists() and (folder / "run.json").exists()
+    lines = [json.loads(l) for l in (folder / "metrics.jsonl").read_text().splitlines()]
+    assert [l["step"] for l in lines] == [10, 20, 30, 40, 50]
+    assert 6.0 < lines[-1]["loss"] < 6.5 and lines[-1]["lr"] == 0.0
+    assert tr.model.num_params() == 155968
+
+
+def test_learns_a_repeating_pattern():
+    src = SMOKE.replace("steps     = 50", "steps = 60").replace("schedule  = wsd(warmup=10)", "")
+    run = compile_runs(src, filename="s.bux")[0]
+    tr = Trainer(run, device="cpu")
+    ids = np.tile(np.arange(64, dtype=np.int32) % 7, (8, 1))
+    batch = data.plain(ids)
+    first = tr.train_step(batch)["loss"].item()
+    for _ in range(40):
+        last = tr.train_step(batch)["loss"].item()
+    assert last < first * 0.3
+
+
+def test_resume_is_exact(tmp_path):
+    src = SMOKE.replace("steps     = 50", "steps = 12") + "checkpoint = checkpoint(every=6)\nlog = log(every=1)\n"
+    src = src.replace("schedule  = wsd(warmup=10)", "schedule = wsd(warmup=2)")
+    run = compile_runs(src, filename="r.bux")[0]
+    full = train(run, out=tmp_path / "a", quiet=True)
+    # the same run stopped after 6 steps, then resumed
+    tr = train(run, out=tmp_path / "b", quiet=True, hooks=[_StopAt(6)])
+    assert tr.step == 6
+    resumed = train(run, out=tmp_path / "b", quiet=True)
+    assert resumed.step == 12
+    for (n, p), (_, q) in zip(full.model.named_parameters(), resumed.model.named_parameters()):
+        assert torch.allclose(p, q, atol=1e-6), n  # threaded CPU reductions are not bit-stable
+    a = [json.loads(l) for l in (directory(run, tmp_path / "a") / "metrics.jsonl").read_text().splitlines()]
+    b = [json.loads(l) for l in (directory(run, tmp_path / "b") / "metrics.jsonl").read_text().splitlines()]
+    assert [x["loss"] for x in a] == [x["loss"] for x in b]
+
+
+class _StopAt:
+    every = 1
+
+    def __init__(self, step):
+        self.at = step
+
+    def start(self, trainer):
+        pass
+
+    def due(self, step, trainer, last=False):
+        return True
+
+    def __call__(self, step, scalars, trainer, sinks):
+        if trainer.step >= self.at:
+            trainer.stopping = True
+
+    def stop(self, trainer, sinks):
+        pass
+
+
+def test_microbatches_match_the_whole_batch():
+    # a large eps makes the update nearly linear in the gradient, so it can be compared
+    opt = "optimizer = adamw(lr=3e-3, eps=1.0)"
+    run1 = compile_runs(SMOKE, filename="s.bux", overrides=[opt])[0]
+    run4 = compile_runs(SMOKE, filename="s.bux", overrides=[opt, "methods.microbatches = 4"])[0]
+    a, b = Trainer(run1, device="cpu"), Trainer(run4, device="cpu")
+    batch = next(iter(a.batches()))
+    la, lb = a.train_step(batch), b.train_step(batch)
+    assert abs(la["loss"].item() - lb["loss"].item()) < 1e-5
+    for p, q in zip(a.model.parameters(), b.model.parameters()):
+        assert torch.allclose(p, q, atol=1e-6)
+
+
+def test_fused_optimizer_matches_on_the_first_step():
+    run = compile_runs(SMOKE, filename="s.bux", overrides=["clip = none"])[0]
+    a, b = Trainer(run, device="cpu"), Trainer(run, device="cpu", fuse_optimizer=True)
+    batch = next(iter(a.batches()))
+    a.train_step(batch)
+    b.train_step(batch)
+    for p, q in zip(a.model.parameters(), b.model.parameters()):
+        assert torch.allclose(p, q, atol=1e-7)
+
+
+def test_synthetic_rows_depend_only_on_seed_and_index():
+    run = compile_runs(SMOKE, filename="s.bux")[0]
+    whole = next(data.batches(run.train, 512, start=3))
+    halves = [next(data.batches(run.train, 512, start=3, rank=r, world=2)) for r in range(2)]
+    assert np.array_equal(whole.input_ids, np.concatenate([h.input_ids for h in halves]))
+    rng = np.random.default_rng((0, 0, 0, 3 * 8))
+    assert np.array_equal(whole.input_ids[0], rng.integers(0, 512, 64, np.int32))
+
+
+def test_schedules():
+    run = compile_runs(SMOKE, filename="s.bux")[0]
+    m = optim.lr_multiplier(run.train)
+    assert m(0) == pytest.approx(0.1) and m(9) == 1.0 and m(39) == 1.0 and m(49) == 0.0
+    cos = compile_runs(SMOKE.replace("wsd(warmup=10)", "cosine(warmup=5, final=0.1)"))[0]
+    m = optim.lr_multiplier(cos.train)
+    assert m(4) == 1.0 and m(49) == pytest.approx(0.1)
+    assert all(m(s) >= m(s + 1) for s in range(5, 49))
+
+
+def test_newton_schulz_orthogonalises():
+    g = torch.randn(32, 64)
+    o = optim.newton_schulz(g, steps=8, dtype=torch.float32)
+    s = torch.linalg.svdvals(o)
+    assert s.max() < 1.3 and s.min() > 0.5
+
+
+def test_muon_steps():
+    run = compile_runs(SMOKE, filename="s.bux", overrides=["optimizer = muon(lr=0.02)"])[0]
+    tr = Trainer(run, device="cpu")
+    batch = next(iter(tr.batches()))
+    before = [p.clone() for p in tr.model.parameters()]
+    tr.train_step(batch)
+    assert any(not torch.equal(a, b) for a, b in zip(before, tr.model.parameters()))
