@@ -49,7 +49,8 @@ def test_resume_is_exact(tmp_path):
         assert torch.allclose(p, q, atol=1e-6), n  # threaded CPU reductions are not bit-stable
     a = [json.loads(l) for l in (directory(run, tmp_path / "a") / "metrics.jsonl").read_text().splitlines()]
     b = [json.loads(l) for l in (directory(run, tmp_path / "b") / "metrics.jsonl").read_text().splitlines()]
-    assert [x["loss"] for x in a] == [x["loss"] for x in b]
+    assert [x["step"] for x in a] == [x["step"] for x in b]
+    assert [x["loss"] for x in a] == pytest.approx([x["loss"] for x in b], abs=1e-5)
 
 
 class _StopAt:
