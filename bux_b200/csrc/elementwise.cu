@@ -492,6 +492,37 @@ __global__ void ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, const int*
 // bf16 shadow copy of the updated weights. Moments: fp32, bf16, or 8-bit block-scaled
 // (e4m3 values with one E8M0 scale per 32 elements; the second moment is stored as its
 // square root so that its dynamic range fits).
+// Each lane owns 8 consecutive elements (one 128-bit access of bf16); four adjacent
+// lanes form one 32-element scale block of the 8-bit moments and share its amax by
+// two shuffles. The buffer length may be ragged: tail elements take scalar paths.
+template <typename TT> struct Vec8;
+template <> struct Vec8<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&f)[8]) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&f)[8]) {
+    reinterpret_cast<float4*>(p)[0] = make_float4(f[0], f[1], f[2], f[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(f[4], f[5], f[6], f[7]);
+  }
+};
+template <> struct Vec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&f)[8]) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    float2 t;
+    t = unpack_bf16(v.x); f[0] = t.x; f[1] = t.y;
+    t = unpack_bf16(v.y); f[2] = t.x; f[3] = t.y;
+    t = unpack_bf16(v.z); f[4] = t.x; f[5] = t.y;
+    t = unpack_bf16(v.w); f[6] = t.x; f[7] = t.y;
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&f)[8]) {
+    uint4 v;
+    v.x = pack_bf16(f[0], f[1]); v.y = pack_bf16(f[2], f[3]);
+    v.z = pack_bf16(f[4], f[5]); v.w = pack_bf16(f[6], f[7]);
+    *reinterpret_cast<uint4*>(p) = v;
+  }
+};
+
 template <typename PT, typename GT, int MOM>
 __global__ void adamw_kernel(PT* __restrict__ p, const GT* __restrict__ g, void* __restrict__ m_,
                              void* __restrict__ v_, uint8_t* __restrict__ m_sf, uint8_t* __restrict__ v_sf,
@@ -499,57 +530,95 @@ __global__ void adamw_kernel(PT* __restrict__ p, const GT* __restrict__ g, void*
                              float eps, float wd, float bc1, float bc2, const float* __restrict__ grad_scale_ptr,
                              float grad_scale_const) {
   const float gscale = grad_scale_ptr ? *grad_scale_ptr * grad_scale_const : grad_scale_const;
-  // each thread owns 32 consecutive elements (one 8-bit scale block)
-  const long blocks = (n + 31) / 32;
-  for (long b = (long)blockIdx.x * blockDim.x + threadIdx.x; b < blocks; b += (long)gridDim.x * blockDim.x) {
-    const long i0 = b * 32;
-    const int cnt = (int)min(32L, n - i0);
-    float pm[32], pv[32];
+  const long groups = (n + 7) / 8;
+  // whole warps iterate together so that the 4-lane shuffles below are always converged
+  const long warp_groups = (groups + 31) / 32 * 32;
+  for (long gi = (long)blockIdx.x * blockDim.x + threadIdx.x; gi < warp_groups; gi += (long)gridDim.x * blockDim.x) {
+    const long i0 = gi * 8;
+    const bool active = i0 < n;
+    const bool full = i0 + 8 <= n;
+    const int cnt = active ? (int)min(8L, n - i0) : 0;
+    float pw[8], gr[8], pm[8], pv[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { pw[j] = 0.f; gr[j] = 0.f; pm[j] = 0.f; pv[j] = 0.f; }
+    if (full) {
+      Vec8<PT>::load(p + i0, pw);
+      Vec8<GT>::load(g + i0, gr);
+    } else {
+      for (int j = 0; j < cnt; ++j) { pw[j] = (float)p[i0 + j]; gr[j] = (float)g[i0 + j]; }
+    }
+    const long blk = i0 >> 5;
     if (MOM == MOM_F32) {
-      for (int j = 0; j < cnt; ++j) { pm[j] = reinterpret_cast<float*>(m_)[i0 + j]; pv[j] = reinterpret_cast<float*>(v_)[i0 + j]; }
+      if (full) { Vec8<float>::load(reinterpret_cast<float*>(m_) + i0, pm); Vec8<float>::load(reinterpret_cast<float*>(v_) + i0, pv); }
+      else for (int j = 0; j < cnt; ++j) { pm[j] = reinterpret_cast<float*>(m_)[i0 + j]; pv[j] = reinterpret_cast<float*>(v_)[i0 + j]; }
     } else if (MOM == MOM_BF16) {
-      for (int j = 0; j < cnt; ++j) {
+      if (full) { Vec8<__nv_bfloat16>::load(reinterpret_cast<__nv_bfloat16*>(m_) + i0, pm); Vec8<__nv_bfloat16>::load(reinterpret_cast<__nv_bfloat16*>(v_) + i0, pv); }
+      else for (int j = 0; j < cnt; ++j) {
         pm[j] = __bfloat162float(reinterpret_cast<__nv_bfloat16*>(m_)[i0 + j]);
         pv[j] = __bfloat162float(reinterpret_cast<__nv_bfloat16*>(v_)[i0 + j]);
       }
-    } else {
-      const float sm = __uint_as_float((uint32_t)max((int)m_sf[b], 1) << 23);
-      const float sv = __uint_as_float((uint32_t)max((int)v_sf[b], 1) << 23);
-      for (int j = 0; j < cnt; ++j) {
-        const __half_raw hm = __nv_cvt_fp8_to_halfraw(reinterpret_cast<uint8_t*>(m_)[i0 + j], __NV_E4M3);
-        const __half_raw hv = __nv_cvt_fp8_to_halfraw(reinterpret_cast<uint8_t*>(v_)[i0 + j], __NV_E4M3);
-        pm[j] = __half2float(__half(hm)) * sm;
-        const float rv = __half2float(__half(hv)) * sv;
+    } else if (active) {
+      const float sm = __uint_as_float((uint32_t)max((int)m_sf[blk], 1) << 23);
+      const float sv = __uint_as_float((uint32_t)max((int)v_sf[blk], 1) << 23);
+      uint8_t mb[8], vb[8];
+      if (full) {
+        *reinterpret_cast<uint2*>(mb) = *reinterpret_cast<const uint2*>(reinterpret_cast<uint8_t*>(m_) + i0);
+        *reinterpret_cast<uint2*>(vb) = *reinterpret_cast<const uint2*>(reinterpret_cast<uint8_t*>(v_) + i0);
+      } else {
+        for (int j = 0; j < 8; ++j) { mb[j] = j < cnt ? reinterpret_cast<uint8_t*>(m_)[i0 + j] : 0; vb[j] = j < cnt ? reinterpret_cast<uint8_t*>(v_)[i0 + j] : 0; }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        pm[j] = __half2float(__half(__nv_cvt_fp8_to_halfraw(mb[j], __NV_E4M3))) * sm;
+        const float rv = __half2float(__half(__nv_cvt_fp8_to_halfraw(vb[j], __NV_E4M3))) * sv;
         pv[j] = rv * rv;
       }
     }
     float am = 0.f, av = 0.f;
-    for (int j = 0; j < cnt; ++j) {
-      const float gr = (float)g[i0 + j] * gscale;
-      pm[j] = b1 * pm[j] + (1.f - b1) * gr;
-      pv[j] = b2 * pv[j] + (1.f - b2) * gr * gr;
-      const float w = (float)p[i0 + j];
-      const float upd = (pm[j] / bc1) / (sqrtf(pv[j] / bc2) + eps) + wd * w;
-      const float nw = w - lr * upd;
-      p[i0 + j] = (PT)nw;
-      if (shadow) shadow[i0 + j] = __float2bfloat16(nw);
-      am = fmaxf(am, fabsf(pm[j]));
-      av = fmaxf(av, sqrtf(pv[j]));
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float gg = gr[j] * gscale;
+      pm[j] = b1 * pm[j] + (1.f - b1) * gg;
+      pv[j] = b2 * pv[j] + (1.f - b2) * gg * gg;
+      const float upd = (pm[j] / bc1) / (sqrtf(pv[j] / bc2) + eps) + wd * pw[j];
+      pw[j] -= lr * upd;
+      if (j < cnt) { am = fmaxf(am, fabsf(pm[j])); av = fmaxf(av, sqrtf(pv[j])); }
+    }
+    if (full) {
+      Vec8<PT>::store(p + i0, pw);
+      if (shadow) Vec8<__nv_bfloat16>::store(shadow + i0, pw);
+    } else {
+      for (int j = 0; j < cnt; ++j) { p[i0 + j] = (PT)pw[j]; if (shadow) shadow[i0 + j] = __float2bfloat16(pw[j]); }
     }
     if (MOM == MOM_F32) {
-      for (int j = 0; j < cnt; ++j) { reinterpret_cast<float*>(m_)[i0 + j] = pm[j]; reinterpret_cast<float*>(v_)[i0 + j] = pv[j]; }
+      if (full) { Vec8<float>::store(reinterpret_cast<float*>(m_) + i0, pm); Vec8<float>::store(reinterpret_cast<float*>(v_) + i0, pv); }
+      else for (int j = 0; j < cnt; ++j) { reinterpret_cast<float*>(m_)[i0 + j] = pm[j]; reinterpret_cast<float*>(v_)[i0 + j] = pv[j]; }
     } else if (MOM == MOM_BF16) {
-      for (int j = 0; j < cnt; ++j) {
+      if (full) { Vec8<__nv_bfloat16>::store(reinterpret_cast<__nv_bfloat16*>(m_) + i0, pm); Vec8<__nv_bfloat16>::store(reinterpret_cast<__nv_bfloat16*>(v_) + i0, pv); }
+      else for (int j = 0; j < cnt; ++j) {
         reinterpret_cast<__nv_bfloat16*>(m_)[i0 + j] = __float2bfloat16(pm[j]);
         reinterpret_cast<__nv_bfloat16*>(v_)[i0 + j] = __float2bfloat16(pv[j]);
       }
     } else {
-      const uint8_t em = (uint8_t)max((int)e8m0_of(am), 1), ev = (uint8_t)max((int)e8m0_of(av), 1);
-      const float im = e8m0_inv(em), iv = e8m0_inv(ev);
-      m_sf[b] = em; v_sf[b] = ev;
-      for (int j = 0; j < cnt; ++j) {
-        reinterpret_cast<uint8_t*>(m_)[i0 + j] = __nv_cvt_float_to_fp8(pm[j] * im, __NV_SATFINITE, __NV_E4M3);
-        reinterpret_cast<uint8_t*>(v_)[i0 + j] = __nv_cvt_float_to_fp8(sqrtf(pv[j]) * iv, __NV_SATFINITE, __NV_E4M3);
+      // amax over the 4 lanes of the scale block
+      am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1)); am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+      av = fmaxf(av, __shfl_xor_sync(0xffffffffu, av, 1)); av = fmaxf(av, __shfl_xor_sync(0xffffffffu, av, 2));
+      if (active) {
+        const uint8_t em = (uint8_t)max((int)e8m0_of(am), 1), ev = (uint8_t)max((int)e8m0_of(av), 1);
+        const float im = e8m0_inv(em), iv = e8m0_inv(ev);
+        if ((threadIdx.x & 3) == 0) { m_sf[blk] = em; v_sf[blk] = ev; }
+        uint8_t mb[8], vb[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          mb[j] = __nv_cvt_float_to_fp8(pm[j] * im, __NV_SATFINITE, __NV_E4M3);
+          vb[j] = __nv_cvt_float_to_fp8(sqrtf(pv[j]) * iv, __NV_SATFINITE, __NV_E4M3);
+        }
+        if (full) {
+          *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(m_) + i0) = *reinterpret_cast<uint2*>(mb);
+          *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(v_) + i0) = *reinterpret_cast<uint2*>(vb);
+        } else {
+          for (int j = 0; j < cnt; ++j) { reinterpret_cast<uint8_t*>(m_)[i0 + j] = mb[j]; reinterpret_cast<uint8_t*>(v_)[i0 + j] = vb[j]; }
+        }
       }
     }
   }
@@ -700,8 +769,8 @@ void ce_fwd_bwd(void* logits, const int* targets, const float* mask, float* loss
 const char* adamw(void* p, bool p_bf16, const void* g, bool g_bf16, void* m, void* v, uint8_t* m_sf, uint8_t* v_sf, int mom,
                   void* shadow, long n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
                   const float* gscale_ptr, float gscale, cudaStream_t s) {
-  const int grid = grid_for((n + 31) / 32, 128);
-#define AW(PT, GT, MOM_) adamw_kernel<PT, GT, MOM_><<<grid, 128, 0, s>>>((PT*)p, (const GT*)g, m, v, m_sf, v_sf, (__nv_bfloat16*)shadow, n, lr, b1, b2, eps, wd, bc1, bc2, gscale_ptr, gscale)
+  const int grid = grid_for((n + 7) / 8, 256, 148 * 32);
+#define AW(PT, GT, MOM_) adamw_kernel<PT, GT, MOM_><<<grid, 256, 0, s>>>((PT*)p, (const GT*)g, m, v, m_sf, v_sf, (__nv_bfloat16*)shadow, n, lr, b1, b2, eps, wd, bc1, bc2, gscale_ptr, gscale)
 #define AW_MOM(PT, GT) { if (mom == MOM_F32) AW(PT, GT, MOM_F32); else if (mom == MOM_BF16) AW(PT, GT, MOM_BF16); else AW(PT, GT, MOM_FP8); return nullptr; }
   if (!p_bf16 && g_bf16) AW_MOM(float, __nv_bfloat16)
   if (!p_bf16 && !g_bf16) AW_MOM(float, float)
