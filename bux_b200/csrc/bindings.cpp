@@ -7,6 +7,7 @@
 #include <torch/library.h>
 
 #include "attention_sm100.h"
+#include "comm_sm100.h"
 #include "elementwise.h"
 #include "gemm_sm100.h"
 
@@ -45,7 +46,7 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& c, const c10::optional<Tenso
           const c10::optional<Tensor>& sfb, const c10::optional<Tensor>& group_offsets,
           const c10::optional<Tensor>& status, int64_t kind, int64_t mode, int64_t M, int64_t N,
           int64_t K, int64_t k_total, int64_t groups, bool a_mn, bool b_mn, int64_t out_kind,
-          int64_t bn, int64_t sms) {
+          int64_t bn, int64_t sms, const c10::optional<Tensor>& wait_flags, int64_t wait_epoch) {
   check_cuda(a, "a"); check_cuda(b, "b"); check_cuda(c, "c");
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "a and b are 2-D views");
   c10::cuda::CUDAGuard guard(a.device());
@@ -68,6 +69,9 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& c, const c10::optional<Tenso
   TORCH_CHECK(mode == bux::MODE_DENSE || g.group_offsets != nullptr, "grouped modes need group_offsets");
   g.status = status_ptr(status);
   g.sms = (int)sms;
+  if (wait_flags.has_value()) {
+    g.wait_flags = opt_i32(wait_flags); g.wait_world = (int)wait_flags->numel(); g.wait_epoch = (int)wait_epoch;
+  }
   const char* err = bux::gemm_launch(g, stream_of(a));
   TORCH_CHECK(err == nullptr, "bux gemm: ", err);
 }
@@ -221,10 +225,58 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
   TORCH_CHECK(err == nullptr, "bux attention backward: ", err);
 }
 
+// ------------------------------------------------------------------ expert-parallel exchange
+const uint64_t* u64_ptr(const Tensor& t) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kLong && t.is_contiguous(), "expected an int64 CUDA table of addresses");
+  return reinterpret_cast<const uint64_t*>(t.data_ptr());
+}
+void ep_push_rows(const Tensor& x, const Tensor& src_token, const Tensor& dst_rank, const Tensor& dst_row,
+                  const c10::optional<Tensor>& row_scale, const Tensor& peer_base, int64_t sms) {
+  check_cuda(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  bux::ep_push_rows(x.data_ptr(), src_token.data_ptr<int>(), dst_rank.data_ptr<int>(), dst_row.data_ptr<int>(),
+                    opt_f32(row_scale), u64_ptr(peer_base), dst_row.numel(), (int)x.size(-1), (int)sms, stream_of(x));
+}
+void ep_signal(const Tensor& peer_flags, int64_t channel, int64_t world, int64_t my_rank, int64_t epoch) {
+  c10::cuda::CUDAGuard guard(peer_flags.device());
+  bux::ep_signal(u64_ptr(peer_flags), (int)channel, (int)world, (int)my_rank, (int)epoch, stream_of(peer_flags));
+}
+void ep_pull_combine(const Tensor& peer_base, const Tensor& rank_of, const Tensor& row_of, const c10::optional<Tensor>& w,
+                     Tensor& out, const c10::optional<Tensor>& flags, int64_t epoch, const c10::optional<Tensor>& status,
+                     double limit_s) {
+  check_cuda(out, "out");
+  c10::cuda::CUDAGuard guard(out.device());
+  const int* fl = opt_i32(flags);
+  bux::ep_pull_combine(u64_ptr(peer_base), rank_of.data_ptr<int>(), row_of.data_ptr<int>(), opt_f32(w), out.data_ptr(),
+                       out.size(0), (int)row_of.size(1), (int)out.size(1), fl, fl ? (int)flags->numel() : 0, (int)epoch,
+                       (uint64_t)(limit_s * 1e9), status_ptr(status), stream_of(out));
+}
+void ep_pull_dot(const Tensor& peer_base, const Tensor& rank_of, const Tensor& row_of, const Tensor& dout, Tensor& dw) {
+  check_cuda(dout, "dout");
+  c10::cuda::CUDAGuard guard(dout.device());
+  bux::ep_pull_dot(u64_ptr(peer_base), rank_of.data_ptr<int>(), row_of.data_ptr<int>(), dout.data_ptr(), dw.data_ptr<float>(),
+                   row_of.numel(), (int)row_of.size(1), (int)dout.size(1), stream_of(dout));
+}
+void zero_pad_rows(Tensor& buf, const Tensor& offsets, const Tensor& counts) {
+  check_cuda(buf, "buf");
+  c10::cuda::CUDAGuard guard(buf.device());
+  bux::zero_pad_rows(buf.data_ptr(), offsets.data_ptr<int>(), counts.data_ptr<int>(), (int)counts.numel(), (int)buf.size(-1), stream_of(buf));
+}
+void ep_wait(const Tensor& flags, int64_t epoch, const c10::optional<Tensor>& status, double limit_s) {
+  c10::cuda::CUDAGuard guard(flags.device());
+  bux::ep_wait(flags.data_ptr<int>(), (int)flags.numel(), (int)epoch, (uint64_t)(limit_s * 1e9), status_ptr(status), stream_of(flags));
+}
+
 }  // namespace
 
 TORCH_LIBRARY(bux_b200, m) {
-  m.def("gemm(Tensor a, Tensor b, Tensor(a!) c, Tensor? sfa, Tensor? sfb, Tensor? group_offsets, Tensor? status, int kind, int mode, int M, int N, int K, int k_total, int groups, bool a_mn, bool b_mn, int out_kind, int bn, int sms) -> ()", &gemm);
+  m.def("ep_push_rows(Tensor x, Tensor src_token, Tensor dst_rank, Tensor dst_row, Tensor? row_scale, Tensor peer_base, int sms) -> ()", &ep_push_rows);
+  m.def("ep_signal(Tensor peer_flags, int channel, int world, int my_rank, int epoch) -> ()", &ep_signal);
+  m.def("ep_pull_combine(Tensor peer_base, Tensor rank_of, Tensor row_of, Tensor? w, Tensor(a!) out, Tensor? flags, int epoch, Tensor? status, float limit_s) -> ()", &ep_pull_combine);
+  m.def("ep_pull_dot(Tensor peer_base, Tensor rank_of, Tensor row_of, Tensor dout, Tensor(a!) dw) -> ()", &ep_pull_dot);
+  m.def("zero_pad_rows(Tensor(a!) buf, Tensor offsets, Tensor counts) -> ()", &zero_pad_rows);
+  m.def("ep_wait(Tensor flags, int epoch, Tensor? status, float limit_s) -> ()", &ep_wait);
+  m.def("gemm(Tensor a, Tensor b, Tensor(a!) c, Tensor? sfa, Tensor? sfb, Tensor? group_offsets, Tensor? status, int kind, int mode, int M, int N, int K, int k_total, int groups, bool a_mn, bool b_mn, int out_kind, int bn, int sms, Tensor? wait_flags=None, int wait_epoch=0) -> ()", &gemm);
   m.def("rmsnorm_fwd(Tensor x, Tensor? w, Tensor(a!) y, Tensor(b!) rstd, float eps) -> ()", &rmsnorm_fwd);
   m.def("rmsnorm_bwd(Tensor x, Tensor? w, Tensor dy, Tensor rstd, Tensor(a!) dx, Tensor? dw) -> ()", &rmsnorm_bwd);
   m.def("norm_rope(bool bwd, Tensor x, Tensor? w, Tensor cos, Tensor sin, Tensor(a!) y, Tensor? rstd, Tensor? dy, Tensor? dw, int tokens, int heads, int D, int stride_x, int stride_y, float eps) -> ()", &norm_rope);

@@ -1,0 +1,200 @@
+// Expert-parallel token exchange over NVLink peer memory, issued from inside kernels.
+//
+// Every rank maps every peer's receive buffers (symmetric memory) and holds their base
+// addresses in a small device table. The exchange is then plain loads and stores:
+//   ep_push_rows     each rank writes its token rows straight into the expert-sorted
+//                    receive buffer of the rank that owns the expert (P2P 16-byte
+//                    stores), optionally scaled (the backward sends w * dout).
+//   ep_signal        after a push (stream order), publishes an epoch number in every
+//                    peer's flag row with a system-scope release store.
+//   ep_pull_combine  out[t] = sum_j w[t,j] * y_peer[rank(t,j)][row(t,j)]: the combine
+//                    reads the expert outputs where they were produced (P2P 16-byte
+//                    loads), after a bounded wait for the owners' "output ready" flags.
+//   ep_pull_dot      dw[t,j] = <y_peer[rank][row], dout[t]> for the router's gradient.
+// The consumer GEMM waits for the senders' flags in its TMA producer warp
+// (GemmParams::wait_flags), so nothing on the host separates exchange and compute.
+//
+// All waits are bounded by wall-clock time; a wait that runs out records itself in the
+// status word and the kernel returns. No load here is a TMA / cluster-multicast load.
+//
+// Reference counterparts: parallel/experts.py:256-460 (all_to_all / ragged_all_to_all)
+// and the TransformerEngine NCCL-EP primitives of parallel/nccl_ep.py:359-474.
+#include "comm_sm100.h"
+#include "common.cuh"
+
+namespace bux {
+
+constexpr int KID_EP = 4;
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Wait until flags[0..world) >= epoch. One lane per peer, bounded.
+__device__ __forceinline__ bool wait_flags(const int* flags, int world, int epoch, uint64_t limit_ns,
+                                           Status* st, int site) {
+  bool ok = true;
+  if (threadIdx.x < world) {
+    const uint64_t t0 = global_ns();
+    while (ld_acquire_sys(flags + threadIdx.x) < epoch) {
+      if (global_ns() - t0 > limit_ns) { ok = false; report_failure(st, KID_EP, site); break; }
+      __nanosleep(200);
+    }
+  }
+  return ok;
+}
+
+// rows: one warp per sorted pick. peer_base[r] = base of rank r's receive buffer
+// ([cap rows, d] bf16). dst_rank / dst_row / src_token: int32[picks]; dst_row < 0 = dropped.
+__global__ void ep_push_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ src_token,
+                                    const int* __restrict__ dst_rank, const int* __restrict__ dst_row,
+                                    const float* __restrict__ row_scale, const uint64_t* __restrict__ peer_base,
+                                    long picks, int d) {
+  const int lane = threadIdx.x & 31;
+  const int vec = d / 8;
+  for (long i = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < picks;
+       i += (long)gridDim.x * (blockDim.x >> 5)) {
+    const int row = dst_row[i];
+    if (row < 0) continue;
+    const uint4* src = reinterpret_cast<const uint4*>(x + (long)src_token[i] * d);
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(peer_base[dst_rank[i]]) + (long)row * d);
+    const float s = row_scale ? row_scale[i] : 1.f;
+    for (int c = lane; c < vec; c += 32) {
+      uint4 v = src[c];
+      if (row_scale) {
+        uint32_t* u = &v.x;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { const float2 f = unpack_bf16(u[q]); u[q] = pack_bf16(f.x * s, f.y * s); }
+      }
+      dst[c] = v;
+    }
+  }
+}
+
+// one thread per peer: flag row `channel` of peer p, slot my_rank <- epoch
+__global__ void ep_signal_kernel(const uint64_t* __restrict__ peer_flags, int channel, int world,
+                                 int my_rank, int epoch) {
+  if (threadIdx.x < world) {
+    __threadfence_system();
+    int* flags = reinterpret_cast<int*>(peer_flags[threadIdx.x]) + (long)channel * world;
+    st_release_sys(flags + my_rank, epoch);
+  }
+}
+
+// out[t] = sum_j w[t,j] * y_peer[rank][row]; waits for every peer's flag first.
+__global__ void ep_pull_combine_kernel(const uint64_t* __restrict__ peer_base, const int* __restrict__ rank_of,
+                                       const int* __restrict__ row_of, const float* __restrict__ w,
+                                       __nv_bfloat16* __restrict__ out, long tokens, int k, int d,
+                                       const int* __restrict__ flags, int world, int epoch,
+                                       uint64_t limit_ns, Status* st) {
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if (flags != nullptr) {
+    if (!wait_flags(flags, world, epoch, limit_ns, st, 1)) ok_s = 0;
+    __syncthreads();
+    if (!ok_s) return;
+  }
+  const int vec = d / 8;
+  const long total = tokens * vec;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long t = i / vec; const int c = (int)(i % vec);
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int j = 0; j < k; ++j) {
+      const int r = row_of[t * k + j];
+      if (r < 0) continue;
+      const float ww = w ? w[t * k + j] : 1.f;
+      const uint4 v = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(peer_base[rank_of[t * k + j]]) + (long)r * d)[c];
+      const uint32_t* u = &v.x;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) { const float2 f = unpack_bf16(u[q]); acc[2 * q] += ww * f.x; acc[2 * q + 1] += ww * f.y; }
+    }
+    uint4 o;
+    o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);
+    o.z = pack_bf16(acc[4], acc[5]); o.w = pack_bf16(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(out + t * d)[c] = o;
+  }
+}
+
+// dw[t,j] = <y_peer[rank][row], dout[t]>: one warp per pick
+__global__ void ep_pull_dot_kernel(const uint64_t* __restrict__ peer_base, const int* __restrict__ rank_of,
+                                   const int* __restrict__ row_of, const __nv_bfloat16* __restrict__ dout,
+                                   float* __restrict__ dw, long picks, int k, int d) {
+  const int lane = threadIdx.x & 31;
+  const int vec = d / 8;
+  for (long i = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < picks;
+       i += (long)gridDim.x * (blockDim.x >> 5)) {
+    const int r = row_of[i];
+    float dot = 0.f;
+    if (r >= 0) {
+      const uint4* y = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(peer_base[rank_of[i]]) + (long)r * d);
+      const uint4* g = reinterpret_cast<const uint4*>(dout + (i / k) * d);
+      for (int c = lane; c < vec; c += 32) {
+        const uint4 a = y[c], b = g[c];
+        const uint32_t* au = &a.x; const uint32_t* bu = &b.x;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { const float2 f = unpack_bf16(au[q]), h = unpack_bf16(bu[q]); dot += f.x * h.x + f.y * h.y; }
+      }
+    }
+    dot = warp_sum(dot);
+    if (lane == 0) dw[i] = dot;
+  }
+}
+
+// Waits for flags on the stream (used where the consumer is not one of our kernels).
+__global__ void ep_wait_kernel(const int* __restrict__ flags, int world, int epoch, uint64_t limit_ns, Status* st) {
+  wait_flags(flags, world, epoch, limit_ns, st, 2);
+}
+
+// Rows [start[g] + count[g], start[g + 1]) of each group are padding up to the GEMM tile:
+// clear them so that contractions over rows (weight gradients) see zeros there.
+__global__ void zero_pad_rows_kernel(__nv_bfloat16* __restrict__ buf, const int* __restrict__ offsets,
+                                     const int* __restrict__ counts, int d) {
+  const int g = blockIdx.x;
+  const int first = offsets[g] + counts[g], last = offsets[g + 1];
+  const int vec = d / 8;
+  for (int r = first + blockIdx.y; r < last; r += gridDim.y)
+    for (int c = threadIdx.x; c < vec; c += blockDim.x)
+      reinterpret_cast<uint4*>(buf + (long)r * d)[c] = make_uint4(0, 0, 0, 0);
+}
+
+static inline int blocks_for(long warps_needed, int warps_per_block, int cap) {
+  long g = (warps_needed + warps_per_block - 1) / warps_per_block;
+  return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+void ep_push_rows(const void* x, const int* src_token, const int* dst_rank, const int* dst_row,
+                  const float* row_scale, const uint64_t* peer_base, long picks, int d, int sms, cudaStream_t s) {
+  // a modest number of CTAs keeps most SMs free for the GEMMs that run beside the exchange
+  ep_push_rows_kernel<<<blocks_for(picks, 8, sms > 0 ? sms * 4 : 148 * 4), 256, 0, s>>>(
+      (const __nv_bfloat16*)x, src_token, dst_rank, dst_row, row_scale, peer_base, picks, d);
+}
+void ep_signal(const uint64_t* peer_flags, int channel, int world, int my_rank, int epoch, cudaStream_t s) {
+  ep_signal_kernel<<<1, 32, 0, s>>>(peer_flags, channel, world, my_rank, epoch);
+}
+void ep_pull_combine(const uint64_t* peer_base, const int* rank_of, const int* row_of, const float* w, void* out,
+                     long tokens, int k, int d, const int* flags, int world, int epoch, uint64_t limit_ns,
+                     Status* st, cudaStream_t s) {
+  long work = tokens * (d / 8);
+  int grid = (int)((work + 255) / 256 > 148 * 8 ? 148 * 8 : (work + 255) / 256);
+  ep_pull_combine_kernel<<<grid < 1 ? 1 : grid, 256, 0, s>>>(peer_base, rank_of, row_of, w, (__nv_bfloat16*)out,
+                                                            tokens, k, d, flags, world, epoch, limit_ns, st);
+}
+void ep_pull_dot(const uint64_t* peer_base, const int* rank_of, const int* row_of, const void* dout, float* dw,
+                 long picks, int k, int d, cudaStream_t s) {
+  ep_pull_dot_kernel<<<blocks_for(picks, 8, 148 * 8), 256, 0, s>>>(peer_base, rank_of, row_of,
+                                                                    (const __nv_bfloat16*)dout, dw, picks, k, d);
+}
+void zero_pad_rows(void* buf, const int* offsets, const int* counts, int groups, int d, cudaStream_t s) {
+  zero_pad_rows_kernel<<<dim3(groups, 16), 256, 0, s>>>((__nv_bfloat16*)buf, offsets, counts, d);
+}
+void ep_wait(const int* flags, int world, int epoch, uint64_t limit_ns, Status* st, cudaStream_t s) {
+  ep_wait_kernel<<<1, 32, 0, s>>>(flags, world, epoch, limit_ns, st);
+}
+
+}  // namespace bux

@@ -1,0 +1,21 @@
+// Launchers of the expert-parallel exchange kernels (comm_sm100.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace bux {
+
+struct Status;
+
+void ep_push_rows(const void* x, const int* src_token, const int* dst_rank, const int* dst_row,
+                  const float* row_scale, const uint64_t* peer_base, long picks, int d, int sms, cudaStream_t s);
+void ep_signal(const uint64_t* peer_flags, int channel, int world, int my_rank, int epoch, cudaStream_t s);
+void ep_pull_combine(const uint64_t* peer_base, const int* rank_of, const int* row_of, const float* w, void* out,
+                     long tokens, int k, int d, const int* flags, int world, int epoch, uint64_t limit_ns,
+                     Status* st, cudaStream_t s);
+void ep_pull_dot(const uint64_t* peer_base, const int* rank_of, const int* row_of, const void* dout, float* dw,
+                 long picks, int k, int d, cudaStream_t s);
+void zero_pad_rows(void* buf, const int* offsets, const int* counts, int groups, int d, cudaStream_t s);
+void ep_wait(const int* flags, int world, int epoch, uint64_t limit_ns, Status* st, cudaStream_t s);
+
+}  // namespace bux

@@ -153,6 +153,21 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
       TileWalk walk(p, BN);
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
+      if (p.wait_flags != nullptr) {
+        // operand A is being written by peer GPUs: wait for every sender's flag
+        const uint64_t t0 = global_ns();
+        for (int r = 0; r < p.wait_world && ok; ++r) {
+          int v;
+          do {
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p.wait_flags + r) : "memory");
+            if (v >= p.wait_epoch) break;
+            if (global_ns() - t0 > p.wait_limit_ns) { ok = false; *abort_flag = 1; report_failure(st, KID_GEMM, 5); break; }
+            __nanosleep(100);
+          } while (true);
+        }
+        // order the TMA (async proxy) reads after the flags were seen
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+      }
       for (TileCoord c = walk.next(); c.valid && ok; c = walk.next()) {
         const int b_row0 = (p.mode == MODE_GROUPED_ROWS ? c.group * p.N : 0) + c.n0;
         // MN-major B of a grouped-rows GEMM is stored [groups * K, N]
@@ -389,6 +404,7 @@ const char* gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   p.groups = a.groups; p.group_offsets = a.group_offsets;
   p.c = a.c; p.ldc = a.ldc; p.out_kind = a.out_kind;
   p.sfa = a.sfa; p.sfb = a.sfb; p.status = a.status;
+  p.wait_flags = a.wait_flags; p.wait_world = a.wait_world; p.wait_epoch = a.wait_epoch; p.wait_limit_ns = a.wait_limit_ns;
   const int elem = a.kind == KIND_BF16 ? 2 : 1;
   const int bk = a.kind == KIND_BF16 ? 64 : 128;
   const int bn = a.bn;

@@ -22,6 +22,9 @@ struct GemmParams {
   const int* group_offsets;  // groups + 1 entries: row (or K) range of each group
   Status* status;
   int mode, M, N, K, k_total, groups, ldc, out_kind;
+  // optional: before its first load the producer waits (bounded) until
+  // wait_flags[0..wait_world) >= wait_epoch: senders on peer GPUs filled operand A
+  const int* wait_flags; int wait_world, wait_epoch; unsigned long long wait_limit_ns;
 };
 
 // What a caller fills in. `a_outer/a_inner` are the stored dims of A (inner contiguous):
@@ -37,6 +40,8 @@ struct GemmArgs {
   const int* group_offsets = nullptr;
   Status* status = nullptr;
   int sms = 0;
+  const int* wait_flags = nullptr; int wait_world = 0, wait_epoch = 0;
+  unsigned long long wait_limit_ns = 5000000000ull;
 };
 
 // Returns nullptr on success, else a static message.

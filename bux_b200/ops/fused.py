@@ -240,3 +240,126 @@ def moe_reference(x, w_gate_up, w_down, weights, experts, act="swish", limit=Non
     out = torch.zeros(t, d, dtype=torch.float32, device=x.device)
     out = out.index_add(0, tok, ys.float() * wflat.float())
     return out.to(x.dtype)
+
+
+# ------------------------------------------------------------------ experts on rows that are already sorted
+class _ExpertsOnSorted(torch.autograd.Function):
+    """The expert stack on rows that already sit in expert-sorted, 128-padded order
+    (what an expert-parallel rank receives): y[r] = expert_{group(r)}(xs[r]).
+
+    `io` (optional) couples it to the exchange: ``io.before_forward()`` /
+    ``io.before_backward()`` make the stream wait for the senders' flags (or return
+    (flags, epoch) for the first GEMM to wait on in-kernel), ``io.y_out`` / ``io.dx_out``
+    are the buffers peers read the results from, and ``io.after_forward()`` /
+    ``io.after_backward()`` publish "ready"."""
+
+    @staticmethod
+    def forward(ctx, xs, offsets, counts, w_gu, w_down, act, limit, up_offset, mx, io):
+        K = _K()
+        rows, d = xs.shape
+        e, f2, _ = w_gu.shape
+        f = f2 // 2
+        kind = K.KIND_MXFP8 if mx else K.KIND_BF16
+        wait = io.before_forward(in_kernel=not mx) if io is not None else None
+        wf, we = wait if wait is not None else (None, 0)
+        if counts is not None:
+            K.zero_pad_rows(xs, offsets, counts)
+        if mx:
+            xq, xsf, xtq, xtsf = K.quant_mxfp8(xs, rowwise=True, colwise=True)
+            gq, gsf, _, _ = K.quant_mxfp8_batched(w_gu.detach(), rowwise=True)
+            h = K.grouped_gemm(xq, gq, offsets, f2, d, kind=kind, asf=xsf, bsf=gsf)
+            del xq, xsf, gq, gsf
+            saved_x = (xtq, xtsf)
+        else:
+            h = K.grouped_gemm(xs, w_gu.view(e * f2, d), offsets, f2, d, wait_flags=wf, wait_epoch=we)
+            saved_x = (xs.clone(), None)
+        a = K.glu_fwd(h, act, None, limit, up_offset)
+        y_out = io.y_out(rows, d) if io is not None else None
+        if mx:
+            aq, asf, _, _ = K.quant_mxfp8(a)
+            dq, dsf, _, _ = K.quant_mxfp8_batched(w_down.detach(), rowwise=True)
+            y = K.grouped_gemm(aq, dq, offsets, d, f, kind=kind, asf=asf, bsf=dsf, out=y_out)
+        else:
+            y = K.grouped_gemm(a, w_down.view(e * d, f), offsets, d, f, out=y_out)
+        if io is not None:
+            io.after_forward()
+        ctx.save_for_backward(saved_x[0], saved_x[1], offsets, counts, w_gu, w_down, h)
+        ctx.cfg = (act, limit, up_offset, mx, io)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        K = _K()
+        xsave, xtsf, offsets, counts, w_gu, w_down, h = ctx.saved_tensors
+        act, limit, up_offset, mx, io = ctx.cfg
+        e, f2, d = w_gu.shape
+        f = f2 // 2
+        kind = K.KIND_MXFP8 if mx else K.KIND_BF16
+        if io is not None:
+            dy = io.before_backward(dy)
+        if counts is not None:
+            K.zero_pad_rows(dy, offsets, counts)
+        a = K.glu_fwd(h, act, None, limit, up_offset)
+        g_gu = getattr(w_gu, "main_grad", None)
+        g_down = getattr(w_down, "main_grad", None)
+        if mx:
+            dyq, dysf, dytq, dytsf = K.quant_mxfp8(dy, rowwise=True, colwise=True)
+            _, _, atq, atsf = K.quant_mxfp8(a, rowwise=False, colwise=True)
+            dw_down = K.grouped_gemm_k(dytq, atq, offsets, d, f, kind=kind, asf=dytsf, bsf=atsf,
+                                       out=g_down, accumulate=g_down is not None)
+            del dytq, dytsf, atq, atsf
+            wdt = w_down.detach().transpose(1, 2).contiguous()
+            tq, tsf, _, _ = K.quant_mxfp8_batched(wdt, rowwise=True)
+            da = K.grouped_gemm(dyq, tq, offsets, f, d, kind=kind, asf=dysf, bsf=tsf)
+            del wdt, tq, tsf, dyq, dysf
+        else:
+            dw_down = K.grouped_gemm_k(dy, a, offsets, d, f, a_mn=True, b_mn=True, out=g_down,
+                                       accumulate=g_down is not None)
+            da = K.grouped_gemm(dy, w_down.view(e * d, f), offsets, f, d, b_mn=True)
+        del a
+        dh, _ = K.glu_bwd(h, da, act, None, limit, up_offset)
+        del da
+        rows = dh.shape[0]
+        dx_out = io.dx_out(rows, d) if io is not None else None
+        if mx:
+            hq, hsf, htq, htsf = K.quant_mxfp8(dh, rowwise=True, colwise=True)
+            dw_gu = K.grouped_gemm_k(htq, xsave, offsets, f2, d, kind=kind, asf=htsf, bsf=xtsf,
+                                     out=g_gu, accumulate=g_gu is not None)
+            del htq, htsf
+            wgt = w_gu.detach().transpose(1, 2).contiguous()
+            tq, tsf, _, _ = K.quant_mxfp8_batched(wgt, rowwise=True)
+            dxs = K.grouped_gemm(hq, tq, offsets, d, f2, kind=kind, asf=hsf, bsf=tsf, out=dx_out)
+        else:
+            dw_gu = K.grouped_gemm_k(dh, xsave, offsets, f2, d, a_mn=True, b_mn=True, out=g_gu,
+                                     accumulate=g_gu is not None)
+            dxs = K.grouped_gemm(dh, w_gu.view(e * f2, d), offsets, d, f2, b_mn=True, out=dx_out)
+        if io is not None:
+            io.after_backward()
+        gw_gu = None if g_gu is not None else dw_gu.to(w_gu.dtype)
+        gw_down = None if g_down is not None else dw_down.to(w_down.dtype)
+        return dxs, None, None, gw_gu, gw_down, None, None, None, None, None
+
+
+def experts_on_sorted(xs, offsets, counts, w_gate_up, w_down, *, act="swish", limit=None,
+                      up_offset=0.0, fmt="bf16", io=None):
+    """Expert stack over pre-sorted rows; see `_ExpertsOnSorted`. Falls back to plain
+    PyTorch (per-group matmuls) off the GPU."""
+    mx = fmt in ("mxfp8", "mxfp8_2d")
+    if kernels_on(xs):
+        return _ExpertsOnSorted.apply(xs, offsets, counts, w_gate_up, w_down, act, float(limit or 0.0),
+                                      float(up_offset), mx, io)
+    f = w_gate_up.shape[1] // 2
+    off = offsets.tolist()
+    cnt = counts.tolist() if counts is not None else [off[g + 1] - off[g] for g in range(len(off) - 1)]
+    parts, at = [], 0
+    for g in range(len(off) - 1):
+        if off[g] > at:
+            parts.append(xs.new_zeros(off[g] - at, w_down.shape[1]))
+        seg = xs[off[g]: off[g] + cnt[g]]
+        hh = seg @ w_gate_up[g].to(seg.dtype).t()
+        aa = ref.glu(hh[:, :f], hh[:, f:], act, limit, up_offset)
+        parts.append(aa @ w_down[g].to(seg.dtype).t())
+        at = off[g] + cnt[g]
+    if xs.shape[0] > at:
+        parts.append(xs.new_zeros(xs.shape[0] - at, w_down.shape[1]))
+    return torch.cat(parts)

@@ -79,7 +79,8 @@ def gemm_mxfp8(aq, asf, bq, bsf, m: int, n: int, k: int, *, out=None, out_dtype=
 
 
 def grouped_gemm(a, b, offsets: torch.Tensor, n: int, k: int, *, kind: int = KIND_BF16, asf=None,
-                 bsf=None, b_mn: bool = False, out=None, bn: int = 128, sms: int = 0) -> torch.Tensor:
+                 bsf=None, b_mn: bool = False, out=None, bn: int = 128, sms: int = 0,
+                 wait_flags=None, wait_epoch: int = 0) -> torch.Tensor:
     """Rows of `a` ([R,k], sorted by group; offsets int32[G+1]) times group g's weight.
     b: [G*n, k] (K-major) or [G*k, n] (b_mn). Returns [R, n] bf16."""
     groups = offsets.numel() - 1
@@ -88,7 +89,7 @@ def grouped_gemm(a, b, offsets: torch.Tensor, n: int, k: int, *, kind: int = KIN
     if kind == KIND_MXFP8:
         a, b = a.view(torch.uint8), b.view(torch.uint8)
     ops().gemm(a, b, out, asf, bsf, offsets, status_word(a.device), kind, MODE_GROUPED_ROWS,
-               a.shape[0], n, k, k, groups, False, b_mn, OUT_BF16, bn, sms)
+               a.shape[0], n, k, k, groups, False, b_mn, OUT_BF16, bn, sms, wait_flags, wait_epoch)
     _count()
     return out
 
@@ -284,3 +285,39 @@ def attn_bwd(q, k, v, o, do, lse, *, causal=True, window=0, sinks=None, scale=No
                    scale if scale is not None else d ** -0.5, causal, window or 0)
     _count(2)
     return dq, dk, dv, dsinks
+
+
+# ------------------------------------------------------------------ expert-parallel exchange
+def ep_push_rows(x, src_token, dst_rank, dst_row, peer_base, row_scale=None, sms: int = 0) -> None:
+    ops().ep_push_rows(x, src_token, dst_rank, dst_row, row_scale, peer_base, sms)
+    _count()
+
+
+def ep_signal(peer_flags, channel: int, world: int, my_rank: int, epoch: int) -> None:
+    ops().ep_signal(peer_flags, channel, world, my_rank, epoch)
+    _count()
+
+
+def ep_pull_combine(peer_base, rank_of, row_of, w, tokens: int, d: int, dtype, flags=None, epoch: int = 0,
+                    limit_s: float = 5.0):
+    out = torch.empty(tokens, d, dtype=dtype, device=rank_of.device)
+    ops().ep_pull_combine(peer_base, rank_of, row_of, w, out, flags, epoch, status_word(rank_of.device), limit_s)
+    _count()
+    return out
+
+
+def ep_pull_dot(peer_base, rank_of, row_of, dout):
+    dw = torch.empty(row_of.shape, dtype=torch.float32, device=dout.device)
+    ops().ep_pull_dot(peer_base, rank_of, row_of, dout, dw)
+    _count()
+    return dw
+
+
+def ep_wait(flags, epoch: int, limit_s: float = 5.0) -> None:
+    ops().ep_wait(flags, epoch, status_word(flags.device), limit_s)
+    _count()
+
+
+def zero_pad_rows(buf, offsets, counts) -> None:
+    ops().zero_pad_rows(buf, offsets, counts)
+    _count()

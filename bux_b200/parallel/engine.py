@@ -1,0 +1,250 @@
+"""`Parallel`: what one rank knows about the mesh, and the explicit collectives of a step.
+
+One process per GPU (``torch.distributed``, NCCL on GPUs, gloo on CPU). The mesh's six
+axes become process groups; the trainer asks this object for its batch rows, hands it
+the model to shard (`prepare_model`), and calls it around the backward
+(`grad_sync`, `finish_grads`) and for scalars (`sum_scalar`, `max_int`).
+
+What is explicit here was implicit in the reference (GSPMD inserted it from sharding
+annotations, ``parallel/layout.py:95-220``, ``parallel/place.py:70-137``):
+data-parallel gradient all-reduce, ZeRO-1 / FSDP sharding of parameters and optimizer
+state (`fsdp.py`), tensor parallelism (`tensor.py`), expert parallelism
+(`experts.py`), pipeline stages (`pipeline.py`).
+"""
+
+from __future__ import annotations
+
+import os
+from contextlib import contextmanager
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from . import mesh as M
+
+
+class Parallel:
+    def __init__(self, train, device=None):
+        if not dist.is_initialized():
+            raise RuntimeError("torch.distributed is not initialised")
+        self.train = train
+        self.world = dist.get_world_size()
+        self.rank = dist.get_rank()
+        self.device = device if device is not None else torch.device("cpu")
+        self.shape = M.sizes(train.mesh, self.world)
+        if M.size(train.mesh, self.world) != self.world:
+            raise ValueError(f"the mesh {self.shape} needs {M.size(train.mesh, self.world)} devices, "
+                             f"and {self.world} joined")
+        self.coords = M.coordinates(self.rank, self.shape)
+        self._groups: dict = {}
+        layout = train.layout
+        batch_axes = tuple(a for a in M._axes_of(layout.batch) if self.shape[a] > 1)
+        self.batch_axes = batch_axes
+        # every rank creates every group, in the same order
+        for axes in self._all_axis_sets():
+            self._make_groups(axes)
+        self.data_group = self.group(batch_axes) if batch_axes else None
+        self.data_world = 1
+        for a in batch_axes:
+            self.data_world *= self.shape[a]
+        self.data_rank = self._index_in(batch_axes)
+        self.expert_group = self.group(("expert",)) if self.shape["expert"] > 1 else None
+        self.tensor_group = self.group(("tensor",)) if self.shape["tensor"] > 1 else None
+        self.stage_group = self.group(("stage",)) if self.shape["stage"] > 1 else None
+        self.replicated: list = []   # (param, group) whose gradients are summed over group
+        self._norm_w: dict = {}
+        self.fsdp = None
+
+    # ------------------------------------------------------------------ groups
+    def _all_axis_sets(self) -> list:
+        sets = [tuple(a for a in M._axes_of(self.train.layout.batch) if self.shape[a] > 1)]
+        sets += [(a,) for a in M.AXES if self.shape[a] > 1]
+        fs = tuple(a for a in M._axes_of(self.train.layout.fsdp) if self.shape[a] > 1)
+        sets.append(fs)
+        sets.append(tuple(a for a in M.AXES if self.shape[a] > 1 and a not in ("expert",)))
+        out = []
+        for s in sets:
+            if s and s not in out:
+                out.append(s)
+        return out
+
+    def _make_groups(self, axes: tuple) -> None:
+        seen = set()
+        for r in range(self.world):
+            ranks = tuple(M.group_ranks(r, self.shape, axes))
+            if ranks in seen:
+                continue
+            seen.add(ranks)
+            g = dist.new_group(list(ranks))
+            if self.rank in ranks:
+                self._groups[axes] = g
+
+    def group(self, axes: tuple):
+        axes = tuple(a for a in axes if self.shape[a] > 1)
+        if not axes:
+            return None
+        if axes not in self._groups:
+            raise KeyError(f"no process group over {axes}")
+        return self._groups[axes]
+
+    def _index_in(self, axes: tuple) -> int:
+        idx = 0
+        for a in M.AXES:
+            if a in axes:
+                idx = idx * self.shape[a] + self.coords[a]
+        return idx
+
+    # ------------------------------------------------------------------ the model
+    def prepare_model(self, model) -> None:
+        """Shard what the mesh shards: experts over ``expert``, then (tensor / fsdp) the
+        rest; what stays whole is marked for gradient all-reduce over the batch axes."""
+        from ..models.layers.moe import MoE
+        from .experts import ExpertParallel
+
+        t = self.train
+        expert_params = set()
+        if self.expert_group is not None:
+            me, n = dist.get_rank(self.expert_group), self.shape["expert"]
+            ep = ExpertParallel(self.expert_group, t.methods.moe, t.methods.capacity)
+            for m in model.modules():
+                if isinstance(m, MoE):
+                    el = m.c.num_experts // n
+                    for name in ("experts_gate_up", "experts_down"):
+                        p = getattr(m, name)
+                        local = torch.nn.Parameter(p.data[me * el:(me + 1) * el].clone())
+                        setattr(m, name, local)
+                        expert_params.add(local)
+                    m.ep = ep
+            self.ep = ep
+        if self.tensor_group is not None:
+            from . import tensor
+
+            tensor.shard_model(model, self)
+        fs_axes = tuple(a for a in M._axes_of(t.layout.fsdp) if self.shape[a] > 1 and a == "fsdp")
+        if fs_axes and self.shape["fsdp"] > 1:
+            from .fsdp import FSDP
+
+            self.fsdp = FSDP(model, self, skip=expert_params)
+        # gradients of whole (replicated) parameters are summed over the batch axes;
+        # expert shards are replicated only over the batch axes that are not `expert`
+        for name, p in model.named_parameters():
+            if getattr(p, "_bux_sharded", False):
+                continue
+            if p in expert_params:
+                axes = tuple(a for a in self.batch_axes if a != "expert")
+            else:
+                axes = self.batch_axes
+            g = self.group(axes) if axes else None
+            if g is not None:
+                self.replicated.append((p, g))
+                self._norm_w[name] = 1.0 / dist.get_world_size(g)
+        with torch.no_grad():
+            for p, g in self.replicated:
+                dist.broadcast(p.data, src=dist.get_global_rank(g, 0), group=g)
+
+    def norm_weight(self, name: str) -> float:
+        """Share of a parameter's squared gradient this rank contributes to the global
+        norm: 1 for shards, 1/replicas for replicated parameters (summed over all ranks)."""
+        return self._norm_w.get(name, 1.0)
+
+    # ------------------------------------------------------------------ gradients
+    @contextmanager
+    def grad_sync(self, model, last: bool):
+        if self.fsdp is not None:
+            with self.fsdp.microbatch(last):
+                yield
+        else:
+            yield
+
+    def finish_grads(self, model) -> None:
+        """Sum the gradients of replicated parameters over their replicas (bucketed)."""
+        if self.fsdp is not None:
+            self.fsdp.finish()
+        by_group: dict = {}
+        for p, g in self.replicated:
+            grad = getattr(p, "main_grad", None)
+            grad = grad if grad is not None else p.grad
+            if grad is not None:
+                by_group.setdefault(g, []).append(grad)
+        for g, grads in by_group.items():
+            bucket: list = []
+            size = 0
+            for grad in grads:
+                bucket.append(grad)
+                size += grad.numel() * grad.element_size()
+                if size >= 256 << 20:
+                    self._all_reduce_bucket(bucket, g)
+                    bucket, size = [], 0
+            if bucket:
+                self._all_reduce_bucket(bucket, g)
+
+    @staticmethod
+    def _all_reduce_bucket(grads: list, group) -> None:
+        by_dtype: dict = {}
+        for gr in grads:
+            by_dtype.setdefault(gr.dtype, []).append(gr)
+        for same in by_dtype.values():
+            flat = torch.cat([gr.reshape(-1) for gr in same])
+            dist.all_reduce(flat, group=group)
+            off = 0
+            for gr in same:
+                n = gr.numel()
+                gr.copy_(flat[off:off + n].view_as(gr))
+                off += n
+
+    # ------------------------------------------------------------------ scalars
+    def sum_scalar(self, t: torch.Tensor, data_only: bool = False) -> torch.Tensor:
+        g = self.data_group if data_only else None
+        if data_only and g is None:
+            return t
+        dist.all_reduce(t, group=g)
+        return t
+
+    def max_int(self, value: int) -> int:
+        t = torch.tensor([value], dtype=torch.int64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return int(t.item())
+
+    def barrier(self) -> None:
+        dist.barrier()
+
+    # ------------------------------------------------------------------ checkpoints
+    def checkpoint_tree(self, trainer, state_tree):
+        """The tree this rank writes: rank 0 writes whole leaves; shards are gathered to
+        it first (parameters here are small next to a node's host memory)."""
+        tree = state_tree(trainer)
+        if self.fsdp is not None:
+            tree = self.fsdp.gather_tree(tree)
+        if self.expert_group is not None:
+            tree = _gather_experts(tree, self.expert_group)
+        return tree if self.rank == 0 else None
+
+
+def _gather_experts(tree: dict, group) -> dict:
+    world = dist.get_world_size(group)
+    for part in tree.values():
+        for name in list(part):
+            if "experts_gate_up" in name or "experts_down" in name:
+                t = part[name]
+                full = [torch.empty_like(t) for _ in range(world)]
+                dist.all_gather(full, t.contiguous(), group=group)
+                part[name] = torch.cat(full, dim=0) if t.dim() >= 3 else torch.cat(full)
+    return tree
+
+
+def init_distributed(device: Optional[torch.device] = None) -> bool:
+    """Join the job the environment describes (torchrun / SLURM / Open MPI variables).
+    Returns whether there is more than one process."""
+    env = os.environ
+    world = int(env.get("WORLD_SIZE") or env.get("SLURM_STEP_NUM_TASKS") or env.get("OMPI_COMM_WORLD_SIZE") or 1)
+    if world <= 1:
+        return False
+    if not dist.is_initialized():
+        rank = int(env.get("RANK") or env.get("SLURM_PROCID") or env.get("OMPI_COMM_WORLD_RANK") or 0)
+        env.setdefault("MASTER_ADDR", "127.0.0.1")
+        env.setdefault("MASTER_PORT", "29500")
+        backend = "nccl" if device is not None and device.type == "cuda" else "gloo"
+        kw = {"device_id": device} if backend == "nccl" else {}
+        dist.init_process_group(backend, rank=rank, world_size=world, **kw)
+    return True

@@ -1,0 +1,88 @@
+"""Multi-GPU paths: NCCL ranks as child processes (needs >= 2 GPUs, else skipped).
+NVLS is switched off for these short-lived test ranks."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+MOE = """
+d_model=256
+vocab_size=512
+n = rmsnorm
+a = gqa(num_heads=4, num_kv_heads=2, head_dim=64, rope=rope())
+e = moe(num_experts=8, top_k=2, expert=gated_mlp(intermediate_size=128, activation=swish))
+block = [n a] [n e]
+model = embed block^2 n head
+data = synthetic
+optimizer = adamw(lr=1e-3, eps=1.0)
+seq_len = 256
+batch = 8
+steps = 4
+methods = methods(remat=full)
+"""
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, overrides, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import torch.distributed as dist
+
+    from bux_b200.lang import compile_runs
+    from bux_b200.ops import kernels as K
+    from bux_b200.parallel.engine import Parallel
+    from bux_b200.train.trainer import Trainer
+
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    run = compile_runs(MOE, filename="p.bux", overrides=overrides)[0]
+    par = Parallel(run.train, dev)
+    tr = Trainer(run, device=dev, parallel=par)
+    feed = iter(tr.batches())
+    losses = [tr.train_step(next(feed))["loss"].item() for _ in range(2)]
+    torch.cuda.synchronize()
+    K.check_status(dev, "ep test")
+    if rank == 0:
+        torch.save({"losses": losses,
+                    "state": {n: p.detach().float().cpu() for n, p in tr.model.named_parameters()}}, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("fmt", ["compute", "mxfp8"])
+def test_fused_expert_parallel_matches_one_gpu(cuda, tmp_path, fmt):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+
+    from bux_b200.lang import compile_runs
+    from bux_b200.train.trainer import Trainer
+
+    prec = f"precision = precision(compute=bfloat16, matmuls={fmt})"
+    run = compile_runs(MOE, filename="p.bux", overrides=[prec])[0]
+    tr = Trainer(run, device=cuda)
+    feed = iter(tr.batches())
+    want = [tr.train_step(next(feed))["loss"].item() for _ in range(2)]
+    state = {n: p.detach().float().cpu() for n, p in tr.model.named_parameters()}
+    out = str(tmp_path / "r0.pt")
+    mp.spawn(_worker, args=(2, _free_port(), [prec, "mesh = mesh(expert=2)", "methods.moe = fused_ep",
+                                              "methods.capacity = 2.0"], out), nprocs=2, join=True)
+    got = torch.load(out)
+    assert got["losses"] == pytest.approx(want, abs=3e-2)
+    for name, p in state.items():
+        g = got["state"][name]
+        if "experts_" in name:
+            p = p[: g.shape[0]]
+        err = ((g - p).norm() / p.norm().clamp_min(1e-9)).item()
+        assert err < 2e-2, (name, err)

@@ -1,0 +1,88 @@
+"""Multi-rank logic on CPU: gloo ranks spawned as processes, compared with one rank."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from bux_b200.lang import compile_runs
+
+MOE = """
+d_model=32
+vocab_size=64
+n = rmsnorm
+a = gqa(num_heads=2, num_kv_heads=1, rope=rope())
+e = moe(num_experts=4, top_k=2, expert=gated_mlp(intermediate_size=16, activation=swish))
+block = [n a] [n e]
+model = embed block^2 n head
+data = synthetic
+optimizer = adamw(lr=1e-2, eps=1.0)
+seq_len = 16
+batch = 8
+steps = 4
+precision = precision(compute=float32)
+"""
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, src, overrides, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from bux_b200.parallel.engine import Parallel
+    from bux_b200.train.trainer import Trainer
+
+    torch.set_num_threads(1)
+    run = compile_runs(src, filename="p.bux", overrides=overrides)[0]
+    par = Parallel(run.train, torch.device("cpu"))
+    tr = Trainer(run, device="cpu", parallel=par)
+    feed = iter(tr.batches())
+    losses = [tr.train_step(next(feed))["loss"].item() for _ in range(2)]
+    state = {n: p.detach().clone() for n, p in tr.model.named_parameters()}
+    if rank == 0:
+        torch.save({"losses": losses, "state": state}, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _single(src, overrides=()):
+    from bux_b200.train.trainer import Trainer
+
+    run = compile_runs(src, filename="p.bux", overrides=list(overrides))[0]
+    tr = Trainer(run, device="cpu")
+    feed = iter(tr.batches())
+    losses = [tr.train_step(next(feed))["loss"].item() for _ in range(2)]
+    return losses, {n: p.detach().clone() for n, p in tr.model.named_parameters()}
+
+
+def _spawn(world, src, overrides, tmp_path):
+    out = str(tmp_path / "rank0.pt")
+    mp.spawn(_worker, args=(world, _free_port(), src, list(overrides), out), nprocs=world, join=True)
+    return torch.load(out)
+
+
+def test_data_parallel_matches_one_rank(tmp_path):
+    want_losses, want = _single(MOE)
+    got = _spawn(2, MOE, ["mesh = mesh(data=2)"], tmp_path)
+    assert got["losses"] == pytest.approx(want_losses, abs=1e-5)
+    for name, p in want.items():
+        assert torch.allclose(got["state"][name], p, atol=1e-5), name
+
+
+def test_expert_parallel_matches_one_rank(tmp_path):
+    want_losses, want = _single(MOE)
+    got = _spawn(2, MOE, ["mesh = mesh(expert=2)", "methods.moe = all_to_all", "methods.capacity = 4.0"], tmp_path)
+    assert got["losses"] == pytest.approx(want_losses, abs=1e-5)
+    for name, p in want.items():
+        g = got["state"][name]
+        if "experts_" in name:
+            p = p[: g.shape[0]]  # rank 0 holds the first half of the experts
+        assert torch.allclose(g, p, atol=1e-5), name
