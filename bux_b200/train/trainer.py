@@ -100,6 +100,7 @@ class Trainer:
         self.fuse_optimizer = fuse_optimizer
         self._pending_factor = None
         self._prev_norm_sq = None
+        self._norm_acc = None
         self._hooks_installed = False
         self.stretches = curriculum.stretches(t)
         self.timers = Timers()
@@ -191,7 +192,18 @@ class Trainer:
         if self.parallel is not None:
             self.parallel.finish_grads(self.model)
         if self.fuse_optimizer:
-            norm = None if self._prev_norm_sq is None else self._prev_norm_sq.sqrt()
+            # parameters whose gradients had to be summed over ranks first are updated now,
+            # with the same (delayed) clip factor as the ones updated during the backward
+            lr_s, factor = self._release
+            for name, p in self.model.named_parameters():
+                g = self.optimizer.grad_of(p)
+                if g is None or not p.requires_grad:
+                    continue
+                self._add_norm(g, p.device, self.parallel.norm_weight(name) if self.parallel else 1.0)
+                self.optimizer.update_param(name, p, lr_s, 1.0, factor)
+            if self._norm_acc is not None and self.parallel is not None:
+                self._norm_acc = self.parallel.sum_scalar(self._norm_acc)
+            norm = None if self._norm_acc is None else self._norm_acc.sqrt()
             self._prev_norm_sq = self._norm_acc
             self._norm_acc = None
         else:
@@ -213,26 +225,31 @@ class Trainer:
         if self._hooks_installed:
             return
         self._hooks_installed = True
-        self._norm_acc = None
         names = {p: n for n, p in self.model.named_parameters()}
+        later = {id(p) for p, _ in self.parallel.replicated} if self.parallel is not None else set()
 
         def hook(p):
             lr_scale, factor = self._release
             g = self.optimizer.grad_of(p)
-            if g is not None and self.train.clip is not None:
-                if self._norm_acc is None:
-                    self._norm_acc = torch.zeros(1, dtype=torch.float32, device=p.device)
-                if g.is_cuda and g.is_contiguous() and g.dtype in (torch.float32, torch.bfloat16):
-                    from ..ops import kernels as K
-
-                    K.sumsq(g, self._norm_acc)
-                else:
-                    self._norm_acc += g.float().square().sum()
+            if g is not None:
+                self._add_norm(g, p.device, 1.0)
             self.optimizer.update_param(names[p], p, lr_scale, 1.0, factor)
 
         for p in self.model.parameters():
-            if p.requires_grad:
+            if p.requires_grad and id(p) not in later:
                 p.register_post_accumulate_grad_hook(hook)
+
+    def _add_norm(self, g, device, weight: float) -> None:
+        if self.train.clip is None:
+            return
+        if self._norm_acc is None:
+            self._norm_acc = torch.zeros(1, dtype=torch.float32, device=device)
+        if weight == 1.0 and g.is_cuda and g.is_contiguous() and g.dtype in (torch.float32, torch.bfloat16):
+            from ..ops import kernels as K
+
+            K.sumsq(g, self._norm_acc)
+        else:
+            self._norm_acc += g.float().square().sum() * weight
 
     def _delayed_clip_factor(self):
         """With the update fused into the backward the step's own norm is not known
