@@ -225,30 +225,45 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
         }
         if (m_ref == -INFINITY) m_ref = mx;
       }
+      // rows whose whole tile is visible skip the per-element mask
+      const bool full_row = kv0 + KT - 1 <= hi_key && kv0 >= lo_key && kv0 + KT <= p.S;
       for (int attempt = 0; attempt < 2; ++attempt) {
         float sum = 0.f, mx = -INFINITY;
         const float ref = m_ref == -INFINITY ? 0.f : m_ref;
-#pragma unroll 1
-        for (int c = 0; c < KT; c += 32) {
-          uint32_t v[32];
-          tmem_ld_x32(t_s + c, v);
+        uint32_t v[2][32];
+        tmem_ld_x32(t_s, v[0]);
+#pragma unroll
+        for (int ci = 0; ci < KT / 32; ++ci) {
+          const int c = ci * 32;
           tmem_ld_wait();
+          // the next chunk's load runs while this one is turned into probabilities
+          if (ci + 1 < KT / 32) tmem_ld_x32(t_s + c + 32, v[(ci + 1) & 1]);
+          const uint32_t(&cur)[32] = v[ci & 1];
           uint32_t packed[16];
+          if (full_row) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float pr[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int kv = kv0 + c + i + e;
-              const bool keep = kv < p.S && kv <= hi_key && kv >= lo_key;
-              const float sv = __uint_as_float(v[i + e]) * p.scale_log2;
-              if (keep) mx = fmaxf(mx, sv);
-              pr[e] = keep ? exp2f(sv - ref) : 0.f;
+            for (int i = 0; i < 32; i += 2) {
+              const float s0 = __uint_as_float(cur[i]) * p.scale_log2, s1 = __uint_as_float(cur[i + 1]) * p.scale_log2;
+              mx = fmaxf(mx, fmaxf(s0, s1));
+              const float p0 = exp2f(s0 - ref), p1 = exp2f(s1 - ref);
+              sum += p0 + p1;
+              packed[i >> 1] = pack_bf16(p0, p1);
             }
-            const uint32_t pk = pack_bf16(pr[0], pr[1]);
-            const float2 back = unpack_bf16(pk);
-            sum += back.x + back.y;
-            packed[i >> 1] = pk;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              float pr[2];
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const int kv = kv0 + c + i + e;
+                const bool keep = kv < p.S && kv <= hi_key && kv >= lo_key;
+                const float sv = __uint_as_float(cur[i + e]) * p.scale_log2;
+                if (keep) mx = fmaxf(mx, sv);
+                pr[e] = keep ? exp2f(sv - ref) : 0.f;
+              }
+              sum += pr[0] + pr[1];
+              packed[i >> 1] = pack_bf16(pr[0], pr[1]);
+            }
           }
           uint8_t* chunk = myP + (c >> 6) * 16384 + r * 128;
 #pragma unroll
