@@ -8,8 +8,9 @@
 //    whole walk and are written once (no atomics, no per-head partials to reduce).
 //    Per step, on the tensor core:  S = Q·K^T,  dP = dO·V^T,  then with
 //    P = exp(S·scale − lse) and dS = P∘(dP − delta)·scale written to shared memory by
-//    the softmax warps:  dV += P^T·dO,  dK += dS^T·Q,  dQ = dS·K. dQ leaves through
-//    fp32 vector atomics (different key tiles add to the same query rows).
+//    the softmax warps:  dV += P^T·dO,  dK += dS^T·Q,  dQ = dS·K. dQ (different key
+//    tiles add to the same query rows) is staged in the P / dS buffers once the step's
+//    MMAs are done and leaves as TMA reduce-adds of fp32, one per warp and 32 columns.
 //    The [rows x 64-column] swizzled tiles that TMA writes serve both as K-major
 //    operands (contraction along the head dim) and as MN-major operands (contraction
 //    along the rows); only the descriptors differ.
@@ -60,6 +61,7 @@ struct AttnBwdParams {
   alignas(64) CUtensorMap tmap_do;
   alignas(64) CUtensorMap tmap_k;
   alignas(64) CUtensorMap tmap_v;
+  alignas(64) CUtensorMap tmap_dq;
   const float* lse; const float* delta;
   float* dq; void* dk; void* dv; Status* status;
   int B, T, S, H, G;
@@ -194,7 +196,7 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
     }
   } else {
     // -------------------------------------------------------------- softmax / drain warps
-    const int r = threadIdx.x;
+    const int r = threadIdx.x, lane = threadIdx.x & 31;
     const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
     bool ok = true;
     for (int s = 0; s < n_steps && ok; ++s) {
@@ -209,25 +211,49 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
       ok = warp_all(mbar_wait(sdp_full, s & 1, abort_flag, st, KID_ATTN_BWD, 6));
       if (!ok) break;
       tc_fence_after();
-#pragma unroll 1
-      for (int c = 0; c < BT; c += 32) {
-        uint32_t sv[32], dv[32];
-        tmem_ld_x32(t_s + lane_addr + c, sv);
-        tmem_ld_x32(t_dp + lane_addr + c, dv);
+      // the dQ tile of the previous step was staged where P and dS go: its reduction must
+      // have read this warp's rows before they are overwritten
+      if (lane == 0) tma_store_wait_read();
+      __syncwarp();
+      const bool full_row = row_ok && kv0 + BT - 1 <= hi_key && kv0 >= lo_key && kv0 + BT <= p.S && lse2 > -INFINITY;
+      const bool any_row = row_ok && lse2 > -INFINITY;
+      uint32_t sv[2][32], dv[2][32];
+      tmem_ld_x32(t_s + lane_addr, sv[0]);
+      tmem_ld_x32(t_dp + lane_addr, dv[0]);
+#pragma unroll
+      for (int ci = 0; ci < BT / 32; ++ci) {
+        const int c = ci * 32;
         tmem_ld_wait();
+        if (ci + 1 < BT / 32) {
+          tmem_ld_x32(t_s + lane_addr + c + 32, sv[(ci + 1) & 1]);
+          tmem_ld_x32(t_dp + lane_addr + c + 32, dv[(ci + 1) & 1]);
+        }
+        const uint32_t(&cs)[32] = sv[ci & 1];
+        const uint32_t(&cd)[32] = dv[ci & 1];
         uint32_t pp[16], ds[16];
+        if (full_row) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float pr[2], dr[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int kv = kv0 + c + i + e;
-            const bool keep = row_ok && kv < p.S && kv <= hi_key && kv >= lo_key && lse2 > -INFINITY;
-            pr[e] = keep ? exp2f(__uint_as_float(sv[i + e]) * p.scale_log2 - lse2) : 0.f;
-            dr[e] = pr[e] * (__uint_as_float(dv[i + e]) - dlt) * p.scale;
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = exp2f(__uint_as_float(cs[i]) * p.scale_log2 - lse2);
+            const float p1 = exp2f(__uint_as_float(cs[i + 1]) * p.scale_log2 - lse2);
+            pp[i >> 1] = pack_bf16(p0, p1);
+            ds[i >> 1] = pack_bf16(p0 * (__uint_as_float(cd[i]) - dlt) * p.scale,
+                                   p1 * (__uint_as_float(cd[i + 1]) - dlt) * p.scale);
           }
-          pp[i >> 1] = pack_bf16(pr[0], pr[1]);
-          ds[i >> 1] = pack_bf16(dr[0], dr[1]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float pr[2], dr[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int kv = kv0 + c + i + e;
+              const bool keep = any_row && kv < p.S && kv <= hi_key && kv >= lo_key;
+              pr[e] = keep ? exp2f(__uint_as_float(cs[i + e]) * p.scale_log2 - lse2) : 0.f;
+              dr[e] = pr[e] * (__uint_as_float(cd[i + e]) - dlt) * p.scale;
+            }
+            pp[i >> 1] = pack_bf16(pr[0], pr[1]);
+            ds[i >> 1] = pack_bf16(dr[0], dr[1]);
+          }
         }
         const int base = (c >> 6) * 16384 + r * 128;
 #pragma unroll
@@ -240,26 +266,40 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(p_ready);
-      // drain dQ of this step
+      // dQ of this step: tensor memory -> this warp's rows of the staging tiles (the P / dS
+      // buffers, free once the step's MMAs have completed) -> one reduce-add per 32 columns
       ok = warp_all(mbar_wait(dq_full, s & 1, abort_flag, st, KID_ATTN_BWD, 7));
       if (!ok) break;
       tc_fence_after();
-      float* dqrow = p.dq + (((size_t)b * p.T + (row_ok ? q : 0)) * p.H + h) * D;
-#pragma unroll 1
-      for (int c = 0; c < D; c += 32) {
-        uint32_t v[32];
-        tmem_ld_x32(t_dp + lane_addr + c, v);
-        tmem_ld_wait();
-        if (row_ok) {
+      {
+        uint32_t v[2][32];
+        tmem_ld_x32(t_dp + lane_addr, v[0]);
 #pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            atomicAdd(reinterpret_cast<float4*>(dqrow + c + i),
-                      make_float4(__uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])));
+        for (int ci = 0; ci < D / 32; ++ci) {
+          tmem_ld_wait();
+          if (ci + 1 < D / 32) tmem_ld_x32(t_dp + lane_addr + (ci + 1) * 32, v[(ci + 1) & 1]);
+          const uint32_t(&cur)[32] = v[ci & 1];
+          uint8_t* dst = sP + ci * 16384 + r * 128;
+#pragma unroll
+          for (int sl = 0; sl < 8; ++sl)
+            *reinterpret_cast<uint4*>(dst + ((sl ^ (r & 7)) << 4)) =
+                make_uint4(cur[4 * sl], cur[4 * sl + 1], cur[4 * sl + 2], cur[4 * sl + 3]);
         }
       }
       tc_fence_before();
       mbar_arrive(dq_done);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        const int row0 = b * p.T + (i_lo + s % per_head) * BT + warp * 32;
+#pragma unroll
+        for (int ci = 0; ci < D / 32; ++ci)
+          tma_reduce_add_2d(&p.tmap_dq, sP + ci * 16384 + warp * 4096, h * D + ci * 32, row0);
+        tma_store_commit();
+      }
     }
+    if (lane == 0) tma_store_wait_all();
+    __syncwarp();
     // dK / dV of this key tile: complete once the last step's MMAs have (dq_full waited above)
     // tcgen05.ld is warp-collective: every thread of the warp takes part, only the
     // stores are masked.
@@ -314,6 +354,7 @@ static const char* attn_bwd_launch_d(const AttnArgs& a, cudaStream_t stream) {
   if ((err = make_tmap_2d(&p.tmap_do, a.d_o, 2, (uint64_t)a.B * a.T, qw, qw * 2, 64, BT))) return err;
   if ((err = make_tmap_2d(&p.tmap_k, a.k, 2, (uint64_t)a.B * a.S, kw, kw * 2, 64, BT))) return err;
   if ((err = make_tmap_2d(&p.tmap_v, a.v, 2, (uint64_t)a.B * a.S, kw, kw * 2, 64, BT))) return err;
+  if ((err = make_tmap_2d(&p.tmap_dq, a.dq, 4, (uint64_t)a.B * a.T, qw, qw * 4, 32, 32))) return err;
   p.lse = a.lse; p.delta = a.delta; p.dq = reinterpret_cast<float*>(a.dq); p.dk = a.dk; p.dv = a.dv;
   p.status = a.status;
   p.B = a.B; p.T = a.T; p.S = a.S; p.H = a.H; p.G = a.G;

@@ -368,7 +368,8 @@ const char* make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uin
   if (!bound) { cudaFree(nullptr); bound = true; }
   if (reinterpret_cast<uintptr_t>(base) % 16 != 0) return "tensor base is not 16-byte aligned";
   if (row_stride_bytes % 16 != 0) return "row stride is not a multiple of 16 bytes";
-  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUtensorMapDataType dt = elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                         : elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {row_stride_bytes};
   cuuint32_t box[2] = {box_cols, box_rows};

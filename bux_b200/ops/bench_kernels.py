@@ -92,9 +92,15 @@ def bench_grouped(rows: list, pk: dict) -> None:
                  "tflops": flops / ms / 1e9, "of_peak": flops / ms / 1e9 / pk["bf16_tflops"]})
 
 
+SMALL = False
+
+
 def bench_attention(rows: list, pk: dict) -> None:
     dev = "cuda"
-    for b, t, h, g, d in [(8, 4096, 32, 4, 128), (8, 4096, 16, 8, 128), (4, 4096, 64, 8, 64)]:
+    shapes = [(8, 4096, 32, 4, 128), (8, 4096, 16, 8, 128), (4, 4096, 64, 8, 64)]
+    if SMALL:  # a profiler-sized case: same kernel and tile walk, 2 sequences
+        shapes = [(2, 4096, 32, 4, 128)]
+    for b, t, h, g, d in shapes:
         q = torch.randn(b, t, h, d, device=dev).bfloat16()
         k = torch.randn(b, t, g, d, device=dev).bfloat16()
         v = torch.randn(b, t, g, d, device=dev).bfloat16()
@@ -144,7 +150,10 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default=None)
     ap.add_argument("--only", default="")
+    ap.add_argument("--small", action="store_true", help="profiler-sized shapes (attention only)")
     args = ap.parse_args()
+    global SMALL
+    SMALL = args.small
     pk = peaks()
     rows: list = []
     for name, fn in (("gemm", bench_gemm), ("grouped", bench_grouped), ("attention", bench_attention),
