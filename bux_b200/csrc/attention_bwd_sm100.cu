@@ -25,7 +25,7 @@ namespace bux {
 
 constexpr int KID_ATTN_BWD = 3;
 constexpr int BT = 128;
-constexpr int BWD_THREADS = 192;
+constexpr int BWD_THREADS = 320;  // 8 softmax warps (two per TMEM lane quadrant), TMA warp, MMA warp
 constexpr float LOG2E_B = 1.4426950408889634f;
 
 // one warp per (b, t, h) row of D elements
@@ -116,18 +116,18 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(qdo_empty, 1); mbar_init(sdp_full, 1);
-    mbar_init(p_ready, 128); mbar_init(dq_full, 1); mbar_init(dq_done, 128);
+    mbar_init(p_ready, 256); mbar_init(dq_full, 1); mbar_init(dq_done, 256);
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 5) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
+  if (warp == 9) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dv = tmem_base + 256, t_dk = tmem_base + 384;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // -------------------------------------------------------------- TMA producer
     if (elect_one() && n_steps > 0) {
       mbar_expect_tx(kv_full, 2 * Cfg::TILE_BYTES);
@@ -146,7 +146,7 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // -------------------------------------------------------------- MMA issuer
     if (elect_one() && n_steps > 0) {
       const uint32_t id_s = make_idesc(FMT_BF16, FMT_BF16, 128, BT, false, false);
@@ -196,8 +196,11 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
     }
   } else {
     // -------------------------------------------------------------- softmax / drain warps
-    const int r = threadIdx.x, lane = threadIdx.x & 31;
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    // Two warps share each 32-lane quadrant of tensor memory: warps 0-3 take the first 64
+    // columns of S / dP, warps 4-7 the other 64, so each scheduler has two warps to
+    // interleave and the exp / dS chain per step is half as long.
+    const int r = threadIdx.x & 127, lane = threadIdx.x & 31, half = warp >> 2;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     bool ok = true;
     for (int s = 0; s < n_steps && ok; ++s) {
       const int h = g * hpg + s / per_head;
@@ -217,19 +220,14 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
       __syncwarp();
       const bool full_row = row_ok && kv0 + BT - 1 <= hi_key && kv0 >= lo_key && kv0 + BT <= p.S && lse2 > -INFINITY;
       const bool any_row = row_ok && lse2 > -INFINITY;
-      uint32_t sv[2][32], dv[2][32];
-      tmem_ld_x32(t_s + lane_addr, sv[0]);
-      tmem_ld_x32(t_dp + lane_addr, dv[0]);
-#pragma unroll
-      for (int ci = 0; ci < BT / 32; ++ci) {
-        const int c = ci * 32;
+      const int c_first = half * 64;
+#pragma unroll 1
+      for (int ci = 0; ci < 2; ++ci) {
+        const int c = c_first + ci * 32;
+        uint32_t cs[32], cd[32];
+        tmem_ld_x32(t_s + lane_addr + c, cs);
+        tmem_ld_x32(t_dp + lane_addr + c, cd);
         tmem_ld_wait();
-        if (ci + 1 < BT / 32) {
-          tmem_ld_x32(t_s + lane_addr + c + 32, sv[(ci + 1) & 1]);
-          tmem_ld_x32(t_dp + lane_addr + c + 32, dv[(ci + 1) & 1]);
-        }
-        const uint32_t(&cs)[32] = sv[ci & 1];
-        const uint32_t(&cd)[32] = dv[ci & 1];
         uint32_t pp[16], ds[16];
         if (full_row) {
 #pragma unroll
@@ -255,10 +253,10 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
             ds[i >> 1] = pack_bf16(dr[0], dr[1]);
           }
         }
-        const int base = (c >> 6) * 16384 + r * 128;
+        const int base = half * 16384 + r * 128;
 #pragma unroll
         for (int sl = 0; sl < 4; ++sl) {
-          const int slot = (((c & 63) >> 3) + sl) ^ (r & 7);
+          const int slot = ((ci << 2) + sl) ^ (r & 7);
           *reinterpret_cast<uint4*>(sP + base + (slot << 4)) = make_uint4(pp[4 * sl], pp[4 * sl + 1], pp[4 * sl + 2], pp[4 * sl + 3]);
           *reinterpret_cast<uint4*>(sdS + base + (slot << 4)) = make_uint4(ds[4 * sl], ds[4 * sl + 1], ds[4 * sl + 2], ds[4 * sl + 3]);
         }
@@ -271,19 +269,21 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
       ok = warp_all(mbar_wait(dq_full, s & 1, abort_flag, st, KID_ATTN_BWD, 7));
       if (!ok) break;
       tc_fence_after();
+      // This warp stages the 32-column chunks half, half+2, ... of its 32 rows: the
+      // same shared-memory rows it writes P and dS to, so every hazard on the staging
+      // tiles stays inside the warp.
       {
-        uint32_t v[2][32];
-        tmem_ld_x32(t_dp + lane_addr, v[0]);
+        uint32_t v[D / 64][32];
 #pragma unroll
-        for (int ci = 0; ci < D / 32; ++ci) {
-          tmem_ld_wait();
-          if (ci + 1 < D / 32) tmem_ld_x32(t_dp + lane_addr + (ci + 1) * 32, v[(ci + 1) & 1]);
-          const uint32_t(&cur)[32] = v[ci & 1];
-          uint8_t* dst = sP + ci * 16384 + r * 128;
+        for (int j = 0; j < D / 64; ++j) tmem_ld_x32(t_dp + lane_addr + (half + 2 * j) * 32, v[j]);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < D / 64; ++j) {
+          uint8_t* dst = sP + (half + 2 * j) * 16384 + r * 128;
 #pragma unroll
           for (int sl = 0; sl < 8; ++sl)
             *reinterpret_cast<uint4*>(dst + ((sl ^ (r & 7)) << 4)) =
-                make_uint4(cur[4 * sl], cur[4 * sl + 1], cur[4 * sl + 2], cur[4 * sl + 3]);
+                make_uint4(v[j][4 * sl], v[j][4 * sl + 1], v[j][4 * sl + 2], v[j][4 * sl + 3]);
         }
       }
       tc_fence_before();
@@ -291,10 +291,12 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        const int row0 = b * p.T + (i_lo + s % per_head) * BT + warp * 32;
+        const int row0 = b * p.T + (i_lo + s % per_head) * BT + (warp & 3) * 32;
 #pragma unroll
-        for (int ci = 0; ci < D / 32; ++ci)
-          tma_reduce_add_2d(&p.tmap_dq, sP + ci * 16384 + warp * 4096, h * D + ci * 32, row0);
+        for (int j = 0; j < D / 64; ++j) {
+          const int ci = half + 2 * j;
+          tma_reduce_add_2d(&p.tmap_dq, sP + ci * 16384 + (warp & 3) * 4096, h * D + ci * 32, row0);
+        }
         tma_store_commit();
       }
     }
@@ -310,7 +312,7 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
       __nv_bfloat16* dkrow = reinterpret_cast<__nv_bfloat16*>(p.dk) + (((size_t)b * p.S + (store ? kv : 0)) * p.G + g) * D;
       __nv_bfloat16* dvrow = reinterpret_cast<__nv_bfloat16*>(p.dv) + (((size_t)b * p.S + (store ? kv : 0)) * p.G + g) * D;
 #pragma unroll 1
-      for (int c = 0; c < D; c += 32) {
+      for (int c = half * (D / 2); c < (half + 1) * (D / 2); c += 32) {
         uint32_t a[32], bb[32];
         if (n_steps > 0 && all_ok) {
           tmem_ld_x32(t_dk + lane_addr + c, a);
@@ -341,7 +343,7 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, Cfg::TMEM_COLS); }
+  if (warp == 9) { tc_fence_after(); tmem_dealloc(tmem_base, Cfg::TMEM_COLS); }
 }
 
 template <int D>
