@@ -130,8 +130,9 @@ class Parallel:
         # expert shards are replicated only over the batch axes that are not `expert`
         for name, p in model.named_parameters():
             if getattr(p, "_bux_sharded", False):
-                continue
-            if p in expert_params:
+                # the reduce-scatter summed over `fsdp`; other replicas (HSDP) all-reduce
+                axes = tuple(a for a in self.batch_axes if a != "fsdp")
+            elif p in expert_params:
                 axes = tuple(a for a in self.batch_axes if a != "expert")
             else:
                 axes = self.batch_axes

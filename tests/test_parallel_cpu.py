@@ -86,3 +86,34 @@ def test_expert_parallel_matches_one_rank(tmp_path):
         if "experts_" in name:
             p = p[: g.shape[0]]  # rank 0 holds the first half of the experts
         assert torch.allclose(g, p, atol=1e-5), name
+
+
+def _check_rows(got, want, world=2):
+    """Rank 0 holds the first rows of every sharded parameter."""
+    for name, p in want.items():
+        g = got["state"][name]
+        if g.shape != p.shape:
+            p = p[: g.shape[0]]
+        assert torch.allclose(g, p, atol=1e-5), name
+
+
+@pytest.mark.parametrize("extra", [
+    [],                                   # ZeRO-3: gather per block
+    ["methods.remat = full"],             # ... and again in the replay of each block
+    ["layout = layout(zero=1)"],          # whole parameters for the step, sharded optimizer state
+    ["methods.microbatches = 2"],
+])
+def test_fsdp_matches_one_rank(tmp_path, extra):
+    base = [e for e in extra if "microbatches" in e]
+    want_losses, want = _single(MOE, base)
+    got = _spawn(2, MOE, ["mesh = mesh(fsdp=2)", *extra], tmp_path)
+    assert got["losses"] == pytest.approx(want_losses, abs=1e-5)
+    _check_rows(got, want)
+    assert any(got["state"][n].shape != p.shape for n, p in want.items())  # something was sharded
+
+
+def test_hsdp_matches_one_rank(tmp_path):
+    want_losses, want = _single(MOE)
+    got = _spawn(4, MOE, ["mesh = mesh(data=2, fsdp=2)"], tmp_path)
+    assert got["losses"] == pytest.approx(want_losses, abs=1e-5)
+    _check_rows(got, want)
