@@ -214,7 +214,7 @@ class MLP(nn.Module):
         if self.gated:
             h = self.gate_up(x, ctx)
             if c.up_softcap is not None:
-                f = c.intermediate_size
+                f = getattr(self, "f_local", c.intermediate_size)
                 up = c.up_softcap * torch.tanh(h[..., f:].float() / c.up_softcap)
                 h = torch.cat((h[..., :f], up.to(h.dtype)), dim=-1)
             a = ops.glu(h, c.activation, None, c.limit, c.up_offset)

@@ -40,6 +40,17 @@ def limit_groups(choice: torch.Tensor, groups: int, keep: int) -> torch.Tensor:
     return torch.where(kept.unsqueeze(-1), grouped, torch.full_like(grouped, float("-inf"))).view(b, t, n)
 
 
+class _ScaleGrad(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, share):
+        ctx.share = share
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g * ctx.share, None
+
+
 class MoE(nn.Module):
     def __init__(self, c: L.MoEConfig, b: BuildContext):
         super().__init__()
@@ -51,6 +62,7 @@ class MoE(nn.Module):
         d = b.width if isinstance(b.width, int) else b.d_model
         e, f = c.num_experts, c.expert.intermediate_size
         self.d, self.e, self.f = d, e, f
+        self.tp_share = 1.0
         self.router = Linear(d, e + (c.num_shared_experts if c.shared_expert_sink else 0),
                              c.router_bias, b, role="router")
         self.router.weight.data = self.router.weight.data.float()
@@ -92,7 +104,9 @@ class MoE(nn.Module):
             picks = torch.zeros_like(scores).scatter_add_(-1, idx, torch.ones_like(idx, dtype=scores.dtype))
             w = c.aux_loss_weight
             if w:
-                ctx.report("balance_loss", balance_loss(scores, picks, c.top_k, c.aux_loss_scope == "sequence"), w)
+                # under tensor parallelism every rank reports the same loss: each gives 1/n of its gradient
+                seen = scores if self.tp_share == 1.0 else _ScaleGrad.apply(scores, self.tp_share)
+                ctx.report("balance_loss", balance_loss(seen, picks, c.top_k, c.aux_loss_scope == "sequence"), w)
             if hasattr(self, "router_load"):
                 self.router_load += picks.detach().sum((0, 1))
         weights = scores.gather(-1, idx)

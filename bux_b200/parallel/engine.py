@@ -55,6 +55,8 @@ class Parallel:
         self.replicated: list = []   # (param, group) whose gradients are summed over group
         self._norm_w: dict = {}
         self.fsdp = None
+        self.tensor_sharded: set = set()
+        self.tensor_layout: dict = {}
 
     # ------------------------------------------------------------------ groups
     def _all_axis_sets(self) -> list:
@@ -137,12 +139,20 @@ class Parallel:
             else:
                 axes = self.batch_axes
             g = self.group(axes) if axes else None
+            copies = 1
             if g is not None:
                 self.replicated.append((p, g))
-                self._norm_w[name] = 1.0 / dist.get_world_size(g)
+                copies = dist.get_world_size(g)
+            if self.tensor_group is not None and id(p) not in self.tensor_sharded:
+                copies *= self.shape["tensor"]
+            if copies > 1:
+                self._norm_w[name] = 1.0 / copies
         with torch.no_grad():
             for p, g in self.replicated:
                 dist.broadcast(p.data, src=dist.get_global_rank(g, 0), group=g)
+        # whole parameters with a partial gradient under tensor parallelism: summed there too
+        for p in getattr(self, "tensor_partial", ()):
+            self.replicated.append((p, self.tensor_group))
 
     def norm_weight(self, name: str) -> float:
         """Share of a parameter's squared gradient this rank contributes to the global
@@ -217,6 +227,10 @@ class Parallel:
         tree = state_tree(trainer)
         if self.fsdp is not None:
             tree = self.fsdp.gather_tree(tree)
+        if self.tensor_group is not None:
+            from . import tensor
+
+            tree = tensor.gather_tree(tree, self)
         if self.expert_group is not None:
             tree = _gather_experts(tree, self.expert_group)
         return tree if self.rank == 0 else None

@@ -117,3 +117,47 @@ def test_hsdp_matches_one_rank(tmp_path):
     got = _spawn(4, MOE, ["mesh = mesh(data=2, fsdp=2)"], tmp_path)
     assert got["losses"] == pytest.approx(want_losses, abs=1e-5)
     _check_rows(got, want)
+
+
+DENSE = MOE.replace("e = moe(num_experts=4, top_k=2, expert=gated_mlp(intermediate_size=16, activation=swish))",
+                    "e = gated_mlp(intermediate_size=48, activation=swish)")
+
+
+def _tensor_worker(rank, world, port, src, overrides, out):
+    """Like `_worker`, but rank 0 saves whole tensors (gathered over the tensor axis)."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from bux_b200.ckpt.store import state_tree
+    from bux_b200.parallel.engine import Parallel
+    from bux_b200.train.trainer import Trainer
+
+    torch.set_num_threads(1)
+    run = compile_runs(src, filename="p.bux", overrides=overrides)[0]
+    par = Parallel(run.train, torch.device("cpu"))
+    tr = Trainer(run, device="cpu", parallel=par)
+    feed = iter(tr.batches())
+    losses = [tr.train_step(next(feed))["loss"].item() for _ in range(2)]
+    tree = par.checkpoint_tree(tr, state_tree)
+    if rank == 0:
+        torch.save({"losses": losses, "state": tree["0"]}, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("src,extra", ids=["dense", "moe", "dense-sp", "moe-sp"], argvalues=[
+    (DENSE, []),
+    (MOE, []),
+    (DENSE, ["layout = layout(stream=tensor)"]),
+    (MOE.replace("optimizer = adamw", "loss = loss(); optimizer = adamw"), ["layout = layout(stream=tensor)"]),
+])
+def test_tensor_parallel_matches_one_rank(tmp_path, src, extra):  # noqa: D103
+    src = src.replace("model = embed block^2 n head", "model = embed block^2 n head(tied=false)")
+    src = src.replace("num_heads=2, num_kv_heads=1", "num_heads=4, num_kv_heads=2, qk_norm=rmsnorm")
+    want_losses, want = _single(src)
+    out = str(tmp_path / "rank0.pt")
+    mp.spawn(_tensor_worker, args=(2, _free_port(), src, ["mesh = mesh(tensor=2)", *extra], out), nprocs=2, join=True)
+    got = torch.load(out)
+    assert got["losses"] == pytest.approx(want_losses, abs=1e-5)
+    for name, p in want.items():
+        assert torch.allclose(got["state"][name], p, atol=1e-5), name
