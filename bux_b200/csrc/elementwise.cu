@@ -312,97 +312,142 @@ __device__ __forceinline__ size_t sf_offset(long i, int j, int sf_cols_padded) {
   return ((size_t)rb * (sf_cols_padded >> 2) + cb) * 512 + (ri & 31) * 16 + (ri >> 5) * 4 + cj;
 }
 
-// Tile: 32 rows x 128 columns per block of 128 threads. Optional row gather
-// (`row_index[r]` = source row of output row r, negative = zero row) fuses the MoE
-// permute into the quantiser.
+// Tile: 128 rows x 128 columns per block of 256 threads, staged once in shared memory as
+// bf16 (row pitch 272 bytes: 16-byte accesses of 8 consecutive rows hit 8 different bank
+// groups). Each tile fills exactly one 512-byte scale tile of the row-wise output and one
+// of the transposed output, written as whole tiles (padding scales included), and every
+// byte of both quantised outputs inside the padded extents, so the caller allocates
+// without clearing. Optional row gather (`row_index[r]` = source row of output row r,
+// negative = zero row) fuses the MoE permute into the quantiser.
 //   q_row [R, C] e4m3, sf_row tiles over (R, C/32);  q_col [C, R_pad] e4m3 (R_pad = ld_col),
 //   sf_col tiles over (C, R_pad/32).
-__global__ void quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long ld_x,
-                                   const int* __restrict__ row_index,
-                                   uint8_t* __restrict__ q_row, uint8_t* __restrict__ sf_row,
-                                   uint8_t* __restrict__ q_col, uint8_t* __restrict__ sf_col,
-                                   long rows, int cols, long ld_col, long x_batch_stride) {
-  __shared__ float tile[32][129];
+constexpr int QT = 128;
+constexpr int QPITCH = 136;
+
+__device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d) {
+  const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return (uint32_t)lo | ((uint32_t)hi << 16);
+}
+
+__global__ void __launch_bounds__(256)
+quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long ld_x,
+                   const int* __restrict__ row_index,
+                   uint8_t* __restrict__ q_row, uint8_t* __restrict__ sf_row,
+                   uint8_t* __restrict__ q_col, uint8_t* __restrict__ sf_col,
+                   long rows, int cols, long ld_col, long x_batch_stride) {
+  __shared__ __align__(16) __nv_bfloat16 tile[QT][QPITCH];
+  __shared__ __align__(16) uint8_t sfr[512];
+  __shared__ __align__(16) uint8_t sfc[512];
+  const int sf_cols_row = ((cols / 32) + 3) & ~3;
+  const int sf_cols_col = (int)(((ld_col / 32) + 3) & ~3L);
   if (blockIdx.z > 0) {
     // batched: matrix z of a stack, every output advanced by its own size
     const long z = blockIdx.z;
-    const int sfc_row = ((cols / 32) + 3) & ~3;
-    const long sfc_col = ((ld_col / 32) + 3) & ~3L;
     x += z * x_batch_stride;
-    if (q_row) { q_row += z * rows * cols; sf_row += z * ((rows + 127) / 128) * (sfc_row / 4) * 512; }
-    if (q_col) { q_col += z * (long)cols * ld_col; sf_col += z * ((cols + 127) / 128) * (sfc_col / 4) * 512; }
+    if (q_row) { q_row += z * rows * cols; sf_row += z * ((rows + 127) / 128) * (sf_cols_row / 4) * 512; }
+    if (q_col) { q_col += z * (long)cols * ld_col; sf_col += z * ((cols + 127) / 128) * (sf_cols_col / 4) * 512; }
   }
-  const long r0 = (long)blockIdx.y * 32;
-  const int c0 = blockIdx.x * 128;
-  // load: 32 rows x 128 cols, 16 threads per row (8 elements each), 8 rows per pass
-  for (int pass = 0; pass < 4; ++pass) {
-    const int rr = pass * 8 + (threadIdx.x >> 4);
-    const int cc = (threadIdx.x & 15) * 8;
-    const long r = r0 + rr;
-    long src = r;
-    if (row_index && r < rows) src = row_index[r];
-    float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (r < rows && src >= 0 && c0 + cc < cols) {
-      const uint4 v = *reinterpret_cast<const uint4*>(x + src * ld_x + c0 + cc);
-      float2 t;
-      t = unpack_bf16(v.x); f[0] = t.x; f[1] = t.y;
-      t = unpack_bf16(v.y); f[2] = t.x; f[3] = t.y;
-      t = unpack_bf16(v.z); f[4] = t.x; f[5] = t.y;
-      t = unpack_bf16(v.w); f[6] = t.x; f[7] = t.y;
+  const int tid = threadIdx.x;
+  const long r0 = (long)blockIdx.y * QT;
+  const int c0 = blockIdx.x * QT;
+  {
+    // load: 16 threads per row (8 elements each), 16 rows per pass; all loads first
+    uint4 v[8];
+    const int cc = (tid & 15) * 8;
+#pragma unroll
+    for (int pass = 0; pass < 8; ++pass) {
+      const long r = r0 + pass * 16 + (tid >> 4);
+      long src = r;
+      if (row_index && r < rows) src = row_index[r];
+      v[pass] = make_uint4(0, 0, 0, 0);
+      if (r < rows && src >= 0 && c0 + cc < cols)
+        v[pass] = *reinterpret_cast<const uint4*>(x + src * ld_x + c0 + cc);
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) tile[rr][cc + j] = f[j];
+    for (int pass = 0; pass < 8; ++pass)
+      *reinterpret_cast<uint4*>(&tile[pass * 16 + (tid >> 4)][cc]) = v[pass];
   }
   __syncthreads();
-  const int sf_cols_row = ((cols / 32) + 3) & ~3;
   if (q_row) {
-    // thread -> (row = tid / 4, 32-column block = tid % 4)
-    const int rr = threadIdx.x >> 2, cb = threadIdx.x & 3;
+    // thread -> row tid % 128, 32-column blocks tid / 128 and tid / 128 + 2
+    const int rr = tid & 127;
     const long r = r0 + rr;
-    if (r < rows && c0 + cb * 32 < cols) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int cb = (tid >> 7) + 2 * i;
+      float f[32];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint4 w = *reinterpret_cast<const uint4*>(&tile[rr][cb * 32 + k * 8]);
+        float2 t;
+        t = unpack_bf16(w.x); f[8 * k] = t.x; f[8 * k + 1] = t.y;
+        t = unpack_bf16(w.y); f[8 * k + 2] = t.x; f[8 * k + 3] = t.y;
+        t = unpack_bf16(w.z); f[8 * k + 4] = t.x; f[8 * k + 5] = t.y;
+        t = unpack_bf16(w.w); f[8 * k + 6] = t.x; f[8 * k + 7] = t.y;
+      }
       float amax = 0.f;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(tile[rr][cb * 32 + j]));
+      for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(f[j]));
+      const bool live = r < rows && c0 + cb * 32 < cols;
       const uint8_t e = e8m0_of(amax);
       const float inv = e8m0_inv(e);
-      uint32_t packed[8];
+      sfr[(rr & 31) * 16 + (rr >> 5) * 4 + cb] = live ? e : (uint8_t)127;
+      if (live) {
+        uint32_t packed[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float a = tile[rr][cb * 32 + 4 * j] * inv, b = tile[rr][cb * 32 + 4 * j + 1] * inv;
-        const float c = tile[rr][cb * 32 + 4 * j + 2] * inv, d = tile[rr][cb * 32 + 4 * j + 3] * inv;
-        const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
-        const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
-        packed[j] = (uint32_t)lo | ((uint32_t)hi << 16);
+        for (int j = 0; j < 8; ++j)
+          packed[j] = cvt_e4m3x4(f[4 * j] * inv, f[4 * j + 1] * inv, f[4 * j + 2] * inv, f[4 * j + 3] * inv);
+        uint4* dst = reinterpret_cast<uint4*>(q_row + r * cols + c0 + cb * 32);
+        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
       }
-      uint4* dst = reinterpret_cast<uint4*>(q_row + r * cols + c0 + cb * 32);
-      dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-      dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-      sf_row[sf_offset(r, (c0 >> 5) + cb, sf_cols_row)] = e;
     }
   }
   if (q_col) {
-    // thread -> column; 32 rows of this tile form one scale block of the transposed copy
-    const int cc = threadIdx.x;
-    const int c = c0 + cc;
-    if (c < cols) {
+    // thread -> columns 2*(tid % 64) and +1, 32-row block tid / 64: one scale block each
+    const int cp = tid & 63, rb = tid >> 6;
+    uint32_t w[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) w[j] = *reinterpret_cast<const uint32_t*>(&tile[rb * 32 + j][2 * cp]);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int cc = 2 * cp + half;
+      const int c = c0 + cc;
       float amax = 0.f;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(tile[j][cc]));
+      for (int j = 0; j < 32; ++j) {
+        const float2 t = unpack_bf16(w[j]);
+        amax = fmaxf(amax, fabsf(half ? t.y : t.x));
+      }
+      const bool live = c < cols;
       const uint8_t e = e8m0_of(amax);
       const float inv = e8m0_inv(e);
-      uint32_t packed[8];
+      sfc[(cc & 31) * 16 + (cc >> 5) * 4 + rb] = live ? e : (uint8_t)127;
+      if (live) {
+        uint32_t packed[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(tile[4 * j][cc] * inv, tile[4 * j + 1][cc] * inv), __NV_SATFINITE, __NV_E4M3);
-        const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(tile[4 * j + 2][cc] * inv, tile[4 * j + 3][cc] * inv), __NV_SATFINITE, __NV_E4M3);
-        packed[j] = (uint32_t)lo | ((uint32_t)hi << 16);
+        for (int j = 0; j < 8; ++j) {
+          const float2 t0 = unpack_bf16(w[4 * j]), t1 = unpack_bf16(w[4 * j + 1]);
+          const float2 t2 = unpack_bf16(w[4 * j + 2]), t3 = unpack_bf16(w[4 * j + 3]);
+          packed[j] = half ? cvt_e4m3x4(t0.y * inv, t1.y * inv, t2.y * inv, t3.y * inv)
+                           : cvt_e4m3x4(t0.x * inv, t1.x * inv, t2.x * inv, t3.x * inv);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(q_col + (size_t)c * ld_col + r0 + rb * 32);
+        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
       }
-      uint4* dst = reinterpret_cast<uint4*>(q_col + (size_t)c * ld_col + r0);
-      dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-      dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-      const int sf_cols_col = (int)(((ld_col / 32) + 3) & ~3);
-      sf_col[sf_offset(c, (int)(r0 >> 5), sf_cols_col)] = e;
     }
+  }
+  __syncthreads();
+  // one whole 512-byte scale tile per output
+  if (q_row && tid < 32) {
+    uint8_t* dst = sf_row + ((size_t)blockIdx.y * (sf_cols_row >> 2) + blockIdx.x) * 512;
+    reinterpret_cast<uint4*>(dst)[tid] = reinterpret_cast<const uint4*>(sfr)[tid];
+  }
+  if (q_col && tid >= 32 && tid < 64) {
+    uint8_t* dst = sf_col + ((size_t)blockIdx.x * (sf_cols_col >> 2) + blockIdx.y) * 512;
+    reinterpret_cast<uint4*>(dst)[tid - 32] = reinterpret_cast<const uint4*>(sfc)[tid - 32];
   }
 }
 
@@ -760,8 +805,9 @@ void glu_bwd(const void* h, const void* dout, void* dh, const float* row_scale, 
   glu_bwd_kernel<<<grid_for(rows * (f / 8), 256), 256, 0, s>>>((const __nv_bfloat16*)h, (const __nv_bfloat16*)dout, (__nv_bfloat16*)dh, row_scale, d_row_scale, rows, f, kind, limit, up_offset);
 }
 void quant_mxfp8(const void* x, long ld_x, const int* row_index, uint8_t* q_row, uint8_t* sf_row, uint8_t* q_col, uint8_t* sf_col, long rows, int cols, long ld_col, int batch, long x_batch_stride, cudaStream_t s) {
-  dim3 grid((cols + 127) / 128, (unsigned)((rows + 31) / 32), batch);
-  quant_mxfp8_kernel<<<grid, 128, 0, s>>>((const __nv_bfloat16*)x, ld_x, row_index, q_row, sf_row, q_col, sf_col, rows, cols, ld_col, x_batch_stride);
+  const long extent = q_col ? (ld_col > rows ? ld_col : rows) : rows;  // the transposed copy is padded to ld_col
+  dim3 grid((cols + 127) / 128, (unsigned)((extent + 127) / 128), batch);
+  quant_mxfp8_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, ld_x, row_index, q_row, sf_row, q_col, sf_col, rows, cols, ld_col, x_batch_stride);
 }
 void ce_fwd_bwd(void* logits, const int* targets, const float* mask, float* loss, float* logz, long rows, int vocab, long ld, float grad_scale, float z_weight, float softcap, cudaStream_t s) {
   ce_fwd_bwd_kernel<<<(unsigned)rows, 512, 0, s>>>((__nv_bfloat16*)logits, targets, mask, loss, logz, vocab, ld, grad_scale, z_weight, softcap);

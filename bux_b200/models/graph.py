@@ -127,6 +127,17 @@ class Repeated(nn.Module):
         return x
 
 
+_OFFLOADED: list = []   # blocks whose inputs sit in host memory, in forward order
+_SIDE: dict = {}
+
+
+def _side_stream(device):
+    key = torch.device(device).index
+    if key not in _SIDE:
+        _SIDE[key] = torch.cuda.Stream(device=device)
+    return _SIDE[key]
+
+
 class _Remat(torch.autograd.Function):
     """Activation checkpointing of one block: the forward keeps only the block's input
     (optionally in pinned host memory), the backward reruns the block and differentiates
@@ -138,23 +149,52 @@ class _Remat(torch.autograd.Function):
         fctx.holder = holder
         fctx.cuda_rng = torch.cuda.get_rng_state(x.device) if x.is_cuda else None
         fctx.cpu_rng = torch.get_rng_state()
-        with torch.no_grad():
-            y, aux = holder.run(x, replay=False)
         fctx.host = None
         if holder.offload and x.is_cuda:
+            # the copy runs on a side stream so the block's kernels do not wait for PCIe
             host = holder.pinned(x)
-            host.copy_(x, non_blocking=True)
+            side = _side_stream(x.device)
+            side.wait_stream(torch.cuda.current_stream(x.device))
+            with torch.cuda.stream(side):
+                host.copy_(x, non_blocking=True)
+            x.record_stream(side)
             fctx.host = host
             fctx.device = x.device
+            fctx.fetched = None
+            _OFFLOADED.append(fctx)
         else:
             fctx.save_for_backward(x)
+        with torch.no_grad():
+            y, aux = holder.run(x, replay=False)
         return (y, *aux)
+
+    @staticmethod
+    def _fetch(fctx) -> None:
+        """Start the host → device copy of a block's input on the side stream."""
+        main = torch.cuda.current_stream(fctx.device)
+        side = _side_stream(fctx.device)
+        buf = torch.empty(fctx.host.shape, dtype=fctx.host.dtype, device=fctx.device)
+        side.wait_stream(main)  # the buffer's previous owner ran on the main stream
+        with torch.cuda.stream(side):
+            buf.copy_(fctx.host, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(side)
+        fctx.fetched = (buf, done)
 
     @staticmethod
     def backward(fctx, dy, *daux):
         holder = fctx.holder
         if fctx.host is not None:
-            x = fctx.host.to(fctx.device, non_blocking=True)
+            if fctx.fetched is None:
+                _Remat._fetch(fctx)
+            x, done = fctx.fetched
+            fctx.fetched = None
+            torch.cuda.current_stream(fctx.device).wait_event(done)
+            if _OFFLOADED and _OFFLOADED[-1] is fctx:
+                _OFFLOADED.pop()
+            # the block that goes backward next: its input travels while this one computes
+            if _OFFLOADED and _OFFLOADED[-1].fetched is None:
+                _Remat._fetch(_OFFLOADED[-1])
         else:
             (x,) = fctx.saved_tensors
         x = x.detach().requires_grad_(True)

@@ -95,9 +95,10 @@ class GQA(nn.Module):
         c = self.c
         bsz, t, _ = x.shape
         qkv = self.qkv(x, ctx)
-        q = qkv[..., : self.q_rows].reshape(bsz, t, self.h, self.d)
-        k = qkv[..., self.q_rows: self.q_rows + self.k_rows].reshape(bsz, t, self.g, self.d)
-        v = qkv[..., self.q_rows + self.k_rows:].reshape(bsz, t, self.g, self.dv)
+        q, k, v = qkv.split((self.q_rows, self.k_rows, self.v_rows), dim=-1)  # backward: one cat
+        q = q.reshape(bsz, t, self.h, self.d)
+        k = k.reshape(bsz, t, self.g, self.d)
+        v = v.reshape(bsz, t, self.g, self.dv)
         for port in self.ports:  # value residual / kv sharing through taps
             if port.name == "v" and port.mode != "write":
                 v = 0.5 * (v + ctx.read(port.tap, port.mode == "pop"))

@@ -85,8 +85,7 @@ class MoE(nn.Module):
     # ------------------------------------------------------------------ routing
     def route(self, x: torch.Tensor, ctx: Context):
         c = self.c
-        logits = nn.functional.linear(x.float(), self.router.weight.float(),
-                                      None if self.router.bias is None else self.router.bias.float())
+        logits = ops.linear_f32(x, self.router.weight, self.router.bias)
         logits = logits * c.router_logit_scale
         if c.random_logits and ctx.training:
             drawn = torch.randn_like(logits)

@@ -227,6 +227,42 @@ class _LinearMX(torch.autograd.Function):
         return dx, dw
 
 
+class _LinearF32Out(torch.autograd.Function):
+    """fp32 logits from 16-bit operands: products of bf16 values are exact in the fp32
+    accumulator, so this equals casting both operands up first, without the casts."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        K = _K()
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        ctx.save_for_backward(x2, w)
+        ctx.shape = x.shape
+        bn = 128 if w.shape[0] <= 128 else 256
+        return K.gemm_bf16(x2, w, out_dtype=torch.float32, bn=bn).view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        K = _K()
+        x2, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).to(torch.bfloat16).contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = K.gemm_bf16(dy2, w, b_mn=True).view(ctx.shape)
+        if ctx.needs_input_grad[1]:
+            dw = K.gemm_bf16(dy2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32).to(w.dtype)
+        return dx, dw
+
+
+def linear_f32(x, w, bias=None):
+    """x·W^T (+ bias) in fp32 (router logits, gates)."""
+    k, n = x.shape[-1], w.shape[0]
+    if (kernels_on(x) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k % 8 == 0
+            and n % 8 == 0):
+        y = _LinearF32Out.apply(x, w)
+        return y if bias is None else y + bias.float()
+    return F.linear(x.float(), w.float(), None if bias is None else bias.float())
+
+
 def linear(x, w, bias=None, fmt: str = "bf16"):
     """x [..., in] times w [out, in]^T (+ bias). `fmt`: "bf16" (compute dtype) or "mxfp8"."""
     k, n = x.shape[-1], w.shape[0]

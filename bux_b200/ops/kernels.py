@@ -130,11 +130,11 @@ def quant_mxfp8_batched(x: torch.Tensor, *, rowwise: bool = True, colwise: bool 
     if rowwise:
         assert r % 128 == 0 or e == 1, "rowwise scale tiles of a stack need R % 128 == 0"
         q_row = torch.empty(e * r, c, dtype=torch.float8_e4m3fn, device=dev)
-        sf_row = torch.full((e * sf_bytes(r, c),), 127, dtype=torch.uint8, device=dev)
+        sf_row = torch.empty(e * sf_bytes(r, c), dtype=torch.uint8, device=dev)
     if colwise:
         assert r % 128 == 0 and c % 128 == 0
         q_col = torch.empty(e * c, r, dtype=torch.float8_e4m3fn, device=dev)
-        sf_col = torch.full((e * sf_bytes(c, r),), 127, dtype=torch.uint8, device=dev)
+        sf_col = torch.empty(e * sf_bytes(c, r), dtype=torch.uint8, device=dev)
     xc = x.contiguous()
     ops().quant_mxfp8(xc, None, None if q_row is None else q_row.view(torch.uint8), sf_row,
                       None if q_col is None else q_col.view(torch.uint8), sf_col, r, c, r, e, r * c)
@@ -154,11 +154,12 @@ def quant_mxfp8(x: torch.Tensor, *, rowwise: bool = True, colwise: bool = False,
     q_row = sf_row = q_col = sf_col = None
     if rowwise:
         q_row = torch.empty(r, c, dtype=torch.float8_e4m3fn, device=dev)
-        sf_row = torch.full((sf_bytes(r, c),), 127, dtype=torch.uint8, device=dev)
+        sf_row = torch.empty(sf_bytes(r, c), dtype=torch.uint8, device=dev)
     r_pad = -(-r // 128) * 128
     if colwise:
-        q_col = torch.zeros(c, r_pad, dtype=torch.float8_e4m3fn, device=dev)
-        sf_col = torch.full((sf_bytes(c, r_pad),), 127, dtype=torch.uint8, device=dev)
+        # the kernel writes every byte of both outputs, padding included
+        q_col = torch.empty(c, r_pad, dtype=torch.float8_e4m3fn, device=dev)
+        sf_col = torch.empty(sf_bytes(c, r_pad), dtype=torch.uint8, device=dev)
     ops().quant_mxfp8(x2, row_index, None if q_row is None else q_row.view(torch.uint8), sf_row,
                       None if q_col is None else q_col.view(torch.uint8), sf_col, r, c, r_pad, 1, 0)
     _count()

@@ -23,7 +23,7 @@ import torch
 from ..config import training as T
 from ..lang import ir
 from ..lang.printer import run_to_source
-from ..models import Model, Precision
+from ..models import Model, Precision, graph
 from . import curriculum, data, objective, optim
 
 
@@ -178,6 +178,7 @@ class Trainer:
             self._release = (lr_scale, self._delayed_clip_factor())
             self.optimizer.step_count += 1
         self.model.train()
+        graph._OFFLOADED.clear()
         loss_sum = torch.zeros((), dtype=torch.float32, device=self.device)
         terms: dict = {}
         for k, mb in enumerate(micro):
