@@ -169,7 +169,7 @@ __global__ void norm_rope_kernel(const __nv_bfloat16* __restrict__ x, const floa
         // y_lo = a c - b s, y_hi = a s + b c  =>  da = g_lo c + g_hi s, db = -g_lo s + g_hi c
         g[j] = upper ? (-other * s[j] + g[j] * c[j]) : (g[j] * c[j] + other * s[j]);
       }
-      __nv_bfloat16* dxp = y + tok * stride_tok_x + (long)head * D + lane * E;  // y doubles as dx
+      __nv_bfloat16* dxp = y + tok * stride_tok_y + (long)head * D + lane * E;  // y doubles as dx (dense, like dy)
       if (w) {
         const float r = rstd_io[item];
         float dot = 0.f;

@@ -66,7 +66,7 @@ class _NormRope(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, cos, sin, eps):
         K = _K()
-        xc = x.contiguous()
+        xc = x if K.token_stride(x) is not None else x.contiguous()  # a slice of qkv is read in place
         wf = None if w is None else w.float().contiguous()
         y, rstd = K.norm_rope_fwd(xc, wf, cos, sin, eps)
         ctx.save_for_backward(xc, w, cos, sin, rstd)
@@ -228,36 +228,46 @@ class _LinearMX(torch.autograd.Function):
 
 
 class _LinearF32Out(torch.autograd.Function):
-    """fp32 logits from 16-bit operands: products of bf16 values are exact in the fp32
-    accumulator, so this equals casting both operands up first, without the casts."""
+    """fp32 logits on the bf16 tensor cores. Products of bf16 values are exact in the fp32
+    accumulator; an fp32 weight enters as hi + lo (two bf16 halves, 16 mantissa bits
+    together) stacked into one GEMM whose two column halves are added."""
 
     @staticmethod
     def forward(ctx, x, w):
         K = _K()
         x2 = x.reshape(-1, x.shape[-1]).contiguous()
-        ctx.save_for_backward(x2, w)
-        ctx.shape = x.shape
-        bn = 128 if w.shape[0] <= 128 else 256
-        return K.gemm_bf16(x2, w, out_dtype=torch.float32, bn=bn).view(*x.shape[:-1], w.shape[0])
+        n = w.shape[0]
+        if w.dtype == torch.float32:
+            hi = w.to(torch.bfloat16)
+            lo = (w - hi.float()).to(torch.bfloat16)
+            y2 = K.gemm_bf16(x2, torch.cat((hi, lo), dim=0), out_dtype=torch.float32, bn=256 if 2 * n > 128 else 128)
+            y = y2[:, :n] + y2[:, n:]
+            wb = hi
+        else:
+            y = K.gemm_bf16(x2, w, out_dtype=torch.float32, bn=128 if n <= 128 else 256)
+            wb = w
+        ctx.save_for_backward(x2, wb)
+        ctx.shape, ctx.w_dtype = x.shape, w.dtype
+        return y.view(*x.shape[:-1], n)
 
     @staticmethod
     def backward(ctx, dy):
         K = _K()
-        x2, w = ctx.saved_tensors
+        x2, wb = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1]).to(torch.bfloat16).contiguous()
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            dx = K.gemm_bf16(dy2, w, b_mn=True).view(ctx.shape)
+            dx = K.gemm_bf16(dy2, wb, b_mn=True).view(ctx.shape)
         if ctx.needs_input_grad[1]:
-            dw = K.gemm_bf16(dy2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32).to(w.dtype)
+            dw = K.gemm_bf16(dy2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32).to(ctx.w_dtype)
         return dx, dw
 
 
 def linear_f32(x, w, bias=None):
     """x·W^T (+ bias) in fp32 (router logits, gates)."""
     k, n = x.shape[-1], w.shape[0]
-    if (kernels_on(x) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k % 8 == 0
-            and n % 8 == 0):
+    if (kernels_on(x) and x.dtype == torch.bfloat16 and w.dtype in (torch.bfloat16, torch.float32)
+            and k % 8 == 0 and n % 8 == 0):
         y = _LinearF32Out.apply(x, w)
         return y if bias is None else y + bias.float()
     return F.linear(x.float(), w.float(), None if bias is None else bias.float())

@@ -183,13 +183,26 @@ def rmsnorm_bwd(x, w, dy, rstd, need_dw: bool = True):
     return dx, dw
 
 
+def token_stride(x) -> Optional[int]:
+    """Elements between tokens of x [..., T, H, D] when heads are dense and the leading
+    dimensions collapse into one (a column slice of a fused projection); else None."""
+    d, h = x.shape[-1], x.shape[-2]
+    if x.stride(-1) != 1 or x.stride(-2) != d or x.dim() < 3:
+        return None
+    step = x.stride(-3)
+    for i in range(x.dim() - 4, -1, -1):
+        if x.stride(i) != x.shape[i + 1] * x.stride(i + 1):
+            return None
+    return step if step % 8 == 0 and x.data_ptr() % 16 == 0 else None
+
+
 def norm_rope_fwd(x, w, cos, sin, eps: float):
-    """x: [..., T, H, D] contiguous; cos/sin: [tokens, D/2] fp32."""
+    """x: [..., T, H, D], dense or a column slice (see `token_stride`); cos/sin: [tokens, D/2] fp32."""
     d, h = x.shape[-1], x.shape[-2]
     tokens = x.numel() // (h * d)
-    y = torch.empty_like(x)
+    y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
     rstd = torch.empty(tokens * h, dtype=torch.float32, device=x.device) if w is not None else None
-    ops().norm_rope(False, x, w, cos, sin, y, rstd, None, None, tokens, h, d, h * d, h * d, eps)
+    ops().norm_rope(False, x, w, cos, sin, y, rstd, None, None, tokens, h, d, token_stride(x), h * d, eps)
     _count()
     return y, rstd
 
@@ -197,9 +210,9 @@ def norm_rope_fwd(x, w, cos, sin, eps: float):
 def norm_rope_bwd(x, w, cos, sin, rstd, dy, eps: float):
     d, h = x.shape[-1], x.shape[-2]
     tokens = x.numel() // (h * d)
-    dx = torch.empty_like(x)
+    dx = torch.empty(x.shape, dtype=x.dtype, device=x.device)
     dw = torch.zeros(d, dtype=torch.float32, device=x.device) if w is not None else None
-    ops().norm_rope(True, x, w, cos, sin, dx, rstd, dy, dw, tokens, h, d, h * d, h * d, eps)
+    ops().norm_rope(True, x, w, cos, sin, dx, rstd, dy, dw, tokens, h, d, token_stride(x), h * d, eps)
     _count()
     return dx, dw
 

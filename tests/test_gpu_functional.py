@@ -98,3 +98,22 @@ def test_norm_glu_attention_autograd(cuda):
     orf, _ = ref.attention(qr, kr, vr)
     orf.square().sum().backward()
     assert rel_err(q.grad, qr.grad) < 4e-2 and rel_err(k.grad, kr.grad) < 4e-2
+
+
+@pytest.mark.gpu
+def test_linear_f32_matches_fp32_matmul():
+    from bux_b200.ops import functional as F_
+
+    torch.manual_seed(0)
+    x = torch.randn(512, 256, device="cuda").bfloat16().requires_grad_(True)
+    for dtype in (torch.float32, torch.bfloat16):
+        w = (torch.randn(128, 256, device="cuda") * 0.05).to(dtype).requires_grad_(True)
+        y = F_.linear_f32(x, w)
+        want = x.float() @ w.float().t()
+        assert y.dtype == torch.float32
+        assert torch.allclose(y, want, atol=2e-4 if dtype == torch.float32 else 1e-5, rtol=1e-4)
+        g = torch.randn_like(y)
+        dx, dw = torch.autograd.grad(y, (x, w), g)
+        gb = g.bfloat16().float()
+        assert torch.allclose(dx.float(), (gb @ w.float()), atol=2e-2, rtol=2e-2)
+        assert torch.allclose(dw.float(), gb.t() @ x.float(), atol=2e-2, rtol=2e-2)
