@@ -360,6 +360,8 @@ def train(run: ir.Run, out="runs", cache=".", hooks=None, sinks=None, device=Non
     if sinks is None:
         sinks = [S.Console(run.name, t.steps), S.JSONL(folder, resume_step=resumed)] if not quiet \
             else [S.JSONL(folder, resume_step=resumed)]
+    if not any(isinstance(s_, S.LatestMetrics) for s_ in sinks):
+        sinks = [*sinks, S.LatestMetrics()]
     if main and not quiet:
         dev = f"{parallel.world if parallel is not None else 1} × {trainer.device.type}"
         n = trainer.model.num_params()
