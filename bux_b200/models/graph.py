@@ -271,11 +271,8 @@ class GraphBuilder:
         self.embedding = None
         self.layer_count = 0
         self.num_layers = sum(1 for _ in arch.layers())
-        self.algebra_factory = None
-        if arch.residual is not None:
-            from . import residual
-
-            self.algebra_factory = lambda: residual.build(arch.residual, arch.d_model)
+        self.depth = 0      # residual branches around the node being built
+        self.branches = 0   # top-level branches built so far: the algebra numbers them
 
     def build(self, node):
         if node.share is not None:
@@ -300,8 +297,22 @@ class GraphBuilder:
         if isinstance(node, ir.Seq):
             return Sequence([self.build(n) for n in node.items])
         if isinstance(node, ir.Residual):
-            algebra = self.algebra_factory() if self.algebra_factory else None
-            return ResidualBranch(self.build(node.body), algebra)
+            # only a branch outside any other goes through the residual algebra
+            algebra = None
+            if self.arch.residual is not None and self.depth == 0:
+                from . import residual
+
+                algebra = residual.build(self.arch.residual, self.arch.d_model, self.branches)
+                for name in getattr(algebra, "no_weight_decay", ()):
+                    if hasattr(algebra, name):
+                        getattr(algebra, name).no_weight_decay = True
+                self.branches += 1
+            self.depth += 1
+            try:
+                body = self.build(node.body)
+            finally:
+                self.depth -= 1
+            return ResidualBranch(body, algebra)
         if isinstance(node, ir.Sum):
             return Parallel([self.build(n) for n in node.terms], product=False)
         if isinstance(node, ir.Prod):

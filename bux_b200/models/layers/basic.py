@@ -129,6 +129,9 @@ class Embedding(nn.Module):
         self.norm = Norm(c.norm, b.d_model) if c.norm is not None else None
         self.scale = math.sqrt(b.d_model) if c.scale_by_sqrt_dim else None
         self.dropout = c.dropout
+        from ..residual import widening
+
+        self.widen = widening(b.residual)
 
     def forward(self, ids, ctx: Context):
         x = self.tokens.embedding[ctx.input_ids]
@@ -142,6 +145,8 @@ class Embedding(nn.Module):
             x = self.norm(x, ctx)
         if self.dropout and ctx.training:
             x = nn.functional.dropout(x, self.dropout)
+        if self.widen is not None:  # the residual algebra's widened stream starts as copies
+            x = x.unsqueeze(2).expand(-1, -1, self.widen, -1).contiguous()
         return x
 
 

@@ -93,6 +93,7 @@ class Context:
         self.heads: list = []
         self._rope: dict = {}
         self.branch_index = 0
+        self.pending_read = None  # single-pass hyper-connections: the read the last branch computed
 
     # taps are named stacks
     def push(self, name: str, value) -> None:
