@@ -1,0 +1,79 @@
+"""Causal depthwise convolutions over the tokens: the ``conv`` and ``short_conv`` layers
+and the short convs inside the recurrent mixers (reference: ``architecture/layers/conv.py``,
+``architecture/recurrent/ssm.py:324``).
+
+Weights are [channels, taps]; tap j multiplies the token j positions back. Taps that
+would reach across a document start are dropped (packed rows).
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+from torch import nn
+
+from ..registry import BuildContext, Context, register
+from .basic import Linear
+
+
+class CausalDepthwise(nn.Module):
+    """y[t] = sum_j w[:, j] x[t-j] (+ bias)."""
+
+    def __init__(self, d: int, taps: int, zero: bool = False, bias: bool = False):
+        super().__init__()
+        w = torch.zeros(d, taps) if zero else torch.empty(d, taps).uniform_(-1, 1) / math.sqrt(taps)
+        self.weight = nn.Parameter(w)
+        self.bias = nn.Parameter(torch.zeros(d)) if bias else None
+
+    def forward(self, x, ctx: Optional[Context] = None):
+        t = x.shape[1]
+        pos = None
+        if ctx is not None and getattr(ctx, "segments", None) is not None:
+            pos = ctx.positions
+        w = self.weight.to(x.dtype)
+        y = x * w[:, 0]
+        for j in range(1, min(w.shape[1], t)):
+            shifted = nn.functional.pad(x[:, : t - j], (0, 0, j, 0))
+            if pos is not None:
+                shifted = shifted * (pos >= j).unsqueeze(-1).to(x.dtype)
+            y = y + shifted * w[:, j]
+        return y if self.bias is None else y + self.bias.to(y.dtype)
+
+
+class Conv(nn.Module):
+    """``conv``: a causal depthwise conv of the stream."""
+
+    def __init__(self, c, b: BuildContext):
+        super().__init__()
+        width = b.width if isinstance(b.width, int) else b.d_model
+        self.conv = CausalDepthwise(width, c.size, bias=c.bias)
+
+    def forward(self, x, ctx: Context):
+        return self.conv(x, ctx)
+
+
+class ShortConv(nn.Module):
+    """``short_conv`` (LFM2): B, C, u from the input; C * conv(B * u), projected back."""
+
+    def __init__(self, c, b: BuildContext):
+        super().__init__()
+        width = b.width if isinstance(b.width, int) else b.d_model
+        self.in_proj = Linear(width, 3 * width, c.bias, b)
+        self.conv = CausalDepthwise(width, c.conv_size, bias=c.bias)
+        self.out_proj = Linear(width, width, c.bias, b, init_role="out")
+
+    def forward(self, x, ctx: Context):
+        bb, cc, u = self.in_proj(x, ctx).chunk(3, -1)
+        return self.out_proj(cc * self.conv(bb * u, ctx), ctx)
+
+
+@register("conv")
+def _conv(c, b):
+    return Conv(c, b)
+
+
+@register("short_conv")
+def _short_conv(c, b):
+    return ShortConv(c, b)

@@ -23,6 +23,7 @@ import torch
 from torch import nn
 
 from ..config import layers as L
+from .layers.conv import CausalDepthwise
 from .registry import BuildContext, Context, register
 
 _EPS = 1e-6
@@ -256,28 +257,6 @@ class AttentionResidual(nn.Module):
     def forward(self, x, body, ctx: Context):
         y = body(self.read(x), ctx)
         return torch.cat([x, y.unsqueeze(2)], 2)
-
-
-class CausalDepthwise(nn.Module):
-    """y[t] = sum_j w[:, j] x[t-j], taps that would cross a document start dropped."""
-
-    def __init__(self, d: int, taps: int, zero: bool = False, bias: bool = False):
-        super().__init__()
-        self.weight = nn.Parameter(torch.zeros(d, taps) if zero else torch.randn(d, taps) * (1.0 / math.sqrt(taps)))
-        self.bias = nn.Parameter(torch.zeros(d)) if bias else None
-
-    def forward(self, x, ctx: Optional[Context] = None):
-        b, t, d = x.shape
-        pos = None
-        if ctx is not None and getattr(ctx, "positions", None) is not None and ctx.segments is not None:
-            pos = ctx.positions
-        y = x * self.weight[:, 0].to(x.dtype)
-        for j in range(1, min(self.weight.shape[1], t)):
-            shifted = nn.functional.pad(x[:, : t - j], (0, 0, j, 0))
-            if pos is not None:
-                shifted = shifted * (pos >= j).unsqueeze(-1).to(x.dtype)
-            y = y + shifted * self.weight[:, j].to(x.dtype)
-        return y if self.bias is None else y + self.bias.to(y.dtype)
 
 
 def _msar_layout(s: int, block: int, expansions: int):
