@@ -104,6 +104,8 @@ class GQA(nn.Module):
                 v = 0.5 * (v + ctx.read(port.tap, port.mode == "pop"))
             elif port.name == "kv" and port.mode != "write":
                 k, v = ctx.read(port.tap, port.mode == "pop")
+            elif port.name == "ve" and port.mode != "write":  # value embeddings join the values
+                v = v + ctx.read(port.tap, port.mode == "pop").reshape(v.shape).to(v.dtype)
         q = self._norm_rope(q, getattr(self, "q_norm", None), ctx)
         kv_shared = any(p.name == "kv" and p.mode != "write" for p in self.ports)
         if not kv_shared:

@@ -190,7 +190,7 @@ class Head(nn.Module):
     def forward(self, x, ctx: Context):
         out = HeadOutput(x, self.matrix(), self.bias, self.c.softcap, name=f"head{len(ctx.heads)}")
         ctx.heads.append(out)
-        return out
+        return x  # the stream goes on (multi-token prediction stacks more heads after it)
 
 
 @register("head")

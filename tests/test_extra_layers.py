@@ -1,0 +1,82 @@
+"""mla, value_embed, nextn, engram, doc_copy on CPU."""
+import pytest
+import torch
+
+from bux_b200.lang import compile_runs
+from bux_b200.models.layers import extra as X
+from bux_b200.train.trainer import Trainer
+
+SRC = """
+d_model=32
+vocab_size=64
+n = rmsnorm
+a = {attn}
+m = gated_mlp(intermediate_size=48, activation=swish)
+block = [n a] [n m]
+model = {model}
+data = synthetic
+optimizer = adamw(lr=1e-2)
+seq_len = 32
+batch = 2
+steps = 3
+precision = precision(compute=float32)
+{extra}
+"""
+GQA = "gqa(num_heads=2, num_kv_heads=1, rope=rope())"
+
+
+def _train(attn=GQA, model="embed block^2 n head", extra=""):
+    run = compile_runs(SRC.format(attn=attn, model=model, extra=extra), filename="x.bux")[0]
+    tr = Trainer(run, device="cpu")
+    batch = next(iter(tr.batches()))
+    losses = [tr.train_step(batch)["loss"].item() for _ in range(4)]
+    assert all(torch.isfinite(torch.tensor(losses))) and losses[-1] < losses[0]
+    return tr
+
+
+def test_mla_trains():
+    _train("mla(num_heads=2, kv_lora_rank=8, q_lora_rank=8, qk_nope_head_dim=8, qk_rope_head_dim=4, v_head_dim=8)")
+
+
+def test_value_embeddings_reach_the_attention_values():
+    tr = _train("gqa(num_heads=2, num_kv_heads=1, rope=rope(), ve=$ve!)",
+                model="embed (value_embed(features=16, ve=@ve) block)^2 n head")
+    assert any("table" in n for n, _ in tr.model.named_parameters())
+
+
+def test_nextn_adds_a_second_head():
+    tr = _train(model="embed block @h n head $h nextn block n head", extra="loss = loss(mtp=0.3)")
+    ids = torch.randint(0, 64, (2, 32))
+    ctx = tr.model(ids, torch.arange(32).expand(2, 32), None, training=False)
+    assert len(ctx.heads) == 2
+
+
+def test_engram_trains_and_takes_distinct_primes():
+    tr = _train(model="embed engram(head_dim=4, table_size=50, num_heads=2, conv_size=2) block^2 n head")
+    (e,) = [m for m in tr.model.modules() if isinstance(m, X.Engram)]
+    primes = e.primes.flatten().tolist()
+    assert len(set(primes)) == len(primes) == 4 and all(X._is_prime(p) and p >= 50 for p in primes)
+
+
+def test_copy_candidates_by_hand():
+    #          0  1  2  3  4  5  6  7
+    tokens = torch.tensor([[5, 6, 7, 5, 6, 9, 5, 6]])
+    within = torch.arange(8).unsqueeze(0)
+    doc = torch.zeros(1, 8, dtype=torch.long)
+    cand, bucket = X.copy_candidates(tokens, within, doc, [1, 2], counts=3)
+    # position 4 ends "5 6", seen ending at 1 → candidate is token 2 (7); length rank 2, once
+    assert cand[0, 4].item() == 7 and bucket[0, 4].item() == (2 - 1) * 3 + 1
+    # position 7 ends "5 6" again: latest earlier occurrence ended at 4 → candidate 9, twice
+    assert cand[0, 7].item() == 9 and bucket[0, 7].item() == (2 - 1) * 3 + 2
+    # position 3 ends "5" (seen at 0) but "7 5" never: length 1, candidate 6
+    assert cand[0, 3].item() == 6 and bucket[0, 3].item() == 1
+    assert cand[0, 0].item() == 0 and bucket[0, 0].item() == 0
+    # a document boundary hides earlier occurrences
+    doc2 = torch.tensor([[0, 0, 0, 1, 1, 1, 1, 1]])
+    within2 = torch.tensor([[0, 1, 2, 0, 1, 2, 3, 4]])
+    cand2, _ = X.copy_candidates(tokens, within2, doc2, [1, 2], counts=3)
+    assert cand2[0, 4].item() == 0 and cand2[0, 7].item() == 9
+
+
+def test_doc_copy_trains():
+    _train(model="embed doc_copy(lengths=[1, 2, 3]) block^2 n head")
