@@ -106,6 +106,11 @@ class Parallel:
 
         t = self.train
         expert_params = set()
+        self.pipeline = None
+        if self.stage_group is not None:
+            from .pipeline import Pipeline
+
+            self.pipeline = Pipeline(model, self)  # first: the rest shards what this stage keeps
         if self.expert_group is not None:
             me, n = dist.get_rank(self.expert_group), self.shape["expert"]
             ep = ExpertParallel(self.expert_group, t.methods.moe, t.methods.capacity)
@@ -233,6 +238,8 @@ class Parallel:
             tree = tensor.gather_tree(tree, self)
         if self.expert_group is not None:
             tree = _gather_experts(tree, self.expert_group)
+        if getattr(self, "pipeline", None) is not None:
+            tree = self.pipeline.gather_tree(tree)
         return tree if self.rank == 0 else None
 
 

@@ -181,7 +181,11 @@ class Trainer:
         graph._OFFLOADED.clear()
         loss_sum = torch.zeros((), dtype=torch.float32, device=self.device)
         terms: dict = {}
-        for k, mb in enumerate(micro):
+        pipe = getattr(self.parallel, "pipeline", None) if self.parallel is not None else None
+        if pipe is not None:
+            loss_sum, terms = pipe.run(self, micro, inv_count, n_micro, world)
+            torch.distributed.all_reduce(loss_sum, group=pipe.group)  # the last stage holds it
+        for k, mb in enumerate(micro if pipe is None else ()):
             last = k == len(micro) - 1
             sync = self.parallel.grad_sync(self.model, last) if self.parallel is not None else _null()
             with sync:

@@ -161,3 +161,39 @@ def test_tensor_parallel_matches_one_rank(tmp_path, src, extra):  # noqa: D103
     assert got["losses"] == pytest.approx(want_losses, abs=1e-5)
     for name, p in want.items():
         assert torch.allclose(got["state"][name], p, atol=1e-5), name
+
+
+def test_schedule_tables_are_valid():
+    from bux_b200.parallel import schedule as S
+
+    for name, make in S.TABLES.items():
+        for stages, micro in [(2, 2), (2, 4), (4, 4), (4, 8), (3, 5)]:
+            table = make(stages, micro)
+            S.check(table, micro)
+            if name in ("1f1b", "zbh1"):  # stage s keeps at most S - s microbatches alive
+                assert all(S.alive(ops) <= stages - s for s, ops in enumerate(table))
+    assert S.bubble(4, 8) == pytest.approx(3 / 11)
+    assert S.bubble(1, 8) == 0.0
+
+
+def test_pipeline_shares_balance_the_stages():
+    from bux_b200.parallel.pipeline import shares
+
+    assert shares([1.0] * 8, 4) == [2, 2, 2, 2]
+    assert shares([1.0] * 8, 2, last_extra=2.0) == [5, 3]
+    assert sum(shares([1.0, 3.0, 1.0, 1.0, 2.0], 3)) == 5
+
+
+@pytest.mark.parametrize("method", ["gpipe", "1f1b", "zbh1"])
+def test_pipeline_matches_one_rank(tmp_path, method):
+    src = DENSE.replace("model = embed block^2 n head", "model = embed block^4 n head(tied=false)")
+    over = ["methods.microbatches = 4"]
+    want_losses, want = _single(src, over)
+    out = str(tmp_path / "rank0.pt")
+    mp.spawn(_tensor_worker, args=(2, _free_port(), src, ["mesh = mesh(stage=2)", f"methods.pipeline = \"{method}\"", *over], out),
+             nprocs=2, join=True)
+    got = torch.load(out)
+    assert got["losses"] == pytest.approx(want_losses, abs=1e-5)
+    assert set(got["state"]) >= set(want)
+    for name, p in want.items():
+        assert torch.allclose(got["state"][name], p, atol=1e-5), name
