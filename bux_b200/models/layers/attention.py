@@ -113,9 +113,15 @@ class GQA(nn.Module):
         for port in self.ports:
             if port.mode == "write":
                 ctx.push(port.tap, v if port.name == "v" else (k, v))
-        out = ops.attention(q, k, v, causal=True, window=c.sliding_window_size,
-                            sinks=getattr(self, "sinks", None), softcap=c.softcap, scale=c.scale,
-                            segments=ctx.segments)
+        kw = dict(causal=True, window=c.sliding_window_size, sinks=getattr(self, "sinks", None),
+                  softcap=c.softcap, scale=c.scale, segments=ctx.segments)
+        cp = getattr(ctx.parallel, "context_group", None) if ctx.parallel is not None else None
+        if cp is not None:
+            from ...parallel import context
+
+            out = context.attend(ops.attention, q, k, v, cp, ctx.methods.attention, **kw)
+        else:
+            out = ops.attention(q, k, v, **kw)
         if c.output_norm is not None:
             out = self.out_norm(out, ctx)
         out = out.reshape(bsz, t, self.h * self.dv)

@@ -52,6 +52,7 @@ class Parallel:
         self.expert_group = self.group(("expert",)) if self.shape["expert"] > 1 else None
         self.tensor_group = self.group(("tensor",)) if self.shape["tensor"] > 1 else None
         self.stage_group = self.group(("stage",)) if self.shape["stage"] > 1 else None
+        self.context_group = self.group(("context",)) if self.shape["context"] > 1 else None
         self.replicated: list = []   # (param, group) whose gradients are summed over group
         self._norm_w: dict = {}
         self.fsdp = None
@@ -158,6 +159,12 @@ class Parallel:
         # whole parameters with a partial gradient under tensor parallelism: summed there too
         for p in getattr(self, "tensor_partial", ()):
             self.replicated.append((p, self.tensor_group))
+        # context parallelism: every rank sees its positions only, so every gradient is partial
+        if self.context_group is not None and "context" not in self.batch_axes:
+            n = self.shape["context"]
+            for name, p in model.named_parameters():
+                self.replicated.append((p, self.context_group))
+                self._norm_w[name] = self._norm_w.get(name, 1.0) / n
 
     def norm_weight(self, name: str) -> float:
         """Share of a parameter's squared gradient this rank contributes to the global
@@ -216,6 +223,22 @@ class Parallel:
             return t
         dist.all_reduce(t, group=g)
         return t
+
+    def sum_positions(self, t: torch.Tensor) -> torch.Tensor:
+        """Sum over the ranks that hold different positions of the same rows."""
+        if self.context_group is not None:
+            dist.all_reduce(t, group=self.context_group)
+        return t
+
+    def positions_span(self, length: int) -> tuple:
+        """(start, stop) of this rank's positions of a row of `length`."""
+        if self.context_group is None:
+            return 0, length
+        n, r = self.shape["context"], self.coords["context"]
+        if length % n:
+            raise ValueError(f"seq_len {length} does not divide over context={n}")
+        per = length // n
+        return r * per, (r + 1) * per
 
     def max_int(self, value: int) -> int:
         t = torch.tensor([value], dtype=torch.int64, device=self.device)

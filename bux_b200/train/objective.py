@@ -41,8 +41,10 @@ class LossParts:
     terms: dict = field(default_factory=dict)
 
 
-def compute(ctx, batch, loss_cfg: T.LossConfig) -> LossParts:
-    """Loss of one forward `ctx` on `batch` = (input_ids, position_ids, loss_mask)."""
+def compute(ctx, batch, loss_cfg: T.LossConfig, span=None) -> LossParts:
+    """Loss of one forward `ctx` on `batch` = (input_ids, position_ids, loss_mask). With
+    `span` = (start, stop) the forward saw only those positions of the rows (context
+    parallelism): targets come from the whole rows, then the span is taken."""
     ids, pos, lmask = batch
     dev = ids.device
     total = torch.zeros((), dtype=torch.float32, device=dev)
@@ -52,6 +54,8 @@ def compute(ctx, batch, loss_cfg: T.LossConfig) -> LossParts:
     for k, head in enumerate(ctx.heads):
         shift = k + 1 if k > 0 else 1  # head k>0 is an MTP head looking k+1 ahead
         tgt, mask = targets_and_mask(ids, pos, lmask, shift)
+        if span is not None:
+            tgt, mask = tgt[:, span[0]:span[1]], mask[:, span[0]:span[1]]
         h = head.hidden.reshape(-1, head.hidden.shape[-1])
         s, n = ops.cross_entropy_head(h, head.weight, tgt.reshape(-1), mask.reshape(-1).float(),
                                       bias=head.bias, z_weight=loss_cfg.z if k == 0 else 0.0,

@@ -146,13 +146,20 @@ class Trainer:
 
     def forward_loss(self, mb, inv_count, n_micro: int, world: int, training: bool = True):
         ids, pos, mask = mb
+        span = None
+        if self.parallel is not None and self.parallel.context_group is not None:
+            # this rank's positions; the loss still sees whole rows for its targets
+            span = self.parallel.positions_span(ids.shape[1])
+            ids, pos = ids[:, span[0]:span[1]], pos[:, span[0]:span[1]]
         segments = None
         if bool((pos[:, 1:] <= pos[:, :-1]).any()) if pos.device.type == "cpu" else False:
             segments = torch.cumsum((pos == 0).long(), dim=1)
         ctx = self.model(ids, pos, segments, training=training, precision=self.precision,
                          methods=self.train.methods, parallel=self.parallel, step=self.step)
-        parts = objective.compute(ctx, mb, self.train.loss)
+        parts = objective.compute(ctx, mb, self.train.loss, span=span)
         loss = parts.total_sum * inv_count + parts.per_batch / (n_micro * world)
+        if span is not None:  # per-batch terms are reported by every rank of the row
+            loss = parts.total_sum * inv_count + parts.per_batch / (n_micro * world * self.parallel.shape["context"])
         return loss, parts
 
     def train_step(self, batch: data.Batch) -> dict:
@@ -216,6 +223,7 @@ class Trainer:
         self.model.step_end_update()
         if self.parallel is not None:
             loss_sum = self.parallel.sum_scalar(loss_sum.view(1), data_only=True).view(())
+            loss_sum = self.parallel.sum_positions(loss_sum)
         self.step += 1
         self.tokens += cfg.batch * cfg.seq_len
         base_lr = t.optimizer.lr

@@ -197,3 +197,15 @@ def test_pipeline_matches_one_rank(tmp_path, method):
     assert set(got["state"]) >= set(want)
     for name, p in want.items():
         assert torch.allclose(got["state"][name], p, atol=1e-5), name
+
+
+@pytest.mark.parametrize("method,heads", [("ulysses", "num_heads=4, num_kv_heads=2"),
+                                          ("gathered", "num_heads=4, num_kv_heads=2"),
+                                          ("auto", "num_heads=2, num_kv_heads=1")])
+def test_context_parallel_matches_one_rank(tmp_path, method, heads):
+    src = DENSE.replace("num_heads=2, num_kv_heads=1", heads)
+    want_losses, want = _single(src)
+    got = _spawn(2, src, ["mesh = mesh(context=2)", f"methods.attention = {method}"], tmp_path)
+    assert got["losses"] == pytest.approx(want_losses, abs=1e-5)
+    for name, p in want.items():
+        assert torch.allclose(got["state"][name], p, atol=1e-5), name
