@@ -1,0 +1,104 @@
+"""Documents of a ``text(...)`` or ``chat(...)`` source: token ids and a loss mask each.
+
+A text document is ``[bos] tokens [eos]`` with every token a target. A chat document is
+rendered by a template into segments; only the segments of the roles ``train_on`` names
+are targets (``assistant``: every assistant turn; ``last``: the last one; ``all``).
+Reference: ``data/documents.py:78-281``, ``data/templates.py``.
+"""
+
+from __future__ import annotations
+
+import glob
+import hashlib
+import json
+from typing import Iterator
+
+import numpy as np
+
+CHATML = ("{% for m in messages %}<|im_start|>{{ m.role }}\n{{ m.content }}<|im_end|>\n{% endfor %}")
+
+
+def files_of(path: str) -> list:
+    found = sorted(glob.glob(path))
+    if not found:
+        raise FileNotFoundError(f"no files match {path!r}")
+    return found
+
+
+def key_of(ids: np.ndarray) -> int:
+    """63-bit content hash: the document's place in the shuffle."""
+    return int.from_bytes(hashlib.blake2b(ids.tobytes(), digest_size=8).digest(), "big") >> 1
+
+
+def in_split(key: int, split) -> bool:
+    u = key / float(1 << 63)
+    return split[0] <= u < split[1]
+
+
+def _records(path: str, column: str) -> Iterator:
+    import pyarrow.parquet as pq
+
+    for f in files_of(path):
+        if f.endswith((".jsonl", ".json")):
+            with open(f) as fh:
+                for line in fh:
+                    if line.strip():
+                        yield json.loads(line)[column]
+            continue
+        pf = pq.ParquetFile(f)
+        for batch in pf.iter_batches(columns=[column]):
+            yield from batch.column(0).to_pylist()
+
+
+def text(c, tok, tok_cfg=None) -> Iterator:
+    bos = tok.token_id(tok_cfg.bos) if (c.bos and tok_cfg is not None) else (tok.token_id("<|endoftext|>") if c.bos else None)
+    eos = tok.token_id(tok_cfg.eos) if (c.eos and tok_cfg is not None) else (tok.token_id("<|endoftext|>") if c.eos else None)
+    for value in _records(c.path, c.column):
+        if not value:
+            continue
+        ids = tok.encode(value)
+        if bos is not None:
+            ids = [bos, *ids]
+        if eos is not None:
+            ids = [*ids, eos]
+        arr = np.asarray(ids, np.int32)
+        yield arr, np.ones(len(arr), bool)
+
+
+def render(messages: list, template: str) -> list:
+    """[(text, role)] segments of a conversation: the template is applied one message at a
+    time so each piece of text knows whose turn it is."""
+    try:
+        import jinja2
+
+        env = jinja2.Environment()
+        tpl = env.from_string(template)
+        return [(tpl.render(messages=[m]), m["role"]) for m in messages]
+    except ImportError:
+        return [(f"<|im_start|>{m['role']}\n{m['content']}<|im_end|>\n", m["role"]) for m in messages]
+
+
+def chat(c, tok, tok_cfg=None) -> Iterator:
+    template = c.template or CHATML
+    for messages in _records(c.path, c.column):
+        if not messages:
+            continue
+        segs = render(messages, template)
+        last_assistant = max((i for i, (_, r) in enumerate(segs) if r == "assistant"), default=-1)
+        ids, mask = [], []
+        for i, (piece, role) in enumerate(segs):
+            t = tok.encode(piece)
+            on = (c.train_on == "all" or (role == "assistant" and (c.train_on == "assistant" or i == last_assistant)))
+            ids.extend(t)
+            mask.extend([on] * len(t))
+        if ids:
+            yield np.asarray(ids, np.int32), np.asarray(mask, bool)
+
+
+def documents(c, tok, tok_cfg=None) -> Iterator:
+    """(key, input_ids, loss_mask) of the source's documents inside its split."""
+    make = text if c.type == "text" else chat
+    for ids, mask in make(c, tok, tok_cfg):
+        k = key_of(ids)
+        if in_split(k, c.split):
+            yield k, ids, mask

@@ -1,0 +1,92 @@
+"""Tokenizers behind the ``tokenizer(name=...)`` setting.
+
+``name="bytes"`` is the built-in byte tokenizer (ids 0..255 are the bytes, special
+tokens follow); any other name is a ``tokenizer.json`` of the HF ``tokenizers`` library:
+a path, or a folder / name under ``BUX_TOKENIZERS`` (no network access is assumed).
+Reference: ``data/tokenizer.py``.
+"""
+
+from __future__ import annotations
+
+import os
+from pathlib import Path
+
+
+class ByteTokenizer:
+    def __init__(self, specials=("<|endoftext|>",)):
+        self.specials = list(dict.fromkeys(specials))
+        self.special_ids = {s: 256 + i for i, s in enumerate(self.specials)}
+        self.vocab_size = 256 + len(self.specials)
+
+    def token_id(self, token: str) -> int:
+        return self.special_ids[token]
+
+    def encode(self, text: str) -> list:
+        out, i = [], 0
+        while i < len(text):
+            hit = next((s for s in self.specials if text.startswith(s, i)), None)
+            if hit is not None:
+                out.append(self.special_ids[hit])
+                i += len(hit)
+                continue
+            j = min((k for k in (text.find(s, i) for s in self.specials) if k >= 0), default=len(text))
+            out.extend(text[i:j].encode("utf-8"))
+            i = j
+        return out
+
+    def decode(self, ids) -> str:
+        inv = {v: k for k, v in self.special_ids.items()}
+        parts, run = [], bytearray()
+        for t in ids:
+            if t < 256:
+                run.append(t)
+            else:
+                parts.append(run.decode("utf-8", "replace"))
+                run = bytearray()
+                parts.append(inv.get(int(t), ""))
+        parts.append(run.decode("utf-8", "replace"))
+        return "".join(parts)
+
+
+class FileTokenizer:
+    """A ``tokenizer.json`` of the HF ``tokenizers`` library."""
+
+    def __init__(self, path: Path, added=()):
+        from tokenizers import Tokenizer
+
+        self.tok = Tokenizer.from_file(str(path))
+        if added:
+            self.tok.add_special_tokens(list(added))
+        self.vocab_size = self.tok.get_vocab_size()
+
+    def token_id(self, token: str) -> int:
+        i = self.tok.token_to_id(token)
+        if i is None:
+            raise KeyError(f"the tokenizer has no token {token!r}")
+        return i
+
+    def encode(self, text: str) -> list:
+        return self.tok.encode(text, add_special_tokens=False).ids
+
+    def decode(self, ids) -> str:
+        return self.tok.decode(list(ids), skip_special_tokens=False)
+
+
+def find(name: str) -> Path:
+    cands = [Path(name), Path(name) / "tokenizer.json"]
+    for root in os.environ.get("BUX_TOKENIZERS", "").split(os.pathsep):
+        if root:
+            cands += [Path(root) / name / "tokenizer.json", Path(root) / f"{name}.json"]
+    for p in cands:
+        if p.is_file():
+            return p
+    raise FileNotFoundError(f"no tokenizer file for {name!r}: give a path to a tokenizer.json, or put it "
+                            f"under a folder listed in BUX_TOKENIZERS")
+
+
+def load(config):
+    """`config`: a ``tokenizer(...)`` setting (None means the byte tokenizer)."""
+    if config is None or config.name == "bytes":
+        specials = ("<|endoftext|>",) if config is None else (config.bos, config.eos, *config.added)
+        return ByteTokenizer(specials)
+    return FileTokenizer(find(config.name), config.added)

@@ -1,0 +1,102 @@
+"""Data preparation: tokenizer, documents, the three packings, the pipeline and its reader."""
+import json
+from types import SimpleNamespace as NS
+
+import numpy as np
+import pytest
+
+from bux_b200.data import packing as P
+from bux_b200.data import prepared, tokenizer as TK
+
+
+def test_byte_tokenizer_round_trip():
+    tok = TK.ByteTokenizer(("<|endoftext|>", "<|im_start|>"))
+    text = "héllo<|endoftext|>wörld<|im_start|>"
+    ids = tok.encode(text)
+    assert tok.decode(ids) == text
+    assert ids.count(256) == 1 and ids.count(257) == 1 and tok.vocab_size == 258
+
+
+def _show(rows):
+    return ["".join("ABCD"[d] * n for d, _, n in row) for row in rows]
+
+
+def test_the_three_packings_on_the_documented_example():
+    lengths = [5, 3, 10, 2]  # A, B, C, D in rows of 8
+    concat = P.plan(lengths, 8, NS(type="concat"))
+    assert [sum(n for *_, n in r) for r in concat[:2]] == [8, 8]
+    greedy = P.plan(lengths, 8, NS(type="greedy", long="drop", max_docs=None))
+    assert _show(greedy) == ["AAAAABBB", "DD"]
+    best = P.plan(lengths, 8, NS(type="best_fit", long="split", max_docs=None, sort=True))
+    assert sorted(_show(best)) == sorted(["CCCCCCCC", "AAAAABBB", "CCCDD"])
+    trunc = P.plan(lengths, 8, NS(type="best_fit", long="truncate", max_docs=None, sort=True))
+    assert sorted(_show(trunc)) == sorted(["CCCCCCCC", "AAAAABBB", "DD"])
+
+
+def test_every_token_is_a_target_once_except_document_firsts():
+    rng = np.random.default_rng(0)
+    lengths = rng.integers(2, 40, 50).tolist()
+    docs = [np.arange(n, dtype=np.int32) + 1000 * i for i, n in enumerate(lengths)]
+    masks = [np.ones(n, bool) for n in lengths]
+    for pk in (NS(type="best_fit", long="split", max_docs=None, sort=True, doc_mask=True),
+               NS(type="greedy", long="split", max_docs=3, doc_mask=True)):
+        rows = P.plan(lengths, 16, pk)
+        assert all(sum(p[2] for p in row) <= 16 for row in rows)
+        ids, pos, mask = P.materialize(rows, docs, masks, 16, True)
+        targets = ids[mask]
+        assert len(set(targets.tolist())) == len(targets) == sum(lengths) - len(lengths)
+        # positions restart at every document and at every piece
+        assert (pos[:, 0] == 0).all()
+
+
+def test_permutation_is_a_bijection():
+    for n in (1, 2, 7, 100, 257):
+        got = sorted(prepared.permuted(i, n, (3, 1)) for i in range(n))
+        assert got == list(range(n))
+    a = [prepared.permuted(i, 100, (3, 1)) for i in range(100)]
+    b = [prepared.permuted(i, 100, (3, 2)) for i in range(100)]
+    assert a != b and a != list(range(100))
+
+
+def test_prepare_and_train_on_text(tmp_path):
+    import torch
+
+    from bux_b200.data import pipeline
+    from bux_b200.lang import compile_runs
+    from bux_b200.train.trainer import Trainer
+
+    data = tmp_path / "docs.jsonl"
+    rng = np.random.default_rng(1)
+    with open(data, "w") as f:
+        for i in range(200):
+            words = " ".join(rng.choice(["alpha", "beta", "gamma", "delta"], rng.integers(3, 30)))
+            f.write(json.dumps({"text": f"doc {i}: {words}"}) + "\n")
+    src = f"""
+d_model=32
+vocab_size=257
+n = rmsnorm
+block = [n gqa(num_heads=2, num_kv_heads=1, rope=rope())] [n gated_mlp(intermediate_size=48, activation=swish)]
+model = embed block^2 n head
+data = text(path="{data}")
+tokenizer = tokenizer(name="bytes")
+optimizer = adamw(lr=1e-2)
+seq_len = 64
+batch = 4
+steps = 8
+precision = precision(compute=float32)
+"""
+    run = compile_runs(src, filename="t.bux")[0]
+    (job,) = pipeline.jobs(run.train, tmp_path / "packed")
+    folder = pipeline.prepare(job, echo=lambda *_: None)
+    meta = json.loads((folder / "dataset.json").read_text())
+    assert folder.name.startswith("text-") and meta["vocab_size"] == 257 and meta["stats"]["rows"] > 10
+    assert pipeline.prepare(job, echo=lambda *_: None) == folder  # not prepared twice
+    tr = Trainer(run, device="cpu", cache=tmp_path / "packed")
+    feed = iter(tr.batches())
+    first = next(feed)
+    assert first.input_ids.shape == (4, 64) and first.loss_mask.any()
+    assert (first.position_ids[:, 1:] <= first.position_ids[:, :-1]).any()  # several documents per row
+    losses = [tr.train_step(b)["loss"].item() for b in [first] + [next(feed) for _ in range(7)]]
+    assert losses[-1] < losses[0]
+    again = next(iter(Trainer(run, device="cpu", cache=tmp_path / "packed").batches()))
+    assert np.array_equal(again.input_ids, first.input_ids)  # batch i depends on the seed and i only
