@@ -1,0 +1,139 @@
+"""Standard decoder families: when an architecture is exactly one of them, the export is
+written in that family's own Hugging Face format (config fields and tensor names), so
+stock `transformers` and stock vLLM load and serve it with their own kernels.
+
+Families: ``llama`` (pre-norm GQA + SwiGLU), ``qwen3`` (the same with per-head q/k
+RMSNorm), ``qwen3_moe`` (qwen3 with softmax top-k routed SwiGLU experts).
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..config import layers as L
+from ..lang import ir
+
+MIXERS = ("gqa", "mla", "csa", "gla", "deltanet", "gdn", "kda", "gdn2", "lightning", "rwkv7", "mamba", "mamba2",
+          "conv", "short_conv")
+
+
+def _block_parts(block) -> Optional[tuple]:
+    """(norm, gqa, norm, ffn) configs of a ``[norm attn] [norm ffn]`` block, else None."""
+    if not isinstance(block, ir.Seq) or len(block.items) != 2:
+        return None
+    out = []
+    for br in block.items:
+        if not isinstance(br, ir.Residual) or not isinstance(br.body, ir.Seq) or len(br.body.items) != 2:
+            return None
+        a, b = br.body.items
+        if not (isinstance(a, ir.Layer) and isinstance(b, ir.Layer)):
+            return None
+        out += [a.config, b.config]
+    return tuple(out)
+
+
+def _plain_norm(c) -> bool:
+    return (isinstance(c, L.NormalizationConfig) and c.type == "rmsnorm" and c.affine and not c.bias
+            and not c.zero_centered and not c.scale_input)
+
+
+def detect(arch: ir.Architecture) -> Optional[str]:
+    if arch.residual is not None:
+        return None
+    g = arch.graph
+    if not isinstance(g, ir.Seq) or len(g.items) != 4:
+        return None
+    emb, rep, norm, head = g.items
+    if not (isinstance(emb, ir.Layer) and emb.config.type == "embed" and isinstance(rep, ir.Repeat)
+            and isinstance(norm, ir.Layer) and _plain_norm(norm.config)
+            and isinstance(head, ir.Layer) and head.config.type == "head"):
+        return None
+    e = emb.config
+    if e.max_positions is not None or e.scale_by_sqrt_dim or e.norm is not None or head.config.softcap or head.config.bias:
+        return None
+    parts = _block_parts(rep.body)
+    if parts is None or rep.body.share is not None:
+        return None
+    n1, attn, n2, ffn = parts
+    if not (_plain_norm(n1) and _plain_norm(n2) and isinstance(attn, L.GQAConfig)):
+        return None
+    a = attn
+    plain = (a.rope is not None and a.rope.layout == "half" and a.rope.fraction == 1.0 and a.rope.scaling is None
+             and not a.bias and not a.sinks and not a.gated and a.softcap is None and a.sliding_window_size is None
+             and a.scale is None and a.output_norm is None and not a.qk_norm_all_heads
+             and all(getattr(a, f) in (None, False) for f in ("kv_conv_size", "differential", "k_eq_v", "indexer")))
+    if not plain:
+        return None
+    qk = a.qk_norm is not None and _plain_norm(a.qk_norm)
+    if a.qk_norm is not None and not qk:
+        return None
+    if isinstance(ffn, L.MLPConfig):
+        ok = (ffn.type == "gated_mlp" and ffn.activation == "swish" and not ffn.bias and ffn.limit is None
+              and not ffn.up_offset and ffn.up_softcap is None)
+        return ("qwen3" if qk else "llama") if ok else None
+    if isinstance(ffn, L.MoEConfig) and qk:
+        x = ffn.expert
+        ok = (ffn.router == "softmax" and not ffn.num_shared_experts and ffn.num_groups == 1
+              and not ffn.router_bias and ffn.load_balancing not in ("aux_free", "smebu")
+              and ffn.routed_scaling_factor == 1.0 and ffn.router_logit_scale == 1.0
+              and x.type == "gated_mlp" and x.activation == "swish" and x.limit is None and not x.up_offset)
+        return "qwen3_moe" if ok else None
+    return None
+
+
+def convert(family: str, arch: ir.Architecture, t: dict, dtype) -> tuple:
+    """(config.json dict, tensors under the family's names) from the exported tensors `t`."""
+    emb, rep, norm, head = arch.graph.items
+    n1, attn, n2, ffn = _block_parts(rep.body)
+    d = arch.d_model
+    hd = attn.head_dim or d // attn.num_heads
+    layers = rep.times
+    out = {"model.embed_tokens.weight": t["graph.items.0.tokens.embedding"],
+           "model.norm.weight": t["graph.items.2.scale"]}
+    tied = head.config.tied
+    if not tied:
+        out["lm_head.weight"] = t["graph.items.3.proj.weight"]
+    for i in range(layers):
+        src = f"graph.items.1.items.{i}.items"
+        dst = f"model.layers.{i}"
+        out[f"{dst}.input_layernorm.weight"] = t[f"{src}.0.body.items.0.scale"]
+        out[f"{dst}.post_attention_layernorm.weight"] = t[f"{src}.1.body.items.0.scale"]
+        at = f"{src}.0.body.items.1"
+        for p in "qkvo":
+            out[f"{dst}.self_attn.{p}_proj.weight"] = t[f"{at}.{p}.weight"]
+        if family != "llama":
+            out[f"{dst}.self_attn.q_norm.weight"] = t[f"{at}.q_norm.scale"]
+            out[f"{dst}.self_attn.k_norm.weight"] = t[f"{at}.k_norm.scale"]
+        ff = f"{src}.1.body.items.1"
+        if family == "qwen3_moe":
+            out[f"{dst}.mlp.gate.weight"] = t[f"{ff}.router.weight"]
+            gate, up, down = t[f"{ff}.experts.gate"], t[f"{ff}.experts.up"], t[f"{ff}.experts.down"]
+            for e in range(gate.shape[0]):
+                out[f"{dst}.mlp.experts.{e}.gate_proj.weight"] = gate[e]
+                out[f"{dst}.mlp.experts.{e}.up_proj.weight"] = up[e]
+                out[f"{dst}.mlp.experts.{e}.down_proj.weight"] = down[e]
+        else:
+            for p in ("gate", "up", "down"):
+                out[f"{dst}.mlp.{p}_proj.weight"] = t[f"{ff}.{p}.weight"]
+    cfg = {
+        "vocab_size": arch.vocab_size, "hidden_size": d, "num_hidden_layers": layers,
+        "num_attention_heads": attn.num_heads, "num_key_value_heads": attn.num_kv_heads, "head_dim": hd,
+        "rms_norm_eps": n1.eps, "rope_theta": attn.rope.base, "hidden_act": "silu", "attention_bias": False,
+        "attention_dropout": 0.0, "max_position_embeddings": 131072, "tie_word_embeddings": bool(tied),
+        "torch_dtype": str(dtype).removeprefix("torch."), "use_cache": True,
+        "rope_parameters": {"rope_type": "default", "rope_theta": attn.rope.base},
+    }
+    if family == "llama":
+        cfg.update(model_type="llama", architectures=["LlamaForCausalLM"], intermediate_size=ffn.intermediate_size,
+                   mlp_bias=False)
+    elif family == "qwen3":
+        cfg.update(model_type="qwen3", architectures=["Qwen3ForCausalLM"], intermediate_size=ffn.intermediate_size)
+    else:
+        cfg.update(model_type="qwen3_moe", architectures=["Qwen3MoeForCausalLM"],
+                   intermediate_size=ffn.expert.intermediate_size, moe_intermediate_size=ffn.expert.intermediate_size,
+                   num_experts=ffn.num_experts, num_experts_per_tok=ffn.top_k, norm_topk_prob=bool(ffn.normalize_top_k),
+                   decoder_sparse_step=1, mlp_only_layers=[], output_router_logits=False,
+                   router_aux_loss_coef=ffn.aux_loss_weight or 0.0)
+    return cfg, {k: v.to(dtype) if v.is_floating_point() else v for k, v in out.items()}

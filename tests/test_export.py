@@ -1,0 +1,80 @@
+"""Export: a trained run → a Hugging Face folder that computes the same logits, in the
+bux format and, for standard decoders, in the family's own format read by transformers."""
+import json
+
+import pytest
+import torch
+
+from bux_b200.export import check as C
+from bux_b200.export import export, native, weights as W
+from bux_b200.lang import compile_runs
+from bux_b200.train.trainer import train
+
+BASE = """
+d_model=32
+vocab_size=64
+n = rmsnorm
+a = gqa(num_heads=4, num_kv_heads=2, rope=rope(){qk})
+f = {ffn}
+block = [n a] [n f]
+model = embed block^2 n head(tied=false)
+data = synthetic
+optimizer = adamw(lr=1e-2)
+seq_len = 16
+batch = 4
+steps = 3
+checkpoint = checkpoint(every=3)
+precision = precision(compute=float32)
+log = log(every=100)
+{extra}
+"""
+DENSE = "gated_mlp(intermediate_size=48, activation=swish)"
+MOE = "moe(num_experts=4, top_k=2, expert=gated_mlp(intermediate_size=16, activation=swish))"
+
+
+def _trained(tmp_path, qk="", ffn=DENSE, extra=""):
+    run = compile_runs(BASE.format(qk=qk, ffn=ffn, extra=extra), filename="e.bux")[0]
+    tr = train(run, out=tmp_path / "runs", device="cpu", quiet=True)
+    (folder,) = list((tmp_path / "runs").iterdir())
+    return run, tr, folder
+
+
+def test_weight_names_split_and_fuse_back(tmp_path):
+    run, tr, _ = _trained(tmp_path, ffn=MOE)
+    t = W.tensors(tr.model)
+    names = set(t)
+    assert any(n.endswith(".q.weight") for n in names) and not any("qkv" in n for n in names)
+    assert any(n.endswith("experts.gate") for n in names) and any(n.endswith("experts.down") for n in names)
+    back = W.fused(tr.model, t)
+    own = tr.model.state_dict()
+    assert set(back) == set(own)
+    assert all(torch.equal(back[k], own[k]) for k in own)
+
+
+def test_detects_standard_families():
+    fam = lambda qk, ffn, extra="": native.detect(compile_runs(BASE.format(qk=qk, ffn=ffn, extra=extra), filename="e.bux")[0].arch)
+    assert fam("", DENSE) == "llama"
+    assert fam(", qk_norm=rmsnorm", DENSE) == "qwen3"
+    assert fam(", qk_norm=rmsnorm", MOE) == "qwen3_moe"
+    assert fam(", sinks=true", DENSE) is None
+    assert fam("", DENSE, "residual = hc(expansion=2)") is None
+
+
+def test_bux_format_round_trip(tmp_path):
+    run, tr, folder = _trained(tmp_path, qk=", sinks=true")   # not a standard family
+    out = export(folder, tmp_path / "hf", dtype="float32", check=True, echo=lambda *_: None)
+    cfg = json.loads((out / "config.json").read_text())
+    assert cfg["model_type"] == "bux" and cfg["bux"]["run"] == run.id and cfg["bux_layer_types"].count("gqa") == 2 and cfg["layer_types"] == ["full_attention"] * 2
+    assert (out / "modeling_bux.py").exists() and (out / "model.safetensors").exists()
+    report = C.compare(tr.model, out)
+    assert report["ok"] and report["max_abs_error"] < 1e-4
+
+
+@pytest.mark.parametrize("qk,ffn,family", [("", DENSE, "llama"), (", qk_norm=rmsnorm", DENSE, "qwen3"),
+                                           (", qk_norm=rmsnorm", MOE, "qwen3_moe")])
+def test_standard_families_load_in_transformers(tmp_path, qk, ffn, family):
+    run, tr, folder = _trained(tmp_path, qk=qk, ffn=ffn)
+    out = export(folder, tmp_path / "hf", dtype="float32", echo=lambda *_: None)
+    assert json.loads((out / "config.json").read_text())["model_type"] == family
+    report = C.compare(tr.model, out)   # transformers' own implementation of the family
+    assert report["ok"] and report["max_abs_error"] < 2e-3, report
