@@ -46,7 +46,8 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& c, const c10::optional<Tenso
           const c10::optional<Tensor>& sfb, const c10::optional<Tensor>& group_offsets,
           const c10::optional<Tensor>& status, int64_t kind, int64_t mode, int64_t M, int64_t N,
           int64_t K, int64_t k_total, int64_t groups, bool a_mn, bool b_mn, int64_t out_kind,
-          int64_t bn, int64_t sms, const c10::optional<Tensor>& wait_flags, int64_t wait_epoch) {
+          int64_t bn, int64_t sms, const c10::optional<Tensor>& wait_flags, int64_t wait_epoch,
+          int64_t wait_rows, int64_t m_rotate, bool wait_on_k) {
   check_cuda(a, "a"); check_cuda(b, "b"); check_cuda(c, "c");
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "a and b are 2-D views");
   c10::cuda::CUDAGuard guard(a.device());
@@ -71,7 +72,9 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& c, const c10::optional<Tenso
   g.sms = (int)sms;
   if (wait_flags.has_value()) {
     g.wait_flags = opt_i32(wait_flags); g.wait_world = (int)wait_flags->numel(); g.wait_epoch = (int)wait_epoch;
+    g.wait_rows = (int)wait_rows; g.wait_on_k = wait_on_k;
   }
+  g.m_rotate = (int)m_rotate;
   const char* err = bux::gemm_launch(g, stream_of(a));
   TORCH_CHECK(err == nullptr, "bux gemm: ", err);
 }
@@ -262,6 +265,24 @@ void zero_pad_rows(Tensor& buf, const Tensor& offsets, const Tensor& counts) {
   c10::cuda::CUDAGuard guard(buf.device());
   bux::zero_pad_rows(buf.data_ptr(), offsets.data_ptr<int>(), counts.data_ptr<int>(), (int)counts.numel(), (int)buf.size(-1), stream_of(buf));
 }
+void tp_push_block(const Tensor& src, const Tensor& peer_base, int64_t my_rank, int64_t sms) {
+  check_cuda(src, "src");
+  TORCH_CHECK(src.is_contiguous() && src.scalar_type() == at::kBFloat16 && src.size(-1) % 8 == 0, "tp_push_block: contiguous bf16 rows, width % 8 == 0");
+  c10::cuda::CUDAGuard guard(src.device());
+  const int d = (int)src.size(-1);
+  bux::tp_push_block(src.data_ptr(), reinterpret_cast<const uint64_t*>(peer_base.data_ptr<int64_t>()), (int)peer_base.numel(),
+                     (int)my_rank, src.numel() / d, d, (int)sms, stream_of(src));
+}
+void tp_pull_reduce(const Tensor& peer_base, int64_t my_rank, Tensor& out, const c10::optional<Tensor>& residual,
+                    const c10::optional<Tensor>& flags, int64_t epoch, const c10::optional<Tensor>& status, double limit_s) {
+  check_cuda(out, "out");
+  TORCH_CHECK(out.is_contiguous() && out.scalar_type() == at::kBFloat16 && out.size(-1) % 8 == 0, "tp_pull_reduce: contiguous bf16 rows");
+  c10::cuda::CUDAGuard guard(out.device());
+  const int d = (int)out.size(-1);
+  bux::tp_pull_reduce(reinterpret_cast<const uint64_t*>(peer_base.data_ptr<int64_t>()), (int)peer_base.numel(), (int)my_rank,
+                      out.numel() / d, d, out.data_ptr(), residual.has_value() ? residual->data_ptr() : nullptr,
+                      opt_i32(flags), (int)epoch, (uint64_t)(limit_s * 1e9), status_ptr(status), stream_of(out));
+}
 void ep_wait(const Tensor& flags, int64_t epoch, const c10::optional<Tensor>& status, double limit_s) {
   c10::cuda::CUDAGuard guard(flags.device());
   bux::ep_wait(flags.data_ptr<int>(), (int)flags.numel(), (int)epoch, (uint64_t)(limit_s * 1e9), status_ptr(status), stream_of(flags));
@@ -276,7 +297,9 @@ TORCH_LIBRARY(bux_b200, m) {
   m.def("ep_pull_dot(Tensor peer_base, Tensor rank_of, Tensor row_of, Tensor dout, Tensor(a!) dw) -> ()", &ep_pull_dot);
   m.def("zero_pad_rows(Tensor(a!) buf, Tensor offsets, Tensor counts) -> ()", &zero_pad_rows);
   m.def("ep_wait(Tensor flags, int epoch, Tensor? status, float limit_s) -> ()", &ep_wait);
-  m.def("gemm(Tensor a, Tensor b, Tensor(a!) c, Tensor? sfa, Tensor? sfb, Tensor? group_offsets, Tensor? status, int kind, int mode, int M, int N, int K, int k_total, int groups, bool a_mn, bool b_mn, int out_kind, int bn, int sms, Tensor? wait_flags=None, int wait_epoch=0) -> ()", &gemm);
+  m.def("tp_push_block(Tensor src, Tensor peer_base, int my_rank, int sms) -> ()", &tp_push_block);
+  m.def("tp_pull_reduce(Tensor peer_base, int my_rank, Tensor(a!) out, Tensor? residual, Tensor? flags, int epoch, Tensor? status, float limit_s) -> ()", &tp_pull_reduce);
+  m.def("gemm(Tensor a, Tensor b, Tensor(a!) c, Tensor? sfa, Tensor? sfb, Tensor? group_offsets, Tensor? status, int kind, int mode, int M, int N, int K, int k_total, int groups, bool a_mn, bool b_mn, int out_kind, int bn, int sms, Tensor? wait_flags=None, int wait_epoch=0, int wait_rows=0, int m_rotate=0, bool wait_on_k=False) -> ()", &gemm);
   m.def("rmsnorm_fwd(Tensor x, Tensor? w, Tensor(a!) y, Tensor(b!) rstd, float eps) -> ()", &rmsnorm_fwd);
   m.def("rmsnorm_bwd(Tensor x, Tensor? w, Tensor dy, Tensor rstd, Tensor(a!) dx, Tensor? dw) -> ()", &rmsnorm_bwd);
   m.def("norm_rope(bool bwd, Tensor x, Tensor? w, Tensor cos, Tensor sin, Tensor(a!) y, Tensor? rstd, Tensor? dy, Tensor? dw, int tokens, int heads, int D, int stride_x, int stride_y, float eps) -> ()", &norm_rope);

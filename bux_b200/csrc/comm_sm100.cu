@@ -163,6 +163,58 @@ __global__ void zero_pad_rows_kernel(__nv_bfloat16* __restrict__ buf, const int*
       reinterpret_cast<uint4*>(buf + (long)r * d)[c] = make_uint4(0, 0, 0, 0);
 }
 
+// Tensor / sequence parallelism: this rank's block of rows goes into every peer's gather
+// buffer at row `my_rank * rows` (its own included), 16 bytes per store.
+__global__ void tp_push_block_kernel(const uint4* __restrict__ src, const uint64_t* __restrict__ peer_base,
+                                     int world, int my_rank, long vecs_per_block) {
+  const long total = vecs_per_block * world;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    // peers in rotated order so the ranks do not all write to the same GPU at once
+    const int step = (int)(i / vecs_per_block);
+    const int peer = (my_rank + 1 + step) % world;
+    const long v = i % vecs_per_block;
+    uint4* dst = reinterpret_cast<uint4*>(peer_base[peer]) + (long)my_rank * vecs_per_block + v;
+    *dst = src[v];
+  }
+}
+
+// out[r, :] = (residual[r, :] +) sum over peers p of partial_p[my_rank * rows + r, :]: the
+// reduce-scatter of row-parallel partial sums by peer loads, fp32 accumulation. Waits
+// (bounded) for every peer's flag first.
+__global__ void tp_pull_reduce_kernel(const uint64_t* __restrict__ peer_base, int world, int my_rank, long rows,
+                                      int d, __nv_bfloat16* __restrict__ out,
+                                      const __nv_bfloat16* __restrict__ residual, const int* __restrict__ flags,
+                                      int epoch, uint64_t limit_ns, Status* st) {
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if (flags != nullptr) {
+    if (!wait_flags(flags, world, epoch, limit_ns, st, 3)) ok_s = 0;
+    __syncthreads();
+    if (!ok_s) return;
+  }
+  const int vec = d / 8;
+  const long total = rows * vec;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (residual != nullptr) {
+      const uint4 v = reinterpret_cast<const uint4*>(residual)[i];
+      float2 t;
+      t = unpack_bf16(v.x); acc[0] = t.x; acc[1] = t.y; t = unpack_bf16(v.y); acc[2] = t.x; acc[3] = t.y;
+      t = unpack_bf16(v.z); acc[4] = t.x; acc[5] = t.y; t = unpack_bf16(v.w); acc[6] = t.x; acc[7] = t.y;
+    }
+    for (int s = 0; s < world; ++s) {
+      const int peer = (my_rank + s) % world;
+      const uint4 v = *(reinterpret_cast<const uint4*>(peer_base[peer]) + (long)my_rank * total + i);
+      float2 t;
+      t = unpack_bf16(v.x); acc[0] += t.x; acc[1] += t.y; t = unpack_bf16(v.y); acc[2] += t.x; acc[3] += t.y;
+      t = unpack_bf16(v.z); acc[4] += t.x; acc[5] += t.y; t = unpack_bf16(v.w); acc[6] += t.x; acc[7] += t.y;
+    }
+    reinterpret_cast<uint4*>(out)[i] = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]),
+                                                  pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+  }
+}
+
 static inline int blocks_for(long warps_needed, int warps_per_block, int cap) {
   long g = (warps_needed + warps_per_block - 1) / warps_per_block;
   return (int)(g < 1 ? 1 : (g > cap ? cap : g));
@@ -192,6 +244,22 @@ void ep_pull_dot(const uint64_t* peer_base, const int* rank_of, const int* row_o
 }
 void zero_pad_rows(void* buf, const int* offsets, const int* counts, int groups, int d, cudaStream_t s) {
   zero_pad_rows_kernel<<<dim3(groups, 16), 256, 0, s>>>((__nv_bfloat16*)buf, offsets, counts, d);
+}
+void tp_push_block(const void* src, const uint64_t* peer_base, int world, int my_rank, long rows, int d, int sms,
+                   cudaStream_t s) {
+  const long vecs = rows * d / 8;
+  const long work = vecs * world;
+  const int cap = (sms > 0 ? sms : 32) * 4;   // a few SMs: the GEMM runs beside it
+  int grid = (int)((work + 255) / 256 > cap ? cap : (work + 255) / 256);
+  tp_push_block_kernel<<<grid < 1 ? 1 : grid, 256, 0, s>>>((const uint4*)src, peer_base, world, my_rank, vecs);
+}
+void tp_pull_reduce(const uint64_t* peer_base, int world, int my_rank, long rows, int d, void* out,
+                    const void* residual, const int* flags, int epoch, uint64_t limit_ns, Status* st,
+                    cudaStream_t s) {
+  const long work = rows * (d / 8);
+  int grid = (int)((work + 255) / 256 > 148 * 8 ? 148 * 8 : (work + 255) / 256);
+  tp_pull_reduce_kernel<<<grid < 1 ? 1 : grid, 256, 0, s>>>(peer_base, world, my_rank, rows, d, (__nv_bfloat16*)out,
+                                                           (const __nv_bfloat16*)residual, flags, epoch, limit_ns, st);
 }
 void ep_wait(const int* flags, int world, int epoch, uint64_t limit_ns, Status* st, cudaStream_t s) {
   ep_wait_kernel<<<1, 32, 0, s>>>(flags, world, epoch, limit_ns, st);

@@ -16,6 +16,11 @@ void ep_pull_combine(const uint64_t* peer_base, const int* rank_of, const int* r
 void ep_pull_dot(const uint64_t* peer_base, const int* rank_of, const int* row_of, const void* dout, float* dw,
                  long picks, int k, int d, cudaStream_t s);
 void zero_pad_rows(void* buf, const int* offsets, const int* counts, int groups, int d, cudaStream_t s);
+void tp_push_block(const void* src, const uint64_t* peer_base, int world, int my_rank, long rows, int d, int sms,
+                   cudaStream_t s);
+void tp_pull_reduce(const uint64_t* peer_base, int world, int my_rank, long rows, int d, void* out,
+                    const void* residual, const int* flags, int epoch, uint64_t limit_ns, Status* st,
+                    cudaStream_t s);
 void ep_wait(const int* flags, int world, int epoch, uint64_t limit_ns, Status* st, cudaStream_t s);
 
 }  // namespace bux

@@ -80,6 +80,7 @@ struct TileWalk {
       int rows_here = min(GM, m_tiles - sup * GM);
       int mt = sup * GM + local % rows_here;
       int nt = local / rows_here;
+      if (p.m_rotate) mt = (mt + p.m_rotate) % m_tiles;
       c.group = 0; c.m0 = mt * BM; c.m_end = p.M; c.n0 = nt * bn; c.k0 = 0; c.k1 = p.K;
       c.valid = true;
     } else if (p.mode == MODE_GROUPED_ROWS) {
@@ -153,7 +154,23 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
       TileWalk walk(p, BN);
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
-      if (p.wait_flags != nullptr) {
+      uint32_t seen = 0;  // senders whose flag this CTA has seen (wait_rows mode)
+      auto wait_sender = [&](int r) -> bool {
+        if (r >= p.wait_world) r = p.wait_world - 1;
+        if (seen >> r & 1u) return true;
+        const uint64_t t0 = global_ns();
+        int v;
+        do {
+          asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p.wait_flags + r) : "memory");
+          if (v >= p.wait_epoch) break;
+          if (global_ns() - t0 > p.wait_limit_ns) { *abort_flag = 1; report_failure(st, KID_GEMM, 6); return false; }
+          __nanosleep(100);
+        } while (true);
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        seen |= 1u << r;
+        return true;
+      };
+      if (p.wait_flags != nullptr && p.wait_rows == 0) {
         // operand A is being written by peer GPUs: wait for every sender's flag
         const uint64_t t0 = global_ns();
         for (int r = 0; r < p.wait_world && ok; ++r) {
@@ -172,7 +189,14 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
         const int b_row0 = (p.mode == MODE_GROUPED_ROWS ? c.group * p.N : 0) + c.n0;
         // MN-major B of a grouped-rows GEMM is stored [groups * K, N]
         const int b_k_off = (B_MN && p.mode == MODE_GROUPED_ROWS) ? c.group * p.K : 0;
+        if (p.wait_flags != nullptr && p.wait_rows > 0 && !p.wait_on_k) {
+          // a tile may straddle two senders' row blocks
+          if (!wait_sender(c.m0 / p.wait_rows) || !wait_sender((min(c.m0 + BM, p.M) - 1) / p.wait_rows)) { ok = false; break; }
+        }
         for (int k = c.k0; k < c.k1; k += Cfg::BK_ELEMS) {
+          if (p.wait_flags != nullptr && p.wait_rows > 0 && p.wait_on_k) {
+            if (!wait_sender(k / p.wait_rows) || !wait_sender((min(k + Cfg::BK_ELEMS, c.k1) - 1) / p.wait_rows)) { ok = false; break; }
+          }
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, st, KID_GEMM, 1)) { ok = false; break; }
           uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
           uint8_t* sb = sa + Cfg::A_BYTES;
@@ -406,6 +430,8 @@ const char* gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   p.c = a.c; p.ldc = a.ldc; p.out_kind = a.out_kind;
   p.sfa = a.sfa; p.sfb = a.sfb; p.status = a.status;
   p.wait_flags = a.wait_flags; p.wait_world = a.wait_world; p.wait_epoch = a.wait_epoch; p.wait_limit_ns = a.wait_limit_ns;
+  p.wait_rows = a.wait_rows; p.m_rotate = a.m_rotate; p.wait_on_k = a.wait_on_k ? 1 : 0;
+  if (a.wait_world > 32) return "at most 32 senders can be waited for";
   const int elem = a.kind == KIND_BF16 ? 2 : 1;
   const int bk = a.kind == KIND_BF16 ? 64 : 128;
   const int bn = a.bn;

@@ -25,6 +25,8 @@ struct GemmParams {
   // optional: before its first load the producer waits (bounded) until
   // wait_flags[0..wait_world) >= wait_epoch: senders on peer GPUs filled operand A
   const int* wait_flags; int wait_world, wait_epoch; unsigned long long wait_limit_ns;
+  // wait_rows > 0: per-sender row blocks (see GemmArgs); m_rotate in tiles
+  int wait_rows, m_rotate, wait_on_k;
 };
 
 // What a caller fills in. `a_outer/a_inner` are the stored dims of A (inner contiguous):
@@ -42,6 +44,11 @@ struct GemmArgs {
   int sms = 0;
   const int* wait_flags = nullptr; int wait_world = 0, wait_epoch = 0;
   unsigned long long wait_limit_ns = 5000000000ull;
+  // wait_rows > 0: the flagged operand arrives in blocks of wait_rows rows per sender
+  // (rows of A, or of the contraction dimension with wait_on_k); a tile waits only for
+  // the sender of its rows. m_rotate (dense mode, in tiles) starts the walk at this
+  // rank's own rows, which need no wait.
+  int wait_rows = 0, m_rotate = 0; bool wait_on_k = false;
 };
 
 // Returns nullptr on success, else a static message.

@@ -62,8 +62,17 @@ class Linear(nn.Module):
         init_weight(self.weight, bctx.init, init_role)
         self.bias = nn.Parameter(torch.zeros(fan_out, dtype=bctx.dtype)) if bias else None
         self.role = role
+        self.tp_fused = None  # (kind, group, reorder) when the tensor-parallel collective runs in the GEMM
 
     def forward(self, x, ctx: Optional[Context] = None):
+        if self.tp_fused is not None and ops.kernels_on(x) and x.dtype == torch.bfloat16:
+            from ...parallel import tensor_fused as TF
+
+            kind, group, reorder = self.tp_fused
+            if kind == "gather":
+                return TF.gather_matmul(x, self.weight, group, reorder)
+            return TF.matmul_scatter(x, self.weight, group, ctx.input_ids.shape[0] if ctx is not None else x.shape[0],
+                                     reorder)
         fmt = ctx.precision.of(self.role) if ctx is not None else "bf16"
         return ops.linear(x, self.weight, self.bias, fmt=fmt)
 

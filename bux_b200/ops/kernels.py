@@ -53,15 +53,20 @@ def check_status(device, what: str = "kernel") -> None:
 # ------------------------------------------------------------------ GEMM
 def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
               out: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16,
-              accumulate: bool = False, bn: int = 256, sms: int = 0) -> torch.Tensor:
-    """C = A · B^T. A is [M,K] (or stored [K,M] with a_mn), B is [N,K] (or [K,N] with b_mn)."""
+              accumulate: bool = False, bn: int = 256, sms: int = 0, wait_flags=None, wait_epoch: int = 0,
+              wait_rows: int = 0, m_rotate: int = 0, wait_on_k: bool = False) -> torch.Tensor:
+    """C = A · B^T. A is [M,K] (or stored [K,M] with a_mn), B is [N,K] (or [K,N] with b_mn).
+    With `wait_flags` (int32[senders]) an operand is being written by peer GPUs in blocks
+    of `wait_rows` rows per sender (rows of A, or of the contraction with `wait_on_k`):
+    a tile's loads wait for its sender's flag to reach `wait_epoch`; `m_rotate` (tiles)
+    starts the walk at this rank's own rows."""
     m, k = (a.shape[1], a.shape[0]) if a_mn else a.shape
     n = b.shape[1] if b_mn else b.shape[0]
     if out is None:
         out = torch.empty(m, n, dtype=out_dtype, device=a.device)
     kind = OUT_BF16 if out.dtype == torch.bfloat16 else (OUT_F32_ACC if accumulate else OUT_F32)
     ops().gemm(a, b, out, None, None, None, status_word(a.device), KIND_BF16, MODE_DENSE, m, n, k, k, 1,
-               a_mn, b_mn, kind, bn, sms)
+               a_mn, b_mn, kind, bn, sms, wait_flags, wait_epoch, wait_rows, m_rotate, wait_on_k)
     _count()
     return out
 
@@ -329,6 +334,19 @@ def ep_pull_dot(peer_base, rank_of, row_of, dout):
 
 def ep_wait(flags, epoch: int, limit_s: float = 5.0) -> None:
     ops().ep_wait(flags, epoch, status_word(flags.device), limit_s)
+    _count()
+
+
+def tp_push_block(src, peer_base, my_rank: int, sms: int = 0) -> None:
+    """This rank's rows → row block `my_rank` of every peer's gather buffer (P2P stores)."""
+    ops().tp_push_block(src, peer_base, my_rank, sms)
+    _count()
+
+
+def tp_pull_reduce(peer_base, my_rank: int, out, residual=None, flags=None, epoch: int = 0,
+                   limit_s: float = 5.0) -> None:
+    """out = (residual +) Σ_peers partial_peer[row block my_rank] (P2P loads, fp32 sums)."""
+    ops().tp_pull_reduce(peer_base, my_rank, out, residual, flags, epoch, status_word(out.device), limit_s)
     _count()
 
 

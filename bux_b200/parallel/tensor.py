@@ -170,6 +170,8 @@ def shard_model(model: nn.Module, par) -> None:
     group = par.tensor_group
     n, r = dist.get_world_size(group), dist.get_rank(group)
     sequence = "tensor" in _axes(par.train.layout.stream)
+    # the collectives run inside the GEMM kernels (NVLink peers, bf16, sequence-parallel stream)
+    fused = (par.train.methods.tensor == "fused" and sequence and par.device.type == "cuda")
     par.tensor_partial = []
     layout: dict = {}
     done: set = set()
@@ -205,7 +207,10 @@ def shard_model(model: nn.Module, par) -> None:
             for name in ("q_norm", "k_norm", "out_norm"):
                 if hasattr(m, name):
                     par.tensor_partial.extend(getattr(m, name).parameters())
-            _hook(m, group, sequence)
+            if fused and not hasattr(m, "gate") and m.qkv.bias is None and m.o.bias is None:
+                m.qkv.tp_fused, m.o.tp_fused = ("gather", group, True), ("scatter", group, True)
+            else:
+                _hook(m, group, sequence)
             done.add(id(m))
         elif isinstance(m, MoE):
             f = m.f
@@ -227,7 +232,12 @@ def shard_model(model: nn.Module, par) -> None:
     for m in model.modules():
         if isinstance(m, MLP) and id(m) not in done:
             mlp(m)
-            _hook(m, group, sequence)
+            first = m.gate_up if m.gated else m.up
+            if fused and first.bias is None and m.down.bias is None and m.c.up_softcap is None:
+                # rows stay in the kernels' (rank, batch, position) order between the two GEMMs
+                first.tp_fused, m.down.tp_fused = ("gather", group, False), ("scatter", group, False)
+            else:
+                _hook(m, group, sequence)
             done.add(id(m))
     par.tensor_inside = {id(p) for m in model.modules() if id(m) in done for p in m.parameters()}
     par.tensor_layout = {name: layout[id(p)] for name, p in model.named_parameters() if id(p) in layout}

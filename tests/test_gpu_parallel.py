@@ -86,3 +86,65 @@ def test_fused_expert_parallel_matches_one_gpu(cuda, tmp_path, fmt):
             p = p[: g.shape[0]]
         err = ((g - p).norm() / p.norm().clamp_min(1e-9)).item()
         assert err < 2e-2, (name, err)
+
+
+DENSE = MOE.replace("e = moe(num_experts=8, top_k=2, expert=gated_mlp(intermediate_size=128, activation=swish))",
+                    "e = gated_mlp(intermediate_size=512, activation=swish)") \
+           .replace("model = embed block^2 n head", "model = embed block^2 n head(tied=false)")
+
+
+def _tensor_worker(rank, world, port, overrides, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import torch.distributed as dist
+
+    from bux_b200.ckpt.store import state_tree
+    from bux_b200.lang import compile_runs
+    from bux_b200.ops import kernels as K
+    from bux_b200.parallel.engine import Parallel
+    from bux_b200.train.trainer import Trainer
+
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    run = compile_runs(DENSE, filename="p.bux", overrides=overrides)[0]
+    par = Parallel(run.train, dev)
+    tr = Trainer(run, device=dev, parallel=par)
+    feed = iter(tr.batches())
+    launches = K.launches
+    losses = [tr.train_step(next(feed))["loss"].item() for _ in range(2)]
+    torch.cuda.synchronize()
+    K.check_status(dev, "tensor parallel test")
+    tree = par.checkpoint_tree(tr, state_tree)
+    if rank == 0:
+        torch.save({"losses": losses, "launches": K.launches - launches,
+                    "state": {n: p.detach().float().cpu() for n, p in tree["0"].items()}}, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("method", ["gspmd", "fused"])
+def test_sequence_parallel_tensor_parallel_matches_one_gpu(cuda, tmp_path, method):
+    """`fused`: all-gather→GEMM and GEMM→reduce-scatter inside the kernels over peer memory."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+
+    from bux_b200.lang import compile_runs
+    from bux_b200.train.trainer import Trainer
+
+    prec = "precision = precision(compute=bfloat16)"
+    run = compile_runs(DENSE, filename="p.bux", overrides=[prec])[0]
+    tr = Trainer(run, device=cuda)
+    feed = iter(tr.batches())
+    want = [tr.train_step(next(feed))["loss"].item() for _ in range(2)]
+    state = {n: p.detach().float().cpu() for n, p in tr.model.named_parameters()}
+    out = str(tmp_path / "r0.pt")
+    mp.spawn(_tensor_worker, args=(2, _free_port(), [prec, "mesh = mesh(tensor=2)", "layout = layout(stream=tensor)",
+                                                     f"methods.tensor = {method}"], out), nprocs=2, join=True)
+    got = torch.load(out)
+    assert got["losses"] == pytest.approx(want, abs=3e-2)
+    for name, p in state.items():
+        err = ((got["state"][name] - p).norm() / p.norm().clamp_min(1e-9)).item()
+        assert err < 2e-2, (name, err)

@@ -1,0 +1,63 @@
+"""render, reference pages, language-server features and the stdio server."""
+import io
+import json
+from pathlib import Path
+
+from bux_b200.lang import compile_runs, reference
+from bux_b200.lang.lsp import Server, features
+from bux_b200.lang.render import render
+
+SMOKE = (Path(__file__).resolve().parent.parent / "examples" / "experiments" / "smoke.bux").read_text()
+
+
+def test_render_shows_the_repeat_and_branches():
+    text = render(compile_runs(SMOKE, filename="smoke.bux")[0].arch)
+    assert "×2" in text and "gqa(4/2 heads)" in text and "⊕" in text and "head (tied)" in text
+
+
+def test_reference_lists_every_layer_and_setting():
+    text = reference.reference()
+    for name in ("gqa", "moe", "kda", "mamba2", "adamw", "checkpoint", "mesh"):
+        assert f"`{name}`" in text
+
+
+def test_features():
+    src = "d_model = 64\nvocab_size = 32\nattn = gqa(num_heads=4, num_kv_heads=2)\nmodel = embed [rmsnorm attn] rmsnorm head\noptimizer = adamw(lr=1e-3)\ndata = synthetic\nseq_len = 8\nbatch = 2\nsteps = 1\n"
+    assert features.diagnostics(src) == []
+    bad = src.replace("num_heads=4", "num_heads=3")
+    diags = features.diagnostics(bad)
+    assert diags and diags[0]["range"]["start"]["line"] == 2
+    assert "num_heads" in features.hover(src, 2, 8)                     # on `gqa`
+    assert "line 3" in features.hover(src, 3, 24)                       # on the use of `attn`
+    assert features.definition(src, 3, 24)["start"] == {"line": 2, "character": 0}
+    labels = [c["label"] for c in features.completion(src[:src.index("num_kv")], 2, len("attn = gqa(num_heads=4, "))]
+    assert "num_kv_heads" in labels and "sliding_window_size" in labels
+    tops = [c["label"] for c in features.completion("model = em", 0, 10)]
+    assert "embed" in tops and all(t.startswith("em") for t in tops)
+
+
+def _frame(msg):
+    body = json.dumps({"jsonrpc": "2.0", **msg}).encode()
+    return f"Content-Length: {len(body)}\r\n\r\n".encode() + body
+
+
+def test_server_over_stdio():
+    uri = "file:///x.bux"
+    inp = io.BytesIO(b"".join(_frame(m) for m in [
+        {"id": 1, "method": "initialize", "params": {}},
+        {"method": "textDocument/didOpen", "params": {"textDocument": {"uri": uri, "text": "model = embed head\nd_model = 8\n"}}},
+        {"id": 2, "method": "textDocument/hover", "params": {"textDocument": {"uri": uri}, "position": {"line": 0, "character": 9}}},
+        {"id": 3, "method": "shutdown"}, {"method": "exit"}]))
+    out = io.BytesIO()
+    Server(inp, out).serve()
+    raw = out.getvalue()
+    msgs = []
+    while raw:
+        head, _, rest = raw.partition(b"\r\n\r\n")
+        n = int(head.split(b":")[1])
+        msgs.append(json.loads(rest[:n]))
+        raw = rest[n:]
+    assert msgs[0]["result"]["capabilities"]["hoverProvider"]
+    diag = next(m for m in msgs if m.get("method") == "textDocument/publishDiagnostics")
+    assert diag["params"]["diagnostics"]  # the file has no vocab_size / optimizer ...
+    assert next(m for m in msgs if m.get("id") == 2)["result"]["contents"]["value"].startswith("embed")
