@@ -61,3 +61,41 @@ def test_server_over_stdio():
     diag = next(m for m in msgs if m.get("method") == "textDocument/publishDiagnostics")
     assert diag["params"]["diagnostics"]  # the file has no vocab_size / optimizer ...
     assert next(m for m in msgs if m.get("id") == 2)["result"]["contents"]["value"].startswith("embed")
+
+
+def test_studio_api(tmp_path):
+    import threading
+    import urllib.request
+    from http.server import ThreadingHTTPServer
+
+    from bux_b200.studio import Studio
+    from bux_b200.studio.server import set_value
+
+    assert set_value("a = 1\nb = f(\n  x)\nc = 2\n", "b", "g()") == "a = 1\nb = g()\nc = 2\n"
+    assert set_value("a = 1\n", "steps", "9").endswith("steps = 9\n")
+    f = tmp_path / "s.bux"
+    f.write_text(SMOKE)
+    studio = Studio(f, out=tmp_path / "runs")
+    server = ThreadingHTTPServer(("127.0.0.1", 0), studio.handler())
+    port = server.server_address[1]
+    threading.Thread(target=server.serve_forever, daemon=True).start()
+    try:
+        def call(path, body=None, token=studio.token):
+            req = urllib.request.Request(f"http://127.0.0.1:{port}{path}?token={token}",
+                                         data=None if body is None else json.dumps(body).encode())
+            with urllib.request.urlopen(req) as r:
+                return json.loads(r.read())
+
+        view = call("/api/view")
+        assert view["runs"][0]["id"] == "5a4f0f7d85" and view["runs"][0]["params"] == 155968 and "×2" in view["graph"]
+        edited = call("/api/set", {"name": "steps", "value": "20"})
+        assert not edited["diagnostics"] and "steps = 20" in f.read_text().replace("    ", " ").replace("  ", " ")
+        broken = call("/api/source", {"source": SMOKE.replace("num_heads=4", "num_heads=3")})
+        assert broken["diagnostics"] and "num_heads=3" not in f.read_text()   # the file keeps its last good text
+        try:
+            call("/api/view", token="nope")
+            raise AssertionError("a bad token must be refused")
+        except urllib.error.HTTPError as e:
+            assert e.code == 403
+    finally:
+        server.shutdown()
