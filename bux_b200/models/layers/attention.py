@@ -93,8 +93,8 @@ class GQA(nn.Module):
 
     def forward(self, x, ctx: Context):
         c = self.c
-        bsz, t, _ = x.shape
         qkv = self.qkv(x, ctx)
+        bsz, t = qkv.shape[:2]  # with the sequence gathered inside the projection, longer than x
         q, k, v = qkv.split((self.q_rows, self.k_rows, self.v_rows), dim=-1)  # backward: one cat
         q = q.reshape(bsz, t, self.h, self.d)
         k = k.reshape(bsz, t, self.g, self.d)
