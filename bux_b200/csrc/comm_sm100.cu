@@ -163,11 +163,12 @@ __global__ void zero_pad_rows_kernel(__nv_bfloat16* __restrict__ buf, const int*
       reinterpret_cast<uint4*>(buf + (long)r * d)[c] = make_uint4(0, 0, 0, 0);
 }
 
-// Tensor / sequence parallelism: this rank's block of rows goes into every peer's gather
-// buffer at row `my_rank * rows` (its own included), 16 bytes per store.
+// Tensor / sequence parallelism: this rank's block of rows goes into every other rank's
+// gather buffer at row `my_rank * rows`, 16 bytes per store (its own copy is a local
+// copy made by the caller, which lets the GEMM start on it at once).
 __global__ void tp_push_block_kernel(const uint4* __restrict__ src, const uint64_t* __restrict__ peer_base,
                                      int world, int my_rank, long vecs_per_block) {
-  const long total = vecs_per_block * world;
+  const long total = vecs_per_block * (world - 1);
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
     // peers in rotated order so the ranks do not all write to the same GPU at once
     const int step = (int)(i / vecs_per_block);
@@ -248,8 +249,9 @@ void zero_pad_rows(void* buf, const int* offsets, const int* counts, int groups,
 void tp_push_block(const void* src, const uint64_t* peer_base, int world, int my_rank, long rows, int d, int sms,
                    cudaStream_t s) {
   const long vecs = rows * d / 8;
-  const long work = vecs * world;
-  const int cap = (sms > 0 ? sms : 32) * 4;   // a few SMs: the GEMM runs beside it
+  const long work = vecs * (world - 1);
+  if (work <= 0) return;
+  const int cap = (sms > 0 ? sms : 148) * 4;  // small CTAs without shared memory: they fit beside the GEMM's
   int grid = (int)((work + 255) / 256 > cap ? cap : (work + 255) / 256);
   tp_push_block_kernel<<<grid < 1 ? 1 : grid, 256, 0, s>>>((const uint4*)src, peer_base, world, my_rank, vecs);
 }

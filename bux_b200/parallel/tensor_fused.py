@@ -77,14 +77,35 @@ def fabric(role: str, group, device, rows_local: int, width: int) -> Fabric:
     return _FABRICS[key]
 
 
+_SIDE: dict = {}
+
+
+def _side(device) -> torch.cuda.Stream:
+    key = torch.device(device).index
+    if key not in _SIDE:
+        _SIDE[key] = torch.cuda.Stream(device=device)
+    return _SIDE[key]
+
+
 def _gather(group, x_l: torch.Tensor):
-    """Starts the exchange of this rank's rows; returns (fabric, epoch the GEMM waits for)."""
+    """Starts the exchange of this rank's rows on a side stream, so the GEMM that follows on
+    the main stream runs beside it (its tiles wait for their senders' flags); returns
+    (fabric, epoch the GEMM waits for). This rank's own block is copied and flagged
+    first: the GEMM starts on it."""
     from ..ops import kernels as K
 
     f = fabric("gather", group, x_l.device, x_l.shape[0], x_l.shape[1])
+    main, side = torch.cuda.current_stream(x_l.device), _side(x_l.device)
     f.wait_free()
-    K.tp_push_block(x_l, f.ptrs, f.me)
-    return f, f.signal(CH_READY)
+    side.wait_stream(main)
+    with torch.cuda.stream(side):
+        K.tp_push_block(x_l, f.ptrs, f.me)
+        epoch = f.signal(CH_READY)
+    x_l.record_stream(side)
+    # own rows: a local copy, flagged at once
+    f.buf[f.me * f.rows:(f.me + 1) * f.rows].copy_(x_l)
+    f.flags[CH_READY, f.me].fill_(epoch)
+    return f, epoch
 
 
 def _scatter(group, device, rows_local: int, width: int, gemm_into, residual=None):
