@@ -34,7 +34,8 @@ def reference_arm(args) -> int:
     why = None
     ref = ROOT / "baseline" / "_ref"
     if not ref.exists():
-        why = "baseline/_ref is not installed"
+        why = ("baseline/_ref is not installed: the reference's build backend (uv_build) and its JAX stack "
+               "(jax, flax, optax, orbax-checkpoint) are neither in the image nor in the offline wheelhouse")
     else:
         sys.path.insert(0, str(ref))
         try:

@@ -171,8 +171,9 @@ class Optimizer:
 
     def __init__(self, named_params: Iterable, config, *, moments: str = "float32",
                  master: bool = True, clip: Optional[float] = 1.0, reduce: Optional[Callable] = None,
-                 norm_weight: Optional[Callable] = None):
+                 norm_weight: Optional[Callable] = None, shard_group=None, orthogonalize: str = "gather"):
         self.c = config
+        self.shard_group, self.orthogonalize = shard_group, orthogonalize
         self.named = [(n, p) for n, p in named_params if p.requires_grad]
         self.moments, self.clip, self.reduce = moments, clip, reduce
         self.norm_weight = norm_weight
@@ -308,7 +309,11 @@ class Optimizer:
         buf.mul_(c.momentum).add_(gf, alpha=1 - c.momentum)
         upd = gf * (1 - c.momentum) + buf * c.momentum if c.nesterov else buf
         ns_dtype = torch.float32 if (c.ns_dtype == "float32" or not p.is_cuda) else torch.bfloat16
-        o = newton_schulz(upd, c.ns_steps, c.ns_coefficients, ns_dtype).float()
+        whole_rows = getattr(p, "_bux_rows", None)
+        if getattr(p, "_bux_sharded", False) and self.shard_group is not None and whole_rows is not None:
+            o = self._orthogonalize_shards(name, upd, whole_rows, ns_dtype)
+        else:
+            o = newton_schulz(upd, c.ns_steps, c.ns_coefficients, ns_dtype).float()
         if "neuron_v" in st:  # NorMuon: per-neuron second moment of the orthogonal update
             v = st["neuron_v"]
             v.mul_(c.b2).add_(o.square().mean(-1, keepdim=True), alpha=1 - c.b2)
@@ -316,6 +321,8 @@ class Optimizer:
             o = o / (v.sqrt() + c.eps)
             o = o * (scale_before / (o.norm() + 1e-12))
         rows, cols = p.shape[-2], p.shape[-1]
+        if whole_rows is not None and p.dim() == 2:
+            rows = whole_rows  # the scale follows the whole matrix, not this rank's rows
         if c.consistent_rms is not None:
             o = o * (c.consistent_rms * math.sqrt(max(rows, cols)))
         else:
@@ -331,6 +338,36 @@ class Optimizer:
         target.add_(o.to(target.dtype), alpha=-lr)
         if "master" in st:
             p.data.copy_(target)
+
+    def _orthogonalize_shards(self, name: str, upd: torch.Tensor, whole_rows: int, ns_dtype) -> torch.Tensor:
+        """Newton–Schulz needs whole matrices; parameters sharded by rows over the fsdp
+        group are put together first (reference: ``train/optim.py:829-1088`` there).
+        ``gather`` (and ``gspmd``): every rank all-gathers the update, orthogonalises the
+        whole matrix and keeps its rows. ``owner``: one rank per matrix (round robin by
+        name) receives the rows, orthogonalises and sends each rank's rows back, so the
+        Newton–Schulz FLOPs are spread over the ranks instead of repeated on all."""
+        import torch.distributed as dist
+
+        c, g = self.c, self.shard_group
+        world, me = dist.get_world_size(g), dist.get_rank(g)
+        upd = upd.contiguous()
+        if self.orthogonalize != "owner":
+            parts = [torch.empty_like(upd) for _ in range(world)]
+            dist.all_gather(parts, upd, group=g)
+            whole = newton_schulz(torch.cat(parts, dim=-2), c.ns_steps, c.ns_coefficients, ns_dtype).float()
+            per = whole_rows // world
+            return whole.narrow(-2, me * per, per).contiguous()
+        owner = sum(name.encode()) % world
+        src = dist.get_global_rank(g, owner)
+        parts = [torch.empty_like(upd) for _ in range(world)] if me == owner else None
+        dist.gather(upd, parts, dst=src, group=g)
+        out = torch.empty_like(upd, dtype=torch.float32)
+        pieces = None
+        if me == owner:
+            whole = newton_schulz(torch.cat(parts, dim=-2), c.ns_steps, c.ns_coefficients, ns_dtype).float()
+            pieces = [x.contiguous() for x in whole.chunk(world, dim=-2)]
+        dist.scatter(out, pieces, src=src, group=g)
+        return out
 
     # ---- checkpointing
     def state_dict(self) -> dict:

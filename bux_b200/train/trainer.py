@@ -92,7 +92,9 @@ class Trainer:
             self.model.named_parameters(), t.optimizer, moments=moments or t.precision.moments,
             master=use_master, clip=t.clip,
             reduce=parallel.sum_scalar if parallel is not None else None,
-            norm_weight=parallel.norm_weight if parallel is not None else None)
+            norm_weight=parallel.norm_weight if parallel is not None else None,
+            shard_group=parallel.fsdp.group if parallel is not None and parallel.fsdp is not None else None,
+            orthogonalize=t.methods.orthogonalize)
         self.lr_at = optim.lr_multiplier(t)
         self.step = 0
         self.tokens = 0

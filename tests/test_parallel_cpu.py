@@ -209,3 +209,12 @@ def test_context_parallel_matches_one_rank(tmp_path, method, heads):
     assert got["losses"] == pytest.approx(want_losses, abs=1e-5)
     for name, p in want.items():
         assert torch.allclose(got["state"][name], p, atol=1e-5), name
+
+
+@pytest.mark.parametrize("how", ["gather", "owner"])
+def test_muon_on_fsdp_shards_matches_one_rank(tmp_path, how):
+    src = DENSE.replace("optimizer = adamw(lr=1e-2, eps=1.0)", "optimizer = muon(lr=1e-2, ns_dtype=float32)")
+    want_losses, want = _single(src)
+    got = _spawn(2, src, ["mesh = mesh(fsdp=2)", f"methods.orthogonalize = {how}"], tmp_path)
+    assert got["losses"] == pytest.approx(want_losses, abs=1e-5)
+    _check_rows(got, want)
