@@ -385,7 +385,19 @@ def train(run: ir.Run, out="runs", cache=".", hooks=None, sinks=None, device=Non
         S.echo(f"{run.name}: {curriculum.si(n)} parameters, {curriculum.summary(t)}, "
                f"{value_to_source(t.optimizer)}, {value_to_source(t.schedule)}")
         S.echo(f"{run.name}: log every {t.log.every}")
+    if main and not quiet and t.log.trackers:
+        from . import trackers
+
+        sinks = [*sinks, *trackers.build(t.log.trackers, folder, run)]
     all_hooks = [H.Log(t.log, run, trainer)]
+    if t.ema is not None:
+        from .ema import Ship
+
+        all_hooks.insert(0, Ship(t.ema, t.steps))   # before the eval and the checkpoint read the weights
+    if t.observe is not None:
+        from .observe import Observe
+
+        all_hooks.append(Observe(t.observe, folder))
     for e in T.evals(t):
         all_hooks.append(H.Eval(e))
     if ckpt is not None:

@@ -129,3 +129,28 @@ def test_muon_steps():
     before = [p.clone() for p in tr.model.parameters()]
     tr.train_step(batch)
     assert any(not torch.equal(a, b) for a, b in zip(before, tr.model.parameters()))
+
+
+def test_ema_ships_a_blend_and_observe_logs_per_layer_stats(tmp_path):
+    import json
+
+    from bux_b200.lang import compile_runs
+    from bux_b200.train import ema
+    from bux_b200.train.trainer import train
+
+    src = SMOKE
+    over = ["steps = 12", "schedule = constant", "ema = ema(window=4, blend=0.5)", "observe = observe(every=4, histograms=true)",
+            "log = log(every=4)"]
+    run = compile_runs(src, filename="smoke.bux", overrides=over)[0]
+    assert ema.first(run.train.ema, 12) == 9
+    tr = train(run, out=tmp_path, device="cpu", quiet=True)
+    st = tr.optimizer.state
+    name = next(n for n, _ in tr.model.named_parameters())
+    assert "ema" in st[name]
+    folder = next(tmp_path.iterdir())
+    lines = [json.loads(x) for x in (folder / "metrics.jsonl").read_text().splitlines()]
+    keys = set().union(*(set(x) for x in lines))
+    assert any(k.startswith("param/") for k in keys) and any(k.startswith("update/") for k in keys)
+    assert any(k.startswith("act/graph") for k in keys)
+    hist = [json.loads(x) for x in (folder / "histograms.jsonl").read_text().splitlines()]
+    assert hist and hist[0]["step"] == 4 and sum(hist[0]["histograms"][name]) == tr.model.get_parameter(name).numel()
