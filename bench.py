@@ -150,7 +150,9 @@ def main() -> int:
     tight = n <= 2
     trainer = Trainer(run, device=device, parallel=parallel, fuse_optimizer=True,
                       moments="fp8" if tight else "bfloat16", master=False)
-    trainer.model.set_remat(True, offload=tight)
+    # with the experts spread over four or more GPUs there is room to keep every layer's
+    # attention output, so the backward's rerun of a block skips the attention forward
+    trainer.model.set_remat(True, offload=tight, keep_attention=n >= 4)
     feed = iter(trainer.batches())
     tokens_per_step = args.rows * n * args.seq_len
 
@@ -219,7 +221,7 @@ def main() -> int:
                        "parallelism": f"ep{n}" if n > 1 else "1 gpu (all experts local)",
                        "optimizer": "adamw, bf16 master, " + ("8-bit block-scaled moments" if tight else "bf16 moments")
                                     + ", expert updates fused into the backward, clip by the previous step's norm",
-                       "remat": "per block", "l2": "inputs and weights exceed L2 (126 MB) every step",
+                       "remat": "per block" + (", attention outputs kept" if n >= 4 else ""), "l2": "inputs and weights exceed L2 (126 MB) every step",
                        "loss_last_step": loss},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d,

@@ -116,12 +116,13 @@ class Repeated(nn.Module):
         self.items = nn.ModuleList(items)
         self.remat = False
         self.offload = False  # keep each pass's input in pinned host memory
+        self.keep_attention = False  # keep attention outputs too, so the replay skips that kernel
 
     def forward(self, x, ctx: Context):
         for i, item in enumerate(self.items):
             if (self.remat and ctx.training and torch.is_grad_enabled() and isinstance(x, torch.Tensor)
                     and x.requires_grad):
-                x = _checkpointed(item, x, ctx, self.offload, (id(self), i))
+                x = _checkpointed(item, x, ctx, self.offload, (id(self), i), self.keep_attention)
             else:
                 x = item(x, ctx)
         return x
@@ -220,8 +221,9 @@ class _BlockRun:
 
     _pinned: dict = {}
 
-    def __init__(self, block, ctx: Context, offload: bool, key):
+    def __init__(self, block, ctx: Context, offload: bool, key, keep_attention: bool = False):
         self.block, self.ctx, self.offload, self.key = block, ctx, offload, key
+        self.kept = [] if keep_attention else None
         self.names: list = []
         self.taps = {k: list(v) for k, v in ctx.taps.items()}
         self.ports = dict(ctx.ports)
@@ -241,10 +243,19 @@ class _BlockRun:
         if replay:
             ctx.taps = {k: list(v) for k, v in self.taps.items()}
             ctx.metrics, ctx.ports = {}, dict(self.ports)
+            ctx.tail_values_unused = _ends_in_plain_moe_branch(self.block)
+        from ..ops import functional as OF
+
+        if self.kept is not None:
+            OF.attention_replay = ("load", iter(self.kept)) if replay else ("save", self.kept)
         try:
             y = self.block(x, ctx)
             reported = ctx.losses
         finally:
+            OF.attention_replay = None
+            ctx.tail_values_unused = False
+            if replay:
+                self.kept = None
             if replay:
                 ctx.taps, ctx.losses, ctx.metrics, ctx.ports, ctx.branch_index = saved
             else:
@@ -254,8 +265,21 @@ class _BlockRun:
         return y, [reported[n] for n in self.names]
 
 
-def _checkpointed(block, x, ctx: Context, offload: bool = False, key=None):
-    holder = _BlockRun(block, ctx, offload, key)
+def _ends_in_plain_moe_branch(block) -> bool:
+    """Whether the block's last op is ``x + moe(...)``: in a replay nothing reads that sum's
+    values (the add's backward needs none), so the experts' combine can skip moving them."""
+    from .layers.moe import MoE
+
+    last = block.items[-1] if isinstance(block, Sequence) and len(block.items) else block
+    if not isinstance(last, ResidualBranch) or getattr(last, "algebra", None) is not None:
+        return False
+    body = last.body
+    tail = body.items[-1] if isinstance(body, Sequence) and len(body.items) else body
+    return isinstance(tail, MoE)
+
+
+def _checkpointed(block, x, ctx: Context, offload: bool = False, key=None, keep_attention: bool = False):
+    holder = _BlockRun(block, ctx, offload, key, keep_attention)
     y, *aux = _Remat.apply(x, holder)
     for name, value in zip(holder.names, aux):
         prev = ctx.losses.get(name)

@@ -49,13 +49,16 @@ class Model(nn.Module):
         ctx = self(input_ids, **kw)
         return ctx.heads[0].logits()
 
-    def set_remat(self, on: bool, offload: bool = False) -> None:
+    def set_remat(self, on: bool, offload: bool = False, keep_attention: bool = False) -> None:
         """Checkpoint every pass of every repeated block (keep only its input, rerun it
-        in the backward); `offload` keeps those inputs in pinned host memory."""
+        in the backward); `offload` keeps those inputs in pinned host memory;
+        `keep_attention` also keeps each attention's output and log-sum-exp, so the rerun
+        skips the attention forward kernel (the remat preset that keeps ``attention.out``)."""
         for m in self.modules():
             if isinstance(m, Repeated):
                 m.remat = on
                 m.offload = offload
+                m.keep_attention = keep_attention and on
 
     def step_end_update(self) -> None:
         for m in self.modules():

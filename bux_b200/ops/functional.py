@@ -298,13 +298,25 @@ def ref_linear_mxfp8(x, w, bias=None):
 
 
 # ------------------------------------------------------------------ attention
+# Activation checkpointing may keep attention outputs across the replay of a block: the
+# first run appends (o, lse) here, the replay takes them back in the same order instead of
+# running the forward kernel again. ("save", list) / ("load", iterator) / None.
+attention_replay = None
+
+
 class _Attention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, sinks, causal, window, scale):
         K = _K()
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         sk = None if sinks is None else sinks.float().contiguous()
-        o, lse = K.attn_fwd(q, k, v, causal=causal, window=window, sinks=sk, scale=scale)
+        mode = attention_replay
+        if mode is not None and mode[0] == "load":
+            o, lse = next(mode[1])
+        else:
+            o, lse = K.attn_fwd(q, k, v, causal=causal, window=window, sinks=sk, scale=scale)
+            if mode is not None:
+                mode[1].append((o, lse))
         ctx.save_for_backward(q, k, v, o, lse, sk)
         ctx.cfg = (causal, window, scale)
         return o

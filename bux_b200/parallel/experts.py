@@ -187,12 +187,18 @@ class _Combine(torch.autograd.Function):
     dw by a pulled dot product, and w·dout pushed into the owners' dy buffers."""
 
     @staticmethod
-    def forward(ctx, y, weights, ep: FusedEP, r: Route, tokens: int):
+    def forward(ctx, y, weights, ep: FusedEP, r: Route, tokens: int, values_unused: bool = False):
         from ..ops import kernels as K
 
         w = weights.float().contiguous()
-        out = K.ep_pull_combine(ep.tables["y"], r.rank_of, r.row_of, w, tokens, ep.d, y.dtype,
-                                flags=ep.flags[CH_Y], epoch=ep.epoch[CH_Y])
+        ctx.y_epoch = ep.epoch[CH_Y]
+        if values_unused:
+            # the replay of a checkpointed block whose last op this is: only the graph is
+            # needed, so the rows stay where they are (nothing crosses NVLink)
+            out = torch.empty(tokens, ep.d, dtype=y.dtype, device=y.device)
+        else:
+            out = K.ep_pull_combine(ep.tables["y"], r.rank_of, r.row_of, w, tokens, ep.d, y.dtype,
+                                    flags=ep.flags[CH_Y], epoch=ctx.y_epoch)
         ctx.save_for_backward(w)
         ctx.ep, ctx.r, ctx.rows, ctx.wdtype = ep, r, y.shape[0], weights.dtype
         return out
@@ -204,11 +210,12 @@ class _Combine(torch.autograd.Function):
         (w,) = ctx.saved_tensors
         ep, r = ctx.ep, ctx.r
         dout = dout.contiguous()
+        K.ep_wait(ep.flags[CH_Y], ctx.y_epoch)   # the owners' rows of this forward are complete
         dw = K.ep_pull_dot(ep.tables["y"], r.rank_of, r.row_of, dout)
         scale = w.reshape(-1)[r.order].contiguous()
         K.ep_push_rows(dout, r.src_token, r.dst_rank, r.dst_row, ep.tables["dy"], row_scale=scale)
         ep.signal(CH_DY)
-        return ep.bufs["dy"][:ctx.rows], dw.to(ctx.wdtype), None, None, None
+        return ep.bufs["dy"][:ctx.rows], dw.to(ctx.wdtype), None, None, None, None
 
 
 # ====================================================================== library all-to-all
@@ -323,7 +330,7 @@ class ExpertParallel:
             io = _IO(ep, ep.epoch[CH_X])
             y = fused.experts_on_sorted(xs, r.offsets, r.counts, moe.experts_gate_up, moe.experts_down,
                                         io=io, **kw)
-            return _Combine.apply(y, weights, ep, r, t)
+            return _Combine.apply(y, weights, ep, r, t, bool(getattr(ctx, "tail_values_unused", False)))
         rows = x[r.src_token.long()]
         xs = _A2A.apply(rows, r.dst_rank, r.dst_row, self.group, cap)
         y = fused.experts_on_sorted(xs, r.offsets, r.counts, moe.experts_gate_up, moe.experts_down, **kw)

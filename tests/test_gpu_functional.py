@@ -117,3 +117,37 @@ def test_linear_f32_matches_fp32_matmul():
         gb = g.bfloat16().float()
         assert torch.allclose(dx.float(), (gb @ w.float()), atol=2e-2, rtol=2e-2)
         assert torch.allclose(dw.float(), gb.t() @ x.float(), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.gpu
+def test_remat_that_keeps_attention_outputs_matches_plain_remat():
+    from bux_b200.lang import compile_runs
+    from bux_b200.ops import kernels as K
+    from bux_b200.train.trainer import Trainer
+
+    src = """
+d_model=256
+vocab_size=512
+n = rmsnorm
+block = [n gqa(num_heads=4, num_kv_heads=2, head_dim=64, rope=rope())] [n gated_mlp(intermediate_size=512, activation=swish)]
+model = embed block^2 n head
+data = synthetic
+optimizer = adamw(lr=1e-3)
+seq_len = 256
+batch = 4
+steps = 4
+precision = precision(compute=bfloat16)
+"""
+    run = compile_runs(src, filename="k.bux")[0]
+    out = []
+    for keep in (False, True):
+        tr = Trainer(run, device="cuda")
+        tr.model.set_remat(True, keep_attention=keep)
+        feed = iter(tr.batches())
+        before = K.launches
+        losses = [tr.train_step(next(feed))["loss"].item() for _ in range(2)]
+        out.append((losses, K.launches - before, {n: p.detach().float().clone() for n, p in tr.model.named_parameters()}))
+    (l0, n0, s0), (l1, n1, s1) = out
+    assert l0 == l1                      # the same kernels on the same inputs: bit-identical
+    assert n1 == n0 - 2 * 2              # one attention forward less per block and step
+    assert all(torch.equal(s0[k], s1[k]) for k in s0)
