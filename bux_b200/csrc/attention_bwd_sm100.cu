@@ -221,6 +221,7 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
       const bool full_row = row_ok && kv0 + BT - 1 <= hi_key && kv0 >= lo_key && kv0 + BT <= p.S && lse2 > -INFINITY;
       const bool any_row = row_ok && lse2 > -INFINITY;
       const int c_first = half * 64;
+      const float nlse2 = -lse2, ndlt = -dlt * p.scale;
 #pragma unroll 1
       for (int ci = 0; ci < 2; ++ci) {
         const int c = c_first + ci * 32;
@@ -232,11 +233,12 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
         if (full_row) {
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            const float p0 = exp2f(__uint_as_float(cs[i]) * p.scale_log2 - lse2);
-            const float p1 = exp2f(__uint_as_float(cs[i + 1]) * p.scale_log2 - lse2);
+            // P = 2^(s·scale·log2e − lse·log2e); dS = P·(dP·scale − delta·scale)
+            const float p0 = ex2_approx(fmaf(__uint_as_float(cs[i]), p.scale_log2, nlse2));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(cs[i + 1]), p.scale_log2, nlse2));
             pp[i >> 1] = pack_bf16(p0, p1);
-            ds[i >> 1] = pack_bf16(p0 * (__uint_as_float(cd[i]) - dlt) * p.scale,
-                                   p1 * (__uint_as_float(cd[i + 1]) - dlt) * p.scale);
+            ds[i >> 1] = pack_bf16(p0 * fmaf(__uint_as_float(cd[i]), p.scale, ndlt),
+                                   p1 * fmaf(__uint_as_float(cd[i + 1]), p.scale, ndlt));
           }
         } else {
 #pragma unroll
@@ -246,8 +248,8 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
             for (int e = 0; e < 2; ++e) {
               const int kv = kv0 + c + i + e;
               const bool keep = any_row && kv < p.S && kv <= hi_key && kv >= lo_key;
-              pr[e] = keep ? exp2f(__uint_as_float(cs[i + e]) * p.scale_log2 - lse2) : 0.f;
-              dr[e] = pr[e] * (__uint_as_float(cd[i + e]) - dlt) * p.scale;
+              pr[e] = keep ? ex2_approx(fmaf(__uint_as_float(cs[i + e]), p.scale_log2, nlse2)) : 0.f;
+              dr[e] = pr[e] * fmaf(__uint_as_float(cd[i + e]), p.scale, ndlt);
             }
             pp[i >> 1] = pack_bf16(pr[0], pr[1]);
             ds[i >> 1] = pack_bf16(dr[0], dr[1]);

@@ -228,8 +228,9 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
       // rows whose whole tile is visible skip the per-element mask
       const bool full_row = kv0 + KT - 1 <= hi_key && kv0 >= lo_key && kv0 + KT <= p.S;
       for (int attempt = 0; attempt < 2; ++attempt) {
-        float sum = 0.f, mx = -INFINITY;
+        float sum = 0.f, sum1 = 0.f, mx = -INFINITY, mx_raw = -INFINITY;
         const float ref = m_ref == -INFINITY ? 0.f : m_ref;
+        const float nref = -ref, sc = p.scale_log2;
         uint32_t v[2][32];
         tmem_ld_x32(t_s, v[0]);
 #pragma unroll
@@ -243,10 +244,12 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
           if (full_row) {
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-              const float s0 = __uint_as_float(cur[i]) * p.scale_log2, s1 = __uint_as_float(cur[i + 1]) * p.scale_log2;
-              mx = fmaxf(mx, fmaxf(s0, s1));
-              const float p0 = exp2f(s0 - ref), p1 = exp2f(s1 - ref);
-              sum += p0 + p1;
+              // per element: one max on the raw score, one fused multiply-add, one ex2, one add
+              const float x0 = __uint_as_float(cur[i]), x1 = __uint_as_float(cur[i + 1]);
+              mx_raw = fmaxf(mx_raw, fmaxf(x0, x1));
+              const float p0 = ex2_approx(fmaf(x0, sc, nref)), p1 = ex2_approx(fmaf(x1, sc, nref));
+              sum += p0;
+              sum1 += p1;
               packed[i >> 1] = pack_bf16(p0, p1);
             }
           } else {
@@ -257,9 +260,9 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
               for (int e = 0; e < 2; ++e) {
                 const int kv = kv0 + c + i + e;
                 const bool keep = kv < p.S && kv <= hi_key && kv >= lo_key;
-                const float sv = __uint_as_float(cur[i + e]) * p.scale_log2;
-                if (keep) mx = fmaxf(mx, sv);
-                pr[e] = keep ? exp2f(sv - ref) : 0.f;
+                const float xv = __uint_as_float(cur[i + e]);
+                if (keep) mx_raw = fmaxf(mx_raw, xv);
+                pr[e] = keep ? ex2_approx(fmaf(xv, sc, nref)) : 0.f;
               }
               sum += pr[0] + pr[1];
               packed[i >> 1] = pack_bf16(pr[0], pr[1]);
@@ -273,6 +276,8 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
                 make_uint4(packed[4 * sl], packed[4 * sl + 1], packed[4 * sl + 2], packed[4 * sl + 3]);
           }
         }
+        sum += sum1;
+        mx = mx_raw * sc;  // the scale is positive: the max of the scaled scores
         // The reference only moves when a row max outgrows it by a wide margin: P and the
         // running sums stay exact relative to the reference, so this is rare.
         const bool redo = mx > m_ref + RESCALE_THRESHOLD;

@@ -153,6 +153,12 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* s
                "r"(smem_u32(src)), "r"(x), "r"(y)
                : "memory");
 }
+// 2^x on the special-function unit, one instruction (denormal results flush to zero).
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 // Adds a shared-memory tile of fp32 into global memory through the tensor map (L2 reductions
 // at line granularity: far cheaper than per-thread atomics for whole tiles).
 __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* m, const void* src, int x, int y) {
