@@ -25,7 +25,7 @@ from . import rope as rope_lib
 from .basic import Linear, Norm
 
 _UNSUPPORTED = ("kv_conv_size", "differential", "paired", "k_eq_v", "power_scale", "log_scale",
-                "relative_bias", "indexer", "gate_input_rank", "gate_output_rank", "gate_cross_head")
+                "relative_bias", "gate_input_rank", "gate_output_rank", "gate_cross_head")
 
 
 class GQA(nn.Module):
@@ -58,6 +58,11 @@ class GQA(nn.Module):
         if c.output_norm is not None:
             self.out_norm = Norm(c.output_norm, self.dv)
         self.ports = ()
+        if c.indexer is not None and not any(p.name == "index" and p.mode != "write" for p in (b.ports or ())):
+            from .sparse import Indexer
+
+            rot = rope_lib.rotated_dims(self.d, c.rope.fraction) if c.rope is not None else 0
+            self.indexer = Indexer(c.indexer, width, c.rope, rot, b)
         if c.rope is not None:
             inv, gain = rope_lib.inverse_frequencies(c.rope, self.d)
             self.register_buffer("inv_freq", inv, persistent=False)
@@ -113,6 +118,9 @@ class GQA(nn.Module):
         for port in self.ports:
             if port.mode == "write":
                 ctx.push(port.tap, v if port.name == "v" else (k, v))
+        if c.indexer is not None:
+            out = self._sparse(x, q, k, v, ctx)
+            return self._finish(out, x, bsz, t, ctx)
         kw = dict(causal=True, window=c.sliding_window_size, sinks=getattr(self, "sinks", None),
                   softcap=c.softcap, scale=c.scale, segments=ctx.segments)
         cp = getattr(ctx.parallel, "context_group", None) if ctx.parallel is not None else None
@@ -122,6 +130,33 @@ class GQA(nn.Module):
             out = context.attend(ops.attention, q, k, v, cp, ctx.methods.attention, **kw)
         else:
             out = ops.attention(q, k, v, **kw)
+        return self._finish(out, x, bsz, t, ctx)
+
+    def _sparse(self, x, q, k, v, ctx: Context):
+        """Attention over the keys an indexer kept (its own, or another layer's through
+        the ``index`` port), and the indexer's distillation loss."""
+        from . import sparse as S
+
+        c = self.c
+        t = q.shape[1]
+        seen = S.seen_mask(ctx, t, c.sliding_window_size)
+        reads = [p for p in self.ports if p.name == "index" and p.mode != "write"]
+        scores = None
+        if reads:
+            kept = ctx.read(reads[0].tap, reads[0].mode == "pop") & seen
+        else:
+            scores = self.indexer.scores(x, ctx)
+            kept = S.top_mask(scores, seen, c.indexer.top_k)
+        for p in self.ports:
+            if p.name == "index" and p.mode == "write":
+                ctx.push(p.tap, kept)
+        out, target = S.attend_kept(q, k, v, kept, c.scale, getattr(self, "sinks", None), c.softcap)
+        if scores is not None and ctx.training and c.indexer.loss_weight:
+            ctx.report("indexer_loss", S.indexer_loss(scores, kept, target), c.indexer.loss_weight)
+        return out
+
+    def _finish(self, out, x, bsz, t, ctx: Context):
+        c = self.c
         if c.output_norm is not None:
             out = self.out_norm(out, ctx)
         out = out.reshape(bsz, t, self.h * self.dv)

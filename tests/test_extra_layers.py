@@ -80,3 +80,32 @@ def test_copy_candidates_by_hand():
 
 def test_doc_copy_trains():
     _train(model="embed doc_copy(lengths=[1, 2, 3]) block^2 n head")
+
+
+def test_sparse_attention_with_an_indexer():
+    from bux_b200.models.layers import sparse as S
+
+    # top_mask keeps the k best of the seen keys, the first of equal ones
+    sc = torch.tensor([[[3.0, 1.0, 3.0, 2.0]]])
+    seen = torch.tensor([[[True, True, True, False]]])
+    assert S.top_mask(sc, seen, 2).tolist() == [[[True, False, True, False]]]
+    # with every key kept the sparse path is plain causal attention, and the loss is finite
+    attn = "gqa(num_heads=2, num_kv_heads=1, rope=rope(), indexer=indexer(num_heads=2, head_dim=8, top_k=8))"
+    tr = _train(attn)
+    assert any("indexer" in n for n, _ in tr.model.named_parameters())
+    ids = torch.randint(0, 64, (2, 32))
+    ctx = tr.model(ids, torch.arange(32).expand(2, 32), None, training=True)
+    assert "indexer_loss" in ctx.losses and torch.isfinite(ctx.losses["indexer_loss"])
+    # the loss trains the indexer only
+    loss = ctx.losses["indexer_loss"]
+    grads = torch.autograd.grad(loss, [p for p in tr.model.parameters()], allow_unused=True)
+    touched = {n for (n, _), g in zip(tr.model.named_parameters(), grads) if g is not None and g.abs().sum() > 0}
+    assert touched and all("indexer" in n for n in touched)
+
+
+def test_index_port_shares_the_picks():
+    first = "gqa(num_heads=2, num_kv_heads=1, rope=rope(), indexer=indexer(num_heads=2, head_dim=8, top_k=4), index=@picks)"
+    model = "embed [n a] [n m] [n gqa(num_heads=2, num_kv_heads=1, rope=rope(), indexer=indexer(num_heads=2, head_dim=8, top_k=4), index=$picks!)] n head"
+    tr = _train(first, model=model)
+    names = [n for n, _ in tr.model.named_parameters() if "indexer" in n]
+    assert names and all(".items.1." in n for n in names)   # only the first layer owns an indexer
