@@ -154,3 +154,37 @@ def test_ema_ships_a_blend_and_observe_logs_per_layer_stats(tmp_path):
     assert any(k.startswith("act/graph") for k in keys)
     hist = [json.loads(x) for x in (folder / "histograms.jsonl").read_text().splitlines()]
     assert hist and hist[0]["step"] == 4 and sum(hist[0]["histograms"][name]) == tr.model.get_parameter(name).numel()
+
+
+def test_remat_auto_takes_the_cheapest_preset_that_fits():
+    from bux_b200.train import fitting
+
+    run = compile_runs(SMOKE, filename="smoke.bux")[0]
+    tr = Trainer(run, device="cpu")
+    peaks = {(False, False, False): 100, (True, True, False): 70, (True, False, False): 50, (True, False, True): 30}
+
+    def probe(trainer, batch):
+        rep = next(m for m in trainer.model.modules() if hasattr(m, "keep_attention"))
+        p = peaks[(rep.remat, rep.keep_attention, rep.offload)]
+        if p == 100:
+            raise torch.OutOfMemoryError("no room")
+        return p
+
+    got = fitting.fit(tr, None, capacity=60, probe=probe)
+    assert got.name == "block" and got.peak_bytes == 50
+    assert [n for n, _ in got.tried] == ["none", "block, attention kept", "block"]
+    with pytest.raises(MemoryError):
+        fitting.fit(tr, None, capacity=10, probe=probe)
+
+
+def test_profiler_commands():
+    from bux_b200.train import profilers
+
+    assert profilers.TOOLS["ncu"][1:3] == ["--clock-control", "none"]
+    with pytest.raises(ValueError):
+        profilers.command("torch", "out")
+    with pytest.raises(ValueError):
+        profilers.command("vtune", "out")
+    if profilers.available("ncu"):
+        cmd = profilers.command("ncu", "runs/x", argv=["-m", "bux_b200", "train", "f.bux"])
+        assert cmd[0] == "ncu" and "runs/x/profile" in cmd and cmd[-4:] == ["-m", "bux_b200", "train", "f.bux"]
