@@ -39,13 +39,17 @@ struct GemmCfg {
   static constexpr int B_BYTES = BN * 128;
   static constexpr int SF_BYTES = KIND == KIND_MXFP8 ? 512 * (1 + BN / 128) : 0;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SF_BYTES;
-  static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 8 ? 8 : (200 * 1024) / STAGE_BYTES;
+  // epilogue staging: per warp 32 rows x 64 bf16 columns (4 KB), one or two slabs per warp
+  static constexpr int EPI_SLABS = (KIND == KIND_MXFP8 && BN == 256) ? 1 : 2;
+  static constexpr int EPI_BYTES = EPI_SLABS * 4 * 4096;
+  static constexpr int BUDGET = 227 * 1024 - 1024 - 256 - 1024 - EPI_BYTES;
+  static constexpr int STAGES = BUDGET / STAGE_BYTES > 8 ? 8 : BUDGET / STAGE_BYTES;
   static constexpr int ACC_STAGES = (2 * BN + (KIND == KIND_MXFP8 ? STAGES * 4 * (1 + BN / 128) : 0)) <= 512 ? 2 : 1;
   static constexpr int ACC_COLS = ACC_STAGES * BN;
   static constexpr int SF_COLS_PER_STAGE = KIND == KIND_MXFP8 ? 4 * (1 + BN / 128) : 0;
   static constexpr int TMEM_COLS = 512;
   static constexpr int UMMA_K = KIND == KIND_BF16 ? 16 : 32;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 struct TileCoord {
@@ -119,7 +123,9 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the 128B-swizzle atom is 8 rows x 128 bytes.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  static_assert((STAGES * Cfg::STAGE_BYTES) % 1024 == 0, "the epilogue slabs swizzle by address bits 7-9");
+  uint8_t* epi_smem = smem + STAGES * Cfg::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + Cfg::EPI_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + STAGES;
   uint64_t* acc_full = bars + 2 * STAGES;
@@ -282,6 +288,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
     TileWalk walk(p, BN);
     int acc = 0; uint32_t acc_phase = 0;
+    int epi_round = 0;
     bool ok = true;
     for (TileCoord c = walk.next(); c.valid && ok; c = walk.next()) {
       if (!warp_all(mbar_wait(&acc_full[acc], acc_phase, abort_flag, st, KID_GEMM, 4))) { ok = false; break; }
@@ -292,6 +299,56 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
       size_t out_row = (size_t)row;
       if (p.mode == MODE_GROUPED_K) out_row += (size_t)c.group * p.M;
       const uint32_t t_addr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
+      // full bf16 tiles leave through shared memory and TMA stores: whole 128-byte lines,
+      // asynchronous, and the accumulator is released as soon as it has been read
+      const bool by_tma = p.tma_store && (p.mode == MODE_DENSE || c.m_end - c.m0 >= BM);
+      if (by_tma) {
+        uint8_t* mine = epi_smem + quad * 4096;
+        constexpr int ROUNDS = BN / 64;
+#pragma unroll 1
+        for (int round = 0; round < ROUNDS; ++round) {
+          const int n = c.n0 + round * 64;
+          if (n >= p.N) break;
+          uint8_t* slab = mine + (Cfg::EPI_SLABS == 2 ? (epi_round & 1) * 16384 : 0);
+          // the store that last read this slab must have finished reading it
+          if (lane == 0) {
+            if (Cfg::EPI_SLABS == 2) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            else tma_store_wait_read();
+          }
+          __syncwarp();
+          uint32_t r0[32], r1[32];
+          tmem_ld_x32(t_addr + round * 64, r0);
+          tmem_ld_x32(t_addr + round * 64 + 32, r1);
+          tmem_ld_wait();
+          uint8_t* rowp = slab + lane * 128;
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            const uint32_t* src = v < 4 ? &r0[8 * v] : &r1[8 * (v - 4)];
+            uint4 q;
+            if (empty_k) {
+              q = make_uint4(0, 0, 0, 0);
+            } else {
+              q.x = pack_bf16(__uint_as_float(src[0]), __uint_as_float(src[1]));
+              q.y = pack_bf16(__uint_as_float(src[2]), __uint_as_float(src[3]));
+              q.z = pack_bf16(__uint_as_float(src[4]), __uint_as_float(src[5]));
+              q.w = pack_bf16(__uint_as_float(src[6]), __uint_as_float(src[7]));
+            }
+            *reinterpret_cast<uint4*>(rowp + ((v ^ (lane & 7)) << 4)) = q;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&p.tmap_c, slab, n, c.m0 + quad * 32);
+            tma_store_commit();
+          }
+          ++epi_round;
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+        continue;
+      }
 #pragma unroll 1
       for (int col = 0; col < BN; col += 32) {
         uint32_t r[32];
@@ -348,6 +405,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
   }
 
   // ---------------------------------------------------------------- teardown
+  if (warp >= 2 && lane == 0) tma_store_wait_all();  // this warp's stores have left shared memory and landed
   tc_fence_before();
   __syncthreads();
   if (*abort_flag) {
@@ -445,6 +503,13 @@ const char* gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   if (a.b_mn) err = make_tmap_2d(&p.tmap_b, a.b, elem, a.b_outer, a.b_inner, a.ldb_bytes, 64, bk);
   else        err = make_tmap_2d(&p.tmap_b, a.b, elem, a.b_outer, a.b_inner, a.ldb_bytes, bk, bn);
   if (err) return err;
+  p.tma_store = 0;
+  if (a.out_kind == OUT_BF16 && a.mode != MODE_GROUPED_K && a.ldc % 8 == 0 &&
+      reinterpret_cast<uintptr_t>(a.c) % 16 == 0) {
+    // rows of C: every row the walk can touch (grouped rows: the sorted, padded row count)
+    if (make_tmap_2d(&p.tmap_c, a.c, 2, (uint64_t)a.M, (uint64_t)a.N, (uint64_t)a.ldc * 2, 64, 32) == nullptr)
+      p.tma_store = 1;
+  }
   const int sms = a.sms > 0 ? a.sms : 148;
 #define BUX_GEMM_CASE(KIND_, BN_, AMN_, BMN_) \
   if (a.kind == KIND_ && bn == BN_ && a.a_mn == AMN_ && a.b_mn == BMN_) \

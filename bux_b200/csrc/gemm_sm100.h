@@ -16,6 +16,7 @@ enum { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2 };
 struct GemmParams {
   alignas(64) CUtensorMap tmap_a;
   alignas(64) CUtensorMap tmap_b;
+  alignas(64) CUtensorMap tmap_c;   // bf16 output as [32 rows x 64 columns] boxes (TMA-store epilogue)
   const uint8_t* sfa;        // MXFP8 scale tiles of A (512 bytes per 128 rows x 128 K)
   const uint8_t* sfb;
   void* c;
@@ -27,6 +28,7 @@ struct GemmParams {
   const int* wait_flags; int wait_world, wait_epoch; unsigned long long wait_limit_ns;
   // wait_rows > 0: per-sender row blocks (see GemmArgs); m_rotate in tiles
   int wait_rows, m_rotate, wait_on_k;
+  int tma_store;  // the epilogue stages bf16 tiles in shared memory and stores them by TMA
 };
 
 // What a caller fills in. `a_outer/a_inner` are the stored dims of A (inner contiguous):
