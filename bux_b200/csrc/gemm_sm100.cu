@@ -301,7 +301,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
       const uint32_t t_addr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
       // full bf16 tiles leave through shared memory and TMA stores: whole 128-byte lines,
       // asynchronous, and the accumulator is released as soon as it has been read
-      const bool by_tma = p.tma_store && (p.mode == MODE_DENSE || c.m_end - c.m0 >= BM);
+      const bool by_tma = p.tma_store && (p.mode != MODE_GROUPED_ROWS || c.m_end - c.m0 >= BM);
       if (by_tma) {
         uint8_t* mine = epi_smem + quad * 4096;
         constexpr int ROUNDS = BN / 64;
@@ -338,7 +338,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&p.tmap_c, slab, n, c.m0 + quad * 32);
+            tma_store_2d(&p.tmap_c, slab, n, (p.mode == MODE_GROUPED_K ? c.group * p.M : 0) + c.m0 + quad * 32);
             tma_store_commit();
           }
           ++epi_round;
@@ -504,10 +504,12 @@ const char* gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   else        err = make_tmap_2d(&p.tmap_b, a.b, elem, a.b_outer, a.b_inner, a.ldb_bytes, bk, bn);
   if (err) return err;
   p.tma_store = 0;
-  if (a.out_kind == OUT_BF16 && a.mode != MODE_GROUPED_K && a.ldc % 8 == 0 &&
-      reinterpret_cast<uintptr_t>(a.c) % 16 == 0) {
-    // rows of C: every row the walk can touch (grouped rows: the sorted, padded row count)
-    if (make_tmap_2d(&p.tmap_c, a.c, 2, (uint64_t)a.M, (uint64_t)a.N, (uint64_t)a.ldc * 2, 64, 32) == nullptr)
+  if (a.out_kind == OUT_BF16 && a.ldc % 8 == 0 && reinterpret_cast<uintptr_t>(a.c) % 16 == 0 &&
+      (a.mode != MODE_GROUPED_K || a.M % BM == 0)) {
+    // rows of C: every row the walk can touch (grouped rows: the sorted, padded row count;
+    // grouped contraction: the groups' [M, N] outputs stacked)
+    const uint64_t rows = a.mode == MODE_GROUPED_K ? (uint64_t)a.groups * a.M : (uint64_t)a.M;
+    if (make_tmap_2d(&p.tmap_c, a.c, 2, rows, (uint64_t)a.N, (uint64_t)a.ldc * 2, 64, 32) == nullptr)
       p.tma_store = 1;
   }
   const int sms = a.sms > 0 ? a.sms : 148;

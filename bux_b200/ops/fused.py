@@ -85,6 +85,11 @@ def cross_entropy_head(x, w, targets, mask=None, *, bias=None, z_weight: float =
     return total, count
 
 
+def _grad_dtype(w: torch.Tensor):
+    """bf16 weight gradients leave the GEMM as bf16; anything else as fp32."""
+    return torch.bfloat16 if w.dtype == torch.bfloat16 else torch.float32
+
+
 # ------------------------------------------------------------------ sorted MoE experts
 def sort_picks(experts: torch.Tensor, num_experts: int, align: int = 128):
     """Expert-sorted, `align`-padded layout of the T·k picks, with static shapes.
@@ -164,7 +169,8 @@ class _SortedExperts(torch.autograd.Function):
             _, _, atq, atsf = K.quant_mxfp8(a, rowwise=False, colwise=True)
             # dW_down[e] = dy_e^T · a_e
             dw_down = K.grouped_gemm_k(dytq, atq, offsets, d, f, kind=kind, asf=dytsf, bsf=atsf,
-                                       out=g_down, accumulate=g_down is not None)
+                                       out=g_down, accumulate=g_down is not None,
+                                     out_dtype=_grad_dtype(w_down))
             del dytq, dytsf, atq, atsf
             # da = dy · W_down  (per expert, contraction over d): B = W_down^T rows [f, d]
             wdt = w_down.detach().transpose(1, 2).contiguous()
@@ -173,7 +179,8 @@ class _SortedExperts(torch.autograd.Function):
             del wdt, tq, tsf, dyq, dysf
         else:
             dw_down = K.grouped_gemm_k(dy, a, offsets, d, f, a_mn=True, b_mn=True, out=g_down,
-                                       accumulate=g_down is not None)
+                                       accumulate=g_down is not None,
+                                     out_dtype=_grad_dtype(w_down))
             da = K.grouped_gemm(dy, w_down.view(e * d, f), offsets, f, d, b_mn=True)
         del dy, a
         dh, _ = K.glu_bwd(h, da, act, None, limit, up_offset)
@@ -182,7 +189,8 @@ class _SortedExperts(torch.autograd.Function):
             hq, hsf, htq, htsf = K.quant_mxfp8(dh, rowwise=True, colwise=True)
             _, _, xtq, xtsf = K.quant_mxfp8(x, rowwise=False, colwise=True, row_index=row_index, rows=rows)
             dw_gu = K.grouped_gemm_k(htq, xtq, offsets, f2, d, kind=kind, asf=htsf, bsf=xtsf,
-                                     out=g_gu, accumulate=g_gu is not None)
+                                     out=g_gu, accumulate=g_gu is not None,
+                                     out_dtype=_grad_dtype(w_gu))
             del htq, htsf, xtq, xtsf
             wgt = w_gu.detach().transpose(1, 2).contiguous()  # [E, d, 2f]
             tq, tsf, _, _ = K.quant_mxfp8_batched(wgt, rowwise=True)
@@ -190,7 +198,8 @@ class _SortedExperts(torch.autograd.Function):
         else:
             xs = K.gather_rows(x, row_index, rows)
             dw_gu = K.grouped_gemm_k(dh, xs, offsets, f2, d, a_mn=True, b_mn=True, out=g_gu,
-                                     accumulate=g_gu is not None)
+                                     accumulate=g_gu is not None,
+                                     out_dtype=_grad_dtype(w_gu))
             dxs = K.grouped_gemm(dh, w_gu.view(e * f2, d), offsets, d, f2, b_mn=True)
         dx = K.combine_rows(dxs, pos, None, t)
         gw_gu = None if g_gu is not None else dw_gu.to(w_gu.dtype)
@@ -306,7 +315,8 @@ class _ExpertsOnSorted(torch.autograd.Function):
             dyq, dysf, dytq, dytsf = K.quant_mxfp8(dy, rowwise=True, colwise=True)
             _, _, atq, atsf = K.quant_mxfp8(a, rowwise=False, colwise=True)
             dw_down = K.grouped_gemm_k(dytq, atq, offsets, d, f, kind=kind, asf=dytsf, bsf=atsf,
-                                       out=g_down, accumulate=g_down is not None)
+                                       out=g_down, accumulate=g_down is not None,
+                                     out_dtype=_grad_dtype(w_down))
             del dytq, dytsf, atq, atsf
             wdt = w_down.detach().transpose(1, 2).contiguous()
             tq, tsf, _, _ = K.quant_mxfp8_batched(wdt, rowwise=True)
@@ -314,7 +324,8 @@ class _ExpertsOnSorted(torch.autograd.Function):
             del wdt, tq, tsf, dyq, dysf
         else:
             dw_down = K.grouped_gemm_k(dy, a, offsets, d, f, a_mn=True, b_mn=True, out=g_down,
-                                       accumulate=g_down is not None)
+                                       accumulate=g_down is not None,
+                                     out_dtype=_grad_dtype(w_down))
             da = K.grouped_gemm(dy, w_down.view(e * d, f), offsets, f, d, b_mn=True)
         del a
         dh, _ = K.glu_bwd(h, da, act, None, limit, up_offset)
@@ -324,14 +335,16 @@ class _ExpertsOnSorted(torch.autograd.Function):
         if mx:
             hq, hsf, htq, htsf = K.quant_mxfp8(dh, rowwise=True, colwise=True)
             dw_gu = K.grouped_gemm_k(htq, xsave, offsets, f2, d, kind=kind, asf=htsf, bsf=xtsf,
-                                     out=g_gu, accumulate=g_gu is not None)
+                                     out=g_gu, accumulate=g_gu is not None,
+                                     out_dtype=_grad_dtype(w_gu))
             del htq, htsf
             wgt = w_gu.detach().transpose(1, 2).contiguous()
             tq, tsf, _, _ = K.quant_mxfp8_batched(wgt, rowwise=True)
             dxs = K.grouped_gemm(hq, tq, offsets, d, f2, kind=kind, asf=hsf, bsf=tsf, out=dx_out)
         else:
             dw_gu = K.grouped_gemm_k(dh, xsave, offsets, f2, d, a_mn=True, b_mn=True, out=g_gu,
-                                     accumulate=g_gu is not None)
+                                     accumulate=g_gu is not None,
+                                     out_dtype=_grad_dtype(w_gu))
             dxs = K.grouped_gemm(dh, w_gu.view(e * f2, d), offsets, d, f2, b_mn=True, out=dx_out)
         if io is not None:
             io.after_backward()

@@ -108,15 +108,17 @@ def grouped_gemm(a, b, offsets: torch.Tensor, n: int, k: int, *, kind: int = KIN
 
 def grouped_gemm_k(a, b, offsets: torch.Tensor, m: int, n: int, *, kind: int = KIND_BF16, asf=None,
                    bsf=None, a_mn: bool = False, b_mn: bool = False, out=None,
-                   accumulate: bool = False, bn: Optional[int] = None, sms: int = 0) -> torch.Tensor:
+                   accumulate: bool = False, bn: Optional[int] = None, sms: int = 0,
+                   out_dtype=torch.float32) -> torch.Tensor:
     """out[g] (+)= A[:, kg] · B[:, kg]^T for each group's contraction range kg (weight
     gradients of grouped experts). K-major: a [m, Ktot], b [n, Ktot]; MN-major: a [Ktot, m],
-    b [Ktot, n]. Returns fp32 [G, m, n]."""
+    b [Ktot, n]. Returns [G, m, n] in `out_dtype` (fp32, or bf16 written straight from the
+    accumulator when that is what the gradient is kept in)."""
     bn = _tile_width(n) if bn is None else bn
     groups = offsets.numel() - 1
     ktot = a.shape[0] if a_mn else a.shape[1]
     if out is None:
-        out = torch.empty(groups, m, n, dtype=torch.float32, device=a.device)
+        out = torch.empty(groups, m, n, dtype=out_dtype, device=a.device)
         accumulate = False
     if kind == KIND_MXFP8:
         a, b = a.view(torch.uint8), b.view(torch.uint8)
