@@ -152,7 +152,13 @@ def main() -> int:
                       moments="fp8" if tight else "bfloat16", master=False)
     # with the experts spread over four or more GPUs there is room to keep every layer's
     # attention output, so the backward's rerun of a block skips the attention forward
-    trainer.model.set_remat(True, offload=tight, keep_attention=n >= 4)
+    # On one or two GPUs the kept outputs go to pinned host memory with the block inputs
+    # (1.6 GB per block and GPU), if the host has the room.
+    import psutil
+
+    host_room = psutil.virtual_memory().available / max(1, n) > 160e9
+    keep_attention = n >= 4 or host_room
+    trainer.model.set_remat(True, offload=tight, keep_attention=keep_attention)
     feed = iter(trainer.batches())
     tokens_per_step = args.rows * n * args.seq_len
 
@@ -221,7 +227,8 @@ def main() -> int:
                        "parallelism": f"ep{n}" if n > 1 else "1 gpu (all experts local)",
                        "optimizer": "adamw, bf16 master, " + ("8-bit block-scaled moments" if tight else "bf16 moments")
                                     + ", expert updates fused into the backward, clip by the previous step's norm",
-                       "remat": "per block" + (", attention outputs kept" if n >= 4 else ""), "l2": "inputs and weights exceed L2 (126 MB) every step",
+                       "remat": "per block" + (", attention outputs kept" if keep_attention else "")
+                       + (", inputs and kept outputs in pinned host memory" if tight else ""), "l2": "inputs and weights exceed L2 (126 MB) every step",
                        "loss_last_step": loss},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d,

@@ -304,10 +304,12 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
       const bool by_tma = p.tma_store && (p.mode != MODE_GROUPED_ROWS || c.m_end - c.m0 >= BM);
       if (by_tma) {
         uint8_t* mine = epi_smem + quad * 4096;
-        constexpr int ROUNDS = BN / 64;
+        const int out_row0 = (p.mode == MODE_GROUPED_K ? c.group * p.M : 0) + c.m0 + quad * 32;
+        // a slab is 32 rows x 128 bytes: 64 bf16 columns, or 32 fp32 columns
+        const int slab_cols = p.out_kind == OUT_BF16 ? 64 : 32;
 #pragma unroll 1
-        for (int round = 0; round < ROUNDS; ++round) {
-          const int n = c.n0 + round * 64;
+        for (int col = 0; col < BN; col += slab_cols) {
+          const int n = c.n0 + col;
           if (n >= p.N) break;
           uint8_t* slab = mine + (Cfg::EPI_SLABS == 2 ? (epi_round & 1) * 16384 : 0);
           // the store that last read this slab must have finished reading it
@@ -316,29 +318,42 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
             else tma_store_wait_read();
           }
           __syncwarp();
-          uint32_t r0[32], r1[32];
-          tmem_ld_x32(t_addr + round * 64, r0);
-          tmem_ld_x32(t_addr + round * 64 + 32, r1);
-          tmem_ld_wait();
           uint8_t* rowp = slab + lane * 128;
+          if (p.out_kind == OUT_BF16) {
+            uint32_t r0[32], r1[32];
+            tmem_ld_x32(t_addr + col, r0);
+            tmem_ld_x32(t_addr + col + 32, r1);
+            tmem_ld_wait();
 #pragma unroll
-          for (int v = 0; v < 8; ++v) {
-            const uint32_t* src = v < 4 ? &r0[8 * v] : &r1[8 * (v - 4)];
-            uint4 q;
-            if (empty_k) {
-              q = make_uint4(0, 0, 0, 0);
-            } else {
-              q.x = pack_bf16(__uint_as_float(src[0]), __uint_as_float(src[1]));
-              q.y = pack_bf16(__uint_as_float(src[2]), __uint_as_float(src[3]));
-              q.z = pack_bf16(__uint_as_float(src[4]), __uint_as_float(src[5]));
-              q.w = pack_bf16(__uint_as_float(src[6]), __uint_as_float(src[7]));
+            for (int v = 0; v < 8; ++v) {
+              const uint32_t* src = v < 4 ? &r0[8 * v] : &r1[8 * (v - 4)];
+              uint4 q;
+              if (empty_k) {
+                q = make_uint4(0, 0, 0, 0);
+              } else {
+                q.x = pack_bf16(__uint_as_float(src[0]), __uint_as_float(src[1]));
+                q.y = pack_bf16(__uint_as_float(src[2]), __uint_as_float(src[3]));
+                q.z = pack_bf16(__uint_as_float(src[4]), __uint_as_float(src[5]));
+                q.w = pack_bf16(__uint_as_float(src[6]), __uint_as_float(src[7]));
+              }
+              *reinterpret_cast<uint4*>(rowp + ((v ^ (lane & 7)) << 4)) = q;
             }
-            *reinterpret_cast<uint4*>(rowp + ((v ^ (lane & 7)) << 4)) = q;
+          } else {
+            uint32_t r0[32];
+            tmem_ld_x32(t_addr + col, r0);
+            tmem_ld_wait();
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+              uint4 q = empty_k ? make_uint4(0, 0, 0, 0)
+                                : make_uint4(r0[4 * v], r0[4 * v + 1], r0[4 * v + 2], r0[4 * v + 3]);
+              *reinterpret_cast<uint4*>(rowp + ((v ^ (lane & 7)) << 4)) = q;
+            }
           }
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&p.tmap_c, slab, n, (p.mode == MODE_GROUPED_K ? c.group * p.M : 0) + c.m0 + quad * 32);
+            if (p.out_kind == OUT_F32_ACC) tma_reduce_add_2d(&p.tmap_c, slab, n, out_row0);
+            else tma_store_2d(&p.tmap_c, slab, n, out_row0);
             tma_store_commit();
           }
           ++epi_round;
@@ -504,12 +519,14 @@ const char* gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   else        err = make_tmap_2d(&p.tmap_b, a.b, elem, a.b_outer, a.b_inner, a.ldb_bytes, bk, bn);
   if (err) return err;
   p.tma_store = 0;
-  if (a.out_kind == OUT_BF16 && a.ldc % 8 == 0 && reinterpret_cast<uintptr_t>(a.c) % 16 == 0 &&
+  const int c_elem = a.out_kind == OUT_BF16 ? 2 : 4;
+  if (a.ldc * c_elem % 16 == 0 && reinterpret_cast<uintptr_t>(a.c) % 16 == 0 &&
       (a.mode != MODE_GROUPED_K || a.M % BM == 0)) {
     // rows of C: every row the walk can touch (grouped rows: the sorted, padded row count;
-    // grouped contraction: the groups' [M, N] outputs stacked)
+    // grouped contraction: the groups' [M, N] outputs stacked). Boxes are 32 rows x 128 bytes;
+    // fp32 accumulation into C is a TMA reduce-add (no read of C by the SMs).
     const uint64_t rows = a.mode == MODE_GROUPED_K ? (uint64_t)a.groups * a.M : (uint64_t)a.M;
-    if (make_tmap_2d(&p.tmap_c, a.c, 2, rows, (uint64_t)a.N, (uint64_t)a.ldc * 2, 64, 32) == nullptr)
+    if (make_tmap_2d(&p.tmap_c, a.c, c_elem, rows, (uint64_t)a.N, (uint64_t)a.ldc * c_elem, 128 / c_elem, 32) == nullptr)
       p.tma_store = 1;
   }
   const int sms = a.sms > 0 ? a.sms : 148;

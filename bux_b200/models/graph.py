@@ -167,19 +167,45 @@ class _Remat(torch.autograd.Function):
             fctx.save_for_backward(x)
         with torch.no_grad():
             y, aux = holder.run(x, replay=False)
+        if fctx.host is not None and holder.kept:
+            # kept attention outputs follow the block's input to the host
+            side = _side_stream(x.device)
+            side.wait_stream(torch.cuda.current_stream(x.device))
+            hosted = []
+            with torch.cuda.stream(side):
+                for i, pair in enumerate(holder.kept):
+                    on_host = []
+                    for j, t in enumerate(pair):
+                        h = holder.pinned(t, slot=(i, j))
+                        h.copy_(t, non_blocking=True)
+                        t.record_stream(side)
+                        on_host.append(h)
+                    hosted.append(tuple(on_host))
+            holder.kept = hosted
         return (y, *aux)
 
     @staticmethod
     def _fetch(fctx) -> None:
-        """Start the host → device copy of a block's input on the side stream."""
+        """Start the host → device copies of a block's input (and of the attention
+        outputs kept with it) on the side stream."""
         main = torch.cuda.current_stream(fctx.device)
         side = _side_stream(fctx.device)
         buf = torch.empty(fctx.host.shape, dtype=fctx.host.dtype, device=fctx.device)
-        side.wait_stream(main)  # the buffer's previous owner ran on the main stream
+        kept = fctx.holder.kept
+        back = None
+        if kept:
+            back = [tuple(torch.empty(h.shape, dtype=h.dtype, device=fctx.device) for h in pair) for pair in kept]
+        side.wait_stream(main)  # the buffers' previous owners ran on the main stream
         with torch.cuda.stream(side):
             buf.copy_(fctx.host, non_blocking=True)
+            if back is not None:
+                for pair, dst in zip(kept, back):
+                    for h, d in zip(pair, dst):
+                        d.copy_(h, non_blocking=True)
             done = torch.cuda.Event()
             done.record(side)
+        if back is not None:
+            fctx.holder.kept = back
         fctx.fetched = (buf, done)
 
     @staticmethod
@@ -228,8 +254,8 @@ class _BlockRun:
         self.taps = {k: list(v) for k, v in ctx.taps.items()}
         self.ports = dict(ctx.ports)
 
-    def pinned(self, x):
-        k = (self.key, tuple(x.shape), x.dtype)
+    def pinned(self, x, slot=None):
+        k = (self.key, slot, tuple(x.shape), x.dtype)
         buf = _BlockRun._pinned.get(k)
         if buf is None:
             buf = torch.empty(x.shape, dtype=x.dtype, device="cpu", pin_memory=True)

@@ -16,7 +16,7 @@ import torch.nn.functional as F
 from . import reference as ref
 from .functional import _K, _quant_weight, kernels_on
 
-CE_CHUNK_BYTES = 1 << 30  # logits held at once (bf16)
+CE_CHUNK_BYTES = 1 << 31  # logits held at once (bf16): fewer, larger chunks mean fewer passes over dW
 
 
 # ------------------------------------------------------------------ LM head + loss
