@@ -152,12 +152,9 @@ def main() -> int:
                       moments="fp8" if tight else "bfloat16", master=False)
     # with the experts spread over four or more GPUs there is room to keep every layer's
     # attention output, so the backward's rerun of a block skips the attention forward
-    # On one or two GPUs the kept outputs go to pinned host memory with the block inputs
-    # (1.6 GB per block and GPU), if the host has the room.
-    import psutil
-
-    host_room = psutil.virtual_memory().available / max(1, n) > 160e9
-    keep_attention = n >= 4 or host_room
+    # (On one or two GPUs they would have to follow the block inputs to pinned host memory:
+    # measured slower, PCIe becomes the bound, so they are recomputed there.)
+    keep_attention = n >= 4
     trainer.model.set_remat(True, offload=tight, keep_attention=keep_attention)
     feed = iter(trainer.batches())
     tokens_per_step = args.rows * n * args.seq_len
