@@ -154,7 +154,18 @@ def main() -> int:
     # attention output, so the backward's rerun of a block skips the attention forward
     # (On one or two GPUs they would have to follow the block inputs to pinned host memory:
     # measured slower, PCIe becomes the bound, so they are recomputed there.)
-    keep_attention = n >= 4
+    keep_attention = False
+    if not tight:
+        arch = run.arch
+        attn = next(l.config for l in arch.layers() if l.config.type == "gqa")
+        blocks = sum(1 for l in arch.layers() if l.config.type == "gqa")
+        tokens = args.rows * args.seq_len
+        hd = attn.head_dim or arch.d_model // attn.num_heads
+        kept = tokens * attn.num_heads * (hd * 2 + 4)          # o in bf16 and the log-sum-exp in fp32
+        inputs = tokens * arch.d_model * 2
+        free, _ = torch.cuda.mem_get_info(device)
+        # 60 GB of slack: exchange buffers, one block's working set, the loss chunks
+        keep_attention = free > blocks * (kept + inputs) + 60e9
     trainer.model.set_remat(True, offload=tight, keep_attention=keep_attention)
     feed = iter(trainer.batches())
     tokens_per_step = args.rows * n * args.seq_len
