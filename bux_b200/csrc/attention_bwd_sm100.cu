@@ -157,15 +157,18 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
       bool ok = mbar_wait(kv_full, 0, abort_flag, st, KID_ATTN_BWD, 2);
       for (int s = 0; s < n_steps && ok; ++s) {
         ok = mbar_wait(qdo_full, s & 1, abort_flag, st, KID_ATTN_BWD, 3);
-        // the S / dQ columns of the previous step must have been drained
-        if (ok && s > 0) ok = mbar_wait(dq_done, (s - 1) & 1, abort_flag, st, KID_ATTN_BWD, 4);
         if (!ok) break;
         tc_fence_after();
+        // S has columns of its own (read before p_ready of the step before): it runs while
+        // the previous dQ, which shares dP's columns, is still being drained
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
           mma_f16(t_s, make_smem_desc(aQ + off, 0, 1024, 2), make_smem_desc(aK + off, 0, 1024, 2), id_s, kk > 0);
         }
+        if (s > 0) ok = mbar_wait(dq_done, (s - 1) & 1, abort_flag, st, KID_ATTN_BWD, 4);
+        if (!ok) break;
+        tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
