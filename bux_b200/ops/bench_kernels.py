@@ -149,6 +149,23 @@ def bench_memory_bound(rows: list, pk: dict) -> None:
                  "of_peak": gb / ms * 1e3 / pk["hbm_gbs"]})
 
 
+def bench_muon(rows: list, pk: dict) -> None:
+    """Muon's Newton–Schulz iteration (five quintic steps) on the framework's GEMM beside the
+    same iteration on library matmuls."""
+    from ..ops import functional as F_
+    from ..train import optim
+
+    for m, n in ((2048, 8192), (4096, 4096)):
+        g = torch.randn(m, n, device="cuda")
+        flops = 5 * (2.0 * m * m * n * 2 + 2.0 * m * m * m)
+        ms = timed(lambda: optim.newton_schulz(g, 5))
+        F_.set_kernels(False)
+        ms_lib = timed(lambda: optim.newton_schulz(g, 5))
+        F_.set_kernels(True)
+        rows.append({"kernel": "muon newton_schulz x5", "shape": f"{m}x{n}", "ms": ms, "tflops": flops / ms / 1e9,
+                     "library_ms": ms_lib, "of_peak": flops / ms / 1e9 / pk["bf16_tflops"]})
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default=None)
@@ -160,7 +177,7 @@ def main() -> None:
     pk = peaks()
     rows: list = []
     for name, fn in (("gemm", bench_gemm), ("grouped", bench_grouped), ("attention", bench_attention),
-                     ("memory", bench_memory_bound)):
+                     ("memory", bench_memory_bound), ("muon", bench_muon)):
         if not args.only or args.only in name:
             fn(rows, pk)
     K.check_status(torch.device("cuda"), "bench_kernels")

@@ -134,11 +134,38 @@ def newton_schulz(g: torch.Tensor, steps: int = 5, coefficients: str = "jordan",
         x = x.transpose(-1, -2)
     scale = 1.02 if coefficients == "polar_express" else 1.0
     x = x / (x.float().norm(dim=(-2, -1), keepdim=True) * scale + 1e-7).to(dtype)
+    if x.is_cuda and dtype == torch.bfloat16 and _tensor_core_shapes(x):
+        x = _newton_schulz_tcgen05(x.contiguous(), steps, table)
+        return x.transpose(-1, -2) if transposed else x
     for i in range(steps):
         a, b, c = table[min(i, len(table) - 1)]
         gram = x @ x.transpose(-1, -2)
         x = a * x + (b * gram + c * (gram @ gram)) @ x
     return x.transpose(-1, -2) if transposed else x
+
+
+def _tensor_core_shapes(x: torch.Tensor) -> bool:
+    """The TMA descriptors of the GEMM want every row pitch a multiple of 16 bytes."""
+    from ..ops import functional as ops
+    return ops.kernels_on(x) and x.dim() in (2, 3) and x.shape[-1] % 8 == 0 and x.shape[-2] % 8 == 0
+
+
+def _newton_schulz_tcgen05(x: torch.Tensor, steps: int, table) -> torch.Tensor:
+    """The quintic iteration on this framework's own tcgen05 GEMM: three GEMMs per step
+    (X·Xᵀ, A·A, and (bA + cA²)·X with X read as the MN-major operand, so nothing is
+    transposed in memory), the polynomial and the `aX +` as two fused elementwise ops.
+    A stack of matrices [e, m, n] runs matrix by matrix."""
+    from ..ops import kernels as K
+    if x.dim() == 3:
+        return torch.stack([_newton_schulz_tcgen05(x[e].contiguous(), steps, table) for e in range(x.shape[0])])
+    for i in range(steps):
+        a, b, c = table[min(i, len(table) - 1)]
+        gram = K.gemm_bf16(x, x)                    # [m, m] = X Xᵀ
+        poly = K.gemm_bf16(gram, gram)              # A² (A is symmetric: A·Aᵀ)
+        poly = torch.add(poly.mul_(c), gram, alpha=b)
+        step = K.gemm_bf16(poly, x, b_mn=True)      # [m, n]: X stored [k=m, n]
+        x = step.add_(x, alpha=a)
+    return x
 
 
 # ------------------------------------------------------------------ optimizer

@@ -152,3 +152,22 @@ precision = precision(compute=bfloat16)
     assert n1 == n0 - 2 * 2              # one attention forward less per block and step
     # dQ is summed by fp32 reductions whose order varies from run to run: close, not bit-equal
     assert all(torch.allclose(s0[k], s1[k], atol=2e-3, rtol=2e-2) for k in s0)
+
+
+@pytest.mark.parametrize("shape", [(512, 2048), (2048, 768), (3, 256, 512)])
+def test_newton_schulz_on_the_tcgen05_gemm_matches_fp32(shape):
+    """Muon's orthogonalisation through the framework's GEMM against the same iteration in
+    fp32 PyTorch; the result is close to an orthogonal factor (singular values near 1)."""
+    from bux_b200.ops import kernels as K
+    from bux_b200.train import optim
+
+    torch.manual_seed(0)
+    g = torch.randn(*shape, device="cuda")
+    before = K.launches
+    got = optim.newton_schulz(g, steps=5, dtype=torch.bfloat16).float()
+    want = optim.newton_schulz(g, steps=5, dtype=torch.float32)
+    assert got.shape == want.shape
+    assert (got - want).norm() / want.norm() < 0.06
+    s = torch.linalg.svdvals(got.reshape(-1, *shape[-2:])[0])
+    assert 0.5 < s.min() and s.max() < 1.3
+    assert K.launches >= before + 15  # three GEMMs per step, per matrix
