@@ -143,6 +143,28 @@ void quant_mxfp8(const Tensor& x, const c10::optional<Tensor>& row_index, const 
   bux::quant_mxfp8(x.data_ptr(), x.stride(-2), opt_i32(row_index), qr, sr, qc, sc, rows, (int)cols, ld_col, (int)batch, x_batch_stride, stream_of(x));
 }
 
+void quant_mxfp8_glu(const Tensor& h, const c10::optional<Tensor>& dout, const c10::optional<Tensor>& q_row,
+                     const c10::optional<Tensor>& sf_row, const c10::optional<Tensor>& q_col,
+                     const c10::optional<Tensor>& sf_col, int64_t ld_col, int64_t kind, double limit, double up_offset) {
+  TORCH_CHECK(h.is_cuda() && h.scalar_type() == at::kBFloat16 && h.dim() == 2 && h.is_contiguous(), "quant_glu: contiguous bf16 h [rows, 2f]");
+  const int64_t rows = h.size(0), f = h.size(1) / 2;
+  TORCH_CHECK(f % 32 == 0, "quant_glu: f % 32 == 0");
+  const void* dp = nullptr;
+  if (dout.has_value()) {
+    TORCH_CHECK(dout->is_cuda() && dout->scalar_type() == at::kBFloat16 && dout->is_contiguous() &&
+                dout->size(0) == rows && dout->size(1) == f, "quant_glu: contiguous bf16 dout [rows, f]");
+    TORCH_CHECK(f % 128 == 0, "quant_glu: the gradient wants f % 128 == 0");
+    dp = dout->data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(h.device());
+  uint8_t* qr = q_row.has_value() ? reinterpret_cast<uint8_t*>(q_row->data_ptr()) : nullptr;
+  uint8_t* sr = sf_row.has_value() ? reinterpret_cast<uint8_t*>(sf_row->data_ptr()) : nullptr;
+  uint8_t* qc = q_col.has_value() ? reinterpret_cast<uint8_t*>(q_col->data_ptr()) : nullptr;
+  uint8_t* sc = sf_col.has_value() ? reinterpret_cast<uint8_t*>(sf_col->data_ptr()) : nullptr;
+  TORCH_CHECK(qc == nullptr || ld_col % 32 == 0, "quant_glu: transposed copy needs a row count padded to 32");
+  bux::quant_mxfp8_glu(h.data_ptr(), dp, qr, sr, qc, sc, rows, (int)f, ld_col, (int)kind, (float)limit, (float)up_offset, stream_of(h));
+}
+
 // ------------------------------------------------------------------ loss / optimiser / MoE rows
 void ce_fwd_bwd(Tensor& logits, const Tensor& targets, const c10::optional<Tensor>& mask, Tensor& loss,
                 const c10::optional<Tensor>& logz, double grad_scale, double z_weight, double softcap) {
@@ -306,6 +328,7 @@ TORCH_LIBRARY(bux_b200, m) {
   m.def("glu_fwd(Tensor h, Tensor(a!) out, Tensor? row_scale, int kind, float limit, float up_offset) -> ()", &glu_fwd);
   m.def("glu_bwd(Tensor h, Tensor dout, Tensor(a!) dh, Tensor? row_scale, Tensor? d_row_scale, int kind, float limit, float up_offset) -> ()", &glu_bwd);
   m.def("quant_mxfp8(Tensor x, Tensor? row_index, Tensor? q_row, Tensor? sf_row, Tensor? q_col, Tensor? sf_col, int rows, int cols, int ld_col, int batch, int x_batch_stride) -> ()", &quant_mxfp8);
+  m.def("quant_mxfp8_glu(Tensor h, Tensor? dout, Tensor? q_row, Tensor? sf_row, Tensor? q_col, Tensor? sf_col, int ld_col, int kind, float limit, float up_offset) -> ()", &quant_mxfp8_glu);
   m.def("ce_fwd_bwd(Tensor(a!) logits, Tensor targets, Tensor? mask, Tensor(b!) loss, Tensor? logz, float grad_scale, float z_weight, float softcap) -> ()", &ce_fwd_bwd);
   m.def("adamw(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor? m_sf, Tensor? v_sf, Tensor? shadow, Tensor? grad_scale, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2, float grad_scale_const) -> ()", &adamw);
   m.def("sumsq(Tensor g, Tensor(a!) out) -> ()", &sumsq);

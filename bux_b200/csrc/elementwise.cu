@@ -330,12 +330,69 @@ __device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float 
   return (uint32_t)lo | ((uint32_t)hi << 16);
 }
 
-__global__ void __launch_bounds__(256)
+// What the quantiser reads its 128×128 tile from: the matrix itself, or a gated activation
+// computed on the way in (the activation, or its gradient, is then never written as bf16).
+#ifndef QUANT_CTAS
+#define QUANT_CTAS 5
+#endif
+enum { QSRC_PLAIN = 0, QSRC_GLU_FWD = 1, QSRC_GLU_BWD = 2 };
+struct QuantGlu {
+  const __nv_bfloat16* dout;  // GLU_BWD: gradient of the activation's output [rows, f]
+  int f;                      // h is [rows, 2f]: gate columns, then up columns
+  int kind;
+  float limit, up_offset;
+};
+
+// Eight gated activations from eight gates and ups (same rounding as glu_fwd_kernel).
+__device__ __forceinline__ uint4 glu_fwd8(const uint4& gv, const uint4& uv, const QuantGlu& gp) {
+  uint4 o; uint32_t* ou = &o.x; const uint32_t* gu = &gv.x; const uint32_t* uu = &uv.x;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float2 g = unpack_bf16(gu[j]), u = unpack_bf16(uu[j]);
+    if (gp.limit > 0.f) {
+      g.x = fminf(g.x, gp.limit); g.y = fminf(g.y, gp.limit);
+      u.x = fminf(fmaxf(u.x, -gp.limit), gp.limit); u.y = fminf(fmaxf(u.y, -gp.limit), gp.limit);
+    }
+    ou[j] = pack_bf16(act_fwd(g.x, gp.kind) * (u.x + gp.up_offset), act_fwd(g.y, gp.kind) * (u.y + gp.up_offset));
+  }
+  return o;
+}
+// Eight gradients of the gate (up_half false) or of the up (true) columns (as glu_bwd_kernel).
+__device__ __forceinline__ uint4 glu_bwd8(const uint4& gv, const uint4& uv, const uint4& dv, bool up_half,
+                                          const QuantGlu& gp) {
+  uint4 o; uint32_t* ou = &o.x;
+  const uint32_t* gu = &gv.x; const uint32_t* uu = &uv.x; const uint32_t* du = &dv.x;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 g = unpack_bf16(gu[j]), u = unpack_bf16(uu[j]), d = unpack_bf16(du[j]);
+    const float gx[2] = {g.x, g.y}, ux[2] = {u.x, u.y}, dx[2] = {d.x, d.y};
+    float r[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      bool g_pass = true, u_pass = true;
+      float gg = gx[e], uu_ = ux[e];
+      if (gp.limit > 0.f) {
+        if (gg > gp.limit) { gg = gp.limit; g_pass = false; }
+        if (uu_ > gp.limit) { uu_ = gp.limit; u_pass = false; }
+        if (uu_ < -gp.limit) { uu_ = -gp.limit; u_pass = false; }
+      }
+      if (up_half) r[e] = u_pass ? dx[e] * act_fwd(gg, gp.kind) : 0.f;
+      else r[e] = g_pass ? dx[e] * (uu_ + gp.up_offset) * act_grad(gg, gp.kind) : 0.f;
+    }
+    ou[j] = pack_bf16(r[0], r[1]);
+  }
+  return o;
+}
+
+template <int SRC>
+__global__ void __launch_bounds__(256, QUANT_CTAS)
 quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long ld_x,
                    const int* __restrict__ row_index,
                    uint8_t* __restrict__ q_row, uint8_t* __restrict__ sf_row,
                    uint8_t* __restrict__ q_col, uint8_t* __restrict__ sf_col,
-                   long rows, int cols, long ld_col, long x_batch_stride) {
+                   long rows, int cols, long ld_col, long x_batch_stride, QuantGlu gp) {
+  // Registers are kept low (values are re-read from the shared tile rather than held) so
+  // that six blocks fit an SM: the kernel is a stream, and blocks in flight hide its latency.
   __shared__ __align__(16) __nv_bfloat16 tile[QT][QPITCH];
   __shared__ __align__(16) uint8_t sfr[512];
   __shared__ __align__(16) uint8_t sfc[512];
@@ -351,91 +408,128 @@ quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long ld_x,
   const int tid = threadIdx.x;
   const long r0 = (long)blockIdx.y * QT;
   const int c0 = blockIdx.x * QT;
-  {
-    // load: 16 threads per row (8 elements each), 16 rows per pass; all loads first
-    uint4 v[8];
-    const int cc = (tid & 15) * 8;
+  const int cc = (tid & 15) * 8;  // load: 16 threads per row (8 elements each), 16 rows per pass
+  if (SRC == QSRC_PLAIN) {
 #pragma unroll
-    for (int pass = 0; pass < 8; ++pass) {
-      const long r = r0 + pass * 16 + (tid >> 4);
-      long src = r;
-      if (row_index && r < rows) src = row_index[r];
-      v[pass] = make_uint4(0, 0, 0, 0);
-      if (r < rows && src >= 0 && c0 + cc < cols)
-        v[pass] = *reinterpret_cast<const uint4*>(x + src * ld_x + c0 + cc);
+    for (int base = 0; base < 8; base += 4) {
+      uint4 v[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const long r = r0 + (base + i) * 16 + (tid >> 4);
+        long src = r;
+        if (row_index && r < rows) src = row_index[r];
+        v[i] = make_uint4(0, 0, 0, 0);
+        if (r < rows && src >= 0 && c0 + cc < cols)
+          v[i] = *reinterpret_cast<const uint4*>(x + src * ld_x + c0 + cc);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        *reinterpret_cast<uint4*>(&tile[(base + i) * 16 + (tid >> 4)][cc]) = v[i];
     }
+  } else {
+    // the tile is computed from h (and dout), two rows' loads in flight per thread.
+    // GLU_FWD: cols == f, column c pairs h[:, c] with h[:, f + c]. GLU_BWD: cols == 2f and
+    // a tile lies in one half (f % 128 == 0): gate gradients, then up gradients.
+    const bool up_half = SRC == QSRC_GLU_BWD && c0 >= gp.f;
+    const int hc = (up_half ? c0 - gp.f : c0) + cc;  // gate column in h
+#pragma unroll 1
+    for (int base = 0; base < 8; base += 2) {
+      uint4 g[2], u[2], d[2];
 #pragma unroll
-    for (int pass = 0; pass < 8; ++pass)
-      *reinterpret_cast<uint4*>(&tile[pass * 16 + (tid >> 4)][cc]) = v[pass];
+      for (int i = 0; i < 2; ++i) {
+        const long r = r0 + (base + i) * 16 + (tid >> 4);
+        g[i] = u[i] = d[i] = make_uint4(0, 0, 0, 0);
+        if (r < rows && c0 + cc < cols) {
+          g[i] = *reinterpret_cast<const uint4*>(x + r * ld_x + hc);
+          u[i] = *reinterpret_cast<const uint4*>(x + r * ld_x + gp.f + hc);
+          if (SRC == QSRC_GLU_BWD) d[i] = *reinterpret_cast<const uint4*>(gp.dout + r * (long)gp.f + hc);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const long r = r0 + (base + i) * 16 + (tid >> 4);
+        uint4 o = make_uint4(0, 0, 0, 0);
+        if (r < rows && c0 + cc < cols)
+          o = SRC == QSRC_GLU_FWD ? glu_fwd8(g[i], u[i], gp) : glu_bwd8(g[i], u[i], d[i], up_half, gp);
+        *reinterpret_cast<uint4*>(&tile[(base + i) * 16 + (tid >> 4)][cc]) = o;
+      }
+    }
   }
   __syncthreads();
   if (q_row) {
     // thread -> row tid % 128, 32-column blocks tid / 128 and tid / 128 + 2
     const int rr = tid & 127;
     const long r = r0 + rr;
-#pragma unroll
+#pragma unroll 1
     for (int i = 0; i < 2; ++i) {
       const int cb = (tid >> 7) + 2 * i;
-      float f[32];
+      uint4 w[4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const uint4 w = *reinterpret_cast<const uint4*>(&tile[rr][cb * 32 + k * 8]);
-        float2 t;
-        t = unpack_bf16(w.x); f[8 * k] = t.x; f[8 * k + 1] = t.y;
-        t = unpack_bf16(w.y); f[8 * k + 2] = t.x; f[8 * k + 3] = t.y;
-        t = unpack_bf16(w.z); f[8 * k + 4] = t.x; f[8 * k + 5] = t.y;
-        t = unpack_bf16(w.w); f[8 * k + 6] = t.x; f[8 * k + 7] = t.y;
-      }
+      for (int k = 0; k < 4; ++k) w[k] = *reinterpret_cast<const uint4*>(&tile[rr][cb * 32 + k * 8]);
       float amax = 0.f;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(f[j]));
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t* u = &w[k].x;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 t = unpack_bf16(u[j]);
+          amax = fmaxf(amax, fmaxf(fabsf(t.x), fabsf(t.y)));
+        }
+      }
       const bool live = r < rows && c0 + cb * 32 < cols;
       const uint8_t e = e8m0_of(amax);
       const float inv = e8m0_inv(e);
       sfr[(rr & 31) * 16 + (rr >> 5) * 4 + cb] = live ? e : (uint8_t)127;
       if (live) {
-        uint32_t packed[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          packed[j] = cvt_e4m3x4(f[4 * j] * inv, f[4 * j + 1] * inv, f[4 * j + 2] * inv, f[4 * j + 3] * inv);
         uint4* dst = reinterpret_cast<uint4*>(q_row + r * cols + c0 + cb * 32);
-        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+#pragma unroll
+        for (int hv = 0; hv < 2; ++hv) {
+          uint32_t packed[4];
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {
+            const uint4& ww = w[2 * hv + k];
+            const float2 a = unpack_bf16(ww.x), b = unpack_bf16(ww.y), c = unpack_bf16(ww.z), d = unpack_bf16(ww.w);
+            packed[2 * k] = cvt_e4m3x4(a.x * inv, a.y * inv, b.x * inv, b.y * inv);
+            packed[2 * k + 1] = cvt_e4m3x4(c.x * inv, c.y * inv, d.x * inv, d.y * inv);
+          }
+          dst[hv] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        }
       }
     }
   }
   if (q_col) {
-    // thread -> columns 2*(tid % 64) and +1, 32-row block tid / 64: one scale block each
+    // thread -> columns 2*(tid % 64) and +1, 32-row block tid / 64: one scale block each.
+    // One pass over the tile for both maxima, one per column to convert.
     const int cp = tid & 63, rb = tid >> 6;
-    uint32_t w[32];
-#pragma unroll
-    for (int j = 0; j < 32; ++j) w[j] = *reinterpret_cast<const uint32_t*>(&tile[rb * 32 + j][2 * cp]);
-#pragma unroll
+    float amax0 = 0.f, amax1 = 0.f;
+#pragma unroll 8
+    for (int j = 0; j < 32; ++j) {
+      const float2 t = unpack_bf16(*reinterpret_cast<const uint32_t*>(&tile[rb * 32 + j][2 * cp]));
+      amax0 = fmaxf(amax0, fabsf(t.x));
+      amax1 = fmaxf(amax1, fabsf(t.y));
+    }
+#pragma unroll 1
     for (int half = 0; half < 2; ++half) {
-      const int cc = 2 * cp + half;
-      const int c = c0 + cc;
-      float amax = 0.f;
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const float2 t = unpack_bf16(w[j]);
-        amax = fmaxf(amax, fabsf(half ? t.y : t.x));
-      }
+      const int ccol = 2 * cp + half;
+      const int c = c0 + ccol;
       const bool live = c < cols;
-      const uint8_t e = e8m0_of(amax);
+      const uint8_t e = e8m0_of(half ? amax1 : amax0);
       const float inv = e8m0_inv(e);
-      sfc[(cc & 31) * 16 + (cc >> 5) * 4 + rb] = live ? e : (uint8_t)127;
+      sfc[(ccol & 31) * 16 + (ccol >> 5) * 4 + rb] = live ? e : (uint8_t)127;
       if (live) {
-        uint32_t packed[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float2 t0 = unpack_bf16(w[4 * j]), t1 = unpack_bf16(w[4 * j + 1]);
-          const float2 t2 = unpack_bf16(w[4 * j + 2]), t3 = unpack_bf16(w[4 * j + 3]);
-          packed[j] = half ? cvt_e4m3x4(t0.y * inv, t1.y * inv, t2.y * inv, t3.y * inv)
-                           : cvt_e4m3x4(t0.x * inv, t1.x * inv, t2.x * inv, t3.x * inv);
-        }
         uint4* dst = reinterpret_cast<uint4*>(q_col + (size_t)c * ld_col + r0 + rb * 32);
-        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+#pragma unroll
+        for (int hv = 0; hv < 2; ++hv) {
+          uint32_t packed[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int row = rb * 32 + hv * 16 + 4 * j;
+            const __nv_bfloat16* col = &tile[row][ccol];
+            packed[j] = cvt_e4m3x4(__bfloat162float(col[0]) * inv, __bfloat162float(col[QPITCH]) * inv,
+                                   __bfloat162float(col[2 * QPITCH]) * inv, __bfloat162float(col[3 * QPITCH]) * inv);
+          }
+          dst[hv] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        }
       }
     }
   }
@@ -807,7 +901,16 @@ void glu_bwd(const void* h, const void* dout, void* dh, const float* row_scale, 
 void quant_mxfp8(const void* x, long ld_x, const int* row_index, uint8_t* q_row, uint8_t* sf_row, uint8_t* q_col, uint8_t* sf_col, long rows, int cols, long ld_col, int batch, long x_batch_stride, cudaStream_t s) {
   const long extent = q_col ? (ld_col > rows ? ld_col : rows) : rows;  // the transposed copy is padded to ld_col
   dim3 grid((cols + 127) / 128, (unsigned)((extent + 127) / 128), batch);
-  quant_mxfp8_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, ld_x, row_index, q_row, sf_row, q_col, sf_col, rows, cols, ld_col, x_batch_stride);
+  quant_mxfp8_kernel<QSRC_PLAIN><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, ld_x, row_index, q_row, sf_row, q_col, sf_col, rows, cols, ld_col, x_batch_stride, QuantGlu{});
+}
+void quant_mxfp8_glu(const void* h, const void* dout, uint8_t* q_row, uint8_t* sf_row, uint8_t* q_col, uint8_t* sf_col,
+                     long rows, int f, long ld_col, int kind, float limit, float up_offset, cudaStream_t s) {
+  const int cols = dout ? 2 * f : f;
+  const long extent = q_col ? (ld_col > rows ? ld_col : rows) : rows;
+  dim3 grid((cols + 127) / 128, (unsigned)((extent + 127) / 128), 1);
+  QuantGlu gp{(const __nv_bfloat16*)dout, f, kind, limit, up_offset};
+  if (dout) quant_mxfp8_kernel<QSRC_GLU_BWD><<<grid, 256, 0, s>>>((const __nv_bfloat16*)h, 2L * f, nullptr, q_row, sf_row, q_col, sf_col, rows, cols, ld_col, 0, gp);
+  else quant_mxfp8_kernel<QSRC_GLU_FWD><<<grid, 256, 0, s>>>((const __nv_bfloat16*)h, 2L * f, nullptr, q_row, sf_row, q_col, sf_col, rows, cols, ld_col, 0, gp);
 }
 void ce_fwd_bwd(void* logits, const int* targets, const float* mask, float* loss, float* logz, long rows, int vocab, long ld, float grad_scale, float z_weight, float softcap, cudaStream_t s) {
   ce_fwd_bwd_kernel<<<(unsigned)rows, 512, 0, s>>>((__nv_bfloat16*)logits, targets, mask, loss, logz, vocab, ld, grad_scale, z_weight, softcap);

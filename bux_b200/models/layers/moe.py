@@ -31,6 +31,31 @@ def balance_loss(scores: torch.Tensor, picks: torch.Tensor, k: int, per_sequence
     return scores.shape[-1] * (f * p).sum(-1).mean()
 
 
+def budget_loss(scores: torch.Tensor, picks: torch.Tensor, c: L.MoEConfig, per_sequence: bool) -> torch.Tensor:
+    """LongCat-Flash's balance loss with zero experts (reference:
+    ``architecture/experts/moe.py:512-546``): Σ_j f_j P_j over the FFN experts and the zero
+    experts as one more; 1 when the FFN experts take their budget of a token's picks evenly."""
+    over = (1,) if per_sequence else (0, 1)
+    n, budget = c.num_experts, c.ffn_budget
+    count = picks.float().mean(over)
+    p = (scores / scores.sum(-1, keepdim=True)).mean(over)
+    f = n / budget * count[..., :n]
+    f_zero = count[..., n:].sum(-1) / (c.top_k - budget)
+    return ((f * p[..., :n]).sum(-1) + f_zero * p[..., n:].sum(-1)).mean()
+
+
+def budget_move(load: torch.Tensor, c: L.MoEConfig) -> torch.Tensor:
+    """The router-bias move with zero experts: each FFN expert by rate · (1 − load / target),
+    target = its even share of the FFN budget; the zero experts' bias stays 0
+    (``architecture/experts/moe.py:427-449`` there)."""
+    n = c.num_experts
+    target = c.ffn_budget * load.sum(-1, keepdim=True) / (c.top_k * n)
+    picked = target > 0
+    shortfall = torch.where(picked, 1 - load[..., :n] / torch.where(picked, target, torch.ones_like(target)),
+                            torch.zeros_like(load[..., :n]))
+    return torch.cat([c.bias_update_rate * shortfall, torch.zeros_like(load[..., n:])], -1)
+
+
 def limit_groups(choice: torch.Tensor, groups: int, keep: int) -> torch.Tensor:
     b, t, n = choice.shape
     grouped = choice.view(b, t, groups, n // groups)
@@ -54,25 +79,34 @@ class _ScaleGrad(torch.autograd.Function):
 class MoE(nn.Module):
     def __init__(self, c: L.MoEConfig, b: BuildContext):
         super().__init__()
-        if c.num_zero_experts or c.latent_size is not None or c.expert_norm is not None:
-            raise NotImplementedError("moe: zero experts, LatentMoE and expert_norm are not built yet")
         if c.expert.type != "gated_mlp":
             raise NotImplementedError("moe: routed experts are gated MLPs in this framework")
         self.c = c
         d = b.width if isinstance(b.width, int) else b.d_model
         e, f = c.num_experts, c.expert.intermediate_size
-        self.d, self.e, self.f = d, e, f
+        scored = e + c.num_zero_experts  # the router scores the zero experts after the routed ones
+        inner = c.latent_size or d       # the width the routed experts see (LatentMoE: narrower)
+        self.d, self.e, self.f, self.inner = d, e, f, inner
         self.tp_share = 1.0
-        self.router = Linear(d, e + (c.num_shared_experts if c.shared_expert_sink else 0),
+        self.router = Linear(d, scored + (c.num_shared_experts if c.shared_expert_sink else 0),
                              c.router_bias, b, role="router")
         self.router.weight.data = self.router.weight.data.float()
-        self.experts_gate_up = nn.Parameter(torch.empty(e, 2 * f, d, dtype=b.dtype))
-        self.experts_down = nn.Parameter(torch.empty(e, d, f, dtype=b.dtype))
+        if c.latent_size is not None:
+            self.to_latent = Linear(d, inner, False, b, role="latent")
+            self.from_latent = Linear(inner, d, False, b, role="latent")
+        if c.latent_input_norm is not None:
+            self.latent_input_norm = Norm(c.latent_input_norm, inner)
+        if c.latent_output_norm is not None:
+            self.latent_output_norm = Norm(c.latent_output_norm, inner)
+        if c.expert_norm is not None:
+            self.expert_norm = Norm(c.expert_norm, inner)
+        self.experts_gate_up = nn.Parameter(torch.empty(e, 2 * f, inner, dtype=b.dtype))
+        self.experts_down = nn.Parameter(torch.empty(e, inner, f, dtype=b.dtype))
         init_weight(self.experts_gate_up, b.init)
         init_weight(self.experts_down, b.init, "out")
         if c.load_balancing in ("aux_free", "smebu"):
-            self.register_buffer("router_bias", torch.zeros(e))
-            self.register_buffer("router_load", torch.zeros(e))
+            self.register_buffer("router_bias", torch.zeros(scored))
+            self.register_buffer("router_load", torch.zeros(scored))
             self.register_buffer("bias_velocity", torch.zeros(e))
         if c.num_shared_experts:
             sc = c.shared_expert or c.expert
@@ -91,7 +125,7 @@ class MoE(nn.Module):
             drawn = torch.randn_like(logits)
             logits = drawn + (logits - logits.detach())
         scores = ref.router_scores(logits, c.router)
-        n = c.num_experts
+        n = c.num_experts + c.num_zero_experts
         scores, sinks = scores[..., :n], scores[..., n:]
         choice = scores
         if hasattr(self, "router_bias"):
@@ -105,7 +139,10 @@ class MoE(nn.Module):
             if w:
                 # under tensor parallelism every rank reports the same loss: each gives 1/n of its gradient
                 seen = scores if self.tp_share == 1.0 else _ScaleGrad.apply(scores, self.tp_share)
-                ctx.report("balance_loss", balance_loss(seen, picks, c.top_k, c.aux_loss_scope == "sequence"), w)
+                per_sequence = c.aux_loss_scope == "sequence"
+                loss = (budget_loss(seen, picks, c, per_sequence) if c.num_zero_experts
+                        else balance_loss(seen, picks, c.top_k, per_sequence))
+                ctx.report("balance_loss", loss, w)
             if hasattr(self, "router_load"):
                 self.router_load += picks.detach().sum((0, 1))
         weights = scores.gather(-1, idx)
@@ -125,6 +162,10 @@ class MoE(nn.Module):
         load = self.router_load
         if load.sum() == 0:
             return
+        if c.num_zero_experts:
+            self.router_bias.add_(budget_move(load, c))
+            load.zero_()
+            return
         err = load.mean() - load
         if c.load_balancing == "smebu":
             step = torch.tanh(err / load.mean().clamp_min(1.0) / c.bias_softclamp) * c.bias_softclamp
@@ -141,16 +182,47 @@ class MoE(nn.Module):
         c = self.c
         bsz, t, d = x.shape
         idx, weights, sinks = self.route(x, ctx)
-        flat = x.reshape(bsz * t, d)
+        z = x
+        if c.latent_size is not None:
+            z = self.to_latent(x, ctx)
+        if c.latent_input_norm is not None:
+            z = self.latent_input_norm(z, ctx)
+        inner = z.shape[-1]
+        flat = z.reshape(bsz * t, inner)
         fmt = ctx.precision.of("experts")
         ec = c.expert
+        w_ffn, idx_ffn = weights, idx
+        if c.num_zero_experts:
+            # a zero expert is the token itself times its weight; its picks run no FFN (they
+            # are handed to a routed expert with weight 0, which leaves the sum unchanged)
+            if self.ep is not None:
+                raise NotImplementedError("moe: zero experts under expert parallelism")
+            is_zero = idx >= c.num_experts
+            w_ffn = torch.where(is_zero, torch.zeros_like(weights), weights)
+            idx_ffn = torch.where(is_zero, idx - c.num_experts, idx) % c.num_experts
         if self.ep is not None:
-            out = self.ep(self, flat, weights.reshape(bsz * t, -1), idx.reshape(bsz * t, -1), ctx, fmt)
+            if c.expert_norm is not None:
+                raise NotImplementedError("moe: expert_norm under expert parallelism")
+            out = self.ep(self, flat, w_ffn.reshape(bsz * t, -1), idx_ffn.reshape(bsz * t, -1), ctx, fmt)
+        elif c.expert_norm is not None:
+            # each expert's output is normalised before the weighted sum: the rows are
+            # needed one by one, so this runs the per-expert statement of the layer
+            out = ops.moe_reference(flat, self.experts_gate_up, self.experts_down,
+                                          w_ffn.reshape(bsz * t, -1), idx_ffn.reshape(bsz * t, -1),
+                                          ec.activation, ec.limit, ec.up_offset,
+                                          row_fn=lambda rows: self.expert_norm(rows, ctx))
         else:
             out = ops.moe_experts(flat, self.experts_gate_up, self.experts_down,
-                                  weights.reshape(bsz * t, -1), idx.reshape(bsz * t, -1),
+                                  w_ffn.reshape(bsz * t, -1), idx_ffn.reshape(bsz * t, -1),
                                   act=ec.activation, limit=ec.limit, up_offset=ec.up_offset, fmt=fmt)
-        out = out.view(bsz, t, d)
+        out = out.view(bsz, t, inner)
+        if c.num_zero_experts:
+            zero = torch.where(is_zero, weights, torch.zeros_like(weights)).sum(-1, keepdim=True)
+            out = out + (z.float() * zero).to(out.dtype)
+        if c.latent_output_norm is not None:
+            out = self.latent_output_norm(out, ctx)
+        if c.latent_size is not None:
+            out = self.from_latent(out, ctx)
         if c.num_shared_experts:
             shared = self.shared(x, ctx)
             if c.shared_expert_gate:

@@ -136,13 +136,14 @@ class _SortedExperts(torch.autograd.Function):
         else:
             xs = K.gather_rows(x, row_index, rows)
             h = K.grouped_gemm(xs, w_gu.view(e * f2, d), offsets, f2, d)
-        a = K.glu_fwd(h, act, None, limit, up_offset)
         if mx:
-            aq, asf, _, _ = K.quant_mxfp8(a)
+            # the activation is quantised as it is computed: no bf16 copy of it exists
+            aq, asf, _, _ = K.quant_mxfp8_glu(h, None, act, limit=limit, up_offset=up_offset)
             dq, dsf, _, _ = K.quant_mxfp8_batched(w_down.detach(), rowwise=True)
             y = K.grouped_gemm(aq, dq, offsets, d, f, kind=kind, asf=asf, bsf=dsf)
             del aq, asf, dq, dsf
         else:
+            a = K.glu_fwd(h, act, None, limit, up_offset)
             y = K.grouped_gemm(a, w_down.view(e * d, f), offsets, d, f)
         out = K.combine_rows(y, pos, wts, t)
         ctx.save_for_backward(x, w_gu, w_down, wts, row_index, pos, offsets, h, y)
@@ -161,12 +162,13 @@ class _SortedExperts(torch.autograd.Function):
         kind = K.KIND_MXFP8 if mx else K.KIND_BF16
         dy, dwts = K.combine_bwd(y, dout.contiguous(), pos, wts, rows)
         del y
-        a = K.glu_fwd(h, act, None, limit, up_offset)  # recomputed: cheaper than keeping it
         g_gu = getattr(w_gu, "main_grad", None)
         g_down = getattr(w_down, "main_grad", None)
         if mx:
             dyq, dysf, dytq, dytsf = K.quant_mxfp8(dy, rowwise=True, colwise=True)
-            _, _, atq, atsf = K.quant_mxfp8(a, rowwise=False, colwise=True)
+            # the activation is recomputed inside the quantiser (cheaper than keeping it)
+            _, _, atq, atsf = K.quant_mxfp8_glu(h, None, act, rowwise=False, colwise=True,
+                                                limit=limit, up_offset=up_offset)
             # dW_down[e] = dy_e^T · a_e
             dw_down = K.grouped_gemm_k(dytq, atq, offsets, d, f, kind=kind, asf=dytsf, bsf=atsf,
                                        out=g_down, accumulate=g_down is not None,
@@ -178,15 +180,20 @@ class _SortedExperts(torch.autograd.Function):
             da = K.grouped_gemm(dyq, tq, offsets, f, d, kind=kind, asf=dysf, bsf=tsf)
             del wdt, tq, tsf, dyq, dysf
         else:
+            a = K.glu_fwd(h, act, None, limit, up_offset)
             dw_down = K.grouped_gemm_k(dy, a, offsets, d, f, a_mn=True, b_mn=True, out=g_down,
                                        accumulate=g_down is not None,
                                      out_dtype=_grad_dtype(w_down))
             da = K.grouped_gemm(dy, w_down.view(e * d, f), offsets, f, d, b_mn=True)
-        del dy, a
-        dh, _ = K.glu_bwd(h, da, act, None, limit, up_offset)
-        del da
+            del a
+        del dy
         if mx:
+            # the gradient of h goes through bf16: computing it inside the quantiser
+            # (`quant_mxfp8_glu` with `dout`) measured slower than these two passes
+            dh, _ = K.glu_bwd(h, da, act, None, limit, up_offset)
+            del da
             hq, hsf, htq, htsf = K.quant_mxfp8(dh, rowwise=True, colwise=True)
+            del dh
             _, _, xtq, xtsf = K.quant_mxfp8(x, rowwise=False, colwise=True, row_index=row_index, rows=rows)
             dw_gu = K.grouped_gemm_k(htq, xtq, offsets, f2, d, kind=kind, asf=htsf, bsf=xtsf,
                                      out=g_gu, accumulate=g_gu is not None,
@@ -196,6 +203,8 @@ class _SortedExperts(torch.autograd.Function):
             tq, tsf, _, _ = K.quant_mxfp8_batched(wgt, rowwise=True)
             dxs = K.grouped_gemm(hq, tq, offsets, d, f2, kind=kind, asf=hsf, bsf=tsf)
         else:
+            dh, _ = K.glu_bwd(h, da, act, None, limit, up_offset)
+            del da
             xs = K.gather_rows(x, row_index, rows)
             dw_gu = K.grouped_gemm_k(dh, xs, offsets, f2, d, a_mn=True, b_mn=True, out=g_gu,
                                      accumulate=g_gu is not None,
@@ -222,8 +231,10 @@ def moe_experts(x, w_gate_up, w_down, weights, experts, *, act: str = "swish",
     return moe_reference(x, w_gate_up, w_down, weights, experts, act, limit, up_offset)
 
 
-def moe_reference(x, w_gate_up, w_down, weights, experts, act="swish", limit=None, up_offset=0.0):
-    """Differentiable plain-PyTorch experts: sort picks, one matmul pair per expert."""
+def moe_reference(x, w_gate_up, w_down, weights, experts, act="swish", limit=None, up_offset=0.0, row_fn=None):
+    """Differentiable plain-PyTorch experts: sort picks, one matmul pair per expert.
+    `row_fn` (optional) maps the experts' output rows before the weighted sum (a norm of
+    each expert's output)."""
     t, d = x.shape
     e, f2, _ = w_gate_up.shape
     f = f2 // 2
@@ -245,6 +256,8 @@ def moe_reference(x, w_gate_up, w_down, weights, experts, act="swish", limit=Non
         outs.append(a @ w_down[ex].to(seg.dtype).t())
         start += n
     ys = torch.cat(outs) if outs else xs.new_zeros(0, d)
+    if row_fn is not None and ys.shape[0]:
+        ys = row_fn(ys)
     wflat = weights.reshape(-1)[order].unsqueeze(-1)
     out = torch.zeros(t, d, dtype=torch.float32, device=x.device)
     out = out.index_add(0, tok, ys.float() * wflat.float())
@@ -282,13 +295,13 @@ class _ExpertsOnSorted(torch.autograd.Function):
         else:
             h = K.grouped_gemm(xs, w_gu.view(e * f2, d), offsets, f2, d, wait_flags=wf, wait_epoch=we)
             saved_x = (xs.clone(), None)
-        a = K.glu_fwd(h, act, None, limit, up_offset)
         y_out = io.y_out(rows, d) if io is not None else None
         if mx:
-            aq, asf, _, _ = K.quant_mxfp8(a)
+            aq, asf, _, _ = K.quant_mxfp8_glu(h, None, act, limit=limit, up_offset=up_offset)
             dq, dsf, _, _ = K.quant_mxfp8_batched(w_down.detach(), rowwise=True)
             y = K.grouped_gemm(aq, dq, offsets, d, f, kind=kind, asf=asf, bsf=dsf, out=y_out)
         else:
+            a = K.glu_fwd(h, act, None, limit, up_offset)
             y = K.grouped_gemm(a, w_down.view(e * d, f), offsets, d, f, out=y_out)
         if io is not None:
             io.after_forward()
@@ -308,12 +321,12 @@ class _ExpertsOnSorted(torch.autograd.Function):
             dy = io.before_backward(dy)
         if counts is not None:
             K.zero_pad_rows(dy, offsets, counts)
-        a = K.glu_fwd(h, act, None, limit, up_offset)
         g_gu = getattr(w_gu, "main_grad", None)
         g_down = getattr(w_down, "main_grad", None)
         if mx:
             dyq, dysf, dytq, dytsf = K.quant_mxfp8(dy, rowwise=True, colwise=True)
-            _, _, atq, atsf = K.quant_mxfp8(a, rowwise=False, colwise=True)
+            _, _, atq, atsf = K.quant_mxfp8_glu(h, None, act, rowwise=False, colwise=True,
+                                                limit=limit, up_offset=up_offset)
             dw_down = K.grouped_gemm_k(dytq, atq, offsets, d, f, kind=kind, asf=dytsf, bsf=atsf,
                                        out=g_down, accumulate=g_down is not None,
                                      out_dtype=_grad_dtype(w_down))
@@ -323,17 +336,19 @@ class _ExpertsOnSorted(torch.autograd.Function):
             da = K.grouped_gemm(dyq, tq, offsets, f, d, kind=kind, asf=dysf, bsf=tsf)
             del wdt, tq, tsf, dyq, dysf
         else:
+            a = K.glu_fwd(h, act, None, limit, up_offset)
             dw_down = K.grouped_gemm_k(dy, a, offsets, d, f, a_mn=True, b_mn=True, out=g_down,
                                        accumulate=g_down is not None,
                                      out_dtype=_grad_dtype(w_down))
             da = K.grouped_gemm(dy, w_down.view(e * d, f), offsets, f, d, b_mn=True)
-        del a
-        dh, _ = K.glu_bwd(h, da, act, None, limit, up_offset)
-        del da
-        rows = dh.shape[0]
+            del a
+        rows = h.shape[0]
         dx_out = io.dx_out(rows, d) if io is not None else None
         if mx:
+            dh, _ = K.glu_bwd(h, da, act, None, limit, up_offset)
+            del da
             hq, hsf, htq, htsf = K.quant_mxfp8(dh, rowwise=True, colwise=True)
+            del dh
             dw_gu = K.grouped_gemm_k(htq, xsave, offsets, f2, d, kind=kind, asf=htsf, bsf=xtsf,
                                      out=g_gu, accumulate=g_gu is not None,
                                      out_dtype=_grad_dtype(w_gu))
@@ -342,6 +357,8 @@ class _ExpertsOnSorted(torch.autograd.Function):
             tq, tsf, _, _ = K.quant_mxfp8_batched(wgt, rowwise=True)
             dxs = K.grouped_gemm(hq, tq, offsets, d, f2, kind=kind, asf=hsf, bsf=tsf, out=dx_out)
         else:
+            dh, _ = K.glu_bwd(h, da, act, None, limit, up_offset)
+            del da
             dw_gu = K.grouped_gemm_k(dh, xsave, offsets, f2, d, a_mn=True, b_mn=True, out=g_gu,
                                      accumulate=g_gu is not None,
                                      out_dtype=_grad_dtype(w_gu))

@@ -181,6 +181,30 @@ def quant_mxfp8(x: torch.Tensor, *, rowwise: bool = True, colwise: bool = False,
     return q_row, sf_row, q_col, sf_col
 
 
+def quant_mxfp8_glu(h: torch.Tensor, dout: Optional[torch.Tensor] = None, kind: str = "swish", *,
+                    rowwise: bool = True, colwise: bool = False, limit: float = 0.0, up_offset: float = 0.0):
+    """MXFP8 copies of glu(h) [R, f] (`dout` None), or of the gradient of h [R, 2f] for the
+    output gradient `dout` [R, f], computed from h [R, 2f] inside the quantiser: the bf16
+    activation (gradient) is never written. Same values as `quant_mxfp8(glu_fwd(h))` /
+    `quant_mxfp8(glu_bwd(h, dout))`. Returns (q_row, sf_row, q_col, sf_col)."""
+    r, f2 = h.shape
+    c = f2 if dout is not None else f2 // 2
+    dev = h.device
+    q_row = sf_row = q_col = sf_col = None
+    if rowwise:
+        q_row = torch.empty(r, c, dtype=torch.float8_e4m3fn, device=dev)
+        sf_row = torch.empty(sf_bytes(r, c), dtype=torch.uint8, device=dev)
+    r_pad = -(-r // 128) * 128
+    if colwise:
+        q_col = torch.empty(c, r_pad, dtype=torch.float8_e4m3fn, device=dev)
+        sf_col = torch.empty(sf_bytes(c, r_pad), dtype=torch.uint8, device=dev)
+    ops().quant_mxfp8_glu(h, dout, None if q_row is None else q_row.view(torch.uint8), sf_row,
+                          None if q_col is None else q_col.view(torch.uint8), sf_col, r_pad,
+                          ACT_KINDS[kind], float(limit), float(up_offset))
+    _count()
+    return q_row, sf_row, q_col, sf_col
+
+
 # ------------------------------------------------------------------ norms / rope / glu
 def rmsnorm_fwd(x, w, eps: float):
     y = torch.empty_like(x)

@@ -261,3 +261,30 @@ def test_attention_bwd(cuda, d, h, g, t, window, sinks):
     assert rel_err(dq, q.grad) < 3e-2
     if sinks:
         assert rel_err(dsk, sk.grad) < 3e-2
+
+
+@pytest.mark.parametrize("kind,limit,up_offset", [("swish", 0.0, 0.0), ("quick_gelu", 7.0, 1.0)])
+def test_quantiser_that_computes_the_gated_activation_matches_two_passes(kind, limit, up_offset):
+    """glu (and its gradient) computed inside the MXFP8 quantiser gives the bytes that the
+    separate activation kernel followed by the quantiser gives."""
+    from bux_b200.ops import kernels as K
+
+    torch.manual_seed(0)
+    rows, f = 1000, 256  # a ragged last row tile
+    h = (torch.randn(rows, 2 * f, device="cuda") * 3).bfloat16()
+    da = torch.randn(rows, f, device="cuda").bfloat16()
+    a = K.glu_fwd(h, kind, None, limit, up_offset)
+    want = K.quant_mxfp8(a, rowwise=True, colwise=True)
+    got = K.quant_mxfp8_glu(h, None, kind, rowwise=True, colwise=True, limit=limit, up_offset=up_offset)
+    for w, g in zip(want, got):
+        assert torch.equal(w.view(torch.uint8), g.view(torch.uint8))
+    dh, _ = K.glu_bwd(h, da, kind, None, limit, up_offset)
+    want = K.quant_mxfp8(dh, rowwise=True, colwise=True)
+    got = K.quant_mxfp8_glu(h, da, kind, rowwise=True, colwise=True, limit=limit, up_offset=up_offset)
+    for w, g in zip(want, got):
+        assert torch.equal(w.view(torch.uint8), g.view(torch.uint8))
+    # and against the fp32 statement of the op: the dequantised copy is close to glu(h)
+    ref_a = ref.glu(h[:, :f].float(), h[:, f:].float(), kind, limit or None, up_offset)
+    aq, asf, _, _ = K.quant_mxfp8_glu(h, None, kind, limit=limit, up_offset=up_offset)
+    back = ref.dequant_mxfp8(aq, ref.unswizzle_scales(asf, rows, f // 32))
+    assert rel_err(back, ref_a) < 0.04

@@ -1,0 +1,93 @@
+"""MoE variants on CPU: zero experts (LongCat-Flash), LatentMoE (Nemotron 3), expert_norm."""
+import torch
+
+from bux_b200.config import layers as L
+from bux_b200.lang import compile_runs
+from bux_b200.models.layers import moe as M
+from bux_b200.train.trainer import Trainer
+
+SRC = """
+d_model=32
+vocab_size=64
+n = rmsnorm
+a = gqa(num_heads=2, num_kv_heads=1, rope=rope())
+m = moe(num_experts=4, top_k=2, expert=gated_mlp(intermediate_size=16, activation=swish){options})
+block = [n a] [n m]
+model = embed block^2 n head
+data = synthetic
+optimizer = adamw(lr=1e-2)
+seq_len = 32
+batch = 2
+steps = 3
+precision = precision(compute=float32)
+"""
+
+
+def _train(options: str):
+    run = compile_runs(SRC.format(options=options), filename="x.bux")[0]
+    tr = Trainer(run, device="cpu")
+    batch = next(iter(tr.batches()))
+    losses = [tr.train_step(batch)["loss"].item() for _ in range(4)]
+    assert all(torch.isfinite(torch.tensor(losses))) and losses[-1] < losses[0]
+    return tr
+
+
+def _moes(tr):
+    return [m for m in tr.model.modules() if isinstance(m, M.MoE)]
+
+
+def test_zero_experts_pass_tokens_through():
+    tr = _train(", num_zero_experts=2, load_balancing=aux_free")
+    layer = _moes(tr)[0]
+    assert layer.router.weight.shape[0] == 6 and layer.router_bias.shape == (6,)
+    # a router that only ever picks zero experts makes the layer the identity times the weights' sum
+    with torch.no_grad():
+        layer.router.weight.zero_()
+        layer.router_bias.copy_(torch.tensor([0.0, 0, 0, 0, 9, 9]))
+    from bux_b200.models.registry import Context
+
+    x = torch.randn(2, 8, 32)
+    ctx = Context(torch.zeros(2, 8, dtype=torch.long))
+    out = layer(x, ctx)
+    assert torch.allclose(out, x, atol=1e-5)  # normalised top-k weights of the two zero experts sum to 1
+
+
+def test_zero_experts_balance_by_their_budget():
+    c = L.MoEConfig(num_experts=4, top_k=2, num_zero_experts=4, load_balancing="aux_free",
+                    expert=L.MLPConfig(type="gated_mlp", intermediate_size=8, activation="swish"))
+    assert c.ffn_budget == 1.0
+    scores = torch.full((1, 4, 8), 1 / 8)
+    picks = torch.zeros(1, 4, 8)
+    picks[:, :, :4] = 0.25  # each FFN expert a quarter of a pick per token: one FFN pick a token
+    picks[:, :, 4:] = 0.25  # and one zero pick
+    assert torch.allclose(M.budget_loss(scores, picks, c, False), torch.tensor(1.0))
+    load = torch.tensor([10.0, 30, 20, 20, 5, 5, 5, 5])
+    move = M.budget_move(load, c)
+    target = 1.0 * 100 / (2 * 4)
+    assert torch.allclose(move[:4], c.bias_update_rate * (1 - load[:4] / target))
+    assert move[4:].abs().sum() == 0
+
+
+def test_latent_moe_runs_experts_in_a_narrower_space():
+    tr = _train(", latent_size=16, latent_input_norm=rmsnorm, latent_output_norm=rmsnorm, num_shared_experts=1")
+    layer = _moes(tr)[0]
+    assert layer.experts_gate_up.shape == (4, 32, 16) and layer.experts_down.shape == (4, 16, 16)
+    assert layer.to_latent.weight.shape == (16, 32) and layer.from_latent.weight.shape == (32, 16)
+    assert layer.shared.down.weight.shape[0] == 32  # shared experts see the full width
+
+
+def test_expert_norm_normalises_each_experts_output():
+    tr = _train(", expert_norm=rmsnorm")
+    layer = _moes(tr)[0]
+    assert layer.expert_norm.scale.grad is not None or layer.expert_norm.scale.requires_grad
+    # with top_k = 1 and weight 1 the output rows have unit RMS (gain 1)
+    from bux_b200.models.registry import Context
+
+    c = layer.c.model_copy(update={"top_k": 1})
+    layer.c = c
+    with torch.no_grad():
+        layer.expert_norm.scale.fill_(1.0)
+        layer.experts_down.mul_(100.0)  # outputs far above the norm's eps
+    x = torch.randn(2, 8, 32)
+    out = layer(x, Context(torch.zeros(2, 8, dtype=torch.long)))
+    assert torch.allclose(out.float().pow(2).mean(-1).sqrt(), torch.ones(2, 8), atol=1e-3)
