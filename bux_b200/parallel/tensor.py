@@ -192,6 +192,9 @@ def shard_model(model: nn.Module, par) -> None:
         if isinstance(m, GQA):
             _need(m.h % n == 0 and m.g % n == 0, f"{m.h} heads / {m.g} kv heads do not divide by tensor={n}")
             _need(not (m.c.qk_norm is not None and m.c.qk_norm_all_heads), "qk_norm over all heads is not split")
+            extras = [name for name in ("lambda_proj", "xsa_alpha", "k_conv", "rel_proj", "gate_up", "gate_bias",
+                                        "output_gate_down", "cross_gate", "ve_gate", "v_norm") if hasattr(m, name)]
+            _need(not extras, f"gqa with {', '.join(extras)} is not split over tensor ranks yet")
             pieces = [m.q_rows, m.k_rows, m.v_rows]
             split(m.qkv, "weight", 0, pieces, r, n, layout)
             split(m.qkv, "bias", 0, pieces, r, n, layout)
@@ -202,7 +205,7 @@ def shard_model(model: nn.Module, par) -> None:
                 split(m.gate, "weight", 0, [m.gate.weight.shape[0]], r, n, layout)
                 split(m.gate, "bias", 0, [m.gate.weight.shape[0] * n], r, n, layout)
             split(m, "sinks", 0, [m.h], r, n, layout)
-            m.h, m.g = m.h // n, m.g // n
+            m.h, m.g, m.hq = m.h // n, m.g // n, m.hq // n
             m.q_rows, m.k_rows, m.v_rows = m.q_rows // n, m.k_rows // n, m.v_rows // n
             for name in ("q_norm", "k_norm", "out_norm"):
                 if hasattr(m, name):
