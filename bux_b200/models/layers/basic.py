@@ -170,6 +170,7 @@ class HeadOutput:
 
     def __init__(self, hidden, weight, bias=None, softcap=None, name="head"):
         self.hidden, self.weight, self.bias, self.softcap, self.name = hidden, weight, bias, softcap, name
+        self.pointer = None  # a copy pointer's view (`layers.pointer.PointerView`): the loss is then the mixture's
 
     def logits(self) -> torch.Tensor:
         out = nn.functional.linear(self.hidden, self.weight.to(self.hidden.dtype),
@@ -192,12 +193,19 @@ class Head(nn.Module):
             self.proj = Linear(b.width if isinstance(b.width, int) else b.d_model, b.vocab_size,
                                False, b, role="head", init_role="head")
         self.bias = nn.Parameter(torch.zeros(b.vocab_size)) if c.bias else None
+        if c.pointer is not None:
+            from .pointer import CopyPointer
+
+            self.pointer = CopyPointer(c.pointer, b.width if isinstance(b.width, int) else b.d_model,
+                                       b.vocab_size, b)
 
     def matrix(self) -> torch.Tensor:
         return self.tied_to.tokens.embedding if self.tied_to is not None else self.proj.weight
 
     def forward(self, x, ctx: Context):
         out = HeadOutput(x, self.matrix(), self.bias, self.c.softcap, name=f"head{len(ctx.heads)}")
+        if hasattr(self, "pointer") and not ctx.heads:  # the pass's first head carries the pointer
+            out.pointer = self.pointer(x, ctx)
         ctx.heads.append(out)
         return x  # the stream goes on (multi-token prediction stacks more heads after it)
 

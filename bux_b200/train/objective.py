@@ -57,6 +57,12 @@ def compute(ctx, batch, loss_cfg: T.LossConfig, span=None) -> LossParts:
         if span is not None:
             tgt, mask = tgt[:, span[0]:span[1]], mask[:, span[0]:span[1]]
         h = head.hidden.reshape(-1, head.hidden.shape[-1])
+        if getattr(head, "pointer", None) is not None:
+            if span is not None:
+                raise NotImplementedError("a copy pointer with positions split over ranks")
+            ce0, count0 = head.pointer.sums(head, tgt, mask, loss_cfg.z)
+            total = total + ce0
+            continue
         s, n = ops.cross_entropy_head(h, head.weight, tgt.reshape(-1), mask.reshape(-1).float(),
                                       bias=head.bias, z_weight=loss_cfg.z if k == 0 else 0.0,
                                       softcap=head.softcap)
