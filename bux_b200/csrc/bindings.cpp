@@ -128,7 +128,8 @@ void glu_bwd(const Tensor& h, const Tensor& dout, Tensor& dh, const c10::optiona
 }
 
 // ------------------------------------------------------------------ MXFP8 quantiser
-void quant_mxfp8(const Tensor& x, const c10::optional<Tensor>& row_index, const c10::optional<Tensor>& q_row,
+void quant_mxfp8(const Tensor& x, const c10::optional<Tensor>& row_index, const c10::optional<Tensor>& row_scale,
+                 const c10::optional<Tensor>& q_row,
                  const c10::optional<Tensor>& sf_row, const c10::optional<Tensor>& q_col,
                  const c10::optional<Tensor>& sf_col, int64_t rows, int64_t cols, int64_t ld_col,
                  int64_t batch, int64_t x_batch_stride) {
@@ -140,7 +141,7 @@ void quant_mxfp8(const Tensor& x, const c10::optional<Tensor>& row_index, const 
   uint8_t* qc = q_col.has_value() ? reinterpret_cast<uint8_t*>(q_col->data_ptr()) : nullptr;
   uint8_t* sc = sf_col.has_value() ? reinterpret_cast<uint8_t*>(sf_col->data_ptr()) : nullptr;
   TORCH_CHECK(qc == nullptr || ld_col % 32 == 0, "quant: transposed copy needs a row count padded to 32");
-  bux::quant_mxfp8(x.data_ptr(), x.stride(-2), opt_i32(row_index), qr, sr, qc, sc, rows, (int)cols, ld_col, (int)batch, x_batch_stride, stream_of(x));
+  bux::quant_mxfp8(x.data_ptr(), x.stride(-2), opt_i32(row_index), opt_f32(row_scale), qr, sr, qc, sc, rows, (int)cols, ld_col, (int)batch, x_batch_stride, stream_of(x));
 }
 
 void quant_mxfp8_glu(const Tensor& h, const c10::optional<Tensor>& dout, const c10::optional<Tensor>& q_row,
@@ -202,12 +203,12 @@ void gather_rows(const Tensor& x, const Tensor& index, Tensor& out) {
   bux::gather_rows(x.data_ptr(), index.data_ptr<int>(), out.data_ptr(), out.size(0), (int)out.size(1), stream_of(x));
 }
 void combine_bwd(const c10::optional<Tensor>& y, const Tensor& dout, const Tensor& pos, const c10::optional<Tensor>& w,
-                 Tensor& dy, const c10::optional<Tensor>& dw) {
-  check_cuda(dout, "dout"); check_cuda(dy, "dy");
+                 const c10::optional<Tensor>& dy, const c10::optional<Tensor>& dw) {
+  check_cuda(dout, "dout");
   c10::cuda::CUDAGuard guard(dout.device());
   const void* yp = y.has_value() ? y->data_ptr() : nullptr;
   float* dwp = (dw.has_value() && yp) ? dw->data_ptr<float>() : nullptr;
-  bux::combine_bwd(yp, dout.data_ptr(), pos.data_ptr<int>(), opt_f32(w), dy.data_ptr(), dwp, pos.numel(), (int)pos.size(1), (int)dout.size(1), stream_of(dout));
+  bux::combine_bwd(yp, dout.data_ptr(), pos.data_ptr<int>(), opt_f32(w), dy.has_value() ? dy->data_ptr() : nullptr, dwp, pos.numel(), (int)pos.size(1), (int)dout.size(1), stream_of(dout));
 }
 void combine_rows(const Tensor& y, const Tensor& pos, const c10::optional<Tensor>& w, Tensor& out) {
   check_cuda(y, "y"); check_cuda(out, "out");
@@ -327,13 +328,13 @@ TORCH_LIBRARY(bux_b200, m) {
   m.def("norm_rope(bool bwd, Tensor x, Tensor? w, Tensor cos, Tensor sin, Tensor(a!) y, Tensor? rstd, Tensor? dy, Tensor? dw, int tokens, int heads, int D, int stride_x, int stride_y, float eps) -> ()", &norm_rope);
   m.def("glu_fwd(Tensor h, Tensor(a!) out, Tensor? row_scale, int kind, float limit, float up_offset) -> ()", &glu_fwd);
   m.def("glu_bwd(Tensor h, Tensor dout, Tensor(a!) dh, Tensor? row_scale, Tensor? d_row_scale, int kind, float limit, float up_offset) -> ()", &glu_bwd);
-  m.def("quant_mxfp8(Tensor x, Tensor? row_index, Tensor? q_row, Tensor? sf_row, Tensor? q_col, Tensor? sf_col, int rows, int cols, int ld_col, int batch, int x_batch_stride) -> ()", &quant_mxfp8);
+  m.def("quant_mxfp8(Tensor x, Tensor? row_index, Tensor? row_scale, Tensor? q_row, Tensor? sf_row, Tensor? q_col, Tensor? sf_col, int rows, int cols, int ld_col, int batch, int x_batch_stride) -> ()", &quant_mxfp8);
   m.def("quant_mxfp8_glu(Tensor h, Tensor? dout, Tensor? q_row, Tensor? sf_row, Tensor? q_col, Tensor? sf_col, int ld_col, int kind, float limit, float up_offset) -> ()", &quant_mxfp8_glu);
   m.def("ce_fwd_bwd(Tensor(a!) logits, Tensor targets, Tensor? mask, Tensor(b!) loss, Tensor? logz, float grad_scale, float z_weight, float softcap) -> ()", &ce_fwd_bwd);
   m.def("adamw(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor? m_sf, Tensor? v_sf, Tensor? shadow, Tensor? grad_scale, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2, float grad_scale_const) -> ()", &adamw);
   m.def("sumsq(Tensor g, Tensor(a!) out) -> ()", &sumsq);
   m.def("gather_rows(Tensor x, Tensor index, Tensor(a!) out) -> ()", &gather_rows);
-  m.def("combine_bwd(Tensor? y, Tensor dout, Tensor pos, Tensor? w, Tensor(a!) dy, Tensor? dw) -> ()", &combine_bwd);
+  m.def("combine_bwd(Tensor? y, Tensor dout, Tensor pos, Tensor? w, Tensor(a!)? dy, Tensor(b!)? dw) -> ()", &combine_bwd);
   m.def("combine_rows(Tensor y, Tensor pos, Tensor? w, Tensor(a!) out) -> ()", &combine_rows);
   m.def("attn_fwd(Tensor q, Tensor k, Tensor v, Tensor(a!) o, Tensor(b!) lse, Tensor? sinks, Tensor? status, float scale, bool causal, int window) -> ()", &attn_fwd);
   m.def("attn_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor d_o, Tensor lse, Tensor(a!) dq, Tensor(b!) dk, Tensor(c!) dv, Tensor(d!) delta, Tensor? sinks, Tensor? dsinks, Tensor? status, float scale, bool causal, int window) -> ()", &attn_bwd);

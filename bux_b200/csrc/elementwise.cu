@@ -322,7 +322,14 @@ __device__ __forceinline__ size_t sf_offset(long i, int j, int sf_cols_padded) {
 //   q_row [R, C] e4m3, sf_row tiles over (R, C/32);  q_col [C, R_pad] e4m3 (R_pad = ld_col),
 //   sf_col tiles over (C, R_pad/32).
 constexpr int QT = 128;
-constexpr int QPITCH = 136;
+// The 128×128 bf16 tile sits in shared memory without padding, its 16-byte chunks (8 columns)
+// XOR-swizzled by the row, so that three access patterns are all free of bank conflicts:
+// eight consecutive chunks of a row (the load), one chunk of eight consecutive rows (the
+// row-wise pass) and one chunk of rows {8a + 2m + b} (the transposing ldmatrix of the column pass).
+__device__ __forceinline__ int qtile_at(int row, int chunk) {
+  const int g = ((((row >> 3) ^ (row >> 1)) & 3) << 1) | (row & 1);
+  return row * QT + ((chunk ^ g) << 3);
+}
 
 __device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d) {
   const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
@@ -337,6 +344,7 @@ __device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float 
 #endif
 enum { QSRC_PLAIN = 0, QSRC_GLU_FWD = 1, QSRC_GLU_BWD = 2 };
 struct QuantGlu {
+  const float* row_scale;     // PLAIN: output row r is its source row times row_scale[r] (rounded to bf16)
   const __nv_bfloat16* dout;  // GLU_BWD: gradient of the activation's output [rows, f]
   int f;                      // h is [rows, 2f]: gate columns, then up columns
   int kind;
@@ -393,7 +401,7 @@ quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long ld_x,
                    long rows, int cols, long ld_col, long x_batch_stride, QuantGlu gp) {
   // Registers are kept low (values are re-read from the shared tile rather than held) so
   // that six blocks fit an SM: the kernel is a stream, and blocks in flight hide its latency.
-  __shared__ __align__(16) __nv_bfloat16 tile[QT][QPITCH];
+  __shared__ __align__(128) __nv_bfloat16 tile[QT * QT];
   __shared__ __align__(16) uint8_t sfr[512];
   __shared__ __align__(16) uint8_t sfc[512];
   const int sf_cols_row = ((cols / 32) + 3) & ~3;
@@ -419,12 +427,22 @@ quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long ld_x,
         long src = r;
         if (row_index && r < rows) src = row_index[r];
         v[i] = make_uint4(0, 0, 0, 0);
-        if (r < rows && src >= 0 && c0 + cc < cols)
+        if (r < rows && src >= 0 && c0 + cc < cols) {
           v[i] = *reinterpret_cast<const uint4*>(x + src * ld_x + c0 + cc);
+          if (gp.row_scale) {
+            const float rs = gp.row_scale[r];
+            uint32_t* u = &v[i].x;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 t = unpack_bf16(u[j]);
+              u[j] = pack_bf16(t.x * rs, t.y * rs);
+            }
+          }
+        }
       }
 #pragma unroll
       for (int i = 0; i < 4; ++i)
-        *reinterpret_cast<uint4*>(&tile[(base + i) * 16 + (tid >> 4)][cc]) = v[i];
+        *reinterpret_cast<uint4*>(&tile[qtile_at((base + i) * 16 + (tid >> 4), tid & 15)]) = v[i];
     }
   } else {
     // the tile is computed from h (and dout), two rows' loads in flight per thread.
@@ -451,7 +469,7 @@ quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long ld_x,
         uint4 o = make_uint4(0, 0, 0, 0);
         if (r < rows && c0 + cc < cols)
           o = SRC == QSRC_GLU_FWD ? glu_fwd8(g[i], u[i], gp) : glu_bwd8(g[i], u[i], d[i], up_half, gp);
-        *reinterpret_cast<uint4*>(&tile[(base + i) * 16 + (tid >> 4)][cc]) = o;
+        *reinterpret_cast<uint4*>(&tile[qtile_at((base + i) * 16 + (tid >> 4), tid & 15)]) = o;
       }
     }
   }
@@ -465,7 +483,7 @@ quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long ld_x,
       const int cb = (tid >> 7) + 2 * i;
       uint4 w[4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) w[k] = *reinterpret_cast<const uint4*>(&tile[rr][cb * 32 + k * 8]);
+      for (int k = 0; k < 4; ++k) w[k] = *reinterpret_cast<const uint4*>(&tile[qtile_at(rr, cb * 4 + k)]);
       float amax = 0.f;
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
@@ -498,38 +516,35 @@ quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long ld_x,
     }
   }
   if (q_col) {
-    // thread -> columns 2*(tid % 64) and +1, 32-row block tid / 64: one scale block each.
-    // One pass over the tile for both maxima, one per column to convert.
-    const int cp = tid & 63, rb = tid >> 6;
-    float amax0 = 0.f, amax1 = 0.f;
-#pragma unroll 8
-    for (int j = 0; j < 32; ++j) {
-      const float2 t = unpack_bf16(*reinterpret_cast<const uint32_t*>(&tile[rb * 32 + j][2 * cp]));
-      amax0 = fmaxf(amax0, fabsf(t.x));
-      amax1 = fmaxf(amax1, fabsf(t.y));
-    }
-#pragma unroll 1
-    for (int half = 0; half < 2; ++half) {
-      const int ccol = 2 * cp + half;
-      const int c = c0 + ccol;
-      const bool live = c < cols;
-      const uint8_t e = e8m0_of(half ? amax1 : amax0);
+    // A warp takes 8 columns × 32 rows at a time: one transposing ldmatrix hands each thread
+    // eight consecutive rows of one column (thread = column t/4, rows 8·(t%4)..+7), the four
+    // threads of a column share the block's maximum by two shuffles, and each writes 8 bytes.
+    const int warp = tid >> 5, lane = tid & 31;
+    const int m = lane >> 3, i = lane & 7;  // this lane addresses row i of matrix m
+    const int col = lane >> 2, q = lane & 3;
+#pragma unroll 2
+    for (int task = 0; task < 8; ++task) {
+      const int cg = warp * 2 + (task >> 2), rb = task & 3;
+      const int src_row = rb * 32 + 8 * (i >> 1) + 2 * m + (i & 1);
+      const uint32_t addr = (uint32_t)__cvta_generic_to_shared(&tile[qtile_at(src_row, cg)]);
+      uint32_t w0, w1, w2, w3;
+      asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "r"(addr));
+      const float2 a = unpack_bf16(w0), b = unpack_bf16(w1), c = unpack_bf16(w2), d = unpack_bf16(w3);
+      float amax = fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y))),
+                         fmaxf(fmaxf(fabsf(c.x), fabsf(c.y)), fmaxf(fabsf(d.x), fabsf(d.y))));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      const int ccol = cg * 8 + col;
+      const bool live = c0 + ccol < cols;
+      const uint8_t e = e8m0_of(amax);
       const float inv = e8m0_inv(e);
-      sfc[(ccol & 31) * 16 + (ccol >> 5) * 4 + rb] = live ? e : (uint8_t)127;
+      if (q == 0) sfc[(ccol & 31) * 16 + (ccol >> 5) * 4 + rb] = live ? e : (uint8_t)127;
       if (live) {
-        uint4* dst = reinterpret_cast<uint4*>(q_col + (size_t)c * ld_col + r0 + rb * 32);
-#pragma unroll
-        for (int hv = 0; hv < 2; ++hv) {
-          uint32_t packed[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int row = rb * 32 + hv * 16 + 4 * j;
-            const __nv_bfloat16* col = &tile[row][ccol];
-            packed[j] = cvt_e4m3x4(__bfloat162float(col[0]) * inv, __bfloat162float(col[QPITCH]) * inv,
-                                   __bfloat162float(col[2 * QPITCH]) * inv, __bfloat162float(col[3 * QPITCH]) * inv);
-          }
-          dst[hv] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-        }
+        uint2 out;
+        out.x = cvt_e4m3x4(a.x * inv, a.y * inv, b.x * inv, b.y * inv);
+        out.y = cvt_e4m3x4(c.x * inv, c.y * inv, d.x * inv, d.y * inv);
+        *reinterpret_cast<uint2*>(q_col + (size_t)(c0 + ccol) * ld_col + r0 + rb * 32 + 8 * q) = out;
       }
     }
   }
@@ -851,7 +866,7 @@ __global__ void combine_bwd_kernel(const __nv_bfloat16* __restrict__ y, const __
         dot += gf.x * yf.x + gf.y * yf.y;
         ou[q] = pack_bf16(gf.x * ww, gf.y * ww);
       }
-      reinterpret_cast<uint4*>(dy + (long)r * d)[c] = o;
+      if (dy) reinterpret_cast<uint4*>(dy + (long)r * d)[c] = o;
     }
     if (dw) {
       dot = warp_sum(dot);
@@ -898,17 +913,17 @@ void glu_fwd(const void* h, void* out, const float* row_scale, long rows, int f,
 void glu_bwd(const void* h, const void* dout, void* dh, const float* row_scale, float* d_row_scale, long rows, int f, int kind, float limit, float up_offset, cudaStream_t s) {
   glu_bwd_kernel<<<grid_for(rows * (f / 8), 256), 256, 0, s>>>((const __nv_bfloat16*)h, (const __nv_bfloat16*)dout, (__nv_bfloat16*)dh, row_scale, d_row_scale, rows, f, kind, limit, up_offset);
 }
-void quant_mxfp8(const void* x, long ld_x, const int* row_index, uint8_t* q_row, uint8_t* sf_row, uint8_t* q_col, uint8_t* sf_col, long rows, int cols, long ld_col, int batch, long x_batch_stride, cudaStream_t s) {
+void quant_mxfp8(const void* x, long ld_x, const int* row_index, const float* row_scale, uint8_t* q_row, uint8_t* sf_row, uint8_t* q_col, uint8_t* sf_col, long rows, int cols, long ld_col, int batch, long x_batch_stride, cudaStream_t s) {
   const long extent = q_col ? (ld_col > rows ? ld_col : rows) : rows;  // the transposed copy is padded to ld_col
   dim3 grid((cols + 127) / 128, (unsigned)((extent + 127) / 128), batch);
-  quant_mxfp8_kernel<QSRC_PLAIN><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, ld_x, row_index, q_row, sf_row, q_col, sf_col, rows, cols, ld_col, x_batch_stride, QuantGlu{});
+  quant_mxfp8_kernel<QSRC_PLAIN><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, ld_x, row_index, q_row, sf_row, q_col, sf_col, rows, cols, ld_col, x_batch_stride, QuantGlu{row_scale, nullptr, 0, 0, 0.f, 0.f});
 }
 void quant_mxfp8_glu(const void* h, const void* dout, uint8_t* q_row, uint8_t* sf_row, uint8_t* q_col, uint8_t* sf_col,
                      long rows, int f, long ld_col, int kind, float limit, float up_offset, cudaStream_t s) {
   const int cols = dout ? 2 * f : f;
   const long extent = q_col ? (ld_col > rows ? ld_col : rows) : rows;
   dim3 grid((cols + 127) / 128, (unsigned)((extent + 127) / 128), 1);
-  QuantGlu gp{(const __nv_bfloat16*)dout, f, kind, limit, up_offset};
+  QuantGlu gp{nullptr, (const __nv_bfloat16*)dout, f, kind, limit, up_offset};
   if (dout) quant_mxfp8_kernel<QSRC_GLU_BWD><<<grid, 256, 0, s>>>((const __nv_bfloat16*)h, 2L * f, nullptr, q_row, sf_row, q_col, sf_col, rows, cols, ld_col, 0, gp);
   else quant_mxfp8_kernel<QSRC_GLU_FWD><<<grid, 256, 0, s>>>((const __nv_bfloat16*)h, 2L * f, nullptr, q_row, sf_row, q_col, sf_col, rows, cols, ld_col, 0, gp);
 }

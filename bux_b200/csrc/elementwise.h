@@ -16,7 +16,7 @@ const char* norm_rope(bool bwd, const void* x, const float* w, const float* cs, 
                       long stride_x, long stride_y, float eps, cudaStream_t s);
 void glu_fwd(const void* h, void* out, const float* row_scale, long rows, int f, int kind, float limit, float up_offset, cudaStream_t s);
 void glu_bwd(const void* h, const void* dout, void* dh, const float* row_scale, float* d_row_scale, long rows, int f, int kind, float limit, float up_offset, cudaStream_t s);
-void quant_mxfp8(const void* x, long ld_x, const int* row_index, uint8_t* q_row, uint8_t* sf_row, uint8_t* q_col, uint8_t* sf_col, long rows, int cols, long ld_col, int batch, long x_batch_stride, cudaStream_t s);
+void quant_mxfp8(const void* x, long ld_x, const int* row_index, const float* row_scale, uint8_t* q_row, uint8_t* sf_row, uint8_t* q_col, uint8_t* sf_col, long rows, int cols, long ld_col, int batch, long x_batch_stride, cudaStream_t s);
 // Quantise glu(h) [rows, f] (dout null) or the gradient of h [rows, 2f] given dout [rows, f],
 // computed tile by tile from h [rows, 2f]; f % 128 == 0 for the gradient.
 void quant_mxfp8_glu(const void* h, const void* dout, uint8_t* q_row, uint8_t* sf_row, uint8_t* q_col, uint8_t* sf_col,

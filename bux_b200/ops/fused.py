@@ -128,11 +128,14 @@ class _SortedExperts(torch.autograd.Function):
         row_index, pos, offsets = sort_picks(experts, e)
         rows = row_index.numel()
         wts = weights.float().contiguous()
+        xtq = xtsf = None
         if mx:
-            xq, xsf, _, _ = K.quant_mxfp8(x, row_index=row_index, rows=rows)
+            # with a backward to come, the transposed copy for dW is written in the same pass
+            xq, xsf, xtq, xtsf = K.quant_mxfp8(x, row_index=row_index, rows=rows,
+                                               colwise=any(ctx.needs_input_grad))
             gq, gsf, _, _ = K.quant_mxfp8_batched(w_gu.detach(), rowwise=True)
             h = K.grouped_gemm(xq, gq, offsets, f2, d, kind=kind, asf=xsf, bsf=gsf)
-            del gq, gsf
+            del xq, xsf, gq, gsf
         else:
             xs = K.gather_rows(x, row_index, rows)
             h = K.grouped_gemm(xs, w_gu.view(e * f2, d), offsets, f2, d)
@@ -146,26 +149,36 @@ class _SortedExperts(torch.autograd.Function):
             a = K.glu_fwd(h, act, None, limit, up_offset)
             y = K.grouped_gemm(a, w_down.view(e * d, f), offsets, d, f)
         out = K.combine_rows(y, pos, wts, t)
-        ctx.save_for_backward(x, w_gu, w_down, wts, row_index, pos, offsets, h, y)
+        ctx.save_for_backward(x, w_gu, w_down, wts, row_index, pos, offsets, h, y, xtq, xtsf)
         ctx.cfg = (act, limit, up_offset, mx)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         K = _K()
-        x, w_gu, w_down, wts, row_index, pos, offsets, h, y = ctx.saved_tensors
+        x, w_gu, w_down, wts, row_index, pos, offsets, h, y, xtq, xtsf = ctx.saved_tensors
         act, limit, up_offset, mx = ctx.cfg
         t, d = x.shape
         e, f2, _ = w_gu.shape
         f = f2 // 2
         rows = row_index.numel()
         kind = K.KIND_MXFP8 if mx else K.KIND_BF16
-        dy, dwts = K.combine_bwd(y, dout.contiguous(), pos, wts, rows)
+        dout = dout.contiguous()
+        if mx:
+            # dy[r] = w[r]·dout[token(r)] is formed inside the quantiser (a row gather with a
+            # scale), so the bf16 gradient of the experts' rows is never written
+            dwts = K.combine_dots(y, dout, pos)
+            w_row = torch.zeros(rows, dtype=torch.float32, device=dout.device)
+            w_row[pos.reshape(-1).long()] = wts.reshape(-1)
+            dy = None
+        else:
+            dy, dwts = K.combine_bwd(y, dout, pos, wts, rows)
         del y
         g_gu = getattr(w_gu, "main_grad", None)
         g_down = getattr(w_down, "main_grad", None)
         if mx:
-            dyq, dysf, dytq, dytsf = K.quant_mxfp8(dy, rowwise=True, colwise=True)
+            dyq, dysf, dytq, dytsf = K.quant_mxfp8(dout, rowwise=True, colwise=True, row_index=row_index,
+                                                   rows=rows, row_scale=w_row)
             # the activation is recomputed inside the quantiser (cheaper than keeping it)
             _, _, atq, atsf = K.quant_mxfp8_glu(h, None, act, rowwise=False, colwise=True,
                                                 limit=limit, up_offset=up_offset)
@@ -175,10 +188,10 @@ class _SortedExperts(torch.autograd.Function):
                                      out_dtype=_grad_dtype(w_down))
             del dytq, dytsf, atq, atsf
             # da = dy · W_down  (per expert, contraction over d): B = W_down^T rows [f, d]
-            wdt = w_down.detach().transpose(1, 2).contiguous()
-            tq, tsf, _, _ = K.quant_mxfp8_batched(wdt, rowwise=True)
+            # W_down[e]^T quantised along d: the transposed copy the quantiser writes anyway
+            _, _, tq, tsf = K.quant_mxfp8_batched(w_down.detach(), rowwise=False, colwise=True)
             da = K.grouped_gemm(dyq, tq, offsets, f, d, kind=kind, asf=dysf, bsf=tsf)
-            del wdt, tq, tsf, dyq, dysf
+            del tq, tsf, dyq, dysf
         else:
             a = K.glu_fwd(h, act, None, limit, up_offset)
             dw_down = K.grouped_gemm_k(dy, a, offsets, d, f, a_mn=True, b_mn=True, out=g_down,
@@ -194,13 +207,13 @@ class _SortedExperts(torch.autograd.Function):
             del da
             hq, hsf, htq, htsf = K.quant_mxfp8(dh, rowwise=True, colwise=True)
             del dh
-            _, _, xtq, xtsf = K.quant_mxfp8(x, rowwise=False, colwise=True, row_index=row_index, rows=rows)
+            if xtq is None:
+                _, _, xtq, xtsf = K.quant_mxfp8(x, rowwise=False, colwise=True, row_index=row_index, rows=rows)
             dw_gu = K.grouped_gemm_k(htq, xtq, offsets, f2, d, kind=kind, asf=htsf, bsf=xtsf,
                                      out=g_gu, accumulate=g_gu is not None,
                                      out_dtype=_grad_dtype(w_gu))
             del htq, htsf, xtq, xtsf
-            wgt = w_gu.detach().transpose(1, 2).contiguous()  # [E, d, 2f]
-            tq, tsf, _, _ = K.quant_mxfp8_batched(wgt, rowwise=True)
+            _, _, tq, tsf = K.quant_mxfp8_batched(w_gu.detach(), rowwise=False, colwise=True)  # [E*d, 2f]
             dxs = K.grouped_gemm(hq, tq, offsets, d, f2, kind=kind, asf=hsf, bsf=tsf)
         else:
             dh, _ = K.glu_bwd(h, da, act, None, limit, up_offset)
@@ -331,10 +344,10 @@ class _ExpertsOnSorted(torch.autograd.Function):
                                        out=g_down, accumulate=g_down is not None,
                                      out_dtype=_grad_dtype(w_down))
             del dytq, dytsf, atq, atsf
-            wdt = w_down.detach().transpose(1, 2).contiguous()
-            tq, tsf, _, _ = K.quant_mxfp8_batched(wdt, rowwise=True)
+            # W_down[e]^T quantised along d: the transposed copy the quantiser writes anyway
+            _, _, tq, tsf = K.quant_mxfp8_batched(w_down.detach(), rowwise=False, colwise=True)
             da = K.grouped_gemm(dyq, tq, offsets, f, d, kind=kind, asf=dysf, bsf=tsf)
-            del wdt, tq, tsf, dyq, dysf
+            del tq, tsf, dyq, dysf
         else:
             a = K.glu_fwd(h, act, None, limit, up_offset)
             dw_down = K.grouped_gemm_k(dy, a, offsets, d, f, a_mn=True, b_mn=True, out=g_down,
@@ -353,8 +366,7 @@ class _ExpertsOnSorted(torch.autograd.Function):
                                      out=g_gu, accumulate=g_gu is not None,
                                      out_dtype=_grad_dtype(w_gu))
             del htq, htsf
-            wgt = w_gu.detach().transpose(1, 2).contiguous()
-            tq, tsf, _, _ = K.quant_mxfp8_batched(wgt, rowwise=True)
+            _, _, tq, tsf = K.quant_mxfp8_batched(w_gu.detach(), rowwise=False, colwise=True)  # [E*d, 2f]
             dxs = K.grouped_gemm(hq, tq, offsets, d, f2, kind=kind, asf=hsf, bsf=tsf, out=dx_out)
         else:
             dh, _ = K.glu_bwd(h, da, act, None, limit, up_offset)

@@ -151,17 +151,19 @@ def quant_mxfp8_batched(x: torch.Tensor, *, rowwise: bool = True, colwise: bool 
         q_col = torch.empty(e * c, r, dtype=torch.float8_e4m3fn, device=dev)
         sf_col = torch.empty(e * sf_bytes(c, r), dtype=torch.uint8, device=dev)
     xc = x.contiguous()
-    ops().quant_mxfp8(xc, None, None if q_row is None else q_row.view(torch.uint8), sf_row,
+    ops().quant_mxfp8(xc, None, None, None if q_row is None else q_row.view(torch.uint8), sf_row,
                       None if q_col is None else q_col.view(torch.uint8), sf_col, r, c, r, e, r * c)
     _count()
     return q_row, sf_row, q_col, sf_col
 
 
 def quant_mxfp8(x: torch.Tensor, *, rowwise: bool = True, colwise: bool = False,
-                row_index: Optional[torch.Tensor] = None, rows: Optional[int] = None):
+                row_index: Optional[torch.Tensor] = None, rows: Optional[int] = None,
+                row_scale: Optional[torch.Tensor] = None):
     """Quantise bf16 x [R, C] along C (rowwise) and/or along R (colwise; a transposed
     copy [C, R_pad]). With `row_index` (int32[rows]) output row r reads x[row_index[r]]
-    (negative: zeros). Returns (q_row, sf_row, q_col, sf_col); unused ones are None."""
+    (negative: zeros); with `row_scale` (fp32[rows]) it is multiplied by row_scale[r] and
+    rounded to bf16 first. Returns (q_row, sf_row, q_col, sf_col); unused ones are None."""
     x2 = x.reshape(-1, x.shape[-1])
     c = x2.shape[1]
     r = rows if rows is not None else (row_index.numel() if row_index is not None else x2.shape[0])
@@ -175,7 +177,7 @@ def quant_mxfp8(x: torch.Tensor, *, rowwise: bool = True, colwise: bool = False,
         # the kernel writes every byte of both outputs, padding included
         q_col = torch.empty(c, r_pad, dtype=torch.float8_e4m3fn, device=dev)
         sf_col = torch.empty(sf_bytes(c, r_pad), dtype=torch.uint8, device=dev)
-    ops().quant_mxfp8(x2, row_index, None if q_row is None else q_row.view(torch.uint8), sf_row,
+    ops().quant_mxfp8(x2, row_index, row_scale, None if q_row is None else q_row.view(torch.uint8), sf_row,
                       None if q_col is None else q_col.view(torch.uint8), sf_col, r, c, r_pad, 1, 0)
     _count()
     return q_row, sf_row, q_col, sf_col
@@ -307,6 +309,14 @@ def combine_bwd(y, dout, pos, w, rows: int):
     ops().combine_bwd(y, dout, pos, w, dy, dw)
     _count()
     return dy, dw
+
+
+def combine_dots(y, dout, pos):
+    """dw [T, k] of `combine_rows` alone: <y[pos[t, j]], dout[t]> (0 for dropped picks)."""
+    dw = torch.empty(pos.shape, dtype=torch.float32, device=dout.device)
+    ops().combine_bwd(y, dout, pos, None, None, dw)
+    _count()
+    return dw
 
 
 def combine_rows(y, pos, w, tokens: int):
