@@ -104,11 +104,118 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const fl
     for (int i = threadIdx.x; i < d; i += blockDim.x) atomicAdd(&dw[i], dw_part[i]);
 }
 
+// The same backward with one private fp32 slab of dw per warp in shared memory: a lane owns
+// its columns of the slab, so the per-row update is a plain vector read-modify-write (no
+// atomics); the slabs are summed once at the end. Needs 8 warps · d · 4 bytes of shared memory.
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_slab_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                        const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd,
+                        __nv_bfloat16* __restrict__ dx, float* __restrict__ dw, int rows, int d) {
+  extern __shared__ __align__(16) float slabs[];  // [warps][d]
+  const int warps_per_block = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < warps_per_block * d; i += blockDim.x) slabs[i] = 0.f;
+  __syncthreads();
+  float4* mine = reinterpret_cast<float4*>(slabs + (size_t)warp * d);
+  const float4* w4 = reinterpret_cast<const float4*>(w);
+  const int nvec = d / 8;
+  for (int row = blockIdx.x * warps_per_block + warp; row < rows; row += gridDim.x * warps_per_block) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * d);
+    const uint4* gr = reinterpret_cast<const uint4*>(dy + (size_t)row * d);
+    const float r = rstd[row];
+    float dot = 0.f;
+    for (int i = lane; i < nvec; i += 32) {
+      const uint4 xv = xr[i], gv = gr[i];
+      const uint32_t* xu = &xv.x; const uint32_t* gu = &gv.x;
+      float wl[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
+      if (w) {
+        const float4 lo = w4[2 * i], hi = w4[2 * i + 1];
+        wl[0] = lo.x; wl[1] = lo.y; wl[2] = lo.z; wl[3] = lo.w; wl[4] = hi.x; wl[5] = hi.y; wl[6] = hi.z; wl[7] = hi.w;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 a = unpack_bf16(xu[j]), g = unpack_bf16(gu[j]);
+        dot += a.x * g.x * wl[2 * j] + a.y * g.y * wl[2 * j + 1];
+      }
+    }
+    dot = warp_sum(dot);
+    const float c = dot * r * r * r / d;
+    uint4* dxr = reinterpret_cast<uint4*>(dx + (size_t)row * d);
+    for (int i = lane; i < nvec; i += 32) {
+      const uint4 xv = xr[i], gv = gr[i];  // second read of the row: L1 / L2
+      const uint32_t* xu = &xv.x; const uint32_t* gu = &gv.x;
+      float wl[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
+      if (w) {
+        const float4 lo = w4[2 * i], hi = w4[2 * i + 1];
+        wl[0] = lo.x; wl[1] = lo.y; wl[2] = lo.z; wl[3] = lo.w; wl[4] = hi.x; wl[5] = hi.y; wl[6] = hi.z; wl[7] = hi.w;
+      }
+      uint4 o; uint32_t* ou = &o.x;
+      float p[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 a = unpack_bf16(xu[j]), g = unpack_bf16(gu[j]);
+        ou[j] = pack_bf16(r * wl[2 * j] * g.x - a.x * c, r * wl[2 * j + 1] * g.y - a.y * c);
+        p[2 * j] = g.x * a.x * r;
+        p[2 * j + 1] = g.y * a.y * r;
+      }
+      dxr[i] = o;
+      if (dw) {
+        float4 lo = mine[2 * i], hi = mine[2 * i + 1];
+        lo.x += p[0]; lo.y += p[1]; lo.z += p[2]; lo.w += p[3];
+        hi.x += p[4]; hi.y += p[5]; hi.z += p[6]; hi.w += p[7];
+        mine[2 * i] = lo; mine[2 * i + 1] = hi;
+      }
+    }
+  }
+  __syncthreads();
+  if (dw)
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+      float total = 0.f;
+      for (int k = 0; k < warps_per_block; ++k) total += slabs[(size_t)k * d + i];
+      atomicAdd(&dw[i], total);
+    }
+}
+
 // ---------------------------------------------------------------- QK-norm + RoPE
 // x: [tokens, heads, D] bf16 (row stride `stride_tok` elements so it may be a slice of
 // a fused qkv buffer); cos/sin: [tokens, D/2] fp32; w: [D] fp32 or null (no norm).
 // One warp per (token, head): lane l holds D/32 consecutive elements; its rotation
 // partner (element i <-> i + D/2) lives in lane l ^ 16.
+// E consecutive bf16 (E = 2, 4 or 8: one 4-, 8- or 16-byte access; the address is a multiple
+// of E elements because head offsets and token strides are multiples of the head dim).
+template <int E> struct BfVec;
+template <> struct BfVec<2> { using T = uint32_t; };
+template <> struct BfVec<4> { using T = uint2; };
+template <> struct BfVec<8> { using T = uint4; };
+template <int E>
+__device__ __forceinline__ void load_bf16(const __nv_bfloat16* p, float (&out)[E]) {
+  const typename BfVec<E>::T raw = *reinterpret_cast<const typename BfVec<E>::T*>(p);
+  const uint32_t* u = reinterpret_cast<const uint32_t*>(&raw);
+#pragma unroll
+  for (int j = 0; j < E / 2; ++j) { const float2 t = unpack_bf16(u[j]); out[2 * j] = t.x; out[2 * j + 1] = t.y; }
+}
+template <int E>
+__device__ __forceinline__ void store_bf16(__nv_bfloat16* p, const float (&v)[E]) {
+  typename BfVec<E>::T raw;
+  uint32_t* u = reinterpret_cast<uint32_t*>(&raw);
+#pragma unroll
+  for (int j = 0; j < E / 2; ++j) u[j] = pack_bf16(v[2 * j], v[2 * j + 1]);
+  *reinterpret_cast<typename BfVec<E>::T*>(p) = raw;
+}
+template <int E>
+__device__ __forceinline__ void load_f32(const float* p, float (&out)[E]) {
+  if (E % 4 == 0) {
+#pragma unroll
+    for (int j = 0; j < E / 4; ++j) {
+      const float4 t = reinterpret_cast<const float4*>(p)[j];
+      out[4 * j] = t.x; out[4 * j + 1] = t.y; out[4 * j + 2] = t.z; out[4 * j + 3] = t.w;
+    }
+  } else {
+    const float2 t = *reinterpret_cast<const float2*>(p);
+    out[0] = t.x; out[1] = t.y;
+  }
+}
+
 template <int D, bool BWD>
 __global__ void norm_rope_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
                                  const float* __restrict__ cs, const float* __restrict__ sn,
@@ -125,18 +232,20 @@ __global__ void norm_rope_kernel(const __nv_bfloat16* __restrict__ x, const floa
   const int lane = threadIdx.x & 31;
   const long nwarps = (long)gridDim.x * (blockDim.x >> 5);
   const long total = tokens * heads;
+  float dw_lane[E];  // a lane always holds the same E columns: its share of dw stays in registers
+#pragma unroll
+  for (int j = 0; j < E; ++j) dw_lane[j] = 0.f;
   for (long item = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); item < total; item += nwarps) {
     const long tok = item / heads;
     const int head = (int)(item % heads);
     const __nv_bfloat16* xp = x + tok * stride_tok_x + (long)head * D + lane * E;
     float v[E];
-#pragma unroll
-    for (int j = 0; j < E; ++j) v[j] = __bfloat162float(xp[j]);
+    load_bf16<E>(xp, v);
     const bool upper = lane >= 16;
     const int half_idx = (lane & 15) * E;  // index into cos/sin of my first element
     float c[E], s[E];
-#pragma unroll
-    for (int j = 0; j < E; ++j) { c[j] = cs[tok * (D / 2) + half_idx + j]; s[j] = sn[tok * (D / 2) + half_idx + j]; }
+    load_f32<E>(cs + tok * (D / 2) + half_idx, c);
+    load_f32<E>(sn + tok * (D / 2) + half_idx, s);
     if (!BWD) {
       float r = 1.f;
       if (w) {
@@ -150,19 +259,19 @@ __global__ void norm_rope_kernel(const __nv_bfloat16* __restrict__ x, const floa
         for (int j = 0; j < E; ++j) v[j] = v[j] * r * w[lane * E + j];
       }
       __nv_bfloat16* yp = y + tok * stride_tok_y + (long)head * D + lane * E;
+      float out[E];
 #pragma unroll
       for (int j = 0; j < E; ++j) {
         const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
         // lower half: a*c - b*s ; upper half: a*s + b*c  (a = lower, b = upper element)
-        const float out = upper ? (other * s[j] + v[j] * c[j]) : (v[j] * c[j] - other * s[j]);
-        yp[j] = __float2bfloat16(out);
+        out[j] = upper ? (other * s[j] + v[j] * c[j]) : (v[j] * c[j] - other * s[j]);
       }
+      store_bf16<E>(yp, out);
     } else {
       // dy -> d(normed) by the inverse rotation, then RMSNorm backward per head
       const __nv_bfloat16* gp = dy + tok * stride_tok_y + (long)head * D + lane * E;
       float g[E];
-#pragma unroll
-      for (int j = 0; j < E; ++j) g[j] = __bfloat162float(gp[j]);
+      load_bf16<E>(gp, g);
 #pragma unroll
       for (int j = 0; j < E; ++j) {
         const float other = __shfl_xor_sync(0xffffffffu, g[j], 16);
@@ -177,18 +286,21 @@ __global__ void norm_rope_kernel(const __nv_bfloat16* __restrict__ x, const floa
         for (int j = 0; j < E; ++j) dot += g[j] * w[lane * E + j] * v[j];
         dot = warp_sum(dot);
         const float cc = dot * r * r * r / D;
+        float o[E];
 #pragma unroll
         for (int j = 0; j < E; ++j) {
-          atomicAdd(&dw_part[lane * E + j], g[j] * v[j] * r);
-          dxp[j] = __float2bfloat16(r * w[lane * E + j] * g[j] - v[j] * cc);
+          dw_lane[j] += g[j] * v[j] * r;
+          o[j] = r * w[lane * E + j] * g[j] - v[j] * cc;
         }
+        store_bf16<E>(dxp, o);
       } else {
-#pragma unroll
-        for (int j = 0; j < E; ++j) dxp[j] = __float2bfloat16(g[j]);
+        store_bf16<E>(dxp, g);
       }
     }
   }
   if (BWD && dw) {
+#pragma unroll
+    for (int j = 0; j < E; ++j) atomicAdd(&dw_part[lane * E + j], dw_lane[j]);
     __syncthreads();
     for (int i = threadIdx.x; i < D; i += blockDim.x) atomicAdd(&dw[i], dw_part[i]);
   }
@@ -889,6 +1001,13 @@ void rmsnorm_fwd(const void* x, const float* w, void* y, float* rstd, long rows,
 void rmsnorm_bwd(const void* x, const float* w, const void* dy, const float* rstd, void* dx, float* dw, long rows, int d, cudaStream_t s) {
   const int wpb = 8;
   int grid = (int)min((rows + wpb - 1) / wpb, 148L * 4);
+  const size_t slab_bytes = (size_t)wpb * d * sizeof(float);
+  if (d % 8 == 0 && slab_bytes <= 200 * 1024) {
+    if (slab_bytes > 48 * 1024)  // per device, so set at every launch that needs it (a cheap call)
+      cudaFuncSetAttribute(rmsnorm_bwd_slab_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)slab_bytes);
+    rmsnorm_bwd_slab_kernel<<<grid, wpb * 32, slab_bytes, s>>>((const __nv_bfloat16*)x, w, (const __nv_bfloat16*)dy, rstd, (__nv_bfloat16*)dx, dw, (int)rows, d);
+    return;
+  }
   rmsnorm_bwd_kernel<<<grid, wpb * 32, d * sizeof(float), s>>>(
       (const __nv_bfloat16*)x, w, (const __nv_bfloat16*)dy, rstd, (__nv_bfloat16*)dx, dw, (int)rows, d);
 }
