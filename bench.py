@@ -26,6 +26,7 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
+MARGIN_BYTES = 10 << 30  # device memory left free when attention outputs are kept (fragmentation, chunk buffers)
 PUBLISHED_TOK_S_PER_GPU = 42391.0  # reference, 8xB300, MXFP8 `sorted` fsdp=8 (docs/performance/benchmarks.md:188)
 ROWS_PER_GPU = 32                  # 256 rows of 4096 over 8 GPUs
 
@@ -150,23 +151,17 @@ def main() -> int:
     tight = n <= 2
     trainer = Trainer(run, device=device, parallel=parallel, fuse_optimizer=True,
                       moments="fp8" if tight else "bfloat16", master=False)
-    # with the experts spread over four or more GPUs there is room to keep every layer's
-    # attention output, so the backward's rerun of a block skips the attention forward
-    # (On one or two GPUs they would have to follow the block inputs to pinned host memory:
-    # measured slower, PCIe becomes the bound, so they are recomputed there.)
-    keep_attention = False
-    if not tight:
-        arch = run.arch
-        attn = next(l.config for l in arch.layers() if l.config.type == "gqa")
-        blocks = sum(1 for l in arch.layers() if l.config.type == "gqa")
-        tokens = args.rows * args.seq_len
-        hd = attn.head_dim or arch.d_model // attn.num_heads
-        kept = tokens * attn.num_heads * (hd * 2 + 4)          # o in bf16 and the log-sum-exp in fp32
-        inputs = tokens * arch.d_model * 2
-        free, _ = torch.cuda.mem_get_info(device)
-        # 60 GB of slack: exchange buffers, one block's working set, the loss chunks
-        keep_attention = free > blocks * (kept + inputs) + 60e9
-    trainer.model.set_remat(True, offload=tight, keep_attention=keep_attention)
+    # Attention outputs (and their log-sum-exp) are kept on the device for as many blocks as
+    # a measured step leaves room for: the backward's rerun of those blocks skips the
+    # attention forward. One probe step without them gives the peak; the spare memory after
+    # a margin is divided by a block's kept bytes. All ranks take the smallest count.
+    arch = run.arch
+    attn = next(l.config for l in arch.layers() if l.config.type == "gqa")
+    blocks = sum(1 for l in arch.layers() if l.config.type == "gqa")
+    hd = attn.head_dim or arch.d_model // attn.num_heads
+    kept_bytes = args.rows * args.seq_len * attn.num_heads * (hd * 2 + 4)  # o in bf16, lse in fp32
+    trainer.model.set_remat(True, offload=tight, keep_attention=False)
+    keep_blocks = 0
     feed = iter(trainer.batches())
     tokens_per_step = args.rows * n * args.seq_len
 
@@ -177,8 +172,33 @@ def main() -> int:
             return float(out["loss"].item())
         return out
 
-    for _ in range(args.warmup):
-        one_step(True)
+    one_step(True)  # the probe step (an extra warm-up step)
+    torch.cuda.synchronize()
+    free, total_mem = torch.cuda.mem_get_info(device)
+    cached = torch.cuda.memory_reserved(device) - torch.cuda.max_memory_allocated(device)
+    spare = free + max(0, cached) // 2 - MARGIN_BYTES
+    keep_blocks = max(0, min(blocks, int(spare // kept_bytes)))
+    if parallel is not None:
+        import torch.distributed as dist
+
+        agreed = torch.tensor([keep_blocks], device=device)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+        keep_blocks = int(agreed.item())
+    if keep_blocks:
+        trainer.model.set_remat(True, offload=tight, keep_attention=keep_blocks)
+    try:
+        for _ in range(args.warmup):
+            one_step(True)
+    except torch.cuda.OutOfMemoryError:
+        # the estimate was too tight: on one GPU fall back to keeping nothing and warm up again
+        # (with several ranks the others are already inside a collective, so the error stands)
+        if parallel is not None:
+            raise
+        keep_blocks = 0
+        trainer.model.set_remat(True, offload=tight, keep_attention=False)
+        torch.cuda.empty_cache()
+        for _ in range(args.warmup):
+            one_step(True)
     torch.cuda.synchronize()
     if parallel is not None:
         parallel.barrier()
@@ -235,8 +255,9 @@ def main() -> int:
                        "parallelism": f"ep{n}" if n > 1 else "1 gpu (all experts local)",
                        "optimizer": "adamw, bf16 master, " + ("8-bit block-scaled moments" if tight else "bf16 moments")
                                     + ", expert updates fused into the backward, clip by the previous step's norm",
-                       "remat": "per block" + (", attention outputs kept" if keep_attention else "")
-                       + (", inputs and kept outputs in pinned host memory" if tight else ""), "l2": "inputs and weights exceed L2 (126 MB) every step",
+                       "remat": f"per block, attention outputs kept on the device for {keep_blocks} of {blocks} blocks"
+                       + (", block inputs in pinned host memory" if tight else ""),
+                       "peak_mem_gb": round(torch.cuda.max_memory_allocated(device) / 1e9, 1), "l2": "inputs and weights exceed L2 (126 MB) every step",
                        "loss_last_step": loss},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d,

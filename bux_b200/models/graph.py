@@ -116,13 +116,19 @@ class Repeated(nn.Module):
         self.items = nn.ModuleList(items)
         self.remat = False
         self.offload = False  # keep each pass's input in pinned host memory
-        self.keep_attention = False  # keep attention outputs too, so the replay skips that kernel
+        # keep attention outputs too, so the replay skips that kernel: True for every pass, or
+        # a count for the last so many passes only (what the device has room for)
+        self.keep_attention = False
+        self.kept_to_host = False  # with `offload`, kept outputs follow the inputs to pinned host memory
 
     def forward(self, x, ctx: Context):
         for i, item in enumerate(self.items):
             if (self.remat and ctx.training and torch.is_grad_enabled() and isinstance(x, torch.Tensor)
                     and x.requires_grad):
-                x = _checkpointed(item, x, ctx, self.offload, (id(self), i), self.keep_attention)
+                keep = self.keep_attention
+                if keep is not True and keep is not False:
+                    keep = i >= len(self.items) - int(keep)
+                x = _checkpointed(item, x, ctx, self.offload, (id(self), i), keep, self.kept_to_host)
             else:
                 x = item(x, ctx)
         return x
@@ -167,7 +173,7 @@ class _Remat(torch.autograd.Function):
             fctx.save_for_backward(x)
         with torch.no_grad():
             y, aux = holder.run(x, replay=False)
-        if fctx.host is not None and holder.kept:
+        if fctx.host is not None and holder.kept and holder.kept_to_host:
             # kept attention outputs follow the block's input to the host
             side = _side_stream(x.device)
             side.wait_stream(torch.cuda.current_stream(x.device))
@@ -191,7 +197,7 @@ class _Remat(torch.autograd.Function):
         main = torch.cuda.current_stream(fctx.device)
         side = _side_stream(fctx.device)
         buf = torch.empty(fctx.host.shape, dtype=fctx.host.dtype, device=fctx.device)
-        kept = fctx.holder.kept
+        kept = fctx.holder.kept if fctx.holder.kept_to_host else None
         back = None
         if kept:
             back = [tuple(torch.empty(h.shape, dtype=h.dtype, device=fctx.device) for h in pair) for pair in kept]
@@ -247,9 +253,11 @@ class _BlockRun:
 
     _pinned: dict = {}
 
-    def __init__(self, block, ctx: Context, offload: bool, key, keep_attention: bool = False):
+    def __init__(self, block, ctx: Context, offload: bool, key, keep_attention: bool = False,
+                 kept_to_host: bool = False):
         self.block, self.ctx, self.offload, self.key = block, ctx, offload, key
         self.kept = [] if keep_attention else None
+        self.kept_to_host = kept_to_host
         self.names: list = []
         self.taps = {k: list(v) for k, v in ctx.taps.items()}
         self.ports = dict(ctx.ports)
@@ -304,8 +312,9 @@ def _ends_in_plain_moe_branch(block) -> bool:
     return isinstance(tail, MoE)
 
 
-def _checkpointed(block, x, ctx: Context, offload: bool = False, key=None, keep_attention: bool = False):
-    holder = _BlockRun(block, ctx, offload, key, keep_attention)
+def _checkpointed(block, x, ctx: Context, offload: bool = False, key=None, keep_attention: bool = False,
+                  kept_to_host: bool = False):
+    holder = _BlockRun(block, ctx, offload, key, keep_attention, kept_to_host)
     y, *aux = _Remat.apply(x, holder)
     for name, value in zip(holder.names, aux):
         prev = ctx.losses.get(name)
