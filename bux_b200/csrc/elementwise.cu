@@ -223,84 +223,94 @@ __global__ void norm_rope_kernel(const __nv_bfloat16* __restrict__ x, const floa
                                  const __nv_bfloat16* __restrict__ dy, float* __restrict__ dw,
                                  long tokens, int heads, long stride_tok_x, long stride_tok_y,
                                  float eps) {
-  constexpr int E = D / 32;
+  // D/8 lanes per (token, head), eight elements (one 16-byte access) per lane: a warp works
+  // on 256/D items at once. Element i rotates with i + D/2, which lane ^ (LPI/2) holds.
+  constexpr int E = 8;
+  constexpr int LPI = D / E;          // lanes per item: 8, 16 or 32
+  constexpr int IPW = 32 / LPI;       // items per warp
   __shared__ float dw_part[D];
   if (BWD) {
     for (int i = threadIdx.x; i < D; i += blockDim.x) dw_part[i] = 0.f;
     __syncthreads();
   }
   const int lane = threadIdx.x & 31;
+  const int sub = lane / LPI, li = lane % LPI;  // which of the warp's items, and the lane within it
   const long nwarps = (long)gridDim.x * (blockDim.x >> 5);
   const long total = tokens * heads;
+  const long steps = (total + IPW - 1) / IPW;   // whole warps iterate together (shuffles stay converged)
   float dw_lane[E];  // a lane always holds the same E columns: its share of dw stays in registers
 #pragma unroll
   for (int j = 0; j < E; ++j) dw_lane[j] = 0.f;
-  for (long item = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); item < total; item += nwarps) {
-    const long tok = item / heads;
-    const int head = (int)(item % heads);
-    const __nv_bfloat16* xp = x + tok * stride_tok_x + (long)head * D + lane * E;
+  float wl[E];
+#pragma unroll
+  for (int j = 0; j < E; ++j) wl[j] = w ? w[li * E + j] : 1.f;
+  for (long step = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); step < steps; step += nwarps) {
+    const long item = step * IPW + sub;
+    const bool live = item < total;
+    const long tok = live ? item / heads : 0;
+    const int head = live ? (int)(item % heads) : 0;
+    const __nv_bfloat16* xp = x + tok * stride_tok_x + (long)head * D + li * E;
     float v[E];
     load_bf16<E>(xp, v);
-    const bool upper = lane >= 16;
-    const int half_idx = (lane & 15) * E;  // index into cos/sin of my first element
+    const bool upper = li >= LPI / 2;
+    const int half_idx = (li % (LPI / 2)) * E;  // index into cos/sin of my first element
     float c[E], s[E];
     load_f32<E>(cs + tok * (D / 2) + half_idx, c);
     load_f32<E>(sn + tok * (D / 2) + half_idx, s);
     if (!BWD) {
-      float r = 1.f;
       if (w) {
         float ss = 0.f;
 #pragma unroll
         for (int j = 0; j < E; ++j) ss += v[j] * v[j];
-        ss = warp_sum(ss);
-        r = rsqrtf(ss / D + eps);
-        if (lane == 0 && rstd_io) rstd_io[item] = r;
 #pragma unroll
-        for (int j = 0; j < E; ++j) v[j] = v[j] * r * w[lane * E + j];
+        for (int o = LPI / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float r = rsqrtf(ss / D + eps);
+        if (li == 0 && live && rstd_io) rstd_io[item] = r;
+#pragma unroll
+        for (int j = 0; j < E; ++j) v[j] = v[j] * r * wl[j];
       }
-      __nv_bfloat16* yp = y + tok * stride_tok_y + (long)head * D + lane * E;
       float out[E];
 #pragma unroll
       for (int j = 0; j < E; ++j) {
-        const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
+        const float other = __shfl_xor_sync(0xffffffffu, v[j], LPI / 2);
         // lower half: a*c - b*s ; upper half: a*s + b*c  (a = lower, b = upper element)
         out[j] = upper ? (other * s[j] + v[j] * c[j]) : (v[j] * c[j] - other * s[j]);
       }
-      store_bf16<E>(yp, out);
+      if (live) store_bf16<E>(y + tok * stride_tok_y + (long)head * D + li * E, out);
     } else {
       // dy -> d(normed) by the inverse rotation, then RMSNorm backward per head
-      const __nv_bfloat16* gp = dy + tok * stride_tok_y + (long)head * D + lane * E;
       float g[E];
-      load_bf16<E>(gp, g);
+      load_bf16<E>(dy + tok * stride_tok_y + (long)head * D + li * E, g);
 #pragma unroll
       for (int j = 0; j < E; ++j) {
-        const float other = __shfl_xor_sync(0xffffffffu, g[j], 16);
+        const float other = __shfl_xor_sync(0xffffffffu, g[j], LPI / 2);
         // y_lo = a c - b s, y_hi = a s + b c  =>  da = g_lo c + g_hi s, db = -g_lo s + g_hi c
         g[j] = upper ? (-other * s[j] + g[j] * c[j]) : (g[j] * c[j] + other * s[j]);
       }
-      __nv_bfloat16* dxp = y + tok * stride_tok_y + (long)head * D + lane * E;  // y doubles as dx (dense, like dy)
+      __nv_bfloat16* dxp = y + tok * stride_tok_y + (long)head * D + li * E;  // y doubles as dx (dense, like dy)
       if (w) {
-        const float r = rstd_io[item];
+        const float r = rstd_io[live ? item : 0];
         float dot = 0.f;
 #pragma unroll
-        for (int j = 0; j < E; ++j) dot += g[j] * w[lane * E + j] * v[j];
-        dot = warp_sum(dot);
+        for (int j = 0; j < E; ++j) dot += g[j] * wl[j] * v[j];
+#pragma unroll
+        for (int o = LPI / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
         const float cc = dot * r * r * r / D;
-        float o[E];
+        float o8[E];
 #pragma unroll
         for (int j = 0; j < E; ++j) {
-          dw_lane[j] += g[j] * v[j] * r;
-          o[j] = r * w[lane * E + j] * g[j] - v[j] * cc;
+          if (live) dw_lane[j] += g[j] * v[j] * r;
+          o8[j] = r * wl[j] * g[j] - v[j] * cc;
         }
-        store_bf16<E>(dxp, o);
-      } else {
+        if (live) store_bf16<E>(dxp, o8);
+      } else if (live) {
         store_bf16<E>(dxp, g);
       }
     }
   }
   if (BWD && dw) {
 #pragma unroll
-    for (int j = 0; j < E; ++j) atomicAdd(&dw_part[lane * E + j], dw_lane[j]);
+    for (int j = 0; j < E; ++j) atomicAdd(&dw_part[li * E + j], dw_lane[j]);
     __syncthreads();
     for (int i = threadIdx.x; i < D; i += blockDim.x) atomicAdd(&dw[i], dw_part[i]);
   }
@@ -308,8 +318,8 @@ __global__ void norm_rope_kernel(const __nv_bfloat16* __restrict__ x, const floa
 
 // ---------------------------------------------------------------- gated activations
 __device__ __forceinline__ float act_fwd(float g, int kind) {
-  if (kind == ACT_SWISH) return g / (1.f + __expf(-g));
-  if (kind == ACT_QUICK_GELU) return g / (1.f + __expf(-1.702f * g));
+  if (kind == ACT_SWISH) return __fdividef(g, 1.f + __expf(-g));
+  if (kind == ACT_QUICK_GELU) return __fdividef(g, 1.f + __expf(-1.702f * g));
   if (kind == ACT_GELU_TANH) {
     const float u = 0.7978845608f * (g + 0.044715f * g * g * g);
     return 0.5f * g * (1.f + tanhf(u));
@@ -318,8 +328,8 @@ __device__ __forceinline__ float act_fwd(float g, int kind) {
   return g;
 }
 __device__ __forceinline__ float act_grad(float g, int kind) {
-  if (kind == ACT_SWISH) { const float s = 1.f / (1.f + __expf(-g)); return s * (1.f + g * (1.f - s)); }
-  if (kind == ACT_QUICK_GELU) { const float s = 1.f / (1.f + __expf(-1.702f * g)); return s * (1.f + 1.702f * g * (1.f - s)); }
+  if (kind == ACT_SWISH) { const float s = __fdividef(1.f, 1.f + __expf(-g)); return s * (1.f + g * (1.f - s)); }
+  if (kind == ACT_QUICK_GELU) { const float s = __fdividef(1.f, 1.f + __expf(-1.702f * g)); return s * (1.f + 1.702f * g * (1.f - s)); }
   if (kind == ACT_GELU_TANH) {
     const float u = 0.7978845608f * (g + 0.044715f * g * g * g);
     const float t = tanhf(u);
@@ -327,6 +337,19 @@ __device__ __forceinline__ float act_grad(float g, int kind) {
   }
   if (kind == ACT_RELU2) return 2.f * fmaxf(g, 0.f);
   return 1.f;
+}
+
+// act(g) and act'(g) together: the sigmoid kinds share their one exponential and reciprocal.
+__device__ __forceinline__ void act_both(float g, int kind, float& a, float& da) {
+  if (kind == ACT_SWISH || kind == ACT_QUICK_GELU) {
+    const float k = kind == ACT_SWISH ? 1.f : 1.702f;
+    const float s = __fdividef(1.f, 1.f + __expf(-k * g));
+    a = g * s;
+    da = s * (1.f + k * g * (1.f - s));
+    return;
+  }
+  a = act_fwd(g, kind);
+  da = act_grad(g, kind);
 }
 
 // h: [rows, 2f] (gate columns [0,f), up columns [f,2f)); out: [rows, f].
@@ -386,10 +409,11 @@ __global__ void glu_bwd_kernel(const __nv_bfloat16* __restrict__ h, const __nv_b
           if (uu_ > limit) { uu_ = limit; u_pass = false; }
           if (uu_ < -limit) { uu_ = -limit; u_pass = false; }
         }
-        const float a = act_fwd(gg, kind);
+        float a, da;
+        act_both(gg, kind, a, da);
         ds += dx[e] * a * (uu_ + up_offset);
         const float dsc = dx[e] * rs;
-        rg[e] = g_pass ? dsc * (uu_ + up_offset) * act_grad(gg, kind) : 0.f;
+        rg[e] = g_pass ? dsc * (uu_ + up_offset) * da : 0.f;
         ru[e] = u_pass ? dsc * a : 0.f;
       }
       ogu[j] = pack_bf16(rg[0], rg[1]);
@@ -496,8 +520,10 @@ __device__ __forceinline__ uint4 glu_bwd8(const uint4& gv, const uint4& uv, cons
         if (uu_ > gp.limit) { uu_ = gp.limit; u_pass = false; }
         if (uu_ < -gp.limit) { uu_ = -gp.limit; u_pass = false; }
       }
-      if (up_half) r[e] = u_pass ? dx[e] * act_fwd(gg, gp.kind) : 0.f;
-      else r[e] = g_pass ? dx[e] * (uu_ + gp.up_offset) * act_grad(gg, gp.kind) : 0.f;
+      float a, da;
+      act_both(gg, gp.kind, a, da);
+      if (up_half) r[e] = u_pass ? dx[e] * a : 0.f;
+      else r[e] = g_pass ? dx[e] * (uu_ + gp.up_offset) * da : 0.f;
     }
     ou[j] = pack_bf16(r[0], r[1]);
   }
@@ -834,21 +860,30 @@ __global__ void adamw_kernel(PT* __restrict__ p, const GT* __restrict__ g, void*
         for (int j = 0; j < 8; ++j) { mb[j] = j < cnt ? reinterpret_cast<uint8_t*>(m_)[i0 + j] : 0; vb[j] = j < cnt ? reinterpret_cast<uint8_t*>(v_)[i0 + j] : 0; }
       }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        pm[j] = __half2float(__half(__nv_cvt_fp8_to_halfraw(mb[j], __NV_E4M3))) * sm;
-        const float rv = __half2float(__half(__nv_cvt_fp8_to_halfraw(vb[j], __NV_E4M3))) * sv;
-        pv[j] = rv * rv;
+      for (int j = 0; j < 4; ++j) {  // two values per conversion
+        const __nv_fp8x2_storage_t m2 = (__nv_fp8x2_storage_t)(mb[2 * j] | (mb[2 * j + 1] << 8));
+        const __nv_fp8x2_storage_t v2 = (__nv_fp8x2_storage_t)(vb[2 * j] | (vb[2 * j + 1] << 8));
+        const float2 fm = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(m2, __NV_E4M3)));
+        const float2 fv = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(v2, __NV_E4M3)));
+        pm[2 * j] = fm.x * sm; pm[2 * j + 1] = fm.y * sm;
+        const float r0 = fv.x * sv, r1 = fv.y * sv;
+        pv[2 * j] = r0 * r0; pv[2 * j + 1] = r1 * r1;
       }
     }
+    // one approximate square root and one approximate reciprocal per element (the special
+    // function unit): the exact forms cost more instructions than the memory traffic hides
     float am = 0.f, av = 0.f;
+    float sq[8];
+    const float ibc1 = 1.f / bc1, isb2 = rsqrtf(bc2);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float gg = gr[j] * gscale;
       pm[j] = b1 * pm[j] + (1.f - b1) * gg;
       pv[j] = b2 * pv[j] + (1.f - b2) * gg * gg;
-      const float upd = (pm[j] / bc1) / (sqrtf(pv[j] / bc2) + eps) + wd * pw[j];
+      asm("sqrt.approx.f32 %0, %1;" : "=f"(sq[j]) : "f"(pv[j]));
+      const float upd = __fdividef(pm[j] * ibc1, fmaf(sq[j], isb2, eps)) + wd * pw[j];
       pw[j] -= lr * upd;
-      if (j < cnt) { am = fmaxf(am, fabsf(pm[j])); av = fmaxf(av, sqrtf(pv[j])); }
+      if (j < cnt) { am = fmaxf(am, fabsf(pm[j])); av = fmaxf(av, sq[j]); }
     }
     if (full) {
       Vec8<PT>::store(p + i0, pw);
@@ -875,9 +910,11 @@ __global__ void adamw_kernel(PT* __restrict__ p, const GT* __restrict__ g, void*
         if ((threadIdx.x & 3) == 0) { m_sf[blk] = em; v_sf[blk] = ev; }
         uint8_t mb[8], vb[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          mb[j] = __nv_cvt_float_to_fp8(pm[j] * im, __NV_SATFINITE, __NV_E4M3);
-          vb[j] = __nv_cvt_float_to_fp8(sqrtf(pv[j]) * iv, __NV_SATFINITE, __NV_E4M3);
+        for (int j = 0; j < 4; ++j) {
+          const __nv_fp8x2_storage_t m2 = __nv_cvt_float2_to_fp8x2(make_float2(pm[2 * j] * im, pm[2 * j + 1] * im), __NV_SATFINITE, __NV_E4M3);
+          const __nv_fp8x2_storage_t v2 = __nv_cvt_float2_to_fp8x2(make_float2(sq[2 * j] * iv, sq[2 * j + 1] * iv), __NV_SATFINITE, __NV_E4M3);
+          mb[2 * j] = (uint8_t)(m2 & 0xff); mb[2 * j + 1] = (uint8_t)(m2 >> 8);
+          vb[2 * j] = (uint8_t)(v2 & 0xff); vb[2 * j + 1] = (uint8_t)(v2 >> 8);
         }
         if (full) {
           *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(m_) + i0) = *reinterpret_cast<uint2*>(mb);
@@ -1015,7 +1052,7 @@ const char* norm_rope(bool bwd, const void* x, const float* w, const float* cs, 
                       float* rstd, const void* dy, float* dw, long tokens, int heads, int D,
                       long stride_x, long stride_y, float eps, cudaStream_t s) {
   const int wpb = 8;
-  const long items = tokens * heads;
+  const long items = (tokens * heads + (256 / D) - 1) / (256 / D);  // warp steps: 256 / D items each
   int grid = (int)min((items + wpb - 1) / wpb, 148L * 8);
 #define NR_CASE(D_) \
   if (D == D_) { \

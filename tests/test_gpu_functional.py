@@ -140,16 +140,18 @@ precision = precision(compute=bfloat16)
 """
     run = compile_runs(src, filename="k.bux")[0]
     out = []
-    for keep in (False, True):
+    for keep, offload in ((False, False), (True, False), (1, True)):
         tr = Trainer(run, device="cuda")
-        tr.model.set_remat(True, keep_attention=keep)
+        tr.model.set_remat(True, offload=offload, keep_attention=keep)
         feed = iter(tr.batches())
         before = K.launches
         losses = [tr.train_step(next(feed))["loss"].item() for _ in range(2)]
         out.append((losses, K.launches - before, {n: p.detach().float().clone() for n, p in tr.model.named_parameters()}))
-    (l0, n0, s0), (l1, n1, s1) = out
-    assert l0 == pytest.approx(l1, abs=1e-3)
+    (l0, n0, s0), (l1, n1, s1), (l2, n2, s2) = out
+    assert l0 == pytest.approx(l1, abs=1e-3) and l0 == pytest.approx(l2, abs=1e-3)
     assert n1 == n0 - 2 * 2              # one attention forward less per block and step
+    assert n2 == n0 - 2 * 1              # a count keeps the last so many blocks only (inputs on the host)
+    assert all(torch.allclose(s0[k], s2[k], atol=2e-3, rtol=2e-2) for k in s0)
     # dQ is summed by fp32 reductions whose order varies from run to run: close, not bit-equal
     assert all(torch.allclose(s0[k], s1[k], atol=2e-3, rtol=2e-2) for k in s0)
 
