@@ -837,32 +837,40 @@ __global__ void adamw_kernel(PT* __restrict__ p, const GT* __restrict__ g, void*
       Vec8<PT>::load(p + i0, pw);
       Vec8<GT>::load(g + i0, gr);
     } else {
-      for (int j = 0; j < cnt; ++j) { pw[j] = (float)p[i0 + j]; gr[j] = (float)g[i0 + j]; }
+      _Pragma("unroll") for (int j = 0; j < 8; ++j) if (j < cnt) { pw[j] = (float)p[i0 + j]; gr[j] = (float)g[i0 + j]; }
     }
     const long blk = i0 >> 5;
     if (MOM == MOM_F32) {
       if (full) { Vec8<float>::load(reinterpret_cast<float*>(m_) + i0, pm); Vec8<float>::load(reinterpret_cast<float*>(v_) + i0, pv); }
-      else for (int j = 0; j < cnt; ++j) { pm[j] = reinterpret_cast<float*>(m_)[i0 + j]; pv[j] = reinterpret_cast<float*>(v_)[i0 + j]; }
+      else _Pragma("unroll") for (int j = 0; j < 8; ++j) if (j < cnt) { pm[j] = reinterpret_cast<float*>(m_)[i0 + j]; pv[j] = reinterpret_cast<float*>(v_)[i0 + j]; }
     } else if (MOM == MOM_BF16) {
       if (full) { Vec8<__nv_bfloat16>::load(reinterpret_cast<__nv_bfloat16*>(m_) + i0, pm); Vec8<__nv_bfloat16>::load(reinterpret_cast<__nv_bfloat16*>(v_) + i0, pv); }
-      else for (int j = 0; j < cnt; ++j) {
+      else _Pragma("unroll") for (int j = 0; j < 8; ++j) if (j < cnt) {
         pm[j] = __bfloat162float(reinterpret_cast<__nv_bfloat16*>(m_)[i0 + j]);
         pv[j] = __bfloat162float(reinterpret_cast<__nv_bfloat16*>(v_)[i0 + j]);
       }
     } else if (active) {
       const float sm = __uint_as_float((uint32_t)max((int)m_sf[blk], 1) << 23);
       const float sv = __uint_as_float((uint32_t)max((int)v_sf[blk], 1) << 23);
-      uint8_t mb[8], vb[8];
+      // the eight moment bytes of m and of v travel as two 32-bit words each (no byte arrays:
+      // those would live in local memory)
+      uint2 mw = make_uint2(0, 0), vw = make_uint2(0, 0);
       if (full) {
-        *reinterpret_cast<uint2*>(mb) = *reinterpret_cast<const uint2*>(reinterpret_cast<uint8_t*>(m_) + i0);
-        *reinterpret_cast<uint2*>(vb) = *reinterpret_cast<const uint2*>(reinterpret_cast<uint8_t*>(v_) + i0);
+        mw = *reinterpret_cast<const uint2*>(reinterpret_cast<uint8_t*>(m_) + i0);
+        vw = *reinterpret_cast<const uint2*>(reinterpret_cast<uint8_t*>(v_) + i0);
       } else {
-        for (int j = 0; j < 8; ++j) { mb[j] = j < cnt ? reinterpret_cast<uint8_t*>(m_)[i0 + j] : 0; vb[j] = j < cnt ? reinterpret_cast<uint8_t*>(v_)[i0 + j] : 0; }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (j < cnt) {
+            const uint32_t bm = reinterpret_cast<uint8_t*>(m_)[i0 + j], bv = reinterpret_cast<uint8_t*>(v_)[i0 + j];
+            if (j < 4) { mw.x |= bm << (8 * j); vw.x |= bv << (8 * j); }
+            else { mw.y |= bm << (8 * (j - 4)); vw.y |= bv << (8 * (j - 4)); }
+          }
       }
 #pragma unroll
       for (int j = 0; j < 4; ++j) {  // two values per conversion
-        const __nv_fp8x2_storage_t m2 = (__nv_fp8x2_storage_t)(mb[2 * j] | (mb[2 * j + 1] << 8));
-        const __nv_fp8x2_storage_t v2 = (__nv_fp8x2_storage_t)(vb[2 * j] | (vb[2 * j + 1] << 8));
+        const __nv_fp8x2_storage_t m2 = (__nv_fp8x2_storage_t)(((j < 2 ? mw.x : mw.y) >> (16 * (j & 1))) & 0xffffu);
+        const __nv_fp8x2_storage_t v2 = (__nv_fp8x2_storage_t)(((j < 2 ? vw.x : vw.y) >> (16 * (j & 1))) & 0xffffu);
         const float2 fm = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(m2, __NV_E4M3)));
         const float2 fv = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(v2, __NV_E4M3)));
         pm[2 * j] = fm.x * sm; pm[2 * j + 1] = fm.y * sm;
@@ -889,14 +897,14 @@ __global__ void adamw_kernel(PT* __restrict__ p, const GT* __restrict__ g, void*
       Vec8<PT>::store(p + i0, pw);
       if (shadow) Vec8<__nv_bfloat16>::store(shadow + i0, pw);
     } else {
-      for (int j = 0; j < cnt; ++j) { p[i0 + j] = (PT)pw[j]; if (shadow) shadow[i0 + j] = __float2bfloat16(pw[j]); }
+      _Pragma("unroll") for (int j = 0; j < 8; ++j) if (j < cnt) { p[i0 + j] = (PT)pw[j]; if (shadow) shadow[i0 + j] = __float2bfloat16(pw[j]); }
     }
     if (MOM == MOM_F32) {
       if (full) { Vec8<float>::store(reinterpret_cast<float*>(m_) + i0, pm); Vec8<float>::store(reinterpret_cast<float*>(v_) + i0, pv); }
-      else for (int j = 0; j < cnt; ++j) { reinterpret_cast<float*>(m_)[i0 + j] = pm[j]; reinterpret_cast<float*>(v_)[i0 + j] = pv[j]; }
+      else _Pragma("unroll") for (int j = 0; j < 8; ++j) if (j < cnt) { reinterpret_cast<float*>(m_)[i0 + j] = pm[j]; reinterpret_cast<float*>(v_)[i0 + j] = pv[j]; }
     } else if (MOM == MOM_BF16) {
       if (full) { Vec8<__nv_bfloat16>::store(reinterpret_cast<__nv_bfloat16*>(m_) + i0, pm); Vec8<__nv_bfloat16>::store(reinterpret_cast<__nv_bfloat16*>(v_) + i0, pv); }
-      else for (int j = 0; j < cnt; ++j) {
+      else _Pragma("unroll") for (int j = 0; j < 8; ++j) if (j < cnt) {
         reinterpret_cast<__nv_bfloat16*>(m_)[i0 + j] = __float2bfloat16(pm[j]);
         reinterpret_cast<__nv_bfloat16*>(v_)[i0 + j] = __float2bfloat16(pv[j]);
       }
@@ -908,19 +916,24 @@ __global__ void adamw_kernel(PT* __restrict__ p, const GT* __restrict__ g, void*
         const uint8_t em = (uint8_t)max((int)e8m0_of(am), 1), ev = (uint8_t)max((int)e8m0_of(av), 1);
         const float im = e8m0_inv(em), iv = e8m0_inv(ev);
         if ((threadIdx.x & 3) == 0) { m_sf[blk] = em; v_sf[blk] = ev; }
-        uint8_t mb[8], vb[8];
+        uint2 mo = make_uint2(0, 0), vo = make_uint2(0, 0);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const __nv_fp8x2_storage_t m2 = __nv_cvt_float2_to_fp8x2(make_float2(pm[2 * j] * im, pm[2 * j + 1] * im), __NV_SATFINITE, __NV_E4M3);
-          const __nv_fp8x2_storage_t v2 = __nv_cvt_float2_to_fp8x2(make_float2(sq[2 * j] * iv, sq[2 * j + 1] * iv), __NV_SATFINITE, __NV_E4M3);
-          mb[2 * j] = (uint8_t)(m2 & 0xff); mb[2 * j + 1] = (uint8_t)(m2 >> 8);
-          vb[2 * j] = (uint8_t)(v2 & 0xff); vb[2 * j + 1] = (uint8_t)(v2 >> 8);
+          const uint32_t m2 = __nv_cvt_float2_to_fp8x2(make_float2(pm[2 * j] * im, pm[2 * j + 1] * im), __NV_SATFINITE, __NV_E4M3);
+          const uint32_t v2 = __nv_cvt_float2_to_fp8x2(make_float2(sq[2 * j] * iv, sq[2 * j + 1] * iv), __NV_SATFINITE, __NV_E4M3);
+          if (j < 2) { mo.x |= m2 << (16 * j); vo.x |= v2 << (16 * j); }
+          else { mo.y |= m2 << (16 * (j - 2)); vo.y |= v2 << (16 * (j - 2)); }
         }
         if (full) {
-          *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(m_) + i0) = *reinterpret_cast<uint2*>(mb);
-          *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(v_) + i0) = *reinterpret_cast<uint2*>(vb);
+          *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(m_) + i0) = mo;
+          *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(v_) + i0) = vo;
         } else {
-          for (int j = 0; j < cnt; ++j) { reinterpret_cast<uint8_t*>(m_)[i0 + j] = mb[j]; reinterpret_cast<uint8_t*>(v_)[i0 + j] = vb[j]; }
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (j < cnt) {
+              reinterpret_cast<uint8_t*>(m_)[i0 + j] = (uint8_t)(((j < 4 ? mo.x : mo.y) >> (8 * (j & 3))) & 0xff);
+              reinterpret_cast<uint8_t*>(v_)[i0 + j] = (uint8_t)(((j < 4 ? vo.x : vo.y) >> (8 * (j & 3))) & 0xff);
+            }
         }
       }
     }

@@ -389,7 +389,9 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
               reinterpret_cast<uint4*>(dst)[v] = q;
             }
           } else {
-            for (int i = 0; i < valid; ++i) dst[i] = __float2bfloat16(__uint_as_float(r[i]));
+#pragma unroll
+            for (int i = 0; i < 32; ++i)  // unrolled with a predicate: r[] stays in registers
+              if (i < valid) dst[i] = __float2bfloat16(__uint_as_float(r[i]));
           }
         } else {
           float* dst = reinterpret_cast<float*>(p.c) + out_row * p.ldc + n;
@@ -405,10 +407,12 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
               reinterpret_cast<float4*>(dst)[v] = q;
             }
           } else {
-            for (int i = 0; i < valid; ++i) {
-              float x = __uint_as_float(r[i]);
-              dst[i] = p.out_kind == OUT_F32_ACC ? dst[i] + x : x;
-            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i < valid) {
+                const float x = __uint_as_float(r[i]);
+                dst[i] = p.out_kind == OUT_F32_ACC ? dst[i] + x : x;
+              }
           }
         }
       }
