@@ -197,6 +197,16 @@ void sumsq(const Tensor& g, Tensor& out) {
   c10::cuda::CUDAGuard guard(g.device());
   bux::sumsq(g.data_ptr(), g.scalar_type() == at::kBFloat16, g.numel(), out.data_ptr<float>(), stream_of(g));
 }
+void topk_rows(const Tensor& scores, Tensor& idx) {
+  check_cuda(scores, "scores"); check_cuda(idx, "idx");
+  TORCH_CHECK(scores.scalar_type() == at::kFloat && scores.dim() == 2 && scores.is_contiguous(), "topk_rows: contiguous fp32 [rows, n]");
+  TORCH_CHECK(idx.scalar_type() == at::kLong && idx.is_contiguous() && idx.size(0) == scores.size(0), "topk_rows: int64 [rows, k]");
+  TORCH_CHECK(idx.size(1) <= scores.size(1), "topk_rows: k <= n");
+  c10::cuda::CUDAGuard guard(scores.device());
+  const char* err = bux::topk_rows(scores.data_ptr<float>(), reinterpret_cast<long*>(idx.data_ptr<int64_t>()), scores.size(0),
+                                   (int)scores.size(1), (int)idx.size(1), stream_of(scores));
+  TORCH_CHECK(err == nullptr, err);
+}
 void gather_rows(const Tensor& x, const Tensor& index, Tensor& out) {
   check_cuda(x, "x"); check_cuda(out, "out");
   c10::cuda::CUDAGuard guard(x.device());
@@ -333,6 +343,7 @@ TORCH_LIBRARY(bux_b200, m) {
   m.def("ce_fwd_bwd(Tensor(a!) logits, Tensor targets, Tensor? mask, Tensor(b!) loss, Tensor? logz, float grad_scale, float z_weight, float softcap) -> ()", &ce_fwd_bwd);
   m.def("adamw(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor? m_sf, Tensor? v_sf, Tensor? shadow, Tensor? grad_scale, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2, float grad_scale_const) -> ()", &adamw);
   m.def("sumsq(Tensor g, Tensor(a!) out) -> ()", &sumsq);
+  m.def("topk_rows(Tensor scores, Tensor(a!) idx) -> ()", &topk_rows);
   m.def("gather_rows(Tensor x, Tensor index, Tensor(a!) out) -> ()", &gather_rows);
   m.def("combine_bwd(Tensor? y, Tensor dout, Tensor pos, Tensor? w, Tensor(a!)? dy, Tensor(b!)? dw) -> ()", &combine_bwd);
   m.def("combine_rows(Tensor y, Tensor pos, Tensor? w, Tensor(a!) out) -> ()", &combine_rows);

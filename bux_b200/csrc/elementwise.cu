@@ -960,6 +960,44 @@ __global__ void sumsq_kernel(const GT* __restrict__ g, long n, float* __restrict
   }
 }
 
+// ---------------------------------------------------------------- router top-k
+// The k largest of each row of scores [rows, n] (fp32), indices in descending order of value
+// (ties: the lower index first). One warp per row; lane l holds columns l, l + 32, ... in
+// registers and the warp picks one winner per round by shuffles.
+template <int NV>
+__global__ void topk_rows_kernel(const float* __restrict__ scores, long* __restrict__ idx, long rows, int n, int k) {
+  const int lane = threadIdx.x & 31;
+  const long row = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const float* sr = scores + row * n;
+  float v[NV];
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int c = j * 32 + lane;
+    v[j] = c < n ? sr[c] : -INFINITY;
+    if (v[j] != v[j]) v[j] = -INFINITY;  // a NaN never wins
+  }
+  for (int round = 0; round < k; ++round) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int c = j * 32 + lane;
+      if (c < n && (v[j] > best || (v[j] == best && c < at))) { best = v[j]; at = c; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+    }
+    if (lane == 0) idx[row * k + round] = at;
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+      if (j * 32 + lane == at) v[j] = -INFINITY;  // taken: out of the next rounds
+  }
+}
+
 // ---------------------------------------------------------------- MoE gather / combine
 // out[r] = x[index[r]] (zero row when index[r] < 0); rows of d bf16, d % 8 == 0.
 __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ index,
@@ -1117,6 +1155,14 @@ void sumsq(const void* g, bool bf16, long n, float* out, cudaStream_t s) {
   const int grid = grid_for(n, 256 * 8, 148 * 8);
   if (bf16) sumsq_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)g, n, out);
   else sumsq_kernel<float><<<grid, 256, 0, s>>>((const float*)g, n, out);
+}
+const char* topk_rows(const float* scores, long* idx, long rows, int n, int k, cudaStream_t s) {
+  const int wpb = 8;
+  const unsigned grid = (unsigned)((rows + wpb - 1) / wpb);
+#define TK_CASE(NV_) if (n <= NV_ * 32) { topk_rows_kernel<NV_><<<grid, wpb * 32, 0, s>>>(scores, idx, rows, n, k); return nullptr; }
+  TK_CASE(1) TK_CASE(2) TK_CASE(4) TK_CASE(8) TK_CASE(16)
+#undef TK_CASE
+  return "topk_rows: at most 512 columns";
 }
 void gather_rows(const void* x, const int* index, void* out, long rows, int d, cudaStream_t s) {
   gather_rows_kernel<<<grid_for(rows * (d / 8), 256), 256, 0, s>>>((const __nv_bfloat16*)x, index, (__nv_bfloat16*)out, rows, d);

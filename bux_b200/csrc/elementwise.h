@@ -26,6 +26,8 @@ const char* adamw(void* p, bool p_bf16, const void* g, bool g_bf16, void* m, voi
                   void* shadow, long n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
                   const float* gscale_ptr, float gscale, cudaStream_t s);
 void sumsq(const void* g, bool bf16, long n, float* out, cudaStream_t s);
+// indices (int64) of the k largest entries of each fp32 row, descending; n <= 512
+const char* topk_rows(const float* scores, long* idx, long rows, int n, int k, cudaStream_t s);
 void gather_rows(const void* x, const int* index, void* out, long rows, int d, cudaStream_t s);
 void combine_bwd(const void* y, const void* dout, const int* pos, const float* w, void* dy, float* dw, long picks, int k, int d, cudaStream_t s);
 void combine_rows(const void* y, const int* pos, const float* w, void* out, long tokens, int k, int d, cudaStream_t s);

@@ -28,7 +28,6 @@ namespace bux {
 
 constexpr int KID_GEMM = 1;
 constexpr int BM = 128;
-constexpr int GEMM_THREADS = 192;
 
 template <int KIND, int BN>
 struct GemmCfg {
@@ -39,9 +38,17 @@ struct GemmCfg {
   static constexpr int B_BYTES = BN * 128;
   static constexpr int SF_BYTES = KIND == KIND_MXFP8 ? 512 * (1 + BN / 128) : 0;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SF_BYTES;
-  // epilogue staging: per warp 32 rows x 64 bf16 columns (4 KB), one or two slabs per warp
-  static constexpr int EPI_SLABS = (KIND == KIND_MXFP8 && BN == 256) ? 1 : 2;
-  static constexpr int EPI_BYTES = EPI_SLABS * 4 * 4096;
+  // epilogue staging: per warp 32 rows x 64 bf16 columns (4 KB), one or two slabs per warp.
+  // The 256-wide MXFP8 tile has room for one accumulator only (two would leave no TMEM columns
+  // for the scales), so its epilogue is not hidden behind the next tile's MMAs. Eight epilogue
+  // warps (two per TMEM lane quadrant, half the columns each; EPI_WARPS = 8 is supported) drain
+  // it in half the time, but their slabs cost a pipeline stage: measured 4 % faster on the
+  // grouped expert GEMMs and 5 % slower on the dense ones, so four warps stay.
+  static constexpr bool ONE_ACC = KIND == KIND_MXFP8 && BN == 256;
+  static constexpr int EPI_WARPS = 4;
+  static constexpr int THREADS = 64 + 32 * EPI_WARPS;
+  static constexpr int EPI_SLABS = ONE_ACC ? 1 : 2;
+  static constexpr int EPI_BYTES = EPI_SLABS * EPI_WARPS * 4096;
   static constexpr int BUDGET = 227 * 1024 - 1024 - 256 - 1024 - EPI_BYTES;
   static constexpr int STAGES = BUDGET / STAGE_BYTES > 8 ? 8 : BUDGET / STAGE_BYTES;
   static constexpr int ACC_STAGES = (2 * BN + (KIND == KIND_MXFP8 ? STAGES * 4 * (1 + BN / 128) : 0)) <= 512 ? 2 : 1;
@@ -49,7 +56,8 @@ struct GemmCfg {
   static constexpr int SF_COLS_PER_STAGE = KIND == KIND_MXFP8 ? 4 * (1 + BN / 128) : 0;
   static constexpr int TMEM_COLS = 512;
   static constexpr int UMMA_K = KIND == KIND_BF16 ? 16 : 32;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int EPI_OFFSET = (STAGES * STAGE_BYTES + 1023) / 1024 * 1024;
+  static constexpr int SMEM_BYTES = EPI_OFFSET + EPI_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 struct TileCoord {
@@ -115,7 +123,7 @@ struct TileWalk {
 };
 
 template <int KIND, int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__((GemmCfg<KIND, BN>::THREADS), 1)
 gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
   using Cfg = GemmCfg<KIND, BN>;
   constexpr int STAGES = Cfg::STAGES;
@@ -123,8 +131,8 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the 128B-swizzle atom is 8 rows x 128 bytes.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  static_assert((STAGES * Cfg::STAGE_BYTES) % 1024 == 0, "the epilogue slabs swizzle by address bits 7-9");
-  uint8_t* epi_smem = smem + STAGES * Cfg::STAGE_BYTES;
+  // the epilogue slabs swizzle by address bits 7-9: they start on a 1024-byte boundary
+  uint8_t* epi_smem = smem + Cfg::EPI_OFFSET;
   uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + Cfg::EPI_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + STAGES;
@@ -139,7 +147,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < ACC_STAGES; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+    for (int a = 0; a < ACC_STAGES; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], Cfg::EPI_WARPS); }
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -286,6 +294,9 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
   } else {
     // ------------------------------------------------------------ epilogue
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    // with eight epilogue warps, warps 2-5 take the tile's first half of the columns, 6-9 the second
+    constexpr int EPI_COLS = BN * 4 / Cfg::EPI_WARPS;
+    const int col_begin = ((warp - 2) >> 2) * EPI_COLS;
     TileWalk walk(p, BN);
     int acc = 0; uint32_t acc_phase = 0;
     int epi_round = 0;
@@ -303,15 +314,15 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
       // asynchronous, and the accumulator is released as soon as it has been read
       const bool by_tma = p.tma_store && (p.mode != MODE_GROUPED_ROWS || c.m_end - c.m0 >= BM);
       if (by_tma) {
-        uint8_t* mine = epi_smem + quad * 4096;
+        uint8_t* mine = epi_smem + (warp - 2) * 4096;
         const int out_row0 = (p.mode == MODE_GROUPED_K ? c.group * p.M : 0) + c.m0 + quad * 32;
         // a slab is 32 rows x 128 bytes: 64 bf16 columns, or 32 fp32 columns
         const int slab_cols = p.out_kind == OUT_BF16 ? 64 : 32;
 #pragma unroll 1
-        for (int col = 0; col < BN; col += slab_cols) {
+        for (int col = col_begin; col < col_begin + EPI_COLS; col += slab_cols) {
           const int n = c.n0 + col;
           if (n >= p.N) break;
-          uint8_t* slab = mine + (Cfg::EPI_SLABS == 2 ? (epi_round & 1) * 16384 : 0);
+          uint8_t* slab = mine + (Cfg::EPI_SLABS == 2 ? (epi_round & 1) * (Cfg::EPI_WARPS * 4096) : 0);
           // the store that last read this slab must have finished reading it
           if (lane == 0) {
             if (Cfg::EPI_SLABS == 2) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
@@ -365,7 +376,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
         continue;
       }
 #pragma unroll 1
-      for (int col = 0; col < BN; col += 32) {
+      for (int col = col_begin; col < col_begin + EPI_COLS; col += 32) {
         uint32_t r[32];
         tmem_ld_x32(t_addr + col, r);
         tmem_ld_wait();
@@ -496,7 +507,7 @@ static const char* launch_cfg(const GemmParams& p, int sms, cudaStream_t stream)
       return "cudaFuncSetAttribute(max dynamic shared memory) failed";
     configured = true;
   }
-  kern<<<sms, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(p);
+  kern<<<sms, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? nullptr : "gemm kernel launch failed";
 }
 

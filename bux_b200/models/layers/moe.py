@@ -132,7 +132,12 @@ class MoE(nn.Module):
             choice = scores + self.router_bias
         if c.num_groups > 1:
             choice = limit_groups(choice, c.num_groups, c.top_k_groups)
-        idx = choice.topk(c.top_k, dim=-1).indices
+        if ops.kernels_on(x) and choice.shape[-1] <= 512:
+            from ...ops import kernels as K
+
+            idx = K.topk_rows(choice.detach().float(), c.top_k)  # picks carry no gradient: a plain kernel
+        else:
+            idx = choice.topk(c.top_k, dim=-1).indices
         if ctx.training:
             picks = torch.zeros_like(scores).scatter_add_(-1, idx, torch.ones_like(idx, dtype=scores.dtype))
             w = c.aux_loss_weight

@@ -294,6 +294,16 @@ def sumsq(g, out) -> None:
     _count()
 
 
+def topk_rows(scores: torch.Tensor, k: int) -> torch.Tensor:
+    """Indices [..., k] (int64) of the k largest entries along the last dimension of fp32
+    scores (at most 512 wide), in descending order of value; ties go to the lower index."""
+    flat = scores.reshape(-1, scores.shape[-1]).contiguous()
+    idx = torch.empty(flat.shape[0], k, dtype=torch.int64, device=scores.device)
+    ops().topk_rows(flat, idx)
+    _count()
+    return idx.view(*scores.shape[:-1], k)
+
+
 def gather_rows(x, index, rows: int):
     out = torch.empty(rows, x.shape[-1], dtype=x.dtype, device=x.device)
     ops().gather_rows(x, index, out)

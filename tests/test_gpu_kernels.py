@@ -288,3 +288,18 @@ def test_quantiser_that_computes_the_gated_activation_matches_two_passes(kind, l
     aq, asf, _, _ = K.quant_mxfp8_glu(h, None, kind, limit=limit, up_offset=up_offset)
     back = ref.dequant_mxfp8(aq, ref.unswizzle_scales(asf, rows, f // 32))
     assert rel_err(back, ref_a) < 0.04
+
+
+@pytest.mark.parametrize("n,k", [(128, 8), (32, 4), (200, 6), (512, 32)])
+def test_topk_rows_matches_torch(n, k):
+    from bux_b200.ops import kernels as K
+
+    torch.manual_seed(0)
+    scores = torch.randn(1000, n, device="cuda")
+    scores[3, :5] = float("-inf")          # group-limited routing masks entries out
+    got = K.topk_rows(scores, k)
+    want = scores.topk(k, dim=-1)
+    assert torch.equal(scores.gather(-1, got), want.values)   # same values in the same order
+    assert torch.equal(got, want.indices)                      # distinct random values: same indices
+    ties = torch.zeros(4, n, device="cuda")
+    assert torch.equal(K.topk_rows(ties, k), torch.arange(k, device="cuda").expand(4, k))
