@@ -148,6 +148,45 @@ def bench_memory_bound(rows: list, pk: dict) -> None:
     rows.append({"kernel": "glu_fwd (swiglu)", "shape": "262144x1536", "ms": ms, "gbs": gb / ms * 1e3,
                  "of_peak": gb / ms * 1e3 / pk["hbm_gbs"]})
 
+    def row(name, shape, ms, gb):
+        rows.append({"kernel": name, "shape": shape, "ms": ms, "gbs": gb / ms * 1e3,
+                     "of_peak": gb / ms * 1e3 / pk["hbm_gbs"]})
+
+    # the quantiser on expert-sized inputs: plain, with a row gather and scale, and computing the
+    # gated activation on the way in (bytes: what each variant has to read and write)
+    big = 1 << 19 if SMALL else 1 << 20
+    xs = torch.randn(big, 2048, device=dev).bfloat16()
+    row("quant_mxfp8 row", f"{big}x2048", timed(lambda: K.quant_mxfp8(xs)), xs.numel() * 3.03 / 1e9)
+    row("quant_mxfp8 row+col", f"{big}x2048", timed(lambda: K.quant_mxfp8(xs, rowwise=True, colwise=True)),
+        xs.numel() * 4.06 / 1e9)
+    if not SMALL:
+        tok = torch.randn(big // 8, 2048, device=dev).bfloat16()
+        index = torch.randint(0, big // 8, (big,), device=dev, dtype=torch.int32)
+        scale = torch.rand(big, device=dev)
+        row("quant_mxfp8 row+col, gathered and scaled rows", f"{big}x2048 of {big // 8}",
+            timed(lambda: K.quant_mxfp8(tok, rowwise=True, colwise=True, row_index=index, rows=big, row_scale=scale)),
+            (tok.numel() * 2 + big * 2048 * 2.06) / 1e9)
+        hh = torch.randn(big, 1536, device=dev).bfloat16()
+        row("quant_mxfp8_glu row (activation never written)", f"{big}x1536", timed(lambda: K.quant_mxfp8_glu(hh)),
+            (hh.numel() * 2 + big * 768 * 1.03) / 1e9)
+        dyx = torch.randn_like(x)
+        _, rstd = K.rmsnorm_fwd(x, w, 1e-6)
+        row("rmsnorm_bwd", "131072x2048", timed(lambda: K.rmsnorm_bwd(x, w, dyx, rstd)), x.numel() * 6 / 1e9)
+        q = torch.randn(32, 4096, 32, 128, device=dev).bfloat16()
+        pos = torch.arange(4096, device=dev).float()
+        ang = pos[:, None] / (10000 ** (torch.arange(0, 64, device=dev).float() / 64))[None]
+        cos, sin = ang.cos().repeat(32, 1).contiguous(), ang.sin().repeat(32, 1).contiguous()
+        wq = torch.ones(128, device=dev)
+        _, rq = K.norm_rope_fwd(q, wq, cos, sin, 1e-6)
+        row("norm_rope_fwd", "32x4096x32x128", timed(lambda: K.norm_rope_fwd(q, wq, cos, sin, 1e-6)), q.numel() * 4 / 1e9)
+        dq = torch.randn_like(q)
+        row("norm_rope_bwd", "32x4096x32x128", timed(lambda: K.norm_rope_bwd(q, wq, cos, sin, rq, dq, 1e-6)),
+            q.numel() * 6 / 1e9)
+        sc = torch.randn(131072, 128, device=dev)
+        ms = timed(lambda: K.topk_rows(sc, 8))
+        rows.append({"kernel": "topk_rows k=8", "shape": "131072x128", "ms": ms, "gbs": sc.numel() * 4 / 1e9 / ms * 1e3,
+                     "of_peak": sc.numel() * 4 / 1e9 / ms * 1e3 / pk["hbm_gbs"], "library_ms": timed(lambda: sc.topk(8, dim=-1))})
+
 
 def bench_muon(rows: list, pk: dict) -> None:
     """Muon's Newton–Schulz iteration (five quintic steps) on the framework's GEMM beside the
