@@ -267,11 +267,31 @@ const uint64_t* u64_ptr(const Tensor& t) {
   return reinterpret_cast<const uint64_t*>(t.data_ptr());
 }
 void ep_push_rows(const Tensor& x, const Tensor& src_token, const Tensor& dst_rank, const Tensor& dst_row,
-                  const c10::optional<Tensor>& row_scale, const Tensor& peer_base, int64_t sms) {
+                  const c10::optional<Tensor>& row_scale, const Tensor& peer_base, int64_t sms,
+                  const c10::optional<Tensor>& peer_scale) {
   check_cuda(x, "x");
   c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(!peer_scale.has_value() || row_scale.has_value(), "ep_push_rows: peer_scale needs row_scale");
   bux::ep_push_rows(x.data_ptr(), src_token.data_ptr<int>(), dst_rank.data_ptr<int>(), dst_row.data_ptr<int>(),
-                    opt_f32(row_scale), u64_ptr(peer_base), dst_row.numel(), (int)x.size(-1), (int)sms, stream_of(x));
+                    opt_f32(row_scale), u64_ptr(peer_base), peer_scale.has_value() ? u64_ptr(*peer_scale) : nullptr,
+                    dst_row.numel(), (int)x.size(-1), (int)sms, stream_of(x));
+}
+void row_dots(const Tensor& a, const Tensor& b, Tensor& out) {
+  check_cuda(a, "a"); check_cuda(b, "b");
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && a.is_contiguous() && b.is_contiguous() &&
+              a.dim() == 2 && a.sizes() == b.sizes() && a.size(1) % 8 == 0, "row_dots: two contiguous bf16 [rows, d], d % 8 == 0");
+  TORCH_CHECK(out.scalar_type() == at::kFloat && out.numel() >= a.size(0), "row_dots: fp32 out of at least `rows`");
+  c10::cuda::CUDAGuard guard(a.device());
+  bux::row_dots(a.data_ptr(), b.data_ptr(), out.data_ptr<float>(), a.size(0), (int)a.size(1), stream_of(a));
+}
+void ep_pull_scalar(const Tensor& peer_base, const Tensor& rank_of, const Tensor& row_of, Tensor& out,
+                    const c10::optional<Tensor>& flags, int64_t epoch, const c10::optional<Tensor>& status, double limit_s) {
+  check_cuda(out, "out");
+  TORCH_CHECK(out.scalar_type() == at::kFloat && out.numel() == row_of.numel(), "ep_pull_scalar: fp32 out, one per pick");
+  c10::cuda::CUDAGuard guard(out.device());
+  const int* fl = opt_i32(flags);
+  bux::ep_pull_scalar(u64_ptr(peer_base), rank_of.data_ptr<int>(), row_of.data_ptr<int>(), out.data_ptr<float>(), row_of.numel(),
+                      fl, fl ? (int)flags->numel() : 0, (int)epoch, (uint64_t)(limit_s * 1e9), status_ptr(status), stream_of(out));
 }
 void ep_signal(const Tensor& peer_flags, int64_t channel, int64_t world, int64_t my_rank, int64_t epoch) {
   c10::cuda::CUDAGuard guard(peer_flags.device());
@@ -324,7 +344,9 @@ void ep_wait(const Tensor& flags, int64_t epoch, const c10::optional<Tensor>& st
 }  // namespace
 
 TORCH_LIBRARY(bux_b200, m) {
-  m.def("ep_push_rows(Tensor x, Tensor src_token, Tensor dst_rank, Tensor dst_row, Tensor? row_scale, Tensor peer_base, int sms) -> ()", &ep_push_rows);
+  m.def("ep_push_rows(Tensor x, Tensor src_token, Tensor dst_rank, Tensor dst_row, Tensor? row_scale, Tensor peer_base, int sms, Tensor? peer_scale=None) -> ()", &ep_push_rows);
+  m.def("row_dots(Tensor a, Tensor b, Tensor(a!) out) -> ()", &row_dots);
+  m.def("ep_pull_scalar(Tensor peer_base, Tensor rank_of, Tensor row_of, Tensor(a!) out, Tensor? flags, int epoch, Tensor? status, float limit_s) -> ()", &ep_pull_scalar);
   m.def("ep_signal(Tensor peer_flags, int channel, int world, int my_rank, int epoch) -> ()", &ep_signal);
   m.def("ep_pull_combine(Tensor peer_base, Tensor rank_of, Tensor row_of, Tensor? w, Tensor(a!) out, Tensor? flags, int epoch, Tensor? status, float limit_s) -> ()", &ep_pull_combine);
   m.def("ep_pull_dot(Tensor peer_base, Tensor rank_of, Tensor row_of, Tensor dout, Tensor(a!) dw) -> ()", &ep_pull_dot);

@@ -54,7 +54,9 @@ __device__ __forceinline__ bool wait_flags(const int* flags, int world, int epoc
 __global__ void ep_push_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ src_token,
                                     const int* __restrict__ dst_rank, const int* __restrict__ dst_row,
                                     const float* __restrict__ row_scale, const uint64_t* __restrict__ peer_base,
-                                    long picks, int d) {
+                                    const uint64_t* __restrict__ peer_scale, long picks, int d) {
+  // With `peer_scale` (the peers' fp32 [rows] buffers) a row travels as it is and its scale
+  // is stored beside it on the owner, who applies it later; without, the row is scaled here.
   const int lane = threadIdx.x & 31;
   const int vec = d / 8;
   for (long i = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < picks;
@@ -64,9 +66,10 @@ __global__ void ep_push_rows_kernel(const __nv_bfloat16* __restrict__ x, const i
     const uint4* src = reinterpret_cast<const uint4*>(x + (long)src_token[i] * d);
     uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(peer_base[dst_rank[i]]) + (long)row * d);
     const float s = row_scale ? row_scale[i] : 1.f;
+    if (peer_scale != nullptr && lane == 0) reinterpret_cast<float*>(peer_scale[dst_rank[i]])[row] = s;
     for (int c = lane; c < vec; c += 32) {
       uint4 v = src[c];
-      if (row_scale) {
+      if (row_scale && peer_scale == nullptr) {
         uint32_t* u = &v.x;
 #pragma unroll
         for (int q = 0; q < 4; ++q) { const float2 f = unpack_bf16(u[q]); u[q] = pack_bf16(f.x * s, f.y * s); }
@@ -146,6 +149,47 @@ __global__ void ep_pull_dot_kernel(const uint64_t* __restrict__ peer_base, const
   }
 }
 
+// out[r] = <a[r], b[r]> over rows of d bf16 (one warp per row): the owner's share of the router
+// weights' gradient, from the dy rows it received and the y rows it produced.
+__global__ void row_dots_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
+                                float* __restrict__ out, long rows, int d) {
+  const int lane = threadIdx.x & 31;
+  const int vec = d / 8;
+  for (long i = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < rows;
+       i += (long)gridDim.x * (blockDim.x >> 5)) {
+    const uint4* ar = reinterpret_cast<const uint4*>(a + i * d);
+    const uint4* br = reinterpret_cast<const uint4*>(b + i * d);
+    float dot = 0.f;
+    for (int c = lane; c < vec; c += 32) {
+      const uint4 x = ar[c], y = br[c];
+      const uint32_t* xu = &x.x; const uint32_t* yu = &y.x;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) { const float2 f = unpack_bf16(xu[q]), h = unpack_bf16(yu[q]); dot += f.x * h.x + f.y * h.y; }
+    }
+    dot = warp_sum(dot);
+    if (lane == 0) out[i] = dot;
+  }
+}
+
+// out[i] = peer[rank_of[i]][row_of[i]] (fp32 scalars; 0 for dropped picks), after every peer's flag.
+__global__ void ep_pull_scalar_kernel(const uint64_t* __restrict__ peer_base, const int* __restrict__ rank_of,
+                                      const int* __restrict__ row_of, float* __restrict__ out, long picks,
+                                      const int* __restrict__ flags, int world, int epoch, uint64_t limit_ns,
+                                      Status* st) {
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if (flags != nullptr) {
+    if (!wait_flags(flags, world, epoch, limit_ns, st, 3)) ok_s = 0;
+    __syncthreads();
+    if (!ok_s) return;
+  }
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < picks; i += (long)gridDim.x * blockDim.x) {
+    const int r = row_of[i];
+    out[i] = r >= 0 ? reinterpret_cast<const float*>(peer_base[rank_of[i]])[r] : 0.f;
+  }
+}
+
 // Waits for flags on the stream (used where the consumer is not one of our kernels).
 __global__ void ep_wait_kernel(const int* __restrict__ flags, int world, int epoch, uint64_t limit_ns, Status* st) {
   wait_flags(flags, world, epoch, limit_ns, st, 2);
@@ -222,10 +266,20 @@ static inline int blocks_for(long warps_needed, int warps_per_block, int cap) {
 }
 
 void ep_push_rows(const void* x, const int* src_token, const int* dst_rank, const int* dst_row,
-                  const float* row_scale, const uint64_t* peer_base, long picks, int d, int sms, cudaStream_t s) {
+                  const float* row_scale, const uint64_t* peer_base, const uint64_t* peer_scale, long picks, int d,
+                  int sms, cudaStream_t s) {
   // a modest number of CTAs keeps most SMs free for the GEMMs that run beside the exchange
   ep_push_rows_kernel<<<blocks_for(picks, 8, sms > 0 ? sms * 4 : 148 * 4), 256, 0, s>>>(
-      (const __nv_bfloat16*)x, src_token, dst_rank, dst_row, row_scale, peer_base, picks, d);
+      (const __nv_bfloat16*)x, src_token, dst_rank, dst_row, row_scale, peer_base, peer_scale, picks, d);
+}
+void row_dots(const void* a, const void* b, float* out, long rows, int d, cudaStream_t s) {
+  row_dots_kernel<<<blocks_for(rows, 8, 148 * 8), 256, 0, s>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b, out, rows, d);
+}
+void ep_pull_scalar(const uint64_t* peer_base, const int* rank_of, const int* row_of, float* out, long picks,
+                    const int* flags, int world, int epoch, uint64_t limit_ns, Status* st, cudaStream_t s) {
+  int grid = (int)((picks + 255) / 256 > 148 * 4 ? 148 * 4 : (picks + 255) / 256);
+  ep_pull_scalar_kernel<<<grid < 1 ? 1 : grid, 256, 0, s>>>(peer_base, rank_of, row_of, out, picks, flags, world, epoch,
+                                                           limit_ns, st);
 }
 void ep_signal(const uint64_t* peer_flags, int channel, int world, int my_rank, int epoch, cudaStream_t s) {
   ep_signal_kernel<<<1, 32, 0, s>>>(peer_flags, channel, world, my_rank, epoch);

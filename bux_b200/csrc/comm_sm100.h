@@ -8,7 +8,13 @@ namespace bux {
 struct Status;
 
 void ep_push_rows(const void* x, const int* src_token, const int* dst_rank, const int* dst_row,
-                  const float* row_scale, const uint64_t* peer_base, long picks, int d, int sms, cudaStream_t s);
+                  const float* row_scale, const uint64_t* peer_base, const uint64_t* peer_scale, long picks, int d,
+                  int sms, cudaStream_t s);
+// out[r] = <a[r], b[r]> over rows of d bf16
+void row_dots(const void* a, const void* b, float* out, long rows, int d, cudaStream_t s);
+// out[i] = peer[rank_of[i]][row_of[i]] (fp32), after the peers' flags reached `epoch`
+void ep_pull_scalar(const uint64_t* peer_base, const int* rank_of, const int* row_of, float* out, long picks,
+                    const int* flags, int world, int epoch, uint64_t limit_ns, Status* st, cudaStream_t s);
 void ep_signal(const uint64_t* peer_flags, int channel, int world, int my_rank, int epoch, cudaStream_t s);
 void ep_pull_combine(const uint64_t* peer_base, const int* rank_of, const int* row_of, const float* w, void* out,
                      long tokens, int k, int d, const int* flags, int world, int epoch, uint64_t limit_ns,

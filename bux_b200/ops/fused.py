@@ -330,14 +330,18 @@ class _ExpertsOnSorted(torch.autograd.Function):
         e, f2, d = w_gu.shape
         f = f2 // 2
         kind = K.KIND_MXFP8 if mx else K.KIND_BF16
+        dy_scale = None
         if io is not None:
             dy = io.before_backward(dy)
+            dy_scale = io.dy_scale(dy.shape[0])  # the rows' weights, applied here (they arrived unscaled)
         if counts is not None:
             K.zero_pad_rows(dy, offsets, counts)
+        if dy_scale is not None and not mx:
+            dy = (dy.float() * dy_scale.unsqueeze(-1)).to(dy.dtype)
         g_gu = getattr(w_gu, "main_grad", None)
         g_down = getattr(w_down, "main_grad", None)
         if mx:
-            dyq, dysf, dytq, dytsf = K.quant_mxfp8(dy, rowwise=True, colwise=True)
+            dyq, dysf, dytq, dytsf = K.quant_mxfp8(dy, rowwise=True, colwise=True, row_scale=dy_scale)
             _, _, atq, atsf = K.quant_mxfp8_glu(h, None, act, rowwise=False, colwise=True,
                                                 limit=limit, up_offset=up_offset)
             dw_down = K.grouped_gemm_k(dytq, atq, offsets, d, f, kind=kind, asf=dytsf, bsf=atsf,

@@ -361,8 +361,11 @@ def attn_bwd(q, k, v, o, do, lse, *, causal=True, window=0, sinks=None, scale=No
 
 
 # ------------------------------------------------------------------ expert-parallel exchange
-def ep_push_rows(x, src_token, dst_rank, dst_row, peer_base, row_scale=None, sms: int = 0) -> None:
-    ops().ep_push_rows(x, src_token, dst_rank, dst_row, row_scale, peer_base, sms)
+def ep_push_rows(x, src_token, dst_rank, dst_row, peer_base, row_scale=None, sms: int = 0, peer_scale=None) -> None:
+    """Row i of the picks (x[src_token[i]]) → row dst_row[i] of rank dst_rank[i]'s buffer.
+    With `row_scale` the row is multiplied on the way; with `peer_scale` as well (the peers'
+    fp32 [rows] buffers) it travels unscaled and the scale is stored beside it instead."""
+    ops().ep_push_rows(x, src_token, dst_rank, dst_row, row_scale, peer_base, sms, peer_scale)
     _count()
 
 
@@ -384,6 +387,23 @@ def ep_pull_dot(peer_base, rank_of, row_of, dout):
     ops().ep_pull_dot(peer_base, rank_of, row_of, dout, dw)
     _count()
     return dw
+
+
+def row_dots(a, b, out=None):
+    """out[r] = <a[r], b[r]> in fp32 over bf16 rows."""
+    if out is None:
+        out = torch.empty(a.shape[0], dtype=torch.float32, device=a.device)
+    ops().row_dots(a, b, out)
+    _count()
+    return out
+
+
+def ep_pull_scalar(peer_base, rank_of, row_of, flags=None, epoch: int = 0, limit_s: float = 5.0):
+    """out[t, j] = the fp32 value at row row_of[t, j] of rank rank_of[t, j]'s buffer."""
+    out = torch.empty(row_of.shape, dtype=torch.float32, device=row_of.device)
+    ops().ep_pull_scalar(peer_base, rank_of, row_of, out, flags, epoch, status_word(row_of.device), limit_s)
+    _count()
+    return out
 
 
 def ep_wait(flags, epoch: int, limit_s: float = 5.0) -> None:

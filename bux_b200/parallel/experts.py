@@ -7,8 +7,10 @@ Two methods (``methods(moe=...)``):
   owner's expert-sorted receive buffer + epoch flags; the owner's first grouped GEMM
   waits for the flags in its TMA producer warp; combine = P2P loads of the expert
   outputs where they were produced, weighted and summed per token. The backward
-  mirrors it (push w·dout, pull dx, pull-dot for the router weights). No NCCL call
-  moves a token; one tiny all-gather moves the per-expert counts.
+  mirrors it: dout rows are pushed to the owners with their weights beside them, each
+  owner takes the dot products of its dy and y rows for the router weights' gradient
+  (only those scalars cross NVLink again) and applies the weights as it quantises; dx is
+  pulled. No NCCL call moves a token; one tiny all-gather moves the per-expert counts.
 * ``all_to_all`` (also ``nccl_ep`` / ``ragged_all_to_all``, which keep their meaning of
   "library collective"): the same layout through ``torch.distributed.all_to_all_single``,
   the measured baseline and the CPU/gloo path of the tests.
@@ -30,7 +32,7 @@ import torch.distributed as dist
 from ..ops import fused
 
 ALIGN = 128
-CH_X, CH_Y, CH_DY, CH_DX = 0, 1, 2, 3
+CH_X, CH_Y, CH_DY, CH_DX, CH_DOT = 0, 1, 2, 3, 4
 
 
 @dataclass
@@ -103,12 +105,18 @@ class FusedEP:
             buf.zero_()
             self.bufs[key] = buf
             self.tables[key] = torch.tensor([int(p) for p in hdl.buffer_ptrs], dtype=torch.int64, device=device)
+        for key in ("dys", "dots"):  # per-row fp32: the weight of a pushed dy row, and <dy, y> of a row
+            buf = symm.empty(cap_rows, dtype=torch.float32, device=device)
+            hdl = symm.rendezvous(buf, name)
+            buf.zero_()
+            self.bufs[key] = buf
+            self.tables[key] = torch.tensor([int(p) for p in hdl.buffer_ptrs], dtype=torch.int64, device=device)
         flags = symm.empty(8 * self.world, dtype=torch.int32, device=device)
         fh = symm.rendezvous(flags, name)
         flags.zero_()
         self.flags = flags.view(8, self.world)
         self.peer_flags = torch.tensor([int(p) for p in fh.buffer_ptrs], dtype=torch.int64, device=device)
-        self.epoch = [0, 0, 0, 0]
+        self.epoch = [0, 0, 0, 0, 0]
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
 
@@ -151,6 +159,10 @@ class _IO:
         K.ep_wait(self.ep.flags[CH_DY], self.ep.epoch[CH_DY])
         return dy
 
+    def dy_scale(self, rows):
+        """The weights of the dy rows, which arrived unscaled: the expert stack applies them."""
+        return self.ep.bufs["dys"][:rows]
+
     def dx_out(self, rows, d):
         return self.ep.bufs["dx"][:rows]
 
@@ -187,10 +199,17 @@ class _Combine(torch.autograd.Function):
     dw by a pulled dot product, and w·dout pushed into the owners' dy buffers."""
 
     @staticmethod
-    def forward(ctx, y, weights, ep: FusedEP, r: Route, tokens: int, values_unused: bool = False):
+    def forward(ctx, y, weights, ep: FusedEP, r: Route, tokens: int, values_unused: bool = False,
+                y_stays: bool = False):
         from ..ops import kernels as K
 
         w = weights.float().contiguous()
+        # the backward takes <dout row, y row> on this rank: y lives in the shared exchange
+        # buffer, which the next MoE layer overwrites, so it is copied unless the caller says
+        # that the backward runs before anything else uses the buffer (a checkpointed replay)
+        ctx.y_rows = None
+        if any(ctx.needs_input_grad) and not y_stays:
+            ctx.y_rows = y.detach().clone()
         ctx.y_epoch = ep.epoch[CH_Y]
         if values_unused:
             # the replay of a checkpointed block whose last op this is: only the graph is
@@ -210,12 +229,20 @@ class _Combine(torch.autograd.Function):
         (w,) = ctx.saved_tensors
         ep, r = ctx.ep, ctx.r
         dout = dout.contiguous()
-        K.ep_wait(ep.flags[CH_Y], ctx.y_epoch)   # the owners' rows of this forward are complete
-        dw = K.ep_pull_dot(ep.tables["y"], r.rank_of, r.row_of, dout)
+        # dout rows go to the owners as they are, each with its weight beside it
         scale = w.reshape(-1)[r.order].contiguous()
-        K.ep_push_rows(dout, r.src_token, r.dst_rank, r.dst_row, ep.tables["dy"], row_scale=scale)
-        ep.signal(CH_DY)
-        return ep.bufs["dy"][:ctx.rows], dw.to(ctx.wdtype), None, None, None, None
+        K.ep_push_rows(dout, r.src_token, r.dst_rank, r.dst_row, ep.tables["dy"], row_scale=scale,
+                       peer_scale=ep.tables["dys"])
+        e_dy = ep.signal(CH_DY)
+        # as an owner: <dout row, y row> of every row that arrived here (y is this rank's own
+        # output), so that only one scalar per pick crosses NVLink for the router's gradient
+        K.ep_wait(ep.flags[CH_DY], e_dy)
+        y_rows = ctx.y_rows if ctx.y_rows is not None else ep.bufs["y"][:ctx.rows]
+        K.row_dots(ep.bufs["dy"][:ctx.rows], y_rows, ep.bufs["dots"])
+        ctx.y_rows = None
+        e_dot = ep.signal(CH_DOT)
+        dw = K.ep_pull_scalar(ep.tables["dots"], r.rank_of, r.row_of, flags=ep.flags[CH_DOT], epoch=e_dot)
+        return ep.bufs["dy"][:ctx.rows], dw.to(ctx.wdtype), None, None, None, None, None
 
 
 # ====================================================================== library all-to-all
@@ -330,7 +357,8 @@ class ExpertParallel:
             io = _IO(ep, ep.epoch[CH_X])
             y = fused.experts_on_sorted(xs, r.offsets, r.counts, moe.experts_gate_up, moe.experts_down,
                                         io=io, **kw)
-            return _Combine.apply(y, weights, ep, r, t, bool(getattr(ctx, "tail_values_unused", False)))
+            return _Combine.apply(y, weights, ep, r, t, bool(getattr(ctx, "tail_values_unused", False)),
+                                  bool(getattr(ctx, "exchange_buffers_stay", False)))
         rows = x[r.src_token.long()]
         xs = _A2A.apply(rows, r.dst_rank, r.dst_row, self.group, cap)
         y = fused.experts_on_sorted(xs, r.offsets, r.counts, moe.experts_gate_up, moe.experts_down, **kw)

@@ -60,8 +60,8 @@ def _worker(rank, world, port, overrides, out):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("fmt", ["compute", "mxfp8"])
-def test_fused_expert_parallel_matches_one_gpu(cuda, tmp_path, fmt):
+@pytest.mark.parametrize("fmt,remat", [("compute", "full"), ("mxfp8", "full"), ("mxfp8", "none")])
+def test_fused_expert_parallel_matches_one_gpu(cuda, tmp_path, fmt, remat):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
@@ -70,13 +70,15 @@ def test_fused_expert_parallel_matches_one_gpu(cuda, tmp_path, fmt):
     from bux_b200.train.trainer import Trainer
 
     prec = f"precision = precision(compute=bfloat16, matmuls={fmt})"
-    run = compile_runs(MOE, filename="p.bux", overrides=[prec])[0]
+    # without checkpointing no replay refills the exchange buffers before a layer's backward
+    keep = f"methods.remat = {remat}"
+    run = compile_runs(MOE, filename="p.bux", overrides=[prec, keep])[0]
     tr = Trainer(run, device=cuda)
     feed = iter(tr.batches())
     want = [tr.train_step(next(feed))["loss"].item() for _ in range(2)]
     state = {n: p.detach().float().cpu() for n, p in tr.model.named_parameters()}
     out = str(tmp_path / "r0.pt")
-    mp.spawn(_worker, args=(2, _free_port(), [prec, "mesh = mesh(expert=2)", "methods.moe = fused_ep",
+    mp.spawn(_worker, args=(2, _free_port(), [prec, keep, "mesh = mesh(expert=2)", "methods.moe = fused_ep",
                                               "methods.capacity = 2.0"], out), nprocs=2, join=True)
     got = torch.load(out)
     assert got["losses"] == pytest.approx(want, abs=3e-2)
