@@ -102,6 +102,9 @@ def main() -> int:
                     help="debug only: fewer layers (the result is then marked invalid)")
     ap.add_argument("--rows", type=int, default=ROWS_PER_GPU, help="rows of 4096 tokens per GPU per step")
     ap.add_argument("--seq-len", type=int, default=4096)
+    ap.add_argument("--host-rest", action="store_true",
+                    help="blocks whose attention outputs do not fit the device send them to pinned host memory "
+                         "(with host-offloaded block inputs only)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -185,7 +188,7 @@ def main() -> int:
         dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
         keep_blocks = int(agreed.item())
     if keep_blocks:
-        trainer.model.set_remat(True, offload=tight, keep_attention=keep_blocks)
+        trainer.model.set_remat(True, offload=tight, keep_attention=keep_blocks, kept_to_host=args.host_rest and tight)
     try:
         for _ in range(args.warmup):
             one_step(True)
@@ -256,6 +259,7 @@ def main() -> int:
                        "optimizer": "adamw, bf16 master, " + ("8-bit block-scaled moments" if tight else "bf16 moments")
                                     + ", expert updates fused into the backward, clip by the previous step's norm",
                        "remat": f"per block, attention outputs kept on the device for {keep_blocks} of {blocks} blocks"
+                       + (", the others in pinned host memory" if args.host_rest and tight and 0 < keep_blocks < blocks else "")
                        + (", block inputs in pinned host memory" if tight else ""),
                        "peak_mem_gb": round(torch.cuda.max_memory_allocated(device) / 1e9, 1), "l2": "inputs and weights exceed L2 (126 MB) every step",
                        "loss_last_step": loss},

@@ -29,7 +29,7 @@ namespace bux {
 constexpr int KID_GEMM = 1;
 constexpr int BM = 128;
 
-template <int KIND, int BN>
+template <int KIND, int BN, int EW = 4>
 struct GemmCfg {
   // bytes of K per stage row: 128 for both kinds (64 bf16 or 128 fp8)
   static constexpr int BK_ELEMS = KIND == KIND_BF16 ? 64 : 128;
@@ -41,11 +41,11 @@ struct GemmCfg {
   // epilogue staging: per warp 32 rows x 64 bf16 columns (4 KB), one or two slabs per warp.
   // The 256-wide MXFP8 tile has room for one accumulator only (two would leave no TMEM columns
   // for the scales), so its epilogue is not hidden behind the next tile's MMAs. Eight epilogue
-  // warps (two per TMEM lane quadrant, half the columns each; EPI_WARPS = 8 is supported) drain
-  // it in half the time, but their slabs cost a pipeline stage: measured 4 % faster on the
-  // grouped expert GEMMs and 5 % slower on the dense ones, so four warps stay.
+  // warps (EW = 8: two per TMEM lane quadrant, half the columns each) drain it in half the
+  // time, but their slabs cost a pipeline stage: measured 4 % faster on the grouped expert
+  // GEMMs and 5 % slower on the dense ones, so the launcher takes eight for grouped rows only.
   static constexpr bool ONE_ACC = KIND == KIND_MXFP8 && BN == 256;
-  static constexpr int EPI_WARPS = 4;
+  static constexpr int EPI_WARPS = EW;
   static constexpr int THREADS = 64 + 32 * EPI_WARPS;
   static constexpr int EPI_SLABS = ONE_ACC ? 1 : 2;
   static constexpr int EPI_BYTES = EPI_SLABS * EPI_WARPS * 4096;
@@ -122,10 +122,10 @@ struct TileWalk {
   }
 };
 
-template <int KIND, int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__((GemmCfg<KIND, BN>::THREADS), 1)
+template <int KIND, int BN, bool A_MN, bool B_MN, int EW = 4>
+__global__ void __launch_bounds__((GemmCfg<KIND, BN, EW>::THREADS), 1)
 gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
-  using Cfg = GemmCfg<KIND, BN>;
+  using Cfg = GemmCfg<KIND, BN, EW>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int ACC_STAGES = Cfg::ACC_STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -497,10 +497,10 @@ const char* make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uin
   return msg;
 }
 
-template <int KIND, int BN, bool A_MN, bool B_MN>
+template <int KIND, int BN, bool A_MN, bool B_MN, int EW = 4>
 static const char* launch_cfg(const GemmParams& p, int sms, cudaStream_t stream) {
-  using Cfg = GemmCfg<KIND, BN>;
-  auto kern = gemm_sm100_kernel<KIND, BN, A_MN, B_MN>;
+  using Cfg = GemmCfg<KIND, BN, EW>;
+  auto kern = gemm_sm100_kernel<KIND, BN, A_MN, B_MN, EW>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
@@ -557,6 +557,8 @@ const char* gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   BUX_GEMM_CASE(KIND_BF16, 128, true, false)
   BUX_GEMM_CASE(KIND_BF16, 128, true, true)
   BUX_GEMM_CASE(KIND_MXFP8, 128, false, false)
+  if (a.kind == KIND_MXFP8 && bn == 256 && a.mode == MODE_GROUPED_ROWS)
+    return launch_cfg<KIND_MXFP8, 256, false, false, 8>(p, sms, stream);
   BUX_GEMM_CASE(KIND_MXFP8, 256, false, false)
 #undef BUX_GEMM_CASE
   return "no gemm kernel for this configuration";

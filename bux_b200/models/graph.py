@@ -125,10 +125,13 @@ class Repeated(nn.Module):
         for i, item in enumerate(self.items):
             if (self.remat and ctx.training and torch.is_grad_enabled() and isinstance(x, torch.Tensor)
                     and x.requires_grad):
-                keep = self.keep_attention
+                keep, to_host = self.keep_attention, self.kept_to_host
                 if keep is not True and keep is not False:
-                    keep = i >= len(self.items) - int(keep)
-                x = _checkpointed(item, x, ctx, self.offload, (id(self), i), keep, self.kept_to_host)
+                    on_device = i >= len(self.items) - int(keep)
+                    # the last `keep` passes hold their outputs on the device; with `kept_to_host`
+                    # the earlier ones send theirs after their inputs to pinned host memory
+                    keep, to_host = (on_device or to_host), (to_host and not on_device)
+                x = _checkpointed(item, x, ctx, self.offload, (id(self), i), keep, to_host)
             else:
                 x = item(x, ctx)
         return x
