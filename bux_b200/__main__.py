@@ -155,12 +155,12 @@ def _dispatch(args) -> int:
             print(render(r.arch))
         return 0
     if cmd == "train":
-        from .runtime import configure
-        from .train.trainer import train
+        # one process, or one rank of a job started by torchrun / srun / mpirun: `train_here`
+        # joins the job the environment describes and shards the run over its mesh
+        from .launch import train_here
 
-        configure()
         for run in _runs(args):
-            train(run, out=args.out, cache=args.cache, device=args.device, quiet=args.quiet)
+            train_here(run, out=args.out, cache=args.cache, device=args.device, quiet=args.quiet)
         return 0
     if cmd == "launch":
         from .launch import launch

@@ -71,8 +71,15 @@ class Log(Hook):
         tokens = int(host.get("tokens", trainer.tokens))
         dt = max(now - (self.last_time or now), 1e-9)
         steps = max(step - self.last_step, 1)
-        host["tokens_per_s"] = (tokens - self.last_tokens) / dt
-        host["time/step_ms"] = dt / steps * 1000
+        rate, step_ms = (tokens - self.last_tokens) / dt, dt / steps * 1000
+        previous = getattr(self, "previous", None)
+        if previous is not None and step_ms < 0.05 * previous[1]:
+            # the last step's scalars are read right after the step before it was logged (the
+            # log runs one step behind): no time has passed, so the earlier rate stands
+            rate, step_ms = previous
+        self.previous = (rate, step_ms)
+        host["tokens_per_s"] = rate
+        host["time/step_ms"] = step_ms
         host.update(trainer.timers.flush())
         world = trainer.parallel.world if trainer.parallel is not None else 1
         if self.flops_per_token and self.peak:
