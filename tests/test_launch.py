@@ -78,3 +78,28 @@ def test_sigterm_stops_after_the_step_with_a_checkpoint(tmp_path):
     assert st["state"] == "stopped" and 0 < st["step"] < 100000
     saved = [p.name for p in (status.parent / "checkpoints").iterdir()]
     assert str(st["step"]) in saved
+
+
+def _free_port() -> int:
+    import socket
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_train_joins_the_job_torchrun_describes(tmp_path):
+    """`bux train` under torchrun is one sharded job, not a copy of the run per rank: two
+    gloo ranks report a world of two and each holds half the parameters."""
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+           "-m", "bux_b200", "train", str(SMOKE), "steps = 3", "schedule = constant", "mesh = mesh(fsdp=2)",
+           "--device", "cpu", "--out", str(tmp_path)]
+    env = dict(os.environ, PYTHONPATH=str(ROOT))
+    done = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, cwd=tmp_path,
+                          timeout=240, text=True)
+    assert done.returncode == 0, done.stdout[-2000:]
+    assert "on 2 × cpu" in done.stdout
+    assert "78k parameters" in done.stdout       # the 156k-parameter model, sharded over two ranks
+    (status,) = list(tmp_path.glob("*/status.json"))
+    assert json.loads(status.read_text())["state"] == "done"
