@@ -108,6 +108,28 @@ class Pipeline:
                 graph.items[i] = _Skip()
         self.table = S.TABLES[t.methods.pipeline](self.stages, max(1, t.methods.microbatches))[self.stage]
         self.ranks = [dist.get_global_rank(self.group, i) for i in range(self.stages)]
+        self._pair_groups()
+
+    def _pair_groups(self) -> None:
+        """One communicator per pair of neighbouring stages and per direction. NCCL matches
+        the point-to-point operations of a pair in the order each side issued them, and a
+        send waits on the device for its receive: with activations and gradients on one
+        communicator, 1F1B makes both stages send at once (stage s its next activation,
+        stage s+1 its first input gradient) and neither receive is ever posted. On their own
+        communicators each direction is a plain sequence of sends on one side and receives
+        on the other, in the same order. Every rank creates every group (a collective)."""
+        everyone = [None] * dist.get_world_size()
+        dist.all_gather_object(everyone, tuple(self.ranks))
+        self.fwd_next = self.fwd_prev = self.bwd_next = self.bwd_prev = None
+        me = dist.get_rank()
+        for ranks in sorted(set(everyone)):
+            for a, b in zip(ranks[:-1], ranks[1:]):
+                fwd = dist.new_group([a, b])
+                bwd = dist.new_group([a, b])
+                if me == a:
+                    self.fwd_next, self.bwd_next = fwd, bwd
+                if me == b:
+                    self.fwd_prev, self.bwd_prev = fwd, bwd
 
     # ------------------------------------------------------------------ one step
     def run(self, trainer, micro: list, inv_count, n_micro: int, world: int):
@@ -138,7 +160,7 @@ class Pipeline:
                     x_in = None
                 else:
                     x_in = torch.empty(ids.shape[0], ids.shape[1], d, dtype=dtype, device=dev)
-                    dist.recv(x_in, src=prv)
+                    dist.recv(x_in, src=prv, group=self.fwd_prev)
                     x_in.requires_grad_(True)
                     x = x_in
                 x = self.repeat(x, ctx)
@@ -153,7 +175,7 @@ class Pipeline:
                     held[m] = (x_in, loss, None)
                 else:
                     y = x.contiguous()
-                    sends.append(dist.isend(y.detach(), dst=nxt))
+                    sends.append(dist.isend(y.detach(), dst=nxt, group=self.fwd_next))
                     aux = [v for v in ctx.losses.values()]
                     held[m] = (x_in, y, aux)
             elif op == "B":
@@ -162,7 +184,7 @@ class Pipeline:
                     out.backward()
                 else:
                     dy = torch.empty_like(out)
-                    dist.recv(dy, src=nxt)
+                    dist.recv(dy, src=nxt, group=self.bwd_next)
                     outs, grads = [out], [dy]
                     for a in aux or ():
                         if a.requires_grad:  # auxiliary losses of this stage's layers
@@ -170,7 +192,7 @@ class Pipeline:
                             grads.append(torch.ones_like(a))
                     torch.autograd.backward(outs, grads)
                 if x_in is not None:
-                    sends.append(dist.isend(x_in.grad.contiguous(), dst=prv))
+                    sends.append(dist.isend(x_in.grad.contiguous(), dst=prv, group=self.bwd_prev))
             # "W": the weight gradients were produced with the input gradients (autograd
             # does not split a block's backward), so the slot is a no-op here
         for h in sends:
