@@ -61,8 +61,6 @@ def relative_bias(r: torch.Tensor, table: torch.Tensor, t: int) -> torch.Tensor:
 class GQA(nn.Module):
     def __init__(self, c: L.GQAConfig, b: BuildContext):
         super().__init__()
-        if c.paired:
-            raise NotImplementedError("gqa(paired=...) is not built in this framework yet")
         self.c = c
         width = b.width if isinstance(b.width, int) else b.d_model
         ports = tuple(b.ports or ())
@@ -162,6 +160,40 @@ class GQA(nn.Module):
             x = ref.rope(x, cos, sin, interleaved=c.rope.layout == "interleaved")
         return x
 
+    def _norm_rope_paired(self, x, norm: Optional[Norm], ctx: Context):
+        """Paired heads: head i of the token at position p is turned at 2p + (i mod 2)
+        (``attention/gqa.py:664-681`` there); the norm is each head's own, as without pairs."""
+        c = self.c
+        if norm is not None:
+            x = norm(x.flatten(-2), ctx).view_as(x) if c.qk_norm_all_heads else norm(x, ctx)
+        if c.rope is None:
+            return x
+        bsz, t, n, d = x.shape
+        halves = x.reshape(bsz, t, n // 2, 2, d)
+        turned = []
+        for i in (0, 1):
+            cos, sin = rope_lib.tables(2 * ctx.positions + i, self.inv_freq, self.rope_gain)
+            turned.append(ref.rope(halves[..., i, :], cos, sin, interleaved=c.rope.layout == "interleaved"))
+        return torch.stack(turned, 3).reshape(bsz, t, n, d)
+
+    def _attend_paired(self, q, k, v, ctx: Context):
+        """Heads j and j + n/2 interleaved along the sequence into one of twice the length
+        (position 2p: the first half of the heads of token p, 2p + 1: the second half), so a
+        query sees both heads' keys in one softmax; a window counts interleaved positions
+        (``attention/gqa.py:731-747`` there)."""
+        c = self.c
+        bsz, t, h, _ = q.shape
+
+        def pair(a):
+            return a.reshape(bsz, 2 * t, a.shape[2] // 2, a.shape[3])
+
+        segments = None
+        if ctx.segments is not None:
+            segments = ctx.segments.repeat_interleave(2, dim=1)
+        out = ops.attention(pair(q), pair(k), pair(v), causal=True, window=c.sliding_window_size,
+                            softcap=c.softcap, scale=c.scale, segments=segments)
+        return out.reshape(bsz, t, h, -1)
+
     def forward(self, x, ctx: Context):
         c = self.c
         qkv = self.qkv(x, ctx)
@@ -189,15 +221,18 @@ class GQA(nn.Module):
                 v = self._mix_values(v, ctx.read(port.tap, port.mode == "pop"))
             elif port.name == "kv" and port.mode != "write":
                 k, v = ctx.read(port.tap, port.mode == "pop")
-        q = self._norm_rope(q, getattr(self, "q_norm", None), ctx)
+        rotate = self._norm_rope_paired if c.paired else self._norm_rope
+        q = rotate(q, getattr(self, "q_norm", None), ctx)
         if c.power_scale is not None:
             q = (q.float() * power_scale(ctx.positions, c.power_scale, c.power_scale_length)[..., None, None]).to(q.dtype)
         kv_shared = any(p.name == "kv" and p.mode != "write" for p in self.ports)
         if not kv_shared:
-            k = self._norm_rope(k, getattr(self, "k_norm", None), ctx)
+            k = rotate(k, getattr(self, "k_norm", None), ctx)
         for port in self.ports:
             if port.mode == "write":
                 ctx.push(port.tap, v if port.name == "v" else (k, v))
+        if c.paired:
+            return self._finish(self._attend_paired(q, k, v, ctx), x, v, bsz, t, ctx)
         if c.indexer is not None:
             out = self._sparse(x, q, k, v, ctx)
             return self._finish(out, x, v, bsz, t, ctx)

@@ -195,6 +195,7 @@ def shard_model(model: nn.Module, par) -> None:
             extras = [name for name in ("lambda_proj", "xsa_alpha", "k_conv", "rel_proj", "gate_up", "gate_bias",
                                         "output_gate_down", "cross_gate", "ve_gate", "v_norm") if hasattr(m, name)]
             _need(not extras, f"gqa with {', '.join(extras)} is not split over tensor ranks yet")
+            _need(not m.c.paired, "gqa(paired=true) is not split over tensor ranks yet")
             pieces = [m.q_rows, m.k_rows, m.v_rows]
             split(m.qkv, "weight", 0, pieces, r, n, layout)
             split(m.qkv, "bias", 0, pieces, r, n, layout)

@@ -140,3 +140,29 @@ def test_value_embedding_gate_starts_open():
         layer.ve_gate.weight.zero_()
     v, e, x = torch.randn(2, 32, 2, 8), torch.randn(2, 32, 16), torch.randn(2, 32, 32)
     assert torch.allclose(layer._add_value_embedding(x, v, e, _ctx()), v + e.view(2, 32, 2, 8))
+
+
+def test_paired_heads_share_one_softmax():
+    """Paired attention is plain causal attention over the sequence with heads j and j + h/2
+    interleaved: checked against a direct statement for one token pair ordering."""
+    tr = _train("gqa(num_heads=4, num_kv_heads=2, rope=rope(), paired=true, sliding_window_size=16)")
+    layer = _layers(tr)[0]
+    torch.manual_seed(0)
+    b, t, h, g, d = 1, 6, 4, 2, 8
+    q, k, v = torch.randn(b, t, h, d), torch.randn(b, t, g, d), torch.randn(b, t, g, d)
+    layer.c = layer.c.model_copy(update={"sliding_window_size": None})
+    got = layer._attend_paired(q, k, v, _ctx(b, t))
+    # by hand: query head j (j < 2) of token p sits at 2p, head j + 2 at 2p + 1; kv head m at 2p, m + 1 at 2p + 1
+    for j in range(2):            # query head in the interleaved layout (2 of them), kv head 0 serves both
+        for p in range(t):
+            for second in (0, 1):
+                head = j + 2 * second
+                qq = q[0, p, head]
+                keys, vals = [], []
+                for s_pos in range(2 * p + second + 1):
+                    tok, half = divmod(s_pos, 2)
+                    keys.append(k[0, tok, half])   # one kv head per half (g / 2 = 1)
+                    vals.append(v[0, tok, half])
+                logits = torch.stack(keys) @ qq * d ** -0.5
+                want = torch.softmax(logits, 0) @ torch.stack(vals)
+                assert torch.allclose(got[0, p, head], want, atol=1e-5), (j, p, second)
