@@ -33,11 +33,16 @@ class MLA(nn.Module):
 
     def __init__(self, c: L.MLAConfig, b: BuildContext):
         super().__init__()
-        if c.indexer is not None:
-            raise NotImplementedError("mla(indexer=...) is not built in this framework yet")
         self.c = c
         width = b.width if isinstance(b.width, int) else b.d_model
         h, n, r, dv = c.num_heads, c.qk_nope_head_dim, c.qk_rope_head_dim, c.v_head_dim
+        self.ports = tuple(b.ports or ())
+        if c.indexer is not None and not any(p.name == "index" and p.mode != "write" for p in self.ports):
+            from .sparse import Indexer
+
+            # DeepSeek sparse attention on MLA: a lightning indexer of its own picks the keys,
+            # unless the layer reads another layer's picks through the `index` port
+            self.indexer = Indexer(c.indexer, width, c.rope, r, b)
         self.h, self.n, self.r, self.dv, self.rank = h, n, r, dv, c.kv_lora_rank
         latent = c.q_lora_rank
         rms = L.NormalizationConfig(type="rmsnorm")
@@ -77,9 +82,35 @@ class MLA(nn.Module):
             q, k = self.q_norm(q, ctx), self.k_norm(k, ctx)
         q, k = self._rotate(q, ctx), self._rotate(k, ctx)
         scale = c.scale if c.scale is not None else (n + r) ** -0.5
-        out = ops.attention(q, k, v, causal=True, window=c.sliding_window_size, sinks=None,
-                            softcap=c.softcap, scale=scale, segments=ctx.segments)
+        if c.indexer is not None:
+            out = self._sparse(x, q, k, v, scale, ctx)
+        else:
+            out = ops.attention(q, k, v, causal=True, window=c.sliding_window_size, sinks=None,
+                                softcap=c.softcap, scale=scale, segments=ctx.segments)
         return self.o(out.reshape(bsz, t, h * dv), ctx)
+
+    def _sparse(self, x, q, k, v, scale, ctx: Context):
+        """Attention over the keys the indexer kept (its own, or another layer's through the
+        ``index`` port), and the indexer's distillation loss: the dense statement, as `gqa`'s."""
+        from . import sparse as S
+
+        c = self.c
+        t = q.shape[1]
+        seen = S.seen_mask(ctx, t, c.sliding_window_size)
+        reads = [p for p in self.ports if p.name == "index" and p.mode != "write"]
+        scores = None
+        if reads:
+            kept = ctx.read(reads[0].tap, reads[0].mode == "pop") & seen
+        else:
+            scores = self.indexer.scores(x, ctx)
+            kept = S.top_mask(scores, seen, c.indexer.top_k)
+        for p in self.ports:
+            if p.name == "index" and p.mode == "write":
+                ctx.push(p.tap, kept)
+        out, target = S.attend_kept(q, k, v, kept, scale, None, c.softcap)
+        if scores is not None and ctx.training and c.indexer.loss_weight:
+            ctx.report("indexer_loss", S.indexer_loss(scores, kept, target), c.indexer.loss_weight)
+        return out
 
 
 @register("mla")

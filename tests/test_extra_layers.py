@@ -109,3 +109,30 @@ def test_index_port_shares_the_picks():
     tr = _train(first, model=model)
     names = [n for n, _ in tr.model.named_parameters() if "indexer" in n]
     assert names and all(".items.1." in n for n in names)   # only the first layer owns an indexer
+
+
+def test_mla_with_an_indexer():
+    """With every key kept the sparse MLA is the dense one; the indexer gets its own loss."""
+    base = "mla(num_heads=2, kv_lora_rank=8, q_lora_rank=8, qk_nope_head_dim=8, qk_rope_head_dim=4, v_head_dim=8{more})"
+    tr = _train(base.format(more=", indexer=indexer(num_heads=2, head_dim=8, top_k=4)"))
+    assert any("indexer" in n for n, _ in tr.model.named_parameters())
+    ids = torch.randint(0, 64, (2, 32))
+    ctx = tr.model(ids, torch.arange(32).expand(2, 32), None, training=True)
+    assert "indexer_loss" in ctx.losses and torch.isfinite(ctx.losses["indexer_loss"])
+    (layer,) = [m for m in tr.model.modules() if isinstance(m, X.MLA)][:1]
+    x = torch.randn(2, 32, 32)
+    from bux_b200.models.registry import Context
+
+    def run(top_k):
+        layer.c = layer.c.model_copy(update={"indexer": layer.c.indexer.model_copy(update={"top_k": top_k})})
+        return layer(x, Context(torch.zeros(2, 32, dtype=torch.long)))
+
+    with torch.no_grad():
+        everything = run(32)
+        layer_dense_cfg = layer.c.model_copy(update={"indexer": None})
+        sparse_cfg, layer.c = layer.c, layer_dense_cfg
+        dense = layer(x, Context(torch.zeros(2, 32, dtype=torch.long)))
+        layer.c = sparse_cfg
+        few = run(2)
+    assert torch.allclose(everything, dense, atol=1e-5)
+    assert not torch.allclose(few, dense, atol=1e-3)
