@@ -64,6 +64,11 @@ def detect(arch: ir.Architecture) -> Optional[str]:
              and not a.bias and not a.sinks and not a.gated and a.softcap is None and a.sliding_window_size is None
              and a.scale is None and a.output_norm is None and not a.qk_norm_all_heads
              and all(getattr(a, f) in (None, False) for f in ("kv_conv_size", "differential", "k_eq_v", "indexer")))
+    # every other setting of the layer changes what it computes: only its defaults are a standard family
+    allowed = {"type", "num_heads", "num_kv_heads", "head_dim", "v_head_dim", "rope", "qk_norm", "fused_qkv",
+               "value_residual", "value_embed_gate"}
+    plain = plain and all(getattr(a, name) == field.default for name, field in type(a).model_fields.items()
+                          if name not in allowed and not field.is_required())
     if not plain:
         return None
     qk = a.qk_norm is not None and _plain_norm(a.qk_norm)

@@ -29,8 +29,8 @@ def _splits(model) -> dict:
         if isinstance(m, GQA):
             for leaf in ("weight", "bias"):
                 if getattr(m.qkv, leaf, None) is not None:
-                    out[f"{pre}qkv.{leaf}"] = [(f"{pre}q.{leaf}", m.q_rows), (f"{pre}k.{leaf}", m.k_rows),
-                                               (f"{pre}v.{leaf}", m.v_rows)]
+                    parts = [(f"{pre}q.{leaf}", m.q_rows), (f"{pre}k.{leaf}", m.k_rows), (f"{pre}v.{leaf}", m.v_rows)]
+                    out[f"{pre}qkv.{leaf}"] = [p for p in parts if p[1]]  # k_eq_v: no v projection
         elif isinstance(m, MLP) and m.gated:
             f = m.gate_up.weight.shape[0] // 2
             for leaf in ("weight", "bias"):

@@ -78,3 +78,17 @@ def test_standard_families_load_in_transformers(tmp_path, qk, ffn, family):
     assert json.loads((out / "config.json").read_text())["model_type"] == family
     report = C.compare(tr.model, out)   # transformers' own implementation of the family
     assert report["ok"] and report["max_abs_error"] < 2e-3, report
+
+
+@pytest.mark.parametrize("qk", [", k_eq_v=true, differential=true", ", paired=true", ", exclusive=learned, power_scale=0.5",
+                                ", gated=true, gate_input_rank=4, gate_cross_head=true, kv_conv_size=3"])
+def test_less_common_attention_settings_round_trip(tmp_path, qk):
+    """The exported model rebuilds the graph from the architecture, so every setting of the
+    layer survives the export; the fused projection splits only into the parts it has."""
+    run, tr, folder = _trained(tmp_path, qk=qk)
+    assert native.detect(run.arch) is None
+    out = export(folder, tmp_path / "hf", dtype="float32", check=True, echo=lambda *_: None)
+    report = C.compare(tr.model, out)
+    assert report["ok"] and report["max_abs_error"] < 1e-4
+    names = set(W.tensors(tr.model))
+    assert ("k_eq_v" in qk) == (not any(n.endswith(".v.weight") for n in names))
