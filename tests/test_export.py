@@ -58,6 +58,8 @@ def test_detects_standard_families():
     assert fam(", qk_norm=rmsnorm", MOE) == "qwen3_moe"
     assert fam(", sinks=true", DENSE) is None
     assert fam(", paired=true", DENSE) is None and fam(", exclusive=true", DENSE) is None
+    with_pointer = BASE.format(qk="", ffn=DENSE, extra="").replace("head(tied=false)", "head(tied=false, pointer=copy_pointer(dim=8))")
+    assert native.detect(compile_runs(with_pointer, filename="e.bux")[0].arch) is None
     assert fam(", qk_norm=rmsnorm", MOE.replace("top_k=2,", "top_k=2, latent_size=16,")) is None
     assert fam(", qk_norm=rmsnorm", MOE.replace("top_k=2,", "top_k=2, expert_norm=rmsnorm,")) is None
     assert fam(", qk_norm=rmsnorm", MOE.replace("top_k=2,", "top_k=2, random_logits=true,")) == "qwen3_moe"
