@@ -51,8 +51,8 @@ def detect(arch: ir.Architecture) -> Optional[str]:
             and isinstance(head, ir.Layer) and head.config.type == "head"):
         return None
     e = emb.config
-    if e.max_positions is not None or e.scale_by_sqrt_dim or e.norm is not None or head.config.softcap or head.config.bias
-            or head.config.pointer is not None:
+    if (e.max_positions is not None or e.scale_by_sqrt_dim or e.norm is not None or head.config.softcap
+            or head.config.bias or head.config.pointer is not None):
         return None
     parts = _block_parts(rep.body)
     if parts is None or rep.body.share is not None:
