@@ -26,7 +26,7 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-MARGIN_BYTES = 10 << 30  # device memory left free when attention outputs are kept (fragmentation, chunk buffers)
+MARGIN_BYTES = 14 << 30  # device memory left free when attention outputs are kept (fragmentation, chunk buffers)
 PUBLISHED_TOK_S_PER_GPU = 42391.0  # reference, 8xB300, MXFP8 `sorted` fsdp=8 (docs/performance/benchmarks.md:188)
 ROWS_PER_GPU = 32                  # 256 rows of 4096 over 8 GPUs
 
@@ -102,9 +102,6 @@ def main() -> int:
                     help="debug only: fewer layers (the result is then marked invalid)")
     ap.add_argument("--rows", type=int, default=ROWS_PER_GPU, help="rows of 4096 tokens per GPU per step")
     ap.add_argument("--seq-len", type=int, default=4096)
-    ap.add_argument("--host-rest", action="store_true",
-                    help="blocks whose attention outputs do not fit the device send them to pinned host memory "
-                         "(with host-offloaded block inputs only)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -135,7 +132,7 @@ def main() -> int:
         dist.init_process_group("nccl", device_id=device)
         from bux_b200.parallel.engine import Parallel
     n = args.gpus
-    total_steps = args.warmup + args.steps + 2
+    total_steps = args.warmup + 2 * args.steps + 2
     overrides = [f"mesh = mesh(expert={n})", f"batch = {args.rows * n}", f"steps = {2 * total_steps + 4}",
                  f"seq_len = {args.seq_len}", "log = log(every=1000000)",
                  f"methods.moe = {'fused_ep' if n > 1 else 'sorted'}"]
@@ -145,26 +142,28 @@ def main() -> int:
     run = compile_runs(path.read_text(), filename=str(path), overrides=overrides)[0]
     if world > 1:
         parallel = Parallel(run.train, device)
-    # State that fits 180 GB: bf16 master weights as the benchmark names them; on one GPU
-    # the whole model's moments are kept in 8-bit block-scaled form and every gradient is
-    # consumed by the optimizer as soon as the backward produces it.
-    # With four or more GPUs the experts' state is small enough for bf16 moments and
-    # on-device block inputs.
-    single = n == 1
-    tight = n <= 2
-    trainer = Trainer(run, device=device, parallel=parallel, fuse_optimizer=True,
-                      moments="fp8" if tight else "bfloat16", master=False)
+    # One state layout and one activation policy at every N, sized by the one-GPU case (the whole
+    # 30.5B-parameter model on 180 GB): bf16 weights that the optimizer updates in place, 8-bit
+    # block-scaled moments, each block's input kept in pinned host memory, each block rerun in
+    # the backward. Dense parameters and their moments are sharded over the ranks like the
+    # experts (the mesh's expert axis is also the axis parameters are sharded over).
+    # Gradients: with two or more GPUs a rank's gradients (at most 16 GB of bf16) are held to
+    # the end of the step and clipped by the step's own norm; the 61 GB of one GPU's gradients
+    # do not fit beside its state, so there each gradient is consumed by the optimizer as soon
+    # as the backward produces it and the clip factor comes from the previous step's norm.
+    fused_updates = n == 1
+    trainer = Trainer(run, device=device, parallel=parallel, fuse_optimizer=fused_updates,
+                      moments="fp8", master=False)
     # Attention outputs (and their log-sum-exp) are kept on the device for as many blocks as
-    # a measured step leaves room for: the backward's rerun of those blocks skips the
-    # attention forward. One probe step without them gives the peak; the spare memory after
-    # a margin is divided by a block's kept bytes. All ranks take the smallest count.
+    # fit: the backward's rerun of those blocks skips the attention forward. One probe step
+    # without them gives the step's peak; what the device has left after a margin is divided
+    # by a block's kept bytes. All ranks take the smallest count.
     arch = run.arch
     attn = next(l.config for l in arch.layers() if l.config.type == "gqa")
     blocks = sum(1 for l in arch.layers() if l.config.type == "gqa")
     hd = attn.head_dim or arch.d_model // attn.num_heads
     kept_bytes = args.rows * args.seq_len * attn.num_heads * (hd * 2 + 4)  # o in bf16, lse in fp32
-    trainer.model.set_remat(True, offload=tight, keep_attention=False)
-    keep_blocks = 0
+    trainer.model.set_remat(True, offload=True, keep_attention=False)
     feed = iter(trainer.batches())
     tokens_per_step = args.rows * n * args.seq_len
 
@@ -175,33 +174,53 @@ def main() -> int:
             return float(out["loss"].item())
         return out
 
+    def agreed_min(value: int) -> int:
+        if parallel is None:
+            return value
+        import torch.distributed as dist
+
+        t = torch.tensor([value], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return int(t.item())
+
+    torch.cuda.reset_peak_memory_stats(device)
     one_step(True)  # the probe step (an extra warm-up step)
     torch.cuda.synchronize()
     free, total_mem = torch.cuda.mem_get_info(device)
-    cached = torch.cuda.memory_reserved(device) - torch.cuda.max_memory_allocated(device)
-    spare = free + max(0, cached) // 2 - MARGIN_BYTES
-    keep_blocks = max(0, min(blocks, int(spare // kept_bytes)))
-    if parallel is not None:
-        import torch.distributed as dist
+    slack = torch.cuda.memory_reserved(device) - torch.cuda.max_memory_allocated(device)
+    spare = free + max(0, slack) - MARGIN_BYTES
+    keep_blocks = agreed_min(max(0, min(blocks, int(spare // kept_bytes))))
 
-        agreed = torch.tensor([keep_blocks], device=device)
-        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
-        keep_blocks = int(agreed.item())
-    if keep_blocks:
-        trainer.model.set_remat(True, offload=tight, keep_attention=keep_blocks, kept_to_host=args.host_rest and tight)
-    try:
-        for _ in range(args.warmup):
-            one_step(True)
-    except torch.cuda.OutOfMemoryError:
-        # the estimate was too tight: on one GPU fall back to keeping nothing and warm up again
-        # (with several ranks the others are already inside a collective, so the error stands)
-        if parallel is not None:
-            raise
-        keep_blocks = 0
-        trainer.model.set_remat(True, offload=tight, keep_attention=False)
-        torch.cuda.empty_cache()
-        for _ in range(args.warmup):
-            one_step(True)
+    def set_keep(count: int) -> None:
+        trainer.model.set_remat(True, offload=True, keep_attention=count if count else False)
+
+    def guarded(loop):
+        """Run `loop`; if the device runs out of memory, halve the number of kept blocks
+        (all ranks agree on the outcome between loops, never inside a step) and run it again.
+        A timed loop that was cut short is timed again from its start."""
+        nonlocal keep_blocks
+        while True:
+            failed = 0
+            result = None
+            try:
+                result = loop()
+            except torch.cuda.OutOfMemoryError:
+                if parallel is not None:
+                    raise  # the other ranks are inside a collective: the job ends here
+                failed = 1
+            if not failed:
+                return result
+            if keep_blocks == 0:
+                raise RuntimeError("out of device memory with no attention outputs kept")
+            keep_blocks //= 2
+            set_keep(keep_blocks)
+            import gc
+
+            gc.collect()
+            torch.cuda.empty_cache()
+
+    set_keep(keep_blocks)
+    guarded(lambda: [one_step(True) for _ in range(args.warmup)])
     torch.cuda.synchronize()
     if parallel is not None:
         parallel.barrier()
@@ -209,28 +228,39 @@ def main() -> int:
     if rank == 0:
         sampler.start()
     # ---- device-timed region: exactly `steps` steps
-    launches0 = K.launches
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    start.record()
-    last = None
-    for _ in range(args.steps):
-        last = one_step(False)
-    end.record()
-    torch.cuda.synchronize()
-    launches = K.launches - launches0
-    ms = start.elapsed_time(end)
+    def timed():
+        launches0 = K.launches
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if parallel is not None:
+            parallel.barrier()
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(args.steps):
+            one_step(False)
+        end.record()
+        torch.cuda.synchronize()
+        if parallel is not None:
+            parallel.barrier()
+        return start.elapsed_time(end), K.launches - launches0
+
+    ms, launches = guarded(timed)
     K.check_status(device, "bench")
-    # ---- end-to-end region through the public step API, loss read back every step
-    if parallel is not None:
-        parallel.barrier()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    loss = None
-    for _ in range(args.steps):
-        loss = one_step(True)
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
+
+    # ---- end-to-end region through the public step API: every step's batch comes from pinned
+    # host memory (`Trainer.to_device`) and its loss is read back to the host
+    def end_to_end():
+        if parallel is not None:
+            parallel.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        value = None
+        for _ in range(args.steps):
+            value = one_step(True)
+        torch.cuda.synchronize()
+        return time.perf_counter() - t0, value
+
+    e2e_s, loss = guarded(end_to_end)
+    K.check_status(device, "bench (end to end)")
     clocks = sampler.stop() if rank == 0 else None
     times = torch.tensor([ms, e2e_s * 1000], device=device, dtype=torch.float64)
     if parallel is not None:
@@ -255,12 +285,16 @@ def main() -> int:
             "mfu_bf16_peak": value / n * fpt / 2.25e15,
             "config": {"model": "qwen3_30b_a3b" + (f" TRUNCATED to {args.layers} layers: INVALID" if args.layers else ""),
                        "global_batch": args.rows * n, "seq_len": args.seq_len,
-                       "parallelism": f"ep{n}" if n > 1 else "1 gpu (all experts local)",
-                       "optimizer": "adamw, bf16 master, " + ("8-bit block-scaled moments" if tight else "bf16 moments")
-                                    + ", expert updates fused into the backward, clip by the previous step's norm",
-                       "remat": f"per block, attention outputs kept on the device for {keep_blocks} of {blocks} blocks"
-                       + (", the others in pinned host memory" if args.host_rest and tight and 0 < keep_blocks < blocks else "")
-                       + (", block inputs in pinned host memory" if tight else ""),
+                       "parallelism": (f"ep{n} + fsdp{n} (experts split over the expert axis, every other parameter "
+                                       f"and its moments sharded over the same {n} ranks)") if n > 1
+                       else "1 gpu (all experts local)",
+                       "optimizer": "adamw, bf16 master weights, 8-bit block-scaled moments",
+                       "clip": ("by the previous step's norm, updates fused into the backward (one GPU cannot hold "
+                                "61 GB of gradients beside the state)") if fused_updates
+                       else "by this step's own global norm",
+                       "remat": "every block rerun in the backward, block inputs in pinned host memory, attention "
+                                "outputs kept on the device where they fit",
+                       "attention_outputs_kept": f"{keep_blocks} of {blocks} blocks",
                        "peak_mem_gb": round(torch.cuda.max_memory_allocated(device) / 1e9, 1), "l2": "inputs and weights exceed L2 (126 MB) every step",
                        "loss_last_step": loss},
             "clocks": clocks,

@@ -10,6 +10,8 @@ from pathlib import Path
 import numpy as np
 import torch
 
+from .. import runtime
+
 _ZARR_DTYPES = {"float32": "float32", "float64": "float64", "int32": "int32", "int64": "int64",
                 "uint8": "uint8", "bfloat16": "bfloat16", "bool": "bool", "float16": "float16"}
 
@@ -106,7 +108,7 @@ def state_tree(trainer) -> dict:
 
 def save(folder, step: int, trainer) -> None:
     folder = Path(folder)
-    rank = int(os.environ.get("RANK", "0"))
+    rank = runtime.rank()
     final = folder / str(step)
     tmp = folder / f"{step}.orbax-checkpoint-tmp"
     tree = state_tree(trainer) if trainer.parallel is None else trainer.parallel.checkpoint_tree(trainer, state_tree)

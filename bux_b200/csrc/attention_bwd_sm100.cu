@@ -367,12 +367,9 @@ static const char* attn_bwd_launch_d(const AttnArgs& a, cudaStream_t stream) {
   p.B = a.B; p.T = a.T; p.S = a.S; p.H = a.H; p.G = a.G;
   p.scale = a.scale; p.scale_log2 = a.scale * LOG2E_B; p.causal = a.causal ? 1 : 0; p.window = a.window;
   auto kern = attn_bwd_kernel<D>;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
-      return "cudaFuncSetAttribute(max dynamic shared memory) failed";
-    configured = true;
-  }
+  static bool configured[64] = {};
+  if (!allow_dynamic_smem(kern, Cfg::SMEM_BYTES, configured))
+    return "cudaFuncSetAttribute(max dynamic shared memory) failed";
   const long rows = (long)a.B * a.T * a.H;
   attn_delta_kernel<<<(int)min((rows + 7) / 8, 148L * 16), 256, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(a.o), reinterpret_cast<const __nv_bfloat16*>(a.d_o), a.lse,

@@ -364,12 +364,9 @@ static const char* attn_fwd_launch_d(const AttnArgs& a, cudaStream_t stream) {
   p.B = a.B; p.T = a.T; p.S = a.S; p.H = a.H; p.G = a.G;
   p.scale_log2 = a.scale * LOG2E; p.causal = a.causal ? 1 : 0; p.window = a.window;
   auto kern = attn_fwd_kernel<D>;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
-      return "cudaFuncSetAttribute(max dynamic shared memory) failed";
-    configured = true;
-  }
+  static bool configured[64] = {};
+  if (!allow_dynamic_smem(kern, Cfg::SMEM_BYTES, configured))
+    return "cudaFuncSetAttribute(max dynamic shared memory) failed";
   dim3 grid((a.T + 2 * QT - 1) / (2 * QT), a.H, a.B);
   kern<<<grid, FWD_THREADS, Cfg::SMEM_BYTES, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? nullptr : "attention forward launch failed";

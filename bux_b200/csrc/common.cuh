@@ -30,6 +30,20 @@ __device__ __forceinline__ void report_failure(Status* st, int kernel_id, int si
   atomicAdd(&st->count, 1u);
 }
 
+// ---------------------------------------------------------------- launch set-up
+// Opting a kernel in to more than 48 KB of dynamic shared memory applies to the current
+// device only, so the "already done" flag is kept per device (a process may drive several).
+template <typename Kern>
+inline bool allow_dynamic_smem(Kern kern, int bytes, bool (&done)[64]) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  const bool tracked = dev >= 0 && dev < 64;
+  if (tracked && done[dev]) return true;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+  if (tracked) done[dev] = true;
+  return true;
+}
+
 // ---------------------------------------------------------------- small helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

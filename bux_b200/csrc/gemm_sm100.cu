@@ -501,12 +501,9 @@ template <int KIND, int BN, bool A_MN, bool B_MN, int EW = 4>
 static const char* launch_cfg(const GemmParams& p, int sms, cudaStream_t stream) {
   using Cfg = GemmCfg<KIND, BN, EW>;
   auto kern = gemm_sm100_kernel<KIND, BN, A_MN, B_MN, EW>;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
-      return "cudaFuncSetAttribute(max dynamic shared memory) failed";
-    configured = true;
-  }
+  static bool configured[64] = {};
+  if (!allow_dynamic_smem(kern, Cfg::SMEM_BYTES, configured))
+    return "cudaFuncSetAttribute(max dynamic shared memory) failed";
   kern<<<sms, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? nullptr : "gemm kernel launch failed";
 }

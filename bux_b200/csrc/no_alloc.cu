@@ -72,3 +72,18 @@ extern "C" int bux_attn_bwd_static(const void* q, const void* k, const void* v, 
   if (err != nullptr) return fail(4, err, message);
   return 0;
 }
+
+extern "C" int bux_attn_bwd_static_status(unsigned int* code, unsigned int* count, int clear) {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return 3;
+  if (!resolve(device)) return 3;
+  bux::Status host{0u, 0u};
+  // a blocking copy on the legacy default stream: it returns after the work queued before it
+  if (cudaMemcpy(&host, g_status_ptr[device], sizeof(host), cudaMemcpyDeviceToHost) != cudaSuccess) return 4;
+  if (code) *code = host.code;
+  if (count) *count = host.count;
+  if (clear && (host.code != 0u || host.count != 0u) &&
+      cudaMemset(g_status_ptr[device], 0, sizeof(host)) != cudaSuccess)
+    return 4;
+  return 0;
+}

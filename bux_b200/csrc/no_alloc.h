@@ -1,10 +1,10 @@
 // A C entry point for callers that cannot allocate device memory.
 //
 // This has no counterpart in the reference framework. It exists for hosts that embed
-// this library where cudaMalloc is off limits: inside a CUDA-graph capture or another
-// framework's stream-ordered region where an allocation would break the capture, in
-// plugins that must stay within a memory budget fixed at start-up, or in processes
-// whose allocator belongs to someone else (an inference server's arena). Such a caller
+// this library where cudaMalloc is off limits: plugins that must stay within a memory
+// budget fixed at start-up, processes whose device allocator belongs to someone else (an
+// inference server's arena that hands out the whole GPU), and latency-bound loops that
+// cannot afford a driver allocation (it synchronises the device). Such a caller
 // owns every input and output buffer and hands over raw device pointers; the one
 // piece of memory the attention backward needs beyond those (its per-row
 // sum(dO * O) table) lives in a fixed array inside the library.
@@ -34,6 +34,15 @@ int bux_attn_bwd_static(const void* q, const void* k, const void* v, const void*
                         const float* lse, float* dq, void* dk, void* dv, const float* sinks,
                         float* dsinks, int B, int T, int S, int H, int G, int D, float scale,
                         int causal, int window, void* cuda_stream, const char** message);
+
+// The kernels' waits (on their own barriers) are bounded; one that runs out makes the
+// kernel return early and records where in a status word that also lives inside the
+// library, so a call that returned 0 may still have produced no dk/dv. This reads that
+// word on the current device after the work queued so far has finished (it blocks):
+// *code is 0 when no wait ran out, else kernel << 24 | site << 16 | block; *count is the
+// number of waits that ran out since the word was last cleared. `clear` != 0 resets it.
+// Returns 0, or 3 / 4 as above. Either pointer may be null.
+int bux_attn_bwd_static_status(unsigned int* code, unsigned int* count, int clear);
 
 #ifdef __cplusplus
 }

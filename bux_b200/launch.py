@@ -29,6 +29,7 @@ import time
 from pathlib import Path
 from typing import Optional
 
+from . import runtime
 from .lang import compile_runs, ir
 
 
@@ -173,7 +174,7 @@ class _Report:
             self._write(trainer)
 
     def _write(self, trainer) -> None:
-        if int(os.environ.get("RANK", "0")) == 0:
+        if runtime.rank() == 0:
             record(self.folder, step=trainer.step, metrics=self.last)
 
     def stop(self, trainer, sinks) -> None:
@@ -189,7 +190,7 @@ def train_here(run: ir.Run, out="runs", cache=".", device=None, quiet: bool = Fa
 
     configure()
     folder = TR.directory(run, out)
-    main = int(os.environ.get("RANK", "0")) == 0
+    main = runtime.rank() == 0
     parallel = None
     if processes() > 1 or need(run) > 1:
         import torch
@@ -198,7 +199,7 @@ def train_here(run: ir.Run, out="runs", cache=".", device=None, quiet: bool = Fa
 
         dev = torch.device(device) if device else None
         if dev is None and torch.cuda.is_available():
-            dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+            dev = torch.device("cuda", runtime.local_rank())
         if init_distributed(dev):
             parallel = Parallel(run.train, dev)
             device = dev

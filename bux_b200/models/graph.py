@@ -139,6 +139,26 @@ class Repeated(nn.Module):
 
 _OFFLOADED: list = []   # blocks whose inputs sit in host memory, in forward order
 _SIDE: dict = {}
+_IN_FLIGHT: list = []   # (event, tensors) of device → host copies whose sources are still held
+
+
+def _hold_until_copied(event, tensors) -> None:
+    """Keep `tensors` alive until the side-stream copy that reads them is done.
+
+    Their memory goes back to the allocator only after the main stream has been made to
+    wait for the copy, so the allocator's own stream order covers the reuse. (Marking the
+    tensors as used by the side stream instead would leave each freed block unusable until
+    the host sees the copy finished; a host that runs a step ahead of the device then
+    holds every block's input twice.)"""
+    _IN_FLIGHT.append((event, tensors))
+
+
+def _release_copied(device, keep_last: int = 0) -> None:
+    """Let go of the sources of all but the newest `keep_last` copies in flight."""
+    while len(_IN_FLIGHT) > keep_last:
+        event, tensors = _IN_FLIGHT.pop(0)
+        torch.cuda.current_stream(device).wait_event(event)
+        del tensors
 
 
 def _side_stream(device):
@@ -161,13 +181,17 @@ class _Remat(torch.autograd.Function):
         fctx.cpu_rng = torch.get_rng_state()
         fctx.host = None
         if holder.offload and x.is_cuda:
-            # the copy runs on a side stream so the block's kernels do not wait for PCIe
+            # the copy runs on a side stream so the block's kernels do not wait for PCIe; the
+            # copy of the block before this one has had a whole block's time to finish
+            _release_copied(x.device)
             host = holder.pinned(x)
             side = _side_stream(x.device)
             side.wait_stream(torch.cuda.current_stream(x.device))
             with torch.cuda.stream(side):
                 host.copy_(x, non_blocking=True)
-            x.record_stream(side)
+                copied = torch.cuda.Event()
+                copied.record(side)
+            _hold_until_copied(copied, (x,))
             fctx.host = host
             fctx.device = x.device
             fctx.fetched = None
@@ -180,16 +204,19 @@ class _Remat(torch.autograd.Function):
             # kept attention outputs follow the block's input to the host
             side = _side_stream(x.device)
             side.wait_stream(torch.cuda.current_stream(x.device))
-            hosted = []
+            hosted, sources = [], []
             with torch.cuda.stream(side):
                 for i, pair in enumerate(holder.kept):
                     on_host = []
                     for j, t in enumerate(pair):
                         h = holder.pinned(t, slot=(i, j))
                         h.copy_(t, non_blocking=True)
-                        t.record_stream(side)
+                        sources.append(t)
                         on_host.append(h)
                     hosted.append(tuple(on_host))
+                copied = torch.cuda.Event()
+                copied.record(side)
+            _hold_until_copied(copied, tuple(sources))
             holder.kept = hosted
         return (y, *aux)
 
@@ -221,6 +248,7 @@ class _Remat(torch.autograd.Function):
     def backward(fctx, dy, *daux):
         holder = fctx.holder
         if fctx.host is not None:
+            _release_copied(fctx.device)
             if fctx.fetched is None:
                 _Remat._fetch(fctx)
             x, done = fctx.fetched

@@ -63,14 +63,22 @@ class Parallel:
     def _all_axis_sets(self) -> list:
         sets = [tuple(a for a in M._axes_of(self.train.layout.batch) if self.shape[a] > 1)]
         sets += [(a,) for a in M.AXES if self.shape[a] > 1]
-        fs = tuple(a for a in M._axes_of(self.train.layout.fsdp) if self.shape[a] > 1)
-        sets.append(fs)
+        sets.append(self.shard_axes())
         sets.append(tuple(a for a in M.AXES if self.shape[a] > 1 and a not in ("expert",)))
         out = []
         for s in sets:
             if s and s not in out:
                 out.append(s)
         return out
+
+    def shard_axes(self) -> tuple:
+        """The mesh axes whole parameters are sharded over: the layout's ``fsdp`` axes that
+        are larger than one (``fsdp`` and ``expert`` by default, as the reference maps the
+        sharded dimension over (fsdp, context, expert), ``train/config.py:959`` there).
+        ``context`` is left out: its ranks hold different positions of the same rows and sum
+        every gradient over the axis afterwards."""
+        return tuple(a for a in M.AXES if a in M._axes_of(self.train.layout.fsdp)
+                     and a in ("fsdp", "expert") and self.shape[a] > 1)
 
     def _make_groups(self, axes: tuple) -> None:
         seen = set()
@@ -129,17 +137,17 @@ class Parallel:
             from . import tensor
 
             tensor.shard_model(model, self)
-        fs_axes = tuple(a for a in M._axes_of(t.layout.fsdp) if self.shape[a] > 1 and a == "fsdp")
-        if fs_axes and self.shape["fsdp"] > 1:
+        fs_axes = self.shard_axes()
+        if fs_axes:
             from .fsdp import FSDP
 
-            self.fsdp = FSDP(model, self, skip=expert_params)
+            self.fsdp = FSDP(model, self, skip=expert_params, axes=fs_axes)
         # gradients of whole (replicated) parameters are summed over the batch axes;
         # expert shards are replicated only over the batch axes that are not `expert`
         for name, p in model.named_parameters():
             if getattr(p, "_bux_sharded", False):
-                # the reduce-scatter summed over `fsdp`; other replicas (HSDP) all-reduce
-                axes = tuple(a for a in self.batch_axes if a != "fsdp")
+                # the reduce-scatter summed over the sharding axes; other replicas (HSDP) all-reduce
+                axes = tuple(a for a in self.batch_axes if a not in fs_axes)
             elif p in expert_params:
                 axes = tuple(a for a in self.batch_axes if a != "expert")
             else:
@@ -282,11 +290,15 @@ def init_distributed(device: Optional[torch.device] = None) -> bool:
     """Join the job the environment describes (torchrun / SLURM / Open MPI variables).
     Returns whether there is more than one process."""
     env = os.environ
-    world = int(env.get("WORLD_SIZE") or env.get("SLURM_STEP_NUM_TASKS") or env.get("OMPI_COMM_WORLD_SIZE") or 1)
+    from .. import runtime
+
+    world = runtime.world_size()
     if world <= 1:
         return False
     if not dist.is_initialized():
-        rank = int(env.get("RANK") or env.get("SLURM_PROCID") or env.get("OMPI_COMM_WORLD_RANK") or 0)
+        from .. import runtime
+
+        rank = runtime.rank()
         env.setdefault("MASTER_ADDR", "127.0.0.1")
         env.setdefault("MASTER_PORT", "29500")
         backend = "nccl" if device is not None and device.type == "cuda" else "gloo"

@@ -148,9 +148,10 @@ class Unit:
 
 
 class FSDP:
-    def __init__(self, model: nn.Module, par, skip=()):
+    def __init__(self, model: nn.Module, par, skip=(), axes=("fsdp",)):
         t = par.train
-        self.group = par.group(("fsdp",))
+        self.axes = tuple(axes)
+        self.group = par.group(self.axes)
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
         self.keep = t.layout.zero < 3 or getattr(t.methods, "gather", "layer") == "step"

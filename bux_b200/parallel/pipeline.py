@@ -151,6 +151,10 @@ class Pipeline:
             ids, pos, mask = micro[m]
             if op == "F":
                 segments = None
+                if getattr(micro[m], "packed", False):
+                    from ..train.trainer import segments_of
+
+                    segments = segments_of(pos)
                 ctx = Context(ids, pos, segments, training=True, precision=trainer.precision,
                               methods=trainer.train.methods, parallel=trainer.parallel, step=trainer.step)
                 if self.first:

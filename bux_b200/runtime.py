@@ -24,6 +24,36 @@ def configure() -> None:
     os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "8")
 
 
+def _first_int(names, default: int) -> int:
+    for name in names:
+        v = os.environ.get(name)
+        if v not in (None, ""):
+            return int(v)
+    return default
+
+
+def rank() -> int:
+    """This process's rank in the job: from torch.distributed once the job is joined, else
+    from the launcher's environment (torchrun, SLURM's srun, Open MPI's mpirun)."""
+    try:
+        import torch.distributed as dist
+
+        if dist.is_available() and dist.is_initialized():
+            return dist.get_rank()
+    except Exception:  # noqa: BLE001
+        pass
+    return _first_int(("RANK", "SLURM_PROCID", "OMPI_COMM_WORLD_RANK"), 0)
+
+
+def local_rank() -> int:
+    """This process's index among the processes of its node (the GPU it takes)."""
+    return _first_int(("LOCAL_RANK", "SLURM_LOCALID", "OMPI_COMM_WORLD_LOCAL_RANK"), 0)
+
+
+def world_size() -> int:
+    return _first_int(("WORLD_SIZE", "SLURM_STEP_NUM_TASKS", "SLURM_NTASKS", "OMPI_COMM_WORLD_SIZE"), 1)
+
+
 def agree_on_folder(folder, rank: int, world: int, barrier) -> None:
     """Fail early unless every rank sees the same (shared) folder: rank 0 drops a file,
     the others must see it (reference: ``runtime.py:116``, ``train/hooks.py:508``)."""

@@ -17,6 +17,7 @@ from typing import Optional
 
 import torch
 
+from .. import runtime
 from ..config import training as T
 from . import flops as F
 
@@ -67,6 +68,7 @@ class Log(Hook):
 
     def __call__(self, step, scalars, trainer, sinks) -> None:
         host = _host(scalars)  # waits for that step only; the next one is already launched
+        trainer.check_kernels(f"step {step}")
         now = time.perf_counter()
         tokens = int(host.get("tokens", trainer.tokens))
         dt = max(now - (self.last_time or now), 1e-9)
@@ -128,7 +130,7 @@ class Checkpoint(Hook):
     def restore(self, trainer) -> Optional[int]:
         from .. import ckpt
 
-        if int(os.environ.get("RANK", "0")) == 0:
+        if runtime.rank() == 0:
             self.drop_unfinished()
         if trainer.parallel is not None:
             trainer.parallel.barrier()
@@ -146,9 +148,12 @@ class Checkpoint(Hook):
         step = trainer.step
         if step == self.saved_at:
             return
+        if trainer.device.type == "cuda":
+            torch.cuda.synchronize(trainer.device)  # the state read below is the finished step's
+        trainer.check_kernels(f"checkpoint at step {step}")
         ckpt.save(self.folder, step, trainer)
         self.saved_at = step
-        if int(os.environ.get("RANK", "0")) == 0:
+        if runtime.rank() == 0:
             for old in self.steps()[:-self.c.keep]:
                 shutil.rmtree(self.folder / str(old), ignore_errors=True)
 
@@ -200,7 +205,7 @@ class Profile(Hook):
                 return
             self.prof.__exit__(None, None, None)
             self.folder.mkdir(parents=True, exist_ok=True)
-            rank = int(os.environ.get("RANK", "0"))
+            rank = runtime.rank()
             path = self.folder / f"trace_rank{rank}.json"
             self.prof.export_chrome_trace(str(path))
             from . import trace

@@ -15,9 +15,11 @@ import time
 from pathlib import Path
 from typing import Callable, Mapping, Optional
 
+from .. import runtime
+
 
 def is_main_process() -> bool:
-    return int(os.environ.get("RANK", "0")) == 0
+    return runtime.rank() == 0
 
 
 def echo(line: str) -> None:

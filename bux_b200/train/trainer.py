@@ -20,6 +20,7 @@ from typing import Iterable, Optional
 import numpy as np
 import torch
 
+from .. import runtime
 from ..config import training as T
 from ..lang import ir
 from ..lang.printer import run_to_source
@@ -42,8 +43,12 @@ def pick_device(spec: Optional[str] = None) -> torch.device:
     if torch.cuda.is_available():
         import os
 
-        return torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+        return torch.device("cuda", runtime.local_rank())
     return torch.device("cpu")
+
+
+class KernelWaitError(RuntimeError):
+    """A kernel's bounded wait (on a peer's flag, a barrier) ran out during a step."""
 
 
 class Timers:
@@ -104,6 +109,7 @@ class Trainer:
         self._prev_norm_sq = None
         self._norm_acc = None
         self._hooks_installed = False
+        self._status_host = None
         self.stretches = curriculum.stretches(t)
         self.timers = Timers()
 
@@ -143,19 +149,24 @@ class Trainer:
                 t = t.pin_memory().to(self.device, non_blocking=True)
             return t.to(dtype)
 
-        return (put(batch.input_ids, torch.long), put(batch.position_ids, torch.long),
-                put(batch.loss_mask, torch.bool))
+        ids, pos, mask = (put(batch.input_ids, torch.long), put(batch.position_ids, torch.long),
+                          put(batch.loss_mask, torch.bool))
+        # whether any row holds more than one document is read off the host copy (no device
+        # sync); the segment ids themselves are formed on the device in `segments_of`
+        host_pos = np.asarray(batch.position_ids)
+        packed = bool(host_pos.shape[1] > 1 and (host_pos[:, 1:] <= host_pos[:, :-1]).any())
+        return _DeviceBatch((ids, pos, mask), packed)
 
     def forward_loss(self, mb, inv_count, n_micro: int, world: int, training: bool = True):
         ids, pos, mask = mb
+        segments = segments_of(pos) if getattr(mb, "packed", False) else None
         span = None
         if self.parallel is not None and self.parallel.context_group is not None:
             # this rank's positions; the loss still sees whole rows for its targets
             span = self.parallel.positions_span(ids.shape[1])
             ids, pos = ids[:, span[0]:span[1]], pos[:, span[0]:span[1]]
-        segments = None
-        if bool((pos[:, 1:] <= pos[:, :-1]).any()) if pos.device.type == "cpu" else False:
-            segments = torch.cumsum((pos == 0).long(), dim=1)
+            if segments is not None:
+                segments = segments[:, span[0]:span[1]]
         ctx = self.model(ids, pos, segments, training=training, precision=self.precision,
                          methods=self.train.methods, parallel=self.parallel, step=self.step)
         parts = objective.compute(ctx, mb, self.train.loss, span=span)
@@ -172,7 +183,8 @@ class Trainer:
         world = self.parallel.data_world if self.parallel is not None else 1
         dev_batch = self.to_device(batch)
         rows = dev_batch[0].shape[0]
-        micro = [tuple(x[i::n_micro] for x in dev_batch) for i in range(n_micro)] if n_micro > 1 else [dev_batch]
+        micro = ([_DeviceBatch(tuple(x[i::n_micro] for x in dev_batch), dev_batch.packed) for i in range(n_micro)]
+                 if n_micro > 1 else [dev_batch])
         # global number of targets: a device scalar, summed over ranks without a host sync
         count = torch.zeros(1, dtype=torch.float32, device=self.device)
         for mb in micro:
@@ -228,12 +240,47 @@ class Trainer:
             loss_sum = self.parallel.sum_positions(loss_sum)
         self.step += 1
         self.tokens += cfg.batch * cfg.seq_len
+        self._snapshot_kernel_status()
         base_lr = t.optimizer.lr
         out = {"loss": loss_sum, "lr": base_lr * lr_scale, "tokens": self.tokens}
         if norm is not None:
             out["grad_norm"] = norm
         out.update(terms)
         return out
+
+    # ---- the kernels' bounded waits
+    def _snapshot_kernel_status(self) -> None:
+        """Queue a copy of the device's status word (where a kernel's bounded wait records
+        that it ran out) into pinned host memory behind the step's work: reading it later
+        costs no synchronisation beyond the one the reader already made for that step."""
+        if self.device.type != "cuda":
+            return
+        from ..ops import kernels as K
+
+        if self._status_host is None:
+            self._status_host = torch.zeros(2, dtype=torch.int32).pin_memory()
+        self._status_host.copy_(K.status_word(self.device), non_blocking=True)
+
+    def check_kernels(self, what: str = "training step") -> None:
+        """Raise on every rank if a bounded device wait ran out on any rank in a step whose
+        results the host has already read (the log hook, before a checkpoint is written):
+        such a kernel returned without writing its output, so the state is not to be kept."""
+        if self._status_host is None:
+            return
+        code, count = (int(v) for v in self._status_host.tolist())
+        bad = 1 if code else 0
+        if self.parallel is not None and self.parallel.world > 1:
+            bad = self.parallel.max_int(bad)
+        if not bad:
+            return
+        from ..ops import kernels as K
+
+        self.stopping = True
+        K.status_word(self.device).zero_()
+        self._status_host.zero_()
+        where = (f"kernel {code >> 24}, site {(code >> 16) & 0xff}, block {code & 0xffff}; {count} waits in total"
+                 if code else "on another rank")
+        raise KernelWaitError(f"{what}: a bounded device wait ran out ({where}); the step's results are stale")
 
     # ---- optimizer fused into the backward (gradients released as they are produced)
     def _install_release_hooks(self) -> None:
@@ -283,7 +330,8 @@ class Trainer:
         count = torch.zeros(1, dtype=torch.float32, device=self.device)
         for b in data.eval_batches(self.train, e, self.run.arch.vocab_size or 1, self.cache, rank, world):
             mb = self.to_device(b)
-            ctx = self.model(mb[0], mb[1], None, training=False, precision=self.precision,
+            ctx = self.model(mb[0], mb[1], segments_of(mb[1]) if mb.packed else None, training=False,
+                             precision=self.precision,
                              methods=self.train.methods, parallel=self.parallel, step=self.step)
             parts = objective.compute(ctx, mb, self.train.loss)
             total += parts.ce_sum
@@ -337,6 +385,25 @@ class Trainer:
                 t0 = time.perf_counter()
                 h(step, scalars, self, sinks)
                 self.timers.add("hooks", time.perf_counter() - t0)
+
+
+class _DeviceBatch(tuple):
+    """(input_ids, position_ids, loss_mask) on the device, plus `packed`: whether some row
+    holds more than one document (known from the host copy of the positions)."""
+
+    def __new__(cls, parts, packed: bool = False):
+        self = super().__new__(cls, parts)
+        self.packed = packed
+        return self
+
+
+def segments_of(positions: torch.Tensor) -> torch.Tensor:
+    """Document ids (from 1) of every position of packed rows: a document starts at a row's
+    first position and wherever the position ids stop increasing (the reference's rule,
+    ``architecture/common/segments.py:37`` there). Formed on the device, no host sync."""
+    first = torch.ones_like(positions[:, :1], dtype=torch.bool)
+    start = torch.cat([first, positions[:, 1:] <= positions[:, :-1]], dim=1)
+    return start.long().cumsum(dim=1)
 
 
 class _null:

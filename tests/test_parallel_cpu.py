@@ -81,11 +81,10 @@ def test_expert_parallel_matches_one_rank(tmp_path):
     want_losses, want = _single(MOE)
     got = _spawn(2, MOE, ["mesh = mesh(expert=2)", "methods.moe = all_to_all", "methods.capacity = 4.0"], tmp_path)
     assert got["losses"] == pytest.approx(want_losses, abs=1e-5)
-    for name, p in want.items():
-        g = got["state"][name]
-        if "experts_" in name:
-            p = p[: g.shape[0]]  # rank 0 holds the first half of the experts
-        assert torch.allclose(g, p, atol=1e-5), name
+    # rank 0 holds the first half of the experts, and the first rows of every other
+    # parameter: what is not an expert is sharded over the expert axis like over `fsdp`
+    _check_rows(got, want)
+    assert any(got["state"][n].shape != p.shape for n, p in want.items() if "experts_" not in n)
 
 
 def _check_rows(got, want, world=2):

@@ -1,7 +1,8 @@
 """The allocation-free attention backward, called through its exported C symbol.
 
-Some hosts of this library may not allocate device memory (a stream capture in
-progress, a fixed memory budget, an allocator owned by another framework): they call
+Some hosts of this library may not allocate device memory (a memory budget fixed at
+start-up, a device allocator owned by another framework, a loop that cannot afford the
+device-wide synchronisation of a driver allocation): they call
 `bux_attn_bwd_static`, which keeps its one scratch table inside the library. The test
 hands it raw pointers of tensors allocated up front and checks it against the regular
 entry point, twice in a row (the scratch keeps the previous call's contents).
@@ -45,11 +46,23 @@ def test_static_entry_matches_the_regular_one(cuda):
         dq = torch.full(q.shape, 7.0, dtype=torch.float32, device=cuda)
         dk, dv = torch.empty_like(k), torch.empty_like(v)
         dsinks = torch.full((4,), 7.0, device=cuda) if with_sinks else None
+        if call == 0:
+            # the first call on a device resolves the scratch address; later calls must not
+            # change what the driver reports as free either (a cudaMalloc inside the library
+            # would not show in torch's own counter)
+            rc, msg = _call(lib, q, k, v, o, do, lse, sinks, dq, dk, dv, dsinks, window)
+            torch.cuda.synchronize()
+            assert rc == 0, msg
         before = torch.cuda.memory_allocated(cuda)
+        free_before = torch.cuda.mem_get_info(cuda)[0]
         rc, msg = _call(lib, q, k, v, o, do, lse, sinks, dq, dk, dv, dsinks, window)
         torch.cuda.synchronize()
         assert rc == 0, msg
         assert torch.cuda.memory_allocated(cuda) == before
+        assert torch.cuda.mem_get_info(cuda)[0] == free_before
+        code, count = ctypes.c_uint(7), ctypes.c_uint(7)
+        assert lib.bux_attn_bwd_static_status(ctypes.byref(code), ctypes.byref(count), 1) == 0
+        assert (code.value, count.value) == (0, 0)  # no bounded wait ran out
         for got, ref in zip((dq, dk, dv), want[:3]):
             err = ((got.float() - ref.float()).norm() / ref.float().norm()).item()
             assert err < 2e-2, (call, err)
