@@ -144,7 +144,8 @@ void quant_mxfp8(const Tensor& x, const c10::optional<Tensor>& row_index, const 
   bux::quant_mxfp8(x.data_ptr(), x.stride(-2), opt_i32(row_index), opt_f32(row_scale), qr, sr, qc, sc, rows, (int)cols, ld_col, (int)batch, x_batch_stride, stream_of(x));
 }
 
-void quant_mxfp8_glu(const Tensor& h, const c10::optional<Tensor>& dout, const c10::optional<Tensor>& q_row,
+void quant_mxfp8_glu(const Tensor& h, const c10::optional<Tensor>& dout, const c10::optional<Tensor>& row_scale,
+                     const c10::optional<Tensor>& q_row,
                      const c10::optional<Tensor>& sf_row, const c10::optional<Tensor>& q_col,
                      const c10::optional<Tensor>& sf_col, int64_t ld_col, int64_t kind, double limit, double up_offset) {
   TORCH_CHECK(h.is_cuda() && h.scalar_type() == at::kBFloat16 && h.dim() == 2 && h.is_contiguous(), "quant_glu: contiguous bf16 h [rows, 2f]");
@@ -163,7 +164,11 @@ void quant_mxfp8_glu(const Tensor& h, const c10::optional<Tensor>& dout, const c
   uint8_t* qc = q_col.has_value() ? reinterpret_cast<uint8_t*>(q_col->data_ptr()) : nullptr;
   uint8_t* sc = sf_col.has_value() ? reinterpret_cast<uint8_t*>(sf_col->data_ptr()) : nullptr;
   TORCH_CHECK(qc == nullptr || ld_col % 32 == 0, "quant_glu: transposed copy needs a row count padded to 32");
-  bux::quant_mxfp8_glu(h.data_ptr(), dp, qr, sr, qc, sc, rows, (int)f, ld_col, (int)kind, (float)limit, (float)up_offset, stream_of(h));
+  if (row_scale.has_value())
+    TORCH_CHECK(row_scale->is_cuda() && row_scale->scalar_type() == at::kFloat && row_scale->is_contiguous() &&
+                row_scale->numel() >= rows && !dout.has_value(), "quant_glu: row_scale is fp32 [rows], activation only");
+  bux::quant_mxfp8_glu(h.data_ptr(), dp, opt_f32(row_scale), qr, sr, qc, sc, rows, (int)f, ld_col, (int)kind,
+                       (float)limit, (float)up_offset, stream_of(h));
 }
 
 // ------------------------------------------------------------------ loss / optimiser / MoE rows
@@ -361,7 +366,7 @@ TORCH_LIBRARY(bux_b200, m) {
   m.def("glu_fwd(Tensor h, Tensor(a!) out, Tensor? row_scale, int kind, float limit, float up_offset) -> ()", &glu_fwd);
   m.def("glu_bwd(Tensor h, Tensor dout, Tensor(a!) dh, Tensor? row_scale, Tensor? d_row_scale, int kind, float limit, float up_offset) -> ()", &glu_bwd);
   m.def("quant_mxfp8(Tensor x, Tensor? row_index, Tensor? row_scale, Tensor? q_row, Tensor? sf_row, Tensor? q_col, Tensor? sf_col, int rows, int cols, int ld_col, int batch, int x_batch_stride) -> ()", &quant_mxfp8);
-  m.def("quant_mxfp8_glu(Tensor h, Tensor? dout, Tensor? q_row, Tensor? sf_row, Tensor? q_col, Tensor? sf_col, int ld_col, int kind, float limit, float up_offset) -> ()", &quant_mxfp8_glu);
+  m.def("quant_mxfp8_glu(Tensor h, Tensor? dout, Tensor? row_scale, Tensor? q_row, Tensor? sf_row, Tensor? q_col, Tensor? sf_col, int ld_col, int kind, float limit, float up_offset) -> ()", &quant_mxfp8_glu);
   m.def("ce_fwd_bwd(Tensor(a!) logits, Tensor targets, Tensor? mask, Tensor(b!) loss, Tensor? logz, float grad_scale, float z_weight, float softcap) -> ()", &ce_fwd_bwd);
   m.def("adamw(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor? m_sf, Tensor? v_sf, Tensor? shadow, Tensor? grad_scale, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2, float grad_scale_const) -> ()", &adamw);
   m.def("sumsq(Tensor g, Tensor(a!) out) -> ()", &sumsq);

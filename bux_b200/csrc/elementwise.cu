@@ -480,7 +480,8 @@ __device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float 
 #endif
 enum { QSRC_PLAIN = 0, QSRC_GLU_FWD = 1, QSRC_GLU_BWD = 2 };
 struct QuantGlu {
-  const float* row_scale;     // PLAIN: output row r is its source row times row_scale[r] (rounded to bf16)
+  const float* row_scale;     // PLAIN: output row r is its source row times row_scale[r] (rounded to bf16);
+                              // GLU_FWD: the activation of row r times row_scale[r] (as glu_fwd_kernel)
   const __nv_bfloat16* dout;  // GLU_BWD: gradient of the activation's output [rows, f]
   int f;                      // h is [rows, 2f]: gate columns, then up columns
   int kind;
@@ -488,7 +489,7 @@ struct QuantGlu {
 };
 
 // Eight gated activations from eight gates and ups (same rounding as glu_fwd_kernel).
-__device__ __forceinline__ uint4 glu_fwd8(const uint4& gv, const uint4& uv, const QuantGlu& gp) {
+__device__ __forceinline__ uint4 glu_fwd8(const uint4& gv, const uint4& uv, const QuantGlu& gp, float rs) {
   uint4 o; uint32_t* ou = &o.x; const uint32_t* gu = &gv.x; const uint32_t* uu = &uv.x;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
@@ -497,7 +498,8 @@ __device__ __forceinline__ uint4 glu_fwd8(const uint4& gv, const uint4& uv, cons
       g.x = fminf(g.x, gp.limit); g.y = fminf(g.y, gp.limit);
       u.x = fminf(fmaxf(u.x, -gp.limit), gp.limit); u.y = fminf(fmaxf(u.y, -gp.limit), gp.limit);
     }
-    ou[j] = pack_bf16(act_fwd(g.x, gp.kind) * (u.x + gp.up_offset), act_fwd(g.y, gp.kind) * (u.y + gp.up_offset));
+    ou[j] = pack_bf16(act_fwd(g.x, gp.kind) * (u.x + gp.up_offset) * rs,
+                      act_fwd(g.y, gp.kind) * (u.y + gp.up_offset) * rs);
   }
   return o;
 }
@@ -606,7 +608,8 @@ quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long ld_x,
         const long r = r0 + (base + i) * 16 + (tid >> 4);
         uint4 o = make_uint4(0, 0, 0, 0);
         if (r < rows && c0 + cc < cols)
-          o = SRC == QSRC_GLU_FWD ? glu_fwd8(g[i], u[i], gp) : glu_bwd8(g[i], u[i], d[i], up_half, gp);
+          o = SRC == QSRC_GLU_FWD ? glu_fwd8(g[i], u[i], gp, gp.row_scale ? gp.row_scale[r] : 1.f)
+                                  : glu_bwd8(g[i], u[i], d[i], up_half, gp);
         *reinterpret_cast<uint4*>(&tile[qtile_at((base + i) * 16 + (tid >> 4), tid & 15)]) = o;
       }
     }
@@ -1125,12 +1128,13 @@ void quant_mxfp8(const void* x, long ld_x, const int* row_index, const float* ro
   dim3 grid((cols + 127) / 128, (unsigned)((extent + 127) / 128), batch);
   quant_mxfp8_kernel<QSRC_PLAIN><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, ld_x, row_index, q_row, sf_row, q_col, sf_col, rows, cols, ld_col, x_batch_stride, QuantGlu{row_scale, nullptr, 0, 0, 0.f, 0.f});
 }
-void quant_mxfp8_glu(const void* h, const void* dout, uint8_t* q_row, uint8_t* sf_row, uint8_t* q_col, uint8_t* sf_col,
-                     long rows, int f, long ld_col, int kind, float limit, float up_offset, cudaStream_t s) {
+void quant_mxfp8_glu(const void* h, const void* dout, const float* row_scale, uint8_t* q_row, uint8_t* sf_row,
+                     uint8_t* q_col, uint8_t* sf_col, long rows, int f, long ld_col, int kind, float limit,
+                     float up_offset, cudaStream_t s) {
   const int cols = dout ? 2 * f : f;
   const long extent = q_col ? (ld_col > rows ? ld_col : rows) : rows;
   dim3 grid((cols + 127) / 128, (unsigned)((extent + 127) / 128), 1);
-  QuantGlu gp{nullptr, (const __nv_bfloat16*)dout, f, kind, limit, up_offset};
+  QuantGlu gp{dout ? nullptr : row_scale, (const __nv_bfloat16*)dout, f, kind, limit, up_offset};
   if (dout) quant_mxfp8_kernel<QSRC_GLU_BWD><<<grid, 256, 0, s>>>((const __nv_bfloat16*)h, 2L * f, nullptr, q_row, sf_row, q_col, sf_col, rows, cols, ld_col, 0, gp);
   else quant_mxfp8_kernel<QSRC_GLU_FWD><<<grid, 256, 0, s>>>((const __nv_bfloat16*)h, 2L * f, nullptr, q_row, sf_row, q_col, sf_col, rows, cols, ld_col, 0, gp);
 }

@@ -18,9 +18,11 @@ void glu_fwd(const void* h, void* out, const float* row_scale, long rows, int f,
 void glu_bwd(const void* h, const void* dout, void* dh, const float* row_scale, float* d_row_scale, long rows, int f, int kind, float limit, float up_offset, cudaStream_t s);
 void quant_mxfp8(const void* x, long ld_x, const int* row_index, const float* row_scale, uint8_t* q_row, uint8_t* sf_row, uint8_t* q_col, uint8_t* sf_col, long rows, int cols, long ld_col, int batch, long x_batch_stride, cudaStream_t s);
 // Quantise glu(h) [rows, f] (dout null) or the gradient of h [rows, 2f] given dout [rows, f],
-// computed tile by tile from h [rows, 2f]; f % 128 == 0 for the gradient.
-void quant_mxfp8_glu(const void* h, const void* dout, uint8_t* q_row, uint8_t* sf_row, uint8_t* q_col, uint8_t* sf_col,
-                     long rows, int f, long ld_col, int kind, float limit, float up_offset, cudaStream_t s);
+// computed tile by tile from h [rows, 2f]; f % 128 == 0 for the gradient. `row_scale` (fp32
+// [rows], activation only) multiplies row r of the activation before it is rounded.
+void quant_mxfp8_glu(const void* h, const void* dout, const float* row_scale, uint8_t* q_row, uint8_t* sf_row,
+                     uint8_t* q_col, uint8_t* sf_col, long rows, int f, long ld_col, int kind, float limit,
+                     float up_offset, cudaStream_t s);
 void ce_fwd_bwd(void* logits, const int* targets, const float* mask, float* loss, float* logz, long rows, int vocab, long ld, float grad_scale, float z_weight, float softcap, cudaStream_t s);
 const char* adamw(void* p, bool p_bf16, const void* g, bool g_bf16, void* m, void* v, uint8_t* m_sf, uint8_t* v_sf, int mom,
                   void* shadow, long n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,

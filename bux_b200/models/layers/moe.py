@@ -219,7 +219,8 @@ class MoE(nn.Module):
         else:
             out = ops.moe_experts(flat, self.experts_gate_up, self.experts_down,
                                   w_ffn.reshape(bsz * t, -1), idx_ffn.reshape(bsz * t, -1),
-                                  act=ec.activation, limit=ec.limit, up_offset=ec.up_offset, fmt=fmt)
+                                  act=ec.activation, limit=ec.limit, up_offset=ec.up_offset, fmt=fmt,
+                                  chunks=getattr(ctx.methods, "moe_chunks", 1) if ctx.methods is not None else 1)
         out = out.view(bsz, t, inner)
         if c.num_zero_experts:
             zero = torch.where(is_zero, weights, torch.zeros_like(weights)).sum(-1, keepdim=True)

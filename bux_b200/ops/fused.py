@@ -117,122 +117,151 @@ def sort_picks(experts: torch.Tensor, num_experts: int, align: int = 128):
     return row_index, pos.view(t, k), offsets.to(torch.int32)
 
 
+def _row_weights(wts: torch.Tensor, pos: torch.Tensor, rows: int) -> torch.Tensor:
+    """fp32[rows]: the router weight of each expert-sorted row (0 for padding rows)."""
+    w_row = torch.zeros(rows, dtype=torch.float32, device=wts.device)
+    w_row[pos.reshape(-1).long()] = wts.reshape(-1)
+    return w_row
+
+
 class _SortedExperts(torch.autograd.Function):
+    """out[t] = Σ_j w[t,j] · expert_{e[t,j]}(x[t]) on one GPU.
+
+    A row's router weight multiplies its *activation* (a' = w · glu(h)), so the down
+    projection already yields weighted rows and the combine is a plain sum. In the
+    backward the gradient of the weights then falls out of the activation's backward
+    (d w = <da', glu(h)>, one scalar per row from `glu_bwd`), and the experts' outputs are
+    never needed again. Tokens are walked in `chunks` equal ranges, which bounds the
+    sorted intermediates (rows × 2f and rows × d) to one range at a time; weight
+    gradients accumulate over the ranges in fp32."""
+
     @staticmethod
-    def forward(ctx, x, w_gu, w_down, weights, experts, act, limit, up_offset, mx):
+    def forward(ctx, x, w_gu, w_down, weights, experts, act, limit, up_offset, mx, chunks):
         K = _K()
         t, d = x.shape
         e, f2, _ = w_gu.shape
         f = f2 // 2
         kind = K.KIND_MXFP8 if mx else K.KIND_BF16
-        row_index, pos, offsets = sort_picks(experts, e)
-        rows = row_index.numel()
+        grad = any(ctx.needs_input_grad)
         wts = weights.float().contiguous()
-        xtq = xtsf = None
+        chunks = chunks if chunks > 1 and t % chunks == 0 else 1
+        tc = t // chunks
+        out = torch.empty(t, d, dtype=x.dtype, device=x.device)
         if mx:
-            # with a backward to come, the transposed copy for dW is written in the same pass
-            xq, xsf, xtq, xtsf = K.quant_mxfp8(x, row_index=row_index, rows=rows,
-                                               colwise=any(ctx.needs_input_grad))
-            gq, gsf, _, _ = K.quant_mxfp8_batched(w_gu.detach(), rowwise=True)
-            h = K.grouped_gemm(xq, gq, offsets, f2, d, kind=kind, asf=xsf, bsf=gsf)
-            del xq, xsf, gq, gsf
-        else:
-            xs = K.gather_rows(x, row_index, rows)
-            h = K.grouped_gemm(xs, w_gu.view(e * f2, d), offsets, f2, d)
-        if mx:
-            # the activation is quantised as it is computed: no bf16 copy of it exists
-            aq, asf, _, _ = K.quant_mxfp8_glu(h, None, act, limit=limit, up_offset=up_offset)
-            dq, dsf, _, _ = K.quant_mxfp8_batched(w_down.detach(), rowwise=True)
-            y = K.grouped_gemm(aq, dq, offsets, d, f, kind=kind, asf=asf, bsf=dsf)
-            del aq, asf, dq, dsf
-        else:
-            a = K.glu_fwd(h, act, None, limit, up_offset)
-            y = K.grouped_gemm(a, w_down.view(e * d, f), offsets, d, f)
-        out = K.combine_rows(y, pos, wts, t)
-        ctx.save_for_backward(x, w_gu, w_down, wts, row_index, pos, offsets, h, y, xtq, xtsf)
-        ctx.cfg = (act, limit, up_offset, mx)
+            # both orientations of the weights in one pass when a backward follows
+            gq, gsf, gtq, gtsf = K.quant_mxfp8_batched(w_gu.detach(), rowwise=True, colwise=grad)
+            dq, dsf, dtq, dtsf = K.quant_mxfp8_batched(w_down.detach(), rowwise=True, colwise=grad)
+        saved = []
+        for c in range(chunks):
+            xc, ec, wc = x[c * tc:(c + 1) * tc], experts[c * tc:(c + 1) * tc], wts[c * tc:(c + 1) * tc]
+            row_index, pos, offsets = sort_picks(ec, e)
+            rows = row_index.numel()
+            w_row = _row_weights(wc, pos, rows)
+            xtq = xtsf = None
+            if mx:
+                xq, xsf, xtq, xtsf = K.quant_mxfp8(xc, row_index=row_index, rows=rows, colwise=grad)
+                h = K.grouped_gemm(xq, gq, offsets, f2, d, kind=kind, asf=xsf, bsf=gsf)
+                del xq, xsf
+                # the weighted activation is quantised as it is computed: no bf16 copy exists
+                aq, asf, _, _ = K.quant_mxfp8_glu(h, None, act, limit=limit, up_offset=up_offset, row_scale=w_row)
+                y = K.grouped_gemm(aq, dq, offsets, d, f, kind=kind, asf=asf, bsf=dsf)
+                del aq, asf
+            else:
+                xs = K.gather_rows(xc, row_index, rows)
+                h = K.grouped_gemm(xs, w_gu.view(e * f2, d), offsets, f2, d)
+                a = K.glu_fwd(h, act, w_row, limit, up_offset)
+                y = K.grouped_gemm(a, w_down.view(e * d, f), offsets, d, f)
+                del xs, a
+            K.combine_rows_into(y, pos, None, out[c * tc:(c + 1) * tc])
+            del y
+            if grad:
+                saved.append((row_index, pos, offsets, w_row, h, xtq, xtsf))
+        ctx.save_for_backward(x, w_gu, w_down)
+        ctx.chunks_saved = saved
+        ctx.wq = (gtq, gtsf, dtq, dtsf) if mx and grad else None
+        ctx.cfg = (act, limit, up_offset, mx, tc, weights.dtype)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         K = _K()
-        x, w_gu, w_down, wts, row_index, pos, offsets, h, y, xtq, xtsf = ctx.saved_tensors
-        act, limit, up_offset, mx = ctx.cfg
+        x, w_gu, w_down = ctx.saved_tensors
+        act, limit, up_offset, mx, tc, w_dtype = ctx.cfg
+        saved, ctx.chunks_saved = ctx.chunks_saved, None
         t, d = x.shape
         e, f2, _ = w_gu.shape
         f = f2 // 2
-        rows = row_index.numel()
         kind = K.KIND_MXFP8 if mx else K.KIND_BF16
         dout = dout.contiguous()
-        if mx:
-            # dy[r] = w[r]·dout[token(r)] is formed inside the quantiser (a row gather with a
-            # scale), so the bf16 gradient of the experts' rows is never written
-            dwts = K.combine_dots(y, dout, pos)
-            w_row = torch.zeros(rows, dtype=torch.float32, device=dout.device)
-            w_row[pos.reshape(-1).long()] = wts.reshape(-1)
-            dy = None
-        else:
-            dy, dwts = K.combine_bwd(y, dout, pos, wts, rows)
-        del y
         g_gu = getattr(w_gu, "main_grad", None)
         g_down = getattr(w_down, "main_grad", None)
+        many = len(saved) > 1
+        # one range: the GEMM writes the gradient in the dtype it is kept in; several: fp32 sums
+        acc_gu, acc_down = g_gu, g_down
+        if many and acc_gu is None:
+            acc_gu = torch.zeros(e, f2, d, dtype=torch.float32, device=x.device)
+        if many and acc_down is None:
+            acc_down = torch.zeros(e, d, f, dtype=torch.float32, device=x.device)
         if mx:
-            dyq, dysf, dytq, dytsf = K.quant_mxfp8(dout, rowwise=True, colwise=True, row_index=row_index,
-                                                   rows=rows, row_scale=w_row)
-            # the activation is recomputed inside the quantiser (cheaper than keeping it)
-            _, _, atq, atsf = K.quant_mxfp8_glu(h, None, act, rowwise=False, colwise=True,
-                                                limit=limit, up_offset=up_offset)
-            # dW_down[e] = dy_e^T · a_e
-            dw_down = K.grouped_gemm_k(dytq, atq, offsets, d, f, kind=kind, asf=dytsf, bsf=atsf,
-                                       out=g_down, accumulate=g_down is not None,
-                                     out_dtype=_grad_dtype(w_down))
-            del dytq, dytsf, atq, atsf
-            # da = dy · W_down  (per expert, contraction over d): B = W_down^T rows [f, d]
-            # W_down[e]^T quantised along d: the transposed copy the quantiser writes anyway
-            _, _, tq, tsf = K.quant_mxfp8_batched(w_down.detach(), rowwise=False, colwise=True)
-            da = K.grouped_gemm(dyq, tq, offsets, f, d, kind=kind, asf=dysf, bsf=tsf)
-            del tq, tsf, dyq, dysf
-        else:
-            a = K.glu_fwd(h, act, None, limit, up_offset)
-            dw_down = K.grouped_gemm_k(dy, a, offsets, d, f, a_mn=True, b_mn=True, out=g_down,
-                                       accumulate=g_down is not None,
-                                     out_dtype=_grad_dtype(w_down))
-            da = K.grouped_gemm(dy, w_down.view(e * d, f), offsets, f, d, b_mn=True)
-            del a
-        del dy
-        if mx:
-            # the gradient of h goes through bf16: computing it inside the quantiser
-            # (`quant_mxfp8_glu` with `dout`) measured slower than these two passes
-            dh, _ = K.glu_bwd(h, da, act, None, limit, up_offset)
-            del da
-            hq, hsf, htq, htsf = K.quant_mxfp8(dh, rowwise=True, colwise=True)
-            del dh
-            if xtq is None:
-                _, _, xtq, xtsf = K.quant_mxfp8(x, rowwise=False, colwise=True, row_index=row_index, rows=rows)
-            dw_gu = K.grouped_gemm_k(htq, xtq, offsets, f2, d, kind=kind, asf=htsf, bsf=xtsf,
-                                     out=g_gu, accumulate=g_gu is not None,
-                                     out_dtype=_grad_dtype(w_gu))
-            del htq, htsf, xtq, xtsf
-            _, _, tq, tsf = K.quant_mxfp8_batched(w_gu.detach(), rowwise=False, colwise=True)  # [E*d, 2f]
-            dxs = K.grouped_gemm(hq, tq, offsets, d, f2, kind=kind, asf=hsf, bsf=tsf)
-        else:
-            dh, _ = K.glu_bwd(h, da, act, None, limit, up_offset)
-            del da
-            xs = K.gather_rows(x, row_index, rows)
-            dw_gu = K.grouped_gemm_k(dh, xs, offsets, f2, d, a_mn=True, b_mn=True, out=g_gu,
-                                     accumulate=g_gu is not None,
-                                     out_dtype=_grad_dtype(w_gu))
-            dxs = K.grouped_gemm(dh, w_gu.view(e * f2, d), offsets, d, f2, b_mn=True)
-        dx = K.combine_rows(dxs, pos, None, t)
+            gtq, gtsf, dtq, dtsf = ctx.wq
+            ctx.wq = None
+        dx = torch.empty_like(x)
+        dwts = torch.empty(t, saved[0][1].shape[1], dtype=torch.float32, device=x.device)
+        dw_gu = dw_down = None
+        for c, (row_index, pos, offsets, w_row, h, xtq, xtsf) in enumerate(saved):
+            saved[c] = None
+            rows = row_index.numel()
+            dc, xc = dout[c * tc:(c + 1) * tc], x[c * tc:(c + 1) * tc]
+            if mx:
+                # dy[r] = dout[token(r)]: a row gather inside the quantiser (both orientations)
+                dyq, dysf, dytq, dytsf = K.quant_mxfp8(dc, rowwise=True, colwise=True, row_index=row_index, rows=rows)
+                # the weighted activation is recomputed inside the quantiser (cheaper than keeping it)
+                _, _, atq, atsf = K.quant_mxfp8_glu(h, None, act, rowwise=False, colwise=True, limit=limit,
+                                                    up_offset=up_offset, row_scale=w_row)
+                # dW_down[e] = dy_e^T · a'_e
+                dw_down = K.grouped_gemm_k(dytq, atq, offsets, d, f, kind=kind, asf=dytsf, bsf=atsf, out=acc_down,
+                                           accumulate=acc_down is not None, out_dtype=_grad_dtype(w_down))
+                del dytq, dytsf, atq, atsf
+                # da' = dy · W_down (per expert, contraction over d)
+                da = K.grouped_gemm(dyq, dtq, offsets, f, d, kind=kind, asf=dysf, bsf=dtsf)
+                del dyq, dysf
+            else:
+                dy = K.gather_rows(dc, row_index, rows)
+                a = K.glu_fwd(h, act, w_row, limit, up_offset)
+                dw_down = K.grouped_gemm_k(dy, a, offsets, d, f, a_mn=True, b_mn=True, out=acc_down,
+                                           accumulate=acc_down is not None, out_dtype=_grad_dtype(w_down))
+                da = K.grouped_gemm(dy, w_down.view(e * d, f), offsets, f, d, b_mn=True)
+                del a, dy
+            # dh, and per row <da', glu(h)> = the gradient of that row's router weight
+            dh, drs = K.glu_bwd(h, da, act, w_row, limit, up_offset)
+            del da, h
+            dwts[c * tc:(c + 1) * tc] = drs[pos.reshape(-1).long()].view(pos.shape)
+            if mx:
+                hq, hsf, htq, htsf = K.quant_mxfp8(dh, rowwise=True, colwise=True)
+                del dh
+                dw_gu = K.grouped_gemm_k(htq, xtq, offsets, f2, d, kind=kind, asf=htsf, bsf=xtsf, out=acc_gu,
+                                         accumulate=acc_gu is not None, out_dtype=_grad_dtype(w_gu))
+                del htq, htsf, xtq, xtsf
+                dxs = K.grouped_gemm(hq, gtq, offsets, d, f2, kind=kind, asf=hsf, bsf=gtsf)
+                del hq, hsf
+            else:
+                xs = K.gather_rows(xc, row_index, rows)
+                dw_gu = K.grouped_gemm_k(dh, xs, offsets, f2, d, a_mn=True, b_mn=True, out=acc_gu,
+                                         accumulate=acc_gu is not None, out_dtype=_grad_dtype(w_gu))
+                dxs = K.grouped_gemm(dh, w_gu.view(e * f2, d), offsets, d, f2, b_mn=True)
+                del xs, dh
+            K.combine_rows_into(dxs, pos, None, dx[c * tc:(c + 1) * tc])
+            del dxs
         gw_gu = None if g_gu is not None else dw_gu.to(w_gu.dtype)
         gw_down = None if g_down is not None else dw_down.to(w_down.dtype)
-        return dx, gw_gu, gw_down, dwts.to(wts.dtype), None, None, None, None, None
+        return dx, gw_gu, gw_down, dwts.to(w_dtype), None, None, None, None, None, None
 
 
 def moe_experts(x, w_gate_up, w_down, weights, experts, *, act: str = "swish",
-                limit: Optional[float] = None, up_offset: float = 0.0, fmt: str = "bf16"):
+                limit: Optional[float] = None, up_offset: float = 0.0, fmt: str = "bf16", chunks: int = 1):
     """Routed experts on x [T,d]: out[t] = Σ_j weights[t,j] · expert_{experts[t,j]}(x[t]).
-    w_gate_up [E, 2f, d] (gate rows first), w_down [E, d, f]."""
+    w_gate_up [E, 2f, d] (gate rows first), w_down [E, d, f]. `chunks` walks the tokens in that
+    many equal ranges (``methods(moe_chunks=...)``)."""
     e, f2, d = w_gate_up.shape
     f = f2 // 2
     mx = fmt in ("mxfp8", "mxfp8_2d")
@@ -240,7 +269,7 @@ def moe_experts(x, w_gate_up, w_down, weights, experts, *, act: str = "swish",
     if (kernels_on(x) and shapes_ok and act in ("swish", "quick_gelu", "gelu_tanh", "relu2")
             and w_gate_up.dtype == torch.bfloat16):
         return _SortedExperts.apply(x.contiguous(), w_gate_up, w_down, weights, experts, act,
-                                    float(limit or 0.0), float(up_offset), mx)
+                                    float(limit or 0.0), float(up_offset), mx, int(chunks))
     return moe_reference(x, w_gate_up, w_down, weights, experts, act, limit, up_offset)
 
 

@@ -184,11 +184,13 @@ def quant_mxfp8(x: torch.Tensor, *, rowwise: bool = True, colwise: bool = False,
 
 
 def quant_mxfp8_glu(h: torch.Tensor, dout: Optional[torch.Tensor] = None, kind: str = "swish", *,
-                    rowwise: bool = True, colwise: bool = False, limit: float = 0.0, up_offset: float = 0.0):
+                    rowwise: bool = True, colwise: bool = False, limit: float = 0.0, up_offset: float = 0.0,
+                    row_scale: Optional[torch.Tensor] = None):
     """MXFP8 copies of glu(h) [R, f] (`dout` None), or of the gradient of h [R, 2f] for the
     output gradient `dout` [R, f], computed from h [R, 2f] inside the quantiser: the bf16
     activation (gradient) is never written. Same values as `quant_mxfp8(glu_fwd(h))` /
-    `quant_mxfp8(glu_bwd(h, dout))`. Returns (q_row, sf_row, q_col, sf_col)."""
+    `quant_mxfp8(glu_bwd(h, dout))`. `row_scale` (fp32 [rows], activation only) multiplies each
+    row before it is rounded, as `glu_fwd(h, kind, row_scale)`. Returns (q_row, sf_row, q_col, sf_col)."""
     r, f2 = h.shape
     c = f2 if dout is not None else f2 // 2
     dev = h.device
@@ -200,7 +202,7 @@ def quant_mxfp8_glu(h: torch.Tensor, dout: Optional[torch.Tensor] = None, kind: 
     if colwise:
         q_col = torch.empty(c, r_pad, dtype=torch.float8_e4m3fn, device=dev)
         sf_col = torch.empty(sf_bytes(c, r_pad), dtype=torch.uint8, device=dev)
-    ops().quant_mxfp8_glu(h, dout, None if q_row is None else q_row.view(torch.uint8), sf_row,
+    ops().quant_mxfp8_glu(h, dout, row_scale, None if q_row is None else q_row.view(torch.uint8), sf_row,
                           None if q_col is None else q_col.view(torch.uint8), sf_col, r_pad,
                           ACT_KINDS[kind], float(limit), float(up_offset))
     _count()
@@ -334,6 +336,13 @@ def combine_rows(y, pos, w, tokens: int):
     ops().combine_rows(y, pos, w, out)
     _count()
     return out
+
+
+def combine_rows_into(y, pos, w, out) -> None:
+    """out[t] = Σ_j w[t,j] · y[pos[t,j]] (w None: a plain sum) into a contiguous `out` [T, d]."""
+    assert out.is_contiguous()
+    ops().combine_rows(y, pos, w, out)
+    _count()
 
 
 # ------------------------------------------------------------------ attention
