@@ -25,6 +25,9 @@ from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
+# before torch starts its allocator: segments that grow in place (no fragmentation between the
+# step's large transients and the tensors kept across the step)
+os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
 
 MARGIN_BYTES = 14 << 30  # device memory left free when attention outputs are kept (fragmentation, chunk buffers)
 PUBLISHED_TOK_S_PER_GPU = 42391.0  # reference, 8xB300, MXFP8 `sorted` fsdp=8 (docs/performance/benchmarks.md:188)
@@ -174,6 +177,13 @@ def main() -> int:
             return float(out["loss"].item())
         return out
 
+    def note(text: str) -> None:
+        if rank == 0:
+            print(f"[bench] {text}", file=sys.stderr, flush=True)
+
+    def gib(b) -> str:
+        return f"{b / 2 ** 30:.1f} GiB"
+
     def agreed_min(value: int) -> int:
         if parallel is None:
             return value
@@ -183,6 +193,7 @@ def main() -> int:
         dist.all_reduce(t, op=dist.ReduceOp.MIN)
         return int(t.item())
 
+    note(f"state built: {gib(torch.cuda.memory_allocated(device))} allocated")
     torch.cuda.reset_peak_memory_stats(device)
     one_step(True)  # the probe step (an extra warm-up step)
     torch.cuda.synchronize()
@@ -190,6 +201,9 @@ def main() -> int:
     slack = torch.cuda.memory_reserved(device) - torch.cuda.max_memory_allocated(device)
     spare = free + max(0, slack) - MARGIN_BYTES
     keep_blocks = agreed_min(max(0, min(blocks, int(spare // kept_bytes))))
+    note(f"probe step: peak {gib(torch.cuda.max_memory_allocated(device))}, reserved "
+         f"{gib(torch.cuda.memory_reserved(device))}, free {gib(free)} of {gib(total_mem)}; "
+         f"attention outputs kept for {keep_blocks} of {blocks} blocks ({gib(kept_bytes)} each)")
 
     def set_keep(count: int) -> None:
         trainer.model.set_remat(True, offload=True, keep_attention=count if count else False)
@@ -204,10 +218,11 @@ def main() -> int:
             result = None
             try:
                 result = loop()
-            except torch.cuda.OutOfMemoryError:
+            except torch.cuda.OutOfMemoryError as err:
                 if parallel is not None:
                     raise  # the other ranks are inside a collective: the job ends here
                 failed = 1
+                note(f"out of memory at step {trainer.step} with {keep_blocks} blocks kept: {str(err)[:300]}")
             if not failed:
                 return result
             if keep_blocks == 0:
@@ -216,11 +231,19 @@ def main() -> int:
             set_keep(keep_blocks)
             import gc
 
+            from bux_b200.models import graph
+
+            graph._OFFLOADED.clear()
+            graph._IN_FLIGHT.clear()
+            torch.cuda.synchronize()
             gc.collect()
             torch.cuda.empty_cache()
+            note(f"after the failure: {gib(torch.cuda.memory_allocated(device))} allocated, "
+                 f"{gib(torch.cuda.mem_get_info(device)[0])} free; keeping {keep_blocks} blocks")
 
     set_keep(keep_blocks)
     guarded(lambda: [one_step(True) for _ in range(args.warmup)])
+    note(f"warm-up done: peak {gib(torch.cuda.max_memory_allocated(device))}")
     torch.cuda.synchronize()
     if parallel is not None:
         parallel.barrier()
@@ -244,6 +267,7 @@ def main() -> int:
         return start.elapsed_time(end), K.launches - launches0
 
     ms, launches = guarded(timed)
+    note(f"timed region done: {ms / args.steps:.0f} ms per step, peak {gib(torch.cuda.max_memory_allocated(device))}")
     K.check_status(device, "bench")
 
     # ---- end-to-end region through the public step API: every step's batch comes from pinned

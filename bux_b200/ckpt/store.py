@@ -99,10 +99,10 @@ def state_tree(trainer) -> dict:
             continue
         model[name] = b.detach()
     optim_tree: dict = {"count": torch.tensor(opt.step_count), "tokens": torch.tensor(trainer.tokens)}
-    for name, st in opt.state.items():
-        for k, v in st.items():
-            if isinstance(v, torch.Tensor) and k != "master":
-                optim_tree[f"{k}/{name}"] = v
+    shapes = {name: tuple(p.shape) for name, p in trainer.model.named_parameters()}
+    for name in opt.state:
+        for k, v in opt.moments_for_checkpoint(name, shapes[name]).items():
+            optim_tree[f"{k}/{name}"] = v
     return {"0": model, "1": optim_tree}
 
 
@@ -131,7 +131,13 @@ def save(folder, step: int, trainer) -> None:
 
 
 def load(folder, trainer) -> None:
+    """Restore `trainer` from a checkpoint of whole leaves: every rank reads the tree and
+    keeps its own part of each leaf (`Parallel.restore_tree` inverts what
+    `Parallel.checkpoint_tree` gathered), so a run resumes on the mesh it was saved on
+    or on another one."""
     tree, meta = read_tree(Path(folder) / "default")
+    if trainer.parallel is not None:
+        tree = trainer.parallel.restore_tree(trainer, tree)
     opt = trainer.optimizer
     model_state = tree["0"]
     flat_model = flatten(model_state)
@@ -160,6 +166,7 @@ def load(folder, trainer) -> None:
             else:
                 kind, name = path.split("/", 1)
                 name = name.replace("/", ".")
-                dst = opt.state[name][kind]
-                dst.copy_(value.to(dst.device).to(dst.dtype).view_as(dst))
+                if name not in opt.state:
+                    raise KeyError(f"the checkpoint holds optimizer state of '{name}', which this model has not")
+                opt.load_moment(name, kind, value)
     trainer.step = int(meta.get("step", opt.step_count))

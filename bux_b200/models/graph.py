@@ -309,9 +309,6 @@ class _BlockRun:
             ctx.taps = {k: list(v) for k, v in self.taps.items()}
             ctx.metrics, ctx.ports = {}, dict(self.ports)
             ctx.tail_values_unused = _ends_in_plain_moe_branch(self.block)
-            # a replay is followed at once by the block's backward: with one MoE layer in the block,
-            # what that layer leaves in the exchange buffers is still there when its backward runs
-            ctx.exchange_buffers_stay = _moe_layers(self.block) == 1
         from ..ops import functional as OF
 
         if self.kept is not None:
@@ -322,7 +319,6 @@ class _BlockRun:
         finally:
             OF.attention_replay = None
             ctx.tail_values_unused = False
-            ctx.exchange_buffers_stay = False
             if replay:
                 self.kept = None
             if replay:
@@ -332,12 +328,6 @@ class _BlockRun:
         if not replay:
             self.names = list(reported)
         return y, [reported[n] for n in self.names]
-
-
-def _moe_layers(block) -> int:
-    from .layers.moe import MoE
-
-    return sum(1 for m in block.modules() if isinstance(m, MoE))
 
 
 def _ends_in_plain_moe_branch(block) -> bool:

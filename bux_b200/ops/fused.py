@@ -309,88 +309,65 @@ def moe_reference(x, w_gate_up, w_down, weights, experts, act="swish", limit=Non
 # ------------------------------------------------------------------ experts on rows that are already sorted
 class _ExpertsOnSorted(torch.autograd.Function):
     """The expert stack on rows that already sit in expert-sorted, 128-padded order
-    (what an expert-parallel rank receives): y[r] = expert_{group(r)}(xs[r]).
-
-    `io` (optional) couples it to the exchange: ``io.before_forward()`` /
-    ``io.before_backward()`` make the stream wait for the senders' flags (or return
-    (flags, epoch) for the first GEMM to wait on in-kernel), ``io.y_out`` / ``io.dx_out``
-    are the buffers peers read the results from, and ``io.after_forward()`` /
-    ``io.after_backward()`` publish "ready"."""
+    (what an expert-parallel rank receives from a library all-to-all):
+    y[r] = expert_{group(r)}(xs[r])."""
 
     @staticmethod
-    def forward(ctx, xs, offsets, counts, w_gu, w_down, act, limit, up_offset, mx, io):
+    def forward(ctx, xs, offsets, counts, w_gu, w_down, act, limit, up_offset, mx):
         K = _K()
         rows, d = xs.shape
         e, f2, _ = w_gu.shape
         f = f2 // 2
         kind = K.KIND_MXFP8 if mx else K.KIND_BF16
-        wait = io.before_forward(in_kernel=not mx) if io is not None else None
-        wf, we = wait if wait is not None else (None, 0)
+        grad = any(ctx.needs_input_grad)
         if counts is not None:
             K.zero_pad_rows(xs, offsets, counts)
+        wq = None
         if mx:
-            xq, xsf, xtq, xtsf = K.quant_mxfp8(xs, rowwise=True, colwise=True)
-            gq, gsf, _, _ = K.quant_mxfp8_batched(w_gu.detach(), rowwise=True)
+            xq, xsf, xtq, xtsf = K.quant_mxfp8(xs, rowwise=True, colwise=grad)
+            gq, gsf, gtq, gtsf = K.quant_mxfp8_batched(w_gu.detach(), rowwise=True, colwise=grad)
+            dq, dsf, dtq, dtsf = K.quant_mxfp8_batched(w_down.detach(), rowwise=True, colwise=grad)
             h = K.grouped_gemm(xq, gq, offsets, f2, d, kind=kind, asf=xsf, bsf=gsf)
             del xq, xsf, gq, gsf
-            saved_x = (xtq, xtsf)
-        else:
-            h = K.grouped_gemm(xs, w_gu.view(e * f2, d), offsets, f2, d, wait_flags=wf, wait_epoch=we)
-            saved_x = (xs.clone(), None)
-        y_out = io.y_out(rows, d) if io is not None else None
-        if mx:
             aq, asf, _, _ = K.quant_mxfp8_glu(h, None, act, limit=limit, up_offset=up_offset)
-            dq, dsf, _, _ = K.quant_mxfp8_batched(w_down.detach(), rowwise=True)
-            y = K.grouped_gemm(aq, dq, offsets, d, f, kind=kind, asf=asf, bsf=dsf, out=y_out)
+            y = K.grouped_gemm(aq, dq, offsets, d, f, kind=kind, asf=asf, bsf=dsf)
+            saved_x = (xtq, xtsf)
+            wq = (gtq, gtsf, dtq, dtsf)
         else:
+            h = K.grouped_gemm(xs, w_gu.view(e * f2, d), offsets, f2, d)
             a = K.glu_fwd(h, act, None, limit, up_offset)
-            y = K.grouped_gemm(a, w_down.view(e * d, f), offsets, d, f, out=y_out)
-        if io is not None:
-            io.after_forward()
+            y = K.grouped_gemm(a, w_down.view(e * d, f), offsets, d, f)
+            saved_x = (xs.clone(), None)
         ctx.save_for_backward(saved_x[0], saved_x[1], offsets, counts, w_gu, w_down, h)
-        ctx.cfg = (act, limit, up_offset, mx, io)
+        ctx.wq = wq if grad else None
+        ctx.cfg = (act, limit, up_offset, mx)
         return y
 
     @staticmethod
     def backward(ctx, dy):
         K = _K()
         xsave, xtsf, offsets, counts, w_gu, w_down, h = ctx.saved_tensors
-        act, limit, up_offset, mx, io = ctx.cfg
+        act, limit, up_offset, mx = ctx.cfg
         e, f2, d = w_gu.shape
         f = f2 // 2
         kind = K.KIND_MXFP8 if mx else K.KIND_BF16
-        dy_scale = None
-        if io is not None:
-            dy = io.before_backward(dy)
-            dy_scale = io.dy_scale(dy.shape[0])  # the rows' weights, applied here (they arrived unscaled)
+        dy = dy.contiguous()
         if counts is not None:
             K.zero_pad_rows(dy, offsets, counts)
-        if dy_scale is not None and not mx:
-            dy = (dy.float() * dy_scale.unsqueeze(-1)).to(dy.dtype)
         g_gu = getattr(w_gu, "main_grad", None)
         g_down = getattr(w_down, "main_grad", None)
         if mx:
-            dyq, dysf, dytq, dytsf = K.quant_mxfp8(dy, rowwise=True, colwise=True, row_scale=dy_scale)
+            gtq, gtsf, dtq, dtsf = ctx.wq
+            ctx.wq = None
+            dyq, dysf, dytq, dytsf = K.quant_mxfp8(dy, rowwise=True, colwise=True)
             _, _, atq, atsf = K.quant_mxfp8_glu(h, None, act, rowwise=False, colwise=True,
                                                 limit=limit, up_offset=up_offset)
             dw_down = K.grouped_gemm_k(dytq, atq, offsets, d, f, kind=kind, asf=dytsf, bsf=atsf,
                                        out=g_down, accumulate=g_down is not None,
-                                     out_dtype=_grad_dtype(w_down))
+                                       out_dtype=_grad_dtype(w_down))
             del dytq, dytsf, atq, atsf
-            # W_down[e]^T quantised along d: the transposed copy the quantiser writes anyway
-            _, _, tq, tsf = K.quant_mxfp8_batched(w_down.detach(), rowwise=False, colwise=True)
-            da = K.grouped_gemm(dyq, tq, offsets, f, d, kind=kind, asf=dysf, bsf=tsf)
-            del tq, tsf, dyq, dysf
-        else:
-            a = K.glu_fwd(h, act, None, limit, up_offset)
-            dw_down = K.grouped_gemm_k(dy, a, offsets, d, f, a_mn=True, b_mn=True, out=g_down,
-                                       accumulate=g_down is not None,
-                                     out_dtype=_grad_dtype(w_down))
-            da = K.grouped_gemm(dy, w_down.view(e * d, f), offsets, f, d, b_mn=True)
-            del a
-        rows = h.shape[0]
-        dx_out = io.dx_out(rows, d) if io is not None else None
-        if mx:
+            da = K.grouped_gemm(dyq, dtq, offsets, f, d, kind=kind, asf=dysf, bsf=dtsf)
+            del dyq, dysf
             dh, _ = K.glu_bwd(h, da, act, None, limit, up_offset)
             del da
             hq, hsf, htq, htsf = K.quant_mxfp8(dh, rowwise=True, colwise=True)
@@ -399,30 +376,33 @@ class _ExpertsOnSorted(torch.autograd.Function):
                                      out=g_gu, accumulate=g_gu is not None,
                                      out_dtype=_grad_dtype(w_gu))
             del htq, htsf
-            _, _, tq, tsf = K.quant_mxfp8_batched(w_gu.detach(), rowwise=False, colwise=True)  # [E*d, 2f]
-            dxs = K.grouped_gemm(hq, tq, offsets, d, f2, kind=kind, asf=hsf, bsf=tsf, out=dx_out)
+            dxs = K.grouped_gemm(hq, gtq, offsets, d, f2, kind=kind, asf=hsf, bsf=gtsf)
         else:
+            a = K.glu_fwd(h, act, None, limit, up_offset)
+            dw_down = K.grouped_gemm_k(dy, a, offsets, d, f, a_mn=True, b_mn=True, out=g_down,
+                                       accumulate=g_down is not None,
+                                       out_dtype=_grad_dtype(w_down))
+            da = K.grouped_gemm(dy, w_down.view(e * d, f), offsets, f, d, b_mn=True)
+            del a
             dh, _ = K.glu_bwd(h, da, act, None, limit, up_offset)
             del da
             dw_gu = K.grouped_gemm_k(dh, xsave, offsets, f2, d, a_mn=True, b_mn=True, out=g_gu,
                                      accumulate=g_gu is not None,
                                      out_dtype=_grad_dtype(w_gu))
-            dxs = K.grouped_gemm(dh, w_gu.view(e * f2, d), offsets, d, f2, b_mn=True, out=dx_out)
-        if io is not None:
-            io.after_backward()
+            dxs = K.grouped_gemm(dh, w_gu.view(e * f2, d), offsets, d, f2, b_mn=True)
         gw_gu = None if g_gu is not None else dw_gu.to(w_gu.dtype)
         gw_down = None if g_down is not None else dw_down.to(w_down.dtype)
-        return dxs, None, None, gw_gu, gw_down, None, None, None, None, None
+        return dxs, None, None, gw_gu, gw_down, None, None, None, None
 
 
 def experts_on_sorted(xs, offsets, counts, w_gate_up, w_down, *, act="swish", limit=None,
-                      up_offset=0.0, fmt="bf16", io=None):
+                      up_offset=0.0, fmt="bf16"):
     """Expert stack over pre-sorted rows; see `_ExpertsOnSorted`. Falls back to plain
     PyTorch (per-group matmuls) off the GPU."""
     mx = fmt in ("mxfp8", "mxfp8_2d")
     if kernels_on(xs):
-        return _ExpertsOnSorted.apply(xs, offsets, counts, w_gate_up, w_down, act, float(limit or 0.0),
-                                      float(up_offset), mx, io)
+        return _ExpertsOnSorted.apply(xs.contiguous(), offsets, counts, w_gate_up, w_down, act,
+                                      float(limit or 0.0), float(up_offset), mx)
     f = w_gate_up.shape[1] // 2
     off = offsets.tolist()
     cnt = counts.tolist() if counts is not None else [off[g + 1] - off[g] for g in range(len(off) - 1)]

@@ -275,6 +275,16 @@ def glu_bwd(h, dout, kind: str = "swish", row_scale=None, limit: float = 0.0, up
     return dh, drs
 
 
+def glu_bwd_into(h, dout, kind: str, row_scale, d_row_scale, limit: float = 0.0, up_offset: float = 0.0):
+    """`glu_bwd` whose per-row gradient of `row_scale` lands in the caller's fp32 buffer
+    (cleared here first: the kernel adds into it). Returns dh."""
+    dh = torch.empty_like(h)
+    d_row_scale.zero_()
+    ops().glu_bwd(h, dout, dh, row_scale, d_row_scale, ACT_KINDS[kind], limit or 0.0, up_offset)
+    _count()
+    return dh
+
+
 # ------------------------------------------------------------------ loss / optimiser / rows
 def ce_fwd_bwd(logits, targets, mask, grad_scale: float, z_weight: float = 0.0, softcap: float = 0.0):
     """In place: logits become dlogits. Returns per-row loss (fp32)."""
@@ -384,8 +394,11 @@ def ep_signal(peer_flags, channel: int, world: int, my_rank: int, epoch: int) ->
 
 
 def ep_pull_combine(peer_base, rank_of, row_of, w, tokens: int, d: int, dtype, flags=None, epoch: int = 0,
-                    limit_s: float = 5.0):
-    out = torch.empty(tokens, d, dtype=dtype, device=rank_of.device)
+                    limit_s: float = 5.0, out=None):
+    """out[t] = Σ_j w[t,j] · rows of the peers' buffers (w None: a plain sum), into `out` when given."""
+    if out is None:
+        out = torch.empty(tokens, d, dtype=dtype, device=rank_of.device)
+    assert out.is_contiguous() and out.shape == (tokens, d)
     ops().ep_pull_combine(peer_base, rank_of, row_of, w, out, flags, epoch, status_word(rank_of.device), limit_s)
     _count()
     return out
@@ -407,9 +420,11 @@ def row_dots(a, b, out=None):
     return out
 
 
-def ep_pull_scalar(peer_base, rank_of, row_of, flags=None, epoch: int = 0, limit_s: float = 5.0):
+def ep_pull_scalar(peer_base, rank_of, row_of, flags=None, epoch: int = 0, limit_s: float = 5.0, out=None):
     """out[t, j] = the fp32 value at row row_of[t, j] of rank rank_of[t, j]'s buffer."""
-    out = torch.empty(row_of.shape, dtype=torch.float32, device=row_of.device)
+    if out is None:
+        out = torch.empty(row_of.shape, dtype=torch.float32, device=row_of.device)
+    assert out.is_contiguous() and out.shape == row_of.shape and out.dtype == torch.float32
     ops().ep_pull_scalar(peer_base, rank_of, row_of, out, flags, epoch, status_word(row_of.device), limit_s)
     _count()
     return out

@@ -273,6 +273,55 @@ class Parallel:
             tree = self.pipeline.gather_tree(tree)
         return tree if self.rank == 0 else None
 
+    def restore_tree(self, trainer, tree: dict) -> dict:
+        """The inverse of `checkpoint_tree`: from a tree of whole leaves (every rank read it),
+        what this rank holds. In the reverse order of the gathers: a pipeline stage keeps its
+        own layers' leaves, an expert rank its experts, a tensor rank its columns or rows of
+        every split parameter, and the sharding axes this rank's rows. Optimizer leaves have
+        their parameter's shape in a checkpoint, so one rule serves both."""
+        return _restore(self, trainer, tree)
+
+
+def _restore(par: "Parallel", trainer, tree: dict) -> dict:
+    """This rank's part of every leaf of a tree of whole leaves (see `Parallel.restore_tree`)."""
+    params = dict(trainer.model.named_parameters())
+    known = set(params) | {n for n, _ in trainer.model.named_buffers()}
+    piped = getattr(par, "pipeline", None) is not None
+    ep_world = dist.get_world_size(par.expert_group) if par.expert_group is not None else 1
+    ep_rank = dist.get_rank(par.expert_group) if par.expert_group is not None else 0
+    tp_world = par.shape["tensor"]
+    tp_rank = par.coords["tensor"]
+
+    def mine(name: str, t):
+        if not isinstance(t, torch.Tensor) or t.dim() == 0:
+            return t
+        if name not in known:
+            return None if piped else t      # another stage's leaf; otherwise `load` reports it
+        if ep_world > 1 and ("experts_gate_up" in name or "experts_down" in name) and t.dim() >= 1:
+            t = t.chunk(ep_world, dim=0)[ep_rank]
+        lay = par.tensor_layout.get(name)
+        if lay is not None and t.dim() > lay[0] and t.shape[lay[0]] == sum(lay[1]):
+            from . import tensor
+
+            t = tensor.shard_of(t, lay[0], lay[1], tp_rank, tp_world)
+        if par.fsdp is not None and name in par.fsdp.sharded and t.dim() >= 1 \
+                and t.shape[0] == par.fsdp.sharded[name]:
+            t = t.chunk(par.fsdp.world, dim=0)[par.fsdp.rank]
+        return t.contiguous()
+
+    def walk(node: dict) -> dict:
+        out = {}
+        for key, value in node.items():
+            if isinstance(value, dict):
+                out[key] = walk(value)
+            else:
+                kept = mine(key.replace("/", "."), value)
+                if kept is not None:
+                    out[key] = kept
+        return out
+
+    return {part: walk(node) if isinstance(node, dict) else node for part, node in tree.items()}
+
 
 def _gather_experts(tree: dict, group) -> dict:
     world = dist.get_world_size(group)

@@ -88,9 +88,16 @@ def route(idx: torch.Tensor, num_experts: int, group, cap_rows: int) -> Route:
 
 
 # ====================================================================== fused (peer memory)
+SLOTS = 2  # exchange buffers per kind: a chunk's rows travel while the chunk before it computes
+
+
 class FusedEP:
-    """State of the in-kernel exchange for one MoE shape: symmetric buffers, the peers'
-    base addresses, flag rows and epoch counters."""
+    """State of the in-kernel exchange for one MoE shape: symmetric buffers (two slots of
+    each kind, so that consecutive token chunks overlap), the peers' base addresses, flag
+    rows, epoch counters and the side stream the transfers run on."""
+
+    KINDS = (("x", 2), ("y", 2), ("dy", 2), ("dx", 2))   # [cap, d] bf16
+    SCALARS = ("xw", "dots")                               # [cap] fp32: a row's router weight; its gradient
 
     def __init__(self, group, device, d: int, cap_rows: int, dtype=torch.bfloat16):
         import torch.distributed._symmetric_memory as symm
@@ -98,151 +105,291 @@ class FusedEP:
         self.group, self.device, self.d, self.cap = group, device, d, cap_rows
         self.world, self.me = dist.get_world_size(group), dist.get_rank(group)
         name = group.group_name
+        # one symmetric allocation, carved into the pieces (every piece starts 256-byte aligned)
+        pieces, at = {}, 0
+        for key, width in self.KINDS:
+            for slot in range(SLOTS):
+                pieces[(key, slot)] = (at, cap_rows * d * width)
+                at += -(-cap_rows * d * width // 256) * 256
+        for key in self.SCALARS:
+            for slot in range(SLOTS):
+                pieces[(key, slot)] = (at, cap_rows * 4)
+                at += -(-cap_rows * 4 // 256) * 256
+        flags_at = at
+        at += 8 * self.world * 4
+        heap = symm.empty(at, dtype=torch.uint8, device=device)
+        hdl = symm.rendezvous(heap, name)
+        heap.zero_()
+        bases = [int(p) for p in hdl.buffer_ptrs]
+        self.heap = heap
         self.bufs, self.tables = {}, {}
-        for key in ("x", "y", "dy", "dx"):
-            buf = symm.empty(cap_rows, d, dtype=dtype, device=device)
-            hdl = symm.rendezvous(buf, name)
-            buf.zero_()
-            self.bufs[key] = buf
-            self.tables[key] = torch.tensor([int(p) for p in hdl.buffer_ptrs], dtype=torch.int64, device=device)
-        for key in ("dys", "dots"):  # per-row fp32: the weight of a pushed dy row, and <dy, y> of a row
-            buf = symm.empty(cap_rows, dtype=torch.float32, device=device)
-            hdl = symm.rendezvous(buf, name)
-            buf.zero_()
-            self.bufs[key] = buf
-            self.tables[key] = torch.tensor([int(p) for p in hdl.buffer_ptrs], dtype=torch.int64, device=device)
-        flags = symm.empty(8 * self.world, dtype=torch.int32, device=device)
-        fh = symm.rendezvous(flags, name)
-        flags.zero_()
-        self.flags = flags.view(8, self.world)
-        self.peer_flags = torch.tensor([int(p) for p in fh.buffer_ptrs], dtype=torch.int64, device=device)
+        for (key, slot), (off, size) in pieces.items():
+            view = heap[off:off + size]
+            self.bufs[(key, slot)] = (view.view(torch.float32) if key in self.SCALARS
+                                      else view.view(dtype).view(cap_rows, d))
+            self.tables[(key, slot)] = torch.tensor([b + off for b in bases], dtype=torch.int64, device=device)
+        self.flags = heap[flags_at:flags_at + 8 * self.world * 4].view(torch.int32).view(8, self.world)
+        self.peer_flags = torch.tensor([b + flags_at for b in bases], dtype=torch.int64, device=device)
         self.epoch = [0, 0, 0, 0, 0]
+        self.comm = torch.cuda.Stream(device=device)
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
 
-    def bump(self, ch: int) -> int:
+    def signal(self, ch: int) -> int:
+        """Publish the channel's next epoch to every peer, after the current stream's work."""
+        from ..ops import kernels as K
+
         self.epoch[ch] += 1
+        K.ep_signal(self.peer_flags, ch, self.world, self.me, self.epoch[ch])
         return self.epoch[ch]
 
-    def signal(self, ch: int) -> int:
+    def wait(self, ch: int, epoch: int) -> None:
+        """Make the current stream wait (bounded) until every peer has published `epoch`."""
         from ..ops import kernels as K
 
-        e = self.bump(ch)
-        K.ep_signal(self.peer_flags, ch, self.world, self.me, e)
-        return e
+        K.ep_wait(self.flags[ch], epoch)
 
 
-class _IO:
-    """What `_ExpertsOnSorted` needs from the exchange (see its docstring)."""
+def route_chunks(idx: torch.Tensor, num_experts: int, group, cap_rows: int, chunks: int) -> list:
+    """`route` for `chunks` equal token ranges at once: one all-gather of every range's
+    per-expert counts, then local integer work. Returns one `Route` per range, its token
+    indices relative to the range."""
+    t = idx.shape[0]
+    tc = t // chunks
+    world, me = dist.get_world_size(group), dist.get_rank(group)
+    el = num_experts // world
+    k = idx.shape[1]
+    dev = idx.device
+    p = tc * k
+    flat = idx.reshape(chunks, p)
+    order = torch.argsort(flat, dim=1, stable=True)
+    counts = torch.zeros(chunks, num_experts, dtype=torch.int32, device=dev)
+    counts.scatter_add_(1, flat, torch.ones_like(flat, dtype=torch.int32))
+    allc = torch.empty(world, chunks, num_experts, dtype=torch.int32, device=dev)
+    dist.all_gather_into_tensor(allc.view(-1), counts.view(-1), group=group)
+    allc64 = allc.long()
+    before_me = allc64[:me].sum(0)                                 # [C, E] rows of earlier sources
+    total = allc64.sum(0)                                          # [C, E]
+    padded = (total + ALIGN - 1) // ALIGN * ALIGN
+    by_owner = padded.view(chunks, world, el)
+    base = (by_owner.cumsum(2) - by_owner).reshape(chunks, num_experts)   # start on its owner
+    counts64 = counts.long()
+    my_start = counts64.cumsum(1) - counts64
+    sorted_e = flat.gather(1, order)
+    rank_within = torch.arange(p, device=dev).unsqueeze(0) - my_start.gather(1, sorted_e)
+    dst_row = base.gather(1, sorted_e) + before_me.gather(1, sorted_e) + rank_within
+    dropped = dst_row >= cap_rows
+    dst_row = torch.where(dropped, torch.full_like(dst_row, -1), dst_row).to(torch.int32)
+    dst_rank = (sorted_e // el).to(torch.int32)
+    row_of = torch.empty(chunks, p, dtype=torch.int32, device=dev).scatter_(1, order, dst_row)
+    rank_of = torch.empty(chunks, p, dtype=torch.int32, device=dev).scatter_(1, order, dst_rank)
+    mine = slice(me * el, (me + 1) * el)
+    offsets = torch.zeros(chunks, el + 1, dtype=torch.int64, device=dev)
+    offsets[:, :-1] = base[:, mine]
+    offsets[:, -1] = base[:, mine][:, -1] + padded[:, mine][:, -1]
+    offsets = offsets.clamp(max=cap_rows // ALIGN * ALIGN)
+    local_counts = torch.minimum(total[:, mine], offsets[:, 1:] - offsets[:, :-1]).to(torch.int32)
+    offsets = offsets.to(torch.int32)
+    src_token = (order // k).to(torch.int32)
+    n_dropped = dropped.sum(1)
+    return [Route(src_token[c], dst_rank[c], dst_row[c], rank_of[c].view(tc, k), row_of[c].view(tc, k),
+                  offsets[c], local_counts[c], order[c], n_dropped[c]) for c in range(chunks)]
 
-    def __init__(self, ep: FusedEP, x_epoch: int):
-        self.ep, self.x_epoch = ep, x_epoch
-        self.dy_epoch = None
 
-    def before_forward(self, in_kernel: bool):
-        from ..ops import kernels as K
+class _FusedExperts(torch.autograd.Function):
+    """One MoE layer's routed experts across the ranks, token chunk by token chunk, the
+    exchange on a side stream beside the GEMMs.
 
-        if in_kernel:
-            return self.ep.flags[CH_X], self.x_epoch
-        K.ep_wait(self.ep.flags[CH_X], self.x_epoch)
-        return None
+    Per chunk: push my rows (and each row's router weight) into the owners' slot, flag;
+    the owner waits for every sender's flag, runs up/gate GEMM → weighted activation →
+    down GEMM into its output slot, flags; I sum my picks' rows out of the owners' slots.
+    The weight multiplies the activation, so the combine is a plain sum and the weight's
+    gradient comes out of the activation's backward on the owner (one scalar per row,
+    pulled back with dx). The backward mirrors it with the dy / dx slots.
 
-    def y_out(self, rows, d):
-        return self.ep.bufs["y"][:rows]
-
-    def after_forward(self):
-        self.y_epoch = self.ep.signal(CH_Y)
-
-    def before_backward(self, dy):
-        from ..ops import kernels as K
-
-        K.ep_wait(self.ep.flags[CH_DY], self.ep.epoch[CH_DY])
-        return dy
-
-    def dy_scale(self, rows):
-        """The weights of the dy rows, which arrived unscaled: the expert stack applies them."""
-        return self.ep.bufs["dys"][:rows]
-
-    def dx_out(self, rows, d):
-        return self.ep.bufs["dx"][:rows]
-
-    def after_backward(self):
-        self.ep.signal(CH_DX)
-
-
-class _Dispatch(torch.autograd.Function):
-    """Forward: push my rows into the owners' buffers, flag them. Backward: pull the
-    owners' dx rows of my picks and sum them per token."""
+    Slot reuse is safe by construction: the side stream of every rank runs
+    push(0) push(1) pull(0) push(2) pull(1) ... and a pull waits for *every* owner's
+    "output ready" flag, which an owner raises after it has read the slot's input rows;
+    an owner overwrites an output slot only after every sender's next push into that slot's
+    input has been flagged, which each sender issues after its own pull of the old rows."""
 
     @staticmethod
-    def forward(ctx, x, ep: FusedEP, r: Route):
+    def forward(ctx, x, weights, w_gu, w_down, ep: FusedEP, routes, act, limit, up_offset, mx,
+                values_unused, side_stream):
         from ..ops import kernels as K
 
-        K.ep_push_rows(x, r.src_token, r.dst_rank, r.dst_row, ep.tables["x"])
-        ctx.x_epoch = ep.signal(CH_X)
-        ctx.ep, ctx.r, ctx.shape, ctx.dtype = ep, r, x.shape, x.dtype
-        rows = int(ep.cap)
-        return ep.bufs["x"][:rows]
+        t, d = x.shape
+        e, f2, _ = w_gu.shape
+        f = f2 // 2
+        chunks = len(routes)
+        tc = t // chunks
+        kind = K.KIND_MXFP8 if mx else K.KIND_BF16
+        grad = any(ctx.needs_input_grad)
+        main = torch.cuda.current_stream(x.device)
+        comm = ep.comm if side_stream else main
+        wts = weights.float().contiguous()
+        out = torch.empty(t, d, dtype=x.dtype, device=x.device)
+        cap = ep.cap
+        if mx:
+            gq, gsf, gtq, gtsf = K.quant_mxfp8_batched(w_gu.detach(), rowwise=True, colwise=grad)
+            dq, dsf, dtq, dtsf = K.quant_mxfp8_batched(w_down.detach(), rowwise=True, colwise=grad)
+        comm.wait_stream(main)
+        x_epoch, y_epoch, saved = {}, {}, []
 
-    @staticmethod
-    def backward(ctx, dxs):
-        from ..ops import kernels as K
+        def push(c):
+            r = routes[c]
+            with torch.cuda.stream(comm):
+                scale = wts[c * tc:(c + 1) * tc].reshape(-1)[r.order].contiguous()
+                K.ep_push_rows(x[c * tc:(c + 1) * tc], r.src_token, r.dst_rank, r.dst_row, ep.tables[("x", c % SLOTS)],
+                               row_scale=scale, peer_scale=ep.tables[("xw", c % SLOTS)])
+                x_epoch[c] = ep.signal(CH_X)
 
-        ep, r = ctx.ep, ctx.r
-        dx = K.ep_pull_combine(ep.tables["dx"], r.rank_of, r.row_of, None, ctx.shape[0], ctx.shape[1],
-                               ctx.dtype, flags=ep.flags[CH_DX], epoch=ep.epoch[CH_DX])
-        return dx, None, None
+        def compute(c):
+            r, slot = routes[c], c % SLOTS
+            ep.wait(CH_X, x_epoch[c])
+            xs = ep.bufs[("x", slot)]
+            K.zero_pad_rows(xs, r.offsets, r.counts)
+            w_row = ep.bufs[("xw", slot)][:cap]
+            y_out = ep.bufs[("y", slot)]
+            xtq = xtsf = None
+            if mx:
+                xq, xsf, xtq, xtsf = K.quant_mxfp8(xs, rowwise=True, colwise=grad)
+                h = K.grouped_gemm(xq, gq, r.offsets, f2, d, kind=kind, asf=xsf, bsf=gsf)
+                del xq, xsf
+                aq, asf, _, _ = K.quant_mxfp8_glu(h, None, act, limit=limit, up_offset=up_offset, row_scale=w_row)
+                K.grouped_gemm(aq, dq, r.offsets, d, f, kind=kind, asf=asf, bsf=dsf, out=y_out)
+            else:
+                h = K.grouped_gemm(xs, w_gu.view(e * f2, d), r.offsets, f2, d)
+                a = K.glu_fwd(h, act, w_row, limit, up_offset)
+                K.grouped_gemm(a, w_down.view(e * d, f), r.offsets, d, f, out=y_out)
+            y_epoch[c] = ep.signal(CH_Y)
+            if grad:
+                saved.append((h, xtq if mx else xs.clone(), xtsf, w_row.clone()))
 
+        def pull(c):
+            r = routes[c]
+            with torch.cuda.stream(comm):
+                ep.wait(CH_Y, y_epoch[c])
+                if not values_unused:
+                    K.ep_pull_combine(ep.tables[("y", c % SLOTS)], r.rank_of, r.row_of, None, tc, d, x.dtype,
+                                      out=out[c * tc:(c + 1) * tc])
 
-class _Combine(torch.autograd.Function):
-    """Forward: out[t] = Σ_j w[t,j]·y_owner[row(t,j)] read from the owners. Backward:
-    dw by a pulled dot product, and w·dout pushed into the owners' dy buffers."""
-
-    @staticmethod
-    def forward(ctx, y, weights, ep: FusedEP, r: Route, tokens: int, values_unused: bool = False,
-                y_stays: bool = False):
-        from ..ops import kernels as K
-
-        w = weights.float().contiguous()
-        # the backward takes <dout row, y row> on this rank: y lives in the shared exchange
-        # buffer, which the next MoE layer overwrites, so it is copied unless the caller says
-        # that the backward runs before anything else uses the buffer (a checkpointed replay)
-        ctx.y_rows = None
-        if any(ctx.needs_input_grad) and not y_stays:
-            ctx.y_rows = y.detach().clone()
-        ctx.y_epoch = ep.epoch[CH_Y]
-        if values_unused:
-            # the replay of a checkpointed block whose last op this is: only the graph is
-            # needed, so the rows stay where they are (nothing crosses NVLink)
-            out = torch.empty(tokens, ep.d, dtype=y.dtype, device=y.device)
-        else:
-            out = K.ep_pull_combine(ep.tables["y"], r.rank_of, r.row_of, w, tokens, ep.d, y.dtype,
-                                    flags=ep.flags[CH_Y], epoch=ctx.y_epoch)
-        ctx.save_for_backward(w)
-        ctx.ep, ctx.r, ctx.rows, ctx.wdtype = ep, r, y.shape[0], weights.dtype
+        for c in range(min(SLOTS, chunks)):
+            push(c)
+        for c in range(chunks):
+            compute(c)
+            pull(c)
+            if c + SLOTS < chunks:
+                push(c + SLOTS)
+        main.wait_stream(comm)
+        ctx.save_for_backward(x, w_gu, w_down)
+        ctx.held = (saved, (gtq, gtsf, dtq, dtsf) if mx and grad else None)
+        ctx.cfg = (ep, routes, act, limit, up_offset, mx, side_stream, weights.dtype)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         from ..ops import kernels as K
 
-        (w,) = ctx.saved_tensors
-        ep, r = ctx.ep, ctx.r
+        x, w_gu, w_down = ctx.saved_tensors
+        ep, routes, act, limit, up_offset, mx, side_stream, w_dtype = ctx.cfg
+        saved, wq = ctx.held
+        ctx.held = None
+        t, d = x.shape
+        e, f2, _ = w_gu.shape
+        f = f2 // 2
+        chunks = len(routes)
+        tc = t // chunks
+        k = routes[0].row_of.shape[1]
+        kind = K.KIND_MXFP8 if mx else K.KIND_BF16
+        main = torch.cuda.current_stream(x.device)
+        comm = ep.comm if side_stream else main
         dout = dout.contiguous()
-        # dout rows go to the owners as they are, each with its weight beside it
-        scale = w.reshape(-1)[r.order].contiguous()
-        K.ep_push_rows(dout, r.src_token, r.dst_rank, r.dst_row, ep.tables["dy"], row_scale=scale,
-                       peer_scale=ep.tables["dys"])
-        e_dy = ep.signal(CH_DY)
-        # as an owner: <dout row, y row> of every row that arrived here (y is this rank's own
-        # output), so that only one scalar per pick crosses NVLink for the router's gradient
-        K.ep_wait(ep.flags[CH_DY], e_dy)
-        y_rows = ctx.y_rows if ctx.y_rows is not None else ep.bufs["y"][:ctx.rows]
-        K.row_dots(ep.bufs["dy"][:ctx.rows], y_rows, ep.bufs["dots"])
-        ctx.y_rows = None
-        e_dot = ep.signal(CH_DOT)
-        dw = K.ep_pull_scalar(ep.tables["dots"], r.rank_of, r.row_of, flags=ep.flags[CH_DOT], epoch=e_dot)
-        return ep.bufs["dy"][:ctx.rows], dw.to(ctx.wdtype), None, None, None, None, None
+        cap = ep.cap
+        g_gu = getattr(w_gu, "main_grad", None)
+        g_down = getattr(w_down, "main_grad", None)
+        acc_gu, acc_down = g_gu, g_down
+        if chunks > 1 and acc_gu is None:
+            acc_gu = torch.zeros(e, f2, d, dtype=torch.float32, device=x.device)
+        if chunks > 1 and acc_down is None:
+            acc_down = torch.zeros(e, d, f, dtype=torch.float32, device=x.device)
+        if mx:
+            gtq, gtsf, dtq, dtsf = wq
+        dx = torch.empty_like(x)
+        dw = torch.empty(t, k, dtype=torch.float32, device=x.device)
+        comm.wait_stream(main)
+        dy_epoch, dx_epoch = {}, {}
+        result = {}
+
+        def push(c):
+            r = routes[c]
+            with torch.cuda.stream(comm):
+                K.ep_push_rows(dout[c * tc:(c + 1) * tc], r.src_token, r.dst_rank, r.dst_row,
+                               ep.tables[("dy", c % SLOTS)])
+                dy_epoch[c] = ep.signal(CH_DY)
+
+        def compute(c):
+            r, slot = routes[c], c % SLOTS
+            h, xsave, xtsf, w_row = saved[c]
+            saved[c] = None
+            ep.wait(CH_DY, dy_epoch[c])
+            dy = ep.bufs[("dy", slot)]
+            K.zero_pad_rows(dy, r.offsets, r.counts)
+            dots = ep.bufs[("dots", slot)][:cap]
+            dx_out = ep.bufs[("dx", slot)]
+            if mx:
+                dyq, dysf, dytq, dytsf = K.quant_mxfp8(dy, rowwise=True, colwise=True)
+                _, _, atq, atsf = K.quant_mxfp8_glu(h, None, act, rowwise=False, colwise=True, limit=limit,
+                                                    up_offset=up_offset, row_scale=w_row)
+                result["down"] = K.grouped_gemm_k(dytq, atq, r.offsets, d, f, kind=kind, asf=dytsf, bsf=atsf,
+                                                  out=acc_down, accumulate=acc_down is not None,
+                                                  out_dtype=fused._grad_dtype(w_down))
+                del dytq, dytsf, atq, atsf
+                da = K.grouped_gemm(dyq, dtq, r.offsets, f, d, kind=kind, asf=dysf, bsf=dtsf)
+                del dyq, dysf
+            else:
+                a = K.glu_fwd(h, act, w_row, limit, up_offset)
+                result["down"] = K.grouped_gemm_k(dy, a, r.offsets, d, f, a_mn=True, b_mn=True, out=acc_down,
+                                                  accumulate=acc_down is not None,
+                                                  out_dtype=fused._grad_dtype(w_down))
+                da = K.grouped_gemm(dy, w_down.view(e * d, f), r.offsets, f, d, b_mn=True)
+                del a
+            # dh, and <da', glu(h)> per row (the router weight's gradient) straight into the slot
+            dh = K.glu_bwd_into(h, da, act, w_row, dots, limit, up_offset)
+            del da, h
+            if mx:
+                hq, hsf, htq, htsf = K.quant_mxfp8(dh, rowwise=True, colwise=True)
+                del dh
+                result["gu"] = K.grouped_gemm_k(htq, xsave, r.offsets, f2, d, kind=kind, asf=htsf, bsf=xtsf,
+                                                out=acc_gu, accumulate=acc_gu is not None,
+                                                out_dtype=fused._grad_dtype(w_gu))
+                del htq, htsf
+                K.grouped_gemm(hq, gtq, r.offsets, d, f2, kind=kind, asf=hsf, bsf=gtsf, out=dx_out)
+            else:
+                result["gu"] = K.grouped_gemm_k(dh, xsave, r.offsets, f2, d, a_mn=True, b_mn=True, out=acc_gu,
+                                                accumulate=acc_gu is not None, out_dtype=fused._grad_dtype(w_gu))
+                K.grouped_gemm(dh, w_gu.view(e * f2, d), r.offsets, d, f2, b_mn=True, out=dx_out)
+            dx_epoch[c] = ep.signal(CH_DX)
+
+        def pull(c):
+            r = routes[c]
+            with torch.cuda.stream(comm):
+                ep.wait(CH_DX, dx_epoch[c])
+                K.ep_pull_combine(ep.tables[("dx", c % SLOTS)], r.rank_of, r.row_of, None, tc, d, x.dtype,
+                                  out=dx[c * tc:(c + 1) * tc])
+                K.ep_pull_scalar(ep.tables[("dots", c % SLOTS)], r.rank_of, r.row_of, out=dw[c * tc:(c + 1) * tc])
+
+        for c in range(min(SLOTS, chunks)):
+            push(c)
+        for c in range(chunks):
+            compute(c)
+            pull(c)
+            if c + SLOTS < chunks:
+                push(c + SLOTS)
+        main.wait_stream(comm)
+        gw_gu = None if g_gu is not None else result["gu"].to(w_gu.dtype)
+        gw_down = None if g_down is not None else result["down"].to(w_down.dtype)
+        return dx, dw.to(w_dtype), gw_gu, gw_down, None, None, None, None, None, None, None, None
 
 
 # ====================================================================== library all-to-all
@@ -344,21 +491,12 @@ class ExpertParallel:
         k = idx.shape[1]
         el = c.num_experts // self.world
         cap = self.cap_rows(t, k, el)
-        r = route(idx, c.num_experts, self.group, cap)
-        self.dropped = r.dropped
         ec = c.expert
         kw = dict(act=ec.activation, limit=ec.limit, up_offset=ec.up_offset, fmt=fmt)
         if self.method == "fused_ep" and x.is_cuda:
-            key = (d, cap)
-            if key not in self.fused:
-                self.fused[key] = FusedEP(self.group, x.device, d, cap, x.dtype)
-            ep = self.fused[key]
-            xs = _Dispatch.apply(x.contiguous(), ep, r)
-            io = _IO(ep, ep.epoch[CH_X])
-            y = fused.experts_on_sorted(xs, r.offsets, r.counts, moe.experts_gate_up, moe.experts_down,
-                                        io=io, **kw)
-            return _Combine.apply(y, weights, ep, r, t, bool(getattr(ctx, "tail_values_unused", False)),
-                                  bool(getattr(ctx, "exchange_buffers_stay", False)))
+            return self._fused(moe, x, weights, idx, ctx, kw)
+        r = route(idx, c.num_experts, self.group, cap)
+        self.dropped = r.dropped
         rows = x[r.src_token.long()]
         xs = _A2A.apply(rows, r.dst_rank, r.dst_row, self.group, cap)
         y = fused.experts_on_sorted(xs, r.offsets, r.counts, moe.experts_gate_up, moe.experts_down, **kw)
@@ -367,3 +505,27 @@ class ExpertParallel:
         out = torch.zeros(t, d, dtype=torch.float32, device=x.device)
         out = out.index_add(0, r.src_token.long(), picked.float() * wsorted.float())
         return out.to(x.dtype)
+
+    def _fused(self, moe, x, weights, idx, ctx, kw):
+        """The in-kernel exchange: tokens in ``methods(moe_chunks=...)`` equal ranges, the
+        transfers on a side stream with ``methods(moe_stream=true)``."""
+        c = moe.c
+        t, d = x.shape
+        k = idx.shape[1]
+        el = c.num_experts // self.world
+        methods = getattr(ctx, "methods", None)
+        chunks = max(1, int(getattr(methods, "moe_chunks", 1) or 1))
+        if t % chunks:
+            chunks = 1
+        cap = self.cap_rows(t // chunks, k, el)
+        key = (d, cap)
+        if key not in self.fused:
+            self.fused[key] = FusedEP(self.group, x.device, d, cap, x.dtype)
+        ep = self.fused[key]
+        routes = route_chunks(idx, c.num_experts, self.group, cap, chunks)
+        self.dropped = sum(r.dropped for r in routes)
+        mx = kw["fmt"] in ("mxfp8", "mxfp8_2d")
+        return _FusedExperts.apply(x.contiguous(), weights, moe.experts_gate_up, moe.experts_down, ep, routes,
+                                   kw["act"], float(kw["limit"] or 0.0), float(kw["up_offset"]), mx,
+                                   bool(getattr(ctx, "tail_values_unused", False)),
+                                   bool(getattr(methods, "moe_stream", False)))

@@ -144,6 +144,16 @@ def split(module: nn.Module, name: str, dim: int, pieces: list, r: int, n: int, 
     return new
 
 
+def shard_of(whole_tensor: torch.Tensor, dim: int, pieces: list, r: int, n: int) -> torch.Tensor:
+    """What `split` keeps of a whole tensor on rank r of n (the inverse of `whole`)."""
+    parts, off = [], 0
+    for size in pieces:
+        per = size // n
+        parts.append(whole_tensor.narrow(dim, off + r * per, per))
+        off += size
+    return torch.cat(parts, dim=dim).contiguous()
+
+
 def whole(shard: torch.Tensor, dim: int, pieces: list, group) -> torch.Tensor:
     """Inverse of `split` (every rank of the group calls it): the whole tensor."""
     n = dist.get_world_size(group)

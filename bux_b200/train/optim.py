@@ -397,6 +397,35 @@ class Optimizer:
         return out
 
     # ---- checkpointing
+    MOMENT_KEYS = ("m", "v", "momentum", "neuron_v")
+
+    def moments_for_checkpoint(self, name: str, shape) -> dict:
+        """A parameter's optimizer tensors as a checkpoint holds them: in the parameter's
+        shape (so that they shard and gather like the parameter), 8-bit block-scaled
+        moments expanded to fp32 (their scale blocks follow this rank's flat layout, which
+        another mesh does not share)."""
+        st, out = self.state[name], {}
+        for k in self.MOMENT_KEYS:
+            t = st.get(k)
+            if t is None:
+                continue
+            if k in ("m", "v") and f"{k}_sf" in st:
+                t = _from_8bit(t, st[f"{k}_sf"], squared=k == "v")
+            out[k] = t.view(shape) if t.numel() == math.prod(shape) else t
+        return out
+
+    def load_moment(self, name: str, key: str, value: torch.Tensor) -> None:
+        """The inverse: take a checkpoint's tensor (parameter-shaped) into this rank's state."""
+        st = self.state[name]
+        dst = st[key]
+        value = value.to(dst.device)
+        if key in ("m", "v") and f"{key}_sf" in st:
+            q, sf = _to_8bit(value.float().reshape(-1), squared=key == "v")
+            dst.copy_(q)
+            st[f"{key}_sf"].copy_(sf)
+            return
+        dst.copy_(value.to(dst.dtype).reshape(dst.shape))
+
     def state_dict(self) -> dict:
         return {"step": self.step_count, "state": self.state}
 
@@ -409,6 +438,30 @@ class Optimizer:
                         self.state[name][k].copy_(v)
                     else:
                         self.state[name][k] = v
+
+
+def _from_8bit(q: torch.Tensor, sf: torch.Tensor, squared: bool) -> torch.Tensor:
+    """fp32 values of block-scaled e4m3 moments (one E8M0 scale per 32 consecutive values;
+    the second moment is held as its square root): what `adamw_kernel` reads."""
+    n = q.numel()
+    vals = q.view(torch.float8_e4m3fn).float()
+    scale = torch.exp2(sf.clamp_min(1).float() - 127.0).repeat_interleave(32)[:n]
+    out = vals * scale
+    return out * out if squared else out
+
+
+def _to_8bit(x: torch.Tensor, squared: bool) -> tuple:
+    """(e4m3 bytes, E8M0 scale bytes) of fp32 moments, the layout `_from_8bit` reads."""
+    n = x.numel()
+    src = x.clamp_min(0).sqrt() if squared else x
+    blocks = (n + 31) // 32
+    padded = torch.zeros(blocks * 32, dtype=torch.float32, device=x.device)
+    padded[:n] = src
+    amax = padded.view(blocks, 32).abs().amax(1)
+    exp = torch.ceil(torch.log2(amax.clamp_min(1e-38) / 448.0)).clamp(-126, 127)
+    sf = (exp + 127).to(torch.uint8)
+    q = (padded.view(blocks, 32) / torch.exp2(exp).unsqueeze(1)).clamp(-448, 448).to(torch.float8_e4m3fn)
+    return q.view(torch.uint8).reshape(-1)[:n], sf
 
 
 def build_optimizer(model, train: T.TrainConfig, **kw) -> Optimizer:

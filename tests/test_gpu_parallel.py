@@ -60,8 +60,15 @@ def _worker(rank, world, port, overrides, out):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("fmt,remat", [("compute", "full"), ("mxfp8", "full"), ("mxfp8", "none")])
-def test_fused_expert_parallel_matches_one_gpu(cuda, tmp_path, fmt, remat):
+@pytest.mark.parametrize("fmt,remat,extra", [
+    ("compute", "full", []),
+    ("mxfp8", "full", ["methods.moe_chunks = 2", "methods.moe_stream = true"]),
+    ("mxfp8", "full", ["methods.moe_chunks = 4", "methods.moe_stream = true"]),
+    ("mxfp8", "none", ["methods.moe_chunks = 2", "methods.moe_stream = true"]),
+])
+def test_fused_expert_parallel_matches_one_gpu(cuda, tmp_path, fmt, remat, extra):
+    """Every rank count the box offers (2, 4, 8): experts over the ranks with the in-kernel
+    exchange, every other parameter sharded over the same ranks, against one GPU."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
@@ -77,15 +84,38 @@ def test_fused_expert_parallel_matches_one_gpu(cuda, tmp_path, fmt, remat):
     feed = iter(tr.batches())
     want = [tr.train_step(next(feed))["loss"].item() for _ in range(2)]
     state = {n: p.detach().float().cpu() for n, p in tr.model.named_parameters()}
-    out = str(tmp_path / "r0.pt")
-    mp.spawn(_worker, args=(2, _free_port(), [prec, keep, "mesh = mesh(expert=2)", "methods.moe = fused_ep",
-                                              "methods.capacity = 2.0"], out), nprocs=2, join=True)
-    got = torch.load(out)
-    assert got["losses"] == pytest.approx(want, abs=3e-2)
-    for name, p in state.items():
-        g = got["state"][name]
-        if "experts_" in name:
-            p = p[: g.shape[0]]
+    for world in [w for w in (2, 4, 8) if w <= torch.cuda.device_count()]:
+        out = str(tmp_path / f"r0_{world}.pt")
+        mp.spawn(_worker, args=(world, _free_port(), [prec, keep, f"mesh = mesh(expert={world})",
+                                                      "methods.moe = fused_ep", "methods.capacity = 2.0", *extra], out),
+                 nprocs=world, join=True)
+        got = torch.load(out)
+        assert got["losses"] == pytest.approx(want, abs=3e-2), world
+        for name, p in state.items():
+            g = got["state"][name]
+            if g.shape != p.shape:
+                p = p[: g.shape[0]]  # rank 0 holds the first experts and the first rows of the rest
+            err = ((g - p).norm() / p.norm().clamp_min(1e-9)).item()
+            assert err < 2e-2, (world, name, err)
+
+
+def test_fused_expert_parallel_drops_rows_past_the_capacity(cuda, tmp_path):
+    """With a capacity below what the routing needs, the in-kernel exchange and the library
+    all-to-all drop the same picks: two ranks of each must agree."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+
+    prec = "precision = precision(compute=bfloat16, matmuls=compute)"
+    outs = {}
+    for method in ("fused_ep", "all_to_all"):
+        out = str(tmp_path / f"{method}.pt")
+        mp.spawn(_worker, args=(2, _free_port(), [prec, "mesh = mesh(expert=2)", f"methods.moe = {method}",
+                                                  "methods.capacity = 0.6"], out), nprocs=2, join=True)
+        outs[method] = torch.load(out)
+    assert outs["fused_ep"]["losses"] == pytest.approx(outs["all_to_all"]["losses"], abs=3e-2)
+    for name, p in outs["all_to_all"]["state"].items():
+        g = outs["fused_ep"]["state"][name]
         err = ((g - p).norm() / p.norm().clamp_min(1e-9)).item()
         assert err < 2e-2, (name, err)
 

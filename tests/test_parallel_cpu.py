@@ -217,3 +217,57 @@ def test_muon_on_fsdp_shards_matches_one_rank(tmp_path, how):
     got = _spawn(2, src, ["mesh = mesh(fsdp=2)", f"methods.orthogonalize = {how}"], tmp_path)
     assert got["losses"] == pytest.approx(want_losses, abs=1e-5)
     _check_rows(got, want)
+
+
+# ------------------------------------------------------------------ resume on a sharded mesh
+def _resume_worker(rank, world, port, src, overrides, folder, out):
+    """Two steps, a checkpoint, a fresh trainer restored from it, two more steps; and the
+    same four steps without the interruption."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from bux_b200 import ckpt
+    from bux_b200.parallel.engine import Parallel
+    from bux_b200.train.trainer import Trainer
+
+    torch.set_num_threads(1)
+    run = compile_runs(src, filename="p.bux", overrides=overrides)[0]
+
+    def fresh():
+        par = Parallel(run.train, torch.device("cpu"))
+        return Trainer(run, device="cpu", parallel=par)
+
+    whole = fresh()
+    feed = iter(whole.batches())
+    straight = [whole.train_step(next(feed))["loss"].item() for _ in range(4)]
+    first = fresh()
+    feed = iter(first.batches())
+    resumed = [first.train_step(next(feed))["loss"].item() for _ in range(2)]
+    ckpt.save(folder, first.step, first)
+    second = fresh()
+    ckpt.load(os.path.join(folder, str(first.step)), second)
+    assert second.step == 2
+    feed = iter(second.batches())
+    resumed += [second.train_step(next(feed))["loss"].item() for _ in range(2)]
+    if rank == 0:
+        torch.save({"straight": straight, "resumed": resumed}, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,mesh,extra", [
+    (2, "mesh(fsdp=2)", []),
+    (2, "mesh(expert=2)", ["methods.moe = all_to_all", "methods.capacity = 4.0"]),
+    (2, "mesh(tensor=2)", ["a = gqa(num_heads=2, num_kv_heads=2, rope=rope())"]),
+    (2, "mesh(stage=2)", ["methods.microbatches = 2", "model = embed block^2 n head(tied=false)"]),
+    (4, "mesh(fsdp=2, tensor=2)", ["a = gqa(num_heads=2, num_kv_heads=2, rope=rope())"]),
+])
+def test_resume_on_a_sharded_mesh_matches_the_uninterrupted_run(tmp_path, world, mesh, extra):
+    out = str(tmp_path / "r.pt")
+    folder = str(tmp_path / "ckpt")
+    os.makedirs(folder)
+    mp.spawn(_resume_worker, args=(world, _free_port(), MOE, [f"mesh = {mesh}", *extra], folder, out),
+             nprocs=world, join=True)
+    got = torch.load(out)
+    assert got["resumed"][:2] == pytest.approx(got["straight"][:2], abs=1e-6)
+    assert got["resumed"][2:] == pytest.approx(got["straight"][2:], abs=1e-5)
