@@ -1,110 +1,184 @@
-"""Curricula: settings that change at a step (seq_len / batch / data / RoPE) and
-batch ramps, cut into *stretches* of constant shape.
+"""Curricula: a run whose shape changes over its steps.
 
-Behaviour follows the reference (``src/bux/train/curriculum.py:28-228``): a phase
-starts at a step or a share of the steps, phases go in order, a ramp grows the
-batch linearly in multiples, and token accounting sums batch x seq_len per stretch.
+Two things change a run's shape: *phases* (``curriculum = phase(at=..., seq_len=...,
+batch=..., data=..., rope_scaling=..., rope_base=...)``), which switch settings at a step
+or at a share of the steps, and the *batch ramp*, which grows the batch from a small start
+to the run's batch over its first steps. `Timeline` lays both on one axis of steps;
+`stretches` cuts that axis where anything changes, so that the trainer, the data feed and
+the schedules can each walk ranges of steps over which batch, sequence length and data are
+constant.
+
+What it computes matches the reference (``train/curriculum.py:28-228`` there): phase
+starts round a share of the steps to a step, a ramp's batch is linear in the step and
+rounded down to its multiple, tokens are summed stretch by stretch.
 """
 
 from __future__ import annotations
 
-import itertools
+from dataclasses import dataclass
 from typing import NamedTuple, Sequence
-
-CHANGES = ("seq_len", "batch", "data")
-ROPE = {"rope_scaling": "scaling", "rope_base": "base"}
 
 
 class Stretch(NamedTuple):
     start: int
     stop: int
-    config: object  # TrainConfig with that stretch's seq_len, batch and data
+    config: object  # the TrainConfig with that range's seq_len, batch and data
 
 
+@dataclass
+class _Switch:
+    """One phase on the timeline: its first step, the run's settings from then on and the
+    RoPE settings in force from then on."""
+
+    step: int
+    config: object
+    rope: dict
+
+
+class Timeline:
+    """A run's phases and ramp on the axis of steps."""
+
+    SHAPE_FIELDS = ("seq_len", "batch", "data")
+    ROPE_FIELDS = (("rope_scaling", "scaling"), ("rope_base", "base"))
+
+    def __init__(self, t):
+        self.t = t
+        self.ramp = t.batch_ramp
+        self.switches = [_Switch(0, t, {})]
+        for phase in t.curriculum:
+            last = self.switches[-1]
+            shape = {}
+            for field in self.SHAPE_FIELDS:
+                value = getattr(phase, field)
+                if value is not None:
+                    shape[field] = value
+            rope = dict(last.rope)
+            for field, name in self.ROPE_FIELDS:
+                value = getattr(phase, field)
+                if value is not None:
+                    rope[name] = value
+            self.switches.append(_Switch(phase.start(t.steps), last.config.model_copy(update=shape), rope))
+
+    # ---- lookups
+    def switch_at(self, step: int) -> _Switch:
+        current = self.switches[0]
+        for sw in self.switches[1:]:
+            if sw.step <= step:
+                current = sw
+        return current
+
+    def ramp_rows(self, step: int) -> int:
+        """Rows per step at `step` while the ramp runs, rounded down to its multiple."""
+        ramp, full = self.ramp, self.t.batch
+        if step >= ramp.steps:
+            return full
+        unit = ramp.multiple or ramp.start
+        linear = ramp.start + (full - ramp.start) * step // ramp.steps
+        return max(ramp.start, linear - linear % unit)
+
+    def ramp_steps(self) -> list:
+        """The steps at which the ramp's batch reaches each further multiple."""
+        ramp, full = self.ramp, self.t.batch
+        unit = ramp.multiple or ramp.start
+        out = []
+        size = (ramp.start // unit + 1) * unit
+        while size < full:
+            # the first step whose linear value is at least `size`
+            out.append(-((ramp.start - size) * ramp.steps // (full - ramp.start)))
+            size += unit
+        return out
+
+    def config_at(self, step: int):
+        config = self.switch_at(step).config
+        if self.ramp is not None and step < self.ramp.steps:
+            config = config.model_copy(update={"batch": self.ramp_rows(step)})
+        return config
+
+    def boundaries(self) -> list:
+        marks = {sw.step for sw in self.switches}
+        if self.ramp is not None:
+            marks.update(self.ramp_steps())
+            marks.add(self.ramp.steps)
+        return sorted(m for m in marks if m < self.t.steps) + [self.t.steps]
+
+    # ---- validity
+    def check_ramp(self) -> None:
+        ramp, t = self.ramp, self.t
+        if ramp is None:
+            return
+        if ramp.start >= t.batch:
+            raise ValueError(f"the batch ramp starts at {ramp.start} rows, not below the run's "
+                             f"batch of {t.batch}, which it grows to")
+        if ramp.steps > t.steps:
+            raise ValueError(f"the batch ramp takes {ramp.steps} steps, and the run has {t.steps}")
+
+    def check_phases(self) -> None:
+        t = self.t
+        for n in range(1, len(self.switches)):
+            start, before = self.switches[n].step, self.switches[n - 1].step
+            if start >= t.steps:
+                raise ValueError(f"phase {n} starts at step {start}, and the run has {t.steps}")
+            if start <= before:
+                raise ValueError(
+                    f"phase {n} starts at step {start}, not after the phase before it "
+                    f"(step {before}): phases go in the order they start")
+        if self.ramp is None:
+            return
+        for n, phase in enumerate(t.curriculum, 1):
+            start = self.switches[n].step
+            if phase.batch is not None and start < self.ramp.steps:
+                raise ValueError(
+                    f"phase {n} sets the batch at step {start}, before the batch ramp is "
+                    f"over at step {self.ramp.steps}")
+
+
+# ---- the module's functions (what the compiler, the trainer and the CLI call)
 def phases(t) -> list:
     """(first step, settings then) for the start of the run and of every phase."""
-    out = [(0, t)]
-    for ph in t.curriculum:
-        changed = {k: getattr(ph, k) for k in CHANGES if getattr(ph, k) is not None}
-        out.append((ph.start(t.steps), out[-1][1].model_copy(update=changed)))
-    return out
-
-
-def ropes(t) -> list:
-    out = [(0, {})]
-    for ph in t.curriculum:
-        changed = {f: getattr(ph, k) for k, f in ROPE.items() if getattr(ph, k) is not None}
-        out.append((ph.start(t.steps), {**out[-1][1], **changed}))
-    return out
+    return [(sw.step, sw.config) for sw in Timeline(t).switches]
 
 
 def rope_at(t, step: int) -> dict:
-    return next(r for start, r in reversed(ropes(t)) if start <= step)
+    """The RoPE settings (``scaling``, ``base``) the phases have set by `step`."""
+    return Timeline(t).switch_at(step).rope
 
 
 def ramped(ramp, batch: int, step: int) -> int:
-    """Rows per step at `step` of a linear ramp, rounded down to the multiple."""
-    if step >= ramp.steps:
-        return batch
-    grown = ramp.start + (batch - ramp.start) * step // ramp.steps
-    mult = ramp.multiple or ramp.start
-    return max(ramp.start, grown // mult * mult)
+    line = Timeline.__new__(Timeline)
+    line.ramp, line.t = ramp, _Rows(batch)
+    return line.ramp_rows(step)
 
 
-def _ramp_cuts(ramp, batch: int) -> list:
-    mult, rise = ramp.multiple or ramp.start, batch - ramp.start
-    sizes = range((ramp.start // mult + 1) * mult, batch, mult)
-    return [-(-(v - ramp.start) * ramp.steps // rise) for v in sizes]
-
-
-def check_phases(t) -> None:
-    starts = [s for s, _ in phases(t)]
-    for n, (before, start) in enumerate(itertools.pairwise(starts), 1):
-        if start >= t.steps:
-            raise ValueError(f"phase {n} starts at step {start}, and the run has {t.steps}")
-        if start <= before:
-            raise ValueError(
-                f"phase {n} starts at step {start}, not after the phase before it "
-                f"(step {before}): phases go in the order they start")
-    ramp = t.batch_ramp
-    for n, ph in enumerate(t.curriculum, 1):
-        if ramp is not None and ph.batch is not None and starts[n] < ramp.steps:
-            raise ValueError(
-                f"phase {n} sets the batch at step {starts[n]}, before the batch ramp is "
-                f"over at step {ramp.steps}")
+class _Rows:
+    def __init__(self, batch: int):
+        self.batch = batch
 
 
 def check_ramp(t) -> None:
-    ramp = t.batch_ramp
-    if ramp is None:
-        return
-    if ramp.start >= t.batch:
-        raise ValueError(f"the batch ramp starts at {ramp.start} rows, not below the run's "
-                         f"batch of {t.batch}, which it grows to")
-    if ramp.steps > t.steps:
-        raise ValueError(f"the batch ramp takes {ramp.steps} steps, and the run has {t.steps}")
+    Timeline(t).check_ramp()
+
+
+def check_phases(t) -> None:
+    Timeline(t).check_phases()
 
 
 def check(t) -> None:
-    check_ramp(t)
-    check_phases(t)
+    line = Timeline(t)
+    line.check_ramp()
+    line.check_phases()
 
 
 def stretches(t) -> tuple:
-    check(t)
-    starts = phases(t)
-    cuts = {s for s, _ in starts}
-    ramp = t.batch_ramp
-    if ramp is not None:
-        cuts.update(_ramp_cuts(ramp, t.batch), [ramp.steps])
-    bounds = [*sorted(c for c in cuts if c < t.steps), t.steps]
+    """Ranges of steps with constant batch, sequence length and data, in order."""
+    line = Timeline(t)
+    line.check_ramp()
+    line.check_phases()
+    marks = line.boundaries()
     out: list = []
-    for start, stop in itertools.pairwise(bounds):
-        config = next(c for s, c in reversed(starts) if s <= start)
-        if ramp is not None and start < ramp.steps:
-            config = config.model_copy(update={"batch": ramped(ramp, t.batch, start)})
+    for start, stop in zip(marks, marks[1:]):
+        config = line.config_at(start)
         if out and out[-1].config == config:
-            out[-1] = out[-1]._replace(stop=stop)
+            out[-1] = Stretch(out[-1].start, stop, config)
         else:
             out.append(Stretch(start, stop, config))
     return tuple(out)
@@ -115,14 +189,17 @@ def varies(t) -> bool:
 
 
 def tokens(parts: Sequence, steps: int) -> int:
-    total = 0
-    for k, s in enumerate(parts):
-        stop = steps if k == len(parts) - 1 else min(s.stop, steps)
-        total += max(0, stop - s.start) * s.config.batch * s.config.seq_len
+    """Tokens the first `steps` steps read (the last range is open-ended)."""
+    total, last = 0, len(parts) - 1
+    for k, part in enumerate(parts):
+        end = steps if k == last else min(part.stop, steps)
+        if end > part.start:
+            total += (end - part.start) * part.config.batch * part.config.seq_len
     return total
 
 
 def si(n: float) -> str:
+    """Three significant digits with an SI suffix (1.31B, 819k)."""
     for suffix, scale in (("", 1), ("k", 1e3), ("M", 1e6), ("B", 1e9)):
         shown = f"{n / scale:.3g}"
         if "e" not in shown:

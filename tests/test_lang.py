@@ -23,7 +23,7 @@ seq_len   = 64
 batch     = 8
 steps     = 50
 """
-REF = "/root/reference/examples"
+REF = os.environ.get("BUX_REFERENCE_EXAMPLES", "")  # the reference's examples folder, when there is one
 
 
 def test_golden_run_ids():
