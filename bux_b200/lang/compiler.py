@@ -30,6 +30,7 @@ from ..config import training as T
 from . import ir, modules
 from . import syntax as S
 from .syntax import BuxError, Span
+from .widths import GraphTyper
 
 LAYERS = L.LAYERS
 TRAINING = T.TRAINING
@@ -76,11 +77,6 @@ class Bare:
 @dataclass(frozen=True)
 class Macro:
     statement: S.Statement
-
-
-@dataclass(frozen=True)
-class PortValue:
-    port: str
 
 
 class Reported(BuxError):
@@ -889,296 +885,6 @@ class Evaluator:
         return self.data(self.definition(name), st.body.span), st.body.span
 
 
-# ------------------------------------------------------------------ lowering
-@dataclass(eq=False)
-class _Frame:
-    label: str
-    used: list = field(default_factory=list)
-
-
-@dataclass(eq=False)
-class _Entry:
-    value: Any
-    frames: tuple
-    owner: Optional[str] = None
-    used_in: Optional[_Frame] = None
-    popped: bool = False
-
-
-_ON_COPIES = (L.EngramConfig, L.NextNConfig, L.DocCopyConfig)
-
-
-class Lowering:
-    """Types the graph: every layer gets its input width; taps, ports, shared blocks
-    and the residual algebra's widened stream are checked on the way."""
-
-    def __init__(self, ev: Evaluator, d_model: int, residual):
-        self.ev, self.d_model = ev, d_model
-        self.widened = residual is not None and residual.type != "vpgate"
-        self.copies = residual is not None and residual.type in ("hc", "mhc", "gr")
-        self.depth = 0
-        self.stacks: dict = {}
-        self.frames: list = []
-        self.shared: dict = {}
-        self.spans: list = []
-        self.embeddings = 0
-        self.borrowers: list = []
-        self.heads = 0
-
-    def error(self, message: str, hint: Optional[str] = None) -> BuxError:
-        return BuxError(message, self.spans[-1] if self.spans else None, hint)
-
-    @contextmanager
-    def frame(self, label: str):
-        fr = _Frame(label)
-        self.frames.append(fr)
-        try:
-            yield
-        finally:
-            self.frames.pop()
-            for entry in fr.used:
-                if entry.used_in is fr and not entry.popped:
-                    entry.owner = label
-
-    def lower_model(self, graph):
-        first = next(ir.unrolled_layers(graph), None)
-        width: Any = ("tokens" if first is not None and first.config.type == "embed"
-                      else ("streams" if self.widened else self.d_model))
-        typed, _ = self.lower(graph, width)
-        if self.borrowers and self.embeddings != 1:
-            what, span = self.borrowers[0]
-            raise BuxError(f"{what} needs exactly one embedding, found {self.embeddings}", span)
-        return typed
-
-    def lower(self, node, width):
-        span = self.ev.node_spans.get(id(node))
-        if span is not None:
-            self.spans.append(span)
-        try:
-            if node.label is not None and not isinstance(node, ir.Layer):
-                with self.frame(node.label):
-                    typed, out = self._lower(node, width)
-            else:
-                typed, out = self._lower(node, width)
-            if span is not None:
-                self.ev.node(typed, span)
-            if node.share is not None:
-                shared = typed
-                if isinstance(node, ir.Layer) and isinstance(typed, ir.Seq):
-                    shared = typed.items[-1]
-                self.check_shared(node.share, shared)
-            return typed, out
-        finally:
-            if span is not None:
-                self.spans.pop()
-
-    def check_shared(self, share: str, typed) -> None:
-        outside = self.depth == 0
-        first, first_outside = self.shared.setdefault(share, (typed, outside))
-        if ir.strip(first, widths=False) != ir.strip(typed, widths=False):
-            if (isinstance(first, ir.Layer) and isinstance(typed, ir.Layer)
-                    and first.ports != typed.ports):
-                raise self.error(f"shared '{share}' is one module, so every use of it takes "
-                                 "the same ports")
-            raise self.error(f"shared '{share}' is used where it would need different widths")
-        if outside != first_outside and any(isinstance(n, ir.Residual) for n in ir.walk(typed)):
-            raise self.error(
-                f"shared '{share}' has residual branches and is used both outside residual "
-                "branches and inside one, where its branches are built another way",
-                "define a separate block for the uses inside branches")
-
-    def _lower(self, node, width):
-        if isinstance(node, ir.Layer):
-            return self.layer(node, width)
-        if isinstance(node, ir.Seq):
-            typed = []
-            for item in node.items:
-                t, out = self.lower(item, width)
-                typed.append(t)
-                width = out
-            return ir.with_children(node, flatten(typed, ir.Seq, "items")), width
-        if isinstance(node, ir.Residual):
-            return self.residual(node, width)
-        if isinstance(node, (ir.Sum, ir.Prod)):
-            typed, outs = [], []
-            for term in ir.children(node):
-                t, out = self.lower(term, width)
-                typed.append(t)
-                if out is not None and out not in outs:
-                    outs.append(out)
-            if not outs:
-                raise self.error("parallel branches need at least one layer")
-            if len(outs) > 1:
-                raise self.error("parallel branches disagree on width: "
-                                 f"{', '.join(map(str, outs))}")
-            return ir.with_children(node, tuple(typed)), outs[0]
-        if isinstance(node, ir.Neg):
-            t, out = self.lower(node.body, width)
-            return ir.with_children(node, (t,)), out
-        if isinstance(node, ir.Const):
-            return node, None
-        if isinstance(node, ir.Identity):
-            return node, width
-        if isinstance(node, ir.Repeat):
-            return self.repeat(node, width)
-        if isinstance(node, ir.Tap):
-            self.write(node.name, width)
-            return node, width
-        if isinstance(node, ir.Ref):
-            return node, self.read_hidden(node.name, node.pop)
-        raise AssertionError(node)
-
-    def residual(self, node, width):
-        body = node.body
-        if isinstance(body, ir.Layer) and isinstance(body.config, L.EngramConfig):
-            raise self.error("engram adds to the stream itself, so [engram] would add the "
-                             "stream twice", "write it bare: ... engram ...")
-        inner = width
-        if self.widened and self.depth == 0:
-            if width != "streams":
-                extra = ", engram and nextn" if self.copies else ""
-                raise self.error(
-                    "a residual branch needs the widened residual stream, but it was read "
-                    "back into one before this",
-                    f"only branches, taps{extra} keep it; save it with @h and go on from $h")
-            inner = self.d_model
-        elif not isinstance(width, int):
-            raise self.error(f"a residual branch needs hidden states, but receives {width}")
-        self.depth += 1
-        try:
-            typed, out = self.lower(body, inner)
-        finally:
-            self.depth -= 1
-        if out != inner:
-            raise self.error("a residual branch must keep the width, but this one maps "
-                             f"{inner} to {out}")
-        return ir.with_children(node, (typed,)), width
-
-    def repeat(self, node, width):
-        span = self.ev.node_spans.get(id(node.body))
-        text = self.ev.text(span) if span is not None else "the block"
-        label = f"one pass of {f'({text})' if ' ' in text else text}^{node.times}"
-        with self.frame(label):
-            typed, out = self.lower(node.body, width)
-        if out != width:
-            raise self.error("a repeated block must keep the width, but this one maps "
-                             f"{width} to {out}")
-        # Later passes only matter for the tap stacks; skip the walk when none is used.
-        if any(isinstance(n, (ir.Tap, ir.Ref)) or (isinstance(n, ir.Layer) and n.ports)
-               for n in ir.walk(node.body)):
-            for _ in range(node.times - 1):
-                with self.frame(label):
-                    self.lower(node.body, width)
-        else:
-            for n in ir.walk(node.body):
-                if isinstance(n, ir.Layer):
-                    extra = node.times - 1
-                    if n.config.type == "embed":
-                        self.embeddings += extra
-                    elif n.config.type == "head":
-                        self.heads += extra
-        return ir.with_children(node, (typed,)), width
-
-    def write(self, tap: str, value) -> None:
-        self.stacks.setdefault(tap, []).append(_Entry(value, tuple(self.frames)))
-
-    def read_hidden(self, tap: str, pop: bool):
-        value = self.read(tap, pop)
-        if isinstance(value, PortValue):
-            raise self.error(f"tap '{tap}' holds the '{value.port}' port of a layer",
-                             f"read it through the same port: layer({value.port}=${tap})")
-        if value == "streams" and self.depth > 0:
-            raise self.error(f"tap '{tap}' holds the widened residual stream, which only "
-                             "exists outside residual branches",
-                             f"read it back into one first: merge @{tap}")
-        return value
-
-    def read(self, tap: str, pop: bool):
-        stack = self.stacks.get(tap)
-        if stack is None:
-            raise self.error(f"tap '{tap}' is read before anything writes it",
-                             f"write it first with @{tap}")
-        if not stack:
-            raise self.error(f"tap '{tap}' is empty: everything written to it was already "
-                             "popped")
-        entry = stack[-1]
-        if entry.owner is not None and any(o.owner is None for o in stack[:-1]):
-            raise self.error(
-                f"tap '{tap}' here reads the value that '{entry.owner}' wrote and read for "
-                "itself, not the one written before it",
-                f"pop it in '{entry.owner}' with ${tap}! where it is read last, or give one "
-                "of the two taps another name")
-        if entry.owner is None:
-            common = None
-            for written, current in zip(entry.frames, self.frames):
-                if written is not current:
-                    break
-                common = written
-            if common is not None:
-                entry.used_in = common
-                common.used.append(entry)
-        if pop:
-            stack.pop()
-            entry.popped = True
-        return entry.value
-
-    def layer(self, node: ir.Layer, width):
-        config = node.config
-        if width == "logits":
-            raise self.error("nothing can follow the LM head",
-                             "to go on after a head, read a tap: @h norm head $h ...")
-        on_streams = isinstance(config, (L.MergeConfig, L.ValueEmbeddingConfig)) or (
-            self.copies and isinstance(config, _ON_COPIES))
-        if width == "streams" and not on_streams:
-            merge = ir.Layer(config=L.MergeConfig(), width="streams")
-            typed, out = self.layer(node, self.d_model)
-            span = self.ev.node_spans.get(id(node))
-            if span is not None:
-                self.ev.node(typed, span)
-            return ir.Seq(items=(merge, typed)), out
-        out = self.layer_output(config, width)
-        for port in sorted(node.ports, key=lambda p: p.mode == "write"):
-            if port.mode == "write":
-                self.write(port.tap, PortValue(port.name))
-                continue
-            value = self.read(port.tap, port.mode == "pop")
-            if not isinstance(value, PortValue) or value.port != port.name:
-                held = (f"the '{value.port}' port" if isinstance(value, PortValue)
-                        else "hidden states")
-                raise self.error(f"port '{port.name}' reads tap '{port.tap}', which holds {held}")
-        return node.model_copy(update={"width": width}), out
-
-    def layer_output(self, config, width):
-        if isinstance(config, L.MergeConfig):
-            if width != "streams":
-                raise self.error(
-                    "merge reads a widened residual stream back into one, but there is none "
-                    "here",
-                    None if self.widened else
-                    "widen it with residual = hc(...), mhc(...), gr(...), attnres(...) or msar(...)")
-            return self.d_model
-        if config.type == "embed":
-            if width != "tokens":
-                raise self.error("an embedding takes token ids, so it must come first")
-            self.embeddings += 1
-            return "streams" if self.widened and self.depth == 0 else self.d_model
-        if width == "tokens":
-            raise self.error(f"{config.type} needs hidden states, but receives token ids",
-                             "start with an embedding")
-        if isinstance(config, L.LMHeadConfig):
-            self.heads += 1
-            if config.tied and self.spans:
-                self.borrowers.append(("a tied head", self.spans[-1]))
-            return "logits"
-        if isinstance(config, L.LinearConfig):
-            return config.features
-        if isinstance(config, L.NextNConfig):
-            if self.spans:
-                self.borrowers.append(("nextn", self.spans[-1]))
-            return "streams" if self.widened and self.depth == 0 else width
-        return width
-
-
 # ------------------------------------------------------------------ compile
 _SETTING_KINDS = {
     "residual": (tuple(RESIDUALS.values()), " or ".join(f"{t}(...)" for t in RESIDUALS)),
@@ -1210,9 +916,9 @@ def _architecture(ev: Evaluator, entry: str) -> ir.Architecture:
         if ev.incomplete:
             raise Reported()
         raise BuxError("'d_model' is not defined", hint="d_model = 4096")
-    low = Lowering(ev, settings["d_model"], settings["residual"])
+    low = GraphTyper(ev, settings["d_model"], settings["residual"])
     model = ev.graph(ev.definition(entry), ev.statements[entry].name_span)
-    graph = low.lower_model(model)
+    graph = low.run(model)
     if settings["vocab_size"] is None and (low.embeddings or low.heads):
         if ev.incomplete:
             raise Reported()
