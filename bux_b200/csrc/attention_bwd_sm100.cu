@@ -63,6 +63,7 @@ struct AttnBwdParams {
   alignas(64) CUtensorMap tmap_v;
   alignas(64) CUtensorMap tmap_dq;
   const float* lse; const float* delta;
+  const int* row_lo; const int* key_hi;  // documents: see AttnArgs
   float* dq; void* dk; void* dv; Status* status;
   int B, T, S, H, G;
   float scale, scale_log2; int causal, window;
@@ -109,6 +110,8 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
   int i_lo = 0, i_hi = n_qt;
   if (p.causal) i_lo = max(0, (kv0 - shift) / BT);
   if (p.window > 0) i_hi = min(n_qt, (kv0 + BT - 1 - shift + p.window - 1) / BT + 1);
+  // documents: no query past the end of the tile's last key's document sees the tile
+  if (p.key_hi != nullptr) i_hi = min(i_hi, p.key_hi[(size_t)b * p.S + min(kv0 + BT - 1, p.S - 1)] / BT + 1);
   const int per_head = max(0, i_hi - i_lo);
   const int hpg = p.H / p.G;
   const int n_steps = per_head * hpg;
@@ -213,7 +216,8 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
       const float lse2 = row_ok ? p.lse[stat] * LOG2E_B : 0.f;
       const float dlt = row_ok ? p.delta[stat] : 0.f;
       const int hi_key = p.causal ? q + shift : p.S - 1;
-      const int lo_key = p.window > 0 ? q + shift - p.window + 1 : 0;
+      int lo_key = p.window > 0 ? q + shift - p.window + 1 : 0;
+      if (p.row_lo != nullptr && row_ok) lo_key = max(lo_key, p.row_lo[(size_t)b * p.T + q]);
       ok = warp_all(mbar_wait(sdp_full, s & 1, abort_flag, st, KID_ATTN_BWD, 6));
       if (!ok) break;
       tc_fence_after();
@@ -362,6 +366,7 @@ static const char* attn_bwd_launch_d(const AttnArgs& a, cudaStream_t stream) {
   if ((err = make_tmap_2d(&p.tmap_k, a.k, 2, (uint64_t)a.B * a.S, kw, kw * 2, 64, BT))) return err;
   if ((err = make_tmap_2d(&p.tmap_v, a.v, 2, (uint64_t)a.B * a.S, kw, kw * 2, 64, BT))) return err;
   if ((err = make_tmap_2d(&p.tmap_dq, a.dq, 4, (uint64_t)a.B * a.T, qw, qw * 4, 32, 32))) return err;
+  p.row_lo = a.row_lo; p.key_hi = a.key_hi;
   p.lse = a.lse; p.delta = a.delta; p.dq = reinterpret_cast<float*>(a.dq); p.dk = a.dk; p.dv = a.dv;
   p.status = a.status;
   p.B = a.B; p.T = a.T; p.S = a.S; p.H = a.H; p.G = a.G;

@@ -35,6 +35,7 @@ struct AttnFwdParams {
   alignas(64) CUtensorMap tmap_kv_k;
   alignas(64) CUtensorMap tmap_kv_v;
   void* o; float* lse; const float* sinks; Status* status;
+  const int* row_lo;  // [B, T] first visible key of each query (documents), or null
   int B, T, S, H, G;
   float scale_log2; int causal, window;
 };
@@ -93,6 +94,8 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
     hi[x] = s_tiles;
     if (p.causal) hi[x] = min(hi[x], (qx + QT - 1 + shift) / KT + 1);
     lo[x] = p.window > 0 ? max(0, (qx + shift - p.window + 1) / KT) : 0;
+    // documents: the tile's first query has the earliest document start of the tile
+    if (p.row_lo != nullptr && qx < p.T) lo[x] = max(lo[x], p.row_lo[(size_t)b * p.T + qx] / KT);
     if (qx >= p.T || hi[x] <= lo[x]) { lo[x] = 0; hi[x] = 0; }
   }
   const bool any0 = hi[0] > lo[0], any1 = hi[1] > lo[1];
@@ -200,7 +203,8 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
     const int hi_key = p.causal ? q + shift : p.S - 1;
-    const int lo_key = p.window > 0 ? q + shift - p.window + 1 : 0;
+    int lo_key = p.window > 0 ? q + shift - p.window + 1 : 0;
+    if (p.row_lo != nullptr && q < p.T) lo_key = max(lo_key, p.row_lo[(size_t)b * p.T + q]);
     int done = 0;
     for (int j = lo[x]; j < hi[x] && ok; ++j, ++done) {
       const int kv0 = j * KT;
@@ -361,6 +365,7 @@ static const char* attn_fwd_launch_d(const AttnArgs& a, cudaStream_t stream) {
   if ((err = make_tmap_2d(&p.tmap_kv_k, a.k, 2, (uint64_t)a.B * a.S, (uint64_t)a.G * D, (uint64_t)a.G * D * 2, 64, KT))) return err;
   if ((err = make_tmap_2d(&p.tmap_kv_v, a.v, 2, (uint64_t)a.B * a.S, (uint64_t)a.G * D, (uint64_t)a.G * D * 2, 64, KT))) return err;
   p.o = a.o; p.lse = a.lse; p.sinks = a.sinks; p.status = a.status;
+  p.row_lo = a.row_lo;
   p.B = a.B; p.T = a.T; p.S = a.S; p.H = a.H; p.G = a.G;
   p.scale_log2 = a.scale * LOG2E; p.causal = a.causal ? 1 : 0; p.window = a.window;
   auto kern = attn_fwd_kernel<D>;

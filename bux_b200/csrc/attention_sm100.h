@@ -11,12 +11,17 @@ struct Status;
 // lse, delta: [B, H, T] fp32.  sinks / dsinks: [H] fp32 or null.  D is 64 or 128.
 // Causal alignment is bottom-right (query t sees keys <= t + S - T); window > 0 keeps
 // keys in (t + S - T - window, t + S - T].
+// Documents packed into a row (self-attention, T == S): row_lo[b, t] is the first key that
+// query t may see (the start of its document) and key_hi[b, s] the last query that may see
+// key s (the end of its document); both int32, both non-decreasing along a row, or null.
+// The forward and the mask use row_lo; key_hi only bounds the backward's walk over query tiles.
 struct AttnArgs {
   const void* q = nullptr; const void* k = nullptr; const void* v = nullptr;
   void* o = nullptr; float* lse = nullptr;
   const void* d_o = nullptr; void* dq = nullptr; void* dk = nullptr; void* dv = nullptr;
   float* delta = nullptr;
   const float* sinks = nullptr; float* dsinks = nullptr;
+  const int* row_lo = nullptr; const int* key_hi = nullptr;
   int B = 0, T = 0, S = 0, H = 0, G = 0, D = 0;
   float scale = 1.f; bool causal = true; int window = 0;
   Status* status = nullptr;

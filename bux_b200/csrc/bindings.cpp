@@ -232,9 +232,16 @@ void combine_rows(const Tensor& y, const Tensor& pos, const c10::optional<Tensor
 }
 
 // ------------------------------------------------------------------ attention
+const int* doc_bounds(const c10::optional<Tensor>& t, int64_t numel, const char* name) {
+  if (!t.has_value()) return nullptr;
+  TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kInt && t->is_contiguous() && t->numel() == numel,
+              "bux attention: ", name, " is a contiguous int32 tensor with one entry per position");
+  return t->data_ptr<int>();
+}
+
 void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& o, Tensor& lse,
               const c10::optional<Tensor>& sinks, const c10::optional<Tensor>& status,
-              double scale, bool causal, int64_t window) {
+              double scale, bool causal, int64_t window, const c10::optional<Tensor>& row_lo) {
   check_cuda(q, "q"); check_cuda(k, "k"); check_cuda(v, "v"); check_cuda(o, "o");
   c10::cuda::CUDAGuard guard(q.device());
   bux::AttnArgs a;
@@ -244,13 +251,16 @@ void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& o, Tens
   a.S = (int)k.size(1); a.G = (int)k.size(2);
   a.scale = (float)scale; a.causal = causal; a.window = (int)window;
   a.status = status_ptr(status);
+  a.row_lo = doc_bounds(row_lo, q.size(0) * q.size(1), "row_lo");
+  TORCH_CHECK(a.row_lo == nullptr || (causal && a.T == a.S), "bux attention: documents need causal self-attention");
   const char* err = bux::attn_fwd_launch(a, stream_of(q));
   TORCH_CHECK(err == nullptr, "bux attention: ", err);
 }
 void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& d_o,
               const Tensor& lse, Tensor& dq, Tensor& dk, Tensor& dv, Tensor& delta,
               const c10::optional<Tensor>& sinks, const c10::optional<Tensor>& dsinks,
-              const c10::optional<Tensor>& status, double scale, bool causal, int64_t window) {
+              const c10::optional<Tensor>& status, double scale, bool causal, int64_t window,
+              const c10::optional<Tensor>& row_lo, const c10::optional<Tensor>& key_hi) {
   check_cuda(q, "q"); check_cuda(d_o, "do");
   c10::cuda::CUDAGuard guard(q.device());
   bux::AttnArgs a;
@@ -262,6 +272,10 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
   a.S = (int)k.size(1); a.G = (int)k.size(2);
   a.scale = (float)scale; a.causal = causal; a.window = (int)window;
   a.status = status_ptr(status);
+  a.row_lo = doc_bounds(row_lo, q.size(0) * q.size(1), "row_lo");
+  a.key_hi = doc_bounds(key_hi, k.size(0) * k.size(1), "key_hi");
+  TORCH_CHECK((a.row_lo == nullptr) == (a.key_hi == nullptr), "bux attention backward: row_lo and key_hi go together");
+  TORCH_CHECK(a.row_lo == nullptr || (causal && a.T == a.S), "bux attention: documents need causal self-attention");
   const char* err = bux::attn_bwd_launch(a, stream_of(q));
   TORCH_CHECK(err == nullptr, "bux attention backward: ", err);
 }
@@ -374,6 +388,6 @@ TORCH_LIBRARY(bux_b200, m) {
   m.def("gather_rows(Tensor x, Tensor index, Tensor(a!) out) -> ()", &gather_rows);
   m.def("combine_bwd(Tensor? y, Tensor dout, Tensor pos, Tensor? w, Tensor(a!)? dy, Tensor(b!)? dw) -> ()", &combine_bwd);
   m.def("combine_rows(Tensor y, Tensor pos, Tensor? w, Tensor(a!) out) -> ()", &combine_rows);
-  m.def("attn_fwd(Tensor q, Tensor k, Tensor v, Tensor(a!) o, Tensor(b!) lse, Tensor? sinks, Tensor? status, float scale, bool causal, int window) -> ()", &attn_fwd);
-  m.def("attn_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor d_o, Tensor lse, Tensor(a!) dq, Tensor(b!) dk, Tensor(c!) dv, Tensor(d!) delta, Tensor? sinks, Tensor? dsinks, Tensor? status, float scale, bool causal, int window) -> ()", &attn_bwd);
+  m.def("attn_fwd(Tensor q, Tensor k, Tensor v, Tensor(a!) o, Tensor(b!) lse, Tensor? sinks, Tensor? status, float scale, bool causal, int window, Tensor? row_lo) -> ()", &attn_fwd);
+  m.def("attn_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor d_o, Tensor lse, Tensor(a!) dq, Tensor(b!) dk, Tensor(c!) dv, Tensor(d!) delta, Tensor? sinks, Tensor? dsinks, Tensor? status, float scale, bool causal, int window, Tensor? row_lo, Tensor? key_hi) -> ()", &attn_bwd);
 }

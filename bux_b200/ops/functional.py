@@ -306,39 +306,42 @@ attention_replay = None
 
 class _Attention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, sinks, causal, window, scale):
+    def forward(ctx, q, k, v, sinks, causal, window, scale, segments):
         K = _K()
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         sk = None if sinks is None else sinks.float().contiguous()
+        # documents packed into a row: per-query first key and per-key last query
+        row_lo, key_hi = K.document_bounds(segments) if segments is not None else (None, None)
         mode = attention_replay
         if mode is not None and mode[0] == "load":
             o, lse = next(mode[1])
         else:
-            o, lse = K.attn_fwd(q, k, v, causal=causal, window=window, sinks=sk, scale=scale)
+            o, lse = K.attn_fwd(q, k, v, causal=causal, window=window, sinks=sk, scale=scale, row_lo=row_lo)
             if mode is not None:
                 mode[1].append((o, lse))
-        ctx.save_for_backward(q, k, v, o, lse, sk)
+        ctx.save_for_backward(q, k, v, o, lse, sk, row_lo, key_hi)
         ctx.cfg = (causal, window, scale)
         return o
 
     @staticmethod
     def backward(ctx, do):
         K = _K()
-        q, k, v, o, lse, sk = ctx.saved_tensors
+        q, k, v, o, lse, sk, row_lo, key_hi = ctx.saved_tensors
         causal, window, scale = ctx.cfg
         dq, dk, dv, dsk = K.attn_bwd(q, k, v, o, do.contiguous(), lse, causal=causal, window=window,
-                                     sinks=sk, scale=scale)
-        return dq.to(q.dtype), dk, dv, dsk, None, None, None
+                                     sinks=sk, scale=scale, row_lo=row_lo, key_hi=key_hi)
+        return dq.to(q.dtype), dk, dv, dsk, None, None, None, None
 
 
 def attention(q, k, v, *, causal: bool = True, window: Optional[int] = None, sinks=None,
               softcap: Optional[float] = None, scale: Optional[float] = None, segments=None):
     """[B,T,H,D] x [B,S,G,D] softmax attention; returns [B,T,H,D]."""
     d = q.shape[-1]
+    packed = segments is not None
     native = (kernels_on(q) and d in (64, 128) and v.shape[-1] == d and softcap is None
-              and segments is None)
+              and (not packed or (causal and q.shape[1] == k.shape[1])))
     if native:
-        return _Attention.apply(q, k, v, sinks, causal, int(window or 0), scale)
+        return _Attention.apply(q, k, v, sinks, causal, int(window or 0), scale, segments)
     if (q.is_cuda and softcap is None and segments is None and sinks is None and window is None
             and q.dtype in (torch.bfloat16, torch.float16)):
         # library baseline (BUX_KERNELS=off, or a head dim the kernel does not take)

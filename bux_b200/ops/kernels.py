@@ -356,17 +356,26 @@ def combine_rows_into(y, pos, w, out) -> None:
 
 
 # ------------------------------------------------------------------ attention
-def attn_fwd(q, k, v, *, causal=True, window=0, sinks=None, scale=None):
+def document_bounds(segments: torch.Tensor):
+    """(row_lo, key_hi) int32 [B, T] of packed rows from their document ids (non-decreasing
+    along a row): the first position of each position's document, and its last."""
+    seg = segments.contiguous()
+    row_lo = torch.searchsorted(seg, seg, right=False).to(torch.int32)
+    key_hi = (torch.searchsorted(seg, seg, right=True) - 1).to(torch.int32)
+    return row_lo.contiguous(), key_hi.contiguous()
+
+
+def attn_fwd(q, k, v, *, causal=True, window=0, sinks=None, scale=None, row_lo=None):
     b, t, h, d = q.shape
     o = torch.empty_like(q)
     lse = torch.empty(b, h, t, dtype=torch.float32, device=q.device)
     ops().attn_fwd(q, k, v, o, lse, sinks, status_word(q.device), scale if scale is not None else d ** -0.5,
-                   causal, window or 0)
+                   causal, window or 0, row_lo)
     _count()
     return o, lse
 
 
-def attn_bwd(q, k, v, o, do, lse, *, causal=True, window=0, sinks=None, scale=None):
+def attn_bwd(q, k, v, o, do, lse, *, causal=True, window=0, sinks=None, scale=None, row_lo=None, key_hi=None):
     b, t, h, d = q.shape
     dq = torch.zeros(b, t, h, d, dtype=torch.float32, device=q.device)
     dk = torch.empty_like(k)
@@ -374,7 +383,7 @@ def attn_bwd(q, k, v, o, do, lse, *, causal=True, window=0, sinks=None, scale=No
     delta = torch.empty(b, h, t, dtype=torch.float32, device=q.device)
     dsinks = torch.zeros_like(sinks) if sinks is not None else None
     ops().attn_bwd(q, k, v, o, do, lse, dq, dk, dv, delta, sinks, dsinks, status_word(q.device),
-                   scale if scale is not None else d ** -0.5, causal, window or 0)
+                   scale if scale is not None else d ** -0.5, causal, window or 0, row_lo, key_hi)
     _count(2)
     return dq, dk, dv, dsinks
 

@@ -263,6 +263,68 @@ def test_attention_bwd(cuda, d, h, g, t, window, sinks):
         assert rel_err(dsk, sk.grad) < 3e-2
 
 
+def _documents(t: int, lens, device):
+    """Document ids [1, t] of a row packed with documents of the given lengths."""
+    assert sum(lens) == t
+    ids = torch.cat([torch.full((n,), i + 1) for i, n in enumerate(lens)])
+    return ids[None].to(device)
+
+
+@pytest.mark.parametrize("t,h,g,lens,window,sinks", [
+    (4096, 8, 1, None, 0, False),                                             # the benchmark's shape: 8 heads per group
+    (4096, 8, 1, [700, 130, 1, 255, 1000, 58, 512, 384, 999, 57], 0, False),  # ten documents, odd boundaries
+    (1024, 4, 2, [300, 212, 128, 384], 256, True),                            # documents + window + sinks
+    (2048, 4, 2, None, 512, False),                                           # a window far from the diagonal's tile
+])
+def test_attention_long_rows_documents(cuda, t, h, g, lens, window, sinks):
+    """Forward and backward at the lengths the benchmark runs, with packed documents
+    (every query sees only its own document), against the fp32 statement."""
+    from bux_b200.ops import kernels as K
+
+    torch.manual_seed(13)
+    d = 128
+    q = torch.randn(1, t, h, d, device=cuda).bfloat16().requires_grad_()
+    k = torch.randn(1, t, g, d, device=cuda).bfloat16().requires_grad_()
+    v = torch.randn(1, t, g, d, device=cuda).bfloat16().requires_grad_()
+    sk = torch.randn(h, device=cuda).requires_grad_() if sinks else None
+    seg = _documents(t, lens, cuda) if lens else None
+    want, want_lse = ref.attention(q, k, v, causal=True, window=window or None, sinks=sk, segments=seg)
+    do = torch.randn_like(q)
+    want.backward(do)
+    row_lo, key_hi = K.document_bounds(seg) if seg is not None else (None, None)
+    if seg is not None:
+        assert row_lo[0, 0] == 0 and key_hi[0, 0] == lens[0] - 1 and row_lo[0, -1] == t - lens[-1]
+    with torch.no_grad():
+        o, lse = K.attn_fwd(q, k, v, causal=True, window=window, sinks=sk, row_lo=row_lo)
+        dq, dk, dv, dsk = K.attn_bwd(q, k, v, o, do, lse, causal=True, window=window, sinks=sk,
+                                     row_lo=row_lo, key_hi=key_hi)
+    assert rel_err(o, want) < 2e-2
+    assert rel_err(lse, want_lse) < 1e-3
+    assert rel_err(dv, v.grad) < 3e-2
+    assert rel_err(dk, k.grad) < 3e-2
+    assert rel_err(dq, q.grad) < 3e-2
+    if sinks:
+        assert rel_err(dsk, sk.grad) < 3e-2
+
+
+def test_attention_layer_takes_the_kernels_for_packed_rows(cuda):
+    """`functional.attention` with segments runs the kernels (not the quadratic statement)."""
+    from bux_b200.ops import functional as OF
+    from bux_b200.ops import kernels as K
+
+    torch.manual_seed(14)
+    q = torch.randn(2, 512, 4, 64, device=cuda).bfloat16().requires_grad_()
+    k = torch.randn(2, 512, 2, 64, device=cuda).bfloat16().requires_grad_()
+    v = torch.randn(2, 512, 2, 64, device=cuda).bfloat16().requires_grad_()
+    seg = torch.cat([_documents(512, [100, 156, 256], cuda), _documents(512, [512], cuda)])
+    before = K.launches
+    out = OF.attention(q, k, v, causal=True, segments=seg)
+    out.backward(torch.ones_like(out))
+    assert K.launches - before == 3  # forward, delta, backward
+    want, _ = ref.attention(q.detach(), k.detach(), v.detach(), causal=True, segments=seg)
+    assert rel_err(out, want) < 2e-2
+
+
 @pytest.mark.parametrize("kind,limit,up_offset", [("swish", 0.0, 0.0), ("quick_gelu", 7.0, 1.0)])
 def test_quantiser_that_computes_the_gated_activation_matches_two_passes(kind, limit, up_offset):
     """glu (and its gradient) computed inside the MXFP8 quantiser gives the bytes that the
