@@ -295,6 +295,28 @@ void ep_push_rows(const Tensor& x, const Tensor& src_token, const Tensor& dst_ra
                     opt_f32(row_scale), u64_ptr(peer_base), peer_scale.has_value() ? u64_ptr(*peer_scale) : nullptr,
                     dst_row.numel(), (int)x.size(-1), (int)sms, stream_of(x));
 }
+void ep_push_rows_mx(const Tensor& x, const Tensor& src_token, const Tensor& dst_rank, const Tensor& dst_row,
+                     const c10::optional<Tensor>& row_scale, const Tensor& peer_q, const Tensor& peer_sf,
+                     const c10::optional<Tensor>& peer_scale, int64_t sms) {
+  check_cuda(x, "x");
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.is_contiguous() && x.size(-1) % 128 == 0,
+              "ep_push_rows_mx: contiguous bf16 rows of a multiple of 128 columns");
+  c10::cuda::CUDAGuard guard(x.device());
+  bux::ep_push_rows_mx(x.data_ptr(), src_token.data_ptr<int>(), dst_rank.data_ptr<int>(), dst_row.data_ptr<int>(),
+                       opt_f32(row_scale), u64_ptr(peer_q), u64_ptr(peer_sf),
+                       peer_scale.has_value() ? u64_ptr(*peer_scale) : nullptr, dst_row.numel(), (int)x.size(-1),
+                       (int)sms, stream_of(x));
+}
+void requant_mxfp8_cols(const Tensor& q, const Tensor& sf, Tensor& q_col, Tensor& sf_col, int64_t rows, int64_t cols,
+                        int64_t ld_col) {
+  check_cuda(q, "q"); check_cuda(sf, "sf");
+  TORCH_CHECK(q.is_contiguous() && q.element_size() == 1 && q.numel() >= rows * cols && cols % 32 == 0 && ld_col % 32 == 0,
+              "requant_mxfp8_cols: contiguous e4m3 bytes [rows, cols], cols and the padded row count multiples of 32");
+  c10::cuda::CUDAGuard guard(q.device());
+  bux::requant_mxfp8_cols(reinterpret_cast<const uint8_t*>(q.data_ptr()), reinterpret_cast<const uint8_t*>(sf.data_ptr()),
+                          reinterpret_cast<uint8_t*>(q_col.data_ptr()), reinterpret_cast<uint8_t*>(sf_col.data_ptr()),
+                          rows, (int)cols, ld_col, stream_of(q));
+}
 void row_dots(const Tensor& a, const Tensor& b, Tensor& out) {
   check_cuda(a, "a"); check_cuda(b, "b");
   TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && a.is_contiguous() && b.is_contiguous() &&
@@ -364,6 +386,8 @@ void ep_wait(const Tensor& flags, int64_t epoch, const c10::optional<Tensor>& st
 
 TORCH_LIBRARY(bux_b200, m) {
   m.def("ep_push_rows(Tensor x, Tensor src_token, Tensor dst_rank, Tensor dst_row, Tensor? row_scale, Tensor peer_base, int sms, Tensor? peer_scale=None) -> ()", &ep_push_rows);
+  m.def("ep_push_rows_mx(Tensor x, Tensor src_token, Tensor dst_rank, Tensor dst_row, Tensor? row_scale, Tensor peer_q, Tensor peer_sf, Tensor? peer_scale, int sms) -> ()", &ep_push_rows_mx);
+  m.def("requant_mxfp8_cols(Tensor q, Tensor sf, Tensor(a!) q_col, Tensor(b!) sf_col, int rows, int cols, int ld_col) -> ()", &requant_mxfp8_cols);
   m.def("row_dots(Tensor a, Tensor b, Tensor(a!) out) -> ()", &row_dots);
   m.def("ep_pull_scalar(Tensor peer_base, Tensor rank_of, Tensor row_of, Tensor(a!) out, Tensor? flags, int epoch, Tensor? status, float limit_s) -> ()", &ep_pull_scalar);
   m.def("ep_signal(Tensor peer_flags, int channel, int world, int my_rank, int epoch) -> ()", &ep_signal);

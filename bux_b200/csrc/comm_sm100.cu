@@ -79,6 +79,69 @@ __global__ void ep_push_rows_kernel(const __nv_bfloat16* __restrict__ x, const i
   }
 }
 
+// The same push with the rows quantised on the way: each row leaves as d e4m3 bytes plus d/32
+// E8M0 scales (MXFP8 along the row), written straight into the owner's GEMM operand: the bytes
+// into its [cap, d] buffer, the scales into its scale tiles (512-byte tiles of 128 rows x 4
+// scales, the layout tcgen05.cp takes). Half the bytes of a bf16 push cross NVLink, and the
+// owner's first GEMM reads what arrived without a quantiser pass in between.
+// One warp per pick; a warp iteration covers 512 columns (16 bytes per lane, so every store
+// instruction writes 512 contiguous bytes); two neighbouring lanes share a block of 32.
+__global__ void ep_push_rows_mx_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ src_token,
+                                       const int* __restrict__ dst_rank, const int* __restrict__ dst_row,
+                                       const float* __restrict__ row_scale, const uint64_t* __restrict__ peer_q,
+                                       const uint64_t* __restrict__ peer_sf, const uint64_t* __restrict__ peer_scale,
+                                       long picks, int d) {
+  const int lane = threadIdx.x & 31;
+  const int sf_cols = ((d / 32) + 3) & ~3;
+  for (long i = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < picks;
+       i += (long)gridDim.x * (blockDim.x >> 5)) {
+    const int row = dst_row[i];
+    if (row < 0) continue;
+    const int rank = dst_rank[i];
+    const __nv_bfloat16* src = x + (long)src_token[i] * d;
+    uint8_t* q_dst = reinterpret_cast<uint8_t*>(peer_q[rank]) + (long)row * d;
+    uint8_t* sf_dst = reinterpret_cast<uint8_t*>(peer_sf[rank]);
+    if (peer_scale != nullptr && lane == 0) reinterpret_cast<float*>(peer_scale[rank])[row] = row_scale ? row_scale[i] : 1.f;
+    for (int c0 = 0; c0 < d; c0 += 512) {
+      const int col = c0 + lane * 16;
+      const bool live = col < d;
+      uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
+      if (live) {
+        a = *reinterpret_cast<const uint4*>(src + col);
+        b = *reinterpret_cast<const uint4*>(src + col + 8);
+      }
+      float v[16];
+      {
+        const uint32_t* au = &a.x; const uint32_t* bu = &b.x;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 f = unpack_bf16(au[q]), g = unpack_bf16(bu[q]);
+          v[2 * q] = f.x; v[2 * q + 1] = f.y; v[8 + 2 * q] = g.x; v[8 + 2 * q + 1] = g.y;
+        }
+      }
+      float amax = 0.f;
+#pragma unroll
+      for (int q = 0; q < 16; ++q) amax = fmaxf(amax, fabsf(v[q]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));   // the block's other half
+      const uint32_t e = live ? (uint32_t)e8m0_of(amax) : 127u;
+      const float inv = e8m0_inv((uint8_t)e);
+      if (live) {
+        uint4 o;
+        o.x = cvt_e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
+        o.y = cvt_e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
+        o.z = cvt_e4m3x4(v[8] * inv, v[9] * inv, v[10] * inv, v[11] * inv);
+        o.w = cvt_e4m3x4(v[12] * inv, v[13] * inv, v[14] * inv, v[15] * inv);
+        *reinterpret_cast<uint4*>(q_dst + col) = o;
+      }
+      // four consecutive blocks' scales (lanes l, l+2, l+4, l+6) make one 4-byte word of a tile
+      const uint32_t w = e | (__shfl_down_sync(0xffffffffu, e, 2) << 8) | (__shfl_down_sync(0xffffffffu, e, 4) << 16) |
+                         (__shfl_down_sync(0xffffffffu, e, 6) << 24);
+      if ((lane & 7) == 0 && live)
+        *reinterpret_cast<uint32_t*>(sf_dst + sf_offset(row, (col >> 5), sf_cols)) = w;
+    }
+  }
+}
+
 // one thread per peer: flag row `channel` of peer p, slot my_rank <- epoch
 __global__ void ep_signal_kernel(const uint64_t* __restrict__ peer_flags, int channel, int world,
                                  int my_rank, int epoch) {
@@ -271,6 +334,12 @@ void ep_push_rows(const void* x, const int* src_token, const int* dst_rank, cons
   // a modest number of CTAs keeps most SMs free for the GEMMs that run beside the exchange
   ep_push_rows_kernel<<<blocks_for(picks, 8, sms > 0 ? sms * 4 : 148 * 4), 256, 0, s>>>(
       (const __nv_bfloat16*)x, src_token, dst_rank, dst_row, row_scale, peer_base, peer_scale, picks, d);
+}
+void ep_push_rows_mx(const void* x, const int* src_token, const int* dst_rank, const int* dst_row,
+                     const float* row_scale, const uint64_t* peer_q, const uint64_t* peer_sf,
+                     const uint64_t* peer_scale, long picks, int d, int sms, cudaStream_t s) {
+  ep_push_rows_mx_kernel<<<blocks_for(picks, 8, sms > 0 ? sms * 4 : 148 * 4), 256, 0, s>>>(
+      (const __nv_bfloat16*)x, src_token, dst_rank, dst_row, row_scale, peer_q, peer_sf, peer_scale, picks, d);
 }
 void row_dots(const void* a, const void* b, float* out, long rows, int d, cudaStream_t s) {
   row_dots_kernel<<<blocks_for(rows, 8, 148 * 8), 256, 0, s>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b, out, rows, d);

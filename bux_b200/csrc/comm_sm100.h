@@ -10,6 +10,11 @@ struct Status;
 void ep_push_rows(const void* x, const int* src_token, const int* dst_rank, const int* dst_row,
                   const float* row_scale, const uint64_t* peer_base, const uint64_t* peer_scale, long picks, int d,
                   int sms, cudaStream_t s);
+// the same rows quantised on the way (MXFP8 along the row): e4m3 bytes into peer_q[rank] ([cap, d]),
+// E8M0 scales into the scale tiles at peer_sf[rank]; d % 128 == 0
+void ep_push_rows_mx(const void* x, const int* src_token, const int* dst_rank, const int* dst_row,
+                     const float* row_scale, const uint64_t* peer_q, const uint64_t* peer_sf,
+                     const uint64_t* peer_scale, long picks, int d, int sms, cudaStream_t s);
 // out[r] = <a[r], b[r]> over rows of d bf16
 void row_dots(const void* a, const void* b, float* out, long rows, int d, cudaStream_t s);
 // out[i] = peer[rank_of[i]][row_of[i]] (fp32), after the peers' flags reached `epoch`

@@ -363,4 +363,33 @@ __device__ __forceinline__ float2 unpack_bf16(uint32_t u) {
   return __bfloat1622float2(h);
 }
 
+// ---------------------------------------------------------------- MXFP8 (E4M3 values, E8M0 scales of 32)
+// E8M0 byte of 2^ceil(log2(amax / 448)), from the fp32 bit pattern (no log).
+__device__ __forceinline__ uint8_t e8m0_of(float amax) {
+  const float ratio = amax * (1.f / 448.f);
+  uint32_t bits = __float_as_uint(ratio);
+  int e = (int)((bits >> 23) & 0xff);
+  const uint32_t mant = bits & 0x7fffffu;
+  if (e == 0) return 0;            // zero / denormal ratio -> smallest scale (2^-127)
+  if (mant != 0) e += 1;           // round the exponent up
+  return (uint8_t)min(e, 254);
+}
+__device__ __forceinline__ float e8m0_inv(uint8_t e) {
+  // 1 / 2^(e-127) = 2^(127-e); e in [0,254] -> exponent field 254 - e (0 -> denormal ok)
+  const int ef = 254 - (int)e;
+  return ef > 0 ? __uint_as_float((uint32_t)ef << 23) : __uint_as_float(0x00400000u);
+}
+// byte offset of scale (row i, scale column j) in the tensor-core tile layout
+__device__ __forceinline__ size_t sf_offset(long i, int j, int sf_cols_padded) {
+  const long rb = i >> 7; const int ri = (int)(i & 127);
+  const int cb = j >> 2, cj = j & 3;
+  return ((size_t)rb * (sf_cols_padded >> 2) + cb) * 512 + (ri & 31) * 16 + (ri >> 5) * 4 + cj;
+}
+
+__device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d) {
+  const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return (uint32_t)lo | ((uint32_t)hi << 16);
+}
+
 }  // namespace bux

@@ -426,28 +426,6 @@ __global__ void glu_bwd_kernel(const __nv_bfloat16* __restrict__ h, const __nv_b
 }
 
 // ---------------------------------------------------------------- MXFP8 quantiser
-// E8M0 byte of 2^ceil(log2(amax / 448)), from the fp32 bit pattern (no log).
-__device__ __forceinline__ uint8_t e8m0_of(float amax) {
-  const float ratio = amax * (1.f / 448.f);
-  uint32_t bits = __float_as_uint(ratio);
-  int e = (int)((bits >> 23) & 0xff);
-  const uint32_t mant = bits & 0x7fffffu;
-  if (e == 0) return 0;            // zero / denormal ratio -> smallest scale (2^-127)
-  if (mant != 0) e += 1;           // round the exponent up
-  return (uint8_t)min(e, 254);
-}
-__device__ __forceinline__ float e8m0_inv(uint8_t e) {
-  // 1 / 2^(e-127) = 2^(127-e); e in [0,254] -> exponent field 254 - e (0 -> denormal ok)
-  const int ef = 254 - (int)e;
-  return ef > 0 ? __uint_as_float((uint32_t)ef << 23) : __uint_as_float(0x00400000u);
-}
-// byte offset of scale (row i, scale column j) in the tensor-core tile layout
-__device__ __forceinline__ size_t sf_offset(long i, int j, int sf_cols_padded) {
-  const long rb = i >> 7; const int ri = (int)(i & 127);
-  const int cb = j >> 2, cj = j & 3;
-  return ((size_t)rb * (sf_cols_padded >> 2) + cb) * 512 + (ri & 31) * 16 + (ri >> 5) * 4 + cj;
-}
-
 // Tile: 128 rows x 128 columns per block of 256 threads, staged once in shared memory as
 // bf16 (row pitch 272 bytes: 16-byte accesses of 8 consecutive rows hit 8 different bank
 // groups). Each tile fills exactly one 512-byte scale tile of the row-wise output and one
@@ -467,18 +445,13 @@ __device__ __forceinline__ int qtile_at(int row, int chunk) {
   return row * QT + ((chunk ^ g) << 3);
 }
 
-__device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d) {
-  const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
-  const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
-  return (uint32_t)lo | ((uint32_t)hi << 16);
-}
 
 // What the quantiser reads its 128×128 tile from: the matrix itself, or a gated activation
 // computed on the way in (the activation, or its gradient, is then never written as bf16).
 #ifndef QUANT_CTAS
 #define QUANT_CTAS 5
 #endif
-enum { QSRC_PLAIN = 0, QSRC_GLU_FWD = 1, QSRC_GLU_BWD = 2 };
+enum { QSRC_PLAIN = 0, QSRC_GLU_FWD = 1, QSRC_GLU_BWD = 2, QSRC_MX = 3 };
 struct QuantGlu {
   const float* row_scale;     // PLAIN: output row r is its source row times row_scale[r] (rounded to bf16);
                               // GLU_FWD: the activation of row r times row_scale[r] (as glu_fwd_kernel)
@@ -486,7 +459,22 @@ struct QuantGlu {
   int f;                      // h is [rows, 2f]: gate columns, then up columns
   int kind;
   float limit, up_offset;
+  const uint8_t* src_sf;      // MX: the source is e4m3 bytes [rows, cols] with these scale tiles (along cols)
 };
+
+// Eight bf16 values of eight e4m3 bytes times their block's scale 2^(e - 127) (exact in bf16).
+__device__ __forceinline__ uint4 dequant_e4m3x8(uint2 q, uint8_t e) {
+  const float sc = e > 0 ? __uint_as_float((uint32_t)e << 23) : __uint_as_float(0x00400000u);
+  uint4 o; uint32_t* ou = &o.x;
+  const uint32_t w[2] = {q.x, q.y};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const __nv_fp8x2_storage_t pair = (__nv_fp8x2_storage_t)((w[j >> 1] >> (16 * (j & 1))) & 0xffffu);
+    const float2 f = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(pair, __NV_E4M3)));
+    ou[j] = pack_bf16(f.x * sc, f.y * sc);
+  }
+  return o;
+}
 
 // Eight gated activations from eight gates and ups (same rounding as glu_fwd_kernel).
 __device__ __forceinline__ uint4 glu_fwd8(const uint4& gv, const uint4& uv, const QuantGlu& gp, float rs) {
@@ -557,7 +545,22 @@ quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long ld_x,
   const long r0 = (long)blockIdx.y * QT;
   const int c0 = blockIdx.x * QT;
   const int cc = (tid & 15) * 8;  // load: 16 threads per row (8 elements each), 16 rows per pass
-  if (SRC == QSRC_PLAIN) {
+  if (SRC == QSRC_MX) {
+    // the source is already MXFP8 along its columns (what a peer pushed): dequantise into the
+    // tile; the column pass below then quantises along the rows
+    const uint8_t* x8 = reinterpret_cast<const uint8_t*>(x);
+    const int src_sf_cols = ((cols / 32) + 3) & ~3;
+#pragma unroll
+    for (int base = 0; base < 8; ++base) {
+      const long r = r0 + base * 16 + (tid >> 4);
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (r < rows && c0 + cc < cols) {
+        const uint2 q = *reinterpret_cast<const uint2*>(x8 + r * ld_x + c0 + cc);
+        v = dequant_e4m3x8(q, gp.src_sf[sf_offset(r, (c0 + cc) >> 5, src_sf_cols)]);
+      }
+      *reinterpret_cast<uint4*>(&tile[qtile_at(base * 16 + (tid >> 4), tid & 15)]) = v;
+    }
+  } else if (SRC == QSRC_PLAIN) {
 #pragma unroll
     for (int base = 0; base < 8; base += 4) {
       uint4 v[4];
@@ -1126,7 +1129,14 @@ void glu_bwd(const void* h, const void* dout, void* dh, const float* row_scale, 
 void quant_mxfp8(const void* x, long ld_x, const int* row_index, const float* row_scale, uint8_t* q_row, uint8_t* sf_row, uint8_t* q_col, uint8_t* sf_col, long rows, int cols, long ld_col, int batch, long x_batch_stride, cudaStream_t s) {
   const long extent = q_col ? (ld_col > rows ? ld_col : rows) : rows;  // the transposed copy is padded to ld_col
   dim3 grid((cols + 127) / 128, (unsigned)((extent + 127) / 128), batch);
-  quant_mxfp8_kernel<QSRC_PLAIN><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, ld_x, row_index, q_row, sf_row, q_col, sf_col, rows, cols, ld_col, x_batch_stride, QuantGlu{row_scale, nullptr, 0, 0, 0.f, 0.f});
+  quant_mxfp8_kernel<QSRC_PLAIN><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, ld_x, row_index, q_row, sf_row, q_col, sf_col, rows, cols, ld_col, x_batch_stride, QuantGlu{row_scale, nullptr, 0, 0, 0.f, 0.f, nullptr});
+}
+void requant_mxfp8_cols(const uint8_t* q, const uint8_t* sf, uint8_t* q_col, uint8_t* sf_col, long rows, int cols,
+                        long ld_col, cudaStream_t s) {
+  const long extent = ld_col > rows ? ld_col : rows;
+  dim3 grid((cols + 127) / 128, (unsigned)((extent + 127) / 128), 1);
+  quant_mxfp8_kernel<QSRC_MX><<<grid, 256, 0, s>>>((const __nv_bfloat16*)q, cols, nullptr, nullptr, nullptr, q_col, sf_col,
+                                                   rows, cols, ld_col, 0, QuantGlu{nullptr, nullptr, 0, 0, 0.f, 0.f, sf});
 }
 void quant_mxfp8_glu(const void* h, const void* dout, const float* row_scale, uint8_t* q_row, uint8_t* sf_row,
                      uint8_t* q_col, uint8_t* sf_col, long rows, int f, long ld_col, int kind, float limit,
@@ -1134,7 +1144,7 @@ void quant_mxfp8_glu(const void* h, const void* dout, const float* row_scale, ui
   const int cols = dout ? 2 * f : f;
   const long extent = q_col ? (ld_col > rows ? ld_col : rows) : rows;
   dim3 grid((cols + 127) / 128, (unsigned)((extent + 127) / 128), 1);
-  QuantGlu gp{dout ? nullptr : row_scale, (const __nv_bfloat16*)dout, f, kind, limit, up_offset};
+  QuantGlu gp{dout ? nullptr : row_scale, (const __nv_bfloat16*)dout, f, kind, limit, up_offset, nullptr};
   if (dout) quant_mxfp8_kernel<QSRC_GLU_BWD><<<grid, 256, 0, s>>>((const __nv_bfloat16*)h, 2L * f, nullptr, q_row, sf_row, q_col, sf_col, rows, cols, ld_col, 0, gp);
   else quant_mxfp8_kernel<QSRC_GLU_FWD><<<grid, 256, 0, s>>>((const __nv_bfloat16*)h, 2L * f, nullptr, q_row, sf_row, q_col, sf_col, rows, cols, ld_col, 0, gp);
 }

@@ -23,6 +23,10 @@ void quant_mxfp8(const void* x, long ld_x, const int* row_index, const float* ro
 void quant_mxfp8_glu(const void* h, const void* dout, const float* row_scale, uint8_t* q_row, uint8_t* sf_row,
                      uint8_t* q_col, uint8_t* sf_col, long rows, int f, long ld_col, int kind, float limit,
                      float up_offset, cudaStream_t s);
+// The transposed MXFP8 copy ([cols, ld_col], quantised along the rows) of a matrix that is
+// already MXFP8 along its columns (e4m3 bytes [rows, cols] + scale tiles): dequantise, requantise.
+void requant_mxfp8_cols(const uint8_t* q, const uint8_t* sf, uint8_t* q_col, uint8_t* sf_col, long rows, int cols,
+                        long ld_col, cudaStream_t s);
 void ce_fwd_bwd(void* logits, const int* targets, const float* mask, float* loss, float* logz, long rows, int vocab, long ld, float grad_scale, float z_weight, float softcap, cudaStream_t s);
 const char* adamw(void* p, bool p_bf16, const void* g, bool g_bf16, void* m, void* v, uint8_t* m_sf, uint8_t* v_sf, int mom,
                   void* shadow, long n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,

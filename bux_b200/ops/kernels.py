@@ -397,6 +397,27 @@ def ep_push_rows(x, src_token, dst_rank, dst_row, peer_base, row_scale=None, sms
     _count()
 
 
+def ep_push_rows_mx(x, src_token, dst_rank, dst_row, peer_q, peer_sf, row_scale=None, peer_scale=None,
+                    sms: int = 0) -> None:
+    """`ep_push_rows` with the rows quantised on the way (MXFP8 along the row): e4m3 bytes into the
+    peers' [cap, d] byte buffers, E8M0 scales into their scale tiles; `row_scale` (a pick's router
+    weight) is stored beside the row in the peers' fp32 `peer_scale` buffers, not applied."""
+    ops().ep_push_rows_mx(x, src_token, dst_rank, dst_row, row_scale, peer_q, peer_sf, peer_scale, sms)
+    _count()
+
+
+def requant_mxfp8_cols(q: torch.Tensor, sf: torch.Tensor, rows: int, cols: int):
+    """(q_col [cols, rows padded to 128], sf_col): the transposed MXFP8 copy, quantised along the
+    rows, of a matrix that is MXFP8 along its columns already (e4m3 bytes [rows, cols] + scale
+    tiles). Same values as quantising the dequantised matrix column-wise."""
+    r_pad = -(-rows // 128) * 128
+    q_col = torch.empty(cols, r_pad, dtype=torch.float8_e4m3fn, device=q.device)
+    sf_col = torch.empty(sf_bytes(cols, r_pad), dtype=torch.uint8, device=q.device)
+    ops().requant_mxfp8_cols(q.view(torch.uint8), sf, q_col.view(torch.uint8), sf_col, rows, cols, r_pad)
+    _count()
+    return q_col, sf_col
+
+
 def ep_signal(peer_flags, channel: int, world: int, my_rank: int, epoch: int) -> None:
     ops().ep_signal(peer_flags, channel, world, my_rank, epoch)
     _count()

@@ -74,6 +74,8 @@ def _worker(rank, port, out):
             for rep in range(2):  # twice: the second use meets the first one's leftovers in the slots
                 got = grads(lambda x, w: ep(moe, x, w, idx, ctx, fmt))
             results[(fmt, f"fused-c{chunks}-s{int(stream)}")] = [_rel(a, b) for a, b in zip(got, base)]
+            # forward outputs quantise the same rows the same way whatever their order
+            results[(fmt, f"fused-c{chunks}-s{int(stream)}-out")] = [_rel(got[0], want[0]) / 5]
     torch.cuda.synchronize()
     K.check_status(dev, "loopback")
     torch.save(results, out)
