@@ -10,7 +10,7 @@ from typing import Optional
 
 import torch
 
-from . import _build
+from . import _build, checks
 
 KIND_BF16, KIND_MXFP8 = 0, 1
 MODE_DENSE, MODE_GROUPED_ROWS, MODE_GROUPED_K = 0, 1, 2
@@ -24,6 +24,13 @@ launches = 0  # kernels launched through this module (bench.py reports it)
 def ops():
     _build.load(required=True)
     return torch.ops.bux_b200
+
+
+def _out(*shape, dtype, device, op: str, fill=None) -> torch.Tensor:
+    """A kernel's output buffer: between guard regions when kernel checks are on."""
+    if len(shape) == 1 and isinstance(shape[0], (tuple, list, torch.Size)):
+        shape = tuple(shape[0])
+    return checks.guarded_empty(shape, dtype, device, op, fill)
 
 
 def _count(n: int = 1) -> None:
@@ -63,7 +70,7 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: boo
     m, k = (a.shape[1], a.shape[0]) if a_mn else a.shape
     n = b.shape[1] if b_mn else b.shape[0]
     if out is None:
-        out = torch.empty(m, n, dtype=out_dtype, device=a.device)
+        out = _out(m, n, dtype=out_dtype, device=a.device, op="gemm_bf16")
     kind = OUT_BF16 if out.dtype == torch.bfloat16 else (OUT_F32_ACC if accumulate else OUT_F32)
     ops().gemm(a, b, out, None, None, None, status_word(a.device), KIND_BF16, MODE_DENSE, m, n, k, k, 1,
                a_mn, b_mn, kind, bn, sms, wait_flags, wait_epoch, wait_rows, m_rotate, wait_on_k)
@@ -81,7 +88,7 @@ def gemm_mxfp8(aq, asf, bq, bsf, m: int, n: int, k: int, *, out=None, out_dtype=
     """C[m,n] = dequant(A)[m,k] · dequant(B)[n,k]^T; scales in the tiled layout."""
     bn = _tile_width(n) if bn is None else bn
     if out is None:
-        out = torch.empty(m, n, dtype=out_dtype, device=aq.device)
+        out = _out(m, n, dtype=out_dtype, device=aq.device, op="gemm_mxfp8")
     kind = OUT_BF16 if out.dtype == torch.bfloat16 else (OUT_F32_ACC if accumulate else OUT_F32)
     ops().gemm(aq.view(torch.uint8), bq.view(torch.uint8), out, asf, bsf, None, status_word(aq.device),
                KIND_MXFP8, MODE_DENSE, m, n, k, k, 1, False, False, kind, bn, sms)
@@ -97,7 +104,7 @@ def grouped_gemm(a, b, offsets: torch.Tensor, n: int, k: int, *, kind: int = KIN
     bn = _tile_width(n) if bn is None else bn
     groups = offsets.numel() - 1
     if out is None:
-        out = torch.empty(a.shape[0], n, dtype=torch.bfloat16, device=a.device)
+        out = _out(a.shape[0], n, dtype=torch.bfloat16, device=a.device, op="grouped_gemm")
     if kind == KIND_MXFP8:
         a, b = a.view(torch.uint8), b.view(torch.uint8)
     ops().gemm(a, b, out, asf, bsf, offsets, status_word(a.device), kind, MODE_GROUPED_ROWS,
@@ -118,7 +125,7 @@ def grouped_gemm_k(a, b, offsets: torch.Tensor, m: int, n: int, *, kind: int = K
     groups = offsets.numel() - 1
     ktot = a.shape[0] if a_mn else a.shape[1]
     if out is None:
-        out = torch.empty(groups, m, n, dtype=out_dtype, device=a.device)
+        out = _out(groups, m, n, dtype=out_dtype, device=a.device, op="grouped_gemm_k")
         accumulate = False
     if kind == KIND_MXFP8:
         a, b = a.view(torch.uint8), b.view(torch.uint8)
@@ -144,12 +151,12 @@ def quant_mxfp8_batched(x: torch.Tensor, *, rowwise: bool = True, colwise: bool 
     q_row = sf_row = q_col = sf_col = None
     if rowwise:
         assert r % 128 == 0 or e == 1, "rowwise scale tiles of a stack need R % 128 == 0"
-        q_row = torch.empty(e * r, c, dtype=torch.float8_e4m3fn, device=dev)
-        sf_row = torch.empty(e * sf_bytes(r, c), dtype=torch.uint8, device=dev)
+        q_row = _out(e * r, c, dtype=torch.float8_e4m3fn, device=dev, op="quant_mxfp8_batched q_row")
+        sf_row = _out(e * sf_bytes(r, c), dtype=torch.uint8, device=dev, op="quant_mxfp8_batched sf_row")
     if colwise:
         assert r % 128 == 0 and c % 128 == 0
-        q_col = torch.empty(e * c, r, dtype=torch.float8_e4m3fn, device=dev)
-        sf_col = torch.empty(e * sf_bytes(c, r), dtype=torch.uint8, device=dev)
+        q_col = _out(e * c, r, dtype=torch.float8_e4m3fn, device=dev, op="quant_mxfp8_batched q_col")
+        sf_col = _out(e * sf_bytes(c, r), dtype=torch.uint8, device=dev, op="quant_mxfp8_batched sf_col")
     xc = x.contiguous()
     ops().quant_mxfp8(xc, None, None, None if q_row is None else q_row.view(torch.uint8), sf_row,
                       None if q_col is None else q_col.view(torch.uint8), sf_col, r, c, r, e, r * c)
@@ -170,13 +177,13 @@ def quant_mxfp8(x: torch.Tensor, *, rowwise: bool = True, colwise: bool = False,
     dev = x.device
     q_row = sf_row = q_col = sf_col = None
     if rowwise:
-        q_row = torch.empty(r, c, dtype=torch.float8_e4m3fn, device=dev)
-        sf_row = torch.empty(sf_bytes(r, c), dtype=torch.uint8, device=dev)
+        q_row = _out(r, c, dtype=torch.float8_e4m3fn, device=dev, op="quant_mxfp8 q_row")
+        sf_row = _out(sf_bytes(r, c), dtype=torch.uint8, device=dev, op="quant_mxfp8 sf_row")
     r_pad = -(-r // 128) * 128
     if colwise:
         # the kernel writes every byte of both outputs, padding included
-        q_col = torch.empty(c, r_pad, dtype=torch.float8_e4m3fn, device=dev)
-        sf_col = torch.empty(sf_bytes(c, r_pad), dtype=torch.uint8, device=dev)
+        q_col = _out(c, r_pad, dtype=torch.float8_e4m3fn, device=dev, op="quant_mxfp8 q_col")
+        sf_col = _out(sf_bytes(c, r_pad), dtype=torch.uint8, device=dev, op="quant_mxfp8 sf_col")
     ops().quant_mxfp8(x2, row_index, row_scale, None if q_row is None else q_row.view(torch.uint8), sf_row,
                       None if q_col is None else q_col.view(torch.uint8), sf_col, r, c, r_pad, 1, 0)
     _count()
@@ -196,12 +203,12 @@ def quant_mxfp8_glu(h: torch.Tensor, dout: Optional[torch.Tensor] = None, kind: 
     dev = h.device
     q_row = sf_row = q_col = sf_col = None
     if rowwise:
-        q_row = torch.empty(r, c, dtype=torch.float8_e4m3fn, device=dev)
-        sf_row = torch.empty(sf_bytes(r, c), dtype=torch.uint8, device=dev)
+        q_row = _out(r, c, dtype=torch.float8_e4m3fn, device=dev, op="quant_mxfp8_glu q_row")
+        sf_row = _out(sf_bytes(r, c), dtype=torch.uint8, device=dev, op="quant_mxfp8_glu sf_row")
     r_pad = -(-r // 128) * 128
     if colwise:
-        q_col = torch.empty(c, r_pad, dtype=torch.float8_e4m3fn, device=dev)
-        sf_col = torch.empty(sf_bytes(c, r_pad), dtype=torch.uint8, device=dev)
+        q_col = _out(c, r_pad, dtype=torch.float8_e4m3fn, device=dev, op="quant_mxfp8_glu q_col")
+        sf_col = _out(sf_bytes(c, r_pad), dtype=torch.uint8, device=dev, op="quant_mxfp8_glu sf_col")
     ops().quant_mxfp8_glu(h, dout, row_scale, None if q_row is None else q_row.view(torch.uint8), sf_row,
                           None if q_col is None else q_col.view(torch.uint8), sf_col, r_pad,
                           ACT_KINDS[kind], float(limit), float(up_offset))
@@ -211,16 +218,17 @@ def quant_mxfp8_glu(h: torch.Tensor, dout: Optional[torch.Tensor] = None, kind: 
 
 # ------------------------------------------------------------------ norms / rope / glu
 def rmsnorm_fwd(x, w, eps: float):
-    y = torch.empty_like(x)
-    rstd = torch.empty(x.numel() // x.shape[-1], dtype=torch.float32, device=x.device)
+    y = _out(x.shape, dtype=x.dtype, device=x.device, op="rmsnorm_fwd y")
+    rstd = _out(x.numel() // x.shape[-1], dtype=torch.float32, device=x.device, op="rmsnorm_fwd rstd")
     ops().rmsnorm_fwd(x, w, y, rstd, eps)
     _count()
     return y, rstd
 
 
 def rmsnorm_bwd(x, w, dy, rstd, need_dw: bool = True):
-    dx = torch.empty_like(x)
-    dw = torch.zeros(x.shape[-1], dtype=torch.float32, device=x.device) if need_dw and w is not None else None
+    dx = _out(x.shape, dtype=x.dtype, device=x.device, op="rmsnorm_bwd dx")
+    dw = (_out(x.shape[-1], dtype=torch.float32, device=x.device, op="rmsnorm_bwd dw", fill=0.0)
+          if need_dw and w is not None else None)
     ops().rmsnorm_bwd(x, w, dy, rstd, dx, dw)
     _count()
     return dx, dw
@@ -243,8 +251,8 @@ def norm_rope_fwd(x, w, cos, sin, eps: float):
     """x: [..., T, H, D], dense or a column slice (see `token_stride`); cos/sin: [tokens, D/2] fp32."""
     d, h = x.shape[-1], x.shape[-2]
     tokens = x.numel() // (h * d)
-    y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
-    rstd = torch.empty(tokens * h, dtype=torch.float32, device=x.device) if w is not None else None
+    y = _out(x.shape, dtype=x.dtype, device=x.device, op="norm_rope_fwd y")
+    rstd = _out(tokens * h, dtype=torch.float32, device=x.device, op="norm_rope_fwd rstd") if w is not None else None
     ops().norm_rope(False, x, w, cos, sin, y, rstd, None, None, tokens, h, d, token_stride(x), h * d, eps)
     _count()
     return y, rstd
@@ -253,23 +261,24 @@ def norm_rope_fwd(x, w, cos, sin, eps: float):
 def norm_rope_bwd(x, w, cos, sin, rstd, dy, eps: float):
     d, h = x.shape[-1], x.shape[-2]
     tokens = x.numel() // (h * d)
-    dx = torch.empty(x.shape, dtype=x.dtype, device=x.device)
-    dw = torch.zeros(d, dtype=torch.float32, device=x.device) if w is not None else None
+    dx = _out(x.shape, dtype=x.dtype, device=x.device, op="norm_rope_bwd dx")
+    dw = _out(d, dtype=torch.float32, device=x.device, op="norm_rope_bwd dw", fill=0.0) if w is not None else None
     ops().norm_rope(True, x, w, cos, sin, dx, rstd, dy, dw, tokens, h, d, token_stride(x), h * d, eps)
     _count()
     return dx, dw
 
 
 def glu_fwd(h, kind: str = "swish", row_scale=None, limit: float = 0.0, up_offset: float = 0.0):
-    out = torch.empty(*h.shape[:-1], h.shape[-1] // 2, dtype=h.dtype, device=h.device)
+    out = _out(*h.shape[:-1], h.shape[-1] // 2, dtype=h.dtype, device=h.device, op="glu_fwd")
     ops().glu_fwd(h, out, row_scale, ACT_KINDS[kind], limit or 0.0, up_offset)
     _count()
     return out
 
 
 def glu_bwd(h, dout, kind: str = "swish", row_scale=None, limit: float = 0.0, up_offset: float = 0.0):
-    dh = torch.empty_like(h)
-    drs = torch.zeros_like(row_scale) if row_scale is not None else None
+    dh = _out(h.shape, dtype=h.dtype, device=h.device, op="glu_bwd dh")
+    drs = (_out(row_scale.shape, dtype=row_scale.dtype, device=h.device, op="glu_bwd d_row_scale", fill=0.0)
+           if row_scale is not None else None)
     ops().glu_bwd(h, dout, dh, row_scale, drs, ACT_KINDS[kind], limit or 0.0, up_offset)
     _count()
     return dh, drs
@@ -278,7 +287,7 @@ def glu_bwd(h, dout, kind: str = "swish", row_scale=None, limit: float = 0.0, up
 def glu_bwd_into(h, dout, kind: str, row_scale, d_row_scale, limit: float = 0.0, up_offset: float = 0.0):
     """`glu_bwd` whose per-row gradient of `row_scale` lands in the caller's fp32 buffer
     (cleared here first: the kernel adds into it). Returns dh."""
-    dh = torch.empty_like(h)
+    dh = _out(h.shape, dtype=h.dtype, device=h.device, op="glu_bwd dh")
     d_row_scale.zero_()
     ops().glu_bwd(h, dout, dh, row_scale, d_row_scale, ACT_KINDS[kind], limit or 0.0, up_offset)
     _count()
@@ -288,7 +297,7 @@ def glu_bwd_into(h, dout, kind: str, row_scale, d_row_scale, limit: float = 0.0,
 # ------------------------------------------------------------------ loss / optimiser / rows
 def ce_fwd_bwd(logits, targets, mask, grad_scale: float, z_weight: float = 0.0, softcap: float = 0.0):
     """In place: logits become dlogits. Returns per-row loss (fp32)."""
-    loss = torch.empty(logits.shape[0], dtype=torch.float32, device=logits.device)
+    loss = _out(logits.shape[0], dtype=torch.float32, device=logits.device, op="ce_fwd_bwd loss")
     ops().ce_fwd_bwd(logits, targets, mask, loss, None, grad_scale, z_weight, softcap or 0.0)
     _count()
     return loss
@@ -310,14 +319,14 @@ def topk_rows(scores: torch.Tensor, k: int) -> torch.Tensor:
     """Indices [..., k] (int64) of the k largest entries along the last dimension of fp32
     scores (at most 512 wide), in descending order of value; ties go to the lower index."""
     flat = scores.reshape(-1, scores.shape[-1]).contiguous()
-    idx = torch.empty(flat.shape[0], k, dtype=torch.int64, device=scores.device)
+    idx = _out(flat.shape[0], k, dtype=torch.int64, device=scores.device, op="topk_rows")
     ops().topk_rows(flat, idx)
     _count()
     return idx.view(*scores.shape[:-1], k)
 
 
 def gather_rows(x, index, rows: int):
-    out = torch.empty(rows, x.shape[-1], dtype=x.dtype, device=x.device)
+    out = _out(rows, x.shape[-1], dtype=x.dtype, device=x.device, op="gather_rows")
     ops().gather_rows(x, index, out)
     _count()
     return out
@@ -342,7 +351,7 @@ def combine_dots(y, dout, pos):
 
 
 def combine_rows(y, pos, w, tokens: int):
-    out = torch.empty(tokens, y.shape[-1], dtype=y.dtype, device=y.device)
+    out = _out(tokens, y.shape[-1], dtype=y.dtype, device=y.device, op="combine_rows")
     ops().combine_rows(y, pos, w, out)
     _count()
     return out
@@ -367,8 +376,8 @@ def document_bounds(segments: torch.Tensor):
 
 def attn_fwd(q, k, v, *, causal=True, window=0, sinks=None, scale=None, row_lo=None):
     b, t, h, d = q.shape
-    o = torch.empty_like(q)
-    lse = torch.empty(b, h, t, dtype=torch.float32, device=q.device)
+    o = _out(q.shape, dtype=q.dtype, device=q.device, op="attn_fwd o")
+    lse = _out(b, h, t, dtype=torch.float32, device=q.device, op="attn_fwd lse")
     ops().attn_fwd(q, k, v, o, lse, sinks, status_word(q.device), scale if scale is not None else d ** -0.5,
                    causal, window or 0, row_lo)
     _count()
@@ -377,10 +386,10 @@ def attn_fwd(q, k, v, *, causal=True, window=0, sinks=None, scale=None, row_lo=N
 
 def attn_bwd(q, k, v, o, do, lse, *, causal=True, window=0, sinks=None, scale=None, row_lo=None, key_hi=None):
     b, t, h, d = q.shape
-    dq = torch.zeros(b, t, h, d, dtype=torch.float32, device=q.device)
-    dk = torch.empty_like(k)
-    dv = torch.empty_like(v)
-    delta = torch.empty(b, h, t, dtype=torch.float32, device=q.device)
+    dq = _out(b, t, h, d, dtype=torch.float32, device=q.device, op="attn_bwd dq", fill=0.0)
+    dk = _out(k.shape, dtype=k.dtype, device=k.device, op="attn_bwd dk")
+    dv = _out(v.shape, dtype=v.dtype, device=v.device, op="attn_bwd dv")
+    delta = _out(b, h, t, dtype=torch.float32, device=q.device, op="attn_bwd delta")
     dsinks = torch.zeros_like(sinks) if sinks is not None else None
     ops().attn_bwd(q, k, v, o, do, lse, dq, dk, dv, delta, sinks, dsinks, status_word(q.device),
                    scale if scale is not None else d ** -0.5, causal, window or 0, row_lo, key_hi)
@@ -411,8 +420,8 @@ def requant_mxfp8_cols(q: torch.Tensor, sf: torch.Tensor, rows: int, cols: int):
     rows, of a matrix that is MXFP8 along its columns already (e4m3 bytes [rows, cols] + scale
     tiles). Same values as quantising the dequantised matrix column-wise."""
     r_pad = -(-rows // 128) * 128
-    q_col = torch.empty(cols, r_pad, dtype=torch.float8_e4m3fn, device=q.device)
-    sf_col = torch.empty(sf_bytes(cols, r_pad), dtype=torch.uint8, device=q.device)
+    q_col = _out(cols, r_pad, dtype=torch.float8_e4m3fn, device=q.device, op="requant_mxfp8_cols q_col")
+    sf_col = _out(sf_bytes(cols, r_pad), dtype=torch.uint8, device=q.device, op="requant_mxfp8_cols sf_col")
     ops().requant_mxfp8_cols(q.view(torch.uint8), sf, q_col.view(torch.uint8), sf_col, rows, cols, r_pad)
     _count()
     return q_col, sf_col

@@ -4,13 +4,17 @@ Two methods (``methods(moe=...)``):
 
 * ``fused_ep``: the exchange is done by this library's own kernels over NVLink peer
   memory (symmetric buffers). Dispatch = P2P stores of token rows straight into the
-  owner's expert-sorted receive buffer + epoch flags; the owner's first grouped GEMM
-  waits for the flags in its TMA producer warp; combine = P2P loads of the expert
-  outputs where they were produced, weighted and summed per token. The backward
-  mirrors it: dout rows are pushed to the owners with their weights beside them, each
-  owner takes the dot products of its dy and y rows for the router weights' gradient
-  (only those scalars cross NVLink again) and applies the weights as it quantises; dx is
-  pulled. No NCCL call moves a token; one tiny all-gather moves the per-expert counts.
+  owner's expert-sorted receive buffer + epoch flags; with MXFP8 experts the rows are
+  quantised as they are sent (d e4m3 bytes + d/32 scale bytes per row, the reference's
+  wire format, ``parallel/experts.py:326-349`` there) and land as the owner's GEMM operand,
+  scale tiles included. Each row's router weight travels beside it and multiplies the
+  activation, so the combine = P2P loads of the expert outputs where they were produced,
+  summed per token. The backward mirrors it: dout rows are pushed (MXFP8 again), the
+  owner's activation backward yields dx rows and one scalar per row for the router weights'
+  gradient, and both are pulled. Tokens go in ``methods(moe_chunks=...)`` ranges, each
+  range's transfers on a side stream (``methods(moe_stream=true)``) beside the GEMMs of the
+  range before it. No NCCL call moves a token; one small all-gather moves the per-expert
+  counts.
 * ``all_to_all`` (also ``nccl_ep`` / ``ragged_all_to_all``, which keep their meaning of
   "library collective"): the same layout through ``torch.distributed.all_to_all_single``,
   the measured baseline and the CPU/gloo path of the tests.
@@ -96,11 +100,14 @@ class FusedEP:
     each kind, so that consecutive token chunks overlap), the peers' base addresses, flag
     rows, epoch counters and the side stream the transfers run on."""
 
-    KINDS = (("x", 2), ("y", 2), ("dy", 2), ("dx", 2))   # [cap, d] bf16
+    KINDS = (("x", 2), ("y", 2), ("dy", 2), ("dx", 2))   # [cap, d] bf16 (x, dy: e4m3 bytes in the MXFP8 exchange)
+    SCALES = ("xsf", "dysf")                               # scale tiles of x and dy rows that travel as MXFP8
     SCALARS = ("xw", "dots")                               # [cap] fp32: a row's router weight; its gradient
 
     def __init__(self, group, device, d: int, cap_rows: int, dtype=torch.bfloat16):
         import torch.distributed._symmetric_memory as symm
+
+        from ..ops import kernels as K
 
         self.group, self.device, self.d, self.cap = group, device, d, cap_rows
         self.world, self.me = dist.get_world_size(group), dist.get_rank(group)
@@ -115,6 +122,11 @@ class FusedEP:
             for slot in range(SLOTS):
                 pieces[(key, slot)] = (at, cap_rows * 4)
                 at += -(-cap_rows * 4 // 256) * 256
+        sf_size = K.sf_bytes(cap_rows, d) if d % 128 == 0 else 0
+        for key in self.SCALES:
+            for slot in range(SLOTS):
+                pieces[(key, slot)] = (at, sf_size)
+                at += -(-sf_size // 256) * 256
         flags_at = at
         at += 8 * self.world * 4
         heap = symm.empty(at, dtype=torch.uint8, device=device)
@@ -125,8 +137,16 @@ class FusedEP:
         self.bufs, self.tables = {}, {}
         for (key, slot), (off, size) in pieces.items():
             view = heap[off:off + size]
-            self.bufs[(key, slot)] = (view.view(torch.float32) if key in self.SCALARS
-                                      else view.view(dtype).view(cap_rows, d))
+            if key in self.SCALARS:
+                self.bufs[(key, slot)] = view.view(torch.float32)
+            elif key in self.SCALES:
+                self.bufs[(key, slot)] = view
+            else:
+                self.bufs[(key, slot)] = view.view(dtype).view(cap_rows, d)
+                if key in ("x", "dy"):  # the same memory as the e4m3 rows of the MXFP8 exchange
+                    self.bufs[(key + "q", slot)] = view[:cap_rows * d].view(cap_rows, d)
+                    self.tables[(key + "q", slot)] = torch.tensor([b + off for b in bases], dtype=torch.int64,
+                                                                  device=device)
             self.tables[(key, slot)] = torch.tensor([b + off for b in bases], dtype=torch.int64, device=device)
         self.flags = heap[flags_at:flags_at + 8 * self.world * 4].view(torch.int32).view(8, self.world)
         self.peer_flags = torch.tensor([b + flags_at for b in bases], dtype=torch.int64, device=device)
@@ -240,25 +260,34 @@ class _FusedExperts(torch.autograd.Function):
             r = routes[c]
             with torch.cuda.stream(comm):
                 scale = wts[c * tc:(c + 1) * tc].reshape(-1)[r.order].contiguous()
-                K.ep_push_rows(x[c * tc:(c + 1) * tc], r.src_token, r.dst_rank, r.dst_row, ep.tables[("x", c % SLOTS)],
-                               row_scale=scale, peer_scale=ep.tables[("xw", c % SLOTS)])
+                slot = c % SLOTS
+                if mx:  # rows leave as e4m3 bytes + E8M0 scales, straight into the owner's GEMM operand
+                    K.ep_push_rows_mx(x[c * tc:(c + 1) * tc], r.src_token, r.dst_rank, r.dst_row,
+                                      ep.tables[("xq", slot)], ep.tables[("xsf", slot)], row_scale=scale,
+                                      peer_scale=ep.tables[("xw", slot)])
+                else:
+                    K.ep_push_rows(x[c * tc:(c + 1) * tc], r.src_token, r.dst_rank, r.dst_row, ep.tables[("x", slot)],
+                                   row_scale=scale, peer_scale=ep.tables[("xw", slot)])
                 x_epoch[c] = ep.signal(CH_X)
 
         def compute(c):
             r, slot = routes[c], c % SLOTS
             ep.wait(CH_X, x_epoch[c])
-            xs = ep.bufs[("x", slot)]
-            K.zero_pad_rows(xs, r.offsets, r.counts)
             w_row = ep.bufs[("xw", slot)][:cap]
             y_out = ep.bufs[("y", slot)]
             xtq = xtsf = None
             if mx:
-                xq, xsf, xtq, xtsf = K.quant_mxfp8(xs, rowwise=True, colwise=grad)
+                # what arrived is the GEMM's operand already; padding rows are cleared (zero bytes)
+                xq, xsf = ep.bufs[("xq", slot)], ep.bufs[("xsf", slot)]
+                K.zero_pad_rows(xq.view(torch.bfloat16), r.offsets, r.counts)
                 h = K.grouped_gemm(xq, gq, r.offsets, f2, d, kind=kind, asf=xsf, bsf=gsf)
-                del xq, xsf
+                if grad:  # the transposed copy for the weight gradient, before the slot is reused
+                    xtq, xtsf = K.requant_mxfp8_cols(xq, xsf, cap, d)
                 aq, asf, _, _ = K.quant_mxfp8_glu(h, None, act, limit=limit, up_offset=up_offset, row_scale=w_row)
                 K.grouped_gemm(aq, dq, r.offsets, d, f, kind=kind, asf=asf, bsf=dsf, out=y_out)
             else:
+                xs = ep.bufs[("x", slot)]
+                K.zero_pad_rows(xs, r.offsets, r.counts)
                 h = K.grouped_gemm(xs, w_gu.view(e * f2, d), r.offsets, f2, d)
                 a = K.glu_fwd(h, act, w_row, limit, up_offset)
                 K.grouped_gemm(a, w_down.view(e * d, f), r.offsets, d, f, out=y_out)
@@ -324,8 +353,12 @@ class _FusedExperts(torch.autograd.Function):
         def push(c):
             r = routes[c]
             with torch.cuda.stream(comm):
-                K.ep_push_rows(dout[c * tc:(c + 1) * tc], r.src_token, r.dst_rank, r.dst_row,
-                               ep.tables[("dy", c % SLOTS)])
+                if mx:
+                    K.ep_push_rows_mx(dout[c * tc:(c + 1) * tc], r.src_token, r.dst_rank, r.dst_row,
+                                      ep.tables[("dyq", c % SLOTS)], ep.tables[("dysf", c % SLOTS)])
+                else:
+                    K.ep_push_rows(dout[c * tc:(c + 1) * tc], r.src_token, r.dst_rank, r.dst_row,
+                                   ep.tables[("dy", c % SLOTS)])
                 dy_epoch[c] = ep.signal(CH_DY)
 
         def compute(c):
@@ -333,12 +366,12 @@ class _FusedExperts(torch.autograd.Function):
             h, xsave, xtsf, w_row = saved[c]
             saved[c] = None
             ep.wait(CH_DY, dy_epoch[c])
-            dy = ep.bufs[("dy", slot)]
-            K.zero_pad_rows(dy, r.offsets, r.counts)
             dots = ep.bufs[("dots", slot)][:cap]
             dx_out = ep.bufs[("dx", slot)]
             if mx:
-                dyq, dysf, dytq, dytsf = K.quant_mxfp8(dy, rowwise=True, colwise=True)
+                dyq, dysf = ep.bufs[("dyq", slot)], ep.bufs[("dysf", slot)]
+                K.zero_pad_rows(dyq.view(torch.bfloat16), r.offsets, r.counts)
+                dytq, dytsf = K.requant_mxfp8_cols(dyq, dysf, cap, d)
                 _, _, atq, atsf = K.quant_mxfp8_glu(h, None, act, rowwise=False, colwise=True, limit=limit,
                                                     up_offset=up_offset, row_scale=w_row)
                 result["down"] = K.grouped_gemm_k(dytq, atq, r.offsets, d, f, kind=kind, asf=dytsf, bsf=atsf,
@@ -346,8 +379,9 @@ class _FusedExperts(torch.autograd.Function):
                                                   out_dtype=fused._grad_dtype(w_down))
                 del dytq, dytsf, atq, atsf
                 da = K.grouped_gemm(dyq, dtq, r.offsets, f, d, kind=kind, asf=dysf, bsf=dtsf)
-                del dyq, dysf
             else:
+                dy = ep.bufs[("dy", slot)]
+                K.zero_pad_rows(dy, r.offsets, r.counts)
                 a = K.glu_fwd(h, act, w_row, limit, up_offset)
                 result["down"] = K.grouped_gemm_k(dy, a, r.offsets, d, f, a_mn=True, b_mn=True, out=acc_down,
                                                   accumulate=acc_down is not None,
@@ -524,7 +558,8 @@ class ExpertParallel:
         ep = self.fused[key]
         routes = route_chunks(idx, c.num_experts, self.group, cap, chunks)
         self.dropped = sum(r.dropped for r in routes)
-        mx = kw["fmt"] in ("mxfp8", "mxfp8_2d")
+        f = moe.experts_down.shape[-1]
+        mx = kw["fmt"] in ("mxfp8", "mxfp8_2d") and d % 128 == 0 and f % 128 == 0
         return _FusedExperts.apply(x.contiguous(), weights, moe.experts_gate_up, moe.experts_down, ep, routes,
                                    kw["act"], float(kw["limit"] or 0.0), float(kw["up_offset"]), mx,
                                    bool(getattr(ctx, "tail_values_unused", False)),

@@ -18,3 +18,20 @@ def cuda():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     return torch.device("cuda:0")
+
+
+@pytest.fixture(autouse=True)
+def _kernel_checks(request):
+    """With BUX_KERNEL_CHECKS=1 every kernel output sits between guard regions; they are
+    verified after each GPU test."""
+    yield
+    if request.node.get_closest_marker("gpu") is None:
+        return
+    from bux_b200.ops import checks
+
+    if checks.enabled():
+        import torch
+
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        checks.verify()
