@@ -200,7 +200,8 @@ def test_pipeline_matches_one_rank(tmp_path, method):
 
 @pytest.mark.parametrize("method,heads", [("ulysses", "num_heads=4, num_kv_heads=2"),
                                           ("gathered", "num_heads=4, num_kv_heads=2"),
-                                          ("auto", "num_heads=2, num_kv_heads=1")])
+                                          ("auto", "num_heads=2, num_kv_heads=1"),
+                                          ("ring", "num_heads=4, num_kv_heads=2")])
 def test_context_parallel_matches_one_rank(tmp_path, method, heads):
     src = DENSE.replace("num_heads=2, num_kv_heads=1", heads)
     want_losses, want = _single(src)
@@ -271,3 +272,27 @@ def test_resume_on_a_sharded_mesh_matches_the_uninterrupted_run(tmp_path, world,
     got = torch.load(out)
     assert got["resumed"][:2] == pytest.approx(got["straight"][:2], abs=1e-6)
     assert got["resumed"][2:] == pytest.approx(got["straight"][2:], abs=1e-5)
+
+
+def test_blockwise_context_parallel_over_four_ranks(tmp_path):
+    """`ring` with four ranks: every rank works on two half-chunks of the zigzag placement."""
+    src = DENSE.replace("num_heads=2, num_kv_heads=1", "num_heads=4, num_kv_heads=2")
+    want_losses, want = _single(src)
+    got = _spawn(4, src, ["mesh = mesh(context=4)", "methods.attention = ring"], tmp_path)
+    assert got["losses"] == pytest.approx(want_losses, abs=1e-5)
+    for name, p in want.items():
+        assert torch.allclose(got["state"][name], p, atol=1e-5), name
+
+
+def test_merge_by_lse_equals_attention_over_the_union():
+    from bux_b200.ops import reference as ref
+    from bux_b200.parallel.context import merge_by_lse
+
+    torch.manual_seed(0)
+    q = torch.randn(2, 8, 4, 16)
+    k = torch.randn(2, 24, 2, 16)
+    v = torch.randn(2, 24, 2, 16)
+    want, want_lse = ref.attention(q, k, v, causal=False)
+    parts = [ref.attention(q, k[:, s:s + 8], v[:, s:s + 8], causal=False) for s in (0, 8, 16)]
+    got, lse = merge_by_lse([p[0] for p in parts], [p[1] for p in parts])
+    assert torch.allclose(got, want, atol=1e-5) and torch.allclose(lse, want_lse, atol=1e-5)
