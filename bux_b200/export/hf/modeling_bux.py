@@ -1,8 +1,16 @@
 """``BuxForCausalLM``: an exported bux model as a Hugging Face causal LM.
 
-The graph is rebuilt from ``config.bux`` (the architecture's IR) by the ``bux_b200``
-package, which must be importable; weights load from ``model.safetensors`` under the
-exported names (every projection on its own) and are fused back on load."""
+The folder is self-contained: beside this file the exporter writes ``bux_runtime/``, a copy
+of the framework's Python sources (the language's IR, the layer schemas, every layer in
+plain PyTorch, the weight-name mapping), so loading needs torch, transformers and
+safetensors only. Where the ``bux_b200`` package itself is installed it is used instead
+(its sm_100a kernels then run on a B200). The graph is rebuilt from ``config.bux`` (the
+architecture's IR); weights load from ``model.safetensors`` under the exported names (every
+projection on its own) and are fused back on load."""
+
+import importlib
+import sys
+from pathlib import Path
 
 import torch
 from transformers import PreTrainedModel
@@ -14,6 +22,23 @@ except ImportError:  # loaded as a loose file by trust_remote_code
     from configuration_bux import BuxConfig
 
 
+def runtime(folder=None):
+    """The package that builds the model: the installed ``bux_b200`` when there is one, else
+    the ``bux_runtime`` copy that sits in the exported folder (kernels off: plain PyTorch)."""
+    try:
+        return importlib.import_module("bux_b200")
+    except ImportError:
+        pass
+    for place in (folder, Path(__file__).resolve().parent):
+        if place is not None and (Path(place) / "bux_runtime" / "__init__.py").exists():
+            if str(place) not in sys.path:
+                sys.path.insert(0, str(place))
+            rt = importlib.import_module("bux_runtime")
+            importlib.import_module("bux_runtime.ops.functional").set_kernels(False)
+            return rt
+    raise ImportError("neither the bux_b200 package nor the exported folder's bux_runtime copy was found")
+
+
 class BuxForCausalLM(PreTrainedModel):
     config_class = BuxConfig
     base_model_prefix = "model"
@@ -21,25 +46,24 @@ class BuxForCausalLM(PreTrainedModel):
 
     def __init__(self, config: BuxConfig):
         super().__init__(config)
-        from bux_b200.lang import ir
-        from bux_b200.models import Model
-
+        rt = runtime(getattr(config, "_name_or_path", None) or None)
+        ir = importlib.import_module(rt.__name__ + ".lang.ir")
+        models = importlib.import_module(rt.__name__ + ".models")
         arch = ir.Architecture.model_validate(config.bux["architecture"])
         dtype = getattr(torch, str(config.bux.get("dtype", "float32")))
-        self.model = Model(arch, dtype=dtype)
+        self.model = models.Model(arch, dtype=dtype)
 
     def _init_weights(self, module):  # weights always come from the checkpoint
         pass
 
     @classmethod
     def from_pretrained(cls, path, *args, **kwargs):
-        from pathlib import Path
-
         from safetensors.torch import load_file
 
-        from bux_b200.export import weights as W
-
+        rt = runtime(path)
+        W = importlib.import_module(rt.__name__ + ".export.weights")
         config = BuxConfig.from_pretrained(path)
+        config._name_or_path = str(path)
         self = cls(config)
         exported = load_file(str(Path(path) / "model.safetensors"))
         exported = {k.removeprefix("model."): v for k, v in exported.items()}

@@ -60,6 +60,7 @@ def save(run, model, folder, dtype=torch.bfloat16, step=None, family: str = "aut
         }
         for name in ("configuration_bux.py", "modeling_bux.py"):
             shutil.copy(HERE / "hf" / name, folder / name)
+        vendor_runtime(folder)
     (folder / "config.json").write_text(json.dumps(config, indent=1))
     save_file({k: v.contiguous() for k, v in tensors.items()}, str(folder / "model.safetensors"),
               metadata={"format": "pt"})
@@ -67,11 +68,31 @@ def save(run, model, folder, dtype=torch.bfloat16, step=None, family: str = "aut
     return folder
 
 
+def vendor_runtime(folder: Path) -> Path:
+    """Copy this package's Python sources into ``<folder>/bux_runtime`` so that the exported
+    folder loads where the package is not installed (the reference copies its torch layers,
+    ``export/hf/*.py``, for the same reason: ``export/huggingface.py:40-170`` there). Only
+    ``.py`` files travel: no native sources, no built library, no studio assets."""
+    package = HERE.parent
+    target = Path(folder) / "bux_runtime"
+    if target.exists():
+        shutil.rmtree(target)
+    skip = {"csrc", "_ext", "studio", "__pycache__"}
+    for src in sorted(package.rglob("*.py")):
+        rel = src.relative_to(package)
+        if skip & set(rel.parts):
+            continue
+        dst = target / rel
+        dst.parent.mkdir(parents=True, exist_ok=True)
+        shutil.copy(src, dst)
+    return target
+
+
 def card(run, step, family) -> str:
     from ..lang.printer import run_to_source
 
     how = (f"a standard `{family}` checkpoint: any stack that serves that family loads it"
-           if family else "a `bux` checkpoint: load it with `trust_remote_code=True` (needs `bux_b200`), "
-                          "or serve it with the `bux_vllm_b200` plugin")
+           if family else "a `bux` checkpoint: load it with `trust_remote_code=True` (the folder carries the "
+                          "Python sources it needs), or serve it with the `bux_vllm_b200` plugin")
     return (f"# {run.name}\n\nExported from run `{run.id}`" + (f" at step {step}" if step is not None else "")
             + f". This folder is {how}.\n\n```bux\n{run_to_source(run)}\n```\n")

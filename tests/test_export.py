@@ -98,3 +98,38 @@ def test_less_common_attention_settings_round_trip(tmp_path, qk):
     assert report["ok"] and report["max_abs_error"] < 1e-4
     names = set(W.tensors(tr.model))
     assert ("k_eq_v" in qk) == (not any(n.endswith(".v.weight") for n in names))
+
+
+def test_exported_folder_loads_without_the_package(tmp_path):
+    """The exported folder carries the Python sources it needs: a process that cannot import
+    `bux_b200` loads it with transformers alone and computes the trained model's logits."""
+    import subprocess
+    import sys
+
+    run, tr, folder = _trained(tmp_path, qk=", sinks=true")
+    out = export(folder, tmp_path / "hf", dtype="float32", echo=lambda *_: None)
+    assert (out / "bux_runtime" / "models" / "model.py").exists()
+    assert not list((out / "bux_runtime").rglob("*.cu")) and not list((out / "bux_runtime").rglob("*.so"))
+    ids = torch.arange(12).reshape(1, 12) % 64
+    want = tr.model.logits(ids, training=False).float()
+    torch.save({"ids": ids, "want": want}, tmp_path / "probe.pt")
+    script = f"""
+import sys
+sys.path = [p for p in sys.path if p not in ('', {str(__import__('os').path.dirname(__import__('os').path.dirname(__import__('os').path.abspath(__file__))))!r})]
+try:
+    import bux_b200
+    raise SystemExit("bux_b200 is importable here: the test proves nothing")
+except ImportError:
+    pass
+import torch
+from transformers import AutoModelForCausalLM
+model = AutoModelForCausalLM.from_pretrained({str(out)!r}, trust_remote_code=True)
+probe = torch.load({str(tmp_path / 'probe.pt')!r})
+got = model(probe["ids"]).logits
+err = (got - probe["want"]).abs().max().item()
+print("max_abs_error", err)
+assert err < 1e-4, err
+"""
+    proc = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, cwd=str(tmp_path),
+                          env={k: v for k, v in __import__("os").environ.items() if k != "PYTHONPATH"})
+    assert proc.returncode == 0, proc.stdout + proc.stderr
