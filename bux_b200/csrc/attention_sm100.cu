@@ -101,7 +101,14 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
   const bool any0 = hi[0] > lo[0], any1 = hi[1] > lo[1];
   const int j_lo = any0 && any1 ? min(lo[0], lo[1]) : (any0 ? lo[0] : lo[1]);
   const int j_hi = max(hi[0], hi[1]);
-  const int n_tiles = (any0 || any1) ? j_hi - j_lo : 0;
+  // With documents the second query tile may start seeing keys after the first one's last
+  // key tile: the key tiles in between are seen by neither and are not loaded. Tiles that
+  // are loaded are numbered 0, 1, ... (`slot_of`) for the stage rings and their parities.
+  const int gap_at = (any0 && any1 && lo[1] > hi[0]) ? hi[0] : j_hi;
+  const int gap = (any0 && any1 && lo[1] > hi[0]) ? lo[1] - hi[0] : 0;
+  const int n_tiles = (any0 || any1) ? j_hi - j_lo - gap : 0;
+  auto slot_of = [&](int j) { return j - j_lo - (j >= gap_at ? gap : 0); };
+  auto tile_of = [&](int t) { return j_lo + t + (j_lo + t >= gap_at ? gap : 0); };
   Status* st = p.status;
 
   if (threadIdx.x == 0) {
@@ -127,7 +134,7 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
         for (int c = 0; c < DC; ++c)
           tma_load_2d(sQ + x * Cfg::TILE_BYTES + c * 16384, &p.tmap_q, h * D + c * 64, b * p.T + q0 + x * QT, q_full);
       for (int t = 0; t < n_tiles; ++t) {
-        const int row = b * p.S + (j_lo + t) * KT;
+        const int row = b * p.S + tile_of(t) * KT;
         const int ks = t & 1, vs = t % VS;
         if (!mbar_wait(&k_empty[ks], ((t >> 1) & 1) ^ 1, abort_flag, st, KID_ATTN_FWD, 1)) break;
         mbar_expect_tx(&k_full[ks], Cfg::TILE_BYTES);
@@ -149,7 +156,7 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
       int next_s[2] = {lo[0], lo[1]};  // next key tile whose S_x has not been issued
       // S_x(j) = Q_x · K_j^T ; frees K_j when x is its last user
       auto issue_s = [&](int x, int j) {
-        const int t = j - j_lo, ks = t & 1;
+        const int t = slot_of(j), ks = t & 1;
         if (!mbar_wait(&k_full[ks], (t >> 1) & 1, abort_flag, st, KID_ATTN_FWD, 3)) { ok = false; return; }
         tc_fence_after();
         const uint32_t a0 = smem_u32(sQ + x * Cfg::TILE_BYTES), b0 = smem_u32(sK + ks * Cfg::TILE_BYTES);
@@ -166,10 +173,16 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
       };
       ok = mbar_wait(q_full, 0, abort_flag, st, KID_ATTN_FWD, 4);
       int done[2] = {0, 0};  // tiles processed per query tile (for barrier parities)
+      // a query tile's first S is issued when the walk reaches its first key tile (at once for
+      // the tile that starts the walk): issuing it earlier would wait for a key tile that the
+      // two-stage ring cannot hold yet
       for (int x = 0; x < 2 && ok; ++x)
-        if (hi[x] > lo[x]) issue_s(x, lo[x]);
+        if (hi[x] > lo[x] && lo[x] == j_lo) issue_s(x, lo[x]);
       for (int j = j_lo; j < j_hi && ok; ++j) {
-        const int t = j - j_lo, vs = t % VS;
+        if (j >= gap_at && j < gap_at + gap) continue;
+        const int t = slot_of(j), vs = t % VS;
+        for (int x = 0; x < 2 && ok; ++x)
+          if (hi[x] > lo[x] && lo[x] == j && next_s[x] == j && j != j_lo) issue_s(x, j);
         for (int x = 0; x < 2 && ok; ++x) {
           if (!active(x, j)) continue;
           ok = mbar_wait(&p_ready[x], done[x] & 1, abort_flag, st, KID_ATTN_FWD, 5);

@@ -139,8 +139,13 @@ _wq_cache: dict = {}
 
 
 def _quant_weight(w: torch.Tensor):
-    """(rowwise q, sf, colwise q, sf) of a weight, cached until the weight changes."""
+    """(rowwise q, sf, colwise q, sf) of a weight. A parameter's copies are cached until the
+    optimizer changes it (forward, replay and backward of a step share them); a temporary
+    tensor (a weight gathered from shards for one block) is quantised each time: caching it
+    would keep a copy of every gathered weight alive."""
     K = _K()
+    if not isinstance(w, torch.nn.Parameter):
+        return K.quant_mxfp8(w.detach().reshape(-1, w.shape[-1]), rowwise=True, colwise=True)
     key = (w.data_ptr(), tuple(w.shape))
     hit = _wq_cache.get(key)
     if hit is not None and hit[0] == w._version:
@@ -276,6 +281,10 @@ def linear_f32(x, w, bias=None):
 def linear(x, w, bias=None, fmt: str = "bf16"):
     """x [..., in] times w [out, in]^T (+ bias). `fmt`: "bf16" (compute dtype) or "mxfp8"."""
     k, n = x.shape[-1], w.shape[0]
+    if fmt == "nvfp4" and k % 16 == 0 and n % 16 == 0:
+        from . import nvfp4
+
+        return nvfp4.linear(x, w, bias)
     if kernels_on(x) and w.dtype == torch.bfloat16 and k % 8 == 0 and n % 8 == 0:
         if fmt in ("mxfp8", "mxfp8_2d") and k % 128 == 0 and n % 128 == 0:
             y = _LinearMX.apply(x, w)
