@@ -171,6 +171,19 @@ void quant_mxfp8_glu(const Tensor& h, const c10::optional<Tensor>& dout, const c
                        (float)limit, (float)up_offset, stream_of(h));
 }
 
+void quant_nvfp4(const Tensor& x, const Tensor& tensor_scale, Tensor& packed, Tensor& scales) {
+  check_cuda(x, "x");
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.is_contiguous() && x.dim() == 2 && x.size(1) % 16 == 0,
+              "quant_nvfp4: contiguous bf16 [rows, cols], cols % 16 == 0");
+  TORCH_CHECK(tensor_scale.is_cuda() && tensor_scale.scalar_type() == at::kFloat && tensor_scale.numel() == 1,
+              "quant_nvfp4: the tensor scale is one fp32 value on the device");
+  TORCH_CHECK(packed.numel() == x.numel() / 2 && scales.numel() == x.numel() / 16 && packed.element_size() == 1 &&
+              scales.element_size() == 1, "quant_nvfp4: packed [rows, cols/2] and scales [rows, cols/16] bytes");
+  c10::cuda::CUDAGuard guard(x.device());
+  bux::quant_nvfp4(x.data_ptr(), tensor_scale.data_ptr<float>(), reinterpret_cast<uint8_t*>(packed.data_ptr()),
+                   reinterpret_cast<uint8_t*>(scales.data_ptr()), x.size(0), (int)x.size(1), stream_of(x));
+}
+
 // ------------------------------------------------------------------ loss / optimiser / MoE rows
 void ce_fwd_bwd(Tensor& logits, const Tensor& targets, const c10::optional<Tensor>& mask, Tensor& loss,
                 const c10::optional<Tensor>& logz, double grad_scale, double z_weight, double softcap) {
@@ -405,6 +418,7 @@ TORCH_LIBRARY(bux_b200, m) {
   m.def("glu_bwd(Tensor h, Tensor dout, Tensor(a!) dh, Tensor? row_scale, Tensor? d_row_scale, int kind, float limit, float up_offset) -> ()", &glu_bwd);
   m.def("quant_mxfp8(Tensor x, Tensor? row_index, Tensor? row_scale, Tensor? q_row, Tensor? sf_row, Tensor? q_col, Tensor? sf_col, int rows, int cols, int ld_col, int batch, int x_batch_stride) -> ()", &quant_mxfp8);
   m.def("quant_mxfp8_glu(Tensor h, Tensor? dout, Tensor? row_scale, Tensor? q_row, Tensor? sf_row, Tensor? q_col, Tensor? sf_col, int ld_col, int kind, float limit, float up_offset) -> ()", &quant_mxfp8_glu);
+  m.def("quant_nvfp4(Tensor x, Tensor tensor_scale, Tensor(a!) packed, Tensor(b!) scales) -> ()", &quant_nvfp4);
   m.def("ce_fwd_bwd(Tensor(a!) logits, Tensor targets, Tensor? mask, Tensor(b!) loss, Tensor? logz, float grad_scale, float z_weight, float softcap) -> ()", &ce_fwd_bwd);
   m.def("adamw(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor? m_sf, Tensor? v_sf, Tensor? shadow, Tensor? grad_scale, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2, float grad_scale_const) -> ()", &adamw);
   m.def("sumsq(Tensor g, Tensor(a!) out) -> ()", &sumsq);

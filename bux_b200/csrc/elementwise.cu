@@ -10,6 +10,8 @@
 #include "common.cuh"
 #include "elementwise.h"
 
+#include <cuda_fp4.h>
+
 namespace bux {
 
 // ---------------------------------------------------------------- RMSNorm
@@ -704,6 +706,44 @@ quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, long ld_x,
   }
 }
 
+// ---------------------------------------------------------------- NVFP4 quantiser
+// x [rows, cols] bf16 -> E2M1 codes, two per byte (low nibble first), in blocks of 16 along a
+// row with one E4M3 scale each, under one fp32 scale for the tensor (*tensor_scale =
+// amax / (6 * 448), taken by the caller's reduction). One thread per block: two 16-byte loads,
+// the block's largest magnitude, its scale rounded to E4M3, sixteen values rounded to nearest
+// by the hardware's E2M1 conversion, one 8-byte store.
+__global__ void quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ tensor_scale,
+                                   uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, long blocks) {
+  const float ts = *tensor_scale;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < blocks; i += (long)gridDim.x * blockDim.x) {
+    const uint4 a = *reinterpret_cast<const uint4*>(x + i * 16);
+    const uint4 b = *reinterpret_cast<const uint4*>(x + i * 16 + 8);
+    float v[16];
+    const uint32_t* au = &a.x; const uint32_t* bu = &b.x;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float2 f = unpack_bf16(au[q]), g = unpack_bf16(bu[q]);
+      v[2 * q] = f.x; v[2 * q + 1] = f.y; v[8 + 2 * q] = g.x; v[8 + 2 * q + 1] = g.y;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int q = 0; q < 16; ++q) amax = fmaxf(amax, fabsf(v[q]));
+    const __nv_fp8_storage_t sbyte = __nv_cvt_float_to_fp8(fminf(__fdiv_rn(amax, 6.f * ts), 448.f), __NV_SATFINITE, __NV_E4M3);
+    const float scale = __half2float(__half(__nv_cvt_fp8_to_halfraw(sbyte, __NV_E4M3)));
+    const float denom = scale * ts;
+    uint32_t w[2] = {0u, 0u};
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const float lo = denom > 0.f ? __fdiv_rn(v[2 * q], denom) : 0.f;
+      const float hi = denom > 0.f ? __fdiv_rn(v[2 * q + 1], denom) : 0.f;
+      const uint32_t byte = (uint32_t)__nv_cvt_float2_to_fp4x2(make_float2(lo, hi), __NV_E2M1, cudaRoundNearest);
+      w[q >> 2] |= (byte & 0xffu) << (8 * (q & 3));
+    }
+    *reinterpret_cast<uint2*>(packed + i * 8) = make_uint2(w[0], w[1]);
+    scales[i] = sbyte;
+  }
+}
+
 // ---------------------------------------------------------------- cross-entropy
 // One block per row of a logits chunk [rows, vocab] (bf16). Writes per-row loss and
 // logZ (fp32) and overwrites the logits with dlogits = (softmax - onehot) * grad_scale
@@ -1147,6 +1187,11 @@ void quant_mxfp8_glu(const void* h, const void* dout, const float* row_scale, ui
   QuantGlu gp{dout ? nullptr : row_scale, (const __nv_bfloat16*)dout, f, kind, limit, up_offset, nullptr};
   if (dout) quant_mxfp8_kernel<QSRC_GLU_BWD><<<grid, 256, 0, s>>>((const __nv_bfloat16*)h, 2L * f, nullptr, q_row, sf_row, q_col, sf_col, rows, cols, ld_col, 0, gp);
   else quant_mxfp8_kernel<QSRC_GLU_FWD><<<grid, 256, 0, s>>>((const __nv_bfloat16*)h, 2L * f, nullptr, q_row, sf_row, q_col, sf_col, rows, cols, ld_col, 0, gp);
+}
+void quant_nvfp4(const void* x, const float* tensor_scale, uint8_t* packed, uint8_t* scales, long rows, int cols,
+                 cudaStream_t s) {
+  const long blocks = rows * (cols / 16);
+  quant_nvfp4_kernel<<<grid_for(blocks, 256), 256, 0, s>>>((const __nv_bfloat16*)x, tensor_scale, packed, scales, blocks);
 }
 void ce_fwd_bwd(void* logits, const int* targets, const float* mask, float* loss, float* logz, long rows, int vocab, long ld, float grad_scale, float z_weight, float softcap, cudaStream_t s) {
   ce_fwd_bwd_kernel<<<(unsigned)rows, 512, 0, s>>>((__nv_bfloat16*)logits, targets, mask, loss, logz, vocab, ld, grad_scale, z_weight, softcap);

@@ -27,6 +27,9 @@ void quant_mxfp8_glu(const void* h, const void* dout, const float* row_scale, ui
 // already MXFP8 along its columns (e4m3 bytes [rows, cols] + scale tiles): dequantise, requantise.
 void requant_mxfp8_cols(const uint8_t* q, const uint8_t* sf, uint8_t* q_col, uint8_t* sf_col, long rows, int cols,
                         long ld_col, cudaStream_t s);
+// NVFP4 along the rows: E2M1 codes two per byte [rows, cols / 2], E4M3 scale bytes [rows, cols / 16]
+void quant_nvfp4(const void* x, const float* tensor_scale, uint8_t* packed, uint8_t* scales, long rows, int cols,
+                 cudaStream_t s);
 void ce_fwd_bwd(void* logits, const int* targets, const float* mask, float* loss, float* logz, long rows, int vocab, long ld, float grad_scale, float z_weight, float softcap, cudaStream_t s);
 const char* adamw(void* p, bool p_bf16, const void* g, bool g_bf16, void* m, void* v, uint8_t* m_sf, uint8_t* v_sf, int mom,
                   void* shadow, long n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,

@@ -275,6 +275,13 @@ class _Remat(torch.autograd.Function):
                 outs.append(o)
                 grads.append(g)
         torch.autograd.backward(outs, grads)
+        # The forward's context reaches this node (context -> heads -> hidden states -> their
+        # graph -> this node) and this node reached the context through the holder: a cycle
+        # through autograd's C++ edges, which Python's collector cannot see. Cut it here, or
+        # every step's context (its hidden states, tables, positions) stays alive for good.
+        fctx.holder = None
+        holder.ctx = holder.block = None
+        holder.taps = holder.ports = None
         return x.grad, None
 
 

@@ -216,6 +216,19 @@ def quant_mxfp8_glu(h: torch.Tensor, dout: Optional[torch.Tensor] = None, kind: 
     return q_row, sf_row, q_col, sf_col
 
 
+def quant_nvfp4(x: torch.Tensor):
+    """NVFP4 of bf16 x [R, C] along its rows (1 x 16 blocks, to nearest): (packed uint8 [R, C/2],
+    two E2M1 codes per byte with the lower column in the low nibble; E4M3 scale bytes [R, C/16];
+    the fp32 tensor scale). Bit-equal to `nvfp4.pack(nvfp4.quantize(x))`."""
+    r, c = x.shape
+    tensor_scale = (x.abs().max().float().clamp_min(1e-30) / (6.0 * 448.0)).reshape(1)
+    packed = _out(r, c // 2, dtype=torch.uint8, device=x.device, op="quant_nvfp4 packed")
+    scales = _out(r, c // 16, dtype=torch.uint8, device=x.device, op="quant_nvfp4 scales")
+    ops().quant_nvfp4(x.contiguous(), tensor_scale, packed, scales)
+    _count()
+    return packed, scales, tensor_scale
+
+
 # ------------------------------------------------------------------ norms / rope / glu
 def rmsnorm_fwd(x, w, eps: float):
     y = _out(x.shape, dtype=x.dtype, device=x.device, op="rmsnorm_fwd y")

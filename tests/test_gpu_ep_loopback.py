@@ -90,6 +90,6 @@ def test_fused_exchange_on_one_gpu_matches_sorted_experts(cuda, tmp_path):
     mp.spawn(_worker, args=(_free_port(), out), nprocs=1, join=True)
     results = torch.load(out)
     for (fmt, what), errs in results.items():
-        tol = 6e-2 if fmt == "mxfp8" else 2e-2
+        tol = 1e-1 if fmt == "mxfp8" else 2e-2
         # out, dx, d weights, dW_gate_up, dW_down
         assert all(e < tol for e in errs), (fmt, what, errs)

@@ -365,3 +365,20 @@ def test_topk_rows_matches_torch(n, k):
     assert torch.equal(got, want.indices)                      # distinct random values: same indices
     ties = torch.zeros(4, n, device="cuda")
     assert torch.equal(K.topk_rows(ties, k), torch.arange(k, device="cuda").expand(4, k))
+
+
+def test_nvfp4_quantiser_matches_the_recipe(cuda):
+    """The CUDA quantiser (hardware E2M1 conversion) writes the bytes the PyTorch statement
+    of the recipe packs."""
+    from bux_b200.ops import kernels as K
+    from bux_b200.ops import nvfp4 as N
+
+    torch.manual_seed(21)
+    x = (torch.randn(300, 512, device=cuda) * torch.logspace(-2, 2, 512, device=cuda)).bfloat16()
+    packed, scales, ts = K.quant_nvfp4(x)
+    want = N.quantize(x.float())
+    wp, ws = N.pack(want)
+    assert torch.allclose(ts, want.tensor_scale.reshape(1))
+    assert torch.equal(scales, ws)
+    mism = (packed != wp).float().mean().item()
+    assert mism < 1e-3, mism   # ties at a grid midpoint may round differently after the division

@@ -49,6 +49,8 @@ def test_pack_two_codes_per_byte():
 
 
 def test_a_model_trains_with_nvfp4_matmuls():
+    """A few steps with every matmul in NVFP4 stay close to the same steps in fp32, and the
+    first step's gradients point the same way."""
     from bux_b200.train.trainer import Trainer
 
     src = """
@@ -62,11 +64,20 @@ data = synthetic
 optimizer = adamw(lr=3e-3)
 seq_len = 32
 batch = 8
-steps = 30
-precision = precision(compute=float32, matmuls=nvfp4)
+steps = 6
+precision = precision(compute=float32, matmuls={fmt})
 """
-    run = compile_runs(src, filename="n.bux")[0]
-    tr = Trainer(run, device="cpu")
-    feed = iter(tr.batches())
-    losses = [tr.train_step(next(feed))["loss"].item() for _ in range(30)]
-    assert losses[-1] < losses[0] - 0.05 and all(l == l for l in losses)
+    runs = {fmt: compile_runs(src.format(fmt=fmt), filename="n.bux")[0] for fmt in ("compute", "nvfp4")}
+    losses, grads = {}, {}
+    for fmt, run in runs.items():
+        tr = Trainer(run, device="cpu")
+        feed = iter(tr.batches())
+        batch = next(feed)
+        loss, _ = tr.forward_loss(tr.to_device(batch), torch.tensor(1.0 / (8 * 31)), 1, 1)
+        loss.backward()
+        grads[fmt] = torch.cat([p.grad.reshape(-1) for p in tr.model.parameters() if p.grad is not None])
+        tr.model.zero_grad()
+        losses[fmt] = [tr.train_step(b)["loss"].item() for b, _ in zip(feed, range(5))]
+    assert all(abs(a - b) < 0.05 for a, b in zip(losses["nvfp4"], losses["compute"]))
+    cos = torch.nn.functional.cosine_similarity(grads["nvfp4"], grads["compute"], dim=0).item()
+    assert cos > 0.9, cos
