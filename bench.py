@@ -29,7 +29,7 @@ sys.path.insert(0, str(ROOT))
 # step's large transients and the tensors kept across the step)
 os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
 
-MARGIN_BYTES = 20 << 30  # device memory left free when attention outputs are kept (fragmentation, chunk buffers)
+MARGIN_BYTES = 12 << 30  # device memory left free when attention outputs are kept (fragmentation, chunk buffers)
 PUBLISHED_TOK_S_PER_GPU = 42391.0  # reference, 8xB300, MXFP8 `sorted` fsdp=8 (docs/performance/benchmarks.md:188)
 ROWS_PER_GPU = 32                  # 256 rows of 4096 over 8 GPUs
 
