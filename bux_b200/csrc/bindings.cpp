@@ -47,7 +47,7 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& c, const c10::optional<Tenso
           const c10::optional<Tensor>& status, int64_t kind, int64_t mode, int64_t M, int64_t N,
           int64_t K, int64_t k_total, int64_t groups, bool a_mn, bool b_mn, int64_t out_kind,
           int64_t bn, int64_t sms, const c10::optional<Tensor>& wait_flags, int64_t wait_epoch,
-          int64_t wait_rows, int64_t m_rotate, bool wait_on_k) {
+          int64_t wait_rows, int64_t m_rotate, bool wait_on_k, bool wait_on_n) {
   check_cuda(a, "a"); check_cuda(b, "b"); check_cuda(c, "c");
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "a and b are 2-D views");
   c10::cuda::CUDAGuard guard(a.device());
@@ -72,7 +72,7 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& c, const c10::optional<Tenso
   g.sms = (int)sms;
   if (wait_flags.has_value()) {
     g.wait_flags = opt_i32(wait_flags); g.wait_world = (int)wait_flags->numel(); g.wait_epoch = (int)wait_epoch;
-    g.wait_rows = (int)wait_rows; g.wait_on_k = wait_on_k;
+    g.wait_rows = (int)wait_rows; g.wait_on_k = wait_on_k; g.wait_on_n = wait_on_n;
   }
   g.m_rotate = (int)m_rotate;
   const char* err = bux::gemm_launch(g, stream_of(a));
@@ -410,7 +410,7 @@ TORCH_LIBRARY(bux_b200, m) {
   m.def("ep_wait(Tensor flags, int epoch, Tensor? status, float limit_s) -> ()", &ep_wait);
   m.def("tp_push_block(Tensor src, Tensor peer_base, int my_rank, int sms) -> ()", &tp_push_block);
   m.def("tp_pull_reduce(Tensor peer_base, int my_rank, Tensor(a!) out, Tensor? residual, Tensor? flags, int epoch, Tensor? status, float limit_s) -> ()", &tp_pull_reduce);
-  m.def("gemm(Tensor a, Tensor b, Tensor(a!) c, Tensor? sfa, Tensor? sfb, Tensor? group_offsets, Tensor? status, int kind, int mode, int M, int N, int K, int k_total, int groups, bool a_mn, bool b_mn, int out_kind, int bn, int sms, Tensor? wait_flags=None, int wait_epoch=0, int wait_rows=0, int m_rotate=0, bool wait_on_k=False) -> ()", &gemm);
+  m.def("gemm(Tensor a, Tensor b, Tensor(a!) c, Tensor? sfa, Tensor? sfb, Tensor? group_offsets, Tensor? status, int kind, int mode, int M, int N, int K, int k_total, int groups, bool a_mn, bool b_mn, int out_kind, int bn, int sms, Tensor? wait_flags=None, int wait_epoch=0, int wait_rows=0, int m_rotate=0, bool wait_on_k=False, bool wait_on_n=False) -> ()", &gemm);
   m.def("rmsnorm_fwd(Tensor x, Tensor? w, Tensor(a!) y, Tensor(b!) rstd, float eps) -> ()", &rmsnorm_fwd);
   m.def("rmsnorm_bwd(Tensor x, Tensor? w, Tensor dy, Tensor rstd, Tensor(a!) dx, Tensor? dw) -> ()", &rmsnorm_bwd);
   m.def("norm_rope(bool bwd, Tensor x, Tensor? w, Tensor cos, Tensor sin, Tensor(a!) y, Tensor? rstd, Tensor? dy, Tensor? dw, int tokens, int heads, int D, int stride_x, int stride_y, float eps) -> ()", &norm_rope);

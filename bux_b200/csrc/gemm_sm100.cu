@@ -203,12 +203,15 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
         const int b_row0 = (p.mode == MODE_GROUPED_ROWS ? c.group * p.N : 0) + c.n0;
         // MN-major B of a grouped-rows GEMM is stored [groups * K, N]
         const int b_k_off = (B_MN && p.mode == MODE_GROUPED_ROWS) ? c.group * p.K : 0;
-        if (p.wait_flags != nullptr && p.wait_rows > 0 && !p.wait_on_k) {
+        if (p.wait_flags != nullptr && p.wait_rows > 0 && p.wait_on_n) {
+          // operand B's rows (output columns) arrive sender by sender: a weight gathered from its shards
+          if (!wait_sender(c.n0 / p.wait_rows) || !wait_sender((min(c.n0 + BN, p.N) - 1) / p.wait_rows)) { ok = false; break; }
+        } else if (p.wait_flags != nullptr && p.wait_rows > 0 && !p.wait_on_k) {
           // a tile may straddle two senders' row blocks
           if (!wait_sender(c.m0 / p.wait_rows) || !wait_sender((min(c.m0 + BM, p.M) - 1) / p.wait_rows)) { ok = false; break; }
         }
         for (int k = c.k0; k < c.k1; k += Cfg::BK_ELEMS) {
-          if (p.wait_flags != nullptr && p.wait_rows > 0 && p.wait_on_k) {
+          if (p.wait_flags != nullptr && p.wait_rows > 0 && p.wait_on_k && !p.wait_on_n) {
             if (!wait_sender(k / p.wait_rows) || !wait_sender((min(k + Cfg::BK_ELEMS, c.k1) - 1) / p.wait_rows)) { ok = false; break; }
           }
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, st, KID_GEMM, 1)) { ok = false; break; }
@@ -515,7 +518,7 @@ const char* gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   p.c = a.c; p.ldc = a.ldc; p.out_kind = a.out_kind;
   p.sfa = a.sfa; p.sfb = a.sfb; p.status = a.status;
   p.wait_flags = a.wait_flags; p.wait_world = a.wait_world; p.wait_epoch = a.wait_epoch; p.wait_limit_ns = a.wait_limit_ns;
-  p.wait_rows = a.wait_rows; p.m_rotate = a.m_rotate; p.wait_on_k = a.wait_on_k ? 1 : 0;
+  p.wait_rows = a.wait_rows; p.m_rotate = a.m_rotate; p.wait_on_k = a.wait_on_k ? 1 : 0; p.wait_on_n = a.wait_on_n ? 1 : 0;
   if (a.wait_world > 32) return "at most 32 senders can be waited for";
   const int elem = a.kind == KIND_BF16 ? 2 : 1;
   const int bk = a.kind == KIND_BF16 ? 64 : 128;

@@ -27,7 +27,7 @@ struct GemmParams {
   // wait_flags[0..wait_world) >= wait_epoch: senders on peer GPUs filled operand A
   const int* wait_flags; int wait_world, wait_epoch; unsigned long long wait_limit_ns;
   // wait_rows > 0: per-sender row blocks (see GemmArgs); m_rotate in tiles
-  int wait_rows, m_rotate, wait_on_k;
+  int wait_rows, m_rotate, wait_on_k, wait_on_n;
   int tma_store;  // the epilogue stages bf16 tiles in shared memory and stores them by TMA
 };
 
@@ -51,6 +51,7 @@ struct GemmArgs {
   // the sender of its rows. m_rotate (dense mode, in tiles) starts the walk at this
   // rank's own rows, which need no wait.
   int wait_rows = 0, m_rotate = 0; bool wait_on_k = false;
+  bool wait_on_n = false;  // the senders write row blocks of B (sharded weights arriving from their owners)
 };
 
 // Returns nullptr on success, else a static message.

@@ -161,12 +161,19 @@ def clear_weight_cache() -> None:
 
 class _LinearBF16(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w):
+    def forward(ctx, x, w, arrival):
         K = _K()
         x2 = x.reshape(-1, x.shape[-1]).contiguous()
         ctx.save_for_backward(x2, w)
         ctx.shape = x.shape
-        return K.gemm_bf16(x2, w).view(*x.shape[:-1], w.shape[0])
+        if arrival is not None:
+            # w's rows are arriving from the ranks that own them (a sharded weight): the GEMM's
+            # producer warp waits, per tile of output columns, for the owner's flag
+            flags, epoch, rows = arrival
+            y = K.gemm_bf16(x2, w, wait_flags=flags, wait_epoch=epoch, wait_rows=rows, wait_on_n=True)
+        else:
+            y = K.gemm_bf16(x2, w)
+        return y.view(*x.shape[:-1], w.shape[0])
 
     @staticmethod
     def backward(ctx, dy):
@@ -183,7 +190,7 @@ class _LinearBF16(torch.autograd.Function):
                 dw = None
             else:
                 dw = K.gemm_bf16(dy2, x2, a_mn=True, b_mn=True)
-        return dx, dw
+        return dx, dw, None
 
 
 class _LinearMX(torch.autograd.Function):
@@ -289,7 +296,7 @@ def linear(x, w, bias=None, fmt: str = "bf16"):
         if fmt in ("mxfp8", "mxfp8_2d") and k % 128 == 0 and n % 128 == 0:
             y = _LinearMX.apply(x, w)
         else:
-            y = _LinearBF16.apply(x, w)
+            y = _LinearBF16.apply(x, w, getattr(w, "_bux_arrival", None))
         return y if bias is None else y + bias.to(y.dtype)
     if fmt in ("mxfp8", "mxfp8_2d") and k % 32 == 0 and not x.is_cuda:
         return ref_linear_mxfp8(x, w, bias)

@@ -61,10 +61,11 @@ def check_status(device, what: str = "kernel") -> None:
 def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
               out: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16,
               accumulate: bool = False, bn: int = 256, sms: int = 0, wait_flags=None, wait_epoch: int = 0,
-              wait_rows: int = 0, m_rotate: int = 0, wait_on_k: bool = False) -> torch.Tensor:
+              wait_rows: int = 0, m_rotate: int = 0, wait_on_k: bool = False, wait_on_n: bool = False) -> torch.Tensor:
     """C = A · B^T. A is [M,K] (or stored [K,M] with a_mn), B is [N,K] (or [K,N] with b_mn).
     With `wait_flags` (int32[senders]) an operand is being written by peer GPUs in blocks
-    of `wait_rows` rows per sender (rows of A, or of the contraction with `wait_on_k`):
+    of `wait_rows` rows per sender (rows of A, of the contraction with `wait_on_k`, or rows of B
+    with `wait_on_n`: a weight whose shards arrive from their owners):
     a tile's loads wait for its sender's flag to reach `wait_epoch`; `m_rotate` (tiles)
     starts the walk at this rank's own rows."""
     m, k = (a.shape[1], a.shape[0]) if a_mn else a.shape
@@ -73,7 +74,7 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: boo
         out = _out(m, n, dtype=out_dtype, device=a.device, op="gemm_bf16")
     kind = OUT_BF16 if out.dtype == torch.bfloat16 else (OUT_F32_ACC if accumulate else OUT_F32)
     ops().gemm(a, b, out, None, None, None, status_word(a.device), KIND_BF16, MODE_DENSE, m, n, k, k, 1,
-               a_mn, b_mn, kind, bn, sms, wait_flags, wait_epoch, wait_rows, m_rotate, wait_on_k)
+               a_mn, b_mn, kind, bn, sms, wait_flags, wait_epoch, wait_rows, m_rotate, wait_on_k, wait_on_n)
     _count()
     return out
 
