@@ -34,8 +34,21 @@ class CausalDepthwise(nn.Module):
             pos = ctx.positions
         w = self.weight.to(x.dtype)
         y = x * w[:, 0]
-        for j in range(1, min(w.shape[1], t)):
-            shifted = nn.functional.pad(x[:, : t - j], (0, 0, j, 0))
+        taps = w.shape[1]
+        cp = getattr(ctx.parallel, "context_group", None) if ctx is not None and getattr(ctx, "parallel", None) else None
+        before = None
+        if cp is not None and taps > 1:
+            # positions split over ranks: the taps before this rank's first position read the
+            # last positions of the rank before it
+            from ...parallel import recurrence
+
+            before = recurrence.halo(x, min(taps - 1, t), cp)
+        for j in range(1, min(taps, t + (before.shape[1] if before is not None else 0))):
+            if before is not None:
+                joined = torch.cat([before, x], dim=1)
+                shifted = joined[:, before.shape[1] - j: before.shape[1] - j + t]
+            else:
+                shifted = nn.functional.pad(x[:, : t - j], (0, 0, j, 0))
             if pos is not None:
                 shifted = shifted * (pos >= j).unsqueeze(-1).to(x.dtype)
             y = y + shifted * w[:, j]

@@ -55,10 +55,16 @@ def _pair(x, y, gx, gy, strict: bool):
     return torch.stack(out, 2)
 
 
-def scan(q, k, v, g, a=None, b=None, starts: Optional[torch.Tensor] = None, state=None):
+def scan(q, k, v, g, a=None, b=None, starts: Optional[torch.Tensor] = None, state=None, group=None):
     """The recurrence above from `state` (zero if None). q, k, a, b: [B, T, H, dk];
     v: [B, T, H, dv]; g = log w: [B, T, H, dk] or [B, T, H, 1] (<= 0); starts: bool [B, T],
-    true where a document begins. Returns (o [B, T, H, dv] in v's dtype, last state fp32)."""
+    true where a document begins. With `group` the positions are split over its ranks
+    (context parallelism) and the state is handed on between them. Returns (o [B, T, H, dv]
+    in v's dtype, last state fp32)."""
+    if group is not None:
+        from ...parallel import recurrence
+
+        return recurrence.pass_state(scan, q, k, v, g, a, b, starts, group)
     bsz, t, h, dk = k.shape
     dv = v.shape[-1]
     if starts is not None:
@@ -123,11 +129,11 @@ def scan_steps(q, k, v, g, a=None, b=None, starts=None, state=None):
     return torch.stack(outs, 1).to(v.dtype), S
 
 
-def delta_rule(q, k, v, g, beta, starts=None, state=None):
+def delta_rule(q, k, v, g, beta, starts=None, state=None, group=None):
     """S_t = (I - beta k k^T) diag(w) S_{t-1} + beta k v^T, as the rank-one recurrence with
     a = -w k, b = beta k, written key beta k."""
     step = beta.float().unsqueeze(-1) * k.float()
-    return scan(q, step, v, g, -g.float().exp() * k.float(), step, starts, state)
+    return scan(q, step, v, g, -g.float().exp() * k.float(), step, starts, state, group)
 
 
 def l2norm(x, eps: float = 1e-6):
@@ -139,8 +145,14 @@ def _starts(ctx: Context):
     if getattr(ctx, "segments", None) is None:
         return None
     s = ctx.positions == 0
-    s[:, 0] = False  # the row's first position starts from the zero state anyway
+    if _cp(ctx) is None:
+        s[:, 0] = False  # the row's first position starts from the zero state anyway
     return s
+
+
+def _cp(ctx: Context):
+    """The process group the row's positions are split over, or None."""
+    return getattr(ctx.parallel, "context_group", None) if getattr(ctx, "parallel", None) is not None else None
 
 
 # ------------------------------------------------------------------ pieces
@@ -238,7 +250,7 @@ class DeltaNet(LinearAttention):
     def mix(self, x, q, k, v, ctx):
         q, k = l2norm(q) * self.dk ** -0.5, l2norm(k)
         beta = torch.sigmoid(self.b(x, ctx).float())
-        return delta_rule(q, k, v, self.log_decay(x, ctx), beta, _starts(ctx))[0]
+        return delta_rule(q, k, v, self.log_decay(x, ctx), beta, _starts(ctx), group=_cp(ctx))[0]
 
 
 class GatedDeltaNet(DeltaNet):
@@ -304,7 +316,7 @@ class GatedDeltaNet2(LinearAttention):
         erase = erase.repeat_interleave(group, 2)
         write = torch.sigmoid(self.write(x, ctx).float()).reshape(bsz, t, self.hv, -1)
         a = -g.exp() * erase * k.float()
-        return scan(q, k, write * v.float(), g, a, k.float(), _starts(ctx))[0].to(v.dtype)
+        return scan(q, k, write * v.float(), g, a, k.float(), _starts(ctx), group=_cp(ctx))[0].to(v.dtype)
 
 
 class GLA(LinearAttention):
@@ -316,7 +328,7 @@ class GLA(LinearAttention):
 
     def mix(self, x, q, k, v, ctx):
         g = F.logsigmoid(self.f(x).reshape(*k.shape)) / 16
-        return scan(q * self.dk ** -0.5, k, v, g, starts=_starts(ctx))[0]
+        return scan(q * self.dk ** -0.5, k, v, g, starts=_starts(ctx), group=_cp(ctx))[0]
 
 
 def slopes(heads: int, layer: int, layers: int) -> torch.Tensor:
@@ -334,7 +346,7 @@ class Lightning(LinearAttention):
 
     def mix(self, x, q, k, v, ctx):
         g = (-self.slopes.float()[:, None]).expand(*q.shape[:3], 1)
-        return scan(q, k, v, g, starts=_starts(ctx))[0]
+        return scan(q, k, v, g, starts=_starts(ctx), group=_cp(ctx))[0]
 
 
 class RWKV7(nn.Module):
@@ -375,6 +387,10 @@ class RWKV7(nn.Module):
         bsz, t, _ = x.shape
         h, hv, dk, dv = self.h, self.hv, self.dk, self.dv
         prev = F.pad(x[:, :-1], (0, 0, 1, 0))
+        if _cp(ctx) is not None:  # the token before this rank's first one lives on the rank before
+            from ...parallel import recurrence
+
+            prev = torch.cat([recurrence.halo(x, 1, _cp(ctx)), x[:, :-1]], dim=1)
         st = _starts(ctx)
         if st is not None:
             prev = prev * (~st).unsqueeze(-1).to(x.dtype)
@@ -399,7 +415,7 @@ class RWKV7(nn.Module):
 
         r, k, log_w, a, kk = map(split, (r, k, log_w, a, kk))
         kk = l2norm(kk, eps=1e-12)
-        o, _ = scan(r, k, v, log_w, -kk, kk * a, st)
+        o, _ = scan(r, k, v, log_w, -kk, kk * a, st, group=_cp(ctx))
         o = F.layer_norm(o.float(), (dv,), eps=self.eps) * self.norm_scale.float() + self.norm_bias.float()
         o = o + (r * k * self.r_k.float()).sum(-1, keepdim=True) * v.float()
         o = o.reshape(bsz, t, -1)
@@ -449,6 +465,9 @@ class Mamba(nn.Module):
         u = F.silu(self.conv(u, ctx))
         dt, B, C = self.x_proj(u, ctx).split([self.rank, self.n, self.n], -1)
         dt = F.softplus(self.dt_norm(dt, ctx).float() @ self.dt_proj.float() + self.dt_bias.float())
+        if _cp(ctx) is not None:
+            raise NotImplementedError("mamba: a state per channel and position is not handed on between ranks; "
+                                      "use mamba2 (or another mixer of the family) under mesh(context=...)")
         y = mamba_scan(u, dt, -self.A_log.float().exp(), self.b_norm(B, ctx), self.c_norm(C, ctx), _starts(ctx))
         y = (y.float() + u.float() * self.D.float()) * F.silu(z.float())
         return self.out_proj(y.to(x.dtype), ctx)
@@ -482,7 +501,7 @@ class Mamba2(nn.Module):
         B, C = (y.reshape(bsz, t, g, n).repeat_interleave(h // g, 2) for y in (B, C))
         dt = F.softplus(dt.float() + self.dt_bias.float())
         A = -self.A_log.float().exp()
-        y, _ = scan(C, B, dt.unsqueeze(-1) * u.float(), (dt * A).unsqueeze(-1), starts=_starts(ctx))
+        y, _ = scan(C, B, dt.unsqueeze(-1) * u.float(), (dt * A).unsqueeze(-1), starts=_starts(ctx), group=_cp(ctx))
         y = (y.float() + u.float() * self.D.float()[:, None]).reshape(bsz, t, d) * F.silu(z.float())
         y = self.norm(y.reshape(bsz, t, g, -1).to(x.dtype), ctx).reshape(bsz, t, d)
         return self.out_proj(y, ctx)

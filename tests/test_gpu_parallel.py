@@ -213,3 +213,31 @@ def test_fused_fsdp_matches_one_gpu(cuda, tmp_path, remat, micro):
         for name, p in state.items():
             err = ((got["state"][name] - p).norm() / p.norm().clamp_min(1e-9)).item()
             assert err < 2e-2, (world, name, err)
+
+
+@pytest.mark.parametrize("schedule", ["gpipe", "1f1b"])
+def test_pipeline_over_two_gpus_matches_one_gpu(cuda, tmp_path, schedule):
+    """Two stages over NCCL send / receive (each direction of the pair on its own communicator),
+    four microbatches, against one GPU running the same microbatches."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+
+    from bux_b200.lang import compile_runs
+    from bux_b200.train.trainer import Trainer
+
+    base = ["precision = precision(compute=bfloat16, matmuls=compute)", "methods.microbatches = 4",
+            "methods.remat = none"]
+    run = compile_runs(DENSE, filename="p.bux", overrides=base)[0]
+    tr = Trainer(run, device=cuda)
+    feed = iter(tr.batches())
+    want = [tr.train_step(next(feed))["loss"].item() for _ in range(2)]
+    state = {n: p.detach().float().cpu() for n, p in tr.model.named_parameters()}
+    out = str(tmp_path / "r0.pt")
+    mp.spawn(_tensor_worker, args=(2, _free_port(), [*base, "mesh = mesh(stage=2)", f"methods.pipeline = {schedule}"], out),
+             nprocs=2, join=True)
+    got = torch.load(out)
+    assert got["losses"] == pytest.approx(want, abs=3e-2)
+    for name, p in state.items():
+        err = ((got["state"][name] - p).norm() / p.norm().clamp_min(1e-9)).item()
+        assert err < 2e-2, (name, err)

@@ -296,3 +296,39 @@ def test_merge_by_lse_equals_attention_over_the_union():
     parts = [ref.attention(q, k[:, s:s + 8], v[:, s:s + 8], causal=False) for s in (0, 8, 16)]
     got, lse = merge_by_lse([p[0] for p in parts], [p[1] for p in parts])
     assert torch.allclose(got, want, atol=1e-5) and torch.allclose(lse, want_lse, atol=1e-5)
+
+
+RECURRENT = """
+d_model=32
+vocab_size=64
+n = rmsnorm
+mixer = {mixer}
+m = gated_mlp(intermediate_size=48, activation=swish)
+block = [n mixer] [n m]
+model = embed block^2 n head
+data = synthetic
+optimizer = adamw(lr=1e-2, eps=1.0)
+seq_len = 160
+batch = 4
+steps = 3
+precision = precision(compute=float32)
+"""
+
+
+@pytest.mark.parametrize("mixer", [
+    "gdn(num_heads=2, head_dim=8, num_v_heads=4, v_head_dim=8)",      # delta rule, a decay per head, short convs
+    "kda(num_heads=2, head_dim=8)",                                   # a decay per key channel
+    "gla(num_heads=2, head_dim=8)",                                   # no rank-one term
+    "rwkv7(num_heads=2, head_dim=8, decay_rank=4, a_rank=4, v_rank=4, gate_rank=4)",   # token shift
+    "mamba2(state_size=8, head_dim=8, conv_size=3)",
+    "short_conv()",
+])
+def test_recurrent_mixers_under_context_parallelism(tmp_path, mixer):
+    """Positions split over two ranks: the state (and the convolutions' last positions) are
+    handed from the first rank to the second; losses and parameters equal one rank's."""
+    src = RECURRENT.format(mixer=mixer)
+    want_losses, want = _single(src)
+    got = _spawn(2, src, ["mesh = mesh(context=2)"], tmp_path)
+    assert got["losses"] == pytest.approx(want_losses, abs=2e-5)
+    for name, p in want.items():
+        assert torch.allclose(got["state"][name], p, atol=2e-5), name
