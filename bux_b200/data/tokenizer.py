@@ -34,6 +34,10 @@ class ByteTokenizer:
             i = j
         return out
 
+    def token_pieces(self) -> dict:
+        """id → the bytes it stands for (special tokens left out)."""
+        return {i: bytes([i]) for i in range(256)}
+
     def decode(self, ids) -> str:
         inv = {v: k for k, v in self.special_ids.items()}
         parts, run = [], bytearray()
@@ -70,6 +74,37 @@ class FileTokenizer:
 
     def decode(self, ids) -> str:
         return self.tok.decode(list(ids), skip_special_tokens=False)
+
+    def token_pieces(self) -> dict:
+        """id → the bytes it stands for (special / added tokens left out): each id decoded alone."""
+        special = {t.content for t in getattr(self.tok, "get_added_tokens_decoder", lambda: {})().values()}
+        out = {}
+        for piece, i in self.tok.get_vocab().items():
+            if piece in special:
+                continue
+            out[i] = self.tok.decode([i], skip_special_tokens=False).encode("utf-8")
+        return out
+
+
+def prefix_tokens(tokenizer) -> "list":
+    """Each id's prefix token: the id whose bytes are the longest proper prefix of its bytes
+    that the vocabulary has (what prefix-token prediction, ``loss(prefix=...)``, looks up);
+    -1 where there is none (a single byte, a special token). Of ids with the same bytes the
+    first stands for them. Reference: ``data/tokenizer.py:115-135`` there."""
+    import numpy as np
+
+    pieces = tokenizer.token_pieces()
+    first: dict = {}
+    for i in sorted(pieces):
+        first.setdefault(pieces[i], i)
+    table = np.full(tokenizer.vocab_size, -1, np.int32)
+    for i, piece in pieces.items():
+        for cut in range(len(piece) - 1, 0, -1):
+            hit = first.get(piece[:cut])
+            if hit is not None:
+                table[i] = hit
+                break
+    return table
 
 
 def find(name: str) -> Path:

@@ -41,10 +41,25 @@ class LossParts:
     terms: dict = field(default_factory=dict)
 
 
-def compute(ctx, batch, loss_cfg: T.LossConfig, span=None) -> LossParts:
+def prefix_weight(c: T.PrefixConfig, share: float) -> float:
+    """Prefix-token prediction's weight at `share` of the run's steps: its weight for the
+    first `hold` of them, falling linearly to 0 over the next `decay`, then 0
+    (``train/objective.py:309-318`` there)."""
+    if share <= c.hold:
+        return c.weight
+    if c.decay == 0:
+        return 0.0
+    return c.weight * min(1.0, max(0.0, 1 - (share - c.hold) / c.decay))
+
+
+def compute(ctx, batch, loss_cfg: T.LossConfig, span=None, prefixes=None, progress: float = 0.0) -> LossParts:
     """Loss of one forward `ctx` on `batch` = (input_ids, position_ids, loss_mask). With
     `span` = (start, stop) the forward saw only those positions of the rows (context
-    parallelism): targets come from the whole rows, then the span is taken."""
+    parallelism): targets come from the whole rows, then the span is taken. With
+    ``loss(prefix=...)``, `prefixes` (int tensor [vocab]: each id's prefix token, -1 for none)
+    adds the first head's cross-entropy of every target's prefix token, weighted by the
+    schedule at `progress` (the share of the run's steps done); it is reported unweighted as
+    ``prefix_loss``."""
     ids, pos, lmask = batch
     dev = ids.device
     total = torch.zeros((), dtype=torch.float32, device=dev)
@@ -69,6 +84,17 @@ def compute(ctx, batch, loss_cfg: T.LossConfig, span=None) -> LossParts:
         if k == 0:
             ce0, count0 = s, n
             total = total + s
+            if loss_cfg.prefix is not None and prefixes is not None:
+                # the same hidden states against each target's prefix token, where it has one;
+                # a mean over all the targets, as the cross-entropy itself
+                ptgt = prefixes.to(tgt.device)[tgt.reshape(-1).long()]
+                pmask = mask.reshape(-1) & (ptgt >= 0)
+                ps, _ = ops.cross_entropy_head(h, head.weight, ptgt.clamp_min(0), pmask.float(), bias=head.bias,
+                                               softcap=head.softcap)
+                terms["prefix_loss"] = (ps / n.clamp_min(1.0)).detach()
+                w = prefix_weight(loss_cfg.prefix, progress)
+                if w > 0:
+                    total = total + w * ps
         else:
             # an MTP head's mean loss, weighted, spread over the first head's tokens
             w = loss_cfg.mtp / max(1, len(ctx.heads) - 1)

@@ -110,6 +110,7 @@ class Trainer:
         self._norm_acc = None
         self._hooks_installed = False
         self._status_host = None
+        self._prefixes = None
         self.stretches = curriculum.stretches(t)
         self.timers = Timers()
 
@@ -169,7 +170,8 @@ class Trainer:
                 segments = segments[:, span[0]:span[1]]
         ctx = self.model(ids, pos, segments, training=training, precision=self.precision,
                          methods=self.train.methods, parallel=self.parallel, step=self.step)
-        parts = objective.compute(ctx, mb, self.train.loss, span=span)
+        parts = objective.compute(ctx, mb, self.train.loss, span=span, prefixes=self.prefix_table(),
+                                  progress=self.step / max(1, self.train.steps))
         loss = parts.total_sum * inv_count + parts.per_batch / (n_micro * world)
         if span is not None:  # per-batch terms are reported by every rank of the row
             loss = parts.total_sum * inv_count + parts.per_batch / (n_micro * world * self.parallel.shape["context"])
@@ -247,6 +249,22 @@ class Trainer:
             out["grad_norm"] = norm
         out.update(terms)
         return out
+
+    def prefix_table(self):
+        """Each id's prefix token for ``loss(prefix=...)`` (None without it): from the run's
+        tokenizer; ids past the tokenizer's vocabulary, or every id without a tokenizer, have none."""
+        if self.train.loss.prefix is None:
+            return None
+        if self._prefixes is None:
+            vocab = self.run.arch.vocab_size or 1
+            table = torch.full((vocab,), -1, dtype=torch.int64)
+            if self.train.tokenizer is not None:
+                from ..data import tokenizer as TK
+
+                given = torch.from_numpy(TK.prefix_tokens(TK.load(self.train.tokenizer))).long()
+                table[: min(vocab, given.numel())] = given[:vocab]
+            self._prefixes = table.to(self.device)
+        return self._prefixes
 
     # ---- the kernels' bounded waits
     def _snapshot_kernel_status(self) -> None:

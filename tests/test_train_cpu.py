@@ -188,3 +188,40 @@ def test_profiler_commands():
     if profilers.available("ncu"):
         cmd = profilers.command("ncu", "runs/x", argv=["-m", "bux_b200", "train", "f.bux"])
         assert cmd[0] == "ncu" and "runs/x/profile" in cmd and cmd[-4:] == ["-m", "bux_b200", "train", "f.bux"]
+
+
+def test_prefix_token_prediction_weight_schedule_and_loss():
+    """``loss(prefix=...)``: the weight holds, falls linearly, ends at zero; the term is the
+    first head's cross-entropy of each target's prefix token where it has one."""
+    import torch
+
+    from bux_b200.config import training as T
+    from bux_b200.data import tokenizer as TK
+    from bux_b200.train import objective
+    from bux_b200.train.trainer import Trainer
+
+    c = T.PrefixConfig(weight=0.5, hold=0.25, decay=0.5)
+    assert [objective.prefix_weight(c, s) for s in (0.0, 0.25, 0.5, 0.75, 0.9)] == [0.5, 0.5, 0.25, 0.0, 0.0]
+    # the byte tokenizer's pieces are single bytes: none has a proper prefix
+    assert (TK.prefix_tokens(TK.ByteTokenizer()) == -1).all()
+
+    class Pieces:
+        vocab_size = 6
+
+        def token_pieces(self):
+            return {0: b"a", 1: b"ab", 2: b"abc", 3: b"b", 4: b"bc", 5: b"abc"}
+
+    assert TK.prefix_tokens(Pieces()).tolist() == [-1, 0, 1, -1, 3, 1]
+
+    src = SMOKE.replace("schedule  = wsd(warmup=10)", "schedule  = constant").replace("steps     = 50", "steps     = 8\nloss = loss(prefix=prefix(weight=0.5, hold=0.5, decay=0.25))\n"
+                        "tokenizer = tokenizer(name=\"bytes\")")
+    run = compile_runs(src, filename="s.bux")[0]
+    tr = Trainer(run, device="cpu")
+    # every token's prefix is the token before it in the vocabulary (a made-up table)
+    vocab = run.arch.vocab_size
+    tr._prefixes = torch.arange(-1, vocab - 1)
+    feed = iter(tr.batches())
+    outs = [tr.train_step(next(feed)) for _ in range(8)]
+    assert all("prefix_loss" in o for o in outs)
+    first = outs[0]["prefix_loss"].item()
+    assert 3.0 < first < 8.0   # near ln(vocab) at the start
