@@ -107,6 +107,17 @@ def prefix_tokens(tokenizer) -> "list":
     return table
 
 
+def token_bytes(tokenizer) -> "list":
+    """The bytes of text each id stands for (its UTF-8 bytes); 0 for a special token, which
+    stands for none. Bits per byte divide by them (``data/tokenizer.py:137`` there)."""
+    import numpy as np
+
+    table = np.zeros(tokenizer.vocab_size, np.int32)
+    for i, piece in tokenizer.token_pieces().items():
+        table[i] = len(piece)
+    return table
+
+
 def find(name: str) -> Path:
     cands = [Path(name), Path(name) / "tokenizer.json"]
     for root in os.environ.get("BUX_TOKENIZERS", "").split(os.pathsep):

@@ -10,6 +10,8 @@ Reference: ``train/objective.py:53-477`` (`Heads`, `Objective`, `target_mask`).
 
 from __future__ import annotations
 
+import math
+
 from dataclasses import dataclass, field
 from typing import Optional
 
@@ -107,3 +109,52 @@ def compute(ctx, batch, loss_cfg: T.LossConfig, span=None, prefixes=None, progre
     if ce0 is None:
         raise ValueError("the model has no head, so there is nothing to train on")
     return LossParts(total, count0, ce0.detach(), per_batch, terms)
+
+
+# ------------------------------------------------------------------ what an evaluation measures
+def per_token_nats(head, targets: torch.Tensor, rows: int = 4096) -> torch.Tensor:
+    """The head's cross-entropy of every position, [B, T] fp32, its logits formed a slab of
+    positions at a time (an evaluation only: training never holds per-token losses)."""
+    hidden = head.hidden.reshape(-1, head.hidden.shape[-1])
+    flat = targets.reshape(-1)
+    out = torch.empty(flat.shape[0], dtype=torch.float32, device=hidden.device)
+    weight = head.weight.to(hidden.dtype)
+    for s in range(0, hidden.shape[0], rows):
+        logits = torch.nn.functional.linear(hidden[s:s + rows], weight,
+                                            None if head.bias is None else head.bias.to(hidden.dtype)).float()
+        if head.softcap:
+            logits = head.softcap * torch.tanh(logits / head.softcap)
+        out[s:s + rows] = torch.nn.functional.cross_entropy(logits, flat[s:s + rows].long(), reduction="none")
+    return out.view(targets.shape)
+
+
+def held_out(ctx, batch, token_bytes=None, positions=()) -> dict:
+    """What an evaluation measures of the first head on `batch`, each as (sum, what it is a
+    mean of): ``loss`` (nats over targets); with `token_bytes` (int tensor [vocab]: the bytes
+    of text each id stands for, 0 for a special token) ``bpb`` (bits over bytes: a target
+    that stands for no text is left out); and with `positions`, each of them over the targets
+    of each bucket of positions in their documents, named by the bucket's first position
+    (``loss_0``, ``loss_2k``, ...). Reference: ``train/objective.py:408-450`` there."""
+    ids, pos, lmask = batch
+    tgt, mask = targets_and_mask(ids, pos, lmask, 1)
+    nats = per_token_nats(ctx.heads[0], tgt)
+    weights = {"loss": mask.float()}
+    if token_bytes is not None:
+        weights["bpb"] = torch.where(mask, token_bytes.to(tgt.device)[tgt.long()].float(), torch.zeros(()).to(nats))
+    if positions:
+        edges = [0, *positions]
+        names = T.buckets(positions)
+        for base in list(weights):
+            for k, name in enumerate(names):
+                inside = pos >= edges[k]
+                if k + 1 < len(edges):
+                    inside = inside & (pos < edges[k + 1])
+                weights[f"{base}_{name}"] = weights[base] * inside.float()
+    out = {}
+    for name, w in weights.items():
+        counted = (w > 0).float()
+        total = (nats * counted).sum()
+        if name.startswith("bpb"):
+            total = total / math.log(2)
+        out[name] = (total, w.sum())
+    return out

@@ -111,6 +111,7 @@ class Trainer:
         self._hooks_installed = False
         self._status_host = None
         self._prefixes = None
+        self._token_bytes = None
         self.stretches = curriculum.stretches(t)
         self.timers = Timers()
 
@@ -344,21 +345,40 @@ class Trainer:
         self.model.eval()
         rank = self.parallel.data_rank if self.parallel is not None else 0
         world = self.parallel.data_world if self.parallel is not None else 1
-        total = torch.zeros(1, dtype=torch.float32, device=self.device)
-        count = torch.zeros(1, dtype=torch.float32, device=self.device)
+        nbytes = self.token_bytes()
+        sums: dict = {}
         for b in data.eval_batches(self.train, e, self.run.arch.vocab_size or 1, self.cache, rank, world):
             mb = self.to_device(b)
             ctx = self.model(mb[0], mb[1], segments_of(mb[1]) if mb.packed else None, training=False,
                              precision=self.precision,
                              methods=self.train.methods, parallel=self.parallel, step=self.step)
-            parts = objective.compute(ctx, mb, self.train.loss)
-            total += parts.ce_sum
-            count += parts.count
-        if self.parallel is not None:
-            total = self.parallel.sum_scalar(total, data_only=True)
-            count = self.parallel.sum_scalar(count, data_only=True)
+            for name, (total, count) in objective.held_out(ctx, mb, nbytes, e.positions).items():
+                acc = sums.setdefault(name, torch.zeros(2, dtype=torch.float32, device=self.device))
+                acc[0] += total
+                acc[1] += count
         self.model.train()
-        return {f"{e.name}_loss": (total / count.clamp_min(1)).item()}
+        out = {}
+        for name in sorted(sums):   # every rank in the same order
+            acc = sums[name]
+            if self.parallel is not None:
+                acc = self.parallel.sum_scalar(acc, data_only=True)
+            total, count = acc.tolist()
+            out[f"{e.name}_{name}"] = total / count if count > 0 else float("nan")
+        return out
+
+    def token_bytes(self):
+        """The bytes of text each id stands for, for bits per byte (None without a tokenizer)."""
+        if self.train.tokenizer is None:
+            return None
+        if self._token_bytes is None:
+            from ..data import tokenizer as TK
+
+            vocab = self.run.arch.vocab_size or 1
+            table = torch.zeros(vocab, dtype=torch.int64)
+            given = torch.from_numpy(TK.token_bytes(TK.load(self.train.tokenizer))).long()
+            table[: min(vocab, given.numel())] = given[:vocab]
+            self._token_bytes = table.to(self.device)
+        return self._token_bytes
 
     # ------------------------------------------------------------------ state
     def state(self) -> dict:

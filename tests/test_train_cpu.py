@@ -225,3 +225,26 @@ def test_prefix_token_prediction_weight_schedule_and_loss():
     assert all("prefix_loss" in o for o in outs)
     first = outs[0]["prefix_loss"].item()
     assert 3.0 < first < 8.0   # near ln(vocab) at the start
+
+
+def test_evaluation_reports_bits_per_byte_and_position_buckets():
+    """`eval(positions=...)`: the loss over the targets of each bucket of positions, and bits
+    per byte where a tokenizer says how many bytes a token stands for."""
+    import math
+
+    import torch
+
+    from bux_b200.train.trainer import Trainer
+
+    src = SMOKE + 'tokenizer = tokenizer(name="bytes")\neval = eval(data=synthetic, every=10, batches=2, positions=[16, 32])\n'
+    run = compile_runs(src, filename="s.bux")[0]
+    tr = Trainer(run, device="cpu")
+    e = run.train.eval if not isinstance(run.train.eval, (tuple, list)) else run.train.eval[0]
+    got = tr.evaluate(e)
+    assert set(got) == {"eval_loss", "eval_bpb", "eval_loss_0", "eval_loss_16", "eval_loss_32",
+                        "eval_bpb_0", "eval_bpb_16", "eval_bpb_32"}
+    # buckets hold 16, 16 and 31 of a row's 63 targets: the loss is their weighted mean
+    mean = (16 * got["eval_loss_0"] + 16 * got["eval_loss_16"] + 31 * got["eval_loss_32"]) / 63
+    assert mean == pytest.approx(got["eval_loss"], rel=1e-5)
+    # ids below 256 stand for one byte each under the byte tokenizer (the few above for none)
+    assert got["eval_bpb"] == pytest.approx(got["eval_loss"] / math.log(2), rel=1e-2)
