@@ -136,3 +136,59 @@ def test_mla_with_an_indexer():
         few = run(2)
     assert torch.allclose(everything, dense, atol=1e-5)
     assert not torch.allclose(few, dense, atol=1e-3)
+
+
+CSA_SRC = """
+d_model=32
+vocab_size=64
+n = rmsnorm
+a = csa(num_heads=2, head_dim=16, q_lora_rank=16, o_lora_rank=8, o_groups=2, sliding_window_size=8,
+        sinks=true, compress_ratio=4, rope=rope(fraction=0.5, layout=interleaved))
+w = csa(num_heads=2, head_dim=16, sliding_window_size=8)
+m = gated_mlp(intermediate_size=48, activation=swish)
+model = embed [n a] [n m] [n w] [n m] n head
+data = synthetic
+optimizer = adamw(lr=1e-2)
+seq_len = 40
+batch = 2
+steps = 3
+precision = precision(compute=float32)
+"""
+
+
+def test_csa_trains_is_causal_and_sees_compressed_latents_past_its_window():
+    import torch
+
+    from bux_b200.lang import compile_runs
+    from bux_b200.train.trainer import Trainer
+
+    run = compile_runs(CSA_SRC, filename="c.bux")[0]
+    tr = Trainer(run, device="cpu")
+    batch = next(iter(tr.batches()))
+    losses = [tr.train_step(batch)["loss"].item() for _ in range(5)]
+    assert losses[-1] < losses[0]
+    model = tr.model.eval()
+    ids = torch.randint(0, 64, (1, 40), generator=torch.Generator().manual_seed(0))
+    base = model.logits(ids, training=False)
+    later = ids.clone()
+    later[0, 30] = (later[0, 30] + 1) % 64
+    moved = model.logits(later, training=False)
+    assert torch.allclose(base[:, :30], moved[:, :30], atol=1e-5)          # causal
+    # a token 20 positions back is outside both layers' windows (8 + 8): only a compressed
+    # latent can carry it to position 39
+    early = ids.clone()
+    early[0, 2] = (early[0, 2] + 1) % 64
+    far = model.logits(early, training=False)
+    assert not torch.allclose(base[:, 39], far[:, 39], atol=1e-6)
+
+
+def test_csa_refuses_what_is_not_built():
+    import pytest
+
+    from bux_b200.lang import compile_runs
+    from bux_b200.models import Model
+
+    src = CSA_SRC.replace("sinks=true, compress_ratio=4,", "sinks=true, compress_ratio=4, indexer=indexer(num_heads=2, top_k=4),")
+    run = compile_runs(src, filename="c.bux")[0]
+    with pytest.raises(NotImplementedError, match="indexer"):
+        Model(run.arch)
