@@ -86,24 +86,33 @@ def read_tree(folder) -> tuple:
     return unflatten(flat), meta.get("custom_metadata", {})
 
 
-def state_tree(trainer) -> dict:
-    """The checkpoint's tree: "0" the model (fp32, from the master copy where there is
-    one), "1" the optimizer (step, moments by parameter path)."""
+def state_leaves(trainer):
+    """(part, key, tensor) of every leaf of the checkpoint's tree, one at a time: "0" the model
+    (fp32, from the master copy where there is one), "1" the optimizer (step, moments by
+    parameter path, in the parameter's shape). Each tensor is formed when it is asked for, so
+    a writer that lets go of one before it takes the next holds one leaf's copy at a time."""
     opt = trainer.optimizer
-    model = {}
     for name, p in trainer.model.named_parameters():
         st = opt.state.get(name, {})
-        model[name] = st.get("master", p.detach()).float()
+        yield "0", name, st.get("master", p.detach()).float()
     for name, b in trainer.model.named_buffers():
         if name.split(".")[-1] in ("inv_freq",):
             continue
-        model[name] = b.detach()
-    optim_tree: dict = {"count": torch.tensor(opt.step_count), "tokens": torch.tensor(trainer.tokens)}
+        yield "0", name, b.detach()
+    yield "1", "count", torch.tensor(opt.step_count)
+    yield "1", "tokens", torch.tensor(trainer.tokens)
     shapes = {name: tuple(p.shape) for name, p in trainer.model.named_parameters()}
     for name in opt.state:
         for k, v in opt.moments_for_checkpoint(name, shapes[name]).items():
-            optim_tree[f"{k}/{name}"] = v
-    return {"0": model, "1": optim_tree}
+            yield "1", f"{k}/{name}", v
+
+
+def state_tree(trainer) -> dict:
+    """The whole tree at once (small models, tests): ``{"0": model, "1": optimizer}``."""
+    tree: dict = {"0": {}, "1": {}}
+    for part, key, value in state_leaves(trainer):
+        tree[part][key] = value
+    return tree
 
 
 def save(folder, step: int, trainer) -> None:
@@ -111,15 +120,31 @@ def save(folder, step: int, trainer) -> None:
     rank = runtime.rank()
     final = folder / str(step)
     tmp = folder / f"{step}.orbax-checkpoint-tmp"
-    tree = state_tree(trainer) if trainer.parallel is None else trainer.parallel.checkpoint_tree(trainer, state_tree)
+    par = trainer.parallel
+    meta = {"step": step, "methods.stages": trainer.train.methods.stages,
+            "repeat": trainer.train.methods.repeat, "rounds": trainer.train.methods.rounds}
     if rank == 0:
         shutil.rmtree(tmp, ignore_errors=True)
         (tmp / "default").mkdir(parents=True, exist_ok=True)
-    if trainer.parallel is not None:
-        trainer.parallel.barrier()
+    if par is not None:
+        par.barrier()
+    if par is not None and getattr(par, "pipeline", None) is None:
+        # leaf by leaf: every rank takes part in putting a leaf together, the first rank
+        # writes it and lets go of it before the next one (a 30B model with its moments never
+        # sits whole on one device)
+        index = {}
+        for part, key, value in state_leaves(trainer):
+            whole = par.whole_leaf(key, value)
+            if rank == 0:
+                path = f"{part}/{key}"
+                index[path] = write_array(tmp / "default" / path.replace(".", "/"), whole)
+            del whole, value
+        if rank == 0:
+            (tmp / "default" / "_METADATA.json").write_text(json.dumps({"tree": index, "custom_metadata": meta}))
+        tree = None
+    else:
+        tree = state_tree(trainer) if par is None else par.checkpoint_tree(trainer, state_tree)
     if tree is not None:
-        meta = {"step": step, "methods.stages": trainer.train.methods.stages,
-                "repeat": trainer.train.methods.repeat, "rounds": trainer.train.methods.rounds}
         write_tree(tmp / "default", tree, meta)
     if trainer.parallel is not None:
         trainer.parallel.barrier()
@@ -131,42 +156,48 @@ def save(folder, step: int, trainer) -> None:
 
 
 def load(folder, trainer) -> None:
-    """Restore `trainer` from a checkpoint of whole leaves: every rank reads the tree and
-    keeps its own part of each leaf (`Parallel.restore_tree` inverts what
-    `Parallel.checkpoint_tree` gathered), so a run resumes on the mesh it was saved on
-    or on another one."""
-    tree, meta = read_tree(Path(folder) / "default")
-    if trainer.parallel is not None:
-        tree = trainer.parallel.restore_tree(trainer, tree)
+    """Restore `trainer` from a checkpoint of whole leaves, leaf by leaf: every rank reads a
+    leaf, keeps its own part of it (`Parallel.restore_leaf` inverts what the save gathered)
+    and lets go of the rest before it reads the next, so a run resumes on the mesh it was
+    saved on or on another one without any rank ever holding the whole state."""
+    folder = Path(folder) / "default"
+    meta = json.loads((folder / "_METADATA.json").read_text())
+    custom = meta.get("custom_metadata", {})
+    mine = trainer.parallel.restore_leaf(trainer) if trainer.parallel is not None else (lambda name, t: t)
     opt = trainer.optimizer
-    model_state = tree["0"]
-    flat_model = flatten(model_state)
+    params = dict(trainer.model.named_parameters())
+    buffers = dict(trainer.model.named_buffers())
     with torch.no_grad():
-        params = dict(trainer.model.named_parameters())
-        buffers = dict(trainer.model.named_buffers())
-        for path, value in flat_model.items():
-            name = path.replace("/", ".")
-            if name in params:
-                p = params[name]
-                st = opt.state.get(name, {})
-                if "master" in st:
-                    st["master"].copy_(value.to(st["master"].device))
-                p.data.copy_(value.to(p.device).to(p.dtype))
-            elif name in buffers:
-                buffers[name].copy_(value.to(buffers[name].device))
-            else:
-                raise KeyError(f"the checkpoint holds '{name}', which this model has not: the "
-                               "architecture or a method that changes the state's layout differs")
-        flat_opt = flatten(tree["1"])
-        for path, value in flat_opt.items():
-            if path == "count":
+        for path in meta["tree"]:
+            part, key = path.split("/", 1)
+            value = read_array(folder / path.replace(".", "/"))
+            if part == "0":
+                name = key.replace("/", ".")
+                value = mine(name, value)
+                if value is None:
+                    continue
+                if name in params:
+                    p = params[name]
+                    st = opt.state.get(name, {})
+                    if "master" in st:
+                        st["master"].copy_(value.to(st["master"].device))
+                    p.data.copy_(value.to(p.device).to(p.dtype))
+                elif name in buffers:
+                    buffers[name].copy_(value.to(buffers[name].device))
+                else:
+                    raise KeyError(f"the checkpoint holds '{name}', which this model has not: the "
+                                   "architecture or a method that changes the state's layout differs")
+            elif key == "count":
                 opt.step_count = int(value)
-            elif path == "tokens":
+            elif key == "tokens":
                 trainer.tokens = int(value)
             else:
-                kind, name = path.split("/", 1)
+                kind, name = key.split("/", 1)
                 name = name.replace("/", ".")
+                value = mine(name, value)
+                if value is None:
+                    continue
                 if name not in opt.state:
                     raise KeyError(f"the checkpoint holds optimizer state of '{name}', which this model has not")
                 opt.load_moment(name, kind, value)
-    trainer.step = int(meta.get("step", opt.step_count))
+    trainer.step = int(custom.get("step", opt.step_count))

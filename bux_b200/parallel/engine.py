@@ -273,6 +273,32 @@ class Parallel:
             tree = self.pipeline.gather_tree(tree)
         return tree if self.rank == 0 else None
 
+    def whole_leaf(self, key: str, t):
+        """One leaf of the checkpoint's tree put together from every rank's part (all ranks
+        call it, in the same order): `checkpoint_tree` for a single leaf, so that a writer can
+        go leaf by leaf. `key` is the leaf's key in its part (``name`` or ``kind/name``)."""
+        if not isinstance(t, torch.Tensor) or t.dim() == 0:
+            return t
+        name = key.split("/", 1)[1] if "/" in key else key
+        if self.fsdp is not None:
+            rows = self.fsdp.sharded.get(name)
+            if rows is not None and t.shape[0] * self.fsdp.world == rows:
+                t = t.contiguous()
+                whole = torch.empty(self.fsdp.world * t.numel(), dtype=t.dtype, device=t.device)
+                dist.all_gather_into_tensor(whole, t.reshape(-1), group=self.fsdp.group)
+                t = whole.view(rows, *t.shape[1:])
+        lay = self.tensor_layout.get(name)
+        if self.tensor_group is not None and lay is not None and t.dim() > lay[0]:
+            from . import tensor
+
+            t = tensor.whole(t, lay[0], lay[1], self.tensor_group)
+        if self.expert_group is not None and ("experts_gate_up" in name or "experts_down" in name):
+            world = dist.get_world_size(self.expert_group)
+            parts = [torch.empty_like(t) for _ in range(world)]
+            dist.all_gather(parts, t.contiguous(), group=self.expert_group)
+            t = torch.cat(parts, dim=0)
+        return t
+
     def restore_tree(self, trainer, tree: dict) -> dict:
         """The inverse of `checkpoint_tree`: from a tree of whole leaves (every rank read it),
         what this rank holds. In the reverse order of the gathers: a pipeline stage keeps its
@@ -281,9 +307,14 @@ class Parallel:
         their parameter's shape in a checkpoint, so one rule serves both."""
         return _restore(self, trainer, tree)
 
+    def restore_leaf(self, trainer):
+        """`restore_tree` for one leaf at a time: returns ``f(name, whole tensor)`` giving this
+        rank's part (None for a leaf of another pipeline stage)."""
+        return _mine(self, trainer)
 
-def _restore(par: "Parallel", trainer, tree: dict) -> dict:
-    """This rank's part of every leaf of a tree of whole leaves (see `Parallel.restore_tree`)."""
+
+def _mine(par: "Parallel", trainer):
+    """name, tensor → this rank's part of a whole leaf (None: another stage's leaf)."""
     params = dict(trainer.model.named_parameters())
     known = set(params) | {n for n, _ in trainer.model.named_buffers()}
     piped = getattr(par, "pipeline", None) is not None
@@ -308,6 +339,13 @@ def _restore(par: "Parallel", trainer, tree: dict) -> dict:
                 and t.shape[0] == par.fsdp.sharded[name]:
             t = t.chunk(par.fsdp.world, dim=0)[par.fsdp.rank]
         return t.contiguous()
+
+    return mine
+
+
+def _restore(par: "Parallel", trainer, tree: dict) -> dict:
+    """This rank's part of every leaf of a tree of whole leaves (see `Parallel.restore_tree`)."""
+    mine = _mine(par, trainer)
 
     def walk(node: dict) -> dict:
         out = {}
