@@ -120,11 +120,12 @@ class Repeated(nn.Module):
         # a count for the last so many passes only (what the device has room for)
         self.keep_attention = False
         self.kept_to_host = False  # with `offload`, kept outputs follow the inputs to pinned host memory
+        self.first = None          # checkpoint only the first so many passes; the rest keep everything
 
     def forward(self, x, ctx: Context):
         for i, item in enumerate(self.items):
             if (self.remat and ctx.training and torch.is_grad_enabled() and isinstance(x, torch.Tensor)
-                    and x.requires_grad):
+                    and x.requires_grad and (self.first is None or i < self.first)):
                 keep, to_host = self.keep_attention, self.kept_to_host
                 if keep is not True and keep is not False:
                     on_device = i >= len(self.items) - int(keep)

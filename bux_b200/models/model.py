@@ -49,19 +49,22 @@ class Model(nn.Module):
         ctx = self(input_ids, **kw)
         return ctx.heads[0].logits()
 
-    def set_remat(self, on: bool, offload: bool = False, keep_attention=False, kept_to_host: bool = False) -> None:
+    def set_remat(self, on: bool, offload: bool = False, keep_attention=False, kept_to_host: bool = False,
+                  first=None) -> None:
         """Checkpoint every pass of every repeated block (keep only its input, rerun it
         in the backward); `offload` keeps those inputs in pinned host memory;
         `keep_attention` also keeps each attention's output and log-sum-exp, so the rerun
         skips the attention forward kernel (the remat preset that keeps ``attention.out``):
         True for every pass, or a number for the last so many passes of each repeat. Kept
-        outputs stay on the device unless `kept_to_host` sends them after the inputs."""
+        outputs stay on the device unless `kept_to_host` sends them after the inputs. With
+        `first`, only the first so many passes of each repeat are checkpointed."""
         for m in self.modules():
             if isinstance(m, Repeated):
                 m.remat = on
                 m.offload = offload
                 m.keep_attention = keep_attention if on else False
                 m.kept_to_host = kept_to_host
+                m.first = first
 
     def step_end_update(self) -> None:
         for m in self.modules():

@@ -90,8 +90,7 @@ class Trainer:
         experts_fmt = t.precision.experts()
         if experts_fmt:
             self.precision.roles["experts"] = experts_fmt
-        remat = t.methods.remat if isinstance(t.methods.remat, str) else "custom"
-        self.model.set_remat(self._remat_on(remat))
+        self.model.set_remat(**self.remat_policy(t.methods.remat))
         use_master = (self.param_dtype != torch.float32) if master is None else master
         self.optimizer = optim.Optimizer(
             self.model.named_parameters(), t.optimizer, moments=moments or t.precision.moments,
@@ -116,6 +115,39 @@ class Trainer:
         self.timers = Timers()
 
     # ------------------------------------------------------------------ setup
+    # what the token mixers' names of ``remat(save=...)`` cover
+    _MIXER_NAMES = {"attention", "attention.out", "recurrence", "recurrence.out"}
+
+    def remat_policy(self, remat) -> dict:
+        """``methods.remat`` → the arguments of `Model.set_remat`. Every pass of a repeat is
+        checkpointed as a unit (only its input is kept, the pass is rerun in the backward);
+        what a policy can keep on top of that here is the attention outputs:
+
+        * ``none`` keeps everything; ``full`` (and ``dots`` / ``dots_no_batch``, whose finer
+          grain — keeping every matmul's output — this framework does not have) keep only the
+          passes' inputs; ``auto`` decides by a memory estimate (`bux_b200.train.fitting` by
+          trial steps);
+        * ``save_attention``, ``save_qkv_attention``, ``dots_attention`` also keep each
+          attention's output and log-sum-exp, so the rerun skips the attention forward;
+          ``offload_attention`` keeps them, and the passes' inputs, in pinned host memory;
+        * ``remat(save=[...], offload=[...], first=N)``: ``attention`` (or ``attention.out``)
+          in `save` keeps the attention outputs, in `offload` sends them (and the inputs) to
+          the host; `first` checkpoints only the first N passes of each repeat.
+
+        Reference: ``architecture/repeats/remat.py:128-145`` (`PRESETS`, `CANDIDATES`)."""
+        if isinstance(remat, str):
+            if remat in ("save_attention", "save_qkv_attention", "dots_attention"):
+                return {"on": True, "keep_attention": True}
+            if remat == "offload_attention":
+                return {"on": True, "offload": self.device.type == "cuda", "keep_attention": True,
+                        "kept_to_host": self.device.type == "cuda"}
+            return {"on": self._remat_on(remat)}
+        save = set(remat.save) & self._MIXER_NAMES
+        off = set(remat.offload) & self._MIXER_NAMES
+        cuda = self.device.type == "cuda"
+        return {"on": True, "offload": bool(off) and cuda, "keep_attention": bool(save or off),
+                "kept_to_host": bool(off) and cuda, "first": remat.first}
+
     def _remat_on(self, remat: str) -> bool:
         if remat == "none":
             return False

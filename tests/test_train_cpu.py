@@ -248,3 +248,24 @@ def test_evaluation_reports_bits_per_byte_and_position_buckets():
     assert mean == pytest.approx(got["eval_loss"], rel=1e-5)
     # ids below 256 stand for one byte each under the byte tokenizer (the few above for none)
     assert got["eval_bpb"] == pytest.approx(got["eval_loss"] / math.log(2), rel=1e-2)
+
+
+@pytest.mark.parametrize("remat", ["none", "full", "save_attention", "dots_attention", "offload_attention",
+                                   "remat(save=[attention], first=1)"])
+def test_remat_policies_train_the_same(remat):
+    """What a policy keeps changes memory, not numbers: every policy's losses equal `none`'s."""
+    def losses(policy):
+        run = compile_runs(SMOKE, filename="s.bux", overrides=[f"methods.remat = {policy}", "steps = 20"])[0]
+        tr = Trainer(run, device="cpu")
+        feed = iter(tr.batches())
+        return [tr.train_step(next(feed))["loss"].item() for _ in range(3)], tr
+
+    want, _ = losses("none")
+    got, tr = losses(remat)
+    assert got == pytest.approx(want, abs=1e-5)
+    from bux_b200.models.graph import Repeated
+
+    rep = next(m for m in tr.model.modules() if isinstance(m, Repeated))
+    assert rep.remat == (remat != "none")
+    assert bool(rep.keep_attention) == (remat not in ("none", "full"))
+    assert rep.first == (1 if "first" in remat else None)
