@@ -151,7 +151,9 @@ class FusedEP:
         self.flags = heap[flags_at:flags_at + 8 * self.world * 4].view(torch.int32).view(8, self.world)
         self.peer_flags = torch.tensor([b + flags_at for b in bases], dtype=torch.int64, device=device)
         self.epoch = [0, 0, 0, 0, 0]
-        self.comm = torch.cuda.Stream(device=device)
+        # pushes and pulls run on streams of their own: NVLink carries both directions at once
+        self.send = torch.cuda.Stream(device=device)
+        self.recv = torch.cuda.Stream(device=device)
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
 
@@ -227,11 +229,13 @@ class _FusedExperts(torch.autograd.Function):
     gradient comes out of the activation's backward on the owner (one scalar per row,
     pulled back with dx). The backward mirrors it with the dy / dx slots.
 
-    Slot reuse is safe by construction: the side stream of every rank runs
-    push(0) push(1) pull(0) push(2) pull(1) ... and a pull waits for *every* owner's
-    "output ready" flag, which an owner raises after it has read the slot's input rows;
-    an owner overwrites an output slot only after every sender's next push into that slot's
-    input has been flagged, which each sender issues after its own pull of the old rows."""
+    Pushes run on one side stream and pulls on another (the link carries both directions at
+    once). Slot reuse is safe by construction: before a rank pushes chunk c + 2 into the input
+    slot that chunk c used, its push stream waits for *every* owner's "output ready" flag of
+    chunk c, which an owner raises after it has read the slot's input rows; and the flag of
+    that push is raised only after the rank's own pull of chunk c has finished, so an owner,
+    which overwrites an output slot only once every sender's next push into the matching
+    input slot is flagged, never writes over rows that are still being pulled."""
 
     @staticmethod
     def forward(ctx, x, weights, w_gu, w_down, ep: FusedEP, routes, act, limit, up_offset, mx,
@@ -246,21 +250,24 @@ class _FusedExperts(torch.autograd.Function):
         kind = K.KIND_MXFP8 if mx else K.KIND_BF16
         grad = any(ctx.needs_input_grad)
         main = torch.cuda.current_stream(x.device)
-        comm = ep.comm if side_stream else main
+        send, recv = (ep.send, ep.recv) if side_stream else (main, main)
         wts = weights.float().contiguous()
         out = torch.empty(t, d, dtype=x.dtype, device=x.device)
         cap = ep.cap
         if mx:
             gq, gsf, gtq, gtsf = K.quant_mxfp8_batched(w_gu.detach(), rowwise=True, colwise=grad)
             dq, dsf, dtq, dtsf = K.quant_mxfp8_batched(w_down.detach(), rowwise=True, colwise=grad)
-        comm.wait_stream(main)
-        x_epoch, y_epoch, saved = {}, {}, []
+        send.wait_stream(main)
+        recv.wait_stream(main)
+        x_epoch, y_epoch, pulled, saved = {}, {}, {}, []
 
         def push(c):
             r = routes[c]
-            with torch.cuda.stream(comm):
+            with torch.cuda.stream(send):
                 scale = wts[c * tc:(c + 1) * tc].reshape(-1)[r.order].contiguous()
                 slot = c % SLOTS
+                if c >= SLOTS:  # every owner has read what the input slot held
+                    ep.wait(CH_Y, y_epoch[c - SLOTS])
                 if mx:  # rows leave as e4m3 bytes + E8M0 scales, straight into the owner's GEMM operand
                     K.ep_push_rows_mx(x[c * tc:(c + 1) * tc], r.src_token, r.dst_rank, r.dst_row,
                                       ep.tables[("xq", slot)], ep.tables[("xsf", slot)], row_scale=scale,
@@ -268,6 +275,8 @@ class _FusedExperts(torch.autograd.Function):
                 else:
                     K.ep_push_rows(x[c * tc:(c + 1) * tc], r.src_token, r.dst_rank, r.dst_row, ep.tables[("x", slot)],
                                    row_scale=scale, peer_scale=ep.tables[("xw", slot)])
+                if c >= SLOTS and side_stream:  # my own pull of the output slot's old rows is done
+                    send.wait_event(pulled[c - SLOTS])
                 x_epoch[c] = ep.signal(CH_X)
 
         def compute(c):
@@ -297,11 +306,14 @@ class _FusedExperts(torch.autograd.Function):
 
         def pull(c):
             r = routes[c]
-            with torch.cuda.stream(comm):
+            with torch.cuda.stream(recv):
                 ep.wait(CH_Y, y_epoch[c])
                 if not values_unused:
                     K.ep_pull_combine(ep.tables[("y", c % SLOTS)], r.rank_of, r.row_of, None, tc, d, x.dtype,
                                       out=out[c * tc:(c + 1) * tc])
+                if side_stream:
+                    pulled[c] = torch.cuda.Event()
+                    pulled[c].record(recv)
 
         for c in range(min(SLOTS, chunks)):
             push(c)
@@ -310,7 +322,8 @@ class _FusedExperts(torch.autograd.Function):
             pull(c)
             if c + SLOTS < chunks:
                 push(c + SLOTS)
-        main.wait_stream(comm)
+        main.wait_stream(send)
+        main.wait_stream(recv)
         ctx.save_for_backward(x, w_gu, w_down)
         ctx.held = (saved, (gtq, gtsf, dtq, dtsf) if mx and grad else None)
         ctx.cfg = (ep, routes, act, limit, up_offset, mx, side_stream, weights.dtype)
@@ -332,7 +345,7 @@ class _FusedExperts(torch.autograd.Function):
         k = routes[0].row_of.shape[1]
         kind = K.KIND_MXFP8 if mx else K.KIND_BF16
         main = torch.cuda.current_stream(x.device)
-        comm = ep.comm if side_stream else main
+        send, recv = (ep.send, ep.recv) if side_stream else (main, main)
         dout = dout.contiguous()
         cap = ep.cap
         g_gu = getattr(w_gu, "main_grad", None)
@@ -346,19 +359,24 @@ class _FusedExperts(torch.autograd.Function):
             gtq, gtsf, dtq, dtsf = wq
         dx = torch.empty_like(x)
         dw = torch.empty(t, k, dtype=torch.float32, device=x.device)
-        comm.wait_stream(main)
-        dy_epoch, dx_epoch = {}, {}
+        send.wait_stream(main)
+        recv.wait_stream(main)
+        dy_epoch, dx_epoch, pulled = {}, {}, {}
         result = {}
 
         def push(c):
             r = routes[c]
-            with torch.cuda.stream(comm):
+            with torch.cuda.stream(send):
+                if c >= SLOTS:  # every owner has read what the dy slot held
+                    ep.wait(CH_DX, dx_epoch[c - SLOTS])
                 if mx:
                     K.ep_push_rows_mx(dout[c * tc:(c + 1) * tc], r.src_token, r.dst_rank, r.dst_row,
                                       ep.tables[("dyq", c % SLOTS)], ep.tables[("dysf", c % SLOTS)])
                 else:
                     K.ep_push_rows(dout[c * tc:(c + 1) * tc], r.src_token, r.dst_rank, r.dst_row,
                                    ep.tables[("dy", c % SLOTS)])
+                if c >= SLOTS and side_stream:  # my own pull of the dx slot's old rows is done
+                    send.wait_event(pulled[c - SLOTS])
                 dy_epoch[c] = ep.signal(CH_DY)
 
         def compute(c):
@@ -407,11 +425,14 @@ class _FusedExperts(torch.autograd.Function):
 
         def pull(c):
             r = routes[c]
-            with torch.cuda.stream(comm):
+            with torch.cuda.stream(recv):
                 ep.wait(CH_DX, dx_epoch[c])
                 K.ep_pull_combine(ep.tables[("dx", c % SLOTS)], r.rank_of, r.row_of, None, tc, d, x.dtype,
                                   out=dx[c * tc:(c + 1) * tc])
                 K.ep_pull_scalar(ep.tables[("dots", c % SLOTS)], r.rank_of, r.row_of, out=dw[c * tc:(c + 1) * tc])
+                if side_stream:
+                    pulled[c] = torch.cuda.Event()
+                    pulled[c].record(recv)
 
         for c in range(min(SLOTS, chunks)):
             push(c)
@@ -420,7 +441,8 @@ class _FusedExperts(torch.autograd.Function):
             pull(c)
             if c + SLOTS < chunks:
                 push(c + SLOTS)
-        main.wait_stream(comm)
+        main.wait_stream(send)
+        main.wait_stream(recv)
         gw_gu = None if g_gu is not None else result["gu"].to(w_gu.dtype)
         gw_down = None if g_down is not None else result["down"].to(w_down.dtype)
         return dx, dw.to(w_dtype), gw_gu, gw_down, None, None, None, None, None, None, None, None
