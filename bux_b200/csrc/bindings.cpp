@@ -64,7 +64,9 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& c, const c10::optional<Tenso
     g.sfb = reinterpret_cast<const uint8_t*>(sfb->data_ptr());
   }
   g.c = c.data_ptr(); g.ldc = (int)c.stride(c.dim() - 2);
-  TORCH_CHECK(out_kind == bux::OUT_BF16 ? c.scalar_type() == at::kBFloat16 : c.scalar_type() == at::kFloat, "c dtype does not match out_kind");
+  TORCH_CHECK((out_kind == bux::OUT_BF16 || out_kind == bux::OUT_BF16_ACC) ? c.scalar_type() == at::kBFloat16
+                                                                            : c.scalar_type() == at::kFloat,
+              "c dtype does not match out_kind");
   g.M = (int)M; g.N = (int)N; g.K = (int)K; g.k_total = (int)k_total; g.groups = (int)groups;
   g.group_offsets = opt_i32(group_offsets);
   TORCH_CHECK(mode == bux::MODE_DENSE || g.group_offsets != nullptr, "grouped modes need group_offsets");

@@ -171,14 +171,30 @@ __global__ void ep_pull_combine_kernel(const uint64_t* __restrict__ peer_base, c
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
     const long t = i / vec; const int c = (int)(i % vec);
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int j = 0; j < k; ++j) {
-      const int r = row_of[t * k + j];
-      if (r < 0) continue;
-      const float ww = w ? w[t * k + j] : 1.f;
-      const uint4 v = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(peer_base[rank_of[t * k + j]]) + (long)r * d)[c];
-      const uint32_t* u = &v.x;
+    // the picks' rows sit on other GPUs: up to eight loads are put in flight before the first
+    // one is used, so that a thread covers the link's latency once per token, not once per pick
+    for (int j0 = 0; j0 < k; j0 += 8) {
+      uint4 v[8];
+      float ww[8];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) { const float2 f = unpack_bf16(u[q]); acc[2 * q] += ww * f.x; acc[2 * q + 1] += ww * f.y; }
+      for (int jj = 0; jj < 8; ++jj) {
+        const int j = j0 + jj;
+        v[jj] = make_uint4(0, 0, 0, 0);
+        ww[jj] = 0.f;
+        if (j < k) {
+          const int r = row_of[t * k + j];
+          if (r >= 0) {
+            ww[jj] = w ? w[t * k + j] : 1.f;
+            v[jj] = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(peer_base[rank_of[t * k + j]]) + (long)r * d)[c];
+          }
+        }
+      }
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj) {
+        const uint32_t* u = &v[jj].x;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { const float2 f = unpack_bf16(u[q]); acc[2 * q] += ww[jj] * f.x; acc[2 * q + 1] += ww[jj] * f.y; }
+      }
     }
     uint4 o;
     o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);

@@ -316,11 +316,13 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
       // full bf16 tiles leave through shared memory and TMA stores: whole 128-byte lines,
       // asynchronous, and the accumulator is released as soon as it has been read
       const bool by_tma = p.tma_store && (p.mode != MODE_GROUPED_ROWS || c.m_end - c.m0 >= BM);
+      const bool out_bf16 = p.out_kind == OUT_BF16 || p.out_kind == OUT_BF16_ACC;
+      const bool out_adds = p.out_kind == OUT_F32_ACC || p.out_kind == OUT_BF16_ACC;
       if (by_tma) {
         uint8_t* mine = epi_smem + (warp - 2) * 4096;
         const int out_row0 = (p.mode == MODE_GROUPED_K ? c.group * p.M : 0) + c.m0 + quad * 32;
         // a slab is 32 rows x 128 bytes: 64 bf16 columns, or 32 fp32 columns
-        const int slab_cols = p.out_kind == OUT_BF16 ? 64 : 32;
+        const int slab_cols = out_bf16 ? 64 : 32;
 #pragma unroll 1
         for (int col = col_begin; col < col_begin + EPI_COLS; col += slab_cols) {
           const int n = c.n0 + col;
@@ -333,7 +335,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
           }
           __syncwarp();
           uint8_t* rowp = slab + lane * 128;
-          if (p.out_kind == OUT_BF16) {
+          if (out_bf16) {
             uint32_t r0[32], r1[32];
             tmem_ld_x32(t_addr + col, r0);
             tmem_ld_x32(t_addr + col + 32, r1);
@@ -366,7 +368,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            if (p.out_kind == OUT_F32_ACC) tma_reduce_add_2d(&p.tmap_c, slab, n, out_row0);
+            if (out_adds) tma_reduce_add_2d(&p.tmap_c, slab, n, out_row0);   // in C's own type (fp32 or bf16)
             else tma_store_2d(&p.tmap_c, slab, n, out_row0);
             tma_store_commit();
           }
@@ -390,7 +392,12 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
         const int n = c.n0 + col;
         if (!row_ok || n >= p.N) continue;
         const int valid = min(32, p.N - n);
-        if (p.out_kind == OUT_BF16) {
+        if (out_bf16 && out_adds) {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + out_row * p.ldc + n;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (i < valid) dst[i] = __float2bfloat16(__bfloat162float(dst[i]) + __uint_as_float(r[i]));
+        } else if (out_bf16) {
           __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + out_row * p.ldc + n;
           if (valid == 32) {
 #pragma unroll
@@ -534,7 +541,7 @@ const char* gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   else        err = make_tmap_2d(&p.tmap_b, a.b, elem, a.b_outer, a.b_inner, a.ldb_bytes, bk, bn);
   if (err) return err;
   p.tma_store = 0;
-  const int c_elem = a.out_kind == OUT_BF16 ? 2 : 4;
+  const int c_elem = (a.out_kind == OUT_BF16 || a.out_kind == OUT_BF16_ACC) ? 2 : 4;
   if (a.ldc * c_elem % 16 == 0 && reinterpret_cast<uintptr_t>(a.c) % 16 == 0 &&
       (a.mode != MODE_GROUPED_K || a.M % BM == 0)) {
     // rows of C: every row the walk can touch (grouped rows: the sorted, padded row count;

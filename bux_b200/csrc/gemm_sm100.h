@@ -10,7 +10,7 @@ struct Status;
 
 enum { KIND_BF16 = 0, KIND_MXFP8 = 1 };
 enum { MODE_DENSE = 0, MODE_GROUPED_ROWS = 1, MODE_GROUPED_K = 2 };
-enum { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2 };
+enum { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACC = 2, OUT_BF16_ACC = 3 };  // *_ACC: C += A·B^T
 
 // Kernel parameters (passed by value as a __grid_constant__).
 struct GemmParams {

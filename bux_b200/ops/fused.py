@@ -195,13 +195,9 @@ class _SortedExperts(torch.autograd.Function):
         dout = dout.contiguous()
         g_gu = getattr(w_gu, "main_grad", None)
         g_down = getattr(w_down, "main_grad", None)
-        many = len(saved) > 1
-        # one range: the GEMM writes the gradient in the dtype it is kept in; several: fp32 sums
+        # the first range's GEMM writes the gradient in the dtype it is kept in; the GEMMs of the
+        # ranges after it add into that (the sum is rounded to that dtype after each range)
         acc_gu, acc_down = g_gu, g_down
-        if many and acc_gu is None:
-            acc_gu = torch.zeros(e, f2, d, dtype=torch.float32, device=x.device)
-        if many and acc_down is None:
-            acc_down = torch.zeros(e, d, f, dtype=torch.float32, device=x.device)
         if mx:
             gtq, gtsf, dtq, dtsf = ctx.wq
             ctx.wq = None
@@ -221,6 +217,7 @@ class _SortedExperts(torch.autograd.Function):
                 # dW_down[e] = dy_e^T · a'_e
                 dw_down = K.grouped_gemm_k(dytq, atq, offsets, d, f, kind=kind, asf=dytsf, bsf=atsf, out=acc_down,
                                            accumulate=acc_down is not None, out_dtype=_grad_dtype(w_down))
+                acc_down = dw_down
                 del dytq, dytsf, atq, atsf
                 # da' = dy · W_down (per expert, contraction over d)
                 da = K.grouped_gemm(dyq, dtq, offsets, f, d, kind=kind, asf=dysf, bsf=dtsf)
@@ -230,6 +227,7 @@ class _SortedExperts(torch.autograd.Function):
                 a = K.glu_fwd(h, act, w_row, limit, up_offset)
                 dw_down = K.grouped_gemm_k(dy, a, offsets, d, f, a_mn=True, b_mn=True, out=acc_down,
                                            accumulate=acc_down is not None, out_dtype=_grad_dtype(w_down))
+                acc_down = dw_down
                 da = K.grouped_gemm(dy, w_down.view(e * d, f), offsets, f, d, b_mn=True)
                 del a, dy
             # dh, and per row <da', glu(h)> = the gradient of that row's router weight
@@ -241,6 +239,7 @@ class _SortedExperts(torch.autograd.Function):
                 del dh
                 dw_gu = K.grouped_gemm_k(htq, xtq, offsets, f2, d, kind=kind, asf=htsf, bsf=xtsf, out=acc_gu,
                                          accumulate=acc_gu is not None, out_dtype=_grad_dtype(w_gu))
+                acc_gu = dw_gu
                 del htq, htsf, xtq, xtsf
                 dxs = K.grouped_gemm(hq, gtq, offsets, d, f2, kind=kind, asf=hsf, bsf=gtsf)
                 del hq, hsf
@@ -248,6 +247,7 @@ class _SortedExperts(torch.autograd.Function):
                 xs = K.gather_rows(xc, row_index, rows)
                 dw_gu = K.grouped_gemm_k(dh, xs, offsets, f2, d, a_mn=True, b_mn=True, out=acc_gu,
                                          accumulate=acc_gu is not None, out_dtype=_grad_dtype(w_gu))
+                acc_gu = dw_gu
                 dxs = K.grouped_gemm(dh, w_gu.view(e * f2, d), offsets, d, f2, b_mn=True)
                 del xs, dh
             K.combine_rows_into(dxs, pos, None, dx[c * tc:(c + 1) * tc])

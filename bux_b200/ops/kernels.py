@@ -14,7 +14,7 @@ from . import _build, checks
 
 KIND_BF16, KIND_MXFP8 = 0, 1
 MODE_DENSE, MODE_GROUPED_ROWS, MODE_GROUPED_K = 0, 1, 2
-OUT_BF16, OUT_F32, OUT_F32_ACC = 0, 1, 2
+OUT_BF16, OUT_F32, OUT_F32_ACC, OUT_BF16_ACC = 0, 1, 2, 3
 ACT_KINDS = {"swish": 0, "quick_gelu": 1, "gelu_tanh": 2, "relu2": 3}
 
 _status: dict = {}
@@ -130,7 +130,10 @@ def grouped_gemm_k(a, b, offsets: torch.Tensor, m: int, n: int, *, kind: int = K
         accumulate = False
     if kind == KIND_MXFP8:
         a, b = a.view(torch.uint8), b.view(torch.uint8)
-    okind = OUT_BF16 if out.dtype == torch.bfloat16 else (OUT_F32_ACC if accumulate else OUT_F32)
+    if out.dtype == torch.bfloat16:
+        okind = OUT_BF16_ACC if accumulate else OUT_BF16   # the sum is rounded to bf16 after every call
+    else:
+        okind = OUT_F32_ACC if accumulate else OUT_F32
     ops().gemm(a, b, out, asf, bsf, offsets, status_word(a.device), kind, MODE_GROUPED_K, m, n, ktot,
                ktot, groups, a_mn, b_mn, okind, bn, sms)
     _count()

@@ -350,11 +350,9 @@ class _FusedExperts(torch.autograd.Function):
         cap = ep.cap
         g_gu = getattr(w_gu, "main_grad", None)
         g_down = getattr(w_down, "main_grad", None)
-        acc_gu, acc_down = g_gu, g_down
-        if chunks > 1 and acc_gu is None:
-            acc_gu = torch.zeros(e, f2, d, dtype=torch.float32, device=x.device)
-        if chunks > 1 and acc_down is None:
-            acc_down = torch.zeros(e, d, f, dtype=torch.float32, device=x.device)
+        # the first chunk's GEMMs write the weight gradients in the dtype they are kept in; the
+        # later chunks' add into them
+        acc = {"gu": g_gu, "down": g_down}
         if mx:
             gtq, gtsf, dtq, dtsf = wq
         dx = torch.empty_like(x)
@@ -392,18 +390,18 @@ class _FusedExperts(torch.autograd.Function):
                 dytq, dytsf = K.requant_mxfp8_cols(dyq, dysf, cap, d)
                 _, _, atq, atsf = K.quant_mxfp8_glu(h, None, act, rowwise=False, colwise=True, limit=limit,
                                                     up_offset=up_offset, row_scale=w_row)
-                result["down"] = K.grouped_gemm_k(dytq, atq, r.offsets, d, f, kind=kind, asf=dytsf, bsf=atsf,
-                                                  out=acc_down, accumulate=acc_down is not None,
-                                                  out_dtype=fused._grad_dtype(w_down))
+                result["down"] = acc["down"] = K.grouped_gemm_k(
+                    dytq, atq, r.offsets, d, f, kind=kind, asf=dytsf, bsf=atsf, out=acc["down"],
+                    accumulate=acc["down"] is not None, out_dtype=fused._grad_dtype(w_down))
                 del dytq, dytsf, atq, atsf
                 da = K.grouped_gemm(dyq, dtq, r.offsets, f, d, kind=kind, asf=dysf, bsf=dtsf)
             else:
                 dy = ep.bufs[("dy", slot)]
                 K.zero_pad_rows(dy, r.offsets, r.counts)
                 a = K.glu_fwd(h, act, w_row, limit, up_offset)
-                result["down"] = K.grouped_gemm_k(dy, a, r.offsets, d, f, a_mn=True, b_mn=True, out=acc_down,
-                                                  accumulate=acc_down is not None,
-                                                  out_dtype=fused._grad_dtype(w_down))
+                result["down"] = acc["down"] = K.grouped_gemm_k(
+                    dy, a, r.offsets, d, f, a_mn=True, b_mn=True, out=acc["down"],
+                    accumulate=acc["down"] is not None, out_dtype=fused._grad_dtype(w_down))
                 da = K.grouped_gemm(dy, w_down.view(e * d, f), r.offsets, f, d, b_mn=True)
                 del a
             # dh, and <da', glu(h)> per row (the router weight's gradient) straight into the slot
@@ -412,14 +410,15 @@ class _FusedExperts(torch.autograd.Function):
             if mx:
                 hq, hsf, htq, htsf = K.quant_mxfp8(dh, rowwise=True, colwise=True)
                 del dh
-                result["gu"] = K.grouped_gemm_k(htq, xsave, r.offsets, f2, d, kind=kind, asf=htsf, bsf=xtsf,
-                                                out=acc_gu, accumulate=acc_gu is not None,
-                                                out_dtype=fused._grad_dtype(w_gu))
+                result["gu"] = acc["gu"] = K.grouped_gemm_k(
+                    htq, xsave, r.offsets, f2, d, kind=kind, asf=htsf, bsf=xtsf, out=acc["gu"],
+                    accumulate=acc["gu"] is not None, out_dtype=fused._grad_dtype(w_gu))
                 del htq, htsf
                 K.grouped_gemm(hq, gtq, r.offsets, d, f2, kind=kind, asf=hsf, bsf=gtsf, out=dx_out)
             else:
-                result["gu"] = K.grouped_gemm_k(dh, xsave, r.offsets, f2, d, a_mn=True, b_mn=True, out=acc_gu,
-                                                accumulate=acc_gu is not None, out_dtype=fused._grad_dtype(w_gu))
+                result["gu"] = acc["gu"] = K.grouped_gemm_k(
+                    dh, xsave, r.offsets, f2, d, a_mn=True, b_mn=True, out=acc["gu"],
+                    accumulate=acc["gu"] is not None, out_dtype=fused._grad_dtype(w_gu))
                 K.grouped_gemm(dh, w_gu.view(e * f2, d), r.offsets, d, f2, b_mn=True, out=dx_out)
             dx_epoch[c] = ep.signal(CH_DX)
 

@@ -108,6 +108,12 @@ def test_grouped_gemm_contraction(cuda):
                         for g in range(len(counts))])
     got = K.grouped_gemm_k(dy, x, offsets, m, n, a_mn=True, b_mn=True)
     assert rel_err(got, want) < 1e-2
+    # gradients kept in bf16: written by one call, added to by the next (the chunks of a step)
+    first = K.grouped_gemm_k(dy, x, offsets, m, n, a_mn=True, b_mn=True, out_dtype=torch.bfloat16)
+    assert first.dtype == torch.bfloat16 and rel_err(first, want) < 1e-2
+    again = K.grouped_gemm_k(dy, x, offsets, m, n, a_mn=True, b_mn=True, out=first, accumulate=True)
+    assert again is first and rel_err(first, 2 * want) < 1e-2
+    assert first[1].abs().max() == 0   # the empty group stays zero
 
 
 def test_rmsnorm(cuda):
