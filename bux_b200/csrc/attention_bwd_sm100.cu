@@ -64,7 +64,7 @@ struct AttnBwdParams {
   alignas(64) CUtensorMap tmap_dq;
   const float* lse; const float* delta;
   const int* row_lo; const int* key_hi;  // documents: see AttnArgs
-  float* dq; void* dk; void* dv; Status* status;
+  float* dq; void* dk; void* dv; Status* status; unsigned int* phase_cycles;
   int B, T, S, H, G;
   float scale, scale_log2; int causal, window;
 };
@@ -74,10 +74,28 @@ struct AttnBwdCfg {
   static constexpr int DC = D / 64;
   static constexpr int TILE_BYTES = DC * 16384;
   static constexpr int PS_BYTES = 2 * 16384;
-  static constexpr int SMEM_BYTES = 4 * TILE_BYTES + 2 * PS_BYTES + 1024 + 256;
+  // K, V, two Q buffers, dO, P, dS
+  static constexpr int SMEM_BYTES = 5 * TILE_BYTES + 2 * PS_BYTES + 1024 + 256;
   static constexpr int TMEM_COLS = 512;  // S | dP,dQ | dV | dK  (128 columns each)
 };
 
+// Barrier slots (one 8-byte word each).
+enum BwdBar {
+  B_KV_FULL = 0, B_Q_FULL0, B_Q_FULL1, B_Q_FREE0, B_Q_FREE1, B_DO_FULL, B_DO_FREE, B_S_FULL, B_S_READ,
+  B_DP_FULL, B_PDS_READY, B_DQ_FULL, B_DQ_DONE, B_COUNT
+};
+
+// Schedule. Step s pairs the key tile with one (query head, query tile).
+//
+//   tensor core, step s:  dV += P(s)^T·dO | dQ(s) = dS·K | dK += dS^T·Q(s) | dP(s+1) = dO·V^T | S(s+2) = Q·K^T
+//   softmax warps:        P(s+1) from S(s+1), kept in registers while the step's MMAs run;
+//                         dQ(s) out of tensor memory into the P and dS tiles (free once dV and dK
+//                         have run), TMA reduce-adds of fp32 from both; dS(s+1) from dP(s+1) while
+//                         those reduces read shared memory; then P(s+1) and dS(s+1) are stored
+//                         over the staged halves and the next step's MMAs start.
+//
+// Q has two buffers (S runs two steps ahead of dK), dO one (it is free after dV, the step's first
+// MMA). dQ shares dP's columns of tensor memory: dP(s+1) is issued once the warps have read dQ(s).
 template <int D>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
@@ -87,23 +105,28 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
   uint8_t* sV = sK + Cfg::TILE_BYTES;
-  uint8_t* sQ = sV + Cfg::TILE_BYTES;
-  uint8_t* sdO = sQ + Cfg::TILE_BYTES;
+  uint8_t* sQ = sV + Cfg::TILE_BYTES;          // two buffers
+  uint8_t* sdO = sQ + 2 * Cfg::TILE_BYTES;
   uint8_t* sP = sdO + Cfg::TILE_BYTES;
   uint8_t* sdS = sP + Cfg::PS_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + Cfg::PS_BYTES);
-  uint64_t* kv_full = bars;
-  uint64_t* qdo_full = bars + 1;
-  uint64_t* qdo_empty = bars + 2;
-  uint64_t* sdp_full = bars + 3;
-  uint64_t* p_ready = bars + 4;
-  uint64_t* dq_full = bars + 5;
-  uint64_t* dq_done = bars + 6;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  unsigned int* phase = reinterpret_cast<unsigned int*>(bars + B_COUNT + 1);   // 32 counters
 
   const int warp = threadIdx.x >> 5;
   const int jt = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+  // phase timers: one thread of softmax warp 0 and the MMA issuer of the first CTA add the
+  // cycles since their last mark to a counter in shared memory
+  const bool timed = p.phase_cycles != nullptr && (blockIdx.x | blockIdx.y | blockIdx.z) == 0 &&
+                     (threadIdx.x == 0 || warp == 9);
+  unsigned int t_mark = timed ? (unsigned int)clock64() : 0u;
+#define BWD_MARK(slot)                                     \
+  if (timed) {                                             \
+    const unsigned int t_now = (unsigned int)clock64();    \
+    atomicAdd(&phase[(slot)], t_now - t_mark);             \
+    t_mark = t_now;                                        \
+  }
   const int kv0 = jt * BT;
   const int shift = p.S - p.T;
   const int n_qt = (p.T + BT - 1) / BT;
@@ -118,9 +141,15 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
   Status* st = p.status;
 
   if (threadIdx.x == 0) {
-    mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(qdo_empty, 1); mbar_init(sdp_full, 1);
-    mbar_init(p_ready, 256); mbar_init(dq_full, 1); mbar_init(dq_done, 256);
+    mbar_init(bars + B_KV_FULL, 1);
+    mbar_init(bars + B_Q_FULL0, 1); mbar_init(bars + B_Q_FULL1, 1);
+    mbar_init(bars + B_Q_FREE0, 1); mbar_init(bars + B_Q_FREE1, 1);
+    mbar_init(bars + B_DO_FULL, 1); mbar_init(bars + B_DO_FREE, 1);
+    mbar_init(bars + B_S_FULL, 1); mbar_init(bars + B_S_READ, 256);
+    mbar_init(bars + B_DP_FULL, 1); mbar_init(bars + B_PDS_READY, 256);
+    mbar_init(bars + B_DQ_FULL, 1); mbar_init(bars + B_DQ_DONE, 256);
     *abort_flag = 0;
+    for (int i = 0; i < 32; ++i) phase[i] = 0;
     mbar_fence_init();
   }
   if (warp == 9) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
@@ -129,23 +158,42 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dv = tmem_base + 256, t_dk = tmem_base + 384;
+#define BWD_WAIT(slot, parity, site) mbar_wait(bars + (slot), (parity), abort_flag, st, KID_ATTN_BWD, (site))
 
   if (warp == 8) {
     // -------------------------------------------------------------- TMA producer
     if (elect_one() && n_steps > 0) {
-      mbar_expect_tx(kv_full, 2 * Cfg::TILE_BYTES);
-      for (int c = 0; c < DC; ++c) {
-        tma_load_2d(sK + c * 16384, &p.tmap_k, g * D + c * 64, b * p.S + kv0, kv_full);
-        tma_load_2d(sV + c * 16384, &p.tmap_v, g * D + c * 64, b * p.S + kv0, kv_full);
-      }
-      for (int s = 0; s < n_steps; ++s) {
-        if (!mbar_wait(qdo_empty, (s & 1) ^ 1, abort_flag, st, KID_ATTN_BWD, 1)) break;
+      auto load_q = [&](int s) {
         const int h = g * hpg + s / per_head;
         const int row = b * p.T + (i_lo + s % per_head) * BT;
-        mbar_expect_tx(qdo_full, 2 * Cfg::TILE_BYTES);
-        for (int c = 0; c < DC; ++c) {
-          tma_load_2d(sQ + c * 16384, &p.tmap_q, h * D + c * 64, row, qdo_full);
-          tma_load_2d(sdO + c * 16384, &p.tmap_do, h * D + c * 64, row, qdo_full);
+        uint64_t* full = bars + B_Q_FULL0 + (s & 1);
+        mbar_expect_tx(full, Cfg::TILE_BYTES);
+        for (int c = 0; c < DC; ++c)
+          tma_load_2d(sQ + (s & 1) * Cfg::TILE_BYTES + c * 16384, &p.tmap_q, h * D + c * 64, row, full);
+      };
+      auto load_do = [&](int s) {
+        const int h = g * hpg + s / per_head;
+        const int row = b * p.T + (i_lo + s % per_head) * BT;
+        mbar_expect_tx(bars + B_DO_FULL, Cfg::TILE_BYTES);
+        for (int c = 0; c < DC; ++c) tma_load_2d(sdO + c * 16384, &p.tmap_do, h * D + c * 64, row, bars + B_DO_FULL);
+      };
+      mbar_expect_tx(bars + B_KV_FULL, 2 * Cfg::TILE_BYTES);
+      for (int c = 0; c < DC; ++c) {
+        tma_load_2d(sK + c * 16384, &p.tmap_k, g * D + c * 64, b * p.S + kv0, bars + B_KV_FULL);
+        tma_load_2d(sV + c * 16384, &p.tmap_v, g * D + c * 64, b * p.S + kv0, bars + B_KV_FULL);
+      }
+      load_q(0);
+      load_do(0);
+      if (n_steps > 1) load_q(1);
+      for (int s = 0; s < n_steps; ++s) {
+        // dO(s+1) once dP(s) and dV(s) have read dO(s); Q(s+2) once dK(s) has read Q(s)
+        if (s + 1 < n_steps) {
+          if (!BWD_WAIT(B_DO_FREE, s & 1, 1)) break;
+          load_do(s + 1);
+        }
+        if (s + 2 < n_steps) {
+          if (!BWD_WAIT(B_Q_FREE0 + (s & 1), (s >> 1) & 1, 2)) break;
+          load_q(s + 2);
         }
       }
     }
@@ -155,163 +203,233 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
       const uint32_t id_s = make_idesc(FMT_BF16, FMT_BF16, 128, BT, false, false);
       const uint32_t id_acc = make_idesc(FMT_BF16, FMT_BF16, 128, D, true, true);
       const uint32_t id_dq = make_idesc(FMT_BF16, FMT_BF16, 128, D, false, true);
-      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), aDO = smem_u32(sdO);
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ0 = smem_u32(sQ), aDO = smem_u32(sdO);
       const uint32_t aP = smem_u32(sP), aDS = smem_u32(sdS);
-      bool ok = mbar_wait(kv_full, 0, abort_flag, st, KID_ATTN_BWD, 2);
-      for (int s = 0; s < n_steps && ok; ++s) {
-        ok = mbar_wait(qdo_full, s & 1, abort_flag, st, KID_ATTN_BWD, 3);
-        if (!ok) break;
-        tc_fence_after();
-        // S has columns of its own (read before p_ready of the step before): it runs while
-        // the previous dQ, which shares dP's columns, is still being drained
+      auto issue_s = [&](int s) {   // S(s) = Q(s)·K^T
+        const uint32_t aQ = aQ0 + (s & 1) * Cfg::TILE_BYTES;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
           mma_f16(t_s, make_smem_desc(aQ + off, 0, 1024, 2), make_smem_desc(aK + off, 0, 1024, 2), id_s, kk > 0);
         }
-        if (s > 0) ok = mbar_wait(dq_done, (s - 1) & 1, abort_flag, st, KID_ATTN_BWD, 4);
-        if (!ok) break;
-        tc_fence_after();
+        tc_commit(bars + B_S_FULL);
+      };
+      auto issue_dp = [&]() {       // dP = dO·V^T
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
           mma_f16(t_dp, make_smem_desc(aDO + off, 0, 1024, 2), make_smem_desc(aV + off, 0, 1024, 2), id_s, kk > 0);
         }
-        tc_commit(sdp_full);
-        ok = mbar_wait(p_ready, s & 1, abort_flag, st, KID_ATTN_BWD, 5);
+        tc_commit(bars + B_DP_FULL);
+      };
+      bool ok = BWD_WAIT(B_KV_FULL, 0, 3) && BWD_WAIT(B_Q_FULL0, 0, 4);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+        ok = BWD_WAIT(B_DO_FULL, 0, 5);
+      }
+      if (ok) {
+        tc_fence_after();
+        issue_dp();
+        if (n_steps > 1) {
+          ok = BWD_WAIT(B_Q_FULL1, 0, 7) && BWD_WAIT(B_S_READ, 0, 8);
+          if (ok) { tc_fence_after(); issue_s(1); }
+        }
+      }
+      for (int s = 0; s < n_steps && ok; ++s) {
+        const uint32_t aQ = aQ0 + (s & 1) * Cfg::TILE_BYTES;
+        BWD_MARK(17)
+        ok = BWD_WAIT(B_PDS_READY, s & 1, 9);
         if (!ok) break;
+        BWD_MARK(16)
+        if (timed) atomicAdd(&phase[23], 1u);
         tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < BT / 16; ++kk) {  // contraction over the 128 query rows
-          const uint64_t pa = make_smem_desc(aP + kk * 2048, 16384, 1024, 2);
-          const uint64_t dsa = make_smem_desc(aDS + kk * 2048, 16384, 1024, 2);
-          const uint64_t dob = make_smem_desc(aDO + kk * 2048, 16384, 1024, 2);
-          const uint64_t qb = make_smem_desc(aQ + kk * 2048, 16384, 1024, 2);
-          mma_f16(t_dv, pa, dob, id_acc, (s > 0 || kk > 0) ? 1u : 0u);
-          mma_f16(t_dk, dsa, qb, id_acc, (s > 0 || kk > 0) ? 1u : 0u);
-        }
+        for (int kk = 0; kk < BT / 16; ++kk)    // dV += P^T·dO (contraction over the 128 query rows)
+          mma_f16(t_dv, make_smem_desc(aP + kk * 2048, 16384, 1024, 2), make_smem_desc(aDO + kk * 2048, 16384, 1024, 2),
+                  id_acc, (s > 0 || kk > 0) ? 1u : 0u);
+        tc_commit(bars + B_DO_FREE);
 #pragma unroll
-        for (int kk = 0; kk < BT / 16; ++kk) {  // contraction over the 128 keys
+        for (int kk = 0; kk < BT / 16; ++kk) {  // dQ(s) = dS·K, contraction over the 128 keys, into dP's columns
           const uint64_t dsa = make_smem_desc(aDS + (kk >> 2) * 16384 + (kk & 3) * 32, 0, 1024, 2);
-          const uint64_t kb = make_smem_desc(aK + kk * 2048, 16384, 1024, 2);
-          mma_f16(t_dp, dsa, kb, id_dq, kk > 0);
+          mma_f16(t_dp, dsa, make_smem_desc(aK + kk * 2048, 16384, 1024, 2), id_dq, kk > 0);
         }
-        tc_commit(dq_full);
-        tc_commit(qdo_empty);
+        tc_commit(bars + B_DQ_FULL);
+#pragma unroll
+        for (int kk = 0; kk < BT / 16; ++kk)    // dK += dS^T·Q(s)
+          mma_f16(t_dk, make_smem_desc(aDS + kk * 2048, 16384, 1024, 2), make_smem_desc(aQ + kk * 2048, 16384, 1024, 2),
+                  id_acc, (s > 0 || kk > 0) ? 1u : 0u);
+        tc_commit(bars + B_Q_FREE0 + (s & 1));
+        if (s + 1 >= n_steps) break;
+        BWD_MARK(17)
+        ok = BWD_WAIT(B_DQ_DONE, s & 1, 10);
+        BWD_MARK(18)
+        ok = ok && BWD_WAIT(B_DO_FULL, (s + 1) & 1, 11);
+        if (!ok) break;
+        BWD_MARK(19)
+        tc_fence_after();
+        issue_dp();
+        if (s + 2 < n_steps) {
+          BWD_MARK(17)
+          ok = BWD_WAIT(B_Q_FULL0 + (s & 1), ((s + 2) >> 1) & 1, 13);
+          BWD_MARK(21)
+          ok = ok && BWD_WAIT(B_S_READ, (s + 1) & 1, 14);
+          if (!ok) break;
+          BWD_MARK(22)
+          tc_fence_after();
+          issue_s(s + 2);
+        }
       }
     }
   } else {
     // -------------------------------------------------------------- softmax / drain warps
     // Two warps share each 32-lane quadrant of tensor memory: warps 0-3 take the first 64
-    // columns of S / dP, warps 4-7 the other 64, so each scheduler has two warps to
-    // interleave and the exp / dS chain per step is half as long.
+    // columns of S / dP, warps 4-7 the other 64.
     const int r = threadIdx.x & 127, lane = threadIdx.x & 31, half = warp >> 2;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const int c_first = half * 64;
+    const int base = half * 16384 + r * 128;   // this thread's 128 bytes of the P / dS tiles
     bool ok = true;
-    for (int s = 0; s < n_steps && ok; ++s) {
+    // the step ahead's row statistics, loaded a phase before they are used
+    auto row_stats = [&](int s, float& lse2, float& ndlt, int& lo_key, int& hi_key, bool& any_row) {
       const int h = g * hpg + s / per_head;
       const int q = (i_lo + s % per_head) * BT + r;
       const bool row_ok = q < p.T;
       const size_t stat = ((size_t)b * p.H + h) * p.T + (row_ok ? q : 0);
-      const float lse2 = row_ok ? p.lse[stat] * LOG2E_B : 0.f;
-      const float dlt = row_ok ? p.delta[stat] : 0.f;
-      const int hi_key = p.causal ? q + shift : p.S - 1;
-      int lo_key = p.window > 0 ? q + shift - p.window + 1 : 0;
+      lse2 = row_ok ? p.lse[stat] * LOG2E_B : 0.f;
+      ndlt = row_ok ? -p.delta[stat] * p.scale : 0.f;
+      hi_key = p.causal ? q + shift : p.S - 1;
+      lo_key = p.window > 0 ? q + shift - p.window + 1 : 0;
       if (p.row_lo != nullptr && row_ok) lo_key = max(lo_key, p.row_lo[(size_t)b * p.T + q]);
-      ok = warp_all(mbar_wait(sdp_full, s & 1, abort_flag, st, KID_ATTN_BWD, 6));
-      if (!ok) break;
-      tc_fence_after();
-      // the dQ tile of the previous step was staged where P and dS go: its reduction must
-      // have read this warp's rows before they are overwritten
-      if (lane == 0) tma_store_wait_read();
-      __syncwarp();
-      const bool full_row = row_ok && kv0 + BT - 1 <= hi_key && kv0 >= lo_key && kv0 + BT <= p.S && lse2 > -INFINITY;
-      const bool any_row = row_ok && lse2 > -INFINITY;
-      const int c_first = half * 64;
-      const float nlse2 = -lse2, ndlt = -dlt * p.scale;
-#pragma unroll 1
-      for (int ci = 0; ci < 2; ++ci) {
-        const int c = c_first + ci * 32;
-        uint32_t cs[32], cd[32];
-        tmem_ld_x32(t_s + lane_addr + c, cs);
-        tmem_ld_x32(t_dp + lane_addr + c, cd);
-        tmem_ld_wait();
-        uint32_t pp[16], ds[16];
-        if (full_row) {
+      any_row = row_ok && lse2 > -INFINITY;
+    };
+    float lse2 = 0.f, ndlt = 0.f;
+    int lo_key = 0, hi_key = 0;
+    bool any_row = false;
+    if (n_steps > 0) row_stats(0, lse2, ndlt, lo_key, hi_key, any_row);
+
+    // step s = -1 only prepares step 0 (its P and dS); step n_steps - 1 only drains
+    for (int s = -1; s < n_steps && ok; ++s) {
+      const bool ahead = s + 1 < n_steps;
+      uint32_t pp[32];                          // P(s+1), bf16 pairs, this thread's 64 columns
+      const float ndlt_next = ndlt;             // -delta·scale of P(s+1)'s row
+      BWD_MARK(13)
+      if (ahead) {
+        // ---- P(s+1) = exp(S·scale − lse), into registers, while the tensor core runs step s
+        const bool full_row = any_row && kv0 + BT - 1 <= hi_key && kv0 >= lo_key && kv0 + BT <= p.S;
+        const float nlse2 = -lse2;
+        ok = warp_all(BWD_WAIT(B_S_FULL, (s + 1) & 1, 15));
+        if (!ok) break;
+        BWD_MARK(4)
+        tc_fence_after();
+        uint32_t cs[2][32];
+        tmem_ld_x32(t_s + lane_addr + c_first, cs[0]);
+        tmem_ld_x32(t_s + lane_addr + c_first + 32, cs[1]);
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            // P = 2^(s·scale·log2e − lse·log2e); dS = P·(dP·scale − delta·scale)
-            const float p0 = ex2_approx(fmaf(__uint_as_float(cs[i]), p.scale_log2, nlse2));
-            const float p1 = ex2_approx(fmaf(__uint_as_float(cs[i + 1]), p.scale_log2, nlse2));
-            pp[i >> 1] = pack_bf16(p0, p1);
-            ds[i >> 1] = pack_bf16(p0 * fmaf(__uint_as_float(cd[i]), p.scale, ndlt),
-                                   p1 * fmaf(__uint_as_float(cd[i + 1]), p.scale, ndlt));
-          }
-        } else {
+        for (int ci = 0; ci < 2; ++ci) {
+          if (ci == 0) tmem_ld_wait();          // both loads were issued: the second is done as well
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float pr[2], dr[2];
+          for (int i = 0; i < 32; i += 2)
+            pp[ci * 16 + (i >> 1)] = pack_bf16(ex2_approx(fmaf(__uint_as_float(cs[ci][i]), p.scale_log2, nlse2)),
+                                               ex2_approx(fmaf(__uint_as_float(cs[ci][i + 1]), p.scale_log2, nlse2)));
+        }
+        tc_fence_before();
+        mbar_arrive(bars + B_S_READ);           // S(s+1) is in registers: S(s+2) may overwrite it
+        if (!full_row) {
+          // rows that the tile's keys only partly see (the diagonal, a window's edge, a document
+          // start, the sequence end): the hidden keys' probabilities are cleared afterwards
+          const int first = any_row ? max(lo_key - kv0, 0) : BT;          // visible columns: [first, last]
+          const int last = min(min(hi_key, p.S - 1) - kv0, BT - 1);
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int kv = kv0 + c + i + e;
-              const bool keep = any_row && kv < p.S && kv <= hi_key && kv >= lo_key;
-              pr[e] = keep ? ex2_approx(fmaf(__uint_as_float(cs[i + e]), p.scale_log2, nlse2)) : 0.f;
-              dr[e] = pr[e] * fmaf(__uint_as_float(cd[i + e]), p.scale, ndlt);
-            }
-            pp[i >> 1] = pack_bf16(pr[0], pr[1]);
-            ds[i >> 1] = pack_bf16(dr[0], dr[1]);
+          for (int k2 = 0; k2 < 32; ++k2) {
+            const int c0 = c_first + 2 * k2;
+            const uint32_t keep = (c0 >= first && c0 <= last ? 0x0000ffffu : 0u) |
+                                  (c0 + 1 >= first && c0 + 1 <= last ? 0xffff0000u : 0u);
+            pp[k2] &= keep;
           }
         }
-        const int base = half * 16384 + r * 128;
-#pragma unroll
-        for (int sl = 0; sl < 4; ++sl) {
-          const int slot = ((ci << 2) + sl) ^ (r & 7);
-          *reinterpret_cast<uint4*>(sP + base + (slot << 4)) = make_uint4(pp[4 * sl], pp[4 * sl + 1], pp[4 * sl + 2], pp[4 * sl + 3]);
-          *reinterpret_cast<uint4*>(sdS + base + (slot << 4)) = make_uint4(ds[4 * sl], ds[4 * sl + 1], ds[4 * sl + 2], ds[4 * sl + 3]);
-        }
+        if (s + 2 < n_steps) row_stats(s + 2, lse2, ndlt, lo_key, hi_key, any_row);
+        BWD_MARK(5)
       }
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(p_ready);
-      // dQ of this step: tensor memory -> this warp's rows of the staging tiles (the P / dS
-      // buffers, free once the step's MMAs have completed) -> one reduce-add per 32 columns
-      ok = warp_all(mbar_wait(dq_full, s & 1, abort_flag, st, KID_ATTN_BWD, 7));
-      if (!ok) break;
-      tc_fence_after();
-      // This warp stages the 32-column chunks half, half+2, ... of its 32 rows: the
-      // same shared-memory rows it writes P and dS to, so every hazard on the staging
-      // tiles stays inside the warp.
-      {
+      if (s >= 0) {
+        // ---- dQ(s): tensor memory → registers (dP(s+1) may then be issued) → the P tile and the
+        // dS tile, both free once dK(s), the step's last MMA to read them, has run → TMA reduce-adds
+        const int h = g * hpg + s / per_head;
+        ok = warp_all(BWD_WAIT(B_DQ_FULL, s & 1, 18));
+        if (!ok) break;
+        BWD_MARK(8)
+        tc_fence_after();
         uint32_t v[D / 64][32];
 #pragma unroll
         for (int j = 0; j < D / 64; ++j) tmem_ld_x32(t_dp + lane_addr + (half + 2 * j) * 32, v[j]);
         tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < D / 64; ++j) {
-          uint8_t* dst = sP + (half + 2 * j) * 16384 + r * 128;
-#pragma unroll
-          for (int sl = 0; sl < 8; ++sl)
-            *reinterpret_cast<uint4*>(dst + ((sl ^ (r & 7)) << 4)) =
-                make_uint4(v[j][4 * sl], v[j][4 * sl + 1], v[j][4 * sl + 2], v[j][4 * sl + 3]);
-        }
-      }
-      tc_fence_before();
-      mbar_arrive(dq_done);
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
+        tc_fence_before();
+        mbar_arrive(bars + B_DQ_DONE);
+        BWD_MARK(9)
+        ok = warp_all(BWD_WAIT(B_Q_FREE0 + (s & 1), (s >> 1) & 1, 19));
+        if (!ok) break;
+        BWD_MARK(10)
         const int row0 = b * p.T + (i_lo + s % per_head) * BT + (warp & 3) * 32;
 #pragma unroll
         for (int j = 0; j < D / 64; ++j) {
-          const int ci = half + 2 * j;
-          tma_reduce_add_2d(&p.tmap_dq, sP + ci * 16384 + (warp & 3) * 4096, h * D + ci * 32, row0);
+          uint8_t* tile = j == 0 ? sP : sdS;
+#pragma unroll
+          for (int sl = 0; sl < 8; ++sl)
+            *reinterpret_cast<uint4*>(tile + base + ((sl ^ (r & 7)) << 4)) =
+                make_uint4(v[j][4 * sl], v[j][4 * sl + 1], v[j][4 * sl + 2], v[j][4 * sl + 3]);
         }
-        tma_store_commit();
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+#pragma unroll
+          for (int j = 0; j < D / 64; ++j)
+            tma_reduce_add_2d(&p.tmap_dq, (j == 0 ? sP : sdS) + half * 16384 + (warp & 3) * 4096,
+                              h * D + (half + 2 * j) * 32, row0);
+          tma_store_commit();
+        }
+        BWD_MARK(11)
+      }
+      if (ahead) {
+        // ---- dS(s+1) = P∘(dP·scale − delta·scale), then both tiles of step s+1 are stored
+        ok = warp_all(BWD_WAIT(B_DP_FULL, (s + 1) & 1, 17));
+        if (!ok) break;
+        BWD_MARK(0)
+        tc_fence_after();
+        uint32_t ds[32];
+        uint32_t cd[2][32];
+        tmem_ld_x32(t_dp + lane_addr + c_first, cd[0]);
+        tmem_ld_x32(t_dp + lane_addr + c_first + 32, cd[1]);
+        tmem_ld_wait();
+#pragma unroll
+        for (int ci = 0; ci < 2; ++ci) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float2 pv = unpack_bf16(pp[ci * 16 + (i >> 1)]);
+            ds[ci * 16 + (i >> 1)] = pack_bf16(pv.x * fmaf(__uint_as_float(cd[ci][i]), p.scale, ndlt_next),
+                                               pv.y * fmaf(__uint_as_float(cd[ci][i + 1]), p.scale, ndlt_next));
+          }
+        }
+        tc_fence_before();
+        BWD_MARK(1)
+        // both halves of dQ(s) were staged in this warp's rows of the two tiles
+        if (lane == 0) tma_store_wait_read();
+        __syncwarp();
+        BWD_MARK(2)
+#pragma unroll
+        for (int sl = 0; sl < 8; ++sl) {
+          *reinterpret_cast<uint4*>(sP + base + ((sl ^ (r & 7)) << 4)) =
+              make_uint4(pp[4 * sl], pp[4 * sl + 1], pp[4 * sl + 2], pp[4 * sl + 3]);
+          *reinterpret_cast<uint4*>(sdS + base + ((sl ^ (r & 7)) << 4)) =
+              make_uint4(ds[4 * sl], ds[4 * sl + 1], ds[4 * sl + 2], ds[4 * sl + 3]);
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(bars + B_PDS_READY);
+        BWD_MARK(3)
       }
     }
     if (lane == 0) tma_store_wait_all();
     __syncwarp();
-    // dK / dV of this key tile: complete once the last step's MMAs have (dq_full waited above)
+    // the last step's dK (and with it every MMA of the walk) is complete
     // tcgen05.ld is warp-collective: every thread of the warp takes part, only the
     // stores are masked.
     const int kv = kv0 + r;
@@ -348,6 +466,8 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
 
   tc_fence_before();
   __syncthreads();
+  if (p.phase_cycles != nullptr && (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && threadIdx.x < 32)
+    atomicAdd(&p.phase_cycles[threadIdx.x], phase[threadIdx.x]);
   if (*abort_flag) {
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
     __syncthreads();
@@ -368,7 +488,7 @@ static const char* attn_bwd_launch_d(const AttnArgs& a, cudaStream_t stream) {
   if ((err = make_tmap_2d(&p.tmap_dq, a.dq, 4, (uint64_t)a.B * a.T, qw, qw * 4, 32, 32))) return err;
   p.row_lo = a.row_lo; p.key_hi = a.key_hi;
   p.lse = a.lse; p.delta = a.delta; p.dq = reinterpret_cast<float*>(a.dq); p.dk = a.dk; p.dv = a.dv;
-  p.status = a.status;
+  p.status = a.status; p.phase_cycles = a.phase_cycles;
   p.B = a.B; p.T = a.T; p.S = a.S; p.H = a.H; p.G = a.G;
   p.scale = a.scale; p.scale_log2 = a.scale * LOG2E_B; p.causal = a.causal ? 1 : 0; p.window = a.window;
   auto kern = attn_bwd_kernel<D>;

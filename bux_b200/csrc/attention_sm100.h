@@ -25,6 +25,9 @@ struct AttnArgs {
   int B = 0, T = 0, S = 0, H = 0, G = 0, D = 0;
   float scale = 1.f; bool causal = true; int window = 0;
   Status* status = nullptr;
+  // backward only, optional: 32 counters that the CTA of the first key tile adds the cycles of
+  // its phases to (softmax warp 0: slots 0-13, MMA issuer: 16-23), for reading the schedule
+  unsigned int* phase_cycles = nullptr;
 };
 
 const char* attn_fwd_launch(const AttnArgs& a, cudaStream_t stream);

@@ -275,7 +275,8 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
               const Tensor& lse, Tensor& dq, Tensor& dk, Tensor& dv, Tensor& delta,
               const c10::optional<Tensor>& sinks, const c10::optional<Tensor>& dsinks,
               const c10::optional<Tensor>& status, double scale, bool causal, int64_t window,
-              const c10::optional<Tensor>& row_lo, const c10::optional<Tensor>& key_hi) {
+              const c10::optional<Tensor>& row_lo, const c10::optional<Tensor>& key_hi,
+              const c10::optional<Tensor>& phase_cycles) {
   check_cuda(q, "q"); check_cuda(d_o, "do");
   c10::cuda::CUDAGuard guard(q.device());
   bux::AttnArgs a;
@@ -291,6 +292,11 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
   a.key_hi = doc_bounds(key_hi, k.size(0) * k.size(1), "key_hi");
   TORCH_CHECK((a.row_lo == nullptr) == (a.key_hi == nullptr), "bux attention backward: row_lo and key_hi go together");
   TORCH_CHECK(a.row_lo == nullptr || (causal && a.T == a.S), "bux attention: documents need causal self-attention");
+  if (phase_cycles.has_value()) {
+    TORCH_CHECK(phase_cycles->is_cuda() && phase_cycles->scalar_type() == at::kInt && phase_cycles->numel() >= 32 &&
+                    phase_cycles->is_contiguous(), "bux attention backward: phase_cycles is int32[32] on the device");
+    a.phase_cycles = reinterpret_cast<unsigned int*>(phase_cycles->data_ptr<int>());
+  }
   const char* err = bux::attn_bwd_launch(a, stream_of(q));
   TORCH_CHECK(err == nullptr, "bux attention backward: ", err);
 }
@@ -310,17 +316,19 @@ void ep_push_rows(const Tensor& x, const Tensor& src_token, const Tensor& dst_ra
                     opt_f32(row_scale), u64_ptr(peer_base), peer_scale.has_value() ? u64_ptr(*peer_scale) : nullptr,
                     dst_row.numel(), (int)x.size(-1), (int)sms, stream_of(x));
 }
-void ep_push_rows_mx(const Tensor& x, const Tensor& src_token, const Tensor& dst_rank, const Tensor& dst_row,
-                     const c10::optional<Tensor>& row_scale, const Tensor& peer_q, const Tensor& peer_sf,
-                     const c10::optional<Tensor>& peer_scale, int64_t sms) {
+void ep_push_rows_mx(const Tensor& x, const Tensor& rank_of, const Tensor& row_of, const c10::optional<Tensor>& w,
+                     const Tensor& peer_q, const Tensor& peer_sf, const c10::optional<Tensor>& peer_scale, int64_t sms) {
   check_cuda(x, "x");
-  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.is_contiguous() && x.size(-1) % 128 == 0,
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.is_contiguous() && x.dim() == 2 && x.size(1) % 128 == 0,
               "ep_push_rows_mx: contiguous bf16 rows of a multiple of 128 columns");
+  TORCH_CHECK(row_of.dim() == 2 && row_of.size(0) == x.size(0) && row_of.size(1) <= 32 && row_of.is_contiguous() &&
+                  rank_of.is_contiguous() && rank_of.sizes() == row_of.sizes(),
+              "ep_push_rows_mx: rank_of / row_of are [tokens, k <= 32] int32");
+  TORCH_CHECK(!w.has_value() || (w->is_contiguous() && w->numel() == row_of.numel()), "ep_push_rows_mx: w is [tokens, k] fp32");
   c10::cuda::CUDAGuard guard(x.device());
-  bux::ep_push_rows_mx(x.data_ptr(), src_token.data_ptr<int>(), dst_rank.data_ptr<int>(), dst_row.data_ptr<int>(),
-                       opt_f32(row_scale), u64_ptr(peer_q), u64_ptr(peer_sf),
-                       peer_scale.has_value() ? u64_ptr(*peer_scale) : nullptr, dst_row.numel(), (int)x.size(-1),
-                       (int)sms, stream_of(x));
+  bux::ep_push_rows_mx(x.data_ptr(), rank_of.data_ptr<int>(), row_of.data_ptr<int>(), opt_f32(w), u64_ptr(peer_q),
+                       u64_ptr(peer_sf), peer_scale.has_value() ? u64_ptr(*peer_scale) : nullptr, x.size(0),
+                       (int)row_of.size(1), (int)x.size(1), (int)sms, stream_of(x));
 }
 void requant_mxfp8_cols(const Tensor& q, const Tensor& sf, Tensor& q_col, Tensor& sf_col, int64_t rows, int64_t cols,
                         int64_t ld_col) {
@@ -392,6 +400,7 @@ void tp_pull_reduce(const Tensor& peer_base, int64_t my_rank, Tensor& out, const
                       out.numel() / d, d, out.data_ptr(), residual.has_value() ? residual->data_ptr() : nullptr,
                       opt_i32(flags), (int)epoch, (uint64_t)(limit_s * 1e9), status_ptr(status), stream_of(out));
 }
+void set_comm_ctas_per_sm(int64_t n) { bux::set_comm_ctas_per_sm((int)n); }
 void ep_wait(const Tensor& flags, int64_t epoch, const c10::optional<Tensor>& status, double limit_s) {
   c10::cuda::CUDAGuard guard(flags.device());
   bux::ep_wait(flags.data_ptr<int>(), (int)flags.numel(), (int)epoch, (uint64_t)(limit_s * 1e9), status_ptr(status), stream_of(flags));
@@ -401,7 +410,7 @@ void ep_wait(const Tensor& flags, int64_t epoch, const c10::optional<Tensor>& st
 
 TORCH_LIBRARY(bux_b200, m) {
   m.def("ep_push_rows(Tensor x, Tensor src_token, Tensor dst_rank, Tensor dst_row, Tensor? row_scale, Tensor peer_base, int sms, Tensor? peer_scale=None) -> ()", &ep_push_rows);
-  m.def("ep_push_rows_mx(Tensor x, Tensor src_token, Tensor dst_rank, Tensor dst_row, Tensor? row_scale, Tensor peer_q, Tensor peer_sf, Tensor? peer_scale, int sms) -> ()", &ep_push_rows_mx);
+  m.def("ep_push_rows_mx(Tensor x, Tensor rank_of, Tensor row_of, Tensor? w, Tensor peer_q, Tensor peer_sf, Tensor? peer_scale, int sms) -> ()", &ep_push_rows_mx);
   m.def("requant_mxfp8_cols(Tensor q, Tensor sf, Tensor(a!) q_col, Tensor(b!) sf_col, int rows, int cols, int ld_col) -> ()", &requant_mxfp8_cols);
   m.def("row_dots(Tensor a, Tensor b, Tensor(a!) out) -> ()", &row_dots);
   m.def("ep_pull_scalar(Tensor peer_base, Tensor rank_of, Tensor row_of, Tensor(a!) out, Tensor? flags, int epoch, Tensor? status, float limit_s) -> ()", &ep_pull_scalar);
@@ -410,6 +419,7 @@ TORCH_LIBRARY(bux_b200, m) {
   m.def("ep_pull_dot(Tensor peer_base, Tensor rank_of, Tensor row_of, Tensor dout, Tensor(a!) dw) -> ()", &ep_pull_dot);
   m.def("zero_pad_rows(Tensor(a!) buf, Tensor offsets, Tensor counts) -> ()", &zero_pad_rows);
   m.def("ep_wait(Tensor flags, int epoch, Tensor? status, float limit_s) -> ()", &ep_wait);
+  m.def("set_comm_ctas_per_sm(int n) -> ()", &set_comm_ctas_per_sm);
   m.def("tp_push_block(Tensor src, Tensor peer_base, int my_rank, int sms) -> ()", &tp_push_block);
   m.def("tp_pull_reduce(Tensor peer_base, int my_rank, Tensor(a!) out, Tensor? residual, Tensor? flags, int epoch, Tensor? status, float limit_s) -> ()", &tp_pull_reduce);
   m.def("gemm(Tensor a, Tensor b, Tensor(a!) c, Tensor? sfa, Tensor? sfb, Tensor? group_offsets, Tensor? status, int kind, int mode, int M, int N, int K, int k_total, int groups, bool a_mn, bool b_mn, int out_kind, int bn, int sms, Tensor? wait_flags=None, int wait_epoch=0, int wait_rows=0, int m_rotate=0, bool wait_on_k=False, bool wait_on_n=False) -> ()", &gemm);
@@ -429,5 +439,5 @@ TORCH_LIBRARY(bux_b200, m) {
   m.def("combine_bwd(Tensor? y, Tensor dout, Tensor pos, Tensor? w, Tensor(a!)? dy, Tensor(b!)? dw) -> ()", &combine_bwd);
   m.def("combine_rows(Tensor y, Tensor pos, Tensor? w, Tensor(a!) out) -> ()", &combine_rows);
   m.def("attn_fwd(Tensor q, Tensor k, Tensor v, Tensor(a!) o, Tensor(b!) lse, Tensor? sinks, Tensor? status, float scale, bool causal, int window, Tensor? row_lo) -> ()", &attn_fwd);
-  m.def("attn_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor d_o, Tensor lse, Tensor(a!) dq, Tensor(b!) dk, Tensor(c!) dv, Tensor(d!) delta, Tensor? sinks, Tensor? dsinks, Tensor? status, float scale, bool causal, int window, Tensor? row_lo, Tensor? key_hi) -> ()", &attn_bwd);
+  m.def("attn_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor d_o, Tensor lse, Tensor(a!) dq, Tensor(b!) dk, Tensor(c!) dv, Tensor(d!) delta, Tensor? sinks, Tensor? dsinks, Tensor? status, float scale, bool causal, int window, Tensor? row_lo, Tensor? key_hi, Tensor? phase_cycles=None) -> ()", &attn_bwd);
 }

@@ -79,65 +79,84 @@ __global__ void ep_push_rows_kernel(const __nv_bfloat16* __restrict__ x, const i
   }
 }
 
-// The same push with the rows quantised on the way: each row leaves as d e4m3 bytes plus d/32
-// E8M0 scales (MXFP8 along the row), written straight into the owner's GEMM operand: the bytes
-// into its [cap, d] buffer, the scales into its scale tiles (512-byte tiles of 128 rows x 4
-// scales, the layout tcgen05.cp takes). Half the bytes of a bf16 push cross NVLink, and the
-// owner's first GEMM reads what arrived without a quantiser pass in between.
-// One warp per pick; a warp iteration covers 512 columns (16 bytes per lane, so every store
+// The MXFP8 exchange: a token's row is read and quantised once (e4m3 bytes + E8M0 scales along
+// the row) and stored into the buffer of every expert that picked it, so the owner's first GEMM
+// reads what arrived without a quantiser pass in between. One warp per token; lanes 0..k-1 hold
+// the picks' destinations; a warp iteration covers 1024 columns in two halves whose loads are
+// both in flight before the first is used (16 bytes per lane and half, so every store
 // instruction writes 512 contiguous bytes); two neighbouring lanes share a block of 32.
-__global__ void ep_push_rows_mx_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ src_token,
-                                       const int* __restrict__ dst_rank, const int* __restrict__ dst_row,
-                                       const float* __restrict__ row_scale, const uint64_t* __restrict__ peer_q,
-                                       const uint64_t* __restrict__ peer_sf, const uint64_t* __restrict__ peer_scale,
-                                       long picks, int d) {
+__global__ void ep_push_rows_mx_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ rank_of,
+                                       const int* __restrict__ row_of, const float* __restrict__ w,
+                                       const uint64_t* __restrict__ peer_q, const uint64_t* __restrict__ peer_sf,
+                                       const uint64_t* __restrict__ peer_scale, long tokens, int k, int d) {
   const int lane = threadIdx.x & 31;
   const int sf_cols = ((d / 32) + 3) & ~3;
-  for (long i = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < picks;
-       i += (long)gridDim.x * (blockDim.x >> 5)) {
-    const int row = dst_row[i];
-    if (row < 0) continue;
-    const int rank = dst_rank[i];
-    const __nv_bfloat16* src = x + (long)src_token[i] * d;
-    uint8_t* q_dst = reinterpret_cast<uint8_t*>(peer_q[rank]) + (long)row * d;
-    uint8_t* sf_dst = reinterpret_cast<uint8_t*>(peer_sf[rank]);
-    if (peer_scale != nullptr && lane == 0) reinterpret_cast<float*>(peer_scale[rank])[row] = row_scale ? row_scale[i] : 1.f;
-    for (int c0 = 0; c0 < d; c0 += 512) {
-      const int col = c0 + lane * 16;
-      const bool live = col < d;
-      uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
-      if (live) {
-        a = *reinterpret_cast<const uint4*>(src + col);
-        b = *reinterpret_cast<const uint4*>(src + col + 8);
+  for (long t = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < tokens;
+       t += (long)gridDim.x * (blockDim.x >> 5)) {
+    int my_row = -1;
+    unsigned long long my_q = 0, my_sf = 0;
+    if (lane < k) {
+      my_row = row_of[t * k + lane];
+      if (my_row >= 0) {
+        const int rank = rank_of[t * k + lane];
+        my_q = peer_q[rank] + (unsigned long long)my_row * d;
+        my_sf = peer_sf[rank];
+        if (peer_scale != nullptr) reinterpret_cast<float*>(peer_scale[rank])[my_row] = w ? w[t * k + lane] : 1.f;
       }
-      float v[16];
-      {
-        const uint32_t* au = &a.x; const uint32_t* bu = &b.x;
+    }
+    const __nv_bfloat16* src = x + t * d;
+    for (int c0 = 0; c0 < d; c0 += 1024) {
+      uint4 in[2][2];
+      int col[2];
+      bool live[2];
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        col[hh] = c0 + hh * 512 + lane * 16;
+        live[hh] = col[hh] < d;
+        in[hh][0] = in[hh][1] = make_uint4(0, 0, 0, 0);
+        if (live[hh]) {
+          in[hh][0] = *reinterpret_cast<const uint4*>(src + col[hh]);
+          in[hh][1] = *reinterpret_cast<const uint4*>(src + col[hh] + 8);
+        }
+      }
+      uint4 o[2];
+      uint32_t word[2];
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        float v[16];
+        const uint32_t* au = &in[hh][0].x; const uint32_t* bu = &in[hh][1].x;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const float2 f = unpack_bf16(au[q]), g = unpack_bf16(bu[q]);
           v[2 * q] = f.x; v[2 * q + 1] = f.y; v[8 + 2 * q] = g.x; v[8 + 2 * q + 1] = g.y;
         }
-      }
-      float amax = 0.f;
+        float amax = 0.f;
 #pragma unroll
-      for (int q = 0; q < 16; ++q) amax = fmaxf(amax, fabsf(v[q]));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));   // the block's other half
-      const uint32_t e = live ? (uint32_t)e8m0_of(amax) : 127u;
-      const float inv = e8m0_inv((uint8_t)e);
-      if (live) {
-        uint4 o;
-        o.x = cvt_e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
-        o.y = cvt_e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
-        o.z = cvt_e4m3x4(v[8] * inv, v[9] * inv, v[10] * inv, v[11] * inv);
-        o.w = cvt_e4m3x4(v[12] * inv, v[13] * inv, v[14] * inv, v[15] * inv);
-        *reinterpret_cast<uint4*>(q_dst + col) = o;
+        for (int q = 0; q < 16; ++q) amax = fmaxf(amax, fabsf(v[q]));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));   // the block's other half
+        const uint32_t e = live[hh] ? (uint32_t)e8m0_of(amax) : 127u;
+        const float inv = e8m0_inv((uint8_t)e);
+        o[hh].x = cvt_e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
+        o[hh].y = cvt_e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
+        o[hh].z = cvt_e4m3x4(v[8] * inv, v[9] * inv, v[10] * inv, v[11] * inv);
+        o[hh].w = cvt_e4m3x4(v[12] * inv, v[13] * inv, v[14] * inv, v[15] * inv);
+        // four consecutive blocks' scales (lanes l, l+2, l+4, l+6) make one 4-byte word of a tile
+        word[hh] = e | (__shfl_down_sync(0xffffffffu, e, 2) << 8) | (__shfl_down_sync(0xffffffffu, e, 4) << 16) |
+                   (__shfl_down_sync(0xffffffffu, e, 6) << 24);
       }
-      // four consecutive blocks' scales (lanes l, l+2, l+4, l+6) make one 4-byte word of a tile
-      const uint32_t w = e | (__shfl_down_sync(0xffffffffu, e, 2) << 8) | (__shfl_down_sync(0xffffffffu, e, 4) << 16) |
-                         (__shfl_down_sync(0xffffffffu, e, 6) << 24);
-      if ((lane & 7) == 0 && live)
-        *reinterpret_cast<uint32_t*>(sf_dst + sf_offset(row, (col >> 5), sf_cols)) = w;
+      for (int j = 0; j < k; ++j) {
+        const int row = __shfl_sync(0xffffffffu, my_row, j);
+        const unsigned long long q_dst = __shfl_sync(0xffffffffu, my_q, j);
+        const unsigned long long sf_dst = __shfl_sync(0xffffffffu, my_sf, j);
+        if (row < 0) continue;   // a dropped pick (the same for the whole warp)
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          if (!live[hh]) continue;
+          *reinterpret_cast<uint4*>(q_dst + col[hh]) = o[hh];
+          if ((lane & 7) == 0)
+            *reinterpret_cast<uint32_t*>(sf_dst + sf_offset(row, (col[hh] >> 5), sf_cols)) = word[hh];
+        }
+      }
     }
   }
 }
@@ -339,6 +358,11 @@ __global__ void tp_pull_reduce_kernel(const uint64_t* __restrict__ peer_base, in
   }
 }
 
+// CTAs per SM the exchange kernels may take (they run beside GEMMs whose CTAs need the rest)
+static int g_comm_ctas_per_sm = 0;
+void set_comm_ctas_per_sm(int n) { g_comm_ctas_per_sm = n; }
+static inline int comm_cap(int dflt_per_sm) { return 148 * (g_comm_ctas_per_sm > 0 ? g_comm_ctas_per_sm : dflt_per_sm); }
+
 static inline int blocks_for(long warps_needed, int warps_per_block, int cap) {
   long g = (warps_needed + warps_per_block - 1) / warps_per_block;
   return (int)(g < 1 ? 1 : (g > cap ? cap : g));
@@ -348,14 +372,14 @@ void ep_push_rows(const void* x, const int* src_token, const int* dst_rank, cons
                   const float* row_scale, const uint64_t* peer_base, const uint64_t* peer_scale, long picks, int d,
                   int sms, cudaStream_t s) {
   // a modest number of CTAs keeps most SMs free for the GEMMs that run beside the exchange
-  ep_push_rows_kernel<<<blocks_for(picks, 8, sms > 0 ? sms * 4 : 148 * 4), 256, 0, s>>>(
+  ep_push_rows_kernel<<<blocks_for(picks, 8, sms > 0 ? sms * 4 : comm_cap(4)), 256, 0, s>>>(
       (const __nv_bfloat16*)x, src_token, dst_rank, dst_row, row_scale, peer_base, peer_scale, picks, d);
 }
-void ep_push_rows_mx(const void* x, const int* src_token, const int* dst_rank, const int* dst_row,
-                     const float* row_scale, const uint64_t* peer_q, const uint64_t* peer_sf,
-                     const uint64_t* peer_scale, long picks, int d, int sms, cudaStream_t s) {
-  ep_push_rows_mx_kernel<<<blocks_for(picks, 8, sms > 0 ? sms * 4 : 148 * 4), 256, 0, s>>>(
-      (const __nv_bfloat16*)x, src_token, dst_rank, dst_row, row_scale, peer_q, peer_sf, peer_scale, picks, d);
+void ep_push_rows_mx(const void* x, const int* rank_of, const int* row_of, const float* w, const uint64_t* peer_q,
+                     const uint64_t* peer_sf, const uint64_t* peer_scale, long tokens, int k, int d, int sms,
+                     cudaStream_t s) {
+  ep_push_rows_mx_kernel<<<blocks_for(tokens, 8, sms > 0 ? sms * 4 : comm_cap(4)), 256, 0, s>>>(
+      (const __nv_bfloat16*)x, rank_of, row_of, w, peer_q, peer_sf, peer_scale, tokens, k, d);
 }
 void row_dots(const void* a, const void* b, float* out, long rows, int d, cudaStream_t s) {
   row_dots_kernel<<<blocks_for(rows, 8, 148 * 8), 256, 0, s>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b, out, rows, d);
@@ -373,7 +397,8 @@ void ep_pull_combine(const uint64_t* peer_base, const int* rank_of, const int* r
                      long tokens, int k, int d, const int* flags, int world, int epoch, uint64_t limit_ns,
                      Status* st, cudaStream_t s) {
   long work = tokens * (d / 8);
-  int grid = (int)((work + 255) / 256 > 148 * 8 ? 148 * 8 : (work + 255) / 256);
+  const int cap = comm_cap(8);
+  int grid = (int)((work + 255) / 256 > cap ? cap : (work + 255) / 256);
   ep_pull_combine_kernel<<<grid < 1 ? 1 : grid, 256, 0, s>>>(peer_base, rank_of, row_of, w, (__nv_bfloat16*)out,
                                                             tokens, k, d, flags, world, epoch, limit_ns, st);
 }

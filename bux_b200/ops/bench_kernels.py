@@ -96,6 +96,28 @@ def bench_grouped(rows: list, pk: dict) -> None:
 
 
 SMALL = False
+PHASES = False
+
+BWD_PHASES = {13: "loop overhead", 4: "wait S of the step ahead", 5: "P: tmem ld + math, next row statistics",
+              8: "wait dQ", 9: "dQ: tmem ld, arrive", 10: "wait dK (P and dS tiles free)",
+              11: "stage dQ, fence, issue reduces", 0: "wait dP of the step ahead", 1: "dS: tmem ld + math",
+              2: "wait staged dQ read", 3: "store P and dS, fence, arrive",
+              16: "mma: wait P and dS", 17: "mma: issue", 18: "mma: wait dQ read", 19: "mma: wait dO",
+              21: "mma: wait Q", 22: "mma: wait S read"}
+
+
+def attention_bwd_phases(q, k, v, o, do, lse) -> None:
+    """Cycles per step that softmax warp 0 and the MMA issuer of the first key tile's CTA spend in
+    each phase of the backward's schedule."""
+    counters = torch.zeros(32, dtype=torch.int32, device=q.device)
+    K.attn_bwd(q, k, v, o, do, lse, phase_cycles=counters)
+    c = counters.cpu().tolist()
+    steps = max(c[23], 1)
+    print(f"attention backward phases, CTA of key tile 0: {steps} steps, cycles per step")
+    for slot, name in BWD_PHASES.items():
+        print(f"  {name:<52} {c[slot] / steps:9.0f}")
+    print(f"  {'softmax warp total':<52} {sum(c[:14]) / steps:9.0f}")
+    print(f"  {'mma issuer total':<52} {sum(c[16:23]) / steps:9.0f}")
 
 
 def bench_attention(rows: list, pk: dict) -> None:
@@ -112,6 +134,8 @@ def bench_attention(rows: list, pk: dict) -> None:
         o, lse = K.attn_fwd(q, k, v)
         ms_f = timed(lambda: K.attn_fwd(q, k, v), 5)
         ms_b = timed(lambda: K.attn_bwd(q, k, v, o, do, lse), 5)
+        if PHASES:
+            attention_bwd_phases(q, k, v, o, do, lse)
         qt, kt, vt = (x.transpose(1, 2) for x in (q, k, v))
         ms_lib = timed(lambda: torch.nn.functional.scaled_dot_product_attention(qt, kt, vt, is_causal=True,
                                                                                 enable_gqa=True), 5)
@@ -210,9 +234,10 @@ def main() -> None:
     ap.add_argument("--json", default=None)
     ap.add_argument("--only", default="")
     ap.add_argument("--small", action="store_true", help="profiler-sized shapes (gemm, attention)")
+    ap.add_argument("--phases", action="store_true", help="attention backward: cycles per phase of its schedule")
     args = ap.parse_args()
-    global SMALL
-    SMALL = args.small
+    global SMALL, PHASES
+    SMALL, PHASES = args.small, args.phases
     pk = peaks()
     rows: list = []
     for name, fn in (("gemm", bench_gemm), ("grouped", bench_grouped), ("attention", bench_attention),

@@ -401,7 +401,11 @@ def attn_fwd(q, k, v, *, causal=True, window=0, sinks=None, scale=None, row_lo=N
     return o, lse
 
 
-def attn_bwd(q, k, v, o, do, lse, *, causal=True, window=0, sinks=None, scale=None, row_lo=None, key_hi=None):
+def attn_bwd(q, k, v, o, do, lse, *, causal=True, window=0, sinks=None, scale=None, row_lo=None, key_hi=None,
+             phase_cycles=None):
+    """(dq fp32, dk, dv, dsinks). `phase_cycles` (int32[32] on the device, optional): the CTA of the
+    first key tile adds the cycles its softmax warp 0 (slots 0-13) and its MMA issuer (16-23) spent
+    in each phase of the schedule."""
     b, t, h, d = q.shape
     dq = _out(b, t, h, d, dtype=torch.float32, device=q.device, op="attn_bwd dq", fill=0.0)
     dk = _out(k.shape, dtype=k.dtype, device=k.device, op="attn_bwd dk")
@@ -409,7 +413,7 @@ def attn_bwd(q, k, v, o, do, lse, *, causal=True, window=0, sinks=None, scale=No
     delta = _out(b, h, t, dtype=torch.float32, device=q.device, op="attn_bwd delta")
     dsinks = torch.zeros_like(sinks) if sinks is not None else None
     ops().attn_bwd(q, k, v, o, do, lse, dq, dk, dv, delta, sinks, dsinks, status_word(q.device),
-                   scale if scale is not None else d ** -0.5, causal, window or 0, row_lo, key_hi)
+                   scale if scale is not None else d ** -0.5, causal, window or 0, row_lo, key_hi, phase_cycles)
     _count(2)
     return dq, dk, dv, dsinks
 
@@ -423,12 +427,12 @@ def ep_push_rows(x, src_token, dst_rank, dst_row, peer_base, row_scale=None, sms
     _count()
 
 
-def ep_push_rows_mx(x, src_token, dst_rank, dst_row, peer_q, peer_sf, row_scale=None, peer_scale=None,
-                    sms: int = 0) -> None:
-    """`ep_push_rows` with the rows quantised on the way (MXFP8 along the row): e4m3 bytes into the
-    peers' [cap, d] byte buffers, E8M0 scales into their scale tiles; `row_scale` (a pick's router
-    weight) is stored beside the row in the peers' fp32 `peer_scale` buffers, not applied."""
-    ops().ep_push_rows_mx(x, src_token, dst_rank, dst_row, row_scale, peer_q, peer_sf, peer_scale, sms)
+def ep_push_rows_mx(x, rank_of, row_of, peer_q, peer_sf, weights=None, peer_scale=None, sms: int = 0) -> None:
+    """Token t's row → row `row_of[t, j]` of rank `rank_of[t, j]`'s buffers for each of its picks,
+    read and quantised once (MXFP8 along the row): e4m3 bytes into the peers' [cap, d] byte buffers,
+    E8M0 scales into their scale tiles; `weights[t, j]` (a pick's router weight, fp32) is stored
+    beside the row in the peers' fp32 `peer_scale` buffers, not applied."""
+    ops().ep_push_rows_mx(x, rank_of, row_of, weights, peer_q, peer_sf, peer_scale, sms)
     _count()
 
 
@@ -484,6 +488,11 @@ def ep_pull_scalar(peer_base, rank_of, row_of, flags=None, epoch: int = 0, limit
     ops().ep_pull_scalar(peer_base, rank_of, row_of, out, flags, epoch, status_word(row_of.device), limit_s)
     _count()
     return out
+
+
+def set_comm_ctas_per_sm(n: int) -> None:
+    """CTAs per SM the expert-exchange kernels may take (0: each kernel's own default)."""
+    ops().set_comm_ctas_per_sm(int(n))
 
 
 def ep_wait(flags, epoch: int, limit_s: float = 5.0) -> None:

@@ -12,7 +12,8 @@ import json
 from pathlib import Path
 
 COMM_MARKERS = ("nccl", "bux_comm", "ag_gemm", "gemm_rs", "moe_dispatch", "moe_combine", "all_reduce",
-                "allreduce", "reduce_scatter", "all_gather")
+                "allreduce", "reduce_scatter", "all_gather", "ep_push", "ep_pull", "ep_wait", "ep_signal", "tp_push",
+                "tp_pull")
 
 
 def is_comm(name: str) -> bool:

@@ -234,7 +234,7 @@ def test_pipeline_over_two_gpus_matches_one_gpu(cuda, tmp_path, schedule):
     want = [tr.train_step(next(feed))["loss"].item() for _ in range(2)]
     state = {n: p.detach().float().cpu() for n, p in tr.model.named_parameters()}
     out = str(tmp_path / "r0.pt")
-    mp.spawn(_tensor_worker, args=(2, _free_port(), [*base, "mesh = mesh(stage=2)", f"methods.pipeline = {schedule}"], out),
+    mp.spawn(_tensor_worker, args=(2, _free_port(), [*base, "mesh = mesh(stage=2)", f"methods.pipeline = \"{schedule}\""], out),
              nprocs=2, join=True)
     got = torch.load(out)
     assert got["losses"] == pytest.approx(want, abs=3e-2)
