@@ -401,6 +401,15 @@ void tp_pull_reduce(const Tensor& peer_base, int64_t my_rank, Tensor& out, const
                       opt_i32(flags), (int)epoch, (uint64_t)(limit_s * 1e9), status_ptr(status), stream_of(out));
 }
 void set_comm_ctas_per_sm(int64_t n) { bux::set_comm_ctas_per_sm((int)n); }
+void sf_rows_to_tiles(const Tensor& src, Tensor& dst) {
+  check_cuda(src, "src");
+  TORCH_CHECK(src.dim() == 2 && src.scalar_type() == at::kByte && src.is_contiguous() && src.size(1) % 4 == 0 &&
+                  dst.scalar_type() == at::kByte && dst.is_contiguous(), "sf_rows_to_tiles: [rows, sf_cols % 4 == 0] bytes");
+  const int64_t tiles = ((src.size(0) + 127) / 128) * (src.size(1) / 4) * 512;
+  TORCH_CHECK(dst.numel() >= tiles, "sf_rows_to_tiles: the tile buffer holds ", dst.numel(), " bytes, needs ", tiles);
+  c10::cuda::CUDAGuard guard(src.device());
+  bux::sf_rows_to_tiles(src.data_ptr(), dst.data_ptr(), src.size(0), (int)src.size(1), stream_of(src));
+}
 void ep_wait(const Tensor& flags, int64_t epoch, const c10::optional<Tensor>& status, double limit_s) {
   c10::cuda::CUDAGuard guard(flags.device());
   bux::ep_wait(flags.data_ptr<int>(), (int)flags.numel(), (int)epoch, (uint64_t)(limit_s * 1e9), status_ptr(status), stream_of(flags));
@@ -420,6 +429,7 @@ TORCH_LIBRARY(bux_b200, m) {
   m.def("zero_pad_rows(Tensor(a!) buf, Tensor offsets, Tensor counts) -> ()", &zero_pad_rows);
   m.def("ep_wait(Tensor flags, int epoch, Tensor? status, float limit_s) -> ()", &ep_wait);
   m.def("set_comm_ctas_per_sm(int n) -> ()", &set_comm_ctas_per_sm);
+  m.def("sf_rows_to_tiles(Tensor src, Tensor(a!) dst) -> ()", &sf_rows_to_tiles);
   m.def("tp_push_block(Tensor src, Tensor peer_base, int my_rank, int sms) -> ()", &tp_push_block);
   m.def("tp_pull_reduce(Tensor peer_base, int my_rank, Tensor(a!) out, Tensor? residual, Tensor? flags, int epoch, Tensor? status, float limit_s) -> ()", &tp_pull_reduce);
   m.def("gemm(Tensor a, Tensor b, Tensor(a!) c, Tensor? sfa, Tensor? sfb, Tensor? group_offsets, Tensor? status, int kind, int mode, int M, int N, int K, int k_total, int groups, bool a_mn, bool b_mn, int out_kind, int bn, int sms, Tensor? wait_flags=None, int wait_epoch=0, int wait_rows=0, int m_rotate=0, bool wait_on_k=False, bool wait_on_n=False) -> ()", &gemm);

@@ -85,12 +85,15 @@ __global__ void ep_push_rows_kernel(const __nv_bfloat16* __restrict__ x, const i
 // the picks' destinations; a warp iteration covers 1024 columns in two halves whose loads are
 // both in flight before the first is used (16 bytes per lane and half, so every store
 // instruction writes 512 contiguous bytes); two neighbouring lanes share a block of 32.
+// The scales leave row-major ([cap, d/32] bytes, 32 contiguous bytes per row and iteration):
+// in the tensor core's tile layout a row's scales are 4-byte pieces 512 bytes apart, sixteen
+// small packets over NVLink where this sends one; the owner rearranges them (`sf_rows_to_tiles`).
 __global__ void ep_push_rows_mx_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ rank_of,
                                        const int* __restrict__ row_of, const float* __restrict__ w,
                                        const uint64_t* __restrict__ peer_q, const uint64_t* __restrict__ peer_sf,
                                        const uint64_t* __restrict__ peer_scale, long tokens, int k, int d) {
   const int lane = threadIdx.x & 31;
-  const int sf_cols = ((d / 32) + 3) & ~3;
+  const int sf_cols = d / 32;
   for (long t = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < tokens;
        t += (long)gridDim.x * (blockDim.x >> 5)) {
     int my_row = -1;
@@ -100,7 +103,7 @@ __global__ void ep_push_rows_mx_kernel(const __nv_bfloat16* __restrict__ x, cons
       if (my_row >= 0) {
         const int rank = rank_of[t * k + lane];
         my_q = peer_q[rank] + (unsigned long long)my_row * d;
-        my_sf = peer_sf[rank];
+        my_sf = peer_sf[rank] + (unsigned long long)my_row * sf_cols;
         if (peer_scale != nullptr) reinterpret_cast<float*>(peer_scale[rank])[my_row] = w ? w[t * k + lane] : 1.f;
       }
     }
@@ -120,7 +123,7 @@ __global__ void ep_push_rows_mx_kernel(const __nv_bfloat16* __restrict__ x, cons
         }
       }
       uint4 o[2];
-      uint32_t word[2];
+      uint32_t word[2];   // lanes 0, 8, 16, 24: four consecutive blocks' scales of half hh
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
         float v[16];
@@ -140,9 +143,19 @@ __global__ void ep_push_rows_mx_kernel(const __nv_bfloat16* __restrict__ x, cons
         o[hh].y = cvt_e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
         o[hh].z = cvt_e4m3x4(v[8] * inv, v[9] * inv, v[10] * inv, v[11] * inv);
         o[hh].w = cvt_e4m3x4(v[12] * inv, v[13] * inv, v[14] * inv, v[15] * inv);
-        // four consecutive blocks' scales (lanes l, l+2, l+4, l+6) make one 4-byte word of a tile
         word[hh] = e | (__shfl_down_sync(0xffffffffu, e, 2) << 8) | (__shfl_down_sync(0xffffffffu, e, 4) << 16) |
                    (__shfl_down_sync(0xffffffffu, e, 6) << 24);
+      }
+      // rows of a multiple of 512 columns: the iteration's 32 scales as two 16-byte pieces, the
+      // first half's in lane 0, the second's in lane 1 (other widths store the 4-byte words)
+      const bool wide = (sf_cols & 15) == 0;
+      uint4 sfv = make_uint4(0, 0, 0, 0);
+      if (wide) {
+        const uint32_t w0 = __shfl_sync(0xffffffffu, word[0], 0), w1 = __shfl_sync(0xffffffffu, word[0], 8);
+        const uint32_t w2 = __shfl_sync(0xffffffffu, word[0], 16), w3 = __shfl_sync(0xffffffffu, word[0], 24);
+        const uint32_t x0 = __shfl_sync(0xffffffffu, word[1], 0), x1 = __shfl_sync(0xffffffffu, word[1], 8);
+        const uint32_t x2 = __shfl_sync(0xffffffffu, word[1], 16), x3 = __shfl_sync(0xffffffffu, word[1], 24);
+        sfv = (lane & 1) ? make_uint4(x0, x1, x2, x3) : make_uint4(w0, w1, w2, w3);
       }
       for (int j = 0; j < k; ++j) {
         const int row = __shfl_sync(0xffffffffu, my_row, j);
@@ -150,11 +163,14 @@ __global__ void ep_push_rows_mx_kernel(const __nv_bfloat16* __restrict__ x, cons
         const unsigned long long sf_dst = __shfl_sync(0xffffffffu, my_sf, j);
         if (row < 0) continue;   // a dropped pick (the same for the whole warp)
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          if (!live[hh]) continue;
-          *reinterpret_cast<uint4*>(q_dst + col[hh]) = o[hh];
-          if ((lane & 7) == 0)
-            *reinterpret_cast<uint32_t*>(sf_dst + sf_offset(row, (col[hh] >> 5), sf_cols)) = word[hh];
+        for (int hh = 0; hh < 2; ++hh)
+          if (live[hh]) *reinterpret_cast<uint4*>(q_dst + col[hh]) = o[hh];
+        if (wide) {
+          if (lane < 2 && c0 + lane * 512 < d) *reinterpret_cast<uint4*>(sf_dst + (c0 >> 5) + lane * 16) = sfv;
+        } else if ((lane & 7) == 0) {
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh)
+            if (live[hh]) *reinterpret_cast<uint32_t*>(sf_dst + (col[hh] >> 5)) = word[hh];
         }
       }
     }
@@ -293,6 +309,18 @@ __global__ void ep_wait_kernel(const int* __restrict__ flags, int world, int epo
   wait_flags(flags, world, epoch, limit_ns, st, 2);
 }
 
+// Row-major E8M0 scales ([rows, sf_cols] bytes, sf_cols % 4 == 0) → the tensor core's tile layout
+// (512-byte tiles of 128 rows x 4 scales), one 4-byte word per thread.
+__global__ void sf_rows_to_tiles_kernel(const uint32_t* __restrict__ src, uint8_t* __restrict__ dst, long rows,
+                                        int sf_cols) {
+  const int words = sf_cols >> 2;
+  const long total = rows * words;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long row = i / words; const int j = (int)(i % words);
+    *reinterpret_cast<uint32_t*>(dst + sf_offset(row, 4 * j, sf_cols)) = src[i];
+  }
+}
+
 // Rows [start[g] + count[g], start[g + 1]) of each group are padding up to the GEMM tile:
 // clear them so that contractions over rows (weight gradients) see zeros there.
 __global__ void zero_pad_rows_kernel(__nv_bfloat16* __restrict__ buf, const int* __restrict__ offsets,
@@ -406,6 +434,11 @@ void ep_pull_dot(const uint64_t* peer_base, const int* rank_of, const int* row_o
                  long picks, int k, int d, cudaStream_t s) {
   ep_pull_dot_kernel<<<blocks_for(picks, 8, 148 * 8), 256, 0, s>>>(peer_base, rank_of, row_of,
                                                                     (const __nv_bfloat16*)dout, dw, picks, k, d);
+}
+void sf_rows_to_tiles(const void* src, void* dst, long rows, int sf_cols, cudaStream_t s) {
+  const long total = rows * (sf_cols >> 2);
+  int grid = (int)((total + 255) / 256 > 148 * 8 ? 148 * 8 : (total + 255) / 256);
+  sf_rows_to_tiles_kernel<<<grid < 1 ? 1 : grid, 256, 0, s>>>((const uint32_t*)src, (uint8_t*)dst, rows, sf_cols);
 }
 void zero_pad_rows(void* buf, const int* offsets, const int* counts, int groups, int d, cudaStream_t s) {
   zero_pad_rows_kernel<<<dim3(groups, 16), 256, 0, s>>>((__nv_bfloat16*)buf, offsets, counts, d);

@@ -12,8 +12,8 @@ void ep_push_rows(const void* x, const int* src_token, const int* dst_rank, cons
                   int sms, cudaStream_t s);
 // token by token, the rows quantised on the way (MXFP8 along the row): token t's row goes to row
 // row_of[t, j] of rank rank_of[t, j] for each of its k picks (row < 0: dropped), e4m3 bytes into
-// peer_q[rank] ([cap, d]), E8M0 scales into the scale tiles at peer_sf[rank], w[t, j] (1 without w)
-// into peer_scale[rank][row] when given; d % 128 == 0, k <= 32
+// peer_q[rank] ([cap, d]), E8M0 scales row-major into peer_sf[rank] ([cap, d/32] bytes), w[t, j]
+// (1 without w) into peer_scale[rank][row] when given; d % 128 == 0, k <= 32
 void ep_push_rows_mx(const void* x, const int* rank_of, const int* row_of, const float* w, const uint64_t* peer_q,
                      const uint64_t* peer_sf, const uint64_t* peer_scale, long tokens, int k, int d, int sms,
                      cudaStream_t s);
@@ -34,6 +34,8 @@ void tp_push_block(const void* src, const uint64_t* peer_base, int world, int my
 void tp_pull_reduce(const uint64_t* peer_base, int world, int my_rank, long rows, int d, void* out,
                     const void* residual, const int* flags, int epoch, uint64_t limit_ns, Status* st,
                     cudaStream_t s);
+// row-major E8M0 scales [rows, sf_cols] (sf_cols % 4 == 0) -> the GEMM's 512-byte scale tiles
+void sf_rows_to_tiles(const void* src, void* dst, long rows, int sf_cols, cudaStream_t s);
 void set_comm_ctas_per_sm(int n);  // 0: each kernel's own default
 void ep_wait(const int* flags, int world, int epoch, uint64_t limit_ns, Status* st, cudaStream_t s);
 

@@ -19,6 +19,7 @@ from torch import nn
 from ... import ops
 from ...config import layers as L
 from ...ops import reference as ref
+from .. import placement
 from ..registry import BuildContext, Context, register
 from .basic import MLP, Linear, Norm, init_weight
 
@@ -103,7 +104,12 @@ class MoE(nn.Module):
         self.experts_gate_up = nn.Parameter(torch.empty(e, 2 * f, inner, dtype=b.dtype))
         self.experts_down = nn.Parameter(torch.empty(e, inner, f, dtype=b.dtype))
         init_weight(self.experts_gate_up, b.init)
+        rows = placement.expert_rows(e)   # under expert parallelism: this rank's experts only
+        if rows is not None:
+            self.experts_gate_up = placement.keep_rows(self.experts_gate_up, rows)
         init_weight(self.experts_down, b.init, "out")
+        if rows is not None:
+            self.experts_down = placement.keep_rows(self.experts_down, rows)
         if c.load_balancing in ("aux_free", "smebu"):
             self.register_buffer("router_bias", torch.zeros(scored))
             self.register_buffer("router_load", torch.zeros(scored))

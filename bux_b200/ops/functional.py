@@ -355,7 +355,7 @@ def attention(q, k, v, *, causal: bool = True, window: Optional[int] = None, sin
     d = q.shape[-1]
     packed = segments is not None
     native = (kernels_on(q) and d in (64, 128) and v.shape[-1] == d and softcap is None
-              and (not packed or (causal and q.shape[1] == k.shape[1])))
+              and (not packed or (causal and q.shape[1] == k.shape[1] and torch.is_tensor(segments))))
     if native:
         return _Attention.apply(q, k, v, sinks, causal, int(window or 0), scale, segments)
     if (q.is_cuda and softcap is None and segments is None and sinks is None and window is None

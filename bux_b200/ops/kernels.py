@@ -430,10 +430,21 @@ def ep_push_rows(x, src_token, dst_rank, dst_row, peer_base, row_scale=None, sms
 def ep_push_rows_mx(x, rank_of, row_of, peer_q, peer_sf, weights=None, peer_scale=None, sms: int = 0) -> None:
     """Token t's row → row `row_of[t, j]` of rank `rank_of[t, j]`'s buffers for each of its picks,
     read and quantised once (MXFP8 along the row): e4m3 bytes into the peers' [cap, d] byte buffers,
-    E8M0 scales into their scale tiles; `weights[t, j]` (a pick's router weight, fp32) is stored
+    E8M0 scales row-major into their [cap, d/32] byte buffers (`sf_rows_to_tiles` makes the GEMM's
+    tiles of them on the owner); `weights[t, j]` (a pick's router weight, fp32) is stored
     beside the row in the peers' fp32 `peer_scale` buffers, not applied."""
     ops().ep_push_rows_mx(x, rank_of, row_of, weights, peer_q, peer_sf, peer_scale, sms)
     _count()
+
+
+def sf_rows_to_tiles(src: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
+    """Row-major E8M0 scales [rows, cols/32] → the scale tiles a block-scaled GEMM reads."""
+    rows, sf_cols = src.shape
+    if out is None:
+        out = _out(sf_bytes(rows, sf_cols * 32), dtype=torch.uint8, device=src.device, op="sf_rows_to_tiles")
+    ops().sf_rows_to_tiles(src, out)
+    _count()
+    return out
 
 
 def requant_mxfp8_cols(q: torch.Tensor, sf: torch.Tensor, rows: int, cols: int):

@@ -167,7 +167,8 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool
               segments: Optional[torch.Tensor] = None) -> tuple:
     """Softmax attention on [B, T, H, D] queries and [B, S, G, D] keys/values (GQA:
     H % G == 0). `sinks` ([H]) adds one extra logit per head to the softmax
-    denominator only. `segments` ([B, T] ints) confines attention to equal ids.
+    denominator only. `segments` ([B, T] ints, or a pair ([B, T], [B, S]) for queries and keys)
+    confines attention to equal ids.
     Returns (out [B, T, H, Dv], lse [B, H, T])."""
     b, t, h, d = q.shape
     s, g = k.shape[1], k.shape[2]
@@ -187,7 +188,9 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool
         keep &= ki > qi - window
     keep = keep.expand(b, 1, t, s)
     if segments is not None:
-        keep = keep & (segments[:, None, :, None] == segments[:, None, None, :])
+        # one tensor for self-attention, or (the queries' ids, the keys' ids) when they differ
+        seg_q, seg_k = segments if isinstance(segments, (tuple, list)) else (segments, segments)
+        keep = keep & (seg_q[:, None, :, None] == seg_k[:, None, None, :])
     logits = logits.masked_fill(~keep, float("-inf"))
     if sinks is not None:
         sink = sinks.float().view(1, h, 1, 1).expand(b, h, t, 1)

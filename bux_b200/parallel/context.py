@@ -122,22 +122,33 @@ def method_for(name: str, kv_heads: int, heads: int, world: int) -> str:
 def attend(attention, q, k, v, group, method: str, **kw):
     """`attention(q, k, v, **kw)` is the whole-row kernel call; this wraps it for rows
     split by position over `group`."""
-    if kw.get("segments") is not None:
-        raise NotImplementedError("context parallelism of packed rows (document masks) is not built yet")
     c = dist.get_world_size(group)
     how = method_for(method, k.shape[2], q.shape[2], c)
+    segments = kw.get("segments")
+    whole = None
+    if segments is not None:
+        # packed rows: the document ids of the whole row (every rank holds a run of positions)
+        parts = [torch.empty_like(segments) for _ in range(c)]
+        dist.all_gather(parts, segments.contiguous(), group=group)
+        whole = torch.cat(parts, dim=1)
     if how == "ulysses":
         qh, kh, vh = (_ToHeads.apply(x.contiguous(), group) for x in (q, k, v))
         sinks = kw.get("sinks")
         if sinks is not None:  # this rank's heads
             r, per = dist.get_rank(group), q.shape[2] // c
             kw = dict(kw, sinks=sinks[r * per:(r + 1) * per])
+        if whole is not None:  # whole rows of this rank's heads: the kernels' document masks apply as they are
+            kw = dict(kw, segments=whole)
         out = attention(qh, kh, vh, **kw)
         return _ToPositions.apply(out.contiguous(), group)
-    plain = all(kw.get(name) is None for name in ("window", "sinks", "softcap"))
+    plain = all(kw.get(name) is None for name in ("window", "sinks", "softcap", "segments"))
     if how == "ring" and plain and q.shape[1] % 2 == 0:
         return _Ring.apply(q.contiguous(), k.contiguous(), v.contiguous(), group, kw.get("scale"))
     kg, vg = _GatherKV.apply(k, group), _GatherKV.apply(v, group)
+    if whole is not None:
+        # my queries against the gathered keys (those up to my last position): the document ids
+        # of my positions and of the keys'
+        kw = dict(kw, segments=(segments, whole[:, :kg.shape[1]]))
     return attention(q, kg, vg, **kw)
 
 

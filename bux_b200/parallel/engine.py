@@ -107,9 +107,20 @@ class Parallel:
         return idx
 
     # ------------------------------------------------------------------ the model
+    def placement(self):
+        """The context a model is built under, so that sharded stacks of experts are created
+        as this rank's shard (`bux_b200.models.placement`). Pipeline stages still build the
+        whole model first: a stage's share of the blocks is decided on the built graph."""
+        from ..models import placement
+
+        if self.expert_group is not None and self.stage_group is None:
+            return placement.placing(experts=(dist.get_rank(self.expert_group), self.shape["expert"]))
+        return placement.placing()
+
     def prepare_model(self, model) -> None:
         """Shard what the mesh shards: experts over ``expert``, then (tensor / fsdp) the
         rest; what stays whole is marked for gradient all-reduce over the batch axes."""
+        from ..models import placement
         from ..models.layers.moe import MoE
         from .experts import ExpertParallel
 
@@ -128,9 +139,13 @@ class Parallel:
                     el = m.c.num_experts // n
                     for name in ("experts_gate_up", "experts_down"):
                         p = getattr(m, name)
-                        local = torch.nn.Parameter(p.data[me * el:(me + 1) * el].clone())
-                        setattr(m, name, local)
-                        expert_params.add(local)
+                        if getattr(p, "placed_rows", None) is None:   # built whole: keep this rank's experts
+                            p = placement.keep_rows(p, slice(me * el, (me + 1) * el))
+                            setattr(m, name, p)
+                        elif p.placed_rows != slice(me * el, (me + 1) * el):
+                            raise ValueError(f"{name} was built for experts {p.placed_rows}, this rank owns "
+                                             f"{me * el}:{(me + 1) * el}")
+                        expert_params.add(p)
                     m.ep = ep
             self.ep = ep
         if self.tensor_group is not None:

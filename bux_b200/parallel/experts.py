@@ -101,7 +101,7 @@ class FusedEP:
     rows, epoch counters and the side stream the transfers run on."""
 
     KINDS = (("x", 2), ("y", 2), ("dy", 2), ("dx", 2))   # [cap, d] bf16 (x, dy: e4m3 bytes in the MXFP8 exchange)
-    SCALES = ("xsf", "dysf")                               # scale tiles of x and dy rows that travel as MXFP8
+    SCALES = ("xsf", "dysf")                               # [cap, d/32] E8M0 scales of x and dy rows that travel as MXFP8
     SCALARS = ("xw", "dots")                               # [cap] fp32: a row's router weight; its gradient
 
     def __init__(self, group, device, d: int, cap_rows: int, dtype=torch.bfloat16):
@@ -122,7 +122,7 @@ class FusedEP:
             for slot in range(SLOTS):
                 pieces[(key, slot)] = (at, cap_rows * 4)
                 at += -(-cap_rows * 4 // 256) * 256
-        sf_size = K.sf_bytes(cap_rows, d) if d % 128 == 0 else 0
+        sf_size = cap_rows * (d // 32) if d % 128 == 0 else 0   # row-major, as the senders write them
         for key in self.SCALES:
             for slot in range(SLOTS):
                 pieces[(key, slot)] = (at, sf_size)
@@ -140,7 +140,7 @@ class FusedEP:
             if key in self.SCALARS:
                 self.bufs[(key, slot)] = view.view(torch.float32)
             elif key in self.SCALES:
-                self.bufs[(key, slot)] = view
+                self.bufs[(key, slot)] = view.view(cap_rows, d // 32) if sf_size else view
             else:
                 self.bufs[(key, slot)] = view.view(dtype).view(cap_rows, d)
                 if key in ("x", "dy"):  # the same memory as the e4m3 rows of the MXFP8 exchange
@@ -148,6 +148,9 @@ class FusedEP:
                     self.tables[(key + "q", slot)] = torch.tensor([b + off for b in bases], dtype=torch.int64,
                                                                   device=device)
             self.tables[(key, slot)] = torch.tensor([b + off for b in bases], dtype=torch.int64, device=device)
+        # the scale tiles the GEMMs read, made on this rank from the row-major scales that arrived
+        self.tiles = {(key, slot): torch.zeros(K.sf_bytes(cap_rows, d), dtype=torch.uint8, device=device)
+                      for key in self.SCALES for slot in range(SLOTS)} if sf_size else {}
         self.flags = heap[flags_at:flags_at + 8 * self.world * 4].view(torch.int32).view(8, self.world)
         self.peer_flags = torch.tensor([b + flags_at for b in bases], dtype=torch.int64, device=device)
         self.epoch = [0, 0, 0, 0, 0]
@@ -288,7 +291,8 @@ class _FusedExperts(torch.autograd.Function):
             xtq = xtsf = None
             if mx:
                 # what arrived is the GEMM's operand already; padding rows are cleared (zero bytes)
-                xq, xsf = ep.bufs[("xq", slot)], ep.bufs[("xsf", slot)]
+                xq = ep.bufs[("xq", slot)]
+                xsf = K.sf_rows_to_tiles(ep.bufs[("xsf", slot)], out=ep.tiles[("xsf", slot)])
                 K.zero_pad_rows(xq.view(torch.bfloat16), r.offsets, r.counts)
                 h = K.grouped_gemm(xq, gq, r.offsets, f2, d, kind=kind, asf=xsf, bsf=gsf)
                 if grad:  # the transposed copy for the weight gradient, before the slot is reused
@@ -386,7 +390,8 @@ class _FusedExperts(torch.autograd.Function):
             dots = ep.bufs[("dots", slot)][:cap]
             dx_out = ep.bufs[("dx", slot)]
             if mx:
-                dyq, dysf = ep.bufs[("dyq", slot)], ep.bufs[("dysf", slot)]
+                dyq = ep.bufs[("dyq", slot)]
+                dysf = K.sf_rows_to_tiles(ep.bufs[("dysf", slot)], out=ep.tiles[("dysf", slot)])
                 K.zero_pad_rows(dyq.view(torch.bfloat16), r.offsets, r.counts)
                 dytq, dytsf = K.requant_mxfp8_cols(dyq, dysf, cap, d)
                 _, _, atq, atsf = K.quant_mxfp8_glu(h, None, act, rowwise=False, colwise=True, limit=limit,

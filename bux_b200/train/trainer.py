@@ -80,8 +80,9 @@ class Trainer:
         cuda = self.device.type == "cuda"
         self.compute = torch.bfloat16 if (t.precision.compute == "bfloat16" and cuda) else torch.float32
         self.param_dtype = self.compute
-        self.model = Model(run.arch, dtype=self.param_dtype, seed=t.seed if seed is None else seed,
-                           device=self.device)
+        with parallel.placement() if parallel is not None else _null():
+            self.model = Model(run.arch, dtype=self.param_dtype, seed=t.seed if seed is None else seed,
+                               device=self.device)
         if parallel is not None:
             parallel.prepare_model(self.model)
         self.precision = Precision(compute=self.compute, matmuls=t.precision.matmuls,

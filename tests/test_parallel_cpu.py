@@ -284,6 +284,71 @@ def test_blockwise_context_parallel_over_four_ranks(tmp_path):
         assert torch.allclose(got["state"][name], p, atol=1e-5), name
 
 
+def test_experts_are_built_as_the_ranks_shard():
+    """Under `placement.placing` a MoE layer keeps this rank's experts only, with the values a
+    whole build draws for them (and every other parameter unchanged)."""
+    from bux_b200.lang import compile_runs
+    from bux_b200.models import Model, placement
+
+    run = compile_runs(MOE, filename="t.bux")[0]
+    whole = Model(run.arch, seed=3)
+    with placement.placing(experts=(1, 2)):
+        mine = Model(run.arch, seed=3)
+    want = dict(whole.named_parameters())
+    for name, p in mine.named_parameters():
+        if "experts_" in name:
+            assert p.shape[0] == 2 and p.placed_rows == slice(2, 4)
+            assert torch.equal(p, want[name][2:4])
+        else:
+            assert torch.equal(p, want[name])
+
+
+def _packed_cp_worker(rank, world, port, method, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from bux_b200.ops import functional as ops
+    from bux_b200.parallel import context
+
+    torch.manual_seed(0)
+    b, t, h, g, d = 2, 16, 4, 2, 8
+    q, k, v = torch.randn(b, t, h, d), torch.randn(b, t, g, d), torch.randn(b, t, g, d)
+    go = torch.randn(b, t, h, d)
+    segments = torch.tensor([[1] * 5 + [2] * 6 + [3] * 5, [1] * 9 + [2] * 7])   # documents cross the ranks' boundary
+    per = t // world
+    mine = slice(rank * per, (rank + 1) * per)
+    ql, kl, vl = (x[:, mine].clone().requires_grad_() for x in (q, k, v))
+    o = context.attend(ops.attention, ql, kl, vl, dist.group.WORLD, method, causal=True, segments=segments[:, mine])
+    o.backward(go[:, mine])
+    parts = [None] * world
+    dist.all_gather_object(parts, (o.detach(), ql.grad, kl.grad, vl.grad))
+    if rank == 0:
+        torch.save([torch.cat([part[i] for part in parts], dim=1) for i in range(4)], out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("method", ["ulysses", "gathered", "ring"])
+def test_context_parallel_of_packed_rows(tmp_path, method):
+    """Rows of several documents split by position over two ranks: attention stays inside a
+    document on every method (ulysses: whole rows per head; the others: my queries against the
+    gathered keys with both sides' document ids)."""
+    from bux_b200.ops import reference as ref
+
+    out = str(tmp_path / "o.pt")
+    mp.spawn(_packed_cp_worker, args=(2, _free_port(), method, out), nprocs=2, join=True)
+    torch.manual_seed(0)
+    b, t, h, g, d = 2, 16, 4, 2, 8
+    q, k, v = (x.requires_grad_() for x in (torch.randn(b, t, h, d), torch.randn(b, t, g, d), torch.randn(b, t, g, d)))
+    go = torch.randn(b, t, h, d)
+    segments = torch.tensor([[1] * 5 + [2] * 6 + [3] * 5, [1] * 9 + [2] * 7])
+    want, _ = ref.attention(q, k, v, causal=True, segments=segments)
+    want.backward(go)
+    got = torch.load(out)
+    for a, w in zip(got, (want.detach(), q.grad, k.grad, v.grad)):
+        assert torch.allclose(a, w, atol=1e-5)
+
+
 def test_merge_by_lse_equals_attention_over_the_union():
     from bux_b200.ops import reference as ref
     from bux_b200.parallel.context import merge_by_lse
