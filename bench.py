@@ -108,6 +108,8 @@ def main() -> int:
     ap.add_argument("--model", default="qwen3_30b_a3b", choices=["qwen3_30b_a3b", "llama3_8b"],
                     help="the flagship (Qwen3-30B-A3B, MXFP8, experts over the GPUs) or the second benchmark "
                          "(Llama-3-8B, bf16, parameters sharded over the GPUs)")
+    ap.add_argument("--set", action="append", default=[], metavar="NAME=VALUE",
+                    help="one more override of the benchmark's file (an experiment: the JSON line records it)")
     ap.add_argument("--fsdp", default="fused", choices=["fused", "nccl"],
                     help="llama3_8b: all-gather / reduce-scatter by this library's peer-memory kernels or by NCCL")
     args = ap.parse_args()
@@ -158,6 +160,7 @@ def main() -> int:
         path = ROOT / "examples" / "benchmarks" / "qwen3_30b_a3b_mxfp8.bux"
     if args.layers:
         overrides.append(f"model = embed block^{args.layers} norm head")
+    overrides += [o.replace("=", " = ", 1) for o in args.set]
     run = compile_runs(path.read_text(), filename=str(path), overrides=overrides)[0]
     if world > 1:
         parallel = Parallel(run.train, device)
@@ -376,6 +379,8 @@ def main() -> int:
             "gpu_launches": launches,
         }
         if result is not None:
+            if args.set:
+                result["config"]["overrides"] = list(args.set)
             print(json.dumps(result))
     if parallel is not None:
         import torch.distributed as dist

@@ -10,6 +10,7 @@
 #include "comm_sm100.h"
 #include "elementwise.h"
 #include "gemm_sm100.h"
+#include "scan_sm100.h"
 
 namespace {
 
@@ -301,6 +302,41 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
   TORCH_CHECK(err == nullptr, "bux attention backward: ", err);
 }
 
+// ------------------------------------------------------------------ chunkwise recurrence
+void chunk_scan(const Tensor& a1, const Tensor& aux1, const c10::optional<Tensor>& aux3, const Tensor& a4, const Tensor& v,
+                const Tensor& lam, const c10::optional<Tensor>& s0, const c10::optional<Tensor>& out,
+                const c10::optional<Tensor>& x_out, const c10::optional<Tensor>& states, Tensor& s_last,
+                const c10::optional<Tensor>& status, int64_t bh, int64_t n_chunks, bool reverse) {
+  check_cuda(a1, "a1"); check_cuda(aux1, "aux1"); check_cuda(a4, "a4"); check_cuda(v, "v"); check_cuda(lam, "lam");
+  check_cuda(s_last, "s_last");
+  auto bf16 = [](const Tensor& t, int64_t numel, const char* name) {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.is_contiguous() && t.numel() == numel,
+                "chunk_scan: ", name, " must be contiguous bf16 of ", numel, " elements");
+  };
+  const int64_t chunks = bh * n_chunks;
+  TORCH_CHECK(chunks * 128 < (int64_t(1) << 31), "chunk_scan: too many rows for one launch");
+  bf16(a1, chunks * 128 * 128, "a1"); bf16(aux1, chunks * 128 * 64, "aux1"); bf16(a4, chunks * 128 * 128, "a4");
+  bf16(v, chunks * 64 * 128, "v");
+  if (aux3.has_value()) bf16(*aux3, chunks * 64 * 64, "aux3");
+  if (out.has_value()) bf16(*out, chunks * 64 * 128, "out");
+  if (x_out.has_value()) bf16(*x_out, chunks * 64 * 128, "x_out");
+  if (states.has_value()) bf16(*states, chunks * 128 * 128, "states");
+  TORCH_CHECK(lam.scalar_type() == at::kFloat && lam.numel() == chunks * 128, "chunk_scan: lam is fp32 [bh*n, 128]");
+  TORCH_CHECK(s_last.scalar_type() == at::kFloat && s_last.numel() == bh * 128 * 128, "chunk_scan: s_last is fp32 [bh, 128, 128]");
+  TORCH_CHECK(!s0.has_value() || s0->numel() == bh * 128 * 128, "chunk_scan: s0 is fp32 [bh, 128, 128]");
+  c10::cuda::CUDAGuard guard(a1.device());
+  bux::ScanArgs a;
+  a.a1 = a1.data_ptr(); a.aux1 = aux1.data_ptr(); a.aux3 = aux3.has_value() ? aux3->data_ptr() : nullptr;
+  a.a4 = a4.data_ptr(); a.v = v.data_ptr(); a.lam = lam.data_ptr<float>(); a.s0 = opt_f32(s0);
+  a.out = out.has_value() ? out->data_ptr() : nullptr;
+  a.x_out = x_out.has_value() ? x_out->data_ptr() : nullptr;
+  a.states = states.has_value() ? states->data_ptr() : nullptr;
+  a.s_last = s_last.data_ptr<float>();
+  a.bh = (int)bh; a.n_chunks = (int)n_chunks; a.reverse = reverse; a.status = status_ptr(status);
+  const char* err = bux::chunk_scan_launch(a, stream_of(a1));
+  TORCH_CHECK(err == nullptr, "bux chunk_scan: ", err);
+}
+
 // ------------------------------------------------------------------ expert-parallel exchange
 const uint64_t* u64_ptr(const Tensor& t) {
   TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kLong && t.is_contiguous(), "expected an int64 CUDA table of addresses");
@@ -429,6 +465,7 @@ TORCH_LIBRARY(bux_b200, m) {
   m.def("zero_pad_rows(Tensor(a!) buf, Tensor offsets, Tensor counts) -> ()", &zero_pad_rows);
   m.def("ep_wait(Tensor flags, int epoch, Tensor? status, float limit_s) -> ()", &ep_wait);
   m.def("set_comm_ctas_per_sm(int n) -> ()", &set_comm_ctas_per_sm);
+  m.def("chunk_scan(Tensor a1, Tensor aux1, Tensor? aux3, Tensor a4, Tensor v, Tensor lam, Tensor? s0, Tensor? out, Tensor? x_out, Tensor? states, Tensor(a!) s_last, Tensor? status, int bh, int n_chunks, bool reverse) -> ()", &chunk_scan);
   m.def("sf_rows_to_tiles(Tensor src, Tensor(a!) dst) -> ()", &sf_rows_to_tiles);
   m.def("tp_push_block(Tensor src, Tensor peer_base, int my_rank, int sms) -> ()", &tp_push_block);
   m.def("tp_pull_reduce(Tensor peer_base, int my_rank, Tensor(a!) out, Tensor? residual, Tensor? flags, int epoch, Tensor? status, float limit_s) -> ()", &tp_pull_reduce);

@@ -87,11 +87,25 @@ def scan(q, k, v, g, a=None, b=None, starts: Optional[torch.Tensor] = None, stat
         eye = torch.eye(CHUNK, device=k.device)
         T_ = torch.linalg.solve_triangular(eye - _pair(A, Bm, Gp, G, True), eye.expand(bsz, h, n, -1, -1),
                                            upper=False, unitriangular=True)
-        P = T_ @ (A * Gp.exp())             # X = P S_0 + U0
-        U0 = T_ @ (_pair(A, K, Gp, G, True) @ V)
+        P = T_ @ (A * Gp.exp())             # X = P S_0 + W V
+        W = T_ @ _pair(A, K, Gp, G, True)
         Mqb = _pair(Q, Bm, G, G, False)
         Bd = Bm * (end - G).exp()
+    from ...ops import functional as ops_f
+    from ...ops import scan as scan_kernel
+
+    if ops_f.kernels_on(v) and scan_kernel.supported(dk, dv, k.device):
+        # the serial part on the tensor cores, the state in tensor memory across the chunks
+        lam = end.exp().squeeze(-2).expand(bsz, h, n, dk)
+        if rank1:
+            o, last = scan_kernel.chunk_scan(P, Qd, W, Mqk, Mqb, Kd, Bd, V, lam, state)
+        else:
+            o, last = scan_kernel.chunk_scan(None, Qd, None, Mqk, None, Kd, None, V, lam, state)
+        out = o.reshape(bsz, h, n * CHUNK, dv)[:, :, :t].transpose(1, 2)
+        return out.to(v.dtype), last
     local = Mqk @ V
+    if rank1:
+        U0 = W @ V
     outs = []
     decay_end = end.exp().transpose(-1, -2)  # [b, h, n, dk or 1, 1]
     for i in range(n):

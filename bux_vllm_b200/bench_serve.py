@@ -36,6 +36,7 @@ def main() -> int:
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--dtype", default="bfloat16")
     ap.add_argument("--keep", default=None, help="folder to export into (default: a temporary one)")
+    ap.add_argument("--eager", action="store_true", help="no CUDA graphs / compilation in the engine (a quick smoke run)")
     args = ap.parse_args()
 
     os.environ.setdefault("VLLM_ENABLE_V1_MULTIPROCESSING", "0")   # the plugin is registered in this process
@@ -67,7 +68,7 @@ def main() -> int:
     t0 = time.perf_counter()
     llm = LLM(model=str(folder), trust_remote_code=True, dtype=args.dtype, tensor_parallel_size=args.tp,
               max_num_seqs=args.batch, max_model_len=args.prompt + args.generate + 8, skip_tokenizer_init=True,
-              enforce_eager=False, gpu_memory_utilization=0.9)
+              enforce_eager=args.eager, gpu_memory_utilization=0.9)
     load_s = time.perf_counter() - t0
     g = torch.Generator().manual_seed(0)
     vocab = run.arch.vocab_size
