@@ -65,6 +65,14 @@ def scan(q, k, v, g, a=None, b=None, starts: Optional[torch.Tensor] = None, stat
         from ...parallel import recurrence
 
         return recurrence.pass_state(scan, q, k, v, g, a, b, starts, group)
+    if k.is_cuda and v.dtype == torch.bfloat16 and not torch.backends.cuda.matmul.allow_tf32:
+        # bf16 activations: the chunk matrices end up as bf16 operands of the scan kernel, so
+        # their fp32 matmuls may run on the tensor cores in TF32 (three more mantissa bits than bf16)
+        torch.backends.cuda.matmul.allow_tf32 = True
+        try:
+            return scan(q, k, v, g, a, b, starts, state, group)
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = False
     bsz, t, h, dk = k.shape
     dv = v.shape[-1]
     if starts is not None:

@@ -212,6 +212,48 @@ def bench_memory_bound(rows: list, pk: dict) -> None:
                      "of_peak": sc.numel() * 4 / 1e9 / ms * 1e3 / pk["hbm_gbs"], "library_ms": timed(lambda: sc.topk(8, dim=-1))})
 
 
+def bench_scan(rows: list, pk: dict) -> None:
+    """Gated delta rule, 8 rows x 4096 x 16 heads of 128 (the shape the reference quotes for its
+    recurrence kernels): the chunk-scan kernel alone, and the whole `scan` forward + backward with
+    the serial part on the kernel and as the chunk loop in PyTorch."""
+    from ..models.layers import recurrent as R
+    from . import functional as F_
+    from . import scan as S_
+
+    dev = "cuda"
+    b, t, h, d = (2, 4096, 16, 128) if SMALL else (8, 4096, 16, 128)
+    n = t // 64
+    bf = lambda *shape, scale=1.0: (torch.randn(*shape, device=dev) * scale).bfloat16()
+    a1, a4 = bf(b, h, n, 128, 128, scale=0.1), bf(b, h, n, 128, 128, scale=0.1)
+    aux1, aux3 = bf(b, h, n, 128, 64, scale=0.1), bf(b, h, n, 64, 64, scale=0.1)
+    v = bf(b, h, n, 64, 128)
+    lam = torch.rand(b, h, n, 128, device=dev) * 0.5 + 0.5
+    ms = timed(lambda: S_._run(a1, aux1, aux3, a4, v, lam, None, want_out=True, reverse=False), 5)
+    # four chains of 128-row MMAs per chunk: K = 128, 64, 64, 128 over N = 128
+    flops = 2.0 * b * h * n * 128 * 128 * (128 + 64 + 64 + 128)
+    rows.append({"kernel": "chunk_scan (serial part, forward walk)", "shape": f"b{b} t{t} h{h} d{d}", "ms": ms,
+                 "tflops": flops / ms / 1e9, "of_peak": flops / ms / 1e9 / pk["bf16_tflops"]})
+    q = torch.nn.functional.normalize(torch.randn(b, t, h, d, device=dev), dim=-1).bfloat16().requires_grad_()
+    k = torch.nn.functional.normalize(torch.randn(b, t, h, d, device=dev), dim=-1).bfloat16().requires_grad_()
+    vv = torch.randn(b, t, h, d, device=dev).bfloat16().requires_grad_()
+    g = (-torch.rand(b, t, h, 1, device=dev) * 0.1).bfloat16()
+    beta = torch.rand(b, t, h, device=dev).bfloat16()
+
+    def fwd_bwd():
+        o, _ = R.delta_rule(q, k, vv, g, beta)
+        o.float().sum().backward()
+        q.grad = k.grad = vv.grad = None
+
+    ms_kernel = timed(fwd_bwd, 3)
+    F_.set_kernels(False)
+    try:
+        ms_loop = timed(fwd_bwd, 3)
+    finally:
+        F_.set_kernels(True)
+    rows.append({"kernel": "gated delta rule fwd+bwd (scan on the kernel)", "shape": f"b{b} t{t} h{h} d{d}",
+                 "ms": ms_kernel, "tflops": 0.0, "of_peak": 0.0, "library_ms": ms_loop})
+
+
 def bench_muon(rows: list, pk: dict) -> None:
     """Muon's Newton–Schulz iteration (five quintic steps) on the framework's GEMM beside the
     same iteration on library matmuls."""
@@ -241,7 +283,7 @@ def main() -> None:
     pk = peaks()
     rows: list = []
     for name, fn in (("gemm", bench_gemm), ("grouped", bench_grouped), ("attention", bench_attention),
-                     ("memory", bench_memory_bound), ("muon", bench_muon)):
+                     ("memory", bench_memory_bound), ("scan", bench_scan), ("muon", bench_muon)):
         if not args.only or args.only in name:
             fn(rows, pk)
     K.check_status(torch.device("cuda"), "bench_kernels")

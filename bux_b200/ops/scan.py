@@ -78,6 +78,16 @@ class _ChunkScan(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, d_out, d_last):
+        # the operand gradients are fp32 matmuls over bf16-rounded states: TF32 loses nothing more
+        before = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = d_out.is_cuda or before
+        try:
+            return _ChunkScan._backward(ctx, d_out, d_last)
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = before
+
+    @staticmethod
+    def _backward(ctx, d_out, d_last):
         P, Qd, W, Mqk, Mqb, Kd, Bd, V, lam_p, x, states = ctx.saved_tensors
         dk, dv, has_s0 = ctx.dims
         rank1 = P is not None
