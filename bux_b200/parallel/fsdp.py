@@ -173,6 +173,8 @@ class Unit:
         self.release_in_backward = False
         self.index = 0
         self.pending_grads: list = []     # (event, sources) of reductions still running on the side stream
+        self.hold = False                 # keep this microbatch's whole gradients here, reduce later
+        self.held: list = []              # whole gradients of the step's earlier microbatches
 
     # -- the collective halves
     def _by_dtype(self, tensors) -> dict:
@@ -311,6 +313,16 @@ class Unit:
         return self.finish_gather(work, mine)
 
     def scatter(self, grads) -> list:
+        if self.hold or self.held:
+            # gradients stay whole on this rank until the step's last microbatch
+            if not self.held:
+                self.held = [None] * len(grads)
+            for i, g in enumerate(grads):
+                if g is not None:
+                    self.held[i] = g.clone() if self.held[i] is None else self.held[i].add_(g)
+            if self.hold:
+                return [None] * len(grads)
+            grads, self.held = self.held, []
         if self.fused is not None and all(g is None or (g.dtype == torch.bfloat16 and g.is_cuda) for g in grads):
             return self._fused_scatter([None if g is None else g.contiguous() for g in grads])
         shapes = [e[2].shape for e in self.entries]
@@ -384,6 +396,10 @@ class FSDP:
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
         self.keep = t.layout.zero < 3 or getattr(t.methods, "gather", "layer") == "step"
+        # accumulate="unreduced": whole gradients are summed on this rank over the microbatches
+        # of a step and reduce-scattered once, with the last microbatch (the reference's
+        # `_unreduced` path, ``train/trainer.py:844``); "reduced" and "auto": every microbatch
+        self.unreduced = getattr(t.methods, "accumulate", "auto") == "unreduced"
         reduce = getattr(t.precision, "reduce", None)
         self.reduce_dtype = {"float32": torch.float32, "bfloat16": torch.bfloat16}.get(reduce)
         self.sharded: dict = {}           # parameter name → rows of the whole parameter
@@ -475,6 +491,8 @@ class FSDP:
     # ------------------------------------------------------------------ the step
     @contextmanager
     def microbatch(self, last: bool):
+        for u in self.units:
+            u.hold = self.unreduced and not last
         yield
 
     def finish(self) -> None:
@@ -489,6 +507,7 @@ class FSDP:
             u.kept = None
             u.pending = None
             u.pending_grads = []
+            u.held = []
             u.unshadow()
 
     # ------------------------------------------------------------------ checkpoints

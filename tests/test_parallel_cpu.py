@@ -101,6 +101,9 @@ def _check_rows(got, want, world=2):
     ["methods.remat = full"],             # ... and again in the replay of each block
     ["layout = layout(zero=1)"],          # whole parameters for the step, sharded optimizer state
     ["methods.microbatches = 2"],
+    ["methods.microbatches = 2", "methods.accumulate = unreduced"],                          # one reduce-scatter per step
+    ["methods.microbatches = 2", "methods.accumulate = unreduced", "methods.remat = full"],
+    ["methods.microbatches = 2", "methods.accumulate = unreduced", "methods.gather = step"],
 ])
 def test_fsdp_matches_one_rank(tmp_path, extra):
     base = [e for e in extra if "microbatches" in e]
