@@ -37,7 +37,10 @@ def _splits(model) -> dict:
                 if getattr(m.gate_up, leaf, None) is not None:
                     out[f"{pre}gate_up.{leaf}"] = [(f"{pre}gate.{leaf}", f), (f"{pre}up.{leaf}", f)]
         elif isinstance(m, MoE):
-            out[f"{pre}experts_gate_up"] = [(f"{pre}experts.gate", m.f), (f"{pre}experts.up", m.f)]
+            if m.gated:
+                out[f"{pre}experts_gate_up"] = [(f"{pre}experts.gate", m.f), (f"{pre}experts.up", m.f)]
+            else:  # plain MLP experts: the up projection alone
+                out[f"{pre}experts_gate_up"] = [(f"{pre}experts.up", None)]
             out[f"{pre}experts_down"] = [(f"{pre}experts.down", None)]
     return out
 

@@ -11,9 +11,16 @@ rotated, and since the values were rotated with the keys the head outputs are ro
 back by their query's position. ``o_lora_rank`` makes the output projection grouped and
 low-rank. Reference: ``architecture/attention/csa.py:50-377`` there.
 
-This is the layer's dense statement (all t x (t + t) logits), like the other sparse layers
-here; the ``kv`` / ``index`` / ``candidates`` ports and the indexer (top-k over the
-compressed latents) are not built: a query attends to every compressed latent it may see.
+An indexer (``indexer=indexer(...)``) keeps the ``top_k`` compressed latents of each query
+(its queries from the query latent, its keys projected from the compressed latents); without
+one a query attends to every compressed latent it may see. Ports: ``kv`` written pushes the
+compressed latents with the indexer's keys, read reuses them (the layer then has no
+compression of its own, and an indexer it runs scores the keys that came); ``index`` written
+pushes the kept latents, read reuses them (no indexer); ``candidates`` written pushes a coarse
+pool (blocks of ``candidate_block_size`` latents, ``candidate_top_k`` latents in all), read
+confines the indexer's picks to it.
+
+This is the layer's dense statement (all t x (t + t) logits), like the other sparse layers here.
 """
 
 from __future__ import annotations
@@ -33,14 +40,18 @@ from .basic import Linear, Norm, init_weight
 class CSA(nn.Module):
     def __init__(self, c: L.CSAConfig, b: BuildContext):
         super().__init__()
-        if b.ports:
-            raise NotImplementedError("csa: the kv, index and candidates ports are not built")
-        if c.indexer is not None:
-            raise NotImplementedError("csa: the indexer (top-k over the compressed latents) is not built; "
-                                      "without it every query attends to all the compressed latents it may see")
         self.c = c
+        self.ports = list(b.ports or ())
         width = b.width if isinstance(b.width, int) else b.d_model
         h, d, r = c.num_heads, c.head_dim, c.compress_ratio
+        if r is None and (c.indexer is not None or self.ports):
+            raise ValueError("csa: an indexer, and the kv, index and candidates ports, are for compressed "
+                             "latents; set compress_ratio")
+        reads = {p.name for p in self.ports if p.mode != "write"}
+        compresses = r is not None and "kv" not in reads
+        runs_indexer = c.indexer is not None and "index" not in reads
+        if not runs_indexer and any(p.name == "candidates" for p in self.ports):
+            raise ValueError("csa: the candidates port is its indexer's: the layer runs none")
         rank, groups = c.o_lora_rank, c.o_groups
         if rank and h % groups:
             raise ValueError(f"csa: {h} heads do not split into {groups} o_groups")
@@ -52,7 +63,7 @@ class CSA(nn.Module):
         self.q = Linear(latent or width, h * d, False, b, role="q")
         self.kv = Linear(width, d, False, b, role="kv")
         self.kv_norm = Norm(c.latent_norm, d)
-        if r is not None:
+        if compresses:
             self.compress_kv = Linear(width, d, False, b, role="kv")
             self.compress_norm = Norm(c.latent_norm, d)
             if r > 1:
@@ -71,6 +82,12 @@ class CSA(nn.Module):
             inv, gain = rope_lib.inverse_frequencies(c.rope, d)
             self.register_buffer("inv_freq", inv, persistent=False)
             self.rope_gain = gain
+        if runs_indexer:
+            from .sparse import Indexer
+
+            self.indexer = Indexer(c.indexer, width, c.rope, getattr(self, "rotated", 0), b,
+                                   query_width=latent or width, key_width=d if compresses else None,
+                                   key_norm=c.latent_norm)
 
     # ---- rotation of the first `rotated` dims
     def _rotate(self, x, positions, back: bool = False):
@@ -101,7 +118,13 @@ class CSA(nn.Module):
         # rotated to the position of the group's first token
         first = torch.gather(ctx.positions, 1, (torch.arange(t, device=x.device) - (r - 1)).clamp_min(0)
                              .unsqueeze(0).expand_as(ctx.positions))
-        return self._rotate(latent.unsqueeze(2), first)[:, :, 0], valid
+        return self._rotate(latent.unsqueeze(2), first)[:, :, 0], valid, latent, first
+
+    def _port(self, name: str, write: bool):
+        for p in self.ports:
+            if p.name == name and (p.mode == "write") == write:
+                return p
+        return None
 
     def forward(self, x, ctx: Context):
         c = self.c
@@ -126,10 +149,50 @@ class CSA(nn.Module):
         if c.sliding_window_size:
             window = window & ((qi.unsqueeze(1) - qi.unsqueeze(0)) < c.sliding_window_size).unsqueeze(0)
         keys, mask = [kv], [window]
+        picked_scores = kept = None
         if self.ratio is not None:
-            latents, valid = self._compressed(x, ctx, within)
+            from . import sparse as S
+
+            port = self._port("kv", write=False)
+            if port is not None:
+                latents, valid, index_keys = ctx.read(port.tap, port.mode == "pop")
+            else:
+                latents, valid, plain, first = self._compressed(x, ctx, within)
+                index_keys = None
+                if hasattr(self, "indexer") and hasattr(self.indexer, "k"):
+                    index_keys = self.indexer.keys_of(plain, first, ctx)
+            port = self._port("kv", write=True)
+            if port is not None:
+                ctx.push(port.tap, (latents, valid, index_keys))
+            seen = causal & same & valid.unsqueeze(1)           # from its group's last token on
+            kept = seen
+            port = self._port("index", write=False)
+            if port is not None:
+                kept = ctx.read(port.tap, port.mode == "pop") & seen
+            elif hasattr(self, "indexer"):
+                if index_keys is None:
+                    raise ValueError("csa: the latents that came through the kv port carry no indexer keys "
+                                     "(the layer that wrote them runs no indexer)")
+                ic = c.indexer
+                picked_scores = self.indexer.scores_of(x, query, index_keys, ctx)
+                allowed = seen
+                port = self._port("candidates", write=False)
+                if port is not None:
+                    allowed = allowed & ctx.read(port.tap, port.mode == "pop")
+                kept = S.top_mask(picked_scores, allowed, ic.top_k)
+                port = self._port("candidates", write=True)
+                if port is not None:
+                    order = valid.long().cumsum(-1) - 1          # the latents of a row, counted in order
+                    block = (order.clamp_min(0) // ic.candidate_block_size)
+                    blocks = int(block.max().item()) + 1
+                    pool = S.candidate_pool(picked_scores, seen, block, blocks,
+                                            max(ic.candidate_top_k // ic.candidate_block_size, 1))
+                    ctx.push(port.tap, pool & valid.unsqueeze(1))
+            port = self._port("index", write=True)
+            if port is not None:
+                ctx.push(port.tap, kept)
             keys.append(latents)
-            mask.append(causal & same & valid.unsqueeze(1))     # from its group's last token on
+            mask.append(kept)
         k_all = torch.cat(keys, dim=1).float()                                                 # [b, S, d]
         m_all = torch.cat(mask, dim=2)                                                        # [b, t, S]
         logits = torch.einsum("bthd,bsd->bhts", q.float(), k_all) * scale
@@ -141,6 +204,12 @@ class CSA(nn.Module):
             probs = torch.softmax(torch.cat([logits, sink], dim=-1), dim=-1)[..., :-1]
         else:
             probs = torch.softmax(logits, dim=-1)
+        if picked_scores is not None and ctx.training and c.indexer.loss_weight:
+            # the indexer's own loss: KL(attention over the kept latents || softmax of its scores)
+            from . import sparse as S
+
+            target = probs[..., t:].sum(1).detach()
+            ctx.report("indexer_loss", S.indexer_loss(picked_scores, kept, target), c.indexer.loss_weight)
         out = torch.einsum("bhts,bsd->bthd", probs, k_all).to(x.dtype)
         out = self._rotate(out, pos, back=True)
         if hasattr(self, "o_a"):

@@ -98,18 +98,19 @@ class MLA(nn.Module):
         t = q.shape[1]
         seen = S.seen_mask(ctx, t, c.sliding_window_size)
         reads = [p for p in self.ports if p.name == "index" and p.mode != "write"]
-        scores = None
+        picked = None
         if reads:
-            kept = ctx.read(reads[0].tap, reads[0].mode == "pop") & seen
+            kept = ctx.read(reads[0].tap, reads[0].mode == "pop")
+            kept = kept & (seen.unsqueeze(2) if kept.dim() == 4 else seen)
         else:
-            scores = self.indexer.scores(x, ctx)
-            kept = S.top_mask(scores, seen, c.indexer.top_k)
+            picked = self.indexer.pick(x, ctx, seen, c.indexer.top_k)
+            kept = picked.kept
         for p in self.ports:
             if p.name == "index" and p.mode == "write":
                 ctx.push(p.tap, kept)
         out, target = S.attend_kept(q, k, v, kept, scale, None, c.softcap)
-        if scores is not None and ctx.training and c.indexer.loss_weight:
-            ctx.report("indexer_loss", S.indexer_loss(scores, kept, target), c.indexer.loss_weight)
+        if picked is not None and ctx.training and c.indexer.loss_weight:
+            ctx.report("indexer_loss", self.indexer.loss(picked, target), c.indexer.loss_weight)
         return out
 
 

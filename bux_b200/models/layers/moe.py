@@ -80,8 +80,9 @@ class _ScaleGrad(torch.autograd.Function):
 class MoE(nn.Module):
     def __init__(self, c: L.MoEConfig, b: BuildContext):
         super().__init__()
-        if c.expert.type != "gated_mlp":
-            raise NotImplementedError("moe: routed experts are gated MLPs in this framework")
+        # plain MLP experts (one projection up, an activation, one down: Nemotron's relu² experts)
+        # run the per-expert PyTorch statement of the layer; the kernels' path is the gated one
+        self.gated = c.expert.type == "gated_mlp"
         self.c = c
         d = b.width if isinstance(b.width, int) else b.d_model
         e, f = c.num_experts, c.expert.intermediate_size
@@ -101,7 +102,7 @@ class MoE(nn.Module):
             self.latent_output_norm = Norm(c.latent_output_norm, inner)
         if c.expert_norm is not None:
             self.expert_norm = Norm(c.expert_norm, inner)
-        self.experts_gate_up = nn.Parameter(torch.empty(e, 2 * f, inner, dtype=b.dtype))
+        self.experts_gate_up = nn.Parameter(torch.empty(e, (2 if self.gated else 1) * f, inner, dtype=b.dtype))
         self.experts_down = nn.Parameter(torch.empty(e, inner, f, dtype=b.dtype))
         init_weight(self.experts_gate_up, b.init)
         rows = placement.expert_rows(e)   # under expert parallelism: this rank's experts only
@@ -214,14 +215,16 @@ class MoE(nn.Module):
         if self.ep is not None:
             if c.expert_norm is not None:
                 raise NotImplementedError("moe: expert_norm under expert parallelism")
+            if not self.gated:
+                raise NotImplementedError("moe: plain MLP experts under expert parallelism")
             out = self.ep(self, flat, w_ffn.reshape(bsz * t, -1), idx_ffn.reshape(bsz * t, -1), ctx, fmt)
-        elif c.expert_norm is not None:
-            # each expert's output is normalised before the weighted sum: the rows are
-            # needed one by one, so this runs the per-expert statement of the layer
+        elif c.expert_norm is not None or not self.gated:
+            # each expert's output is normalised before the weighted sum (the rows are needed one
+            # by one), or the experts are plain MLPs: the per-expert statement of the layer
+            norm = (lambda rows: self.expert_norm(rows, ctx)) if c.expert_norm is not None else None
             out = ops.moe_reference(flat, self.experts_gate_up, self.experts_down,
                                           w_ffn.reshape(bsz * t, -1), idx_ffn.reshape(bsz * t, -1),
-                                          ec.activation, ec.limit, ec.up_offset,
-                                          row_fn=lambda rows: self.expert_norm(rows, ctx))
+                                          ec.activation, ec.limit, ec.up_offset, row_fn=norm, gated=self.gated)
         else:
             out = ops.moe_experts(flat, self.experts_gate_up, self.experts_down,
                                   w_ffn.reshape(bsz * t, -1), idx_ffn.reshape(bsz * t, -1),

@@ -273,13 +273,15 @@ def moe_experts(x, w_gate_up, w_down, weights, experts, *, act: str = "swish",
     return moe_reference(x, w_gate_up, w_down, weights, experts, act, limit, up_offset)
 
 
-def moe_reference(x, w_gate_up, w_down, weights, experts, act="swish", limit=None, up_offset=0.0, row_fn=None):
+def moe_reference(x, w_gate_up, w_down, weights, experts, act="swish", limit=None, up_offset=0.0, row_fn=None,
+                  gated: bool = True):
     """Differentiable plain-PyTorch experts: sort picks, one matmul pair per expert.
     `row_fn` (optional) maps the experts' output rows before the weighted sum (a norm of
-    each expert's output)."""
+    each expert's output). Without `gated` the experts are plain MLPs: `w_gate_up` is the up
+    projection alone ([E, f, d]) and the activation applies to it."""
     t, d = x.shape
     e, f2, _ = w_gate_up.shape
-    f = f2 // 2
+    f = f2 // 2 if gated else f2
     k = experts.shape[1]
     flat = experts.reshape(-1)
     order = torch.argsort(flat, stable=True)
@@ -294,7 +296,10 @@ def moe_reference(x, w_gate_up, w_down, weights, experts, act="swish", limit=Non
             continue
         seg = xs[start:start + n]
         h = seg @ w_gate_up[ex].to(seg.dtype).t()
-        a = ref.glu(h[:, :f], h[:, f:], act, limit, up_offset)
+        if gated:
+            a = ref.glu(h[:, :f], h[:, f:], act, limit, up_offset)
+        else:
+            a = ref.activation(h.float().clamp(max=limit) if limit is not None else h.float(), act).to(h.dtype)
         outs.append(a @ w_down[ex].to(seg.dtype).t())
         start += n
     ys = torch.cat(outs) if outs else xs.new_zeros(0, d)

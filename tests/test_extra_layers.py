@@ -182,13 +182,138 @@ def test_csa_trains_is_causal_and_sees_compressed_latents_past_its_window():
     assert not torch.allclose(base[:, 39], far[:, 39], atol=1e-6)
 
 
-def test_csa_refuses_what_is_not_built():
+def test_csa_indexer_keeps_the_best_latents_and_its_ports_share_them():
+    """A layer that compresses and indexes writes its latents and picks; the next reuses both
+    (it has neither a compression nor an indexer of its own); a third re-indexes inside the
+    first one's candidate pool."""
+    from bux_b200.lang import compile_runs
+    from bux_b200.models.layers.csa import CSA
+    from bux_b200.train.trainer import Trainer
+
+    src = CSA_SRC.replace("sinks=true, compress_ratio=4,", "sinks=true, compress_ratio=2, "
+                          "indexer=indexer(num_heads=2, head_dim=8, top_k=4, candidate_block_size=2, candidate_top_k=8),")
+    src = src.replace("model = embed [n a] [n m] [n w] [n m] n head",
+                      "model = embed [n a(kv=@kv, index=@picks, candidates=@pool)] [n m] [n a(kv=$kv, index=$picks)] [n m] "
+                      "[n a(kv=$kv, index=@again, candidates=$pool)] [n m] n head")
+    run = compile_runs(src, filename="c.bux")[0]
+    tr = Trainer(run, device="cpu")
+    first, reuse, again = [m for m in tr.model.modules() if isinstance(m, CSA)]
+    assert hasattr(first, "compress_kv") and hasattr(first.indexer, "k")
+    assert not hasattr(reuse, "compress_kv") and not hasattr(reuse, "indexer")
+    assert not hasattr(again, "compress_kv") and hasattr(again, "indexer") and not hasattr(again.indexer, "k")
+    batch = next(iter(tr.batches()))
+    losses = [tr.train_step(batch)["loss"].item() for _ in range(5)]
+    assert losses[-1] < losses[0]
+    ids = torch.randint(0, 64, (1, 40), generator=torch.Generator().manual_seed(0))
+    ctx = tr.model(ids, torch.arange(40).unsqueeze(0), None, training=True)
+    assert torch.isfinite(ctx.losses["indexer_loss"])
+    kept, pool, kept_again = ctx.taps["picks"][-1], ctx.taps["pool"][-1], ctx.taps["again"][-1]
+    latents, valid, index_keys = ctx.taps["kv"][-1]
+    assert index_keys is not None and valid[0].tolist() == [(i + 1) % 2 == 0 for i in range(40)]
+    assert kept.sum(-1).max() == 4 and not (kept & ~valid.unsqueeze(1)).any()       # top 4 of the latents it sees
+    assert pool.sum(-1).max() <= 8 and not (kept_again & ~pool).any()               # picks stay inside the pool
+    # the indexer's loss trains the indexers only
+    grads = torch.autograd.grad(ctx.losses["indexer_loss"], list(tr.model.parameters()), allow_unused=True)
+    touched = {n for (n, _), g in zip(tr.model.named_parameters(), grads) if g is not None and g.abs().sum() > 0}
+    assert touched and all("indexer" in n for n in touched)
+
+
+def test_csa_ports_need_compressed_latents():
     import pytest
 
     from bux_b200.lang import compile_runs
     from bux_b200.models import Model
 
-    src = CSA_SRC.replace("sinks=true, compress_ratio=4,", "sinks=true, compress_ratio=4, indexer=indexer(num_heads=2, top_k=4),")
-    run = compile_runs(src, filename="c.bux")[0]
-    with pytest.raises(NotImplementedError, match="indexer"):
-        Model(run.arch)
+    src = CSA_SRC.replace("w = csa(num_heads=2, head_dim=16, sliding_window_size=8)",
+                          "w = csa(num_heads=2, head_dim=16, sliding_window_size=8, indexer=indexer(num_heads=2, top_k=4))")
+    with pytest.raises(Exception, match="compress"):
+        Model(compile_runs(src, filename="c.bux")[0].arch)
+
+
+def _picked(indexer_cfg: str, t: int = 24, positions=None):
+    """The keys a `gqa(indexer=...)` layer's indexer keeps for random inputs: (layer, picked, seen)."""
+    from bux_b200.models.layers import attention as A
+    from bux_b200.models.layers import sparse as S
+    from bux_b200.models.registry import Context
+
+    torch.manual_seed(0)
+    attn = f"gqa(num_heads=4, num_kv_heads=2, rope=rope(), indexer={indexer_cfg})"
+    tr = _train(attn)
+    layer = [m for m in tr.model.modules() if isinstance(m, A.GQA)][0]
+    x = torch.randn(1, t, 32)
+    ids = torch.zeros(1, t, dtype=torch.long)
+    if positions is None:
+        ctx = Context(ids)
+    else:
+        pos = torch.tensor([positions])
+        segments = (pos == 0).long().cumsum(-1)
+        ctx = Context(ids, pos, segments)
+    seen = S.seen_mask(ctx, t, None)
+    with torch.no_grad():
+        return layer, layer.indexer.pick(x, ctx, seen), seen, ctx
+
+
+def test_indexer_blocks_are_counted_from_each_documents_first_key():
+    from bux_b200.models.layers import sparse as S
+
+    pos = torch.tensor([[0, 1, 2, 3, 4, 0, 1, 2, 3]])
+    assert S.block_ids(pos, 4).tolist() == [[0, 0, 0, 0, 1, 2, 2, 2, 2]]
+    values = torch.tensor([[[1.0, 2.0, 3.0, 4.0, 5.0, 6.0, 7.0, 8.0, 9.0]]])
+    assert S.per_block(values, S.block_ids(pos, 4), 3, "sum").tolist() == [[[10.0, 5.0, 30.0]]]
+    assert S.per_block(values, S.block_ids(pos, 4), 3, "max").tolist() == [[[4.0, 5.0, 9.0]]]
+
+
+def test_indexer_with_mean_pooled_blocks_keeps_whole_blocks_and_its_own_unfinished_one():
+    """QSA: among the blocks a query sees all of it keeps the top_k // block_size best, whole;
+    the keys of its own unfinished block are kept too."""
+    _, picked, seen, _ = _picked("indexer(num_heads=2, head_dim=8, top_k=8, block_size=4, pool=mean)")
+    kept = picked.kept[0]
+    for q in range(24):
+        own = q // 4
+        rows = kept[q].view(6, 4)
+        assert rows[own].tolist() == [k <= q % 4 for k in range(4)]         # its own block, as far as it sees
+        finished = own + 1 if q % 4 == 3 else own                           # blocks the query sees all of
+        whole = [b for b in range(finished) if rows[b].all()]
+        partial = [b for b in range(own) if rows[b].any() and not rows[b].all()]
+        assert not partial and len(whole) >= min(2, finished)               # two whole blocks of four
+        assert not kept[q, q + 1:].any()
+    assert picked.scores.shape[-1] == 6 and picked.block is not None        # the loss runs over blocks
+
+
+def test_indexer_with_max_pooled_blocks_per_group():
+    """MSA: each indexer head picks for one kv group; a block scores its best seen key; the
+    query's own block is always among the top_k // block_size kept."""
+    layer, picked, seen, ctx = _picked(
+        "indexer(num_heads=2, head_dim=8, top_k=8, block_size=4, pool=max, per_group=true, weighted=false, relu=false)")
+    kept = picked.kept[0]                                                   # [t, g, s]
+    assert kept.shape == (24, 2, 24)
+    for q in range(24):
+        for g in range(2):
+            rows = kept[q, g].view(6, 4)
+            own = q // 4
+            assert rows[own].tolist() == [k <= q % 4 for k in range(4)]
+            others = [b for b in range(own) if rows[b].any()]
+            assert all(rows[b].all() for b in others) and len(others) == min(1, own)
+            if others:                                                      # the best of the other blocks
+                best = picked.scores[0, q, g, : own * 4].view(own, 4).amax(-1)
+                assert others[0] == int(best.argmax())
+    assert not torch.equal(kept[:, 0], kept[:, 1])                          # the groups pick apart
+    # attention runs per group over its own picks, and the loss is per group
+    from bux_b200.models.layers import sparse as S
+    q_, k_, v_ = torch.randn(1, 24, 4, 8), torch.randn(1, 24, 2, 8), torch.randn(1, 24, 2, 8)
+    out, target = S.attend_kept(q_, k_, v_, picked.kept, None)
+    assert target.shape == (1, 24, 2, 24) and torch.allclose(target.sum(-1), torch.full((1, 24, 2), 2.0))
+    assert torch.isfinite(layer.indexer.loss(picked, target))
+
+
+def test_indexer_blocks_stop_at_document_boundaries_and_train():
+    positions = list(range(10)) + list(range(14))
+    _, picked, seen, _ = _picked("indexer(num_heads=2, head_dim=8, top_k=8, block_size=4, pool=mean)", positions=positions)
+    assert not (picked.kept & ~seen).any()
+    assert not picked.kept[0, 10:, :10].any()                               # the second document sees none of the first
+    for cfg in ("indexer(num_heads=2, head_dim=8, top_k=8, block_size=4, pool=mean)",
+                "indexer(num_heads=1, head_dim=8, top_k=8, block_size=4, pool=max, per_group=true, weighted=false, relu=false)",
+                "indexer(num_heads=1, head_dim=8, top_k=4, per_group=true, weighted=false)"):
+        tr = _train(f"gqa(num_heads=2, num_kv_heads=1, rope=rope(), indexer={cfg})")
+        ctx = tr.model(torch.randint(0, 64, (2, 32)), torch.arange(32).expand(2, 32), None, training=True)
+        assert torch.isfinite(ctx.losses["indexer_loss"])

@@ -167,6 +167,28 @@ def test_every_reference_example_compiles():
     assert not bad, bad[:5]
 
 
+@pytest.mark.skipif(not os.path.isdir(REF), reason="reference examples not mounted")
+def test_every_reference_architecture_builds():
+    """Every file of the reference's model zoo becomes a module tree (on the meta device)."""
+    import torch
+
+    from bux_b200.models import Model
+
+    bad = []
+    for path in sorted(glob.glob(f"{REF}/architectures/**/*.bux", recursive=True)):
+        src = open(path).read()
+        try:
+            try:
+                arch = compile_runs(src, filename=path)[0].arch
+            except BuxError:
+                arch = compile(src, filename=path)
+            with torch.device("meta"):
+                Model(arch)
+        except Exception as err:  # noqa: BLE001 - every failure is listed
+            bad.append((path, f"{type(err).__name__}: {err}"))
+    assert not bad, bad[:5]
+
+
 def test_own_examples_compile():
     root = os.path.join(os.path.dirname(os.path.dirname(__file__)), "examples")
     for path in sorted(glob.glob(f"{root}/**/*.bux", recursive=True)):

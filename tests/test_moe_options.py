@@ -91,3 +91,35 @@ def test_expert_norm_normalises_each_experts_output():
     x = torch.randn(2, 8, 32)
     out = layer(x, Context(torch.zeros(2, 8, dtype=torch.long)))
     assert torch.allclose(out.float().pow(2).mean(-1).sqrt(), torch.ones(2, 8), atol=1e-3)
+
+
+def test_plain_mlp_experts_match_a_loop_over_the_picks_and_round_trip_through_the_export():
+    """Routed experts that are plain MLPs (one projection up, relu², one down)."""
+    from bux_b200.export import weights as W
+
+    src = SRC.replace("expert=gated_mlp(intermediate_size=16, activation=swish){options}",
+                      "expert=mlp(intermediate_size=16, activation=relu2)")
+    run = compile_runs(src, filename="x.bux")[0]
+    tr = Trainer(run, device="cpu")
+    batch = next(iter(tr.batches()))
+    losses = [tr.train_step(batch)["loss"].item() for _ in range(4)]
+    assert losses[-1] < losses[0]
+    m = _moes(tr)[0]
+    assert m.experts_gate_up.shape == (4, 16, 32) and not m.gated
+    from bux_b200.models.registry import Context
+
+    x = torch.randn(1, 5, 32)
+    ctx = Context(torch.zeros(1, 5, dtype=torch.long), None, None, training=False)
+    idx, w, _ = m.route(x, ctx)
+    want = torch.zeros(5, 32)
+    for t in range(5):
+        for j in range(idx.shape[-1]):
+            e = int(idx[0, t, j])
+            h = torch.relu(x[0, t] @ m.experts_gate_up[e].t()).square()
+            want[t] += w[0, t, j] * (h @ m.experts_down[e].t())
+    assert torch.allclose(m(x, ctx)[0], want, atol=1e-5)
+    exported = W.tensors(tr.model)
+    assert any(k.endswith("experts.up") for k in exported) and not any(k.endswith("experts.gate") for k in exported)
+    back = W.fused(tr.model, exported)
+    for name, p in tr.model.state_dict().items():
+        assert torch.equal(back[name], p), name
