@@ -53,8 +53,16 @@ class BuxForCausalLM(nn.Module):
                 return getattr(inner, name)
             raise
 
-    def forward(self, *args, **kwargs):
-        return self.inner(*args, **kwargs)
+    def forward(self, input_ids, positions, *args, **kwargs):
+        return self.inner(input_ids, positions, *args, **kwargs)
+
+    def embed_input_ids(self, input_ids, *args, **kwargs):
+        """Token embeddings (vLLM's model interface; older releases call it `get_input_embeddings`)."""
+        fn = getattr(self.inner, "embed_input_ids", None) or self.inner.get_input_embeddings
+        return fn(input_ids, *args, **kwargs)
+
+    def get_input_embeddings(self, input_ids, *args, **kwargs):
+        return self.embed_input_ids(input_ids, *args, **kwargs)
 
     def compute_logits(self, *args, **kwargs):
         return self.inner.compute_logits(*args, **kwargs)
