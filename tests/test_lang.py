@@ -189,12 +189,21 @@ def test_every_reference_architecture_builds():
     assert not bad, bad[:5]
 
 
-def test_own_examples_compile():
+def test_own_examples_compile_and_build():
+    import torch
+
+    from bux_b200.models import Model
+
     root = os.path.join(os.path.dirname(os.path.dirname(__file__)), "examples")
-    for path in sorted(glob.glob(f"{root}/**/*.bux", recursive=True)):
+    paths = sorted(glob.glob(f"{root}/**/*.bux", recursive=True))
+    assert len(paths) >= 25
+    for path in paths:
         src = open(path).read()
         try:
-            compile_runs(src, filename=path)
+            archs = [run.arch for run in compile_runs(src, filename=path)]
         except BuxError as err:
             assert "defines a model, not a run" in err.message, (path, str(err))
-            compile(src, filename=path)
+            archs = [compile(src, filename=path)]
+        with torch.device("meta"):
+            for arch in archs:
+                Model(arch)
