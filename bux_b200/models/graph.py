@@ -41,9 +41,19 @@ class ResidualBranch(nn.Module):
     def forward(self, x, ctx: Context):
         algebra = getattr(self, "algebra", None)
         ctx.branch_index += 1
-        if algebra is not None:
-            return algebra(x, self.body, ctx)
-        return x + self.body(x, ctx)
+        outer = ctx.branch_depth == 0
+        if outer:   # precision(first=..., last=...) counts these
+            ctx.precision.branch = ctx.top_branch
+            ctx.top_branch += 1
+        ctx.branch_depth += 1
+        try:
+            if algebra is not None:
+                return algebra(x, self.body, ctx)
+            return x + self.body(x, ctx)
+        finally:
+            ctx.branch_depth -= 1
+            if outer:
+                ctx.precision.branch = -1
 
 
 class Parallel(nn.Module):
@@ -300,6 +310,7 @@ class _BlockRun:
         self.names: list = []
         self.taps = {k: list(v) for k, v in ctx.taps.items()}
         self.ports = dict(ctx.ports)
+        self.branches = (ctx.branch_index, ctx.top_branch)   # where the block's first run starts counting
 
     def pinned(self, x, slot=None):
         k = (self.key, slot, tuple(x.shape), x.dtype)
@@ -311,9 +322,10 @@ class _BlockRun:
 
     def run(self, x, replay: bool):
         ctx = self.ctx
-        saved = (ctx.taps, ctx.losses, ctx.metrics, ctx.ports, ctx.branch_index)
+        saved = (ctx.taps, ctx.losses, ctx.metrics, ctx.ports, ctx.branch_index, ctx.top_branch)
         ctx.losses = {}
         if replay:
+            ctx.branch_index, ctx.top_branch = self.branches   # the branches count as in the first run
             ctx.taps = {k: list(v) for k, v in self.taps.items()}
             ctx.metrics, ctx.ports = {}, dict(self.ports)
             ctx.tail_values_unused = _ends_in_plain_moe_branch(self.block)
@@ -330,7 +342,7 @@ class _BlockRun:
             if replay:
                 self.kept = None
             if replay:
-                ctx.taps, ctx.losses, ctx.metrics, ctx.ports, ctx.branch_index = saved
+                ctx.taps, ctx.losses, ctx.metrics, ctx.ports, ctx.branch_index, ctx.top_branch = saved
             else:
                 ctx.losses = saved[1]
         if not replay:
@@ -359,6 +371,30 @@ def _checkpointed(block, x, ctx: Context, offload: bool = False, key=None, keep_
         prev = ctx.losses.get(name)
         ctx.losses[name] = value if prev is None else prev + value
     return y
+
+
+def count_outer_branches(node: nn.Module) -> int:
+    """Residual branches that are inside no other, in the order they run, up to the first head:
+    what ``precision(first=..., last=...)`` counts."""
+    from .layers.basic import Head
+
+    total = 0
+
+    def walk(m) -> bool:   # True once a head was reached
+        nonlocal total
+        if isinstance(m, Head):
+            return True
+        if isinstance(m, ResidualBranch):
+            total += 1
+            return False
+        children = list(m.items) if isinstance(m, (Sequence, Repeated)) else list(m.children())
+        for child in children:
+            if walk(child):
+                return True
+        return False
+
+    walk(node)
+    return total
 
 
 class GraphBuilder:

@@ -73,8 +73,9 @@ class Linear(nn.Module):
                 return TF.gather_matmul(x, self.weight, group, reorder)
             return TF.matmul_scatter(x, self.weight, group, ctx.input_ids.shape[0] if ctx is not None else x.shape[0],
                                      reorder)
-        fmt = ctx.precision.of(self.role) if ctx is not None else "bf16"
-        return ops.linear(x, self.weight, self.bias, fmt=fmt)
+        if ctx is None:
+            return ops.linear(x, self.weight, self.bias)
+        return ops.linear(x, self.weight, self.bias, fmt=ctx.precision.of(self.role), passes=ctx.precision.passes)
 
 
 # ------------------------------------------------------------------ norms

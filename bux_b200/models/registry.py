@@ -55,14 +55,30 @@ def build_layer(config, bctx: BuildContext):
 
 @dataclass
 class Precision:
-    """Matmul format by role, resolved from ``precision(...)`` for this forward."""
+    """Matmul format by role, resolved from ``precision(...)`` for this forward.
+
+    `first` / `last`: so many residual branches (the ``[...]`` that are inside no other, counted
+    up to the first head: `branches` of them) at the model's start and end multiply in the
+    compute dtype; `branch` is the one that is running (set by the graph). `passes`: which of a
+    projection's GEMMs (fprop, dgrad, wgrad) multiply in the format.
+    Reference: ``architecture/precision/matmuls.py``, ``docs/training/precision.md`` there."""
     compute: torch.dtype = torch.float32
     matmuls: str = "compute"
     roles: dict = field(default_factory=dict)
     enabled: bool = True
+    first: int = 0
+    last: int = 0
+    branches: int = 0
+    passes: tuple = ("fprop", "dgrad", "wgrad")
+    branch: int = -1
+
+    def at_an_edge(self) -> bool:
+        if self.branch < 0 or not (self.first or self.last):
+            return False
+        return self.branch < self.first or self.branch >= self.branches - self.last
 
     def of(self, role: str) -> str:
-        if not self.enabled:
+        if not self.enabled or not self.passes or self.at_an_edge():
             return "bf16"
         fmt = self.roles.get(role) or self.matmuls
         return "bf16" if fmt in ("compute", None) else fmt
@@ -93,6 +109,8 @@ class Context:
         self.heads: list = []
         self._rope: dict = {}
         self.branch_index = 0
+        self.top_branch = 0     # residual branches that are inside no other, run so far
+        self.branch_depth = 0
         self.pending_read = None  # single-pass hyper-connections: the read the last branch computed
 
     # taps are named stacks

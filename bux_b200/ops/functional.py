@@ -194,34 +194,49 @@ class _LinearBF16(torch.autograd.Function):
 
 
 class _LinearMX(torch.autograd.Function):
-    """y = x·W^T with every GEMM in MXFP8: operands are quantised along the dimension
+    """y = x·W^T with the GEMMs of `passes` in MXFP8: operands are quantised along the dimension
     each pass contracts (fprop K, dgrad N, wgrad M), as the reference's block-scaled
-    linear does (architecture/precision/blockscaled.py:81-204). x^T is kept in MXFP8."""
+    linear does (architecture/precision/blockscaled.py:81-204). x^T is kept in MXFP8 for an
+    MXFP8 wgrad; a pass that is not listed multiplies in bf16 and keeps its operand in bf16."""
 
     @staticmethod
-    def forward(ctx, x, w):
+    def forward(ctx, x, w, passes):
         K = _K()
         x2 = x.reshape(-1, x.shape[-1])
         m, k = x2.shape
         n = w.shape[0]
         need_w = w.requires_grad
-        xq, xsf, xtq, xtsf = K.quant_mxfp8(x2, rowwise=True, colwise=need_w)
-        wq, wsf, wtq, wtsf = _quant_weight(w)
-        y = K.gemm_mxfp8(xq, xsf, wq, wsf, m, n, k)
-        ctx.save_for_backward(xtq, xtsf, w)
-        ctx.dims = (m, n, k, x.shape)
+        mx_w = "wgrad" in passes
+        if "fprop" in passes:
+            xq, xsf, xtq, xtsf = K.quant_mxfp8(x2, rowwise=True, colwise=need_w and mx_w)
+            wq, wsf, _, _ = _quant_weight(w)
+            y = K.gemm_mxfp8(xq, xsf, wq, wsf, m, n, k)
+        else:
+            x2 = x2.contiguous()
+            y = K.gemm_bf16(x2, w)
+            xtq = xtsf = None
+            if need_w and mx_w:
+                _, _, xtq, xtsf = K.quant_mxfp8(x2, rowwise=False, colwise=True)
+        if mx_w:
+            ctx.save_for_backward(xtq, xtsf, w)
+        else:
+            ctx.save_for_backward(x2.contiguous(), None, w)
+        ctx.dims = (m, n, k, x.shape, passes)
         return y.view(*x.shape[:-1], n)
 
     @staticmethod
     def backward(ctx, dy):
         K = _K()
-        xtq, xtsf, w = ctx.saved_tensors
-        m, n, k, shape = ctx.dims
+        xt, xtsf, w = ctx.saved_tensors
+        m, n, k, shape, passes = ctx.dims
         dy2 = dy.reshape(-1, n).contiguous()
-        need_dx, need_dw = ctx.needs_input_grad
-        gq, gsf, gtq, gtsf = K.quant_mxfp8(dy2, rowwise=need_dx, colwise=need_dw)
+        need_dx, need_dw = ctx.needs_input_grad[:2]
+        mx_d, mx_w = "dgrad" in passes, "wgrad" in passes
+        gq = gsf = gtq = gtsf = None
+        if (need_dx and mx_d) or (need_dw and mx_w):
+            gq, gsf, gtq, gtsf = K.quant_mxfp8(dy2, rowwise=need_dx and mx_d, colwise=need_dw and mx_w)
         dx = dw = None
-        if need_dx:
+        if need_dx and mx_d:
             _, _, wtq, wtsf = _quant_weight(w)
             n_pad = wtq.shape[1]
             if n_pad != n:  # dy quantised along N must be padded like W^T
@@ -229,14 +244,21 @@ class _LinearMX(torch.autograd.Function):
                 gq2[:, :n] = gq
                 gq = gq2
             dx = K.gemm_mxfp8(gq, gsf, wtq, wtsf, m, k, n_pad).view(shape)
+        elif need_dx:
+            dx = K.gemm_bf16(dy2, w, b_mn=True).view(shape)
         if need_dw:
-            m_pad = gtq.shape[1]
             main = getattr(w, "main_grad", None)
-            if main is not None:
-                K.gemm_mxfp8(gtq, gtsf, xtq, xtsf, n, k, m_pad, out=main, accumulate=True)
+            if mx_w:
+                m_pad = gtq.shape[1]
+                if main is not None:
+                    K.gemm_mxfp8(gtq, gtsf, xt, xtsf, n, k, m_pad, out=main, accumulate=True)
+                else:
+                    dw = K.gemm_mxfp8(gtq, gtsf, xt, xtsf, n, k, m_pad)
+            elif main is not None:
+                K.gemm_bf16(dy2, xt, a_mn=True, b_mn=True, out=main, accumulate=True)
             else:
-                dw = K.gemm_mxfp8(gtq, gtsf, xtq, xtsf, n, k, m_pad)
-        return dx, dw
+                dw = K.gemm_bf16(dy2, xt, a_mn=True, b_mn=True)
+        return dx, dw, None
 
 
 class _LinearF32Out(torch.autograd.Function):
@@ -285,20 +307,28 @@ def linear_f32(x, w, bias=None):
     return F.linear(x.float(), w.float(), None if bias is None else bias.float())
 
 
-def linear(x, w, bias=None, fmt: str = "bf16"):
-    """x [..., in] times w [out, in]^T (+ bias). `fmt`: "bf16" (compute dtype) or "mxfp8"."""
+PASSES = ("fprop", "dgrad", "wgrad")
+
+
+def linear(x, w, bias=None, fmt: str = "bf16", passes=PASSES):
+    """x [..., in] times w [out, in]^T (+ bias). `fmt`: "bf16" (compute dtype), "mxfp8" or
+    "nvfp4"; `passes`: which of the projection's three GEMMs multiply in the format (the others
+    in the compute dtype)."""
     k, n = x.shape[-1], w.shape[0]
+    passes = tuple(passes)
+    if not passes:
+        fmt = "bf16"
     if fmt == "nvfp4" and k % 16 == 0 and n % 16 == 0:
         from . import nvfp4
 
-        return nvfp4.linear(x, w, bias)
+        return nvfp4.linear(x, w, bias, passes=passes)
     if kernels_on(x) and w.dtype == torch.bfloat16 and k % 8 == 0 and n % 8 == 0:
         if fmt in ("mxfp8", "mxfp8_2d") and k % 128 == 0 and n % 128 == 0:
-            y = _LinearMX.apply(x, w)
+            y = _LinearMX.apply(x, w, passes)
         else:
             y = _LinearBF16.apply(x, w, getattr(w, "_bux_arrival", None))
         return y if bias is None else y + bias.to(y.dtype)
-    if fmt in ("mxfp8", "mxfp8_2d") and k % 32 == 0 and not x.is_cuda:
+    if fmt in ("mxfp8", "mxfp8_2d") and k % 32 == 0 and not x.is_cuda and "fprop" in passes:
         return ref_linear_mxfp8(x, w, bias)
     return F.linear(x, w.to(x.dtype), None if bias is None else bias.to(x.dtype))
 

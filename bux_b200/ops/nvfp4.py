@@ -121,13 +121,15 @@ def _matmul(a: Blocks, b: Blocks) -> torch.Tensor:
 
 class _LinearNVFP4(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, seed):
+    def forward(ctx, x, w, seed, passes):
         x2 = x.reshape(-1, x.shape[-1])
-        xq = quantize(x2)
-        wq = quantize(w, tiles=True)
         ctx.save_for_backward(x2, w)
-        ctx.shape, ctx.seed = x.shape, seed
-        return _matmul(xq, wq).to(x.dtype).view(*x.shape[:-1], w.shape[0])
+        ctx.shape, ctx.seed, ctx.passes = x.shape, seed, passes
+        if "fprop" in passes:
+            y = _matmul(quantize(x2), quantize(w, tiles=True))
+        else:
+            y = x2 @ w.to(x2.dtype).t()
+        return y.to(x.dtype).view(*x.shape[:-1], w.shape[0])
 
     @staticmethod
     def backward(ctx, dy):
@@ -135,27 +137,35 @@ class _LinearNVFP4(torch.autograd.Function):
         dy2 = dy.reshape(-1, dy.shape[-1])
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            # dx = dy · W: W^T in 16 x 16 tiles holds W's values
-            dyq = quantize(dy2, stochastic=True, seed=ctx.seed)
-            wtq = quantize(w.t().contiguous(), tiles=True)
-            dx = _matmul(dyq, wtq).to(x2.dtype).view(ctx.shape)
+            if "dgrad" in ctx.passes:
+                # dx = dy · W: W^T in 16 x 16 tiles holds W's values
+                dyq = quantize(dy2, stochastic=True, seed=ctx.seed)
+                wtq = quantize(w.t().contiguous(), tiles=True)
+                dx = _matmul(dyq, wtq).to(x2.dtype).view(ctx.shape)
+            else:
+                dx = (dy2 @ w.to(dy2.dtype)).to(x2.dtype).view(ctx.shape)
         if ctx.needs_input_grad[1]:
-            # dW = dy^T · x, contracted over tokens: both operands transformed along the tokens
-            m = dy2.shape[0]
-            pad = (-m) % BLOCK
-            dyt, xt = dy2.t().float(), x2.t().float()
-            if pad:
-                dyt = torch.nn.functional.pad(dyt, (0, pad))
-                xt = torch.nn.functional.pad(xt, (0, pad))
-            dytq = quantize(dyt.contiguous(), stochastic=True, hadamard=True, seed=ctx.seed + 1)
-            xtq = quantize(xt.contiguous(), hadamard=True)
-            dw = _matmul(dytq, xtq).to(w.dtype)
-        return dx, dw, None
+            if "wgrad" in ctx.passes:
+                # dW = dy^T · x, contracted over tokens: both operands transformed along the tokens
+                m = dy2.shape[0]
+                pad = (-m) % BLOCK
+                dyt, xt = dy2.t().float(), x2.t().float()
+                if pad:
+                    dyt = torch.nn.functional.pad(dyt, (0, pad))
+                    xt = torch.nn.functional.pad(xt, (0, pad))
+                dytq = quantize(dyt.contiguous(), stochastic=True, hadamard=True, seed=ctx.seed + 1)
+                xtq = quantize(xt.contiguous(), hadamard=True)
+                dw = _matmul(dytq, xtq).to(w.dtype)
+            else:
+                dw = (dy2.t() @ x2.to(dy2.dtype)).to(w.dtype)
+        return dx, dw, None, None
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, seed: int = 0) -> torch.Tensor:
-    """x [..., in] · w [out, in]^T (+ bias) with NVFP4 operands in all three products."""
-    y = _LinearNVFP4.apply(x, w, seed)
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, seed: int = 0,
+           passes=("fprop", "dgrad", "wgrad")) -> torch.Tensor:
+    """x [..., in] · w [out, in]^T (+ bias) with NVFP4 operands in the products of `passes`
+    (the others multiply in the compute dtype)."""
+    y = _LinearNVFP4.apply(x, w, seed, tuple(passes))
     return y if bias is None else y + bias.to(y.dtype)
 
 

@@ -85,9 +85,18 @@ class Trainer:
                                device=self.device)
         if parallel is not None:
             parallel.prepare_model(self.model)
+        from ..models.graph import count_outer_branches
+
+        branches = count_outer_branches(self.model.graph)
+
+        def edge(v) -> int:   # a number of branches, or a share of them (rounded up)
+            return math.ceil(v * branches) if isinstance(v, float) else int(v)
+
         self.precision = Precision(compute=self.compute, matmuls=t.precision.matmuls,
                                    roles={k: v for k, v in t.precision.roles.model_dump().items()
-                                          if k != "type" and v is not None})
+                                          if k != "type" and v is not None},
+                                   first=edge(t.precision.first), last=edge(t.precision.last),
+                                   branches=branches, passes=tuple(t.precision.passes))
         experts_fmt = t.precision.experts()
         if experts_fmt:
             self.precision.roles["experts"] = experts_fmt
@@ -202,6 +211,10 @@ class Trainer:
             ids, pos = ids[:, span[0]:span[1]], pos[:, span[0]:span[1]]
             if segments is not None:
                 segments = segments[:, span[0]:span[1]]
+        sw = self.train.precision.switch
+        if sw is not None:   # from that share of the steps on, other GEMMs multiply in the format
+            late = self.step >= round(sw.at * self.train.steps)
+            self.precision.passes = tuple(sw.passes if late else self.train.precision.passes)
         ctx = self.model(ids, pos, segments, training=training, precision=self.precision,
                          methods=self.train.methods, parallel=self.parallel, step=self.step)
         parts = objective.compute(ctx, mb, self.train.loss, span=span, prefixes=self.prefix_table(),
@@ -376,6 +389,7 @@ class Trainer:
     @torch.no_grad()
     def evaluate(self, e: T.EvalConfig) -> dict:
         self.model.eval()
+        self.precision.enabled = self.train.precision.eval != "compute"   # eval=compute: no low-precision matmuls
         rank = self.parallel.data_rank if self.parallel is not None else 0
         world = self.parallel.data_world if self.parallel is not None else 1
         nbytes = self.token_bytes()
@@ -390,6 +404,7 @@ class Trainer:
                 acc[0] += total
                 acc[1] += count
         self.model.train()
+        self.precision.enabled = True
         out = {}
         for name in sorted(sums):   # every rank in the same order
             acc = sums[name]

@@ -269,3 +269,63 @@ def test_remat_policies_train_the_same(remat):
     assert rep.remat == (remat != "none")
     assert bool(rep.keep_attention) == (remat not in ("none", "full"))
     assert rep.first == (1 if "first" in remat else None)
+
+
+PRECISION_SRC = """
+d_model=64
+vocab_size=64
+n = rmsnorm
+block = [n gqa(num_heads=2, num_kv_heads=1, rope=rope())] [n gated_mlp(intermediate_size=128, activation=swish)]
+model = embed block^3 n head
+data = synthetic
+optimizer = adamw(lr=1e-3)
+seq_len = 32
+batch = 2
+steps = 10
+precision = precision(compute=float32{more})
+"""
+
+
+def _logits(more: str, step: int = 0):
+    run = compile_runs(PRECISION_SRC.format(more=more), filename="p.bux")[0]
+    tr = Trainer(run, device="cpu")
+    tr.step = step
+    batch = tr.to_device(next(iter(tr.batches())))
+    loss, _ = tr.forward_loss(batch, 1.0 / batch[0].numel(), 1, 1)
+    return tr, loss.item()
+
+
+def test_precision_first_and_last_keep_edge_branches_in_the_compute_dtype():
+    from bux_b200.models.graph import count_outer_branches
+
+    tr, plain = _logits("")
+    assert count_outer_branches(tr.model.graph) == 6
+    _, low = _logits(", matmuls=mxfp8")
+    assert low != plain
+    _, edges = _logits(", matmuls=mxfp8, first=2, last=4")          # every branch is at an edge
+    assert edges == plain
+    _, shares = _logits(", matmuls=mxfp8, first=0.5, last=0.5")
+    assert shares == plain
+    _, some = _logits(", matmuls=mxfp8, first=2")
+    assert some != plain and some != low
+
+
+def test_precision_passes_switch_and_eval():
+    _, plain = _logits("")
+    _, low = _logits(", matmuls=mxfp8")
+    _, none = _logits(", matmuls=mxfp8, passes=[]")
+    assert none == plain
+    # a switch takes over from a share of the steps on
+    _, before = _logits(", matmuls=mxfp8, switch=switch(at=0.5, passes=[])", step=4)
+    _, after = _logits(", matmuls=mxfp8, switch=switch(at=0.5, passes=[])", step=5)
+    assert before == _logits(", matmuls=mxfp8", step=4)[1] and after == _logits("", step=5)[1]
+    # eval=compute evaluates without the low-precision matmuls
+    src = PRECISION_SRC.format(more=", matmuls=mxfp8, eval=compute") + "eval = eval(data=synthetic, every=5, batches=2)\n"
+    run = compile_runs(src, filename="p.bux")[0]
+    tr = Trainer(run, device="cpu")
+    e = run.train.eval if not isinstance(run.train.eval, (tuple, list)) else run.train.eval[0]
+    in_compute = tr.evaluate(e)
+    assert tr.precision.enabled
+    tr.train.precision.__dict__["eval"] = "train"
+    as_trained = tr.evaluate(e)
+    assert in_compute != as_trained
