@@ -38,6 +38,29 @@ def test_linear(cuda, fmt, tol):
     assert rel_err(w.grad, wr.grad) < tol
 
 
+@pytest.mark.parametrize("passes", [("fprop",), ("dgrad", "wgrad"), ("fprop", "wgrad"), ("dgrad",)])
+def test_linear_mxfp8_in_some_passes_only(cuda, passes):
+    """The GEMMs that `passes` lists multiply in MXFP8, the others exactly as the bf16 linear does."""
+    torch.manual_seed(0)
+    x = torch.randn(4, 96, 256, device=cuda).bfloat16()
+    w = (torch.randn(384, 256, device=cuda) * 0.05).bfloat16()
+    dy = torch.randn(4, 96, 384, device=cuda).bfloat16()
+
+    def run(fmt, only):
+        xi, wi = x.clone().requires_grad_(), w.clone().requires_grad_()
+        y = ops.linear(xi, wi, fmt=fmt, passes=only)
+        y.backward(dy)
+        return {"fprop": y.detach(), "dgrad": xi.grad, "wgrad": wi.grad}
+
+    plain = run("bf16", ("fprop", "dgrad", "wgrad"))
+    low = run("mxfp8", ("fprop", "dgrad", "wgrad"))
+    got = run("mxfp8", passes)
+    for name in ("fprop", "dgrad", "wgrad"):
+        want = low if name in passes else plain
+        assert torch.equal(got[name], want[name]), name
+        assert rel_err(got[name], plain[name]) < 8e-2
+
+
 def test_cross_entropy_head(cuda):
     torch.manual_seed(1)
     x = torch.randn(300, 128, device=cuda).bfloat16().requires_grad_()
