@@ -74,6 +74,8 @@ class GQA(nn.Module):
         self.qkv = Linear(width, self.q_rows + self.k_rows + self.v_rows, c.bias, b, role="q")
         out_bias = c.bias if c.output_bias is None else c.output_bias
         self.o = Linear(self.h * self.dv, width, out_bias, b, role="o", init_role="out")
+        if c.mimetic_vo is not None:
+            self._mimetic_vo(width, c.mimetic_vo, c.mimetic_noise)
         if c.qk_norm is not None:
             per = self.d
             self.q_norm = Norm(c.qk_norm, self.hq * per if c.qk_norm_all_heads else per)
@@ -256,6 +258,27 @@ class GQA(nn.Module):
         else:
             out = ops.attention(q, k, v, **kw)
         return self._finish(out, x, v, bsz, t, ctx)
+
+    def _mimetic_vo(self, width: int, beta: float, noise: float) -> None:
+        """Mimetic V-O init (modded-nanogpt's, after Trockman & Kolter 2023): value head j reads the
+        stream's channels j·dv .. (j+1)·dv times sqrt(beta), every query head of its group writes its
+        output back onto them times -sqrt(beta) / group, so a head that attends to itself subtracts
+        beta / group of those channels; both matrices take noise of std `noise` in place of their
+        own draws. Reference: ``initializers.py:140`` (`mimetic_vo`)."""
+        values, group = self.g * self.dv, self.h // self.g
+        if values > width:
+            raise ValueError(f"mimetic_vo maps {self.g} value heads of {self.dv} onto the stream's channels: "
+                             f"{values} of them do not fit in a width of {width}")
+        root = beta ** 0.5
+        with torch.no_grad():
+            w = self.qkv.weight
+            v = torch.randn(values, width) * noise + root * torch.eye(values, width)
+            w[self.q_rows + self.k_rows:] = v.to(w.dtype)
+            read = torch.arange(self.h * self.dv)
+            channel = (read // self.dv) // group * self.dv + read % self.dv   # query head i's dim r → its value head's dim r
+            o = torch.randn(width, self.h * self.dv) * noise
+            o[channel, read] -= root / group
+            self.o.weight.copy_(o.to(self.o.weight.dtype))
 
     def _add_value_embedding(self, x, v, e, ctx: Context):
         """v + 2·sigmoid(W [x[:n], e[:n]])·e with a gate per kv head (W starts at 0, so the

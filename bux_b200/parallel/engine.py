@@ -188,6 +188,65 @@ class Parallel:
             for name, p in model.named_parameters():
                 self.replicated.append((p, self.context_group))
                 self._norm_w[name] = self._norm_w.get(name, 1.0) / n
+        self._install_early_reduction()
+
+    # ------------------------------------------------------------------ early gradient reduction
+    EARLY_BUCKET_BYTES = 64 << 20
+
+    def _install_early_reduction(self) -> None:
+        """Replicated parameters' gradients are all-reduced while the backward still runs: as
+        each gradient of the step's last microbatch is accumulated it joins a bucket, and a
+        full bucket is summed asynchronously (NCCL's stream beside the backward's kernels);
+        `finish_grads` waits for the buckets and sums what never passed a hook. Parameters that
+        are summed over two groups (context parallelism beside data parallelism) keep the
+        late path. Reference: the overlap pass of ``train/reorder.py:46`` there."""
+        self._early_on = False
+        self._early_open: dict = {}     # group -> (grads, bytes) of the bucket being filled
+        self._early_flying: list = []   # (work, flat, grads)
+        self._early_done: set = set()
+        counts: dict = {}
+        for p, _ in self.replicated:
+            counts[id(p)] = counts.get(id(p), 0) + 1
+        for p, g in self.replicated:
+            if counts[id(p)] != 1 or not p.requires_grad:
+                continue
+
+            def hook(param, group=g):
+                if not self._early_on or param.grad is None:
+                    return
+                grads, size = self._early_open.get(group, ([], 0))
+                grads.append(param.grad)
+                size += param.grad.numel() * param.grad.element_size()
+                self._early_done.add(id(param))
+                if size >= self.EARLY_BUCKET_BYTES:
+                    self._launch_bucket(grads, group)
+                    grads, size = [], 0
+                self._early_open[group] = (grads, size)
+
+            p.register_post_accumulate_grad_hook(hook)
+
+    def _launch_bucket(self, grads: list, group) -> None:
+        by_dtype: dict = {}
+        for gr in grads:
+            by_dtype.setdefault(gr.dtype, []).append(gr)
+        for same in by_dtype.values():
+            flat = torch.cat([gr.reshape(-1) for gr in same])
+            work = dist.all_reduce(flat, group=group, async_op=True)
+            self._early_flying.append((work, flat, same))
+
+    def _finish_early(self) -> None:
+        for group, (grads, _) in self._early_open.items():
+            if grads:
+                self._launch_bucket(grads, group)
+        self._early_open = {}
+        for work, flat, grads in self._early_flying:
+            work.wait()
+            off = 0
+            for gr in grads:
+                n = gr.numel()
+                gr.copy_(flat[off:off + n].view_as(gr))
+                off += n
+        self._early_flying = []
 
     def norm_weight(self, name: str) -> float:
         """Share of a parameter's squared gradient this rank contributes to the global
@@ -197,18 +256,26 @@ class Parallel:
     # ------------------------------------------------------------------ gradients
     @contextmanager
     def grad_sync(self, model, last: bool):
-        if self.fsdp is not None:
-            with self.fsdp.microbatch(last):
+        self._early_on = last   # gradients are complete after the last microbatch's backward
+        try:
+            if self.fsdp is not None:
+                with self.fsdp.microbatch(last):
+                    yield
+            else:
                 yield
-        else:
-            yield
+        finally:
+            self._early_on = False
 
     def finish_grads(self, model) -> None:
         """Sum the gradients of replicated parameters over their replicas (bucketed)."""
         if self.fsdp is not None:
             self.fsdp.finish()
+        self._finish_early()
+        early, self._early_done = self._early_done, set()
         by_group: dict = {}
         for p, g in self.replicated:
+            if id(p) in early:
+                continue   # summed while the backward ran
             grad = getattr(p, "main_grad", None)
             grad = grad if grad is not None else p.grad
             if grad is not None:

@@ -166,3 +166,20 @@ def test_paired_heads_share_one_softmax():
                 logits = torch.stack(keys) @ qq * d ** -0.5
                 want = torch.softmax(logits, 0) @ torch.stack(vals)
                 assert torch.allclose(got[0, p, head], want, atol=1e-5), (j, p, second)
+
+
+def test_mimetic_vo_init_makes_self_attention_subtract_beta_of_the_stream():
+    """With the mimetic V-O init and no noise, a token that attends to itself alone gets
+    -beta of its own first g·dv channels back (value-output map -beta·I on them)."""
+    from bux_b200.lang import compile
+    from bux_b200.models import Model
+    from bux_b200.models.layers.attention import GQA
+
+    arch = compile("d_model=32\nvocab_size=16\n"
+                   "model = embed [gqa(num_heads=4, num_kv_heads=2, head_dim=8, mimetic_vo=0.5, mimetic_noise=0.0, rope=none)] head\n")
+    layer = [m for m in Model(arch).modules() if isinstance(m, GQA)][0]
+    wv = layer.qkv.weight[layer.q_rows + layer.k_rows:]                  # [g·dv, d]
+    vo = layer.o.weight.float() @ wv.float().repeat_interleave(1, 0).view(2, 8, 32).repeat_interleave(2, 0).reshape(32, 32)
+    want = torch.zeros(32, 32)
+    want[:16, :16] = -0.5 * torch.eye(16)
+    assert torch.allclose(vo, want, atol=1e-6)
