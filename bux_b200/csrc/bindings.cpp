@@ -302,6 +302,37 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
   TORCH_CHECK(err == nullptr, "bux attention backward: ", err);
 }
 
+// ------------------------------------------------------------------ causal depthwise convolution
+void causal_conv(bool bwd, const Tensor& in, const Tensor& w, const c10::optional<Tensor>& bias,
+                 const c10::optional<Tensor>& position, Tensor& out) {
+  check_cuda(in, "in"); check_cuda(out, "out");
+  TORCH_CHECK(in.dim() == 3 && in.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16 &&
+                  out.sizes() == in.sizes(), "causal_conv: [B, T, C] bf16 in and out");
+  TORCH_CHECK(w.is_cuda() && w.scalar_type() == at::kFloat && w.is_contiguous() && w.dim() == 2 && w.size(0) == in.size(2),
+              "causal_conv: w is fp32 [C, taps]");
+  TORCH_CHECK(!position.has_value() || position->numel() == in.size(0) * in.size(1), "causal_conv: position is int32 [B, T]");
+  c10::cuda::CUDAGuard guard(in.device());
+  const char* err = bux::causal_conv(bwd, in.data_ptr(), w.data_ptr<float>(), opt_f32(bias), opt_i32(position), out.data_ptr(),
+                                     (int)in.size(0), (int)in.size(1), (int)in.size(2), (int)w.size(1), stream_of(in));
+  TORCH_CHECK(err == nullptr, "bux ", err);
+}
+void causal_conv_wgrad(const Tensor& x, const Tensor& dy, const c10::optional<Tensor>& position, Tensor& dw,
+                       const c10::optional<Tensor>& db) {
+  check_cuda(x, "x"); check_cuda(dy, "dy"); check_cuda(dw, "dw");
+  TORCH_CHECK(x.dim() == 3 && x.scalar_type() == at::kBFloat16 && dy.scalar_type() == at::kBFloat16 && dy.sizes() == x.sizes(),
+              "causal_conv_wgrad: [B, T, C] bf16 x and dy");
+  TORCH_CHECK(dw.scalar_type() == at::kFloat && dw.dim() == 2 && dw.size(0) == x.size(2), "causal_conv_wgrad: dw is fp32 [C, taps]");
+  c10::cuda::CUDAGuard guard(x.device());
+  float* dbp = nullptr;
+  if (db.has_value()) {
+    TORCH_CHECK(db->is_cuda() && db->scalar_type() == at::kFloat && db->numel() == x.size(2), "causal_conv_wgrad: db is fp32 [C]");
+    dbp = db->data_ptr<float>();
+  }
+  const char* err = bux::causal_conv_wgrad(x.data_ptr(), dy.data_ptr(), opt_i32(position), dw.data_ptr<float>(), dbp,
+                                           (int)x.size(0), (int)x.size(1), (int)x.size(2), (int)dw.size(1), stream_of(x));
+  TORCH_CHECK(err == nullptr, "bux ", err);
+}
+
 // ------------------------------------------------------------------ chunkwise recurrence
 void chunk_scan(const Tensor& a1, const Tensor& aux1, const c10::optional<Tensor>& aux3, const Tensor& a4, const Tensor& v,
                 const Tensor& lam, const c10::optional<Tensor>& s0, const c10::optional<Tensor>& out,
@@ -465,6 +496,8 @@ TORCH_LIBRARY(bux_b200, m) {
   m.def("zero_pad_rows(Tensor(a!) buf, Tensor offsets, Tensor counts) -> ()", &zero_pad_rows);
   m.def("ep_wait(Tensor flags, int epoch, Tensor? status, float limit_s) -> ()", &ep_wait);
   m.def("set_comm_ctas_per_sm(int n) -> ()", &set_comm_ctas_per_sm);
+  m.def("causal_conv(bool bwd, Tensor inp, Tensor w, Tensor? bias, Tensor? position, Tensor(a!) out) -> ()", &causal_conv);
+  m.def("causal_conv_wgrad(Tensor x, Tensor dy, Tensor? position, Tensor(a!) dw, Tensor(b!)? db) -> ()", &causal_conv_wgrad);
   m.def("chunk_scan(Tensor a1, Tensor aux1, Tensor? aux3, Tensor a4, Tensor v, Tensor lam, Tensor? s0, Tensor? out, Tensor? x_out, Tensor? states, Tensor(a!) s_last, Tensor? status, int bh, int n_chunks, bool reverse) -> ()", &chunk_scan);
   m.def("sf_rows_to_tiles(Tensor src, Tensor(a!) dst) -> ()", &sf_rows_to_tiles);
   m.def("tp_push_block(Tensor src, Tensor peer_base, int my_rank, int sms) -> ()", &tp_push_block);

@@ -39,6 +39,13 @@ void sumsq(const void* g, bool bf16, long n, float* out, cudaStream_t s);
 const char* topk_rows(const float* scores, long* idx, long rows, int n, int k, cudaStream_t s);
 void gather_rows(const void* x, const int* index, void* out, long rows, int d, cudaStream_t s);
 void combine_bwd(const void* y, const void* dout, const int* pos, const float* w, void* dy, float* dw, long picks, int k, int d, cudaStream_t s);
+// causal depthwise convolution over the tokens (conv_sm100.cu): forward (bwd = false: out = y, `in` = x) and
+// the input gradient (bwd = true: out = dx, `in` = dy); w [C, taps] fp32, position [B, T] int32 or null
+const char* causal_conv(bool bwd, const void* in, const float* w, const float* bias, const int* position, void* out,
+                        int B, int T, int C, int taps, cudaStream_t s);
+// dw [C, taps] and db [C] (or null), fp32, ADDED to what they hold
+const char* causal_conv_wgrad(const void* x, const void* dy, const int* position, float* dw, float* db, int B, int T,
+                              int C, int taps, cudaStream_t s);
 void combine_rows(const void* y, const int* pos, const float* w, void* out, long tokens, int k, int d, cudaStream_t s);
 
 }  // namespace bux

@@ -21,7 +21,7 @@ EXT_DIR = Path(__file__).resolve().parent.parent / "_ext"
 LIB = EXT_DIR / "libbux_b200.so"
 STAMP = EXT_DIR / "libbux_b200.hash"
 CUDA_SOURCES = ("gemm_sm100.cu", "elementwise.cu", "attention_sm100.cu", "attention_bwd_sm100.cu",
-                "comm_sm100.cu", "no_alloc.cu", "scan_sm100.cu")
+                "comm_sm100.cu", "no_alloc.cu", "scan_sm100.cu", "conv_sm100.cu")
 CPP_SOURCES = ("bindings.cpp",)
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-diag-suppress", "177"]

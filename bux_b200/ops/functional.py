@@ -343,6 +343,50 @@ def ref_linear_mxfp8(x, w, bias=None):
     return F.linear(xs, ws.to(xs.dtype), None if bias is None else bias.to(xs.dtype))
 
 
+# ------------------------------------------------------------------ causal depthwise convolution
+class _CausalConv(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias, position):
+        K = _K()
+        x = x.contiguous()
+        wf = w.float().contiguous()
+        pos = None if position is None else position.to(torch.int32).contiguous()
+        ctx.save_for_backward(x, wf, pos)
+        ctx.meta = (w.dtype, None if bias is None else bias.dtype)
+        return K.causal_conv(x, wf, None if bias is None else bias.float().contiguous(), pos)
+
+    @staticmethod
+    def backward(ctx, dy):
+        K = _K()
+        x, wf, pos = ctx.saved_tensors
+        w_dtype, b_dtype = ctx.meta
+        dy = dy.contiguous()
+        dx = K.causal_conv(dy, wf, None, pos, bwd=True) if ctx.needs_input_grad[0] else None
+        dw = db = None
+        if ctx.needs_input_grad[1] or ctx.needs_input_grad[2]:
+            dw, db = K.causal_conv_wgrad(x, dy, wf.shape[1], pos, bias=b_dtype is not None)
+            dw = dw.to(w_dtype)
+            db = None if db is None else db.to(b_dtype)
+        return dx, dw, db, None
+
+
+def causal_conv(x, w, bias=None, position=None):
+    """Causal depthwise convolution over the tokens of [B, T, C] rows: y[t] = Σ_j w[:, j] x[t-j]
+    (+ bias); taps that would reach across a document start (`position` < j) are dropped."""
+    taps = w.shape[1]
+    if kernels_on(x) and x.dim() == 3 and x.shape[-1] % 8 == 0 and taps <= 8:
+        return _CausalConv.apply(x, w, bias, position)
+    t = x.shape[1]
+    wx = w.to(x.dtype)
+    y = x * wx[:, 0]
+    for j in range(1, min(taps, t)):
+        shifted = F.pad(x[:, : t - j], (0, 0, j, 0))
+        if position is not None:
+            shifted = shifted * (position >= j).unsqueeze(-1).to(x.dtype)
+        y = y + shifted * wx[:, j]
+    return y if bias is None else y + bias.to(y.dtype)
+
+
 # ------------------------------------------------------------------ attention
 # Activation checkpointing may keep attention outputs across the replay of a block: the
 # first run appends (o, lse) here, the replay takes them back in the same order instead of

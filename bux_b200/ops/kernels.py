@@ -437,6 +437,26 @@ def ep_push_rows_mx(x, rank_of, row_of, peer_q, peer_sf, weights=None, peer_scal
     _count()
 
 
+def causal_conv(x: torch.Tensor, w: torch.Tensor, bias=None, position=None, bwd: bool = False) -> torch.Tensor:
+    """y[b,t,c] = Σ_j w[c,j] x[b,t-j,c] (+ bias) over [B, T, C] bf16 rows, w fp32 [C, taps <= 8]; a tap
+    is dropped where `position` (int32 [B, T], the position inside its document; None: whole rows)
+    is smaller than j. With `bwd` the same taps run forwards in time: the gradient by x of dy."""
+    out = _out(x.shape, dtype=x.dtype, device=x.device, op="causal_conv")
+    ops().causal_conv(bwd, x, w, bias, position, out)
+    _count()
+    return out
+
+
+def causal_conv_wgrad(x, dy, taps: int, position=None, bias: bool = False):
+    """(dw fp32 [C, taps], db fp32 [C] or None) of `causal_conv`."""
+    c = x.shape[-1]
+    dw = torch.zeros(c, taps, dtype=torch.float32, device=x.device)
+    db = torch.zeros(c, dtype=torch.float32, device=x.device) if bias else None
+    ops().causal_conv_wgrad(x, dy, position, dw, db)
+    _count()
+    return dw, db
+
+
 def sf_rows_to_tiles(src: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
     """Row-major E8M0 scales [rows, cols/32] → the scale tiles a block-scaled GEMM reads."""
     rows, sf_cols = src.shape

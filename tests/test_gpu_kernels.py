@@ -388,3 +388,41 @@ def test_nvfp4_quantiser_matches_the_recipe(cuda):
     assert torch.equal(scales, ws)
     mism = (packed != wp).float().mean().item()
     assert mism < 1e-3, mism   # ties at a grid midpoint may round differently after the division
+
+
+@pytest.mark.parametrize("taps,bias,packed", [(4, False, False), (3, True, True), (8, True, False), (1, False, True)])
+def test_causal_conv_matches_the_shifted_sums(cuda, taps, bias, packed):
+    """The causal depthwise convolution kernels (forward, dx, dw, db) against the PyTorch sum of
+    shifted rows in fp32, with and without document starts inside the rows."""
+    from bux_b200 import ops
+
+    torch.manual_seed(0)
+    b, t, c = 3, 200, 264
+    x = torch.randn(b, t, c, device=cuda).bfloat16().requires_grad_()
+    w = (torch.randn(c, taps, device=cuda) * 0.5).bfloat16().requires_grad_()
+    bb = torch.randn(c, device=cuda).bfloat16().requires_grad_() if bias else None
+    pos = None
+    if packed:
+        pos = torch.arange(t, device=cuda).repeat(b, 1)
+        pos[0, 70:] -= 70
+        pos[1, 5:] -= 5
+        pos[1, 131:] -= 126
+    dy = torch.randn(b, t, c, device=cuda).bfloat16()
+    y = ops.causal_conv(x, w, bb, pos)
+    y.backward(dy)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    br = bb.detach().float().requires_grad_() if bias else None
+    yr = xr * wr[:, 0]
+    for j in range(1, taps):
+        shifted = torch.nn.functional.pad(xr[:, : t - j], (0, 0, j, 0))
+        if pos is not None:
+            shifted = shifted * (pos >= j).unsqueeze(-1).float()
+        yr = yr + shifted * wr[:, j]
+    if bias:
+        yr = yr + br
+    yr.backward(dy.float())
+    assert rel_err(y, yr) < 1e-2
+    assert rel_err(x.grad, xr.grad) < 1e-2
+    assert rel_err(w.grad, wr.grad) < 1e-2
+    if bias:
+        assert rel_err(bb.grad, br.grad) < 1e-2
