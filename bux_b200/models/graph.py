@@ -32,9 +32,10 @@ class Sequence(nn.Module):
 class ResidualBranch(nn.Module):
     """``[body]``: x + body(x), or whatever the residual algebra makes of a branch."""
 
-    def __init__(self, body, algebra: Optional[nn.Module] = None):
+    def __init__(self, body, algebra: Optional[nn.Module] = None, name: str = "branch"):
         super().__init__()
         self.body = body
+        self.name = name   # what observed values of this branch are filed under
         if algebra is not None:
             self.algebra = algebra
 
@@ -45,15 +46,24 @@ class ResidualBranch(nn.Module):
         if outer:   # precision(first=..., last=...) counts these
             ctx.precision.branch = ctx.top_branch
             ctx.top_branch += 1
+        observing = outer and ctx.observing
+        if observing:   # values observed inside are filed under gqa.00, moe.03, ...
+            from . import observe
+
+            count = ctx.branch_names.get(self.name, 0)
+            ctx.branch_names[self.name] = count + 1
+            ctx.observed_branch = f"{self.name}.{count:02d}"
         ctx.branch_depth += 1
         try:
-            if algebra is not None:
-                return algebra(x, self.body, ctx)
-            return x + self.body(x, ctx)
+            y = algebra(x, self.body, ctx) if algebra is not None else x + self.body(x, ctx)
+            if observing:
+                observe.stream(ctx, x, y)
+            return y
         finally:
             ctx.branch_depth -= 1
             if outer:
                 ctx.precision.branch = -1
+                ctx.observed_branch = None
 
 
 class Parallel(nn.Module):
@@ -324,7 +334,9 @@ class _BlockRun:
         ctx = self.ctx
         saved = (ctx.taps, ctx.losses, ctx.metrics, ctx.ports, ctx.branch_index, ctx.top_branch)
         ctx.losses = {}
+        was_observing = ctx.observing
         if replay:
+            ctx.observing = False   # the first run observed
             ctx.branch_index, ctx.top_branch = self.branches   # the branches count as in the first run
             ctx.taps = {k: list(v) for k, v in self.taps.items()}
             ctx.metrics, ctx.ports = {}, dict(self.ports)
@@ -339,6 +351,7 @@ class _BlockRun:
         finally:
             OF.attention_replay = None
             ctx.tail_values_unused = False
+            ctx.observing = was_observing
             if replay:
                 self.kept = None
             if replay:
@@ -446,7 +459,9 @@ class GraphBuilder:
                 body = self.build(node.body)
             finally:
                 self.depth -= 1
-            return ResidualBranch(body, algebra)
+            from . import observe
+
+            return ResidualBranch(body, algebra, observe.branch_name(node))
         if isinstance(node, ir.Sum):
             return Parallel([self.build(n) for n in node.terms], product=False)
         if isinstance(node, ir.Prod):

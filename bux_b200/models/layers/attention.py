@@ -251,6 +251,10 @@ class GQA(nn.Module):
         kw = dict(causal=True, window=c.sliding_window_size, sinks=sinks,
                   softcap=c.softcap, scale=c.scale, segments=ctx.segments)
         cp = getattr(ctx.parallel, "context_group", None) if ctx.parallel is not None else None
+        if ctx.observing and cp is None:
+            from .. import observe
+
+            observe.attention_sample(ctx, q, k, c.scale)
         if cp is not None:
             from ...parallel import context
 

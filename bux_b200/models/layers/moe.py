@@ -157,6 +157,10 @@ class MoE(nn.Module):
                 ctx.report("balance_loss", loss, w)
             if hasattr(self, "router_load"):
                 self.router_load += picks.detach().sum((0, 1))
+        if ctx.observing:
+            from .. import observe
+
+            observe.router(ctx, logits[..., :n], idx, n, getattr(self, "router_bias", None))
         weights = scores.gather(-1, idx)
         if c.normalize_top_k:
             total = weights.sum(-1, keepdim=True) + sinks.sum(-1, keepdim=True)

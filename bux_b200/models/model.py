@@ -36,11 +36,14 @@ class Model(nn.Module):
     def forward(self, input_ids: torch.Tensor, positions: Optional[torch.Tensor] = None,
                 segments: Optional[torch.Tensor] = None, *, training: Optional[bool] = None,
                 precision: Optional[Precision] = None, methods=None, parallel=None,
-                step: int = 0) -> Context:
+                step: int = 0, observe: Optional[dict] = None) -> Context:
         ctx = Context(input_ids, positions, segments,
                       training=self.training if training is None else training,
                       precision=precision or Precision(compute=self.dtype), methods=methods,
                       parallel=parallel, step=step)
+        if observe is not None:   # an observed step: layers file their statistics in ctx.observed
+            ctx.observing = True
+            ctx.observe_histograms = bool(observe.get("histograms"))
         ctx.output = self.graph(input_ids, ctx)
         return ctx
 

@@ -111,6 +111,13 @@ class Context:
         self.branch_index = 0
         self.top_branch = 0     # residual branches that are inside no other, run so far
         self.branch_depth = 0
+        # observe(every=...): set for the forward of an observed step (`bux_b200.models.observe`)
+        self.observing = False
+        self.observe_histograms = False
+        self.observed: dict = {}
+        self.observed_histograms: dict = {}
+        self.observed_branch = None
+        self.branch_names: dict = {}   # how many branches of each name ran so far
         self.pending_read = None  # single-pass hyper-connections: the read the last branch computed
 
     # taps are named stacks

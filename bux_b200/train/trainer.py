@@ -119,6 +119,10 @@ class Trainer:
         self._norm_acc = None
         self._hooks_installed = False
         self._status_host = None
+        self.observing = None          # None, or {"histograms": bool}: what the next training forward observes
+        self.pre_step: list = []       # callables of the number of the step that is about to run
+        self.observed: dict = {}
+        self.observed_histograms: dict = {}
         self._prefixes = None
         self._token_bytes = None
         self.stretches = curriculum.stretches(t)
@@ -216,7 +220,10 @@ class Trainer:
             late = self.step >= round(sw.at * self.train.steps)
             self.precision.passes = tuple(sw.passes if late else self.train.precision.passes)
         ctx = self.model(ids, pos, segments, training=training, precision=self.precision,
-                         methods=self.train.methods, parallel=self.parallel, step=self.step)
+                         methods=self.train.methods, parallel=self.parallel, step=self.step,
+                         observe=self.observing if training else None)
+        if ctx.observed or ctx.observed_histograms:   # an observed step: the hook reads them
+            self.observed, self.observed_histograms = ctx.observed, ctx.observed_histograms
         parts = objective.compute(ctx, mb, self.train.loss, span=span, prefixes=self.prefix_table(),
                                   progress=self.step / max(1, self.train.steps))
         loss = parts.total_sum * inv_count + parts.per_batch / (n_micro * world)
@@ -227,6 +234,8 @@ class Trainer:
     def train_step(self, batch: data.Batch) -> dict:
         """Run one optimizer step on this rank's rows of `batch`; returns device scalars."""
         t = self.train
+        for before in self.pre_step:   # hooks that prepare the step about to run (its number is step + 1)
+            before(self.step + 1)
         cfg = self.config_at(self.step)
         n_micro = max(1, min(t.methods.microbatches, batch.input_ids.shape[0]))
         world = self.parallel.data_world if self.parallel is not None else 1

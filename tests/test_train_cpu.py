@@ -152,8 +152,32 @@ def test_ema_ships_a_blend_and_observe_logs_per_layer_stats(tmp_path):
     keys = set().union(*(set(x) for x in lines))
     assert any(k.startswith("param/") for k in keys) and any(k.startswith("update/") for k in keys)
     assert any(k.startswith("act/graph") for k in keys)
+    # the forward of an observed step files the stream and the attention under their branches
+    for want in ("act/rms/gqa.00", "act/update_rms/gated_mlp.01", "act/max_abs/gqa.01", "act/kurtosis/gated_mlp.00",
+                 "attn/logit_max/gqa.00", "attn/entropy/gqa.01"):
+        assert want in keys, want
+    observed = [x for x in lines if "act/rms/gqa.00" in x]
+    assert [x["step"] for x in observed] == [4, 8, 12] and all(x["act/rms/gqa.00"] > 0 for x in observed)
     hist = [json.loads(x) for x in (folder / "histograms.jsonl").read_text().splitlines()]
     assert hist and hist[0]["step"] == 4 and sum(hist[0]["histograms"][name]) == tr.model.get_parameter(name).numel()
+    assert sum(hist[0]["stream"]["act/hist/gqa.00"]) == 8 * 64 * 64      # batch x seq_len x d_model entries
+
+
+def test_observe_files_the_routers_statistics():
+    src = SMOKE.replace("ffn   = gated_mlp(intermediate_size=4 * d_model, activation=swish)",
+                        "ffn   = moe(num_experts=4, top_k=2, load_balancing=aux_free, expert=gated_mlp(intermediate_size=32, activation=swish))")
+    run = compile_runs(src, filename="smoke.bux", overrides=["steps = 4", "schedule = constant"])[0]
+    tr = Trainer(run, device="cpu")
+    tr.observing = {"histograms": False}
+    tr.train_step(next(iter(tr.batches())))
+    got = tr.observed
+    for want in ("router/max_load/moe.00", "router/min_load/moe.01", "router/dead/moe.00", "router/entropy/moe.01",
+                 "router/z/moe.00", "router/bias_std/moe.01", "act/rms/moe.00"):
+        assert want in got, (want, sorted(got))
+    assert 1.0 <= float(got["router/max_load/moe.00"]) <= 4.0 and float(got["router/dead/moe.00"]) == 0.0
+    tr.observing = None
+    tr.train_step(next(iter(tr.batches())))
+    assert tr.observed is got            # an unobserved step files nothing new
 
 
 def test_remat_auto_takes_the_cheapest_preset_that_fits():
