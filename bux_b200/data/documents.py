@@ -15,7 +15,6 @@ from typing import Iterator
 
 import numpy as np
 
-CHATML = ("{% for m in messages %}<|im_start|>{{ m.role }}\n{{ m.content }}<|im_end|>\n{% endfor %}")
 
 
 def files_of(path: str) -> list:
@@ -65,32 +64,26 @@ def text(c, tok, tok_cfg=None) -> Iterator:
         yield arr, np.ones(len(arr), bool)
 
 
-def render(messages: list, template: str) -> list:
-    """[(text, role)] segments of a conversation: the template is applied one message at a
-    time so each piece of text knows whose turn it is."""
-    try:
-        import jinja2
-
-        env = jinja2.Environment()
-        tpl = env.from_string(template)
-        return [(tpl.render(messages=[m]), m["role"]) for m in messages]
-    except ImportError:
-        return [(f"<|im_start|>{m['role']}\n{m['content']}<|im_end|>\n", m["role"]) for m in messages]
-
-
 def chat(c, tok, tok_cfg=None) -> Iterator:
-    template = c.template or CHATML
+    """Conversations rendered by the source's chat template (`bux_b200.data.templates`); the loss
+    mask follows ``train_on``: every assistant reply (without its header), the last one, or all."""
+    from . import templates
+
+    template = templates.load(c.template)
     for messages in _records(c.path, c.column):
         if not messages:
             continue
-        segs = render(messages, template)
-        last_assistant = max((i for i, (_, r) in enumerate(segs) if r == "assistant"), default=-1)
+        pieces = template.pieces(messages)
+        last_assistant = max((i for i, (_, r, _) in enumerate(pieces) if r == "assistant"), default=-1)
         ids, mask = [], []
-        for i, (piece, role) in enumerate(segs):
-            t = tok.encode(piece)
+        for i, (piece, role, start) in enumerate(pieces):
             on = (c.train_on == "all" or (role == "assistant" and (c.train_on == "assistant" or i == last_assistant)))
-            ids.extend(t)
-            mask.extend([on] * len(t))
+            head, body = (piece[:start], piece[start:]) if on and c.train_on != "all" else ("", piece)
+            for text, trained in ((head, False), (body, on)):
+                if text:
+                    t = tok.encode(text)
+                    ids.extend(t)
+                    mask.extend([trained] * len(t))
         if ids:
             yield np.asarray(ids, np.int32), np.asarray(mask, bool)
 

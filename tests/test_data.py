@@ -100,3 +100,61 @@ precision = precision(compute=float32)
     assert losses[-1] < losses[0]
     again = next(iter(Trainer(run, device="cpu", cache=tmp_path / "packed").batches()))
     assert np.array_equal(again.input_ids, first.input_ids)  # batch i depends on the seed and i only
+
+
+def test_chat_templates_render_prefixes_and_train_on_the_replies(tmp_path):
+    """A Llama-3-style template (a beginning-of-text token once, headers per role) read from a
+    tokenizer folder: what each message adds, and which characters a run trains on."""
+    import json
+
+    from bux_b200.data import templates
+
+    source = ("{{ bos_token }}{% for m in messages %}<|start_header_id|>{{ m['role'] }}<|end_header_id|>\n\n"
+              "{{ m['content'] | trim }}<|eot_id|>{% endfor %}"
+              "{% if add_generation_prompt %}<|start_header_id|>assistant<|end_header_id|>\n\n{% endif %}")
+    (tmp_path / "tokenizer_config.json").write_text(json.dumps(
+        {"bos_token": {"content": "<|begin_of_text|>"}, "eos_token": "<|eot_id|>", "chat_template": source}))
+    t = templates.load(str(tmp_path))
+    msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": " hi "},
+            {"role": "assistant", "content": "hello"}, {"role": "user", "content": "bye"},
+            {"role": "assistant", "content": "ciao"}]
+    whole = t.render(msgs)
+    assert whole.startswith("<|begin_of_text|><|start_header_id|>system") and whole.count("<|begin_of_text|>") == 1
+    assert t.render(msgs[:2], prompt=True).endswith("<|start_header_id|>assistant<|end_header_id|>\n\n")
+    pieces = t.pieces(msgs)
+    assert "".join(p for p, _, _ in pieces) == whole
+    assert [r for _, r, _ in pieces] == ["system", "user", "assistant", "user", "assistant"]
+    text, role, start = pieces[2]
+    assert text[start:] == "hello<|eot_id|>" and text[:start] == "<|start_header_id|>assistant<|end_header_id|>\n\n"
+    assert pieces[1][2] == 0 and "hi<|eot_id|>" in pieces[1][0]          # trimmed as the template says
+    # built-in and inline sources
+    assert templates.load(None).render([{"role": "user", "content": "x"}], prompt=True).endswith("<|im_start|>assistant\n")
+    assert templates.load("chatml").source == templates.CHATML
+    assert templates.load("{{ messages | length }} turns").render(msgs) == "5 turns"
+    import pytest
+
+    with pytest.raises(ValueError):
+        templates.load("no_such_template")
+
+
+def test_chat_documents_mask_only_the_assistants_words(tmp_path):
+    import json
+
+    from bux_b200.config import training as T
+    from bux_b200.data import documents as D
+    from bux_b200.data.tokenizer import load as load_tokenizer
+
+    rows = [{"messages": [{"role": "user", "content": "ab"}, {"role": "assistant", "content": "cd"},
+                          {"role": "user", "content": "ef"}, {"role": "assistant", "content": "gh"}]}]
+    path = tmp_path / "chat.jsonl"
+    path.write_text("\n".join(json.dumps(r) for r in rows))
+    tok = load_tokenizer(T.TokenizerConfig(name="bytes"))
+
+    def trained(train_on):
+        cfg = T.ChatConfig(path=str(path), train_on=train_on)
+        (ids, mask), = list(D.chat(cfg, tok))
+        return bytes(int(i) for i, m in zip(ids, mask) if m).decode()
+
+    assert trained("assistant") == "cd<|im_end|>\ngh<|im_end|>\n"
+    assert trained("last") == "gh<|im_end|>\n"
+    assert trained("all").startswith("<|im_start|>user\nab")
