@@ -151,8 +151,18 @@ def _dispatch(args) -> int:
     if cmd == "render":
         from .lang.render import render
 
-        for r in _runs(args)[:1]:
-            print(render(r.arch))
+        from .lang import BuxError, compile
+
+        try:
+            archs = [r.arch for r in _runs(args)[:1]]
+        except BuxError as err:
+            if "defines a model, not a run" not in err.message:
+                raise
+            # a model file draws as well as a run's
+            path = Path(args.file)
+            archs = [compile(path.read_text(), filename=str(path), entry=args.entry, overrides=args.overrides)]
+        for arch in archs:
+            print(render(arch))
         return 0
     if cmd == "train":
         # one process, or one rank of a job started by torchrun / srun / mpirun: `train_here`
