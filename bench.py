@@ -234,10 +234,13 @@ def main() -> int:
     # with four ranks on one host they cost 0.3 s a step (5.38 s against 5.09 s). All ranks take
     # the same decision and the smallest count.
     inputs_bytes = blocks * args.rows * args.seq_len * arch.d_model * 2
+    if offload and args.inputs == "device":   # asked for: the inputs first, attention outputs with the rest
+        offload = False
+        spare -= inputs_bytes
     keep_blocks = agreed_min(max(0, min(blocks, int(spare // kept_bytes))))
-    if offload and args.inputs != "host":
+    if offload and args.inputs == "auto":
         fits = keep_blocks == blocks and spare - blocks * kept_bytes >= inputs_bytes
-        if args.inputs == "device" or agreed_min(int(fits)):
+        if agreed_min(int(fits)):
             offload = False
     note(f"probe step: peak {gib(torch.cuda.max_memory_allocated(device))}, reserved "
          f"{gib(torch.cuda.memory_reserved(device))}, free {gib(free)} of {gib(total_mem)}; "

@@ -99,3 +99,60 @@ def test_studio_api(tmp_path):
             assert e.code == 403
     finally:
         server.shutdown()
+
+
+def test_trackers_forward_every_logged_step_to_their_package(tmp_path, monkeypatch):
+    """W&B and TensorBoard sinks against stand-ins for the packages (neither is installed here):
+    a W&B run resumes under the id kept in the run's folder; TensorBoard writes scalars only."""
+    import sys
+    import types
+
+    from bux_b200.config import training as T
+    from bux_b200.lang import compile_runs
+    from bux_b200.train import trackers
+
+    calls = {"init": [], "log": [], "scalars": [], "closed": 0}
+    wandb = types.ModuleType("wandb")
+    wandb.util = types.SimpleNamespace(generate_id=lambda: "abc123")
+
+    class _Run:
+        def log(self, values, step):
+            calls["log"].append((step, dict(values)))
+
+        def finish(self):
+            calls["closed"] += 1
+
+    def init(**kw):
+        calls["init"].append(kw)
+        return _Run()
+
+    wandb.init = init
+    monkeypatch.setitem(sys.modules, "wandb", wandb)
+    tb = types.ModuleType("torch.utils.tensorboard")
+
+    class SummaryWriter:
+        def __init__(self, folder):
+            calls["tb_folder"] = folder
+
+        def add_scalar(self, name, value, step):
+            calls["scalars"].append((name, value, step))
+
+        def close(self):
+            calls["closed"] += 1
+
+    tb.SummaryWriter = SummaryWriter
+    monkeypatch.setitem(sys.modules, "torch.utils.tensorboard", tb)
+    run = compile_runs(SMOKE, filename="smoke.bux")[0]
+    configs = [T.WandbConfig(project="p", tags=("a",)), T.TensorBoardConfig()]
+    sinks = trackers.build(configs, tmp_path, run)
+    for s in sinks:
+        s.write(3, {"loss": 1.5, "note": "text"})
+        s.close()
+    assert calls["init"][0]["id"] == "abc123" and calls["init"][0]["resume"] == "allow" and calls["init"][0]["project"] == "p"
+    assert (tmp_path / "wandb_id").read_text() == "abc123"
+    assert calls["log"] == [(3, {"loss": 1.5, "note": "text"})]
+    assert calls["scalars"] == [("loss", 1.5, 3)] and calls["tb_folder"].endswith("tensorboard") and calls["closed"] == 2
+    # a second start of the same run takes the id on file
+    wandb.util = types.SimpleNamespace(generate_id=lambda: "other")
+    trackers.build(configs[:1], tmp_path, run)
+    assert calls["init"][1]["id"] == "abc123"
