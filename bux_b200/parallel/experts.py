@@ -537,6 +537,15 @@ class ExpertParallel:
     def __init__(self, group, method: str = "fused_ep", capacity: Optional[float] = None):
         self.group = group
         self.method = method if method in ("fused_ep",) else "all_to_all"
+        if self.method == "fused_ep":
+            from .. import runtime
+
+            if not runtime.on_one_node(group):
+                # the in-kernel exchange stores into the peers' memory over NVLink: one machine only
+                import warnings
+
+                warnings.warn("methods(moe=fused_ep): the expert axis spans machines; taking moe=all_to_all (NCCL)")
+                self.method = "all_to_all"
         self.capacity = capacity or 1.25
         self.world = dist.get_world_size(group)
         self.fused: dict = {}

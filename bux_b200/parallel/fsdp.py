@@ -406,6 +406,14 @@ class FSDP:
         options = getattr(getattr(t, "compiler", None), "options", "") or ""
         self.fused_comm = None
         fused = "--fsdp=fused" in options.split() and par.device.type == "cuda"
+        if fused:
+            from .. import runtime
+
+            if not runtime.on_one_node(self.group):   # peer-memory kernels: one machine only
+                import warnings
+
+                warnings.warn("compiler(options=\"--fsdp=fused\"): the sharding axes span machines; taking NCCL")
+                fused = False
         skip = {id(p) for p in skip}
         blocks = self._blocks(model)
         self.units: list = []

@@ -182,6 +182,14 @@ def shard_model(model: nn.Module, par) -> None:
     sequence = "tensor" in _axes(par.train.layout.stream)
     # the collectives run inside the GEMM kernels (NVLink peers, bf16, sequence-parallel stream)
     fused = (par.train.methods.tensor == "fused" and sequence and par.device.type == "cuda")
+    if fused:
+        from .. import runtime
+
+        if not runtime.on_one_node(par.tensor_group):   # peer-memory kernels: one machine only
+            import warnings
+
+            warnings.warn("methods(tensor=fused): the tensor axis spans machines; taking the NCCL collectives")
+            fused = False
     par.tensor_partial = []
     layout: dict = {}
     done: set = set()

@@ -71,3 +71,27 @@ def agree_on_folder(folder, rank: int, world: int, barrier) -> None:
     if not seen:
         raise ValueError(f"rank {rank} does not see {folder}: checkpoints and logs need a folder "
                          "every process shares")
+
+
+def node_name() -> str:
+    """The machine this process runs on (``BUX_NODE_NAME`` overrides the host name: for tests,
+    and for containers that share a host name across nodes)."""
+    import socket
+
+    return os.environ.get("BUX_NODE_NAME") or socket.gethostname()
+
+
+_one_node: dict = {}
+
+
+def on_one_node(group) -> bool:
+    """Whether every rank of `group` runs on the same machine: the kernels that load and store
+    over peer memory (NVLink) need that; across machines the NCCL paths take over."""
+    import torch.distributed as dist
+
+    key = id(group)
+    if key not in _one_node:
+        names = [None] * dist.get_world_size(group)
+        dist.all_gather_object(names, node_name(), group=group)
+        _one_node[key] = len(set(names)) == 1
+    return _one_node[key]

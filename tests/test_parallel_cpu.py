@@ -400,3 +400,41 @@ def test_recurrent_mixers_under_context_parallelism(tmp_path, mixer):
     assert got["losses"] == pytest.approx(want_losses, abs=2e-5)
     for name, p in want.items():
         assert torch.allclose(got["state"][name], p, atol=2e-5), name
+
+
+def _node_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      BUX_NODE_NAME=f"node{rank // 2}")
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import warnings
+
+    from bux_b200 import runtime
+    from bux_b200.parallel.experts import ExpertParallel
+
+    pair = None
+    for ranks in ([0, 1], [2, 3]):
+        g = dist.new_group(ranks)
+        if rank in ranks:
+            pair = g
+    with warnings.catch_warnings(record=True) as caught:
+        warnings.simplefilter("always")
+        across = ExpertParallel(dist.group.WORLD, "fused_ep")
+        inside = ExpertParallel(pair, "fused_ep")
+    if rank == 0:
+        torch.save({"world": runtime.on_one_node(dist.group.WORLD), "pair": runtime.on_one_node(pair),
+                    "across": across.method, "inside": inside.method,
+                    "warned": [str(w.message) for w in caught]}, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_peer_memory_paths_are_for_one_machine(tmp_path):
+    """Four ranks that say they run on two machines: the in-kernel expert exchange is kept for a
+    group inside one machine and gives way to NCCL's all-to-all for a group across them."""
+    out = str(tmp_path / "n.pt")
+    mp.spawn(_node_worker, args=(4, _free_port(), out), nprocs=4, join=True)
+    got = torch.load(out)
+    assert got["pair"] is True and got["world"] is False
+    assert got["inside"] == "fused_ep" and got["across"] == "all_to_all"
+    assert len(got["warned"]) == 1 and "spans machines" in got["warned"][0]
