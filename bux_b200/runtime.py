@@ -91,6 +91,10 @@ def on_one_node(group) -> bool:
 
     key = id(group)
     if key not in _one_node:
+        local = _first_int(("LOCAL_WORLD_SIZE", "SLURM_NTASKS_PER_NODE", "OMPI_COMM_WORLD_LOCAL_SIZE"), 0)
+        if "BUX_NODE_NAME" not in os.environ and local and local >= dist.get_world_size():
+            _one_node[key] = True    # the launcher says the whole job is on this machine: nothing to ask
+            return True
         names = [None] * dist.get_world_size(group)
         dist.all_gather_object(names, node_name(), group=group)
         _one_node[key] = len(set(names)) == 1
