@@ -34,7 +34,7 @@ def _free_port() -> int:
 
 def _worker(rank, world, port, overrides, out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
-                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+                      LOCAL_RANK=str(rank), LOCAL_WORLD_SIZE=str(world), NCCL_NVLS_ENABLE="0")
     sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     import torch.distributed as dist
 
@@ -127,7 +127,7 @@ DENSE = MOE.replace("e = moe(num_experts=8, top_k=2, expert=gated_mlp(intermedia
 
 def _tensor_worker(rank, world, port, overrides, out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
-                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+                      LOCAL_RANK=str(rank), LOCAL_WORLD_SIZE=str(world), NCCL_NVLS_ENABLE="0")
     sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     import torch.distributed as dist
 
