@@ -126,6 +126,13 @@ class Trainer:
         self._prefixes = None
         self._token_bytes = None
         self.stretches = curriculum.stretches(t)
+        if t.methods.interleave:
+            # a schedule, not arithmetic: the step's numbers are the same without it
+            import warnings
+
+            warnings.warn("methods(interleave=true): the interleaved step is not built here; the microbatches of a "
+                          "step run one after another (same gradients, no overlap of one's forward with "
+                          "another's backward)")
         self.timers = Timers()
 
     # ------------------------------------------------------------------ setup
