@@ -129,7 +129,6 @@ def main() -> int:
     from bux_b200 import runtime
     from bux_b200.lang import compile_runs
     from bux_b200.ops import kernels as K
-    from bux_b200.train import data as D
     from bux_b200.train.flops import flops_per_token
     from bux_b200.train.trainer import Trainer
 

@@ -15,10 +15,8 @@ this project's own.
 from __future__ import annotations
 
 import difflib
-import itertools
 import operator
 import re
-from contextlib import contextmanager
 from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Any, Callable, Mapping, Optional, Sequence, Union

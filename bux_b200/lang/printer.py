@@ -13,7 +13,6 @@ import re
 
 from pydantic import BaseModel
 
-from ..config import layers as L
 from ..config import training as T
 from . import ir
 

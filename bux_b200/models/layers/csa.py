@@ -25,7 +25,6 @@ This is the layer's dense statement (all t x (t + t) logits), like the other spa
 
 from __future__ import annotations
 
-import math
 
 import torch
 from torch import nn

@@ -10,8 +10,6 @@ grouped tcgen05 GEMM. The checkpoint layer converts.
 
 from __future__ import annotations
 
-import math
-from typing import Optional
 
 import torch
 from torch import nn

@@ -14,7 +14,7 @@ import torch
 import torch.nn.functional as F
 
 from . import reference as ref
-from .functional import _K, _quant_weight, kernels_on
+from .functional import _K, kernels_on
 
 CE_CHUNK_BYTES = 1 << 31  # logits held at once (bf16): fewer, larger chunks mean fewer passes over dW
 

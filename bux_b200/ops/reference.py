@@ -10,7 +10,6 @@ dense MoE (``architecture/experts/moe.py:587``).
 
 from __future__ import annotations
 
-import math
 from typing import Optional
 
 import torch

@@ -7,7 +7,6 @@ Reference: ``parallel/mesh.py:27-182`` (`AXES`, `sizes`, `grid`, `split`).
 
 from __future__ import annotations
 
-from dataclasses import dataclass
 from typing import Optional
 
 AXES = ("stage", "data", "fsdp", "context", "expert", "tensor")

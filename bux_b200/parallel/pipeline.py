@@ -13,7 +13,6 @@ blocks against the neighbour's backward send.
 
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 import torch.distributed as dist

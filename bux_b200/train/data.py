@@ -16,12 +16,10 @@ from __future__ import annotations
 import bisect
 import glob
 import itertools
-import json
 import queue
 import threading
 from dataclasses import dataclass
-from pathlib import Path
-from typing import Iterator, NamedTuple, Optional, Sequence
+from typing import Iterator, NamedTuple, Sequence
 
 import numpy as np
 

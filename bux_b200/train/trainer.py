@@ -41,8 +41,6 @@ def pick_device(spec: Optional[str] = None) -> torch.device:
     if spec:
         return torch.device(spec)
     if torch.cuda.is_available():
-        import os
-
         return torch.device("cuda", runtime.local_rank())
     return torch.device("cpu")
 
