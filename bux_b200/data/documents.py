@@ -16,6 +16,12 @@ from typing import Iterator
 import numpy as np
 
 
+def schema():
+    """Arrow schema of a batch of documents (what the map hands to the shuffle)."""
+    import pyarrow as pa
+
+    return pa.schema([("key", pa.int64()), ("input_ids", pa.list_(pa.int32())), ("loss_mask", pa.list_(pa.bool_()))])
+
 
 def files_of(path: str) -> list:
     found = sorted(glob.glob(path))
@@ -49,10 +55,10 @@ def _records(path: str, column: str) -> Iterator:
             yield from batch.column(0).to_pylist()
 
 
-def text(c, tok, tok_cfg=None) -> Iterator:
+def text(c, tok, tok_cfg=None, values=None) -> Iterator:
     bos = tok.token_id(tok_cfg.bos) if (c.bos and tok_cfg is not None) else (tok.token_id("<|endoftext|>") if c.bos else None)
     eos = tok.token_id(tok_cfg.eos) if (c.eos and tok_cfg is not None) else (tok.token_id("<|endoftext|>") if c.eos else None)
-    for value in _records(c.path, c.column):
+    for value in (_records(c.path, c.column) if values is None else values):
         if not value:
             continue
         ids = tok.encode(value)
@@ -64,13 +70,13 @@ def text(c, tok, tok_cfg=None) -> Iterator:
         yield arr, np.ones(len(arr), bool)
 
 
-def chat(c, tok, tok_cfg=None) -> Iterator:
+def chat(c, tok, tok_cfg=None, values=None) -> Iterator:
     """Conversations rendered by the source's chat template (`bux_b200.data.templates`); the loss
     mask follows ``train_on``: every assistant reply (without its header), the last one, or all."""
     from . import templates
 
     template = templates.load(c.template)
-    for messages in _records(c.path, c.column):
+    for messages in (_records(c.path, c.column) if values is None else values):
         if not messages:
             continue
         pieces = template.pieces(messages)
@@ -88,10 +94,11 @@ def chat(c, tok, tok_cfg=None) -> Iterator:
             yield np.asarray(ids, np.int32), np.asarray(mask, bool)
 
 
-def documents(c, tok, tok_cfg=None) -> Iterator:
-    """(key, input_ids, loss_mask) of the source's documents inside its split."""
+def documents(c, tok, tok_cfg=None, values=None) -> Iterator:
+    """(key, input_ids, loss_mask) of the source's documents inside its split; of `values`
+    (the source's column, record by record) when given, else of the source's files."""
     make = text if c.type == "text" else chat
-    for ids, mask in make(c, tok, tok_cfg):
+    for ids, mask in make(c, tok, tok_cfg, values):
         k = key_of(ids)
         if in_split(k, c.split):
             yield k, ids, mask

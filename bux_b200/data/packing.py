@@ -13,6 +13,14 @@ import bisect
 import numpy as np
 
 
+def schema():
+    """Arrow schema of packed rows (a dataset's parquet parts)."""
+    import pyarrow as pa
+
+    return pa.schema([("input_ids", pa.list_(pa.int32())), ("position_ids", pa.list_(pa.int32())),
+                      ("loss_mask", pa.list_(pa.bool_()))])
+
+
 def _pieces(doc: int, length: int, seq_len: int, long: str) -> list:
     """What a document contributes: itself, or what `long` makes of one longer than a row."""
     if length <= seq_len:

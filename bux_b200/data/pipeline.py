@@ -51,6 +51,52 @@ class Job:
     def folder(self) -> Path:
         return Path(self.cache) / self.name
 
+    # -------------------------------------------------------- the two functions an engine runs
+    def map(self, batches):
+        """Records → documents, a batch at a time: `batches` are Arrow record batches whose
+        first column is the source's column; yields batches in `documents.schema()`. This is
+        the contract of Spark's ``mapInArrow``; the local engine calls it per file."""
+        import pyarrow as pa
+
+        tok = TK.load(self.tokenizer)
+        sch = D.schema()
+        for batch in batches:
+            docs = list(D.documents(self.source, tok, self.tokenizer, values=batch.column(0).to_pylist()))
+            yield pa.record_batch([pa.array([d[0] for d in docs], pa.int64()),
+                                   pa.array([d[1] for d in docs], pa.list_(pa.int32())),
+                                   pa.array([d[2] for d in docs], pa.list_(pa.bool_()))], schema=sch)
+
+    def chunks(self, tokens: int) -> int:
+        """How many chunks (a power of two) documents of `tokens` tokens are shuffled into."""
+        return 1 << max(0, int(np.ceil(np.log2(max(1.0, tokens / self.packing.chunk)))))
+
+    def reduce(self, chunk: int, table):
+        """One chunk's documents (an Arrow table in `documents.schema()`) → (record batches of
+        rows in `packing.schema()`, statistics). Every engine sorts by key first, so the rows
+        do not depend on the order the shuffle delivered the documents in."""
+        import pyarrow as pa
+
+        keys = table.column("key").to_numpy()
+        order = np.argsort(keys, kind="stable")
+        ids = [np.asarray(x, np.int32) for x in table.column("input_ids").take(pa.array(order)).to_pylist()]
+        masks = [np.asarray(x, bool) for x in table.column("loss_mask").take(pa.array(order)).to_pylist()]
+        lengths = [len(x) for x in ids]
+        rows = P.plan(lengths, self.seq_len, self.packing)
+        # rows leave in a random order, fixed by the keys
+        first = int(keys[order[0]]) if len(order) else 0
+        rows = [rows[i] for i in np.random.default_rng(first % (1 << 32)).permutation(len(rows))]
+        a, b, c = P.materialize(rows, ids, masks, self.seq_len, self.packing.doc_mask)
+        out = pa.record_batch([pa.array(list(a), pa.list_(pa.int32())), pa.array(list(b), pa.list_(pa.int32())),
+                               pa.array(list(c), pa.list_(pa.bool_()))], schema=P.schema())
+        st = P.stats(rows, lengths, self.seq_len)
+        st["targets"] = int(c.sum())
+        return [out], st
+
+
+def shift(chunks: int) -> int:
+    """A document of 63-bit key k belongs to chunk ``k >> shift(chunks)``."""
+    return 63 - (chunks.bit_length() - 1)
+
 
 def _sources(data) -> list:
     if isinstance(data, T.MixtureConfig):
@@ -79,72 +125,69 @@ def jobs(train: T.TrainConfig, cache="data/packed") -> list:
     return out
 
 
-def _map(args) -> list:
-    spec_source, tok_cfg_json, files = args
-    source = _source_from(spec_source)
+def _map(args):
+    """One file's documents, as an Arrow table (runs in a worker process)."""
+    import pyarrow as pa
+
+    spec_source, tok_cfg_json, packing_json, seq_len, f = args
+    source = _source_from(spec_source).model_copy(update={"path": f})
     tok_cfg = None if tok_cfg_json is None else T.TokenizerConfig.model_validate(tok_cfg_json)
-    tok = TK.load(tok_cfg)
-    docs = []
-    for f in files:
-        one = source.model_copy(update={"path": f})
-        docs.extend(D.documents(one, tok, tok_cfg))
-    return docs
+    from pydantic import TypeAdapter
+
+    job = Job(source, tok_cfg, TypeAdapter(T.PackingConfig).validate_python(packing_json), seq_len, "")
+    return pa.Table.from_batches(list(job.map(_record_batches(f, source.column))), D.schema())
+
+
+def _record_batches(path: str, column: str, rows: int = 1024):
+    """The source's column of one file, as Arrow record batches."""
+    import pyarrow as pa
+
+    held = []
+    for value in D._records(path, column):
+        held.append(value)
+        if len(held) == rows:
+            yield pa.record_batch([pa.array(held)], names=[column])
+            held = []
+    if held:
+        yield pa.record_batch([pa.array(held)], names=[column])
 
 
 def _source_from(spec: dict):
     return (T.TextConfig if spec["type"] == "text" else T.ChatConfig).model_validate(spec)
 
 
-def _reduce(chunk: list, job: Job, part: Path) -> dict:
+def prepare(job: Job, workers: int = 0, echo=print) -> Path:
     import pyarrow as pa
     import pyarrow.parquet as pq
 
-    chunk.sort(key=lambda d: d[0])
-    ids = [d[1] for d in chunk]
-    masks = [d[2] for d in chunk]
-    lengths = [len(x) for x in ids]
-    rows = P.plan(lengths, job.seq_len, job.packing)
-    # rows leave in a random order, fixed by the keys
-    order = np.random.default_rng(chunk[0][0] % (1 << 32) if chunk else 0).permutation(len(rows))
-    rows = [rows[i] for i in order]
-    a, b, c = P.materialize(rows, ids, masks, job.seq_len, job.packing.doc_mask)
-    table = pa.table({"input_ids": pa.array(list(a), pa.list_(pa.int32())),
-                      "position_ids": pa.array(list(b), pa.list_(pa.int32())),
-                      "loss_mask": pa.array(list(c), pa.list_(pa.bool_()))})
-    pq.write_table(table, part, compression="zstd", row_group_size=max(1, ROW_GROUP_TOKENS // job.seq_len))
-    st = P.stats(rows, lengths, job.seq_len)
-    st["targets"] = int(c.sum())
-    return st
-
-
-def prepare(job: Job, workers: int = 0, echo=print) -> Path:
     folder = job.folder
     if (folder / "dataset.json").exists():
         return folder
     files = D.files_of(job.source.path)
     tok = TK.load(job.tokenizer)
     tasks = [(job.source.model_dump(mode="json"),
-              None if job.tokenizer is None else job.tokenizer.model_dump(mode="json"), [f]) for f in files]
+              None if job.tokenizer is None else job.tokenizer.model_dump(mode="json"),
+              job.packing.model_dump(mode="json"), job.seq_len, f) for f in files]
     if workers and len(tasks) > 1:
         with ProcessPoolExecutor(workers) as pool:
             mapped = list(pool.map(_map, tasks))
     else:
         mapped = [_map(t) for t in tasks]
-    docs = [d for part in mapped for d in part]
-    if not docs:
+    docs = pa.concat_tables(mapped)
+    if docs.num_rows == 0:
         raise ValueError(f"{job.source.path!r} holds no documents in split {job.source.split}")
-    total = sum(len(d[1]) for d in docs)
-    bits = max(0, int(np.ceil(np.log2(max(1.0, total / job.packing.chunk)))))
-    chunks: list = [[] for _ in range(1 << bits)]
-    for d in docs:
-        chunks[d[0] >> (63 - bits) if bits else 0].append(d)
+    lengths = np.asarray([len(x) for x in docs.column("input_ids").to_pylist()])
+    n_chunks = job.chunks(int(lengths.sum()))
+    of = docs.column("key").to_numpy() >> shift(n_chunks)
     tmp = folder.with_name(folder.name + f".tmp{os.getpid()}")
     shutil.rmtree(tmp, ignore_errors=True)
     tmp.mkdir(parents=True)
     parts, stats = [], {}
-    for i, chunk in enumerate(c for c in chunks if c):
+    for i, chunk in enumerate(c for c in range(n_chunks) if (of == c).any()):
         name = f"part-{i:05d}.parquet"
-        st = _reduce(chunk, job, tmp / name)
+        batches, st = job.reduce(chunk, docs.take(pa.array(np.nonzero(of == chunk)[0])))
+        pq.write_table(pa.Table.from_batches(batches, P.schema()), tmp / name, compression="zstd",
+                       row_group_size=max(1, ROW_GROUP_TOKENS // job.seq_len))
         parts.append(name)
         for k, v in st.items():
             stats[k] = stats.get(k, 0) + v

@@ -47,6 +47,9 @@ class Prepared:
 
         self.files = [pq.ParquetFile(folder / p) for p in self.meta["parts"]]
         counts = [f.metadata.num_rows for f in self.files]
+        # where each row group of each part starts (another engine's writer sizes its own groups)
+        self.groups = [np.cumsum([0, *(f.metadata.row_group(g).num_rows for g in range(f.metadata.num_row_groups))])
+                       for f in self.files]
         self.starts = np.cumsum([0, *counts])
         self.total = int(self.starts[-1])
         self.seed, self.seq_len = seed, train.seq_len
@@ -56,8 +59,8 @@ class Prepared:
         f = bisect.bisect_right(self.starts, w) - 1
         local = w - int(self.starts[f])
         pf = self.files[f]
-        per = pf.metadata.row_group(0).num_rows
-        g, at = divmod(local, per)
+        g = bisect.bisect_right(self.groups[f], local) - 1
+        at = local - int(self.groups[f][g])
         key = (f, g)
         if key not in self._cache:
             if len(self._cache) > 8:

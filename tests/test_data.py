@@ -158,3 +158,111 @@ def test_chat_documents_mask_only_the_assistants_words(tmp_path):
     assert trained("assistant") == "cd<|im_end|>\ngh<|im_end|>\n"
     assert trained("last") == "gh<|im_end|>\n"
     assert trained("all").startswith("<|im_start|>user\nab")
+
+
+class _Frame:
+    """What `data.spark` uses of a Spark DataFrame, over one Arrow table held here."""
+
+    def __init__(self, table, key=None):
+        self.table, self.key = table, key
+
+    def select(self, column):
+        return _Frame(self.table.select([column]))
+
+    def mapInArrow(self, fn, ddl):
+        import pyarrow as pa
+
+        from bux_b200.data import documents as D
+
+        assert ddl == "key bigint, input_ids array<int>, loss_mask array<boolean>"
+        # several small batches, as Spark hands a partition over
+        batches = [b for piece in self.table.to_batches(max_chunksize=17) for b in fn([piece])]
+        return _Frame(pa.Table.from_batches(batches, D.schema()))
+
+    def persist(self):
+        return self
+
+    def agg(self, count, tokens):
+        n = self.table.num_rows
+        total = sum(len(x) for x in self.table.column("input_ids").to_pylist())
+        return NS(first=lambda: (n, total or None))
+
+    def groupBy(self, key):
+        return _Frame(self.table, key)
+
+    def applyInArrow(self, fn, ddl):
+        import pyarrow as pa
+
+        from bux_b200.data import packing as P
+
+        assert ddl == "input_ids array<int>, position_ids array<int>, loss_mask array<boolean>"
+        name, shift = self.key
+        of = self.table.column(name).to_numpy() >> shift
+        rng = np.random.default_rng(0)
+        outs = []
+        for c in sorted(set(of.tolist())):
+            rows = np.nonzero(of == c)[0]
+            rng.shuffle(rows)   # a shuffle delivers a group's rows in any order
+            outs.append(fn((pa.scalar(c),), self.table.take(pa.array(rows))))
+        return _Frame(pa.concat_tables(outs) if outs else P.schema().empty_table())
+
+    @property
+    def write(self):
+        frame = self
+
+        class W:
+            def mode(self, m):
+                assert m == "overwrite"
+                return self
+
+            def parquet(self, folder):
+                import os
+
+                import pyarrow.parquet as pq
+
+                os.makedirs(folder, exist_ok=True)
+                pq.write_table(frame.table, f"{folder}/part-00000-spark.parquet")
+
+        return W()
+
+
+_FUNCTIONS = NS(count=lambda c: ("count", c), size=lambda c: ("size", c), sum=lambda c: ("sum", c),
+                shiftright=lambda c, n: NS(alias=lambda name: (c, n)))
+
+
+def test_the_spark_engine_packs_the_rows_the_local_engine_packs(tmp_path):
+    """`data.spark` against a stand-in for a Spark session (pyspark is not installed): the
+    same `Job.map` and `Job.reduce` under mapInArrow / applyInArrow give the local engine's rows."""
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+
+    from bux_b200.config import training as T
+    from bux_b200.data import pipeline, spark
+
+    rng = np.random.default_rng(2)
+    texts = [f"doc {i}: " + " ".join(rng.choice(["alpha", "beta", "gamma"], rng.integers(3, 40))) for i in range(300)]
+    src = tmp_path / "docs.parquet"
+    pq.write_table(pa.table({"text": texts}), src)
+    job = pipeline.Job(T.TextConfig(path=str(src)), T.TokenizerConfig(name="bytes"),
+                       T.BestFitPacking(chunk=4096), 64, str(tmp_path / "local"))
+    local = pipeline.prepare(job, echo=lambda *_: None)
+    meta = json.loads((local / "dataset.json").read_text())
+    assert len(meta["parts"]) > 1   # several chunks: the grouping by key is exercised
+
+    session = NS(read=NS(parquet=lambda path: _Frame(pq.read_table(path))))
+    folder = spark.prepare(job, session, str(tmp_path / "spark"), functions=_FUNCTIONS)
+    assert spark.prepare(job, session, str(tmp_path / "spark"), functions=_FUNCTIONS) == folder
+    smeta = json.loads(open(f"{folder}/dataset.json").read())
+    assert smeta["job"] == meta["job"] and smeta["vocab_size"] == meta["vocab_size"]
+    assert smeta["stats"]["docs"] == 300 and smeta["parts"] == ["part-00000-spark.parquet"]
+
+    def rows_of(folder, parts):
+        t = pa.concat_tables([pq.read_table(f"{folder}/{p}") for p in parts])
+        return sorted(zip(map(tuple, t.column("input_ids").to_pylist()), map(tuple, t.column("position_ids").to_pylist()),
+                          map(tuple, t.column("loss_mask").to_pylist())))
+
+    assert rows_of(local, meta["parts"]) == rows_of(folder, smeta["parts"])
+    # the reader takes the Spark-written folder as it takes the local one
+    train = NS(tokenizer=job.tokenizer, packing=job.packing, seq_len=64)
+    a = prepared.Prepared(job.source, train, tmp_path / "spark", (0, 1), prepare_missing=False)
+    assert a.total == meta["stats"]["rows"] and a.rows(0, 4).input_ids.shape == (4, 64)
