@@ -29,6 +29,9 @@ def _parser() -> argparse.ArgumentParser:
         s.add_argument("--entry", default="model")
         s.add_argument("--only", default=None, help="keep the runs whose name contains TEXT")
         s.add_argument("--index", type=int, default=None, help="keep the run at this index of `plan`")
+        if name == "render":
+            s.add_argument("--expand", action="store_true", help="draw every block in place, not under its own name")
+            s.add_argument("--outline", action="store_true", help="one layer per line, with the widths")
         if name in ("train", "launch", "results", "prepare"):
             s.add_argument("--out", default="runs")
             s.add_argument("--cache", default=".")
@@ -149,9 +152,8 @@ def _dispatch(args) -> int:
             print(r.model_dump_json(indent=1))
         return 0
     if cmd == "render":
-        from .lang.render import render
-
         from .lang import BuxError, compile
+        from .lang.render import outline, render
 
         try:
             archs = [r.arch for r in _runs(args)[:1]]
@@ -162,7 +164,7 @@ def _dispatch(args) -> int:
             path = Path(args.file)
             archs = [compile(path.read_text(), filename=str(path), entry=args.entry, overrides=args.overrides)]
         for arch in archs:
-            print(render(arch))
+            print(outline(arch) if args.outline else render(arch, expand=args.expand), end="" if not args.outline else "\n")
         return 0
     if cmd == "train":
         # one process, or one rank of a job started by torchrun / srun / mpirun: `train_here`

@@ -5,14 +5,67 @@ from pathlib import Path
 
 from bux_b200.lang import compile_runs, reference
 from bux_b200.lang.lsp import Server, features
-from bux_b200.lang.render import render
+from bux_b200.lang.render import outline, render
 
 SMOKE = (Path(__file__).resolve().parent.parent / "examples" / "experiments" / "smoke.bux").read_text()
 
 
-def test_render_shows_the_repeat_and_branches():
-    text = render(compile_runs(SMOKE, filename="smoke.bux")[0].arch)
+def test_outline_shows_the_repeat_and_branches():
+    text = outline(compile_runs(SMOKE, filename="smoke.bux")[0].arch)
     assert "×2" in text and "gqa(4/2 heads)" in text and "⊕" in text and "head (tied)" in text
+
+
+_DEFS = """d_model = 64
+vocab_size = 32
+norm = rmsnorm
+attn = gqa(num_heads=4, num_kv_heads=2)
+ffn = gated_mlp(intermediate_size=128, activation=swish)
+head = head
+"""
+
+
+def _arch(text):
+    from bux_b200.lang import compile
+
+    return compile(_DEFS + text, filename="r.bux")
+
+
+def test_render_draws_residual_branches_under_the_stream():
+    arch = _arch("block = [norm attn] [norm (attn + ffn)]\nmodel = embed block^2 norm head\n")
+    assert render(arch) == (
+        "model\n"
+        "──embed──┤block├×2──norm──head──\n"
+        "\n"
+        "block\n"
+        "──┬────────────⊕──┬────────────────⊕──\n"
+        "  └─norm──attn─┘  └─norm──┬─attn─⊕─┘\n"
+        "                          └─ffn──┘\n"
+    )
+    wide = render(arch, expand=True)
+    assert "┤block├" not in wide and "×2" in wide and wide.count("\n\n") == 0
+
+
+def test_render_products_taps_and_blocks_of_one_label():
+    gate = _arch("swiglu = (linear(features=128) swish * linear(features=128)) linear(features=d_model)\n"
+                 "model = embed [norm swiglu] head\n")
+    assert ("swiglu\n"
+            "──┬─linear──swish─⊗──linear──\n"
+            "  └─linear────────┘\n") in render(gate)
+    two = render(_arch("inner(f) = [norm f]\nouter(g) = inner(g) scale\nmodel = embed outer(attn) outer(ffn) head\n"))
+    assert "┤inner(g)_2├" in two and "norm──ffn" in two
+    taps = render(_arch("a = gqa(num_heads=4, num_kv_heads=4)\nmodel = embed [a(v=@v)] [a(v=$v!)] head\n"))
+    assert "a(v=$v!)" in taps and "a(v=@v)" in taps
+    scaled = render(_arch("model = embed (_ * 2.0 + attn) @skip [ffn] [$skip! scale] head\n"))
+    assert "×2" in scaled and "@skip" in scaled and "$skip!" in scaled
+
+
+def test_render_every_example_architecture():
+    root = Path(__file__).resolve().parent.parent / "examples" / "architectures"
+    from bux_b200.lang import compile
+
+    for path in sorted(root.glob("*.bux")):
+        arch = compile(path.read_text(), filename=str(path))
+        assert render(arch).endswith("\n") and render(arch, expand=True)
 
 
 def test_reference_lists_every_layer_and_setting():
