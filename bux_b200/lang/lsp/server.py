@@ -7,6 +7,7 @@ from __future__ import annotations
 
 import json
 import sys
+from urllib.parse import quote, unquote
 
 from . import features
 
@@ -40,16 +41,29 @@ class Server:
         self.writer.flush()
 
     # -- requests
+    KINDS = {"field": 5, "value": 12, "layer": 7, "setting": 10, "definition": 6, "parameter": 6, "tap": 18,
+             "keyword": 14, "text": 1}
+
+    @staticmethod
+    def path_of(uri: str) -> str:
+        return unquote(uri[len("file://"):]) if uri.startswith("file://") else uri
+
+    def _range(self, text: str, start: int, end: int) -> dict:
+        a, b = features.position_of(text, start), features.position_of(text, end)
+        return {"start": {"line": a[0], "character": a[1]}, "end": {"line": b[0], "character": b[1]}}
+
     def publish(self, uri: str) -> None:
-        self.send({"method": "textDocument/publishDiagnostics",
-                   "params": {"uri": uri, "diagnostics": features.diagnostics(self.docs[uri], uri)}})
+        text = self.docs[uri]
+        found = [{"range": self._range(text, d.start, d.end), "severity": 1, "source": "bux", "message": d.message}
+                 for d in features.diagnostics(text, self.path_of(uri))]
+        self.send({"method": "textDocument/publishDiagnostics", "params": {"uri": uri, "diagnostics": found}})
 
     def handle(self, msg: dict) -> None:
         method, params, rid = msg.get("method"), msg.get("params") or {}, msg.get("id")
         if method == "initialize":
             self.send({"id": rid, "result": {"capabilities": {
                 "textDocumentSync": 1, "hoverProvider": True, "definitionProvider": True,
-                "completionProvider": {"triggerCharacters": ["(", ",", " ", "="]}},
+                "completionProvider": {"triggerCharacters": ["(", ",", " ", "=", ".", "@", "$", '"']}},
                 "serverInfo": {"name": "bux-lsp"}}})
         elif method == "shutdown":
             self.send({"id": rid, "result": None})
@@ -67,19 +81,39 @@ class Server:
             self.docs.pop(params["textDocument"]["uri"], None)
         elif method in ("textDocument/hover", "textDocument/completion", "textDocument/definition"):
             uri = params["textDocument"]["uri"]
-            text = self.docs.get(uri, "")
-            pos = params["position"]
-            if method.endswith("hover"):
-                h = features.hover(text, pos["line"], pos["character"])
-                result = None if h is None else {"contents": {"kind": "plaintext", "value": h}}
-            elif method.endswith("completion"):
-                result = features.completion(text, pos["line"], pos["character"])
-            else:
-                rng = features.definition(text, pos["line"], pos["character"])
-                result = None if rng is None else {"uri": uri, "range": rng}
+            text, path = self.docs.get(uri, ""), self.path_of(uri)
+            at = features.offset_of(text, params["position"]["line"], params["position"]["character"])
+            try:
+                result = self._answer(method, uri, text, path, at)
+            except Exception as err:   # a feature must not take the server down with it
+                self.send({"id": rid, "error": {"code": -32603, "message": f"{type(err).__name__}: {err}"}})
+                return
             self.send({"id": rid, "result": result})
         elif rid is not None:
             self.send({"id": rid, "error": {"code": -32601, "message": f"no method {method}"}})
+
+    def _answer(self, method: str, uri: str, text: str, path: str, at: int):
+        if method.endswith("hover"):
+            h = features.hover(text, at, path)
+            return None if h is None else {"contents": {"kind": "markdown", "value": h.text},
+                                           "range": self._range(text, h.start, h.end)}
+        if method.endswith("completion"):
+            return {"isIncomplete": False, "items": [
+                {"label": c.label, "kind": self.KINDS.get(c.kind, 1), "detail": c.detail, "sortText": c.sort + c.label,
+                 **({"insertText": c.insert} if c.insert else {}),
+                 **({"documentation": {"kind": "markdown", "value": c.doc}} if c.doc else {})}
+                for c in features.complete(text, at, path)]}
+        found = features.definition(text, at, path)
+        if found is None:
+            return None
+        file, start, end = found
+        if file == path:
+            return {"uri": uri, "range": self._range(text, start, end)}
+        try:
+            other = open(file).read()
+        except OSError:
+            return None
+        return {"uri": "file://" + quote(file), "range": self._range(other, start, end)}
 
     def serve(self) -> None:
         while self.running:
