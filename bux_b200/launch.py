@@ -201,6 +201,11 @@ def train_here(run: ir.Run, out="runs", cache=".", device=None, quiet: bool = Fa
         if dev is None and torch.cuda.is_available():
             dev = torch.device("cuda", runtime.local_rank())
         if init_distributed(dev):
+            # before anything is written or compiled: the run's folder must be one for all
+            # ranks, and the native library is built by one rank per copy of the package
+            runtime.agree_on_folder(out)
+            if dev is not None and dev.type == "cuda":
+                runtime.build_in_turn()
             parallel = Parallel(run.train, dev)
             device = dev
     if main:

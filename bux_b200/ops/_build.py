@@ -51,38 +51,50 @@ def _run(cmd: list) -> None:
 
 def build(force: bool = False, verbose: bool = False) -> Path:
     """Compile every CUDA/C++ source for sm_100a and link the shared library."""
-    import torch
-    from torch.utils import cpp_extension as ce
-
     with _lock:
         digest = source_hash()
         if not force and LIB.exists() and STAMP.exists() and STAMP.read_text().strip() == digest:
             return LIB
         EXT_DIR.mkdir(exist_ok=True)
-        obj_dir = EXT_DIR / "obj"
-        obj_dir.mkdir(exist_ok=True)
-        nvcc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
-        includes = [f"-I{p}" for p in ce.include_paths(device_type="cuda")] + [f"-I{CSRC}"]
-        abi = f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"
-        jobs = []
-        for src in _existing(CUDA_SOURCES):
-            obj = obj_dir / (src.stem + ".o")
-            jobs.append(([nvcc, *NVCC_FLAGS, f"-I{CSRC}", "-c", str(src), "-o", str(obj)], obj))
-        for src in _existing(CPP_SOURCES):
-            obj = obj_dir / (src.stem + ".o")
-            jobs.append((["g++", "-O2", "-std=c++17", "-fPIC", abi, *includes, "-DTORCH_API_INCLUDE_EXTENSION_H",
-                          "-c", str(src), "-o", str(obj)], obj))
-        if verbose:
-            print(f"[bux_b200] building {len(jobs)} objects for sm_100a", file=sys.stderr)
-        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as pool:
-            list(pool.map(lambda j: _run(j[0]), jobs))
-        lib_dirs = ce.library_paths(device_type="cuda")
-        link = ["g++", "-shared", "-o", str(LIB), *[str(o) for _, o in jobs],
-                *[f"-L{d}" for d in lib_dirs], *[f"-Wl,-rpath,{d}" for d in lib_dirs],
-                "-lc10", "-ltorch_cpu", "-ltorch", "-lc10_cuda", "-ltorch_cuda", "-lcudart"]
-        _run(link)
-        STAMP.write_text(digest)
-        return LIB
+        # one builder per folder: other processes (ranks that start together) wait here and
+        # then find the library fresh
+        import fcntl
+
+        with open(EXT_DIR / ".lock", "w") as turn:
+            fcntl.flock(turn, fcntl.LOCK_EX)
+            if not force and LIB.exists() and STAMP.exists() and STAMP.read_text().strip() == digest:
+                return LIB
+            return _build_locked(digest, verbose)
+
+
+def _build_locked(digest: str, verbose: bool) -> Path:
+    import torch
+    from torch.utils import cpp_extension as ce
+
+    obj_dir = EXT_DIR / "obj"
+    obj_dir.mkdir(exist_ok=True)
+    nvcc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
+    includes = [f"-I{p}" for p in ce.include_paths(device_type="cuda")] + [f"-I{CSRC}"]
+    abi = f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"
+    jobs = []
+    for src in _existing(CUDA_SOURCES):
+        obj = obj_dir / (src.stem + ".o")
+        jobs.append(([nvcc, *NVCC_FLAGS, f"-I{CSRC}", "-c", str(src), "-o", str(obj)], obj))
+    for src in _existing(CPP_SOURCES):
+        obj = obj_dir / (src.stem + ".o")
+        jobs.append((["g++", "-O2", "-std=c++17", "-fPIC", abi, *includes, "-DTORCH_API_INCLUDE_EXTENSION_H",
+                      "-c", str(src), "-o", str(obj)], obj))
+    if verbose:
+        print(f"[bux_b200] building {len(jobs)} objects for sm_100a", file=sys.stderr)
+    with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as pool:
+        list(pool.map(lambda j: _run(j[0]), jobs))
+    lib_dirs = ce.library_paths(device_type="cuda")
+    link = ["g++", "-shared", "-o", str(LIB), *[str(o) for _, o in jobs],
+            *[f"-L{d}" for d in lib_dirs], *[f"-Wl,-rpath,{d}" for d in lib_dirs],
+            "-lc10", "-ltorch_cpu", "-ltorch", "-lc10_cuda", "-ltorch_cuda", "-lcudart"]
+    _run(link)
+    STAMP.write_text(digest)
+    return LIB
 
 
 def available() -> bool:

@@ -54,23 +54,88 @@ def world_size() -> int:
     return _first_int(("WORLD_SIZE", "SLURM_STEP_NUM_TASKS", "SLURM_NTASKS", "OMPI_COMM_WORLD_SIZE"), 1)
 
 
-def agree_on_folder(folder, rank: int, world: int, barrier) -> None:
-    """Fail early unless every rank sees the same (shared) folder: rank 0 drops a file,
-    the others must see it (reference: ``runtime.py:116``, ``train/hooks.py:508``)."""
+def store():
+    """The job's key-value store (what the processes joined through), or None before they
+    joined: small strings between ranks without a collective and without a device."""
+    import torch.distributed as dist
+
+    if not (dist.is_available() and dist.is_initialized()):
+        return None
+    return dist.distributed_c10d._get_default_store()
+
+
+_asked = 0
+
+
+def shared(folder, timeout_s: float = 60.0) -> bool:
+    """Whether `folder` is one directory for every process of the job: the first process
+    makes a file there and the others must see it. Every process calls it (the same number of
+    times); they talk through `store`, so no rank needs a GPU or a collective for it.
+    A job of one process shares every folder with itself. Reference: ``runtime.py:139``."""
+    import secrets
+    from datetime import timedelta
     from pathlib import Path
 
-    marker = Path(folder) / ".bux_shared_check"
-    if rank == 0:
-        Path(folder).mkdir(parents=True, exist_ok=True)
-        marker.write_text(str(world))
-    barrier()
-    seen = marker.exists()
-    barrier()
-    if rank == 0:
-        marker.unlink(missing_ok=True)
-    if not seen:
-        raise ValueError(f"rank {rank} does not see {folder}: checkpoints and logs need a folder "
-                         "every process shares")
+    global _asked
+    kv = store()
+    me, n = rank(), world_size()
+    if kv is None or n == 1:
+        return True
+    _asked += 1
+    key = f"bux/shared/{_asked}"
+    folder = Path(folder)
+    if me == 0:
+        marker = f".bux-{secrets.token_hex(8)}"
+        folder.mkdir(parents=True, exist_ok=True)
+        (folder / marker).touch()
+        kv.set(f"{key}/marker", marker)
+    kv.wait([f"{key}/marker"], timedelta(seconds=timeout_s))
+    marker = kv.get(f"{key}/marker").decode()
+    # a listing, not a lookup: a network file system may cache that a name was missing
+    seen = folder.is_dir() and marker in os.listdir(folder)
+    kv.set(f"{key}/seen/{me}", "1" if seen else "0")
+    names = [f"{key}/seen/{i}" for i in range(n)]
+    kv.wait(names, timedelta(seconds=timeout_s))
+    every = [kv.get(k) == b"1" for k in names]
+    kv.add(f"{key}/read", 1)
+    if me == 0:
+        while kv.add(f"{key}/read", 0) < n:   # the others have read the answers
+            import time
+
+            time.sleep(0.01)
+        (folder / marker).unlink(missing_ok=True)
+    return all(every)
+
+
+def agree_on_folder(folder) -> None:
+    """Fail early unless every process sees `folder`: checkpoints, logs and the run's status
+    are written by the first process and read by all (reference: ``train/hooks.py:508``)."""
+    if not shared(folder):
+        raise ValueError(f"{folder} is not one directory for every process of the job: checkpoints and "
+                         "logs need a folder every host mounts")
+
+
+def build_in_turn() -> None:
+    """Build (or find) the native library without every rank compiling it at once. Where the
+    package's folder is one for the whole job, the first process builds and the others wait;
+    where each host has its own copy, the first process of each host does. (The build itself
+    also takes a file lock, which covers processes of one host that never joined a job.)
+    The counterpart of the reference's agreement on one compile cache, ``runtime.py:116``."""
+    from .ops import _build
+
+    kv = store()
+    if kv is None or world_size() == 1:
+        _build.load()
+        return
+    import torch.distributed as dist
+
+    one_copy = shared(_build.EXT_DIR.parent)
+    builder = rank() == 0 if one_copy else local_rank() == 0
+    if builder:
+        _build.load()
+    dist.barrier()
+    if not builder:
+        _build.load()
 
 
 def node_name() -> str:

@@ -438,3 +438,38 @@ def test_peer_memory_paths_are_for_one_machine(tmp_path):
     assert got["pair"] is True and got["world"] is False
     assert got["inside"] == "fused_ep" and got["across"] == "all_to_all"
     assert len(got["warned"]) == 1 and "spans machines" in got["warned"][0]
+
+
+def _shared_worker(rank, world, port, folder, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from pathlib import Path
+
+    from bux_b200 import runtime
+
+    one = runtime.shared(Path(folder) / "one")                    # the same folder for every rank
+    own = runtime.shared(Path(folder) / f"host{rank % 2}")        # two "hosts", each with its own
+    refused = False
+    try:
+        runtime.agree_on_folder(Path(folder) / f"host{rank % 2}")
+    except ValueError:
+        refused = True
+    runtime.build_in_turn()                                       # no rank compiles beside another
+    left = sorted(p.name for p in (Path(folder) / "one").iterdir())
+    got = [None] * world
+    dist.all_gather_object(got, (one, own, refused, left))
+    if rank == 0:
+        torch.save(got, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_ranks_agree_on_whether_a_folder_is_shared(tmp_path):
+    """`runtime.shared`: the first rank drops a file, the others must list it; the ranks talk
+    through the job's key-value store. A folder only some ranks see is refused for run output."""
+    out = str(tmp_path / "r.pt")
+    mp.spawn(_shared_worker, args=(3, _free_port(), str(tmp_path), out), nprocs=3, join=True)
+    got = torch.load(out)
+    assert all(one is True and own is False and refused for one, own, refused, _ in got)
+    assert all(left == [] for *_, left in got)                    # the marker is removed again
