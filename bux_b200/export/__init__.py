@@ -25,8 +25,12 @@ def export(run_dir, out, step: Optional[int] = None, dtype: str = "bfloat16", ch
     echo(f"{run.name}: step {step} exported to {folder}")
     if check:
         report = C.compare(model, folder)
-        echo(f"check: max |Δlogit| {report['max_abs_error']:.3g} of {report['logit_scale']:.3g}, "
-             f"argmax agreement {report['argmax_agreement']:.3f}")
-        if not report["ok"]:
+        for r in report.results:
+            echo(f"check [{r.implementation}]: logits off by {r.error:.3g} (relative, tolerance {report.tolerance:.0e}), "
+                 f"argmax agreement {r.agreement:.3f}, greedy {'same' if r.greedy['cache'] == r.greedy['bux'] == r.greedy['no cache'] else 'DIFFERS'}, "
+                 f"left padding {'same' if r.padded else 'DIFFERS'}")
+        for line in report.problems():
+            echo(f"check: {line}")
+        if not report.ok:
             raise SystemExit(1)
     return folder

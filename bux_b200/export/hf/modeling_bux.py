@@ -72,10 +72,24 @@ class BuxForCausalLM(PreTrainedModel):
         self.model.load_state_dict({k: v.to(own[k].dtype) for k, v in state.items() if k in own}, strict=False)
         return self.eval()
 
-    def forward(self, input_ids, position_ids=None, labels=None, **kwargs):
+    @staticmethod
+    def _placed(input_ids, attention_mask, position_ids):
+        """Positions and document ids of a (possibly left-padded) batch: positions count the
+        real tokens of a row from 0; padding is a document of its own that nothing real attends."""
+        if attention_mask is None:
+            if position_ids is None:
+                position_ids = torch.arange(input_ids.shape[1], device=input_ids.device).expand_as(input_ids)
+            return position_ids, None
+        mask = attention_mask.to(torch.long)
         if position_ids is None:
-            position_ids = torch.arange(input_ids.shape[1], device=input_ids.device).expand_as(input_ids)
-        ctx = self.model(input_ids, position_ids, None, training=False)
+            position_ids = (mask.cumsum(-1) - 1).clamp_min(0)
+        return position_ids, (None if bool(mask.all()) else mask.to(torch.int32))
+
+    def forward(self, input_ids, attention_mask=None, position_ids=None, labels=None, all_heads=False, **kwargs):
+        position_ids, segments = self._placed(input_ids, attention_mask, position_ids)
+        ctx = self.model(input_ids, position_ids, segments, training=False)
+        if all_heads:   # every head of the graph (multi-token-prediction heads after the first)
+            return [h.logits().float() for h in ctx.heads]
         logits = ctx.heads[0].logits().float()
         loss = None
         if labels is not None:
@@ -84,9 +98,12 @@ class BuxForCausalLM(PreTrainedModel):
         return CausalLMOutput(loss=loss, logits=logits)
 
     @torch.no_grad()
-    def generate(self, input_ids, max_new_tokens: int = 16, **kwargs):
-        """Greedy decoding by whole-sequence passes (no cache): for checks, not serving."""
+    def generate(self, input_ids, attention_mask=None, max_new_tokens: int = 16, **kwargs):
+        """Greedy decoding by whole-sequence passes (no cache): for checks, not serving. Rows
+        may be left-padded (`attention_mask`); sampling and cache arguments are ignored."""
         for _ in range(max_new_tokens):
-            nxt = self(input_ids).logits[:, -1].argmax(-1, keepdim=True)
+            nxt = self(input_ids, attention_mask=attention_mask).logits[:, -1].argmax(-1, keepdim=True)
             input_ids = torch.cat([input_ids, nxt], dim=1)
+            if attention_mask is not None:
+                attention_mask = torch.cat([attention_mask, torch.ones_like(attention_mask[:, :1])], dim=1)
         return input_ids

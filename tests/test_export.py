@@ -73,7 +73,9 @@ def test_bux_format_round_trip(tmp_path):
     assert cfg["model_type"] == "bux" and cfg["bux"]["run"] == run.id and cfg["bux_layer_types"].count("gqa") == 2 and cfg["layer_types"] == ["full_attention"] * 2
     assert (out / "modeling_bux.py").exists() and (out / "model.safetensors").exists()
     report = C.compare(tr.model, out)
-    assert report["ok"] and report["max_abs_error"] < 1e-4
+    report.check()
+    assert [r.implementation for r in report.results] == ["bux"] and report.max_error < 1e-4
+    assert report.results[0].greedy["cache"] == report.results[0].greedy["bux"] and report.results[0].padded
 
 
 @pytest.mark.parametrize("qk,ffn,family", [("", DENSE, "llama"), (", qk_norm=rmsnorm", DENSE, "qwen3"),
@@ -82,8 +84,9 @@ def test_standard_families_load_in_transformers(tmp_path, qk, ffn, family):
     run, tr, folder = _trained(tmp_path, qk=qk, ffn=ffn)
     out = export(folder, tmp_path / "hf", dtype="float32", echo=lambda *_: None)
     assert json.loads((out / "config.json").read_text())["model_type"] == family
-    report = C.compare(tr.model, out)   # transformers' own implementation of the family
-    assert report["ok"] and report["max_abs_error"] < 2e-3, report
+    report = C.compare(tr.model, out, tolerance=2e-3)   # transformers' own implementation of the family
+    report.check()                                       # logits, greedy with and without its cache, left padding
+    assert [r.implementation for r in report.results] == ["eager", "sdpa"]
 
 
 @pytest.mark.parametrize("qk", [", k_eq_v=true, differential=true", ", paired=true", ", exclusive=learned, power_scale=0.5",
@@ -95,7 +98,8 @@ def test_less_common_attention_settings_round_trip(tmp_path, qk):
     assert native.detect(run.arch) is None
     out = export(folder, tmp_path / "hf", dtype="float32", check=True, echo=lambda *_: None)
     report = C.compare(tr.model, out)
-    assert report["ok"] and report["max_abs_error"] < 1e-4
+    report.check()
+    assert report.max_error < 1e-4
     names = set(W.tensors(tr.model))
     assert ("k_eq_v" in qk) == (not any(n.endswith(".v.weight") for n in names))
 
