@@ -6,4 +6,4 @@ Arrays are stored one folder per state-tree leaf as uncompressed zarr-v3 arrays
 ``_METADATA.json`` records the tree, dtypes, shapes and the layout-affecting methods.
 Every rank writes the leaves it owns; replicated leaves are written by rank 0.
 """
-from .store import load, save, read_tree, write_tree  # noqa: F401
+from .store import load, save, read_tree, wait, write_tree  # noqa: F401

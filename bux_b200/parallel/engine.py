@@ -381,6 +381,67 @@ class Parallel:
             t = torch.cat(parts, dim=0)
         return t
 
+    def _row_split(self, name: str, rows: int):
+        """(parts, index, axes) when the leaf called `name` is cut over the ranks by rows only
+        (the whole leaf is `parts` equal slices along its first axis and this rank holds slice
+        `index`; `axes` are the mesh axes of the cut), (1, 0, ()) when every rank holds all
+        of it, None when it is split another way (tensor parallelism, or two kinds at once)."""
+        if self.tensor_group is not None and name in self.tensor_layout:
+            return None
+        by_expert = self.expert_group is not None and ("experts_gate_up" in name or "experts_down" in name)
+        by_fsdp = self.fsdp is not None and name in self.fsdp.sharded
+        if by_expert and by_fsdp:
+            return None
+        if by_fsdp:
+            if rows * self.fsdp.world != self.fsdp.sharded[name] and rows != self.fsdp.sharded[name]:
+                return None
+            return self.fsdp.world, self.fsdp.rank, tuple(self.fsdp.axes)
+        if by_expert:
+            return self.shape["expert"], dist.get_rank(self.expert_group), ("expert",)
+        return 1, 0, ()
+
+    def leaf_placement(self, key: str, t):
+        """For a writer that lets every rank write its own rows: (parts, index, writer), where
+        `writer` says whether this rank is the one among its replicas that writes slice `index`
+        (`t` is this rank's part). None when the leaf has to be put together first."""
+        if getattr(self, "pipeline", None) is not None:
+            return None
+        if not isinstance(t, torch.Tensor) or t.dim() == 0:
+            return 1, 0, self.rank == 0
+        name = key.split("/", 1)[1] if "/" in key else key     # ``kind/name`` for a moment
+        split = self._row_split(name, t.shape[0])
+        if split is None:
+            return None
+        parts, index, axes = split
+        if parts > 1 and self.fsdp is not None and name in self.fsdp.sharded \
+                and t.shape[0] * parts != self.fsdp.sharded[name]:
+            return None        # this rank holds the whole of a leaf its axes would cut: put it together
+        first_replica = all(self.coords[a] == 0 for a in M.AXES if a not in axes)
+        return parts, index, first_replica
+
+    def restore_rows(self, trainer):
+        """``f(name, shape of the whole leaf)`` giving the (lo, hi) rows this rank holds when
+        rows are all the leaf is cut by on this mesh, else None (`restore_leaf` then cuts the
+        whole leaf). Lets a restore read from disk only what the rank keeps."""
+        known = {n for n, _ in trainer.model.named_parameters()} | {n for n, _ in trainer.model.named_buffers()}
+        piped = getattr(self, "pipeline", None) is not None
+
+        def rows(name: str, shape):
+            if piped or not shape or name not in known:
+                return None
+            split = self._row_split(name, shape[0])
+            if split is None:
+                return None
+            parts, index, _ = split
+            if parts == 1 or shape[0] % parts:
+                return None
+            if self.fsdp is not None and name in self.fsdp.sharded and shape[0] != self.fsdp.sharded[name]:
+                return None
+            per = shape[0] // parts
+            return index * per, (index + 1) * per
+
+        return rows
+
     def restore_tree(self, trainer, tree: dict) -> dict:
         """The inverse of `checkpoint_tree`: from a tree of whole leaves (every rank read it),
         what this rank holds. In the reverse order of the gathers: a pipeline stage keeps its

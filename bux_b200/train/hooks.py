@@ -105,8 +105,9 @@ class Eval(Hook):
 
 
 class Checkpoint(Hook):
-    """Saves ``<run>/checkpoints/<step>/default/`` every N steps and at the end, keeps the
-    most recent `keep`, drops half-written ones on restore. The directory layout and
+    """Saves ``<run>/checkpoints/<step>/default/`` every N steps and at the end (the files are
+    written in the background while training goes on, see `bux_b200.ckpt.store.save`), keeps
+    the most recent `keep`, drops half-written ones on restore. The directory layout and
     state-tree paths are the reference's; array payloads are written by `bux_b200.ckpt`."""
 
     def __init__(self, folder, c: T.CheckpointConfig):
@@ -130,6 +131,7 @@ class Checkpoint(Hook):
     def restore(self, trainer) -> Optional[int]:
         from .. import ckpt
 
+        ckpt.wait()   # a save of this process that still writes in the background
         if runtime.rank() == 0:
             self.drop_unfinished()
         if trainer.parallel is not None:
@@ -165,7 +167,13 @@ class Checkpoint(Hook):
         self.save(trainer)
 
     def stop(self, trainer, sinks) -> None:
+        from .. import ckpt
+
         self.save(trainer)
+        ckpt.wait()   # the run ends with its last checkpoint readable
+        if runtime.rank() == 0:
+            for old in self.steps()[:-self.c.keep]:
+                shutil.rmtree(self.folder / str(old), ignore_errors=True)
 
 
 class Profile(Hook):

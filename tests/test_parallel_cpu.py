@@ -473,3 +473,79 @@ def test_ranks_agree_on_whether_a_folder_is_shared(tmp_path):
     got = torch.load(out)
     assert all(one is True and own is False and refused for one, own, refused, _ in got)
     assert all(left == [] for *_, left in got)                    # the marker is removed again
+
+
+def _shard_writer(rank, world, port, folder, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import json
+    from pathlib import Path
+
+    from bux_b200 import ckpt
+    from bux_b200.ckpt import store
+    from bux_b200.parallel.engine import Parallel
+    from bux_b200.train.trainer import Trainer
+
+    torch.set_num_threads(1)
+    run = compile_runs(MOE, filename="p.bux", overrides=["mesh = mesh(fsdp=2)"])[0]
+    tr = Trainer(run, device="cpu", parallel=Parallel(run.train, torch.device("cpu")))
+    feed = iter(tr.batches())
+    tr.train_step(next(feed))
+    mine = {n: p.detach().clone() for n, p in tr.model.named_parameters()}
+    ckpt.save(folder, tr.step, tr, background=True)
+    tr.train_step(next(feed))          # training goes on while the files are written
+    ckpt.wait()
+    root = Path(folder) / "1" / "default"
+    name = next(n for n in tr.parallel.fsdp.sharded)
+    leaf = root / "0" / name.replace(".", "/")
+    meta = json.loads((leaf / "zarr.json").read_text())
+    chunks = sorted(p.relative_to(leaf / "c").as_posix() for p in (leaf / "c").rglob("*") if p.is_file())
+    rows = meta["shape"][0] // world
+    part = store.read_array(leaf, (rank * rows, (rank + 1) * rows))
+    ragged = store.read_array(leaf, (rows - 1, rows + 2))            # rows of two chunks
+    whole = store.read_array(leaf)
+    got = [None] * world
+    dist.all_gather_object(got, {
+        "chunk_rows": meta["chunk_grid"]["configuration"]["chunk_shape"][0], "rows": rows, "chunks": chunks,
+        "saved_is_the_first_step": bool(torch.equal(part, mine[name].float())),
+        "ragged": bool(torch.equal(ragged, whole[rows - 1:rows + 2])),
+        "no_tmp": not any(p.name.endswith("tmp") for p in Path(folder).iterdir())})
+    if rank == 0:
+        torch.save(got, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_every_rank_writes_its_own_rows_of_a_checkpoint_in_the_background(tmp_path):
+    """A sharded leaf is one array whose chunks are the ranks' rows, each written by the rank
+    that holds it while training goes on; a rank reads back only the rows it keeps; what was
+    saved is the state of the step it was saved at, not of the steps that ran meanwhile."""
+    out = str(tmp_path / "r.pt")
+    os.makedirs(tmp_path / "ckpt")
+    mp.spawn(_shard_writer, args=(2, _free_port(), str(tmp_path / "ckpt"), out), nprocs=2, join=True)
+    for r in torch.load(out):
+        assert r["chunk_rows"] == r["rows"] and len(r["chunks"]) == 2 and r["chunks"][0].startswith("0") and r["chunks"][1].startswith("1")
+        assert r["saved_is_the_first_step"] and r["ragged"] and r["no_tmp"]
+
+
+def test_a_failed_background_save_is_raised_by_the_next_wait(tmp_path, monkeypatch):
+    from bux_b200 import ckpt
+    from bux_b200.ckpt import store
+    from bux_b200.train.trainer import Trainer
+
+    run = compile_runs(MOE, filename="p.bux")[0]
+    tr = Trainer(run, device="cpu")
+
+    def refuse(*a, **k):
+        raise OSError("disk full")
+
+    monkeypatch.setattr(store, "write_tree", refuse)
+    ckpt.save(tmp_path, 0, tr, background=True)
+    with pytest.raises(OSError, match="disk full"):
+        ckpt.wait()
+    ckpt.wait()     # raised once
+    monkeypatch.undo()
+    ckpt.save(tmp_path, 0, tr, background=True)
+    ckpt.wait()
+    assert (tmp_path / "0" / "default" / "_METADATA.json").exists()
