@@ -28,18 +28,40 @@ def device_peak(device) -> float:
     return 0.0
 
 
-def _attention_flops(heads: int, qk_dim: int, v_dim: int, seq_len: int, window) -> float:
-    if window:
-        # query t sees min(t+1, window) keys
-        w = min(window, seq_len)
-        avg = (w * (w + 1) / 2 + (seq_len - w) * w) / seq_len
+def keys_seen(seq_len: int, window=None, positions=None, top_k=None) -> float:
+    """Average number of keys a query attends: query i of its document sees ``i + 1`` keys,
+    at most `window`, at most `top_k` picks. Without `positions` every row is one document of
+    `seq_len` tokens; with the batch's position ids (which restart at every document of a
+    packed row) the average is over the documents as they are (reference: ``train/flops.py:49-99``,
+    the mask's share of the square)."""
+    import numpy as np
+
+    if positions is None:
+        seen = np.arange(1, seq_len + 1, dtype=np.float64)
     else:
-        avg = (seq_len + 1) / 2
-    return 2.0 * heads * (qk_dim + v_dim) * avg
+        seen = np.asarray(positions, dtype=np.float64).reshape(-1) + 1.0
+    for cap in (window, top_k):
+        if cap:
+            seen = np.minimum(seen, float(cap))
+    return float(seen.mean())
 
 
-def layer_forward_flops(c, width, d_model: int, vocab: int, seq_len: int) -> float:
-    """Forward FLOPs per token of one layer."""
+def _attention_flops(heads: int, qk_dim: int, v_dim: int, seq_len: int, window, positions=None, top_k=None) -> float:
+    return 2.0 * heads * (qk_dim + v_dim) * keys_seen(seq_len, window, positions, top_k)
+
+
+def _indexer_flops(ix, w: int, seq_len: int, positions=None) -> float:
+    """The scorer of a sparse attention layer: its projections, and a score for every key a
+    query could see (all of them: that is what picking means), per block when it pools."""
+    if ix is None:
+        return 0.0
+    proj = 2.0 * w * (ix.num_heads * ix.head_dim + ix.head_dim) + (2.0 * w * ix.num_heads if ix.weighted else 0.0)
+    keys = keys_seen(seq_len, None, positions) / max(1, ix.block_size or 1)
+    return proj + 2.0 * ix.num_heads * ix.head_dim * keys
+
+
+def layer_forward_flops(c, width, d_model: int, vocab: int, seq_len: int, positions=None) -> float:
+    """Forward FLOPs per token of one layer (`positions`: a batch's position ids, for packed rows)."""
     w = width if isinstance(width, int) else d_model
     t = c.type
     if t in ("mlp", "gated_mlp"):
@@ -60,7 +82,19 @@ def layer_forward_flops(c, width, d_model: int, vocab: int, seq_len: int) -> flo
         proj = 2.0 * w * (c.num_heads * d + c.num_kv_heads * (d + dv)) + 2.0 * c.num_heads * dv * w
         if c.gated:
             proj += 2.0 * w * (c.num_heads if c.gate_per_head else c.num_heads * dv)
-        return proj + _attention_flops(c.num_heads, d, dv, seq_len, c.sliding_window_size)
+        picks = c.indexer.top_k * (c.indexer.block_size or 1) if c.indexer is not None else None
+        return (proj + _attention_flops(c.num_heads, d, dv, seq_len, c.sliding_window_size, positions, picks)
+                + _indexer_flops(c.indexer, w, seq_len, positions))
+    if t == "csa":
+        d = c.head_dim
+        q = 2.0 * w * c.num_heads * d if c.q_lora_rank is None else 2.0 * (w * c.q_lora_rank + c.q_lora_rank * c.num_heads * d)
+        kv = 2.0 * w * d * (1.0 + 2.0 / c.compress_ratio)         # the window's latent, and the compressor's share per token
+        o = 2.0 * c.num_heads * d * w if c.o_lora_rank is None else 2.0 * (c.num_heads * d * c.o_lora_rank + c.o_lora_rank * w)
+        local = keys_seen(seq_len, c.sliding_window_size, positions)
+        far = keys_seen(seq_len, None, positions) / c.compress_ratio
+        if c.indexer is not None:
+            far = min(far, float(c.indexer.top_k))
+        return q + kv + o + 2.0 * c.num_heads * 2 * d * (local + far) + _indexer_flops(c.indexer, w, seq_len / c.compress_ratio)
     if t == "mla":
         qk = c.qk_nope_head_dim + c.qk_rope_head_dim
         q = 2.0 * w * c.num_heads * qk if c.q_lora_rank is None else \
@@ -68,11 +102,17 @@ def layer_forward_flops(c, width, d_model: int, vocab: int, seq_len: int) -> flo
         kv = 2.0 * w * (c.kv_lora_rank + c.qk_rope_head_dim) + \
             2.0 * c.kv_lora_rank * c.num_heads * (c.qk_nope_head_dim + c.v_head_dim)
         o = 2.0 * c.num_heads * c.v_head_dim * w
-        return q + kv + o + _attention_flops(c.num_heads, qk, c.v_head_dim, seq_len, c.sliding_window_size)
+        picks = c.indexer.top_k * (c.indexer.block_size or 1) if c.indexer is not None else None
+        return (q + kv + o + _attention_flops(c.num_heads, qk, c.v_head_dim, seq_len, c.sliding_window_size, positions, picks)
+                + _indexer_flops(c.indexer, w, seq_len, positions))
     if t == "head":
         return 2.0 * w * vocab
     if t == "linear":
         return 2.0 * w * c.features
+    if t == "nextn":
+        return 2.0 * (2 * w) * w          # the stream and the next token's embedding, joined and projected
+    if t in ("conv", "short_conv"):
+        return 2.0 * w * (c.size if t == "conv" else c.conv_size)
     if isinstance(c, L.LinearAttentionConfig):
         d = c.head_dim
         hv = c.num_v_heads or c.num_heads
@@ -86,9 +126,12 @@ def layer_forward_flops(c, width, d_model: int, vocab: int, seq_len: int) -> flo
     return 0.0
 
 
-def flops_per_token(arch: ir.Architecture, seq_len: int) -> float:
-    """Training FLOPs per token: 3 × the forward's."""
+def flops_per_token(arch: ir.Architecture, seq_len: int, positions=None) -> float:
+    """Training FLOPs per token: 3 × the forward's (a backward is two products per forward
+    product). What a rerun of the forward costs under remat is hardware work, not model work,
+    and is not counted: MFU stays comparable between remat policies. With `positions` (a
+    packed batch's position ids) attention is counted at the keys the documents' queries see."""
     total = 0.0
     for layer in arch.layers():
-        total += layer_forward_flops(layer.config, layer.width, arch.d_model, arch.vocab_size or 0, seq_len)
+        total += layer_forward_flops(layer.config, layer.width, arch.d_model, arch.vocab_size or 0, seq_len, positions)
     return 3.0 * total

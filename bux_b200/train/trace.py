@@ -66,11 +66,41 @@ def classify(events: list) -> dict:
             "idle_ms": ((hi - lo) - length(busy)) / 1000}
 
 
-def comm_ms(path, steps: int = 1) -> dict:
-    """Per-step comm / exposed comm / idle from a chrome trace written by the profiler."""
+def device_events(path) -> dict:
+    """device id → [(name, start_us, duration_us)] of the kernels and copies in a chrome trace
+    written by the profiler (one entry when the trace does not say which device ran what)."""
     data = json.loads(Path(path).read_text())
-    events = [(e.get("name", ""), float(e["ts"]), float(e.get("dur", 0.0)))
-              for e in data.get("traceEvents", [])
-              if e.get("ph") == "X" and e.get("cat", "").lower() in ("kernel", "gpu_memcpy", "gpu_memset")]
-    totals = classify(events)
-    return {k: v / max(steps, 1) for k, v in totals.items()}
+    out: dict = {}
+    for e in data.get("traceEvents", []):
+        if e.get("ph") != "X" or e.get("cat", "").lower() not in ("kernel", "gpu_memcpy", "gpu_memset"):
+            continue
+        device = (e.get("args") or {}).get("device", e.get("pid", 0))
+        out.setdefault(device, []).append((e.get("name", ""), float(e["ts"]), float(e.get("dur", 0.0))))
+    return out
+
+
+def comm_ms(path, steps: int = 1) -> dict:
+    """Per-step comm / exposed comm / idle of a trace: each device's kernels are classed on
+    their own timeline (one GPU's collective does not hide under another GPU's compute), and
+    the numbers are the mean over the devices."""
+    per_device = [classify(events) for events in device_events(path).values()] or [classify([])]
+    n = len(per_device) * max(steps, 1)
+    return {k: sum(d[k] for d in per_device) / n for k in per_device[0]}
+
+
+def kernels(path, top: int = 20) -> list:
+    """The trace's kernels by total time: (name, launches, total ms, share of the busy time)."""
+    totals: dict = {}
+    for events in device_events(path).values():
+        for name, _, dur in events:
+            n, t = totals.get(name, (0, 0.0))
+            totals[name] = (n + 1, t + dur)
+    whole = sum(t for _, t in totals.values()) or 1.0
+    rows = sorted(totals.items(), key=lambda kv: -kv[1][1])[:top]
+    return [(name, n, t / 1000, t / whole) for name, (n, t) in rows]
+
+
+def latest(folder, host: str = None):
+    """The newest trace file under a run's ``profile/`` folder (of `host` when given), or None."""
+    found = [p for p in Path(folder).rglob("*.json") if host is None or host in p.name]
+    return max(found, key=lambda p: p.stat().st_mtime) if found else None

@@ -353,3 +353,71 @@ def test_precision_passes_switch_and_eval():
     tr.train.precision.__dict__["eval"] = "train"
     as_trained = tr.evaluate(e)
     assert in_compute != as_trained
+
+
+def test_flops_per_token_match_a_count_of_the_products_that_run():
+    """The analytic count against torch's FLOP counter over a forward and a backward on CPU
+    (which counts every matrix product that actually ran), and its rules for masks."""
+    import numpy as np
+    from torch.utils.flop_counter import FlopCounterMode
+
+    from bux_b200.train import flops as F
+
+    src = """
+d_model=128
+vocab_size=256
+n = rmsnorm
+a = gqa(num_heads=4, num_kv_heads=2, rope=rope())
+e = moe(num_experts=4, top_k=2, expert=gated_mlp(intermediate_size=64, activation=swish), num_shared_experts=1)
+block = [n a] [n gated_mlp(intermediate_size=256, activation=swish)] [n e]
+model = embed block^2 n head(tied=false)
+data = synthetic
+optimizer = adamw(lr=1e-3)
+seq_len = 32
+batch = 4
+steps = 1
+precision = precision(compute=float32)
+"""
+    run = compile_runs(src, filename="f.bux")[0]
+    tr = Trainer(run, device="cpu")
+    batch = next(iter(tr.batches()))
+    with FlopCounterMode(display=False) as counter:
+        tr.train_step(batch)
+    measured = counter.get_total_flops() / (4 * 32)
+    analytic = F.flops_per_token(run.arch, 32)
+    # the eager statement of attention multiplies the whole square (the analytic count stops at
+    # the diagonal) and the experts' reference path pads; everything else is the same products
+    square = 3 * 2 * 2.0 * 4 * (32 + 32) * (32 - (32 + 1) / 2)
+    assert measured == pytest.approx(analytic + square, rel=0.08), (measured, analytic, square)
+
+    assert F.keys_seen(8) == 4.5 and F.keys_seen(8, window=2) == (1 + 2 * 7) / 8
+    packed = np.array([[0, 1, 2, 3, 0, 1, 0, 0]])          # documents of 4, 2, 1, 1 tokens
+    assert F.keys_seen(8, positions=packed) == (1 + 2 + 3 + 4 + 1 + 2 + 1 + 1) / 8
+    assert F.flops_per_token(run.arch, 32, positions=np.zeros((1, 32), int)) < F.flops_per_token(run.arch, 32)
+    sparse = compile_runs(src.replace("rope=rope())", "rope=rope(), indexer=indexer(num_heads=2, head_dim=16, top_k=4))"), filename="f.bux")[0]
+    long = F.flops_per_token(sparse.arch, 4096) / F.flops_per_token(run.arch, 4096)
+    assert long < 1.0           # picks cap the attended keys; the scorer costs less than it saves
+
+
+def test_trace_reader_splits_communication_from_compute_per_device(tmp_path):
+    """A hand-written chrome trace: communication under compute is hidden, beside it exposed;
+    one GPU's collective does not hide under another GPU's compute."""
+    from bux_b200.train import trace
+
+    def k(name, ts, dur, device):
+        return {"ph": "X", "cat": "kernel", "name": name, "ts": ts, "dur": dur, "args": {"device": device}}
+
+    events = [k("gemm_sm100_kernel", 0, 1000, 0), k("ncclDevKernel_AllGather", 500, 1000, 0),   # 500 hidden, 500 exposed
+              k("attn_fwd_kernel", 2000, 1000, 0),                                                # 500 idle before it
+              k("ep_push_rows_mx", 0, 800, 1), k("gemm_sm100_kernel", 1000, 2000, 1),             # all 800 exposed, 200 idle
+              {"ph": "X", "cat": "cpu_op", "name": "aten::mm", "ts": 0, "dur": 5000}]
+    path = tmp_path / "profile" / "host0.json"
+    path.parent.mkdir()
+    path.write_text(json.dumps({"traceEvents": events}))
+    got = trace.comm_ms(path, steps=1)
+    assert got["comm_ms"] == pytest.approx((1.0 + 0.8) / 2) and got["exposed_comm_ms"] == pytest.approx((0.5 + 0.8) / 2)
+    assert got["idle_ms"] == pytest.approx((0.5 + 0.2) / 2)
+    assert trace.comm_ms(path, steps=2)["comm_ms"] == pytest.approx(0.45)
+    top = trace.kernels(path)
+    assert top[0][0] == "gemm_sm100_kernel" and top[0][1] == 2 and top[0][2] == pytest.approx(3.0)
+    assert trace.latest(tmp_path) == path and trace.latest(tmp_path, host="host9") is None
