@@ -46,7 +46,10 @@ def _parser() -> argparse.ArgumentParser:
     e.add_argument("--check", action="store_true")
     st = sub.add_parser("studio", help="edit and watch a file in the browser")
     st.add_argument("file")
-    st.add_argument("--port", type=int, default=8765)
+    st.add_argument("--port", type=int, default=8765, help="the first port tried (the next few when it is taken)")
+    st.add_argument("--host", default="127.0.0.1")
+    st.add_argument("--out", default="runs", help="where trainings started from the page put their runs")
+    st.add_argument("--no-browser", action="store_true", help="print the URL only")
     return p
 
 
@@ -199,7 +202,7 @@ def _dispatch(args) -> int:
     if cmd == "studio":
         from .studio import serve
 
-        serve(args.file, port=args.port)
+        serve(args.file, port=args.port, out=args.out, host=args.host, browser=not args.no_browser)
         return 0
     raise AssertionError(cmd)
 

@@ -1,18 +1,8 @@
-"""`bux studio FILE`: a local page to edit a `.bux` file and watch what it compiles to.
-
-A stdlib HTTP server with a small JSON API behind a per-session token:
-
-* ``GET  /``                the page (one HTML file, no build step);
-* ``GET  /api/view``        the file's source, its diagnostics, runs (name, id, parameters,
-                            FLOPs per token), the rendered graph of the first run and the
-                            latest metrics of runs found under ``--out``;
-* ``POST /api/source``      replace the file's text (checked first; a text with errors is
-                            kept in memory and reported, the file on disk stays);
-* ``POST /api/set``         a structural edit: set ``name = value`` (appends the setting or
-                            rewrites its statement);
-* ``POST /api/train``       launch the file's runs in a background process (``bux launch``).
-
-Reference: ``studio/server.py``, ``studio/view.py``, ``studio/edits.py``, ``studio/training.py``.
-"""
+"""`bux studio FILE`: a page in the browser that shows a ``.bux`` file three ways at once (its
+source, its model as a diagram, its training and sweep) and edits the file's text from any of
+them. `server` serves the page and the JSON API, `view` says what to draw, `edits` turns a
+visual edit into a splice of the text, `forms` is the inspector, `palette` what can be
+inserted, `training` runs the file from the page; ``static/`` is the page (ES modules, SVG,
+CSS: no build step, no network). Reference: ``studio/*.py``."""
 
 from .server import Studio, serve  # noqa: F401

@@ -140,3 +140,126 @@ def test_a_setting_written_in_a_module_is_changed_by_an_amendment(tmp_path):
     again = edits.set_field(out, *_span(out, "attn", 1), "num_heads", "2", path)
     assert again.count("attn.num_heads") == 1 and "attn.num_heads = 2" in again
     assert forms.inspect(main, s, e, path)["module"].endswith("parts.bux")
+
+
+def _balanced(js: str) -> list:
+    """A crude check of a JavaScript source: brackets pair up outside strings, template
+    literals, comments and regular expressions (no JavaScript engine is installed here)."""
+    stack, problems, i, n = [], [], 0, len(js)
+    pairs = {")": "(", "]": "[", "}": "{"}
+    prev = ""
+    while i < n:
+        ch = js[i]
+        if js.startswith("//", i):
+            i = js.find("\n", i) if js.find("\n", i) >= 0 else n
+            continue
+        if js.startswith("/*", i):
+            i = js.find("*/", i) + 2
+            continue
+        if ch in "\"'":
+            j = i + 1
+            while j < n and js[j] != ch:
+                j += 2 if js[j] == "\\" else 1
+                if j < n and js[j - 1] == "\n" and js[j - 2] != "\\":
+                    problems.append(f"a string runs over a line end near {js[i:i + 30]!r}")
+                    break
+            i, prev = j + 1, ch
+            continue
+        if ch == "`":
+            j = i + 1
+            while j < n and js[j] != "`":
+                if js[j] == "\\":
+                    j += 2
+                elif js.startswith("${", j):
+                    depth, j = 1, j + 2
+                    while j < n and depth:
+                        depth += {"{": 1, "}": -1}.get(js[j], 0)
+                        j += 1
+                else:
+                    j += 1
+            i, prev = j + 1, "`"
+            continue
+        if ch == "/" and prev in "(,=:[!&|?{};\n" + "":
+            j = i + 1
+            in_class = False
+            while j < n and (js[j] != "/" or in_class):
+                if js[j] == "\\":
+                    j += 1
+                elif js[j] == "[":
+                    in_class = True
+                elif js[j] == "]":
+                    in_class = False
+                j += 1
+            i, prev = j + 1, "/"
+            continue
+        if ch in "([{":
+            stack.append((ch, js.count("\n", 0, i) + 1))
+        elif ch in ")]}":
+            if not stack or stack[-1][0] != pairs[ch]:
+                problems.append(f"line {js.count(chr(10), 0, i) + 1}: unmatched {ch}")
+                break
+            stack.pop()
+        if not ch.isspace():
+            prev = ch
+        i += 1
+    problems += [f"line {line}: {ch} never closed" for ch, line in stack]
+    return problems
+
+
+def test_the_page_is_served_with_its_modules_and_the_api_guards_the_file(tmp_path):
+    from http.server import ThreadingHTTPServer
+
+    from bux_b200.studio import Studio
+    from bux_b200.studio.server import STATIC
+
+    for js in STATIC.glob("*.js"):
+        assert _balanced(js.read_text()) == [], js.name
+        for name in __import__("re").findall(r'from "\./([\w.-]+)"', js.read_text()):
+            assert (STATIC / name).exists(), (js.name, name)
+    f = tmp_path / "s.bux"
+    f.write_bytes(SRC.replace("\n", "\r\n").encode())                 # a file with CRLF line ends
+    studio = Studio(f, out=tmp_path / "runs")
+    server = ThreadingHTTPServer(("127.0.0.1", 0), studio.handler({"127.0.0.1"}))
+    port = server.server_address[1]
+    threading.Thread(target=server.serve_forever, daemon=True).start()
+
+    def call(path, body=None, token=studio.token, raw=False, host=None):
+        req = urllib.request.Request(f"http://127.0.0.1:{port}{path}?t={token}", data=None if body is None else json.dumps(body).encode(),
+                                     headers={"Host": host} if host else {})
+        with urllib.request.urlopen(req) as r:
+            return r.read() if raw else json.loads(r.read())
+
+    try:
+        page = call("/", raw=True).decode()
+        assert '<script type="module" src="/static/app.js">' in page
+        assert b"export const api" in call("/static/api.js", raw=True)
+        for bad in (lambda: call("/api/file", token="nope"), lambda: call("/", token="nope", raw=True),
+                    lambda: call("/static/../server.py", raw=True), lambda: call("/api/file", host="evil.example")):
+            with pytest.raises(urllib.error.HTTPError) as err:
+                bad()
+            assert err.value.code in (400, 403, 404)
+        loaded = call("/api/file")
+        assert loaded["source"] == SRC and "\r" not in loaded["source"]
+        v = call("/api/view", {"source": loaded["source"], "run": 1})
+        assert v["errors"] == [] and v["run"] == 1 and v["card"]["layers"] == 11
+        edited = call("/api/edit", {"source": loaded["source"], "edit": {"op": "set_setting", "name": "steps", "value": "20"}})
+        assert "steps = 20\n" in edited["source"]
+        refused = call("/api/edit", {"source": loaded["source"], "edit": {"op": "set_field", "start": 0, "end": 3, "key": "x", "value": "1"}})
+        assert "drawing is behind" in refused["error"]
+        form = call("/api/inspect", {"source": loaded["source"], "start": SRC.index("attn", SRC.index("layer(attn)")), "end": SRC.index("attn", SRC.index("layer(attn)")) + 4})
+        assert form["type"] == "gqa"
+        assert any(c["label"] == "num_kv_heads" for c in call("/api/complete", {"source": "a = gqa(", "offset": 8}))
+        assert call("/api/hover", {"source": loaded["source"], "offset": SRC.index("gqa(")})["text"].startswith("**gqa**")
+        saved = call("/api/save", {"source": edited["source"], "mtime": loaded["mtime"]})
+        assert b"steps = 20\r\n" in f.read_bytes() and b"\n\n" not in f.read_bytes().replace(b"\r\n", b"")   # CRLF kept
+        with pytest.raises(urllib.error.HTTPError) as err:                          # a stale page cannot overwrite
+            call("/api/save", {"source": "x", "mtime": loaded["mtime"]})
+        assert err.value.code == 409
+        call("/api/save", {"source": loaded["source"], "mtime": loaded["mtime"], "overwrite": True})
+        assert call("/api/file")["mtime"] != saved["mtime"]
+        runs = call("/api/runs")
+        assert runs["state"] == "idle" and [r["state"] for r in runs["runs"]] == [None, None]
+        fresh = Studio(tmp_path / "new.bux")
+        assert compile_runs(fresh.source(), filename="new.bux")                    # the template of a new file compiles
+    finally:
+        server.shutdown()

@@ -1,4 +1,4 @@
-"""render, reference pages, language-server features and the stdio server."""
+"""render, reference pages, language-server features, the stdio server, trackers (the studio: test_studio.py)."""
 import io
 import json
 from pathlib import Path
@@ -224,44 +224,6 @@ def test_server_over_stdio():
     assert hover["contents"]["value"].startswith("**embed** — layer") and hover["range"]["start"] == {"line": 0, "character": 8}
     items = next(m for m in msgs if m.get("id") == 4)["result"]["items"]
     assert [i["label"] for i in items] == ["head"] and items[0]["kind"] == 7
-
-
-def test_studio_api(tmp_path):
-    import threading
-    import urllib.request
-    from http.server import ThreadingHTTPServer
-
-    from bux_b200.studio import Studio
-    from bux_b200.studio.server import set_value
-
-    assert set_value("a = 1\nb = f(\n  x)\nc = 2\n", "b", "g()") == "a = 1\nb = g()\nc = 2\n"
-    assert set_value("a = 1\n", "steps", "9").endswith("steps = 9\n")
-    f = tmp_path / "s.bux"
-    f.write_text(SMOKE)
-    studio = Studio(f, out=tmp_path / "runs")
-    server = ThreadingHTTPServer(("127.0.0.1", 0), studio.handler())
-    port = server.server_address[1]
-    threading.Thread(target=server.serve_forever, daemon=True).start()
-    try:
-        def call(path, body=None, token=studio.token):
-            req = urllib.request.Request(f"http://127.0.0.1:{port}{path}?token={token}",
-                                         data=None if body is None else json.dumps(body).encode())
-            with urllib.request.urlopen(req) as r:
-                return json.loads(r.read())
-
-        view = call("/api/view")
-        assert view["runs"][0]["id"] == "5a4f0f7d85" and view["runs"][0]["params"] == 155968 and "×2" in view["graph"]
-        edited = call("/api/set", {"name": "steps", "value": "20"})
-        assert not edited["diagnostics"] and "steps = 20" in f.read_text().replace("    ", " ").replace("  ", " ")
-        broken = call("/api/source", {"source": SMOKE.replace("num_heads=4", "num_heads=3")})
-        assert broken["diagnostics"] and "num_heads=3" not in f.read_text()   # the file keeps its last good text
-        try:
-            call("/api/view", token="nope")
-            raise AssertionError("a bad token must be refused")
-        except urllib.error.HTTPError as e:
-            assert e.code == 403
-    finally:
-        server.shutdown()
 
 
 def test_trackers_forward_every_logged_step_to_their_package(tmp_path, monkeypatch):
