@@ -196,8 +196,12 @@ class _Remat(torch.autograd.Function):
     gradients reach the block's parameters too."""
 
     @staticmethod
-    def forward(fctx, x, holder):
+    def forward(fctx, x, holder, *outside):
+        # `outside`: tensors on the taps when the block starts (written by earlier layers) that
+        # carry gradients. They are inputs of this function, so what the block's replay sends
+        # back to them goes on through the graph that made them, once, with everything else.
         fctx.holder = holder
+        fctx.set_materialize_grads(False)   # an output nobody read has no gradient: skip it, do not make zeros
         fctx.cuda_rng = torch.cuda.get_rng_state(x.device) if x.is_cuda else None
         fctx.cpu_rng = torch.get_rng_state()
         fctx.host = None
@@ -217,8 +221,9 @@ class _Remat(torch.autograd.Function):
             fctx.device = x.device
             fctx.fetched = None
             _OFFLOADED.append(fctx)
+            fctx.save_for_backward(*outside)
         else:
-            fctx.save_for_backward(x)
+            fctx.save_for_backward(x, *outside)
         with torch.no_grad():
             y, aux = holder.run(x, replay=False)
         if fctx.host is not None and holder.kept and holder.kept_to_host:
@@ -239,7 +244,9 @@ class _Remat(torch.autograd.Function):
                 copied.record(side)
             _hold_until_copied(copied, tuple(sources))
             holder.kept = hosted
-        return (y, *aux)
+        # what the block pushed onto taps leaves as outputs too: a later reader's gradient
+        # comes back to this block instead of stopping at a tensor made without a graph
+        return (y, *aux, *holder.pushed)
 
     @staticmethod
     def _fetch(fctx) -> None:
@@ -280,22 +287,27 @@ class _Remat(torch.autograd.Function):
             # the block that goes backward next: its input travels while this one computes
             if _OFFLOADED and _OFFLOADED[-1].fetched is None:
                 _Remat._fetch(_OFFLOADED[-1])
+            outside = fctx.saved_tensors
         else:
-            (x,) = fctx.saved_tensors
+            x, *outside = fctx.saved_tensors
         x = x.detach().requires_grad_(True)
+        # the replay reads detached stand-ins for the tensors other layers wrote: its backward
+        # stops at them, and their gradients leave through this function's return
+        stand_ins = [t.detach().requires_grad_(True) for t in outside]
         devices = [x.device] if x.is_cuda else []
         with torch.random.fork_rng(devices=devices):
             torch.set_rng_state(fctx.cpu_rng)
             if fctx.cuda_rng is not None:
                 torch.cuda.set_rng_state(fctx.cuda_rng, x.device)
             with torch.enable_grad():
-                y, aux = holder.run(x, replay=True)
+                y, aux = holder.run(x, replay=True, stand_ins={id(t): r for t, r in zip(outside, stand_ins)})
         outs, grads = [], []
-        for o, g in zip((y, *aux), (dy, *daux)):
+        for o, g in zip((y, *aux, *holder.pushed), (dy, *daux)):
             if o.requires_grad and g is not None:
                 outs.append(o)
                 grads.append(g)
-        torch.autograd.backward(outs, grads)
+        if outs:
+            torch.autograd.backward(outs, grads)
         # The forward's context reaches this node (context -> heads -> hidden states -> their
         # graph -> this node) and this node reached the context through the holder: a cycle
         # through autograd's C++ edges, which Python's collector cannot see. Cut it here, or
@@ -303,7 +315,8 @@ class _Remat(torch.autograd.Function):
         fctx.holder = None
         holder.ctx = holder.block = None
         holder.taps = holder.ports = None
-        return x.grad, None
+        holder.pushed = []
+        return (x.grad, None, *(r.grad for r in stand_ins))
 
 
 class _BlockRun:
@@ -321,6 +334,18 @@ class _BlockRun:
         self.taps = {k: list(v) for k, v in ctx.taps.items()}
         self.ports = dict(ctx.ports)
         self.branches = (ctx.branch_index, ctx.top_branch)   # where the block's first run starts counting
+        self.pushed: list = []   # tensors the block's last run left on the taps (its own writes)
+
+    def outside(self) -> list:
+        """Tensors on the taps at the block's start that carry gradients (each once)."""
+        seen, out = set(), []
+        for stack in self.taps.values():
+            for value in stack:
+                for t in _tensors_of(value):
+                    if t.requires_grad and id(t) not in seen:
+                        seen.add(id(t))
+                        out.append(t)
+        return out
 
     def pinned(self, x, slot=None):
         k = (self.key, slot, tuple(x.shape), x.dtype)
@@ -330,15 +355,16 @@ class _BlockRun:
             _BlockRun._pinned[k] = buf
         return buf
 
-    def run(self, x, replay: bool):
+    def run(self, x, replay: bool, stand_ins=None):
         ctx = self.ctx
+        before = {id(t) for stack in self.taps.values() for value in stack for t in _tensors_of(value)}
         saved = (ctx.taps, ctx.losses, ctx.metrics, ctx.ports, ctx.branch_index, ctx.top_branch)
         ctx.losses = {}
         was_observing = ctx.observing
         if replay:
             ctx.observing = False   # the first run observed
             ctx.branch_index, ctx.top_branch = self.branches   # the branches count as in the first run
-            ctx.taps = {k: list(v) for k, v in self.taps.items()}
+            ctx.taps = {k: [_swapped(value, stand_ins) for value in v] for k, v in self.taps.items()}
             ctx.metrics, ctx.ports = {}, dict(self.ports)
             ctx.tail_values_unused = _ends_in_plain_moe_branch(self.block)
         from ..ops import functional as OF
@@ -348,6 +374,12 @@ class _BlockRun:
         try:
             y = self.block(x, ctx)
             reported = ctx.losses
+            # what this run left on the taps that was not there before (a tap pushed and popped
+            # inside the block never shows): in the order the stacks hold them, so the first run
+            # and the replay list the same writes
+            swapped = {id(r) for r in (stand_ins or {}).values()}
+            self.pushed = [t for stack in ctx.taps.values() for value in stack for t in _tensors_of(value)
+                           if id(t) not in before and id(t) not in swapped and t.is_floating_point()]
         finally:
             OF.attention_replay = None
             ctx.tail_values_unused = False
@@ -361,6 +393,26 @@ class _BlockRun:
         if not replay:
             self.names = list(reported)
         return y, [reported[n] for n in self.names]
+
+
+def _tensors_of(value) -> tuple:
+    """The tensors of a tap's entry: the entry itself, or the members of a tuple or list."""
+    if isinstance(value, torch.Tensor):
+        return (value,)
+    if isinstance(value, (tuple, list)):
+        return tuple(t for t in value if isinstance(t, torch.Tensor))
+    return ()
+
+
+def _swapped(value, stand_ins):
+    """`value` with every tensor that has a stand-in replaced by it."""
+    if not stand_ins:
+        return value
+    if isinstance(value, torch.Tensor):
+        return stand_ins.get(id(value), value)
+    if isinstance(value, (tuple, list)):
+        return type(value)(stand_ins.get(id(t), t) if isinstance(t, torch.Tensor) else t for t in value)
+    return value
 
 
 def _ends_in_plain_moe_branch(block) -> bool:
@@ -379,10 +431,18 @@ def _ends_in_plain_moe_branch(block) -> bool:
 def _checkpointed(block, x, ctx: Context, offload: bool = False, key=None, keep_attention: bool = False,
                   kept_to_host: bool = False):
     holder = _BlockRun(block, ctx, offload, key, keep_attention, kept_to_host)
-    y, *aux = _Remat.apply(x, holder)
+    y, *rest = _Remat.apply(x, holder, *holder.outside())
+    aux, pushed = rest[:len(holder.names)], rest[len(holder.names):]
     for name, value in zip(holder.names, aux):
         prev = ctx.losses.get(name)
         ctx.losses[name] = value if prev is None else prev + value
+    # the taps hold the function's outputs (which carry its graph), not the tensors the run
+    # under no_grad made
+    raw = holder.pushed
+    if pushed:
+        as_output = {id(t): o for t, o in zip(raw, pushed)}
+        for name, stack in ctx.taps.items():
+            ctx.taps[name] = [_swapped(value, as_output) for value in stack]
     return y
 
 

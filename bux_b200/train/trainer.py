@@ -124,13 +124,7 @@ class Trainer:
         self._prefixes = None
         self._token_bytes = None
         self.stretches = curriculum.stretches(t)
-        if t.methods.interleave:
-            # a schedule, not arithmetic: the step's numbers are the same without it
-            import warnings
-
-            warnings.warn("methods(interleave=true): the interleaved step is not built here; the microbatches of a "
-                          "step run one after another (same gradients, no overlap of one's forward with "
-                          "another's backward)")
+        self._interleave = None        # the schedule of methods(interleave=true), made at the first step
         self.timers = Timers()
 
     # ------------------------------------------------------------------ setup
@@ -269,7 +263,10 @@ class Trainer:
         if pipe is not None:
             loss_sum, terms = pipe.run(self, micro, inv_count, n_micro, world)
             torch.distributed.all_reduce(loss_sum, group=pipe.group)  # the last stage holds it
-        for k, mb in enumerate(micro if pipe is None else ()):
+        schedule = self._interleaved() if (pipe is None and len(micro) > 1 and t.methods.interleave) else None
+        if schedule is not None:
+            loss_sum, terms = schedule.run(micro, inv_count, n_micro, world)
+        for k, mb in enumerate(micro if (pipe is None and schedule is None) else ()):
             last = k == len(micro) - 1
             sync = self.parallel.grad_sync(self.model, last) if self.parallel is not None else _null()
             with sync:
@@ -310,6 +307,26 @@ class Trainer:
             out["grad_norm"] = norm
         out.update(terms)
         return out
+
+    def _interleaved(self):
+        """The schedule of ``methods(interleave=true)``, or None (with a warning, once) where the
+        step cannot be interleaved and its microbatches run one after another."""
+        if self._interleave is None:
+            from . import interleave
+
+            why = interleave.unsupported(self)
+            if why is None:
+                try:
+                    self._interleave = interleave.Interleaved(self)
+                except TypeError as err:
+                    why = str(err)
+            if why is not None:
+                import warnings
+
+                warnings.warn(f"methods(interleave=true): {why}; the microbatches of a step run one after "
+                              "another (the same gradients, nothing overlapped)")
+                self._interleave = False
+        return self._interleave or None
 
     def prefix_table(self):
         """Each id's prefix token for ``loss(prefix=...)`` (None without it): from the run's

@@ -421,3 +421,92 @@ def test_trace_reader_splits_communication_from_compute_per_device(tmp_path):
     top = trace.kernels(path)
     assert top[0][0] == "gemm_sm100_kernel" and top[0][1] == 2 and top[0][2] == pytest.approx(3.0)
     assert trace.latest(tmp_path) == path and trace.latest(tmp_path, host="host9") is None
+
+
+INTERLEAVED = """
+d_model=32
+vocab_size=64
+n = rmsnorm
+a = gqa(num_heads=2, num_kv_heads=1, rope=rope(), value_residual=learned)
+e = moe(num_experts=4, top_k=2, expert=gated_mlp(intermediate_size=16, activation=swish), aux_loss_coef=0.01)
+first = [n a(v=@v)] [n e]
+rest = [n a(v=$v)] [n e]
+model = embed first @skip rest^3 [$skip! scale] n head
+data = synthetic
+optimizer = adamw(lr=1e-2, eps=1.0)
+seq_len = 16
+batch = 8
+steps = 4
+precision = precision(compute=float32)
+methods = methods(microbatches=4{more})
+"""
+
+
+@pytest.mark.parametrize("remat", ["none", "full"])
+def test_interleaved_microbatches_give_the_gradients_of_a_plain_accumulation(remat):
+    """``methods(interleave=true)``: the forward of each microbatch runs piece by piece beside the
+    backward of the one before. A graph with a tap read three pieces later, a port that feeds
+    every later attention and auxiliary losses: what crosses pieces crosses them as always."""
+    from bux_b200.train import interleave
+
+    plain = compile_runs(INTERLEAVED.format(more=f", remat={remat}"), filename="i.bux")[0]
+    mixed = compile_runs(INTERLEAVED.format(more=f", remat={remat}, interleave=true"), filename="i.bux")[0]
+    a, b = Trainer(plain, device="cpu"), Trainer(mixed, device="cpu")
+    order: list = []
+    pieces = interleave.pieces_of(b.model)
+    assert len(pieces) == 9     # embed, first, the tap, three passes of rest, the skip's branch, norm, head
+    for t, m in enumerate(pieces):
+        m.register_forward_hook(lambda mod, args, out, t=t: order.append(("F", t)) if torch.is_grad_enabled() else None)
+        m.register_full_backward_hook(lambda mod, gi, go, t=t: order.append(("B", t)))
+    feed = iter(a.batches())
+    for _ in range(2):
+        batch = next(feed)
+        la, lb = a.train_step(batch), b.train_step(batch)
+        assert la["loss"].item() == pytest.approx(lb["loss"].item(), abs=1e-6)
+        assert la["grad_norm"].item() == pytest.approx(lb["grad_norm"].item(), rel=1e-5)
+    for (name, p), q in zip(a.model.named_parameters(), b.model.parameters()):
+        assert torch.allclose(p, q, atol=1e-6), name
+    sched = b._interleave
+    assert sched and sched.ticks >= 2 * 3 * len(pieces) - 6      # two steps, three overlapped pairs each
+    if remat == "none":
+        # inside an overlapped pair the two halves alternate: a forward piece, then a backward piece
+        first_b = next(i for i, (kind, _) in enumerate(order) if kind == "B")
+        window = order[first_b - 1:first_b + 9]
+        assert [k for k, _ in window] == ["F", "B"] * 5, window
+        back = [t for k, t in window if k == "B"]
+        assert back == list(range(back[0], back[0] - 5, -1)) and back[0] >= 7       # the top pieces first, one a tick
+
+
+def test_interleave_falls_back_where_it_cannot_run():
+    from bux_b200.train import interleave
+
+    run = compile_runs(INTERLEAVED.format(more=", interleave=true"), filename="i.bux")[0]
+    tr = Trainer(run, device="cpu", fuse_optimizer=True)
+    assert "fused into the backward" in interleave.unsupported(tr)
+    with pytest.warns(UserWarning, match="one after another"):
+        tr.train_step(next(iter(tr.batches())))
+    co = interleave.Coroutine(lambda: (_ for _ in ()).throw(ValueError("inside")), "t")
+    with pytest.raises(ValueError, match="inside"):
+        co.resume()
+    assert not co.resume()
+
+
+@pytest.mark.parametrize("model", [
+    "embed first rest^3 n head",                      # written outside every checkpointed block, read inside three
+    "embed first^1 @t rest^2 [$t! scale] n head",     # written inside one checkpointed pass, read inside later ones
+    "embed (first @t rest [$t! scale])^2 n head",     # written and read inside one pass
+])
+def test_checkpointed_blocks_pass_gradients_through_taps_and_ports(model):
+    """``remat=full`` reruns a block in the backward. What the block reads from taps other layers
+    wrote, and what it writes for later readers, crosses the checkpoint as inputs and outputs of
+    the rerun: the gradients are those of a run that keeps everything."""
+    src = INTERLEAVED.replace("model = embed first @skip rest^3 [$skip! scale] n head", "model = " + model)
+    got = {}
+    for remat in ("none", "full"):
+        run = compile_runs(src.format(more=f", remat={remat}"), filename="r.bux")[0]
+        tr = Trainer(run, device="cpu")
+        out = tr.train_step(next(iter(tr.batches())))
+        got[remat] = (out["loss"].item(), {n: p.detach().clone() for n, p in tr.model.named_parameters()})
+    assert got["none"][0] == pytest.approx(got["full"][0], abs=1e-6)
+    for name, p in got["none"][1].items():
+        assert torch.allclose(p, got["full"][1][name], atol=1e-6), name
