@@ -196,3 +196,41 @@ def test_newton_schulz_on_the_tcgen05_gemm_matches_fp32(shape):
     s = torch.linalg.svdvals(got.reshape(-1, *shape[-2:])[0])
     assert 0.5 < s.min() and s.max() < 1.3
     assert K.launches >= before + 15  # three GEMMs per step, per matrix
+
+
+def test_interleaved_microbatches_match_a_plain_accumulation_on_two_streams(cuda):
+    """``methods(interleave=true)`` on the GPU: every microbatch's forward is issued on one of two
+    streams by its parity, beside the backward of the one before on the other. A mixture of
+    experts, a value residual that crosses blocks and ``remat=full``: the parameters after two
+    steps are those of the microbatches run one after another."""
+    from bux_b200.lang import compile_runs
+    from bux_b200.train.trainer import Trainer
+
+    src = """
+d_model=256
+vocab_size=512
+n = rmsnorm
+a = gqa(num_heads=4, num_kv_heads=2, head_dim=64, rope=rope(), value_residual=learned)
+e = moe(num_experts=8, top_k=2, expert=gated_mlp(intermediate_size=128, activation=swish))
+first = [n a(v=@v)] [n e]
+rest = [n a(v=$v)] [n e]
+model = embed first rest^3 n head
+data = synthetic
+optimizer = adamw(lr=1e-3, eps=1.0)
+seq_len = 256
+batch = 8
+steps = 4
+precision = precision(compute=bfloat16)
+methods = methods(microbatches=4, remat=full{more})
+"""
+    out = {}
+    for name, more in (("plain", ""), ("interleaved", ", interleave=true")):
+        tr = Trainer(compile_runs(src.format(more=more), filename="g.bux")[0], device=cuda)
+        feed = iter(tr.batches())
+        losses = [tr.train_step(next(feed))["loss"].item() for _ in range(2)]
+        torch.cuda.synchronize()
+        out[name] = (losses, {n: p.detach().float().cpu() for n, p in tr.model.named_parameters()}, tr._interleave)
+    assert out["interleaved"][2] and out["interleaved"][2].ticks == 2 * 3 * 6      # two steps, three pairs, six pieces
+    assert out["plain"][0] == pytest.approx(out["interleaved"][0], abs=1e-3)
+    for name, p in out["plain"][1].items():
+        assert rel_err(out["interleaved"][1][name], p) < 1e-3, name
