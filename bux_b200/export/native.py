@@ -2,8 +2,11 @@
 written in that family's own Hugging Face format (config fields and tensor names), so
 stock `transformers` and stock vLLM load and serve it with their own kernels.
 
-Families: ``llama`` (pre-norm GQA + SwiGLU), ``qwen3`` (the same with per-head q/k
-RMSNorm), ``qwen3_moe`` (qwen3 with softmax top-k routed SwiGLU experts).
+Families: ``llama`` (pre-norm GQA + SwiGLU), ``mistral`` (llama with one sliding window for
+every layer), ``qwen2`` (llama with biases on q, k and v), ``qwen3`` (llama with per-head q/k
+RMSNorm), ``mixtral`` (llama with softmax top-k routed SwiGLU experts, the picked weights
+renormalised) and ``qwen3_moe`` (the same on qwen3's attention). RoPE scalings (``pi``,
+``llama3``, ``yarn``) are written as the family's ``rope_parameters``.
 """
 
 from __future__ import annotations
@@ -61,13 +64,14 @@ def detect(arch: ir.Architecture) -> Optional[str]:
     if not (_plain_norm(n1) and _plain_norm(n2) and isinstance(attn, L.GQAConfig)):
         return None
     a = attn
-    plain = (a.rope is not None and a.rope.layout == "half" and a.rope.fraction == 1.0 and a.rope.scaling is None
-             and not a.bias and not a.sinks and not a.gated and a.softcap is None and a.sliding_window_size is None
+    plain = (a.rope is not None and a.rope.layout == "half" and a.rope.fraction == 1.0
+             and not a.sinks and not a.gated and a.softcap is None
+             and not (a.bias if a.output_bias is None else a.output_bias)   # no family here biases the output projection
              and a.scale is None and a.output_norm is None and not a.qk_norm_all_heads
              and all(getattr(a, f) in (None, False) for f in ("kv_conv_size", "differential", "k_eq_v", "indexer")))
     # every other setting of the layer changes what it computes: only its defaults are a standard family
     allowed = {"type", "num_heads", "num_kv_heads", "head_dim", "v_head_dim", "rope", "qk_norm", "fused_qkv",
-               "value_residual", "value_embed_gate"}
+               "value_residual", "value_embed_gate", "bias", "output_bias", "sliding_window_size"}
     plain = plain and all(getattr(a, name) == field.default for name, field in type(a).model_fields.items()
                           if name not in allowed and not field.is_required())
     if not plain:
@@ -75,11 +79,19 @@ def detect(arch: ir.Architecture) -> Optional[str]:
     qk = a.qk_norm is not None and _plain_norm(a.qk_norm)
     if a.qk_norm is not None and not qk:
         return None
+    # one variation at a time is a family; two at once (a window and biases, ...) is none of them
+    variations = [bool(a.bias), a.sliding_window_size is not None, qk]
+    if sum(variations) > 1 or (a.v_head_dim not in (None, a.head_dim or arch.d_model // a.num_heads)):
+        return None
+    if isinstance(a.rope.scaling, L.YaRNConfig) and a.rope.scaling.attention_factor_on != "rotary":
+        return None
     if isinstance(ffn, L.MLPConfig):
         ok = (ffn.type == "gated_mlp" and ffn.activation == "swish" and not ffn.bias and ffn.limit is None
               and not ffn.up_offset and ffn.up_softcap is None)
-        return ("qwen3" if qk else "llama") if ok else None
-    if isinstance(ffn, L.MoEConfig) and qk:
+        if not ok:
+            return None
+        return "qwen3" if qk else "qwen2" if a.bias else "mistral" if a.sliding_window_size is not None else "llama"
+    if isinstance(ffn, L.MoEConfig) and not a.bias and a.sliding_window_size is None:
         x = ffn.expert
         ok = (ffn.router == "softmax" and not ffn.num_shared_experts and ffn.num_groups == 1
               and not ffn.router_bias and ffn.load_balancing not in ("aux_free", "smebu")
@@ -90,8 +102,29 @@ def detect(arch: ir.Architecture) -> Optional[str]:
                    "random_logits", "load_balancing", "bias_update_rate", "bias_softclamp", "bias_momentum"}
         ok = ok and all(getattr(ffn, name) == field.default for name, field in type(ffn).model_fields.items()
                         if name not in allowed and not field.is_required())
-        return "qwen3_moe" if ok else None
+        if not ok:
+            return None
+        if qk:
+            return "qwen3_moe"
+        return "mixtral" if ffn.normalize_top_k else None      # Mixtral always renormalises the picked weights
     return None
+
+
+def rope_parameters(rope) -> dict:
+    """A RoPE config in the families' ``rope_parameters`` form."""
+    out = {"rope_type": "default", "rope_theta": rope.base}
+    sc = rope.scaling
+    if isinstance(sc, L.PositionInterpolationConfig):
+        out.update(rope_type="linear", factor=sc.factor)
+    elif isinstance(sc, L.Llama3RoPEScalingConfig):
+        out.update(rope_type="llama3", factor=sc.factor, original_max_position_embeddings=sc.original_max_len,
+                   low_freq_factor=sc.low_freq_factor, high_freq_factor=sc.high_freq_factor)
+    elif isinstance(sc, L.YaRNConfig):
+        out.update(rope_type="yarn", factor=sc.factor, original_max_position_embeddings=sc.original_max_len,
+                   beta_fast=sc.beta_fast, beta_slow=sc.beta_slow)
+        if sc.attention_factor is not None:
+            out["attention_factor"] = sc.attention_factor
+    return out
 
 
 def convert(family: str, arch: ir.Architecture, t: dict, dtype) -> tuple:
@@ -114,17 +147,21 @@ def convert(family: str, arch: ir.Architecture, t: dict, dtype) -> tuple:
         at = f"{src}.0.body.items.1"
         for p in "qkvo":
             out[f"{dst}.self_attn.{p}_proj.weight"] = t[f"{at}.{p}.weight"]
-        if family != "llama":
+        if family in ("qwen3", "qwen3_moe"):
             out[f"{dst}.self_attn.q_norm.weight"] = t[f"{at}.q_norm.scale"]
             out[f"{dst}.self_attn.k_norm.weight"] = t[f"{at}.k_norm.scale"]
+        if family == "qwen2":
+            for p in "qkv":
+                out[f"{dst}.self_attn.{p}_proj.bias"] = t[f"{at}.{p}.bias"]
         ff = f"{src}.1.body.items.1"
-        if family == "qwen3_moe":
-            out[f"{dst}.mlp.gate.weight"] = t[f"{ff}.router.weight"]
+        if family in ("qwen3_moe", "mixtral"):
             gate, up, down = t[f"{ff}.experts.gate"], t[f"{ff}.experts.up"], t[f"{ff}.experts.down"]
+            moe = f"{dst}.mlp" if family == "qwen3_moe" else f"{dst}.block_sparse_moe"
+            names = ("gate_proj", "up_proj", "down_proj") if family == "qwen3_moe" else ("w1", "w3", "w2")
+            out[f"{moe}.gate.weight"] = t[f"{ff}.router.weight"]
             for e in range(gate.shape[0]):
-                out[f"{dst}.mlp.experts.{e}.gate_proj.weight"] = gate[e]
-                out[f"{dst}.mlp.experts.{e}.up_proj.weight"] = up[e]
-                out[f"{dst}.mlp.experts.{e}.down_proj.weight"] = down[e]
+                for name, w in zip(names, (gate, up, down)):
+                    out[f"{moe}.experts.{e}.{name}.weight"] = w[e]
         else:
             for p in ("gate", "up", "down"):
                 out[f"{dst}.mlp.{p}_proj.weight"] = t[f"{ff}.{p}.weight"]
@@ -134,11 +171,23 @@ def convert(family: str, arch: ir.Architecture, t: dict, dtype) -> tuple:
         "rms_norm_eps": n1.eps, "rope_theta": attn.rope.base, "hidden_act": "silu", "attention_bias": False,
         "attention_dropout": 0.0, "max_position_embeddings": 131072, "tie_word_embeddings": bool(tied),
         "torch_dtype": str(dtype).removeprefix("torch."), "use_cache": True,
-        "rope_parameters": {"rope_type": "default", "rope_theta": attn.rope.base},
+        "rope_parameters": rope_parameters(attn.rope),
     }
+    if attn.rope.scaling is not None:
+        cfg["rope_scaling"] = {k: v for k, v in cfg["rope_parameters"].items() if k != "rope_theta"}   # the older key
     if family == "llama":
         cfg.update(model_type="llama", architectures=["LlamaForCausalLM"], intermediate_size=ffn.intermediate_size,
                    mlp_bias=False)
+    elif family == "mistral":
+        cfg.update(model_type="mistral", architectures=["MistralForCausalLM"], intermediate_size=ffn.intermediate_size,
+                   sliding_window=attn.sliding_window_size)
+    elif family == "qwen2":
+        cfg.update(model_type="qwen2", architectures=["Qwen2ForCausalLM"], intermediate_size=ffn.intermediate_size,
+                   use_sliding_window=False, sliding_window=None)
+    elif family == "mixtral":
+        cfg.update(model_type="mixtral", architectures=["MixtralForCausalLM"], intermediate_size=ffn.expert.intermediate_size,
+                   num_local_experts=ffn.num_experts, num_experts_per_tok=ffn.top_k, sliding_window=None,
+                   output_router_logits=False, router_aux_loss_coef=ffn.aux_loss_coef or 0.0, router_jitter_noise=0.0)
     elif family == "qwen3":
         cfg.update(model_type="qwen3", architectures=["Qwen3ForCausalLM"], intermediate_size=ffn.intermediate_size)
     else:
@@ -146,5 +195,5 @@ def convert(family: str, arch: ir.Architecture, t: dict, dtype) -> tuple:
                    intermediate_size=ffn.expert.intermediate_size, moe_intermediate_size=ffn.expert.intermediate_size,
                    num_experts=ffn.num_experts, num_experts_per_tok=ffn.top_k, norm_topk_prob=bool(ffn.normalize_top_k),
                    decoder_sparse_step=1, mlp_only_layers=[], output_router_logits=False,
-                   router_aux_loss_coef=ffn.aux_loss_weight or 0.0)
+                   router_aux_loss_coef=getattr(ffn, "aux_loss_coef", 0.0) or 0.0)
     return cfg, {k: v.to(dtype) if v.is_floating_point() else v for k, v in out.items()}

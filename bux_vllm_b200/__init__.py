@@ -1,7 +1,7 @@
 """bux exports in vLLM.
 
-A checkpoint that `bux_b200.export` wrote in a standard family's format (llama, qwen3,
-qwen3_moe) needs nothing from here: vLLM serves it as that family. This plugin is for
+A checkpoint that `bux_b200.export` wrote in a standard family's format (llama, mistral,
+qwen2, qwen3, mixtral, qwen3_moe) needs nothing from here: vLLM serves it as that family. This plugin is for
 folders in the ``bux`` format (``model_type: "bux"``, the architecture carried as its
 IR): it registers the config with transformers and ``BuxForCausalLM`` with vLLM, a model
 that recognises which of vLLM's own decoder implementations the IR describes, builds

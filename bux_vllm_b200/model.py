@@ -12,8 +12,12 @@ from torch import nn
 
 from . import plan
 
+# family → (vLLM's module, its class, transformers' config class): the modules vLLM's own registry names
 _MODULES = {"llama": ("vllm.model_executor.models.llama", "LlamaForCausalLM", "LlamaConfig"),
+            "mistral": ("vllm.model_executor.models.mistral", "MistralForCausalLM", "MistralConfig"),
+            "qwen2": ("vllm.model_executor.models.qwen2", "Qwen2ForCausalLM", "Qwen2Config"),
             "qwen3": ("vllm.model_executor.models.qwen3", "Qwen3ForCausalLM", "Qwen3Config"),
+            "mixtral": ("vllm.model_executor.models.mixtral", "MixtralForCausalLM", "MixtralConfig"),
             "qwen3_moe": ("vllm.model_executor.models.qwen3_moe", "Qwen3MoeForCausalLM", "Qwen3MoeConfig")}
 
 

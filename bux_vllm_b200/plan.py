@@ -7,7 +7,8 @@ from __future__ import annotations
 import re
 from typing import Iterator, Optional
 
-FAMILIES = {"llama": "LlamaForCausalLM", "qwen3": "Qwen3ForCausalLM", "qwen3_moe": "Qwen3MoeForCausalLM"}
+FAMILIES = {"llama": "LlamaForCausalLM", "mistral": "MistralForCausalLM", "qwen2": "Qwen2ForCausalLM",
+            "qwen3": "Qwen3ForCausalLM", "mixtral": "MixtralForCausalLM", "qwen3_moe": "Qwen3MoeForCausalLM"}
 
 
 def _layer(node, kind=None):
@@ -53,18 +54,49 @@ def family(arch: dict) -> tuple:
     if a["type"] != "gqa":
         return None, f"token mixer '{a['type']}' has no served counterpart in this plugin"
     rope = a.get("rope")
-    odd = [k for k in ("sinks", "gated", "softcap", "sliding_window_size", "bias", "scale", "output_norm",
-                       "differential", "k_eq_v", "indexer", "kv_conv_size") if a.get(k)]
-    if rope is None or rope.get("layout", "half") != "half" or rope.get("fraction", 1.0) != 1.0 or rope.get("scaling"):
+    out_bias = a.get("bias") if a.get("output_bias") is None else a.get("output_bias")
+    odd = [k for k in ("sinks", "gated", "softcap", "scale", "output_norm", "differential", "k_eq_v", "indexer",
+                       "kv_conv_size", "paired", "exclusive", "power_scale", "log_scale", "relative_bias") if a.get(k)]
+    if out_bias:
+        odd.append("output_bias")
+    if rope is None or rope.get("layout", "half") != "half" or rope.get("fraction", 1.0) != 1.0:
         odd.append("rope")
+    elif (rope.get("scaling") or {}).get("attention_factor_on", "rotary") != "rotary":
+        odd.append("rope.scaling.attention_factor_on")
     if odd:
         return None, f"gqa settings without a served counterpart: {', '.join(odd)}"
     qk = a.get("qk_norm") is not None
+    window, bias = a.get("sliding_window_size") is not None, bool(a.get("bias"))
+    if sum((qk, window, bias)) > 1:
+        return None, "more than one of qk_norm, sliding_window_size and bias: no served family has both"
     if f["type"] == "gated_mlp" and f.get("activation") == "swish" and not f.get("bias"):
-        return ("qwen3" if qk else "llama"), ""
-    if f["type"] == "moe" and qk and f.get("router", "softmax") == "softmax" and not f.get("num_shared_experts"):
-        return "qwen3_moe", ""
+        return ("qwen3" if qk else "qwen2" if bias else "mistral" if window else "llama"), ""
+    if (f["type"] == "moe" and not window and not bias and f.get("router", "softmax") == "softmax"
+            and not f.get("num_shared_experts")):
+        if qk:
+            return "qwen3_moe", ""
+        if f.get("normalize_top_k", True):
+            return "mixtral", ""
+        return None, "Mixtral renormalises the picked weights: normalize_top_k=false has no served counterpart"
     return None, f"feed-forward '{f['type']}' has no served counterpart in this plugin"
+
+
+def rope_parameters(rope: dict) -> dict:
+    out = {"rope_type": "default", "rope_theta": rope.get("base", 10000.0)}
+    sc = rope.get("scaling")
+    if not sc:
+        return out
+    if sc["type"] == "pi":
+        out.update(rope_type="linear", factor=sc["factor"])
+    elif sc["type"] == "llama3":
+        out.update(rope_type="llama3", factor=sc["factor"], original_max_position_embeddings=sc.get("original_max_len", 8192),
+                   low_freq_factor=sc.get("low_freq_factor", 1.0), high_freq_factor=sc.get("high_freq_factor", 4.0))
+    else:
+        out.update(rope_type="yarn", factor=sc["factor"], original_max_position_embeddings=sc["original_max_len"],
+                   beta_fast=sc.get("beta_fast", 32.0), beta_slow=sc.get("beta_slow", 1.0))
+        if sc.get("attention_factor") is not None:
+            out["attention_factor"] = sc["attention_factor"]
+    return out
 
 
 def hf_fields(arch: dict, fam: str) -> dict:
@@ -77,8 +109,17 @@ def hf_fields(arch: dict, fam: str) -> dict:
         "head_dim": a.get("head_dim") or d // a["num_heads"], "rms_norm_eps": p["norm"].get("eps", 1e-6),
         "rope_theta": a["rope"].get("base", 10000.0), "hidden_act": "silu", "attention_bias": False,
         "max_position_embeddings": 131072, "tie_word_embeddings": p["tied"],
+        "rope_parameters": rope_parameters(a["rope"]),
     }
-    if fam == "qwen3_moe":
+    if a["rope"].get("scaling"):
+        out["rope_scaling"] = {k: v for k, v in out["rope_parameters"].items() if k != "rope_theta"}
+    if fam == "mistral":
+        out["sliding_window"] = a["sliding_window_size"]
+    if fam == "mixtral":
+        x = f["expert"]
+        out.update(intermediate_size=x["intermediate_size"], num_local_experts=f["num_experts"],
+                   num_experts_per_tok=f["top_k"], sliding_window=None)
+    elif fam == "qwen3_moe":
         x = f["expert"]
         out.update(intermediate_size=x["intermediate_size"], moe_intermediate_size=x["intermediate_size"],
                    num_experts=f["num_experts"], num_experts_per_tok=f["top_k"],
@@ -112,13 +153,18 @@ def rename(name: str, tensor, fam: str) -> Iterator:
     elif branch == 0:
         if leaf in ("q.weight", "k.weight", "v.weight", "o.weight"):
             yield f"{pre}.self_attn.{leaf[0]}_proj.weight", tensor
+        elif leaf in ("q.bias", "k.bias", "v.bias"):
+            yield f"{pre}.self_attn.{leaf[0]}_proj.bias", tensor
         elif leaf in ("q_norm.scale", "k_norm.scale"):
             yield f"{pre}.self_attn.{leaf[:6]}.weight", tensor
     elif leaf in ("gate.weight", "up.weight", "down.weight"):
         yield f"{pre}.mlp.{leaf.split('.')[0]}_proj.weight", tensor
     elif leaf == "router.weight":
-        yield f"{pre}.mlp.gate.weight", tensor
+        yield f"{pre}.{'block_sparse_moe' if fam == 'mixtral' else 'mlp'}.gate.weight", tensor
     elif leaf in ("experts.gate", "experts.up", "experts.down"):
         which = leaf.split(".")[1]
         for e in range(tensor.shape[0]):
-            yield f"{pre}.mlp.experts.{e}.{which}_proj.weight", tensor[e]
+            if fam == "mixtral":
+                yield f"{pre}.block_sparse_moe.experts.{e}.{ {'gate': 'w1', 'up': 'w3', 'down': 'w2'}[which] }.weight", tensor[e]
+            else:
+                yield f"{pre}.mlp.experts.{e}.{which}_proj.weight", tensor[e]

@@ -57,6 +57,9 @@ def test_detects_standard_families():
     assert fam(", qk_norm=rmsnorm", DENSE) == "qwen3"
     assert fam(", qk_norm=rmsnorm", MOE) == "qwen3_moe"
     assert fam(", sinks=true", DENSE) is None
+    assert fam(", bias=true", DENSE) is None and fam(", bias=true, output_bias=false", DENSE) == "qwen2"
+    assert fam(", sliding_window_size=8", DENSE) == "mistral" and fam(", sliding_window_size=8, bias=true, output_bias=false", DENSE) is None
+    assert fam("", MOE) == "mixtral" and fam("", MOE.replace("top_k=2,", "top_k=2, normalize_top_k=false,")) is None
     assert fam(", paired=true", DENSE) is None and fam(", exclusive=true", DENSE) is None
     with_pointer = BASE.format(qk="", ffn=DENSE, extra="").replace("head(tied=false)", "head(tied=false, pointer=copy_pointer(dim=8))")
     assert native.detect(compile_runs(with_pointer, filename="e.bux")[0].arch) is None
@@ -78,10 +81,21 @@ def test_bux_format_round_trip(tmp_path):
     assert report.results[0].greedy["cache"] == report.results[0].greedy["bux"] and report.results[0].padded
 
 
-@pytest.mark.parametrize("qk,ffn,family", [("", DENSE, "llama"), (", qk_norm=rmsnorm", DENSE, "qwen3"),
-                                           (", qk_norm=rmsnorm", MOE, "qwen3_moe")])
+@pytest.mark.parametrize("qk,ffn,family", [
+    ("", DENSE, "llama"), (", qk_norm=rmsnorm", DENSE, "qwen3"), (", qk_norm=rmsnorm", MOE, "qwen3_moe"),
+    (", sliding_window_size=5", DENSE, "mistral"), (", bias=true, output_bias=false", DENSE, "qwen2"), ("", MOE, "mixtral"),
+    ("LLAMA3", DENSE, "llama"), ("YARN", DENSE, "qwen3"), ("PI", DENSE, "llama")])
 def test_standard_families_load_in_transformers(tmp_path, qk, ffn, family):
-    run, tr, folder = _trained(tmp_path, qk=qk, ffn=ffn)
+    scaled = {"LLAMA3": "rope(scaling=llama3(factor=4.0, original_max_len=8))",
+              "YARN": "rope(scaling=yarn(factor=4.0, original_max_len=8)), qk_norm=rmsnorm",
+              "PI": "rope(scaling=pi(factor=2.0))"}.get(qk)
+    if scaled:     # a scaled RoPE: the family's rope_parameters must mean what the layer computes
+        global BASE
+        run = compile_runs(BASE.replace("rope=rope(){qk}", "rope=" + scaled).format(ffn=ffn, extra=""), filename="e.bux")[0]
+        tr = train(run, out=tmp_path / "runs", device="cpu", quiet=True)
+        (folder,) = list((tmp_path / "runs").iterdir())
+    else:
+        run, tr, folder = _trained(tmp_path, qk=qk, ffn=ffn)
     out = export(folder, tmp_path / "hf", dtype="float32", echo=lambda *_: None)
     assert json.loads((out / "config.json").read_text())["model_type"] == family
     report = C.compare(tr.model, out, tolerance=2e-3)   # transformers' own implementation of the family
