@@ -98,12 +98,29 @@ class BuxForCausalLM(PreTrainedModel):
         return CausalLMOutput(loss=loss, logits=logits)
 
     @torch.no_grad()
-    def generate(self, input_ids, attention_mask=None, max_new_tokens: int = 16, **kwargs):
-        """Greedy decoding by whole-sequence passes (no cache): for checks, not serving. Rows
-        may be left-padded (`attention_mask`); sampling and cache arguments are ignored."""
+    def generate(self, input_ids, attention_mask=None, max_new_tokens: int = 16, use_cache: bool = True, **kwargs):
+        """Greedy decoding. With `use_cache` (and a graph whose only state between tokens is
+        attention's keys and values) the prompt runs once and every new token alone, over a
+        key/value cache; otherwise every step is a pass over the whole sequence. Rows may be
+        left-padded (`attention_mask`); sampling arguments are ignored. For checks and light
+        generation: serving goes through vLLM."""
+        rt = runtime(getattr(self.config, "_name_or_path", None) or None)
+        caching = importlib.import_module(rt.__name__ + ".models.cache")
+        if not use_cache or caching.supports(self.model.arch) is not None:
+            for _ in range(max_new_tokens):
+                nxt = self(input_ids, attention_mask=attention_mask).logits[:, -1].argmax(-1, keepdim=True)
+                input_ids = torch.cat([input_ids, nxt], dim=1)
+                if attention_mask is not None:
+                    attention_mask = torch.cat([attention_mask, torch.ones_like(attention_mask[:, :1])], dim=1)
+            return input_ids
+        cache = caching.DecodeCache()
+        mask = torch.ones_like(input_ids) if attention_mask is None else attention_mask.to(input_ids.dtype)
+        positions = (mask.cumsum(-1) - 1).clamp_min(0)
+        new, new_positions, new_mask = input_ids, positions, mask
         for _ in range(max_new_tokens):
-            nxt = self(input_ids, attention_mask=attention_mask).logits[:, -1].argmax(-1, keepdim=True)
+            ctx = self.model(new, new_positions, new_mask.to(torch.int32), training=False, cache=cache)
+            nxt = ctx.heads[0].logits()[:, -1].float().argmax(-1, keepdim=True)
             input_ids = torch.cat([input_ids, nxt], dim=1)
-            if attention_mask is not None:
-                attention_mask = torch.cat([attention_mask, torch.ones_like(attention_mask[:, :1])], dim=1)
+            new, new_positions, new_mask = nxt, positions[:, -1:] + 1, torch.ones_like(nxt)
+            positions = torch.cat([positions, new_positions], dim=1)
         return input_ids

@@ -255,6 +255,14 @@ class GQA(nn.Module):
             from .. import observe
 
             observe.attention_sample(ctx, q, k, c.scale)
+        if ctx.cache is not None:
+            # incremental decoding: the new keys and values join the layer's cache and the new
+            # queries (the last t positions) attend over all of it; padding is never read
+            from ...ops import reference as ref
+
+            k_all, v_all = ctx.cache.extend(self, k, v)
+            out, _ = ref.attention(q, k_all, v_all, **{**kw, "segments": ctx.cache.segments()})
+            return self._finish(out, x, v, bsz, t, ctx)
         if cp is not None:
             from ...parallel import context
 

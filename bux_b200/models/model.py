@@ -36,7 +36,9 @@ class Model(nn.Module):
     def forward(self, input_ids: torch.Tensor, positions: Optional[torch.Tensor] = None,
                 segments: Optional[torch.Tensor] = None, *, training: Optional[bool] = None,
                 precision: Optional[Precision] = None, methods=None, parallel=None,
-                step: int = 0, observe: Optional[dict] = None) -> Context:
+                step: int = 0, observe: Optional[dict] = None, cache=None) -> Context:
+        """`cache` (a `bux_b200.models.cache.DecodeCache`): the tokens continue what it holds;
+        `segments` then marks padding (0) against real tokens (non-zero), nothing else."""
         ctx = Context(input_ids, positions, segments,
                       training=self.training if training is None else training,
                       precision=precision or Precision(compute=self.dtype), methods=methods,
@@ -44,6 +46,10 @@ class Model(nn.Module):
         if observe is not None:   # an observed step: layers file their statistics in ctx.observed
             ctx.observing = True
             ctx.observe_histograms = bool(observe.get("histograms"))
+        if cache is not None:
+            real = torch.ones_like(input_ids, dtype=torch.bool) if segments is None else segments != 0
+            cache.begin(real)
+            ctx.cache, ctx.segments = cache, None
         ctx.output = self.graph(input_ids, ctx)
         return ctx
 

@@ -119,6 +119,7 @@ class Context:
         self.observed_branch = None
         self.branch_names: dict = {}   # how many branches of each name ran so far
         self.pending_read = None  # single-pass hyper-connections: the read the last branch computed
+        self.cache = None         # a `DecodeCache` when the tokens continue what it holds (incremental decoding)
 
     # taps are named stacks
     def push(self, name: str, value) -> None:

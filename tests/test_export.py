@@ -151,3 +151,45 @@ assert err < 1e-4, err
     proc = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, cwd=str(tmp_path),
                           env={k: v for k, v in __import__("os").environ.items() if k != "PYTHONPATH"})
     assert proc.returncode == 0, proc.stdout + proc.stderr
+
+
+def test_decoding_over_a_key_value_cache_equals_whole_sequence_passes():
+    """`DecodeCache`: a prompt in one call and tokens one at a time give the logits of passes
+    over the whole sequence, with sinks, a window, q/k norms, a value residual through a port,
+    experts, and a left-padded row beside a full one; graphs with other state are refused."""
+    from bux_b200.models import Model
+    from bux_b200.models.cache import DecodeCache, supports
+
+    src = """
+d_model=32
+vocab_size=64
+n = rmsnorm
+a = gqa(num_heads=4, num_kv_heads=2, rope=rope(), sinks=true, qk_norm=rmsnorm, softcap=20.0, value_residual=learned)
+w = a(sliding_window_size=4)
+e = moe(num_experts=4, top_k=2, expert=gated_mlp(intermediate_size=16, activation=swish))
+model = embed [n a(v=@v)] [n e] ([n w(v=$v)] [n gated_mlp(intermediate_size=48, activation=gelu)])^2 n head
+"""
+    from bux_b200.lang import compile
+
+    arch = compile(src, filename="c.bux")
+    assert supports(arch) is None
+    model = C.perturbed(Model(arch, dtype=torch.float32), scale=0.05).eval()
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, 64, (2, 10), generator=g)
+    mask = torch.ones(2, 10, dtype=torch.int32)
+    mask[1, :3] = 0                                                   # the second row is left-padded by three
+    pos = (mask.cumsum(-1) - 1).clamp_min(0)
+    with torch.no_grad():
+        whole = model(ids, pos, mask, training=False).heads[0].logits().float()
+        cache = DecodeCache()
+        first = model(ids[:, :6], pos[:, :6], mask[:, :6], training=False, cache=cache).heads[0].logits().float()
+        steps = [model(ids[:, t:t + 1], pos[:, t:t + 1], mask[:, t:t + 1], training=False, cache=cache).heads[0].logits().float()
+                 for t in range(6, 10)]
+    got = torch.cat([first, *steps], dim=1)
+    real = mask.bool()
+    assert torch.allclose(got[real], whole[real], atol=2e-5), (got[real] - whole[real]).abs().max()
+    assert cache.length == 10
+    for bad, why in (("a = gqa(num_heads=4, num_kv_heads=2, indexer=indexer(num_heads=2, head_dim=8, top_k=2))", "indexer"),
+                     ("a = gdn(num_heads=2, head_dim=16)", "gdn"), ("residual = hc(expansion=2)\na = gqa(num_heads=4, num_kv_heads=2)", "hc")):
+        other = compile("d_model=32\nvocab_size=64\n" + bad + "\nmodel = embed [rmsnorm a] rmsnorm head\n", filename="c.bux")
+        assert why in supports(other)
