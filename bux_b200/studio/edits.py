@@ -77,10 +77,6 @@ def _call_of(ix: features.Index, name: str, seen=()):
     raise EditError(f"'{name}' is not written as a call: its settings cannot be set here")
 
 
-def _value_end(source: str, arg: S.Arg, base: int) -> tuple:
-    return arg.span.start - base, arg.span.end - base
-
-
 # ------------------------------------------------------------------------------ settings of a call
 def set_field(source: str, start: int, end: int, key: str, value: Optional[str], path: Optional[str] = None) -> str:
     """Set `key` (dotted for a nested setting: ``rope.base``) of what is written at [start, end)
