@@ -1,14 +1,15 @@
-"""Incremental decoding: a key/value cache for the graphs whose only state between tokens is
-attention's keys and values.
+"""Incremental decoding: the state a graph carries between tokens, kept between calls.
 
 ``Model(..., cache=DecodeCache())`` runs the given tokens as the continuation of what the
 cache holds: every `gqa` layer appends its new keys and values and attends over all of
-them, everything else runs per token as always. A prompt is one call, each decoded token one
+them, the linear-attention mixers (DeltaNet, Gated DeltaNet, GDN-2, KDA, GLA, Lightning)
+continue their recurrent state, causal convolutions keep their last inputs, everything else
+runs per token as always. A prompt is one call, each decoded token one
 more. Rows may be left-padded: the cache keeps which of its positions are real tokens, and
 padding is never attended. `supports(arch)` says whether an architecture can decode this way
-(and why not): layers that carry other state between tokens (recurrent mixers, convolutions,
-compressed or latent attention, n-gram memory, the copy layers) and layers that read keys
-another layer cached are run by whole-sequence passes instead. The attention here is the
+(and why not): layers that carry other state between tokens (RWKV-7, Mamba, compressed or
+latent attention, n-gram memory, the copy layers) and layers that read keys another layer
+cached are run by whole-sequence passes instead. The attention here is the
 plain PyTorch statement: it is for checks and light generation, not for serving.
 Reference: the caches of ``export/hf/attention.py`` there.
 """
@@ -23,6 +24,7 @@ from ..lang import ir
 
 _PER_TOKEN = {"embed", "head", "rmsnorm", "layernorm", "dyt", "mlp", "gated_mlp", "moe", "linear", "act", "scale",
               "dropout", "value_embed", "merge"}
+_CONTINUED = {"deltanet", "gdn", "gdn2", "kda", "gla", "lightning", "conv", "short_conv"}   # state or last inputs cached
 
 
 def supports(arch: ir.Architecture) -> Optional[str]:
@@ -40,7 +42,7 @@ def supports(arch: ir.Architecture) -> Optional[str]:
         elif c.type == "head":
             if c.pointer is not None:
                 return "a copy pointer looks back over the whole context"
-        elif c.type not in _PER_TOKEN:
+        elif c.type not in _PER_TOKEN and c.type not in _CONTINUED:
             return f"'{c.type}' carries state between tokens that is not cached here"
     return None
 
@@ -51,6 +53,8 @@ class DecodeCache:
     def __init__(self):
         self.keys: dict = {}
         self.values: dict = {}
+        self.states: dict = {}     # recurrent mixers: the state after the last cached token
+        self.tails: dict = {}      # causal convolutions: their last inputs
         self.real: Optional[torch.Tensor] = None      # [b, s] bool: False where a row is padded
         self.new_real: Optional[torch.Tensor] = None  # the same for the tokens of the call in flight
 

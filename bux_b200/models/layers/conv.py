@@ -33,8 +33,11 @@ class CausalDepthwise(nn.Module):
         if ctx is not None and getattr(ctx, "segments", None) is not None:
             pos = ctx.positions
         w = self.weight.to(x.dtype)
-        y = x * w[:, 0]
         taps = w.shape[1]
+        cache = getattr(ctx, "cache", None) if ctx is not None else None
+        if cache is not None and taps > 1:
+            return self._continued(x, ctx, cache, pos)
+        y = x * w[:, 0]
         cp = getattr(ctx.parallel, "context_group", None) if ctx is not None and getattr(ctx, "parallel", None) else None
         if cp is None or taps == 1:
             from ... import ops
@@ -57,6 +60,25 @@ class CausalDepthwise(nn.Module):
                 shifted = shifted * (pos >= j).unsqueeze(-1).to(x.dtype)
             y = y + shifted * w[:, j]
         return y if self.bias is None else y + self.bias.to(y.dtype)
+
+
+    def _continued(self, x, ctx, cache, pos):
+        """Incremental decoding: the taps reach back into the inputs of earlier calls, which the
+        cache holds (the last ``taps - 1`` of them; padding and what lies before a row's first
+        token count as zeros)."""
+        from ... import ops
+
+        t, keep = x.shape[1], self.weight.shape[1] - 1
+        tail = cache.tails.get(id(self))
+        real = cache.new_real.unsqueeze(-1).to(x.dtype)
+        if tail is None:       # the prompt: the usual sum (taps that would cross a row's start are dropped)
+            y = ops.causal_conv(x, self.weight, self.bias, pos)
+            joined = nn.functional.pad(x * real, (0, 0, keep, 0))
+        else:
+            joined = torch.cat([tail, x * real], dim=1)
+            y = ops.causal_conv(joined, self.weight, self.bias, None)[:, -t:]
+        cache.tails[id(self)] = joined[:, -keep:]
+        return y
 
 
 class Conv(nn.Module):

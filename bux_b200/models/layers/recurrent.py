@@ -55,7 +55,39 @@ def _pair(x, y, gx, gy, strict: bool):
     return torch.stack(out, 2)
 
 
+_decoding = None   # (cache, layer) while a mixer runs with a `DecodeCache`: `scan` carries its state
+
+
+class decoding:
+    """While active, the layer's `scan` starts from the state the cache holds for it and leaves
+    its last state there (incremental decoding, `bux_b200.models.cache`)."""
+
+    def __init__(self, ctx, layer):
+        self.slot = (ctx.cache, layer) if getattr(ctx, "cache", None) is not None else None
+
+    def __enter__(self):
+        global _decoding
+        self.before, _decoding = _decoding, self.slot
+        return self
+
+    def __exit__(self, *exc):
+        global _decoding
+        _decoding = self.before
+        return False
+
+
 def scan(q, k, v, g, a=None, b=None, starts: Optional[torch.Tensor] = None, state=None, group=None):
+    """`_scan`, continuing the state of a `DecodeCache` when a layer decodes with one."""
+    slot = _decoding
+    if slot is None:
+        return _scan(q, k, v, g, a, b, starts, state, group)
+    cache, layer = slot
+    out, last = _scan(q, k, v, g, a, b, starts, cache.states.get(id(layer)) if state is None else state, group)
+    cache.states[id(layer)] = last
+    return out, last
+
+
+def _scan(q, k, v, g, a=None, b=None, starts: Optional[torch.Tensor] = None, state=None, group=None):
     """The recurrence above from `state` (zero if None). q, k, a, b: [B, T, H, dk];
     v: [B, T, H, dv]; g = log w: [B, T, H, dk] or [B, T, H, 1] (<= 0); starts: bool [B, T],
     true where a document begins. With `group` the positions are split over its ranks
@@ -64,13 +96,13 @@ def scan(q, k, v, g, a=None, b=None, starts: Optional[torch.Tensor] = None, stat
     if group is not None:
         from ...parallel import recurrence
 
-        return recurrence.pass_state(scan, q, k, v, g, a, b, starts, group)
+        return recurrence.pass_state(_scan, q, k, v, g, a, b, starts, group)
     if k.is_cuda and v.dtype == torch.bfloat16 and not torch.backends.cuda.matmul.allow_tf32:
         # bf16 activations: the chunk matrices end up as bf16 operands of the scan kernel, so
         # their fp32 matmuls may run on the tensor cores in TF32 (three more mantissa bits than bf16)
         torch.backends.cuda.matmul.allow_tf32 = True
         try:
-            return scan(q, k, v, g, a, b, starts, state, group)
+            return _scan(q, k, v, g, a, b, starts, state, group)
         finally:
             torch.backends.cuda.matmul.allow_tf32 = False
     bsz, t, h, dk = k.shape
@@ -255,8 +287,9 @@ class LinearAttention(nn.Module):
         return self.o(o, ctx)
 
     def forward(self, x, ctx: Context):
-        q, k, v = self.qkv(x, ctx)
-        return self.output(x, self.mix(x, q, k, v, ctx), ctx)
+        with decoding(ctx, self):
+            q, k, v = self.qkv(x, ctx)
+            return self.output(x, self.mix(x, q, k, v, ctx), ctx)
 
 
 class DeltaNet(LinearAttention):

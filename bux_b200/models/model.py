@@ -49,7 +49,10 @@ class Model(nn.Module):
         if cache is not None:
             real = torch.ones_like(input_ids, dtype=torch.bool) if segments is None else segments != 0
             cache.begin(real)
-            ctx.cache, ctx.segments = cache, None
+            ctx.cache = cache
+            # padding as a document of its own: recurrences restart and convolutions drop their
+            # taps at each row's first real token; attention reads the cache's own marks
+            ctx.segments = None if bool(real.all()) else real.to(torch.int32)
         ctx.output = self.graph(input_ids, ctx)
         return ctx
 

@@ -190,6 +190,44 @@ model = embed [n a(v=@v)] [n e] ([n w(v=$v)] [n gated_mlp(intermediate_size=48, 
     assert torch.allclose(got[real], whole[real], atol=2e-5), (got[real] - whole[real]).abs().max()
     assert cache.length == 10
     for bad, why in (("a = gqa(num_heads=4, num_kv_heads=2, indexer=indexer(num_heads=2, head_dim=8, top_k=2))", "indexer"),
-                     ("a = gdn(num_heads=2, head_dim=16)", "gdn"), ("residual = hc(expansion=2)\na = gqa(num_heads=4, num_kv_heads=2)", "hc")):
+                     ("a = rwkv7(num_heads=2, head_dim=16)", "rwkv7"), ("residual = hc(expansion=2)\na = gqa(num_heads=4, num_kv_heads=2)", "hc")):
         other = compile("d_model=32\nvocab_size=64\n" + bad + "\nmodel = embed [rmsnorm a] rmsnorm head\n", filename="c.bux")
         assert why in supports(other)
+
+
+@pytest.mark.parametrize("mixer", ["gdn(num_heads=2, head_dim=16)", "kda(num_heads=2, head_dim=16)", "deltanet(num_heads=2, head_dim=16)",
+                                   "gla(num_heads=2, head_dim=16)", "lightning(num_heads=2, head_dim=16)",
+                                   "gdn2(num_heads=2, head_dim=16)", "short_conv(conv_size=3)", "conv(size=4)"])
+def test_recurrent_mixers_and_convolutions_continue_from_the_cache(mixer):
+    """A hybrid of one recurrent mixer (or a convolution) and attention decodes token by token to
+    the logits of whole-sequence passes: the recurrent state and the convolutions' last inputs
+    live in the cache; a left-padded row restarts both at its first real token."""
+    from bux_b200.lang import compile
+    from bux_b200.models import Model
+    from bux_b200.models.cache import DecodeCache, supports
+
+    arch = compile(f"""
+d_model=32
+vocab_size=64
+n = rmsnorm
+r = {mixer}
+a = gqa(num_heads=4, num_kv_heads=2, rope=rope())
+f = gated_mlp(intermediate_size=48, activation=swish)
+model = embed ([n r] [n f] [n a] [n f])^2 n head
+""", filename="h.bux")
+    assert supports(arch) is None
+    model = C.perturbed(Model(arch, dtype=torch.float32), scale=0.05).eval()
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, 64, (2, 9), generator=g)
+    mask = torch.ones(2, 9, dtype=torch.int32)
+    mask[1, :2] = 0
+    pos = (mask.cumsum(-1) - 1).clamp_min(0)
+    with torch.no_grad():
+        whole = model(ids, pos, mask, training=False).heads[0].logits().float()
+        cache = DecodeCache()
+        parts = [model(ids[:, :5], pos[:, :5], mask[:, :5], training=False, cache=cache).heads[0].logits().float()]
+        parts += [model(ids[:, t:t + 1], pos[:, t:t + 1], mask[:, t:t + 1], training=False, cache=cache).heads[0].logits().float()
+                  for t in range(5, 9)]
+    got, real = torch.cat(parts, dim=1), mask.bool()
+    assert torch.allclose(got[real], whole[real], atol=5e-5), (got[real] - whole[real]).abs().max()
+    assert supports(compile("d_model=32\nvocab_size=64\nmodel = embed [rmsnorm mamba2(state_size=16, head_dim=16)] rmsnorm head\n", filename="h.bux"))
