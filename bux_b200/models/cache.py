@@ -1,14 +1,14 @@
 """Incremental decoding: the state a graph carries between tokens, kept between calls.
 
 ``Model(..., cache=DecodeCache())`` runs the given tokens as the continuation of what the
-cache holds: every `gqa` layer appends its new keys and values and attends over all of
+cache holds: every `gqa` and `mla` layer appends its new keys and values and attends over all of
 them, the linear-attention mixers (DeltaNet, Gated DeltaNet, GDN-2, KDA, GLA, Lightning)
 continue their recurrent state, causal convolutions keep their last inputs, everything else
 runs per token as always. A prompt is one call, each decoded token one
 more. Rows may be left-padded: the cache keeps which of its positions are real tokens, and
 padding is never attended. `supports(arch)` says whether an architecture can decode this way
-(and why not): layers that carry other state between tokens (RWKV-7, Mamba, compressed or
-latent attention, n-gram memory, the copy layers) and layers that read keys another layer
+(and why not): layers that carry other state between tokens (RWKV-7, Mamba, compressed
+attention, n-gram memory, the copy layers) and layers that read keys another layer
 cached are run by whole-sequence passes instead. The attention here is the
 plain PyTorch statement: it is for checks and light generation, not for serving.
 Reference: the caches of ``export/hf/attention.py`` there.
@@ -39,6 +39,9 @@ def supports(arch: ir.Architecture) -> Optional[str]:
                     return f"gqa({what}=...) needs more than cached keys and values"
             if any(p.name == "kv" and p.mode != "write" for p in layer.ports):
                 return "a layer that reads another layer's keys and values (the kv port) has no cache of its own"
+        elif c.type == "mla":
+            if c.indexer is not None:
+                return "mla(indexer=...) needs more than cached keys and values"
         elif c.type == "head":
             if c.pointer is not None:
                 return "a copy pointer looks back over the whole context"

@@ -84,6 +84,12 @@ class MLA(nn.Module):
         scale = c.scale if c.scale is not None else (n + r) ** -0.5
         if c.indexer is not None:
             out = self._sparse(x, q, k, v, scale, ctx)
+        elif getattr(ctx, "cache", None) is not None:
+            # incremental decoding: the expanded keys and values join the layer's cache (the plain
+            # statement; a serving stack caches the latent and absorbs the expansion instead)
+            k_all, v_all = ctx.cache.extend(self, k, v)
+            out, _ = ref.attention(q, k_all, v_all, causal=True, window=c.sliding_window_size, sinks=None,
+                                   softcap=c.softcap, scale=scale, segments=ctx.cache.segments())
         else:
             out = ops.attention(q, k, v, causal=True, window=c.sliding_window_size, sinks=None,
                                 softcap=c.softcap, scale=scale, segments=ctx.segments)

@@ -197,7 +197,8 @@ model = embed [n a(v=@v)] [n e] ([n w(v=$v)] [n gated_mlp(intermediate_size=48, 
 
 @pytest.mark.parametrize("mixer", ["gdn(num_heads=2, head_dim=16)", "kda(num_heads=2, head_dim=16)", "deltanet(num_heads=2, head_dim=16)",
                                    "gla(num_heads=2, head_dim=16)", "lightning(num_heads=2, head_dim=16)",
-                                   "gdn2(num_heads=2, head_dim=16)", "short_conv(conv_size=3)", "conv(size=4)"])
+                                   "gdn2(num_heads=2, head_dim=16)", "short_conv(conv_size=3)", "conv(size=4)",
+                                   "mla(num_heads=2, kv_lora_rank=16, qk_nope_head_dim=8, qk_rope_head_dim=8, v_head_dim=8, rope=rope())"])
 def test_recurrent_mixers_and_convolutions_continue_from_the_cache(mixer):
     """A hybrid of one recurrent mixer (or a convolution) and attention decodes token by token to
     the logits of whole-sequence passes: the recurrent state and the convolutions' last inputs
