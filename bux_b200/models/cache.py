@@ -2,12 +2,12 @@
 
 ``Model(..., cache=DecodeCache())`` runs the given tokens as the continuation of what the
 cache holds: every `gqa` and `mla` layer appends its new keys and values and attends over all of
-them, the linear-attention mixers (DeltaNet, Gated DeltaNet, GDN-2, KDA, GLA, Lightning)
-continue their recurrent state, causal convolutions keep their last inputs, everything else
+them, the recurrent mixers (DeltaNet, Gated DeltaNet, GDN-2, KDA, GLA, Lightning, RWKV-7,
+Mamba, Mamba-2) continue their state, causal convolutions keep their last inputs, everything else
 runs per token as always. A prompt is one call, each decoded token one
 more. Rows may be left-padded: the cache keeps which of its positions are real tokens, and
 padding is never attended. `supports(arch)` says whether an architecture can decode this way
-(and why not): layers that carry other state between tokens (RWKV-7, Mamba, compressed
+(and why not): layers that carry other state between tokens (compressed and sparse
 attention, n-gram memory, the copy layers) and layers that read keys another layer
 cached are run by whole-sequence passes instead. The attention here is the
 plain PyTorch statement: it is for checks and light generation, not for serving.
@@ -24,7 +24,7 @@ from ..lang import ir
 
 _PER_TOKEN = {"embed", "head", "rmsnorm", "layernorm", "dyt", "mlp", "gated_mlp", "moe", "linear", "act", "scale",
               "dropout", "value_embed", "merge"}
-_CONTINUED = {"deltanet", "gdn", "gdn2", "kda", "gla", "lightning", "conv", "short_conv"}   # state or last inputs cached
+_CONTINUED = {"deltanet", "gdn", "gdn2", "kda", "gla", "lightning", "rwkv7", "mamba", "mamba2", "conv", "short_conv"}
 
 
 def supports(arch: ir.Architecture) -> Optional[str]:

@@ -442,6 +442,12 @@ class RWKV7(nn.Module):
         bsz, t, _ = x.shape
         h, hv, dk, dv = self.h, self.hv, self.dk, self.dv
         prev = F.pad(x[:, :-1], (0, 0, 1, 0))
+        cache = getattr(ctx, "cache", None)
+        if cache is not None:     # incremental decoding: the token before this call's first one
+            last = cache.tails.get(("shift", id(self)))
+            if last is not None:
+                prev = torch.cat([last, x[:, :-1]], dim=1)
+            cache.tails[("shift", id(self))] = x[:, -1:]
         if _cp(ctx) is not None:  # the token before this rank's first one lives on the rank before
             from ...parallel import recurrence
 
@@ -470,7 +476,8 @@ class RWKV7(nn.Module):
 
         r, k, log_w, a, kk = map(split, (r, k, log_w, a, kk))
         kk = l2norm(kk, eps=1e-12)
-        o, _ = scan(r, k, v, log_w, -kk, kk * a, st, group=_cp(ctx))
+        with decoding(ctx, self):
+            o, _ = scan(r, k, v, log_w, -kk, kk * a, st, group=_cp(ctx))
         o = F.layer_norm(o.float(), (dv,), eps=self.eps) * self.norm_scale.float() + self.norm_bias.float()
         o = o + (r * k * self.r_k.float()).sum(-1, keepdim=True) * v.float()
         o = o.reshape(bsz, t, -1)
@@ -480,18 +487,21 @@ class RWKV7(nn.Module):
 
 
 # ------------------------------------------------------------------ state space models
-def mamba_scan(x, dt, A, B, C, starts=None):
+def mamba_scan(x, dt, A, B, C, starts=None, state=None, last: Optional[list] = None):
     """Every channel's state S = exp(dt A) S + (dt x) B, read as y = S·C, one position at a
-    time in fp32. x, dt: [b, t, d]; A: [d, n]; B, C: [b, t, n]."""
+    time in fp32. x, dt: [b, t, d]; A: [d, n]; B, C: [b, t, n]. From `state` (zero if None);
+    the state after the last position is appended to `last` when a list is given."""
     xs, dt, A, B, C = x.float(), dt.float(), A.float(), B.float(), C.float()
     bsz, t, d = xs.shape
-    s = xs.new_zeros(bsz, d, A.shape[-1])
+    s = xs.new_zeros(bsz, d, A.shape[-1]) if state is None else state.float()
     ys = []
     for i in range(t):
         if starts is not None:
             s = s * (~starts[:, i]).view(bsz, 1, 1).float()
         s = (dt[:, i, :, None] * A).exp() * s + (dt[:, i] * xs[:, i]).unsqueeze(-1) * B[:, i, None]
         ys.append((s * C[:, i, None]).sum(-1))
+    if last is not None:
+        last.append(s)
     return torch.stack(ys, 1).to(x.dtype)
 
 
@@ -523,7 +533,12 @@ class Mamba(nn.Module):
         if _cp(ctx) is not None:
             raise NotImplementedError("mamba: a state per channel and position is not handed on between ranks; "
                                       "use mamba2 (or another mixer of the family) under mesh(context=...)")
-        y = mamba_scan(u, dt, -self.A_log.float().exp(), self.b_norm(B, ctx), self.c_norm(C, ctx), _starts(ctx))
+        cache = getattr(ctx, "cache", None)
+        kept: Optional[list] = [] if cache is not None else None
+        y = mamba_scan(u, dt, -self.A_log.float().exp(), self.b_norm(B, ctx), self.c_norm(C, ctx), _starts(ctx),
+                       state=cache.states.get(id(self)) if cache is not None else None, last=kept)
+        if cache is not None:
+            cache.states[id(self)] = kept[0]
         y = (y.float() + u.float() * self.D.float()) * F.silu(z.float())
         return self.out_proj(y.to(x.dtype), ctx)
 
@@ -556,7 +571,8 @@ class Mamba2(nn.Module):
         B, C = (y.reshape(bsz, t, g, n).repeat_interleave(h // g, 2) for y in (B, C))
         dt = F.softplus(dt.float() + self.dt_bias.float())
         A = -self.A_log.float().exp()
-        y, _ = scan(C, B, dt.unsqueeze(-1) * u.float(), (dt * A).unsqueeze(-1), starts=_starts(ctx), group=_cp(ctx))
+        with decoding(ctx, self):
+            y, _ = scan(C, B, dt.unsqueeze(-1) * u.float(), (dt * A).unsqueeze(-1), starts=_starts(ctx), group=_cp(ctx))
         y = (y.float() + u.float() * self.D.float()[:, None]).reshape(bsz, t, d) * F.silu(z.float())
         y = self.norm(y.reshape(bsz, t, g, -1).to(x.dtype), ctx).reshape(bsz, t, d)
         return self.out_proj(y, ctx)

@@ -190,7 +190,7 @@ model = embed [n a(v=@v)] [n e] ([n w(v=$v)] [n gated_mlp(intermediate_size=48, 
     assert torch.allclose(got[real], whole[real], atol=2e-5), (got[real] - whole[real]).abs().max()
     assert cache.length == 10
     for bad, why in (("a = gqa(num_heads=4, num_kv_heads=2, indexer=indexer(num_heads=2, head_dim=8, top_k=2))", "indexer"),
-                     ("a = rwkv7(num_heads=2, head_dim=16)", "rwkv7"), ("residual = hc(expansion=2)\na = gqa(num_heads=4, num_kv_heads=2)", "hc")):
+                     ("a = csa(num_heads=2, head_dim=16, compress_ratio=4)", "csa"), ("residual = hc(expansion=2)\na = gqa(num_heads=4, num_kv_heads=2)", "hc")):
         other = compile("d_model=32\nvocab_size=64\n" + bad + "\nmodel = embed [rmsnorm a] rmsnorm head\n", filename="c.bux")
         assert why in supports(other)
 
@@ -198,6 +198,7 @@ model = embed [n a(v=@v)] [n e] ([n w(v=$v)] [n gated_mlp(intermediate_size=48, 
 @pytest.mark.parametrize("mixer", ["gdn(num_heads=2, head_dim=16)", "kda(num_heads=2, head_dim=16)", "deltanet(num_heads=2, head_dim=16)",
                                    "gla(num_heads=2, head_dim=16)", "lightning(num_heads=2, head_dim=16)",
                                    "gdn2(num_heads=2, head_dim=16)", "short_conv(conv_size=3)", "conv(size=4)",
+                                   "rwkv7(num_heads=2, head_dim=16)", "mamba(state_size=8)", "mamba2(state_size=16, head_dim=16)",
                                    "mla(num_heads=2, kv_lora_rank=16, qk_nope_head_dim=8, qk_rope_head_dim=8, v_head_dim=8, rope=rope())"])
 def test_recurrent_mixers_and_convolutions_continue_from_the_cache(mixer):
     """A hybrid of one recurrent mixer (or a convolution) and attention decodes token by token to
@@ -231,4 +232,4 @@ model = embed ([n r] [n f] [n a] [n f])^2 n head
                   for t in range(5, 9)]
     got, real = torch.cat(parts, dim=1), mask.bool()
     assert torch.allclose(got[real], whole[real], atol=5e-5), (got[real] - whole[real]).abs().max()
-    assert supports(compile("d_model=32\nvocab_size=64\nmodel = embed [rmsnorm mamba2(state_size=16, head_dim=16)] rmsnorm head\n", filename="h.bux"))
+    assert "engram" in supports(compile("d_model=32\nvocab_size=64\nmodel = embed [rmsnorm engram(head_dim=8, table_size=64)] rmsnorm head\n", filename="h.bux"))
