@@ -97,30 +97,56 @@ class BuxForCausalLM(PreTrainedModel):
                                                      labels[:, 1:].reshape(-1), ignore_index=-100)
         return CausalLMOutput(loss=loss, logits=logits)
 
+    @staticmethod
+    def _next(logits, do_sample: bool, temperature: float, top_k, top_p, generator):
+        """The next token of each row from its last position's logits: the largest, or a draw
+        after temperature, top-k and nucleus (top-p) filtering."""
+        if not do_sample:
+            return logits.argmax(-1, keepdim=True)
+        logits = logits / max(float(temperature), 1e-6)
+        if top_k:
+            kth = logits.topk(min(int(top_k), logits.shape[-1]), dim=-1).values[..., -1:]
+            logits = logits.masked_fill(logits < kth, float("-inf"))
+        if top_p is not None and top_p < 1.0:
+            ordered, order = logits.sort(dim=-1, descending=True)
+            mass = ordered.softmax(-1).cumsum(-1)
+            drop = mass - ordered.softmax(-1) >= top_p          # keep the token that crosses top_p
+            logits = logits.masked_fill(drop.scatter(-1, order, drop), float("-inf"))
+        return torch.multinomial(logits.softmax(-1), 1, generator=generator)
+
     @torch.no_grad()
-    def generate(self, input_ids, attention_mask=None, max_new_tokens: int = 16, use_cache: bool = True, **kwargs):
-        """Greedy decoding. With `use_cache` (and a graph whose only state between tokens is
-        attention's keys and values) the prompt runs once and every new token alone, over a
-        key/value cache; otherwise every step is a pass over the whole sequence. Rows may be
-        left-padded (`attention_mask`); sampling arguments are ignored. For checks and light
+    def generate(self, input_ids, attention_mask=None, max_new_tokens: int = 16, use_cache: bool = True,
+                 do_sample: bool = False, temperature: float = 1.0, top_k=None, top_p=None, eos_token_id=None,
+                 pad_token_id=None, generator=None, **kwargs):
+        """Decode `max_new_tokens` tokens: greedily, or by sampling (`do_sample`, `temperature`,
+        `top_k`, `top_p`, `generator`). With `use_cache` (and a graph `models.cache` can carry
+        between tokens) the prompt runs once and every new token alone; otherwise every step is a
+        pass over the whole sequence. Rows may be left-padded (`attention_mask`); a row that has
+        produced `eos_token_id` is filled with `pad_token_id` from then on. For checks and light
         generation: serving goes through vLLM."""
         rt = runtime(getattr(self.config, "_name_or_path", None) or None)
         caching = importlib.import_module(rt.__name__ + ".models.cache")
-        if not use_cache or caching.supports(self.model.arch) is not None:
-            for _ in range(max_new_tokens):
-                nxt = self(input_ids, attention_mask=attention_mask).logits[:, -1].argmax(-1, keepdim=True)
-                input_ids = torch.cat([input_ids, nxt], dim=1)
-                if attention_mask is not None:
-                    attention_mask = torch.cat([attention_mask, torch.ones_like(attention_mask[:, :1])], dim=1)
-            return input_ids
-        cache = caching.DecodeCache()
+        cached = use_cache and caching.supports(self.model.arch) is None
         mask = torch.ones_like(input_ids) if attention_mask is None else attention_mask.to(input_ids.dtype)
         positions = (mask.cumsum(-1) - 1).clamp_min(0)
+        done = torch.zeros(input_ids.shape[0], dtype=torch.bool, device=input_ids.device)
+        fill = pad_token_id if pad_token_id is not None else (eos_token_id if eos_token_id is not None else 0)
+        cache = caching.DecodeCache() if cached else None
         new, new_positions, new_mask = input_ids, positions, mask
         for _ in range(max_new_tokens):
-            ctx = self.model(new, new_positions, new_mask.to(torch.int32), training=False, cache=cache)
-            nxt = ctx.heads[0].logits()[:, -1].float().argmax(-1, keepdim=True)
+            if cached:
+                ctx = self.model(new, new_positions, new_mask.to(torch.int32), training=False, cache=cache)
+                last = ctx.heads[0].logits()[:, -1].float()
+            else:
+                last = self(input_ids, attention_mask=mask).logits[:, -1]
+            nxt = self._next(last, do_sample, temperature, top_k, top_p, generator)
+            if eos_token_id is not None:
+                nxt = torch.where(done.unsqueeze(-1), torch.full_like(nxt, fill), nxt)
+                done = done | (nxt.squeeze(-1) == eos_token_id)
             input_ids = torch.cat([input_ids, nxt], dim=1)
+            mask = torch.cat([mask, torch.ones_like(mask[:, :1])], dim=1)
             new, new_positions, new_mask = nxt, positions[:, -1:] + 1, torch.ones_like(nxt)
             positions = torch.cat([positions, new_positions], dim=1)
+            if eos_token_id is not None and bool(done.all()):
+                break
         return input_ids

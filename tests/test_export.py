@@ -233,3 +233,21 @@ model = embed ([n r] [n f] [n a] [n f])^2 n head
     got, real = torch.cat(parts, dim=1), mask.bool()
     assert torch.allclose(got[real], whole[real], atol=5e-5), (got[real] - whole[real]).abs().max()
     assert "engram" in supports(compile("d_model=32\nvocab_size=64\nmodel = embed [rmsnorm engram(head_dim=8, table_size=64)] rmsnorm head\n", filename="h.bux"))
+
+
+def test_exported_model_samples_and_stops_at_the_end_token(tmp_path):
+    run, tr, folder = _trained(tmp_path, qk=", sinks=true")
+    out = export(folder, tmp_path / "hf", dtype="float32", echo=lambda *_: None)
+    hf = C.load_exported(out)
+    ids = torch.arange(6).reshape(1, 6) % 64
+    greedy = hf.generate(ids, max_new_tokens=5)
+    assert torch.equal(greedy, hf.generate(ids, max_new_tokens=5, use_cache=False))
+    assert torch.equal(greedy, hf.generate(ids, max_new_tokens=5, do_sample=True, top_k=1))          # top-1 sampling is greedy
+    g = lambda: torch.Generator().manual_seed(3)
+    a = hf.generate(ids, max_new_tokens=8, do_sample=True, temperature=1.5, top_p=0.9, generator=g())
+    b = hf.generate(ids, max_new_tokens=8, do_sample=True, temperature=1.5, top_p=0.9, generator=g())
+    assert torch.equal(a, b) and a.shape == (1, 14)
+    eos = int(greedy[0, 7])                                   # the second decoded token ends the row
+    stopped = hf.generate(ids, max_new_tokens=5, eos_token_id=eos, pad_token_id=63)
+    assert stopped.shape[1] <= 8 or (stopped[0, 8:] == 63).all()
+    assert stopped[0, :8].tolist() == greedy[0, :8].tolist() or eos in stopped[0, 6:8].tolist()
