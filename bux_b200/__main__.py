@@ -124,6 +124,37 @@ def main(argv=None) -> int:
         return 1
 
 
+def check_summary(report) -> list:
+    """What ``bux check`` prints for a file without mistakes: the width, the vocabulary and the
+    layers by type; for a run its budget, optimizer, schedule and data; for a sweep its axes
+    (``docs/language/tooling.md`` there: `bux check`). A file without a model is a module and
+    lists what it defines."""
+    from collections import Counter
+
+    from .lang import ir
+    from .lang.printer import config_to_source
+
+    if report.defines is not None:
+        return ["a module: it defines " + ", ".join(report.defines) + ", and no model"]
+    lines = []
+    arch, train = report.arch, report.train
+    if arch is not None:
+        kinds = Counter((l.config.fn if l.config.type == "act" else l.config.type) for l in ir.unrolled_layers(arch.graph))
+        lines.append(f"d_model={arch.d_model} vocab_size={arch.vocab_size} layers={sum(kinds.values())}")
+        lines.append("  ".join(f"{kind}×{n}" for kind, n in kinds.most_common()))
+    if train is not None:
+        tokens = train.steps * train.batch * train.seq_len
+        lines.append(f"{train.steps} steps × {train.batch} × {train.seq_len} tokens = {_si(tokens)} tokens")
+        lines.append(f"optimizer={config_to_source(train.optimizer)} schedule={config_to_source(train.schedule)}")
+        lines.append(f"data={config_to_source(train.data)}")
+    if report.axes:
+        axes = " × ".join(f"{a.where} ({' | '.join(str(o) for o in a.options)})" for a in report.axes)
+        lines.append(f"sweep: {report.runs} runs over {axes}")
+    for d in report.dimensions:
+        lines.append(f"search: {d.where} = {config_to_source(d.space)}")
+    return lines
+
+
 def _dispatch(args) -> int:
     cmd = args.command
     if cmd == "check":
@@ -137,7 +168,8 @@ def _dispatch(args) -> int:
         if report.errors:
             print(f"{len(report.errors)} error(s)", file=sys.stderr)
             return 1
-        print(f"{args.file}: ok, {report.runs} run(s)" if report.train is not None else f"{args.file}: ok")
+        for line in check_summary(report):
+            print(line)
         return 0
     if cmd == "plan":
         runs = _runs(args)

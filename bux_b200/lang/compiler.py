@@ -1249,6 +1249,7 @@ class Report:
     runs: int
     arch: Optional[ir.Architecture] = None
     train: Optional[T.TrainConfig] = None
+    defines: Optional[list] = None   # a module (a file without the entry): the names it defines
 
     @property
     def ok(self) -> bool:
@@ -1271,6 +1272,13 @@ def check(source: str, *, entry: str = "model", filename: str = "<string>",
 
     ev = Evaluator(program, report=report)
     arch = train = None
+    if entry not in ev.chain and not program.incomplete:
+        # a module: a piece that runs build on by name. Every definition is checked on its own.
+        ev.evaluate_all(report)
+        main = next((f for f in program.files if f.filename == filename), program.files[0] if program.files else None)
+        own = [st.name for layer in program.layers for st in layer
+               if main is None or main.start <= st.span.start <= main.stop]
+        return Report(errors, list(ev.axes.values()), list(ev.dims.values()), 0, defines=list(dict.fromkeys(own)))
     try:
         arch = _architecture(ev, entry)
     except BuxError as err:

@@ -299,3 +299,25 @@ def test_the_textmate_grammar_lists_every_builtin_and_matches_a_file():
     tap = next(r for r in grammar["repository"]["expression"]["patterns"] if r.get("name") == "variable.other.tap.bux")
     assert re.findall(tap["match"], _SRC) == ["@v", "@h", "$h!"]
     assert json.loads((folder / "template.json").read_text())["programArgs"]["default"] == "bux-lsp"
+
+
+def test_check_prints_the_summary_of_a_run_a_sweep_and_a_module(tmp_path, capsys):
+    from bux_b200.__main__ import main
+
+    smoke = str(Path(__file__).resolve().parent.parent / "examples" / "experiments" / "smoke.bux")
+    assert main(["check", smoke, "optimizer.lr = 1e-3 | 3e-3"]) == 0
+    assert capsys.readouterr().out.splitlines() == [
+        "d_model=64 vocab_size=512 layers=11",
+        "rmsnorm×5  gqa×2  gated_mlp×2  embed×1  head×1",
+        "50 steps × 8 × 64 tokens = 25.6k tokens",
+        "optimizer=adamw(lr=0.001) schedule=wsd(warmup=10)",
+        "data=synthetic()",
+        "sweep: 2 runs over optimizer.lr (1e-3 | 3e-3)"]
+    recipe = tmp_path / "recipe.bux"
+    recipe.write_text("optimizer = adamw(lr=1e-3)\nschedule = wsd(warmup=10)\nbudget = 100\nsteps = budget\n")
+    assert main(["check", str(recipe)]) == 0
+    assert capsys.readouterr().out.strip() == "a module: it defines optimizer, schedule, budget, steps, and no model"
+    recipe.write_text("optimizer = adamw(lr=1e-3, weight_dacay=0.1)\n")      # a module's definitions are still checked
+    assert main(["check", str(recipe)]) == 1
+    assert "did you mean 'weight_decay'" in capsys.readouterr().err
+    assert features.diagnostics("optimizer = adamw(lr=1e-3)\nsteps = 10\n") == []     # the editor takes a module too
