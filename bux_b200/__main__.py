@@ -177,14 +177,26 @@ def _dispatch(args) -> int:
         print(_table(("id", "params", "tokens", "tok/param", "flops/tok", "gpus", "params/gpu",
                       "optim/gpu", "bubble", "run"), plan_rows(runs)))
         return 0
-    if cmd == "fmt":
-        from .lang.printer import run_to_source
+    if cmd in ("fmt", "json"):
+        from .lang import BuxError, compile
+        from .lang.printer import run_to_source, to_source
 
-        print("\n".join(run_to_source(r) for r in _runs(args)), end="")
-        return 0
-    if cmd == "json":
-        for r in _runs(args):
-            print(r.model_dump_json(indent=1))
+        try:
+            runs = _runs(args)
+        except BuxError as err:
+            if "defines a model, not a run" not in err.message:
+                raise
+            # a model file: its architecture alone
+            path = Path(args.file)
+            arch = compile(path.read_text(), filename=str(path), entry=args.entry, overrides=args.overrides)
+            print(to_source(arch) if cmd == "fmt" else arch.model_dump_json(indent=2), end="" if cmd == "fmt" else "\n")
+            return 0
+        if cmd == "fmt":
+            print("\n".join(run_to_source(r) for r in runs), end="")
+        else:
+            import json as _json
+
+            print(_json.dumps([r.model_dump(mode="json") for r in runs], indent=2))
         return 0
     if cmd == "render":
         from .lang import BuxError, compile
