@@ -38,9 +38,11 @@ def _parser() -> argparse.ArgumentParser:
         if name in ("train", "launch"):
             s.add_argument("--device", default=None)
             s.add_argument("--quiet", action="store_true")
-    e = sub.add_parser("export", help="export a trained run for transformers / vLLM")
-    e.add_argument("run_dir")
+    e = sub.add_parser("export", help="export a trained run (or a file's model without weights) for transformers / vLLM")
+    e.add_argument("run_dir", help="a run's directory, or a .bux file")
     e.add_argument("out")
+    e.add_argument("overrides", nargs="*", help="with a file: statements that redefine the file's own")
+    e.add_argument("--entry", default="model")
     e.add_argument("--step", type=int, default=None)
     e.add_argument("--dtype", default="bfloat16")
     e.add_argument("--check", action="store_true")
@@ -241,6 +243,11 @@ def _dispatch(args) -> int:
     if cmd == "export":
         from .export import export
 
+        if str(args.run_dir).endswith(".bux") and Path(args.run_dir).is_file():
+            from .export import export_architecture
+
+            export_architecture(args.run_dir, args.out, args.overrides, args.entry, args.dtype)
+            return 0
         export(args.run_dir, args.out, step=args.step, dtype=args.dtype, check=args.check)
         return 0
     if cmd == "studio":

@@ -34,3 +34,23 @@ def export(run_dir, out, step: Optional[int] = None, dtype: str = "bfloat16", ch
         if not report.ok:
             raise SystemExit(1)
     return folder
+
+
+def export_architecture(file, out, overrides=(), entry: str = "model", dtype: str = "bfloat16", echo=print) -> Path:
+    """``bux export FILE.bux OUT``: the file's model without weights (`huggingface.save_architecture`)."""
+    from ..lang import compile
+    from . import huggingface
+
+    path = Path(file)
+    arch = compile(path.read_text(), filename=str(path), entry=entry, overrides=list(overrides))
+    dt = {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.float16}[dtype]
+    folder, params = huggingface.save_architecture(arch, out, dtype=dt, name=path.stem)
+    echo(f"{file}: {_si(params)} parameters exported to {folder}, without weights")
+    return folder
+
+
+def _si(n: int) -> str:
+    for unit, size in (("T", 1e12), ("B", 1e9), ("M", 1e6), ("k", 1e3)):
+        if n >= size:
+            return f"{n / size:.3g}{unit}"
+    return str(n)

@@ -46,18 +46,7 @@ def save(run, model, folder, dtype=torch.bfloat16, step=None, family: str = "aut
     if fam is not None:
         config, tensors = native.convert(fam, arch, W.tensors(model, dtype=dtype), dtype)
     else:
-        config = {
-            "model_type": "bux", "architectures": ["BuxForCausalLM"],
-            "auto_map": {"AutoConfig": "configuration_bux.BuxConfig",
-                         "AutoModelForCausalLM": "modeling_bux.BuxForCausalLM"},
-            "vocab_size": arch.vocab_size, "hidden_size": arch.d_model,
-            "num_hidden_layers": sum(1 for t in layer_types(arch) if t in native.MIXERS),
-            "layer_types": cache_types(arch), "bux_layer_types": layer_types(arch),
-            "tie_word_embeddings": any(getattr(l.config, "tied", False) for l in arch.layers()),
-            "torch_dtype": str(dtype).removeprefix("torch."),
-            "bux": {"architecture": json.loads(arch.model_dump_json()), "run": run.id, "name": run.name,
-                    "step": step, "dtype": str(dtype).removeprefix("torch.")},
-        }
+        config = bux_config(arch, dtype, {"run": run.id, "name": run.name, "step": step})
         for name in ("configuration_bux.py", "modeling_bux.py"):
             shutil.copy(HERE / "hf" / name, folder / name)
         vendor_runtime(folder)
@@ -66,6 +55,48 @@ def save(run, model, folder, dtype=torch.bfloat16, step=None, family: str = "aut
               metadata={"format": "pt"})
     (folder / "README.md").write_text(card(run, step, fam))
     return folder
+
+
+def save_architecture(arch, folder, dtype=torch.bfloat16, name: str = "model", family: str = "auto") -> tuple:
+    """Write `arch` without weights: its ``config.json`` (and, in the bux format, its code), but
+    no ``model.safetensors`` (one an earlier export left there is removed). A serving stack can
+    run it on random weights to time an architecture before anything is trained. The model is
+    only ever built on the ``meta`` device (shapes, no memory), so a hundred billion parameters
+    export in seconds. Returns (folder, number of parameters)."""
+    from ..models import Model
+
+    folder = Path(folder)
+    folder.mkdir(parents=True, exist_ok=True)
+    with torch.device("meta"):
+        model = Model(arch, dtype=dtype)
+    params = model.num_params()
+    fam = native.detect(arch) if family == "auto" else (None if family == "bux" else family)
+    if fam is not None:
+        config, _ = native.convert(fam, arch, W.tensors(model, dtype=dtype), dtype)
+    else:
+        config = bux_config(arch, dtype, {"run": None, "name": name, "step": None})
+        for file in ("configuration_bux.py", "modeling_bux.py"):
+            shutil.copy(HERE / "hf" / file, folder / file)
+        vendor_runtime(folder)
+    (folder / "config.json").write_text(json.dumps(config, indent=1))
+    (folder / "model.safetensors").unlink(missing_ok=True)
+    return folder, params
+
+
+def bux_config(arch, dtype, origin: dict) -> dict:
+    """``config.json`` of the bux format: what transformers and serving stacks read, and the IR."""
+    return {
+        "model_type": "bux", "architectures": ["BuxForCausalLM"],
+        "auto_map": {"AutoConfig": "configuration_bux.BuxConfig",
+                     "AutoModelForCausalLM": "modeling_bux.BuxForCausalLM"},
+        "vocab_size": arch.vocab_size, "hidden_size": arch.d_model,
+        "num_hidden_layers": sum(1 for t in layer_types(arch) if t in native.MIXERS),
+        "layer_types": cache_types(arch), "bux_layer_types": layer_types(arch),
+        "tie_word_embeddings": any(getattr(l.config, "tied", False) for l in arch.layers()),
+        "torch_dtype": str(dtype).removeprefix("torch."),
+        "bux": {"architecture": json.loads(arch.model_dump_json()), **origin,
+                "dtype": str(dtype).removeprefix("torch.")},
+    }
 
 
 def vendor_runtime(folder: Path) -> Path:

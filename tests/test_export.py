@@ -251,3 +251,25 @@ def test_exported_model_samples_and_stops_at_the_end_token(tmp_path):
     stopped = hf.generate(ids, max_new_tokens=5, eos_token_id=eos, pad_token_id=63)
     assert stopped.shape[1] <= 8 or (stopped[0, 8:] == 63).all()
     assert stopped[0, :8].tolist() == greedy[0, :8].tolist() or eos in stopped[0, 6:8].tolist()
+
+
+def test_a_file_exports_its_model_without_weights(tmp_path, capsys):
+    """``bux export FILE.bux OUT``: config (and code), no weights; the model is only built on the
+    meta device, so a model far larger than this machine's memory exports."""
+    from pathlib import Path
+
+    from bux_b200.__main__ import main
+
+    root = Path(__file__).resolve().parent.parent / "examples" / "architectures"
+    out = tmp_path / "llama"
+    (out).mkdir()
+    (out / "model.safetensors").write_bytes(b"left by an earlier export")
+    assert main(["export", str(root / "llama3_70b.bux"), str(out)]) == 0
+    assert "70.6B parameters exported" in capsys.readouterr().out and "without weights" 
+    cfg = json.loads((out / "config.json").read_text())
+    assert cfg["model_type"] == "llama" and cfg["num_hidden_layers"] == 80 and not (out / "model.safetensors").exists()
+    out = tmp_path / "hybrid"
+    assert main(["export", str(root / "hybrid_gdn.bux"), str(out), "d_model = 512", "--dtype", "float32"]) == 0
+    cfg = json.loads((out / "config.json").read_text())
+    assert cfg["model_type"] == "bux" and cfg["hidden_size"] == 512 and cfg["bux"]["run"] is None and cfg["torch_dtype"] == "float32"
+    assert (out / "modeling_bux.py").exists() and (out / "bux_runtime" / "models" / "cache.py").exists()
