@@ -11,6 +11,20 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
 
 
+def pytest_collection_modifyitems(config, items):
+    """``BUX_SHARD=i/n`` keeps the tests whose id hashes to shard i of n, so that n runners split
+    the suite between them (every test lands in exactly one shard)."""
+    shard = os.environ.get("BUX_SHARD")
+    if not shard:
+        return
+    import zlib
+
+    i, n = (int(x) for x in shard.split("/"))
+    keep = [item for item in items if zlib.crc32(item.nodeid.encode()) % n == i]
+    config.hook.pytest_deselected(items=[item for item in items if item not in keep])
+    items[:] = keep
+
+
 @pytest.fixture
 def cuda():
     import torch
