@@ -206,7 +206,7 @@ FIELDS = {
     "norm": {
         "eps": "Added to the variance before the square root.", "affine": "Learn a gain per channel.",
         "bias": "Learn a bias per channel.", "zero_centered": "Store the gain as `1 + w` with `w` initialised to zero.",
-        "gain_init": "Initial gain.", "scale_input": "Multiply the input by `sqrt(width)` first.",
+        "gain_init": "Initial gain.", "scale_input": "Multiply by the gain before normalising, `norm(w * x)`, instead of after.",
     },
     "mlp": {
         "intermediate_size": "Hidden width.", "activation": "The nonlinearity (of the gate, for `gated_mlp`).",
@@ -377,6 +377,232 @@ FIELDS.update({
             "multivariate": "Model the dimensions jointly."},
     "wandb": {"project": "Project name.", "entity": "Team or user.", "group": "Group of the run.", "tags": "Tags of the run.", "mode": "`online`, `offline` or `disabled`."},
 })
+
+# ---- notes checked field by field against what the layers compute
+FIELDS["attention"].update({
+    "output_norm": "A norm of each head's output, before the gate.",
+    "gated": "An elementwise gate `act(W x)` from the layer's input on each head's output, before the output projection.",
+    "gate_input_rank": "The gate's projection of the input made low-rank (`silu(x W_d) W_u`, `W_d` of this many columns per head).",
+    "gate_output_rank": "The gate also reads the head's own output through a low-rank map of this rank, added to its logits before the activation.",
+    "gate_cross_head": "A second gate, one value per head, from all the heads' outputs together; it multiplies the first.",
+    "log_scale": "Logits times `1 + log_scale * ln(max(n / log_scale_floor, 1))` at the query's position `n` (from 1), so attention stays sharp at long range.",
+    "log_scale_floor": "Positions up to this one keep their logits' scale.",
+})
+FIELDS["gqa"].update({
+    "bias": "Biases on the projections of the input: q, k, v and the gate.",
+    "output_bias": "A bias on the output projection; `none` follows `bias`.",
+    "power_scale": "Queries times `(1 + n / power_scale_length) ** power_scale` at their position `n` (from 1): keeps attention without RoPE sharp at long range.",
+    "power_scale_length": "The position at which the queries' scale reaches `2 ** power_scale`.",
+    "kv_conv_size": "A causal depthwise convolution of this many taps on keys and values, added to them: `k + conv(k)`.",
+    "exclusive": "Exclusive self-attention: each head's output less its part along the query's own value, `y - (y . v) v / (v . v)`, before the output's norm and gate; `learned` scales what is taken off by a learned factor.",
+    "k_eq_v": "Values come from the key projection (no v projection): each head's projected key, normalised without a gain and not rotated.",
+    "differential": "Differential attention: twice the query heads, each output `a1 - sigmoid(x W) a2` of a pair of heads.",
+    "paired": "Paired-head attention: two query heads (and two key/value heads) are interleaved along the sequence into one of twice the length, so a query sees both heads' keys.",
+    "mimetic_vo": "Mimetic initialisation of V and O at this beta: their kernels start as blocks of `+sqrt(beta)` and `-sqrt(beta)` identities.",
+    "mimetic_noise": "Standard deviation of the noise on V and O under `mimetic_vo`.",
+    "qk_norm_all_heads": "`qk_norm` over all the heads' channels together (one norm of the queries, one of the keys), before they split into heads.",
+})
+FIELDS["mla"].update({"rope": "On the decoupled `qk_rope_head_dim` part; `none` rotates nothing.",
+                      "q_lora_rank": "Width of the latent the queries come from; `none` for a full-rank query projection."})
+FIELDS["csa"].update({
+    "head_dim": "Width of a query head and of a latent (the heads share the latents as their one key/value head).",
+    "compress_ratio": "Tokens pooled into one compressed latent; `none` keeps the window only.",
+    "latent_norm": "Norm of the query latent, the latents, the compressed ones and the indexer's keys.",
+    "o_lora_rank": "Grouped low-rank output projection: `o_groups` groups of heads, each projected to this rank, then mixed back to the width; `none` for one dense projection.",
+})
+FIELDS["mlp"].update({
+    "dropout": "Dropout rate of the output, in training.",
+    "limit": "Clamped GLU: the gate's input is capped at `limit`, the up branch at `+-limit`.",
+    "up_softcap": "Soft cap of the up branch, `cap * tanh(up / cap)`.",
+    "up_offset": "Added to a gated MLP's up branch after it is clipped (gpt-oss: `up + 1`).",
+})
+FIELDS["moe"].update({
+    "num_shared_experts": "Experts every token goes through, run as one MLP of that many times the shared expert's hidden width.",
+    "router": "How logits become scores: a `softmax` over the experts, a `sigmoid` each, or `sqrt(softplus(.))` each.",
+    "router_bias": "A learned bias on the router's logits (unlike `aux_free`'s, which only steers the choice).",
+    "routed_scaling_factor": "Multiplies the picked weights.",
+    "random_logits": "For benchmarks: a training forward routes by random logits, so every expert takes an even share of the picks and a capacity drops few.",
+    "num_groups": "Group-limited routing: the experts are in this many groups, each scored by the sum of its two best experts.",
+    "top_k_groups": "Groups each token picks its experts from.",
+    "load_balancing": "`aux_loss`: a balance loss. `aux_free`: a bias per expert on the scores that pick the top-k (not on the weights), moved after every step toward even loads. `smebu`: that move with momentum and a tanh soft clamp.",
+    "bias_update_rate": "How far the balancing bias moves per training step (`smebu`: at most).",
+    "center_bias": "`aux_free`: subtract the bias's mean after every move (`smebu` always does).",
+    "bias_softclamp": "`smebu`'s kappa: how soon the tanh of the load's deviation saturates.",
+    "bias_momentum": "`smebu`'s beta: the decay of the running average of the moves.",
+    "aux_loss_coef": "Weight of each layer's balance loss `E * sum_e f_e P_e` (share of picks times mean score per expert).",
+    "latent_size": "LatentMoE: routed experts run in a narrower space of this width between a down and an up projection; the router and shared experts see the full width.",
+    "latent_input_norm": "LatentMoE: a norm of the tokens after the down projection.",
+    "latent_output_norm": "A norm of the routed sum, before LatentMoE's up projection.",
+    "expert_norm": "A norm of each routed expert's output.",
+    "shared_expert_sink": "The shared experts are weighted by the router too, normalised with the top-k; otherwise they are added with weight 1.",
+    "num_zero_experts": "Zero-computation experts: identity experts the router scores after the routed ones; a pick of one passes the token through as it is, times its weight, and runs no FFN.",
+    "ffn_experts_per_token": "The FFN experts a token goes through on average, which the balancing steers toward; `none` is what uniform picks give.",
+})
+FIELDS["recurrent"].update({
+    "head_dim": "Width of a query and a key head: the state's rows.",
+    "v_head_dim": "Width of a value head: the state's columns; `none` is `head_dim`.",
+    "num_v_heads": "Value heads; with more of them than query/key heads, each query/key head serves a group of them.",
+    "conv_size": "Taps of a causal depthwise convolution on q, k and v (each then SiLU'd); `none` for none.",
+    "output_gate": "Activation of a gate on the output, after its norm and before the output projection; `none` for no gate.",
+    "gate_rank": "Rank of the decay's projection.",
+    "output_gate_rank": "Rank of the output gate's projection; `none` for full rank.",
+    "gate_lower_bound": "Bounded decay `lower_bound * sigmoid(.)` in `(lower_bound, 0)` instead of `-exp(A) * softplus(.)`; `none`: unbounded.",
+    "negative_eigenvalues": "The erase gate times 2, in (0, 2), so the state's transition may have negative eigenvalues.",
+})
+FIELDS["rwkv7"].update({"gate_rank": "Rank of the output gate's projection.", "output_gate": "The output gate is `act(x G1) G2` with this activation between.",
+                        "conv_size": "`none` only: RWKV-7 shifts tokens instead of convolving.",
+                        "norm_eps": "Epsilon of each head's output layer norm, times the value head's width.", "v_rank": "Rank of the value residual's mix (with the `v` port)."})
+FIELDS["mamba2"].update({"state_size": "State dims of each inner channel (the papers' N).", "num_heads": "`none` is `expand * width // head_dim`.",
+                         "num_groups": "Groups that share B and C, as key/value heads are shared in GQA."})
+FIELDS["mamba"].update({"state_size": "State dims of each inner channel (the papers' N).", "dt_min": "The time steps start log-uniform in `[dt_min, dt_max]`.",
+                        "dt_max": "The largest time step at the start."})
+FIELDS["conv"].update({"size": "Taps: each position sees itself and the `size - 1` before it."})
+FIELDS["short_conv"].update({"bias": "Biases on the projections and the convolution."})
+
+FIELDS["engram"].update({"norm": "Norm of the stream (the query), of the keys, and of the memory's output before the convolution.",
+                         "conv_size": "Taps of the causal convolution over the memory's output, zero-initialised and dilated by `max_ngram_size`; `none` for none.",
+                         "vocab_classes": "Hash each token's class (of this many) instead of its id: id `i` is class `i mod vocab_classes`; `none`: the ids.",
+                         "boundary_token": "N-grams do not reach back past this token (an end-of-text token, say); `none`: no boundary.",
+                         "table_size": "Rows of each head's table: the least prime at or above this that no earlier head has taken.",
+                         "head_dim": "Width of a table row.", "num_heads": "Hash heads per n-gram size, each with a table of its own."})
+FIELDS["doc_copy"].update({"gain": "The copy vector's weight at this site, learned from here.", "lengths": "The context lengths that can match, shortest first.",
+                           "counts": "How many earlier occurrences of a matched context the buckets tell apart (1, 2 and 3 or more by default)."})
+FIELDS["copy_pointer"].update({"token": "The vocabulary row of the `<copy>` token, one that no real token is; `none`: the last row.",
+                               "window": "How far back the pointer looks, in tokens; `none`: the whole document."})
+FIELDS["rope"].update({"base": "Theta, the base of the frequencies (Llama 3: 500000).",
+                       "fraction": "Partial rotary: only this share of each head's dims is rotated, the first ones, in whole pairs."})
+FIELDS["pi"].update({"factor": "How many times longer the context gets: frequencies are divided by it."})
+FIELDS["yarn"].update({"factor": "How many times longer than `original_max_len` the context gets.",
+                       "beta_fast": "Pairs that turn more times than this over the original length keep their frequency.",
+                       "beta_slow": "Pairs that turn fewer times than this have their frequency divided by `factor`.",
+                       "attention_factor": "YaRN's temperature (q . k is scaled by its square); `none` is `0.1 * ln(factor) + 1`; 1 disables it.",
+                       "attention_factor_on": "`rotary` multiplies cos and sin by it (the rotated dims only); `softmax` multiplies the softmax scale by its square (all dims)."})
+FIELDS["llama3"].update({"factor": "What the slowest pairs' frequencies are divided by.",
+                         "low_freq_factor": "Pairs that turn fewer times than this over the original length are divided by `factor`.",
+                         "high_freq_factor": "Pairs that turn more times than this keep their frequency; between the two the scaling is blended."})
+FIELDS["relbias"].update({"rank": "Width of the table's entries and of each head's projection.", "extent": "Offsets (from 0) that have a bias; farther keys get none."})
+FIELDS["indexer"].update({
+    "top_k": "Keys each query keeps (in whole blocks, with `block_size`).",
+    "block_size": "Pick whole blocks of this many keys (`top_k` keys in total), scored as `pool` says.",
+    "pool": "How a block scores: `mean` pools its keys into one, which a query scores once the block is complete (its own unfinished block is kept beside the picks); `max` is its best key's score.",
+    "per_group": "A pick for each key/value head's group of query heads, by an indexer head of its own; else one pick for all heads.",
+    "relu": "ReLU on each head's dot products; else the plain ones.", "weighted": "Learned per-head score weights; else a plain sum.",
+    "norm": "Norm of each query head and of the keys (after block pooling); `none`: no query norm and the layer's own key norm.",
+    "rope_layout": "How the indexer pairs RoPE dims when its keys are the tokens, whatever the layer's own layout.",
+    "candidate_block_size": "What a `candidates` port exports: the best `candidate_top_k` blocks of this many keys, each scored by its best key.",
+    "candidate_top_k": "Blocks in the candidate pool.",
+    "loss_weight": "Weight of the indexer's loss, its only training signal: the KL divergence from the attention over the kept keys to the softmax of its scores. 0 leaves it untrained.",
+    "loss_over": "Whose attention the loss distils: `own`, its layer's; `served`, also that of every layer that reads its picks through the `index` port.",
+})
+FIELDS["hc"].update({
+    "expansion": "Copies of the stream, 2 or more: one is the plain residual stream.",
+    "dynamic": "Coefficients that depend on the stream (a projection that starts at 0) on top of static ones; else static ones alone.",
+    "pre_bias": "`mhc`: the static read logits start at this on the k-th branch's own stream and at minus it on the others.",
+    "post_bias": "As `pre_bias`, for `mhc`'s static write logits.",
+    "res_bias": "`mhc`: the static mixing logits off the diagonal (0 on it): the mixing starts as the identity to within `e^res_bias`.",
+    "single_pass": "A branch reads with the coefficients the branch before it computed.",
+    "norm_eps": "Epsilon of the norm before the dynamic coefficients."})
+FIELDS["gr"].update({"rank": "Rank of the read gate.", "norm_eps": "Epsilon of the streams' RMS norm."})
+FIELDS["attnres"].update({"block_size": "Branch outputs summed into one source; `none`: each is its own source.", "norm_eps": "Epsilon of the keys' RMS norm."})
+FIELDS["msar"].update({"block_size": "Branch outputs summed into one source; `none`: each is its own source.",
+                       "kernel_sizes": "Taps of each stream's convolution after the first (which is the source as it is): 4, 8 and 12 make four streams.",
+                       "norm_eps": "Epsilon of the keys' and the mixer's RMS norms."})
+FIELDS["vpgate"].update({"temperature": "Divides the learned `g` inside the gate's sigmoid.", "eps": "`a = sqrt(max(1 - b^2, eps))`: the stream is never cut off."})
+FIELDS["init"].update({"embed": "How the embedding tables start (the tokens' and the learned positions'; a tied head reads the tokens'); `none`: as the rest.",
+                       "head": "How an untied head starts; `none`: as the rest.",
+                       "out": "How the projections back to the stream's width start (attention's and the mixers' outputs, MLPs' and experts' down); `none`: as the rest."})
+FIELDS["fan"].update({"scale": "The variance times the fan.", "distribution": "What it draws from at that variance: a normal `truncated` at 2 standard deviations, a `gaussian`, or a `uniform`."})
+FIELDS["normal"].update({"std": "The standard deviation, before truncation.", "truncate": "Values farther than this many standard deviations from 0 are drawn again; `none`: none are."})
+
+FIELDS["documents"].update({"path": "A glob of parquet (or JSON-lines) files, relative to the working directory.",
+                            "split": "The documents whose content hash falls in `[start, end)`: `(0.99, 1)` is a 1% held out."})
+FIELDS["text"].update({"column": "The column that holds each document's text."})
+FIELDS["chat"].update({"column": "The column that holds each conversation's messages.",
+                       "train_on": "`assistant`: every reply; `last`: the last reply alone; `all`: every token, prompts and template too."})
+FIELDS["tokens"].update({"path": "A glob of shards of raw token ids.", "header": "Bytes before the tokens in every shard."})
+FIELDS["tokenizer"].update({"bos": "The token a document starts with, where its source sets `bos`.", "eos": "The token a document ends with, where its source sets `eos`.",
+                            "added": "Special tokens appended after the vocabulary, for a chat template the tokenizer lacks."})
+FIELDS["packing"].update({"doc_mask": "Positions restart at every document and attention stays within it.", "chunk": "About how many tokens of documents are packed together (and make one part file).",
+                          "long": "A document longer than a row: `drop`ped, `truncate`d to a row, or `split` into pieces that fill rows.",
+                          "max_docs": "The most documents (and pieces of them) in a row; `none`: as many as fit.", "sort": "Longest first; `false` keeps the shuffled order (online best fit)."})
+FIELDS["adamw"].update({"weight_decay": "Decoupled decay of the matrices, times the learning rate.",
+                        "cautious_weight_decay": "Decay only the entries whose update has the parameter's sign (or is 0), so decay never pulls against the step."})
+FIELDS["muon"].update({
+    "momentum": "Decay of the gradients' average that is orthogonalised.", "nesterov": "Nesterov's look-ahead.",
+    "ns_coefficients": "The iteration's quintics by name: one set for every iteration (`jordan`), or one per iteration (`polar_express`).",
+    "ns_algorithm": "How it iterates: `standard`, or `gram` on the Gram matrix of each matrix's shorter side (fewer products the less square a matrix is).",
+    "ns_restarts": "The iterations after which `gram` restarts from the matrix so far; `none`: after the second and every third after it.",
+    "ns_dtype": "What Newton-Schulz runs in, and what the updates move between devices in.",
+    "consistent_rms": "Updates scaled to this RMS, as AdamW's roughly are, so one learning rate suits both; `none`: scaled by `sqrt(max(1, fan_out / fan_in))`.",
+    "adam": "The AdamW of everything Muon does not take (embeddings, heads, norms, scalars); `none`: `adamw(lr=lr)`."})
+FIELDS["normuon"].update({"b2": "Decay of each neuron's mean-square average.", "eps": "Added to that average's root."})
+FIELDS["ema"].update({"window": "The steps it averages, the run's last (a number, or a share of the steps below 1); a step's weights join at the rate `2 / (window + 1)`.",
+                      "blend": "How much of the average the run ends on: `last + blend * (average - last)`; 1 ends on the average alone."})
+FIELDS["schedule"].update({"warmup": "Steps of linear warm-up, or a share of the steps below 1.", "final": "The multiplier at the last step: a fraction of the peak."})
+FIELDS["wsd"].update({"decay": "The share of the steps the cool-down takes."})
+FIELDS["cosine"].update({"horizon": "The share of the steps at which the cosine reaches `final`: above 1 the run stops before it does, below 1 it holds there."})
+FIELDS["power"].update({"a": "The power law's amplitude, for a batch of one row.", "b": "Its exponent, of the tokens trained.", "decay": "The share of the steps the cool-down takes."})
+FIELDS["multistep"].update({"at": "The shares of the steps at which the rate drops, in order.", "factor": "What each drop multiplies the rate by."})
+FIELDS["piecewise"].update({"pieces": "The pieces in order, each ending later than the one before; the last at 1."})
+FIELDS["piece"].update({"to": "The multiplier it ends at; `none` holds where it starts.", "shape": "How it gets there; `constant` is there at once."})
+FIELDS["phase"].update({"at": "The step it starts at, or a share of the steps (0.9 starts the last tenth).", "seq_len": "Tokens per row; `none`: as before.",
+                        "batch": "Rows per step; `none`: as before.", "data": "A source or a mixture; `none`: as before.",
+                        "rope_scaling": "The RoPE scaling of full-attention layers from then on.", "rope_base": "The RoPE base of full-attention layers from then on (raised for long context)."})
+FIELDS["ramp"].update({"start": "Rows per step at the first step.", "steps": "The steps it takes to reach the run's batch.", "multiple": "The batch sizes it takes are multiples of this; `none`: of `start`."})
+FIELDS["loss"].update({"z": "Weight of the z-loss, `log(Z)^2` of the first head.", "mtp": "Weight of the mean loss of the heads that predict further ahead.",
+                       "prefix": "The first head also predicts each target's prefix token, as `prefix(...)` says; `none`: not."})
+FIELDS["eval"].update({"name": "What its metrics' names start with (`eval_loss`, `eval_bpb`).", "data": "A source or a mixture, as `data` takes.",
+                       "batches": "Batches an evaluation reads, the same ones each time.",
+                       "positions": "Where buckets of targets by position in their document start, after the first at 0: `[2048, 8192]` also logs `..._0`, `..._2k`, `..._8k`."})
+FIELDS["wandb"].update({"group": "`none`: the file's name, which a sweep's runs share.", "entity": "The team or user it is under; `none`: your default.",
+                        "mode": "`online`: as it trains; `offline`: into the run's directory, to sync later; `disabled`: nowhere; `none`: as `WANDB_MODE` says."})
+FIELDS["observe"].update({"every": "Steps between the steps that observe the model.", "histograms": "Take histograms of the stream and the gradients too."})
+FIELDS["profile"].update({"start": "The step after which the trace starts.", "steps": "The steps it traces.", "options": "More flags for nsys or ncu, as its command line writes them."})
+FIELDS["precision"].update({
+    "compute": "The dtype the forward and backward passes run in.",
+    "matmuls": "The format the projections inside blocks multiply in: `compute`, `mxfp8`, `mxfp8_2d` or `nvfp4`.",
+    "roles": "A format by the kind of projection (`roles(...)`).",
+    "first": "The residual branches outside any other at the start of the model that multiply in `compute`: a number of them, or a share (rounded up).",
+    "last": "As `first`, the last ones before the first head.", "passes": "The GEMMs (fprop, dgrad, wgrad) that multiply in the format.",
+    "eval": "Evaluation multiplies as training does, or in `compute`.",
+    "moments": "The dtype the optimizer's moments are kept in between steps (they update in float32).",
+    "reduce": "The dtype gradients are summed over the ranks in: `compute`, or `float32`.",
+    "dispatch": "What the expert exchange sends tokens to their experts in: `compute`, or MXFP8; what comes back, and gradients, go in `compute`."})
+FIELDS["roles"].update({"q": "Attention's queries and gate (gqa, mla, csa, the indexer); `none` follows `precision.matmuls`.", "kv": "Attention's keys and values.",
+                        "o": "Attention's output projection.", "mlp": "MLPs, the shared experts' too.",
+                        "experts": "The routed experts' grouped GEMMs: `compute`, `mxfp8` or `mxfp8_2d`; `none` is `matmuls` where it is one of those, else `compute`.",
+                        "latent": "LatentMoE's projections to and from its latent.", "recurrence": "The recurrent mixers' projections, but the output.",
+                        "recurrence_out": "The recurrent mixers' output projection.", "mtp": "`nextn`'s projection, and every branch after the first head."})
+FIELDS["switch"].update({"passes": "The GEMMs in the format after it; `[]` is none."})
+FIELDS["mesh"].update({"data": "Copies of the model; `none`: the devices that are left.", "fsdp": "Devices that split parameters (and rows of the batch).",
+                       "context": "Devices a row's positions split over.", "expert": "Devices the routed experts split over (and rows of the batch).",
+                       "tensor": "Devices heads, hidden units and the vocabulary split over."})
+FIELDS["layout"].update({"seq": "Positions, inside a layer. " + _AXES, "stream": "Positions of the residual stream, between branches (sequence parallelism). " + _AXES,
+                         "embed": "The model's width. " + _AXES, "latent": "Low-rank bottlenecks (MLA, LatentMoE). " + _AXES,
+                         "layers": "The stacked passes of a repeat run as a loop. " + _AXES, "stages": "The passes of a pipelined repeat, a share per stage. " + _AXES,
+                         "fsdp": "What sharding splits a parameter's first dimension over: the axes that copy dense parameters, but `data` (which HSDP keeps as copies)."})
+FIELDS["remat"].update({"save": "Kept on the device for the backward: `attention`, `recurrence`, ...", "offload": "Moved to the host's memory until the backward reads them.",
+                        "first": "The passes of each repeat it recomputes, from the first; the rest keep everything. `none`: every pass."})
+FIELDS["methods"].update({
+    "attention": "The attention path: `auto` (the kernels where they take the call); over `context`: `ulysses`, `gathered` or `ring`.",
+    "capacity": "The picks an expert rank takes from each peer, as a multiple of its even share; what does not fit is dropped (the `dropped` metric).",
+    "moe_chunks": "The slices of each rank's tokens that expert parallelism sends one after another, so one's exchange runs beside another's experts.",
+    "recurrence": "The linear recurrences: `scan`, all of a row's positions on each rank; over `context`, each rank's positions continue from the state the ranks before pass on.",
+    "states": "What a chunked recurrence's backward reads of its chunks' states: `keep`, from the forward, or `recompute`, from its inputs (less memory, more time).",
+    "repeat": "A repeat's passes: `unroll`, a module each, run in a row.", "rounds": "Times a circular pipeline sends a microbatch round.",
+    "stages": "The passes of the pipelined repeat each stage runs, first to last; `none`: the split that balances the stages.",
+    "orthogonalize": "How Muon reaches whole matrices under sharding: `gather`, each whole on every rank that holds a part; `owner`, each whole on one rank.",
+    "loss": "How the loss takes a head's logits: `chunks`, a chunk of positions at a time, never all of them; `logits`, whole.",
+    "microbatches": "The microbatches a step takes its batch in, adding up their gradients; under a pipeline, those it sends through its stages.",
+    "gather": "Where a step runs its layers more than once, sharded parameters are gathered once a `step`, or as each `layer` runs (one layer's held at a time).",
+    "accumulate": "How microbatch gradients add up: `unreduced`, each rank's own, reduced once a step; `reduced`, every microbatch; `auto` chooses.",
+    "donate": "A step's new state takes the old one's memory."})
+FIELDS["compiler"].update({"reductions": "Where the step's gradient reductions start: `early`, each as its gradient is computed, or after the backward."})
+FIELDS["choice"].update({"options": "The options' names, or the options as written: `swish`, `gelu`."})
+FIELDS["tpe"].update({"startup": "Quasi-random trials before the densities propose.", "candidates": "Points drawn from the best trials' density, to pick from.",
+                      "gamma": "The share of the trials that count as the best.", "multivariate": "One density over every dimension (it sees how they interact), or one each."})
+FIELDS["gp"].update({"startup": "Quasi-random trials before the GP proposes.", "acquisition": "What the next point maximises: expected improvement in logs (`log_ei`), or the upper confidence bound (`ucb`).",
+                     "beta": "`ucb`'s weight of the deviation: mean + beta * deviation."})
 
 TRAIN_FIELDS = {
     "data": "What the model trains on: `text(...)`, `chat(...)`, `tokens(...)`, `synthetic`, or a weighted mixture.",

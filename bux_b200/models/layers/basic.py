@@ -86,12 +86,16 @@ class Norm(nn.Module):
         init = 0.0 if c.zero_centered else c.gain_init
         self.scale = nn.Parameter(torch.full((width,), float(init))) if c.affine else None
         self.bias = nn.Parameter(torch.zeros(width)) if c.bias else None
-        self.scale_input = math.sqrt(width) if c.scale_input else None
 
     def forward(self, x, ctx: Optional[Context] = None):
         c = self.c
-        if self.scale_input is not None:
-            x = x * self.scale_input
+        if c.scale_input and self.scale is not None:
+            # the gain goes on before the statistics, norm(w * x), and not after
+            # (``architecture/layers/norm.py:59-67`` there)
+            gain = (1.0 + self.scale.float()) if c.zero_centered else self.scale.float()
+            x = (x.float() * gain).to(x.dtype)
+            y = ref.rmsnorm(x, None, c.eps) if c.type == "rmsnorm" else ref.layernorm(x, None, None, c.eps)
+            return y if self.bias is None else y + self.bias.to(y.dtype)
         if c.type == "rmsnorm":
             y = ops.rmsnorm(x, self.scale, c.eps, c.zero_centered)
             return y if self.bias is None else y + self.bias.to(y.dtype)

@@ -317,3 +317,26 @@ def test_indexer_blocks_stop_at_document_boundaries_and_train():
         tr = _train(f"gqa(num_heads=2, num_kv_heads=1, rope=rope(), indexer={cfg})")
         ctx = tr.model(torch.randint(0, 64, (2, 32)), torch.arange(32).expand(2, 32), None, training=True)
         assert torch.isfinite(ctx.losses["indexer_loss"])
+
+
+def test_norm_with_scale_input_puts_the_gain_before_the_statistics():
+    """``rmsnorm(scale_input=true)``: norm(w * x), not norm(x) * w (reference: ``architecture/layers/norm.py:59-67``)."""
+    import torch
+
+    from bux_b200.config import layers as L
+    from bux_b200.models.layers.basic import Norm
+
+    torch.manual_seed(0)
+    x = torch.randn(2, 5, 16)
+    for kind in ("rmsnorm", "layernorm"):
+        for zero_centered in (False, True):
+            n = Norm(L.NormalizationConfig(type=kind, scale_input=True, zero_centered=zero_centered, bias=True), 16)
+            with torch.no_grad():
+                n.scale.copy_(torch.rand(16) + 0.5)
+                n.bias.copy_(torch.randn(16))
+            gain = 1 + n.scale if zero_centered else n.scale
+            y = (x * gain).float()
+            if kind == "layernorm":
+                y = y - y.mean(-1, keepdim=True)
+            want = y * torch.rsqrt(y.square().mean(-1, keepdim=True) + 1e-6) + n.bias
+            assert torch.allclose(n(x), want, atol=1e-5), (kind, zero_centered)
