@@ -119,7 +119,7 @@ def test_hover_says_what_a_name_is():
 
     gqa = text("gqa(")
     assert gqa.startswith("**gqa** — layer") and "`num_kv_heads: int" in gqa and "Key/value heads" in gqa
-    assert "`base: float = 10000.0`" in text("base=") and "period" in text("base=")       # a dotted class's field
+    assert "`base: float = 10000.0`" in text("base=") and "Theta" in text("base=")       # a dotted class's field
     assert "sliding_window_size" in text("sliding_window_size=128") and "most recent keys" in text("sliding_window_size=128")
     use = text("local)")                                         # a use of a definition
     assert "local = attn(sliding_window_size=128)" in use and "evaluates to `gqa(" in use and "a `gqa`" in use
