@@ -241,18 +241,26 @@ class MLP(nn.Module):
         if self.gated:
             h = self.gate_up(x, ctx)
             if c.up_softcap is not None:
+                # the up branch is clipped to +-limit, then soft-capped; the gate is capped from
+                # above only (``architecture/layers/mlp.py:28-35`` there)
                 f = getattr(self, "f_local", c.intermediate_size)
-                up = c.up_softcap * torch.tanh(h[..., f:].float() / c.up_softcap)
+                up = h[..., f:].float()
+                if c.limit is not None:
+                    up = up.clamp(-c.limit, c.limit)
+                up = c.up_softcap * torch.tanh(up / c.up_softcap)
                 h = torch.cat((h[..., :f], up.to(h.dtype)), dim=-1)
             a = ops.glu(h, c.activation, None, c.limit, c.up_offset)
         else:
-            h = self.up(x, ctx)
+            h = self.up(x, ctx).float()
             if c.limit is not None:
-                h = h.clamp(max=c.limit)
-            a = ref.activation(h.float(), c.activation).to(h.dtype)
-        if c.dropout and ctx is not None and ctx.training:
-            a = nn.functional.dropout(a, c.dropout)
-        return self.down(a, ctx)
+                h = h.clamp(-c.limit, c.limit)
+            if c.up_softcap is not None:
+                h = c.up_softcap * torch.tanh(h / c.up_softcap)
+            a = ref.activation(h, c.activation).to(x.dtype)
+        y = self.down(a, ctx)
+        if c.dropout and ctx is not None and ctx.training:   # of the output (``architecture/layers/mlp.py:88`` there)
+            y = nn.functional.dropout(y, c.dropout)
+        return y
 
 
 @register("mlp", "gated_mlp")

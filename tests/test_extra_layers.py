@@ -340,3 +340,29 @@ def test_norm_with_scale_input_puts_the_gain_before_the_statistics():
                 y = y - y.mean(-1, keepdim=True)
             want = y * torch.rsqrt(y.square().mean(-1, keepdim=True) + 1e-6) + n.bias
             assert torch.allclose(n(x), want, atol=1e-5), (kind, zero_centered)
+
+
+def test_mlp_clips_soft_caps_and_drops_out_where_the_reference_does():
+    """``mlp`` / ``gated_mlp``: the up branch clipped to +-limit then soft-capped, the gate capped from
+    above only, the offset added after; dropout on the output (``architecture/layers/mlp.py:20-35,88`` there)."""
+    import torch
+    import torch.nn.functional as F
+
+    from bux_b200.lang import compile
+    from bux_b200.models import Model
+
+    torch.manual_seed(0)
+    x = torch.randn(2, 3, 16) * 3
+    for kind in ("mlp", "gated_mlp"):
+        arch = compile(f"d_model=16\nvocab_size=8\nf = {kind}(intermediate_size=32, activation=swish, limit=1.5, up_softcap=1.0"
+                       + (", up_offset=1.0" if kind == "gated_mlp" else "") + ")\nmodel = embed [f] head\n", filename="m.bux")
+        layer = Model(arch, dtype=torch.float32).graph.items[1].body
+        if kind == "gated_mlp":
+            h = x @ layer.gate_up.weight.t()
+            gate, up = h[..., :32], h[..., 32:]
+            up = torch.tanh(up.clamp(-1.5, 1.5) / 1.0) * 1.0
+            want = (F.silu(gate.clamp(max=1.5)) * (up + 1.0)) @ layer.down.weight.t()
+        else:
+            up = torch.tanh((x @ layer.up.weight.t()).clamp(-1.5, 1.5))
+            want = F.silu(up) @ layer.down.weight.t()
+        assert torch.allclose(layer(x), want, atol=1e-5), kind
