@@ -219,14 +219,18 @@ class MoE(nn.Module):
                 raise NotImplementedError("moe: expert_norm under expert parallelism")
             if not self.gated:
                 raise NotImplementedError("moe: plain MLP experts under expert parallelism")
+            if ec.up_softcap is not None:
+                raise NotImplementedError("moe: experts with up_softcap under expert parallelism")
             out = self.ep(self, flat, w_ffn.reshape(bsz * t, -1), idx_ffn.reshape(bsz * t, -1), ctx, fmt)
-        elif c.expert_norm is not None or not self.gated:
+        elif c.expert_norm is not None or not self.gated or ec.up_softcap is not None:
             # each expert's output is normalised before the weighted sum (the rows are needed one
-            # by one), or the experts are plain MLPs: the per-expert statement of the layer
+            # by one), the experts are plain MLPs, or their up branch is soft-capped (the
+            # kernels have no cap): the per-expert statement of the layer
             norm = (lambda rows: self.expert_norm(rows, ctx)) if c.expert_norm is not None else None
             out = ops.moe_reference(flat, self.experts_gate_up, self.experts_down,
                                           w_ffn.reshape(bsz * t, -1), idx_ffn.reshape(bsz * t, -1),
-                                          ec.activation, ec.limit, ec.up_offset, row_fn=norm, gated=self.gated)
+                                          ec.activation, ec.limit, ec.up_offset, row_fn=norm, gated=self.gated,
+                                          up_softcap=ec.up_softcap)
         else:
             out = ops.moe_experts(flat, self.experts_gate_up, self.experts_down,
                                   w_ffn.reshape(bsz * t, -1), idx_ffn.reshape(bsz * t, -1),

@@ -274,7 +274,7 @@ def moe_experts(x, w_gate_up, w_down, weights, experts, *, act: str = "swish",
 
 
 def moe_reference(x, w_gate_up, w_down, weights, experts, act="swish", limit=None, up_offset=0.0, row_fn=None,
-                  gated: bool = True):
+                  gated: bool = True, up_softcap=None):
     """Differentiable plain-PyTorch experts: sort picks, one matmul pair per expert.
     `row_fn` (optional) maps the experts' output rows before the weighted sum (a norm of
     each expert's output). Without `gated` the experts are plain MLPs: `w_gate_up` is the up
@@ -296,10 +296,19 @@ def moe_reference(x, w_gate_up, w_down, weights, experts, act="swish", limit=Non
             continue
         seg = xs[start:start + n]
         h = seg @ w_gate_up[ex].to(seg.dtype).t()
+        # experts activate as an MLP does: the up branch clipped to +-limit, then soft-capped; a
+        # gate capped from above only
         if gated:
-            a = ref.glu(h[:, :f], h[:, f:], act, limit, up_offset)
+            up = h[:, f:]
+            if up_softcap is not None:
+                up = up.float().clamp(-limit, limit) if limit is not None else up.float()
+                up = (up_softcap * torch.tanh(up / up_softcap)).to(h.dtype)
+            a = ref.glu(h[:, :f], up, act, limit, up_offset)
         else:
-            a = ref.activation(h.float().clamp(max=limit) if limit is not None else h.float(), act).to(h.dtype)
+            up = h.float().clamp(-limit, limit) if limit is not None else h.float()
+            if up_softcap is not None:
+                up = up_softcap * torch.tanh(up / up_softcap)
+            a = ref.activation(up, act).to(h.dtype)
         outs.append(a @ w_down[ex].to(seg.dtype).t())
         start += n
     ys = torch.cat(outs) if outs else xs.new_zeros(0, d)

@@ -123,3 +123,27 @@ def test_plain_mlp_experts_match_a_loop_over_the_picks_and_round_trip_through_th
     back = W.fused(tr.model, exported)
     for name, p in tr.model.state_dict().items():
         assert torch.equal(back[name], p), name
+
+
+def test_experts_soft_cap_their_up_branch_as_an_mlp_does():
+    """An expert with ``up_softcap`` (and ``limit``): one expert with every token routed to it is
+    the same function as the dense gated MLP of the same weights."""
+    import torch
+
+    from bux_b200.lang import compile
+    from bux_b200.models import Model
+
+    torch.manual_seed(0)
+    src = ("d_model=16\nvocab_size=8\nf = gated_mlp(intermediate_size=24, activation=swish, limit=1.5, up_softcap=1.0, up_offset=1.0)\n"
+           "e = moe(num_experts=1, top_k=1, expert=f)\nmodel = embed [{0}] head\n")
+    dense = Model(compile(src.format("f"), filename="m.bux"), dtype=torch.float32).graph.items[1].body
+    sparse = Model(compile(src.format("e"), filename="m.bux"), dtype=torch.float32).graph.items[1].body
+    with torch.no_grad():
+        sparse.experts_gate_up[0].copy_(dense.gate_up.weight)
+        sparse.experts_down[0].copy_(dense.down.weight)
+    x = torch.randn(2, 5, 16) * 3
+    from bux_b200.models.registry import Context, Precision
+
+    ids = torch.zeros(2, 5, dtype=torch.long)
+    ctx = Context(ids, None, None, training=False, precision=Precision(compute=torch.float32))
+    assert torch.allclose(sparse(x, ctx), dense(x, ctx), atol=1e-5)
