@@ -83,7 +83,7 @@ class Norm(nn.Module):
     def __init__(self, c: L.NormalizationConfig, width: int):
         super().__init__()
         self.c = c
-        init = 0.0 if c.zero_centered else c.gain_init
+        init = c.gain_init - 1.0 if c.zero_centered else c.gain_init   # the gain 1 + w starts at gain_init too
         self.scale = nn.Parameter(torch.full((width,), float(init))) if c.affine else None
         self.bias = nn.Parameter(torch.zeros(width)) if c.bias else None
 
