@@ -147,16 +147,20 @@ class Embedding(nn.Module):
 
         self.widen = widening(b.residual)
 
-    def forward(self, ids, ctx: Context):
-        x = self.tokens.embedding[ctx.input_ids]
+    def embed_tokens(self, ids, ctx: Context):
+        """A token's row, scaled by sqrt(d) and normalised where the layer says so: what `nextn`
+        reads too (``architecture/layers/embedding.py:78-81`` there)."""
+        x = self.tokens.embedding[ids]
         if x.dtype != ctx.precision.compute:
             x = x.to(ctx.precision.compute)
         if self.scale is not None:
             x = x * self.scale
-        if self.c.max_positions is not None:
+        return x if self.norm is None else self.norm(x, ctx)
+
+    def forward(self, ids, ctx: Context):
+        x = self.embed_tokens(ctx.input_ids, ctx)
+        if self.c.max_positions is not None:   # after the norm: positions are added to the normalised rows
             x = x + self.positions[ctx.positions].to(x.dtype)
-        if self.norm is not None:
-            x = self.norm(x, ctx)
         if self.dropout and ctx.training:
             x = nn.functional.dropout(x, self.dropout)
         if self.widen is not None:  # the residual algebra's widened stream starts as copies

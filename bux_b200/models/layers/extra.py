@@ -178,7 +178,7 @@ class NextN(nn.Module):
         ctx.nextn_runs = getattr(ctx, "nextn_runs", 0) + 1
         k, tokens = ctx.nextn_runs, ctx.input_ids
         ahead = F.pad(tokens[:, k:], (0, min(k, tokens.shape[1])))
-        e = self.embedding.tokens.embedding[ahead].to(x.dtype)
+        e = self.embedding.embed_tokens(ahead, ctx).to(x.dtype)   # scaled and normalised as the embedding's rows are
         e = self.embed_norm(e, ctx)
         if x.dim() == 4:
             hdn = self.hidden_norm(x.reshape(*x.shape[:2], -1), ctx).reshape(x.shape)
