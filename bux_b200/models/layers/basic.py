@@ -240,7 +240,9 @@ class MLP(nn.Module):
             self.up = Linear(width, f, c.bias, b, role=role)
         self.down = Linear(f, width, c.bias, b, role=role, init_role="out")
 
-    def forward(self, x, ctx: Optional[Context] = None):
+    def forward(self, x, ctx: Optional[Context] = None, hidden_scale=None):
+        """`hidden_scale` ([..., f], optional) multiplies the hidden units before the down
+        projection (an MoE's shared experts weighted by the router)."""
         c = self.c
         if self.gated:
             h = self.gate_up(x, ctx)
@@ -261,6 +263,8 @@ class MLP(nn.Module):
             if c.up_softcap is not None:
                 h = c.up_softcap * torch.tanh(h / c.up_softcap)
             a = ref.activation(h, c.activation).to(x.dtype)
+        if hidden_scale is not None:
+            a = (a.float() * hidden_scale).to(a.dtype)
         y = self.down(a, ctx)
         if c.dropout and ctx is not None and ctx.training:   # of the output (``architecture/layers/mlp.py:88`` there)
             y = nn.functional.dropout(y, c.dropout)

@@ -182,13 +182,19 @@ class MoE(nn.Module):
             return
         err = load.mean() - load
         if c.load_balancing == "smebu":
-            step = torch.tanh(err / load.mean().clamp_min(1.0) / c.bias_softclamp) * c.bias_softclamp
-            self.bias_velocity.mul_(c.bias_momentum).add_(step, alpha=1 - c.bias_momentum)
-            self.router_bias.add_(self.bias_velocity, alpha=c.bias_update_rate)
+            # each expert's shortfall of the mean load as a fraction of the mean, soft-clamped by
+            # tanh(kappa .), times the rate, centred over the experts; the bias moves by the moves'
+            # running average (``architecture/experts/moe.py:365-375,407-425`` there)
+            mean = load.mean()
+            shortfall = err / torch.where(mean > 0, mean, torch.ones_like(mean))
+            move = c.bias_update_rate * torch.tanh(c.bias_softclamp * shortfall)
+            move = move - move.mean()
+            self.bias_velocity.mul_(c.bias_momentum).add_(move, alpha=1 - c.bias_momentum)
+            self.router_bias.add_(self.bias_velocity)
         else:
             self.router_bias.add_(torch.sign(err), alpha=c.bias_update_rate)
-        if c.center_bias:
-            self.router_bias.sub_(self.router_bias.mean())
+            if c.center_bias:
+                self.router_bias.sub_(self.router_bias.mean())
         load.zero_()
 
     # ------------------------------------------------------------------ forward
@@ -245,11 +251,18 @@ class MoE(nn.Module):
         if c.latent_size is not None:
             out = self.from_latent(out, ctx)
         if c.num_shared_experts:
-            shared = self.shared(x, ctx)
+            if sinks is not None:
+                # the router scores the shared experts too: each one's share of the hidden units
+                # is weighted by its own score (``architecture/experts/moe.py:390-404`` there)
+                f = self.shared.c.intermediate_size // sinks.shape[-1]
+                if getattr(self.shared, "f_local", self.shared.c.intermediate_size) != self.shared.c.intermediate_size \
+                        and sinks.shape[-1] > 1:
+                    raise NotImplementedError("moe(shared_expert_sink=true) with several shared experts under tensor parallelism")
+                shared = self.shared(x, ctx, hidden_scale=sinks.float().repeat_interleave(f, dim=-1))
+            else:
+                shared = self.shared(x, ctx)
             if c.shared_expert_gate:
                 shared = (shared.float() * torch.sigmoid(self.shared_gate(x, ctx).float())).to(shared.dtype)
-            if sinks is not None:
-                shared = (shared.float() * sinks.sum(-1, keepdim=True)).to(shared.dtype)
             out = out + shared
         return out
 

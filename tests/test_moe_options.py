@@ -147,3 +147,40 @@ def test_experts_soft_cap_their_up_branch_as_an_mlp_does():
     ids = torch.zeros(2, 5, dtype=torch.long)
     ctx = Context(ids, None, None, training=False, precision=Precision(compute=torch.float32))
     assert torch.allclose(sparse(x, ctx), dense(x, ctx), atol=1e-5)
+
+
+def test_shared_experts_scored_by_the_router_and_the_smebu_move():
+    """``shared_expert_sink``: every shared expert's hidden units are weighted by its own score,
+    normalised with the picks. ``smebu``: the bias moves by the running average of the centred,
+    soft-clamped shortfalls (``architecture/experts/moe.py:259-273,365-425`` there)."""
+    import torch
+    import torch.nn.functional as F
+
+    from bux_b200.lang import compile
+    from bux_b200.models import Model
+    from bux_b200.models.registry import Context, Precision
+
+    torch.manual_seed(0)
+    arch = compile("d_model=16\nvocab_size=8\nf = gated_mlp(intermediate_size=8, activation=swish)\n"
+                   "e = moe(num_experts=4, top_k=2, expert=f, num_shared_experts=2, shared_expert_sink=true, load_balancing=smebu,"
+                   " bias_update_rate=0.1, bias_softclamp=2.0, bias_momentum=0.5)\nmodel = embed [e] head\n", filename="m.bux")
+    layer = Model(arch, dtype=torch.float32).graph.items[1].body
+    x = torch.randn(2, 5, 16)
+    ctx = Context(torch.zeros(2, 5, dtype=torch.long), None, None, training=True, precision=Precision(compute=torch.float32))
+    idx, weights, sinks = layer.route(x, ctx)
+    assert sinks.shape[-1] == 2 and torch.allclose(weights.sum(-1) + sinks.sum(-1), torch.ones(2, 5), atol=1e-5)
+    h = x @ layer.shared.gate_up.weight.t()
+    hidden = F.silu(h[..., :16]) * h[..., 16:]
+    want_shared = (hidden * sinks.repeat_interleave(8, dim=-1)) @ layer.shared.down.weight.t()
+    got = layer(x, ctx)
+    from bux_b200 import ops
+
+    routed = ops.moe_reference(x.reshape(10, 16), layer.experts_gate_up, layer.experts_down, weights.reshape(10, 2), idx.reshape(10, 2)).view(2, 5, 16)
+    assert torch.allclose(got, routed + want_shared, atol=1e-5)
+    load = layer.router_load.clone()
+    mean = load.mean()
+    move = 0.1 * torch.tanh(2.0 * (mean - load) / mean)
+    move = move - move.mean()
+    layer.step_end_update()
+    assert torch.allclose(layer.router_bias[:4], 0.5 * move[:4] if move.numel() > 4 else 0.5 * move, atol=1e-6)
+    assert float(layer.router_load.sum()) == 0
