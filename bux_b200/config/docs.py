@@ -309,7 +309,7 @@ FIELDS = {
     "switch": {"at": "Share of the run after which the new passes apply.", "passes": "The passes quantised from then on."},
     "mesh": {"data": "Replicas of the model (the batch is split).", "stage": "Pipeline stages.", "fsdp": "Ranks that shard parameters, gradients and moments.",
              "context": "Ranks that split each sequence.", "expert": "Ranks that split the experts.", "tensor": "Ranks that split heads and hidden units."},
-    "methods": {"attention": "Which attention path runs.", "moe": "How tokens reach experts: `sorted` on one GPU, `all_to_all` or `fused_ep` across GPUs.",
+    "methods": {"attention": "Which attention path runs.", "moe": "How tokens reach experts: `sorted` on one GPU; over the `expert` axis `fused_ep` (the in-kernel exchange over peer memory; `nccl_ep` names it too) or the library all-to-all (`all_to_all`, and every other name).",
                 "capacity": "Rows an expert shard accepts, as a multiple of the even share.", "moe_chunks": "Token chunks the expert exchange is pipelined in.",
                 "moe_stream": "Run the exchange on a side stream.", "remat": "`none`, `full` per block, `auto` (fitted to the memory), or a `remat(save=...)` policy.",
                 "pipeline": "Pipeline schedule: `gpipe`, `1f1b`, `zbh1`, `circular`.", "stages": "Blocks per stage when the balance is set by hand.",

@@ -536,7 +536,9 @@ class ExpertParallel:
 
     def __init__(self, group, method: str = "fused_ep", capacity: Optional[float] = None):
         self.group = group
-        self.method = method if method in ("fused_ep",) else "all_to_all"
+        # `nccl_ep` is the reference's name for its in-kernel exchange: a file written for it takes
+        # this package's counterpart; every other method over the expert axis takes the library all-to-all
+        self.method = "fused_ep" if method in ("fused_ep", "nccl_ep") else "all_to_all"
         if self.method == "fused_ep":
             from .. import runtime
 

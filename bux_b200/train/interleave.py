@@ -110,7 +110,7 @@ def unsupported(trainer) -> Optional[str]:
             return "a pipeline has its own schedule"
         if par.fsdp is not None:
             return "sharded parameters are gathered for one pass at a time"
-        if par.expert_group is not None and getattr(m, "moe", "") == "fused_ep":
+        if par.expert_group is not None and getattr(m, "moe", "") in ("fused_ep", "nccl_ep"):
             return "the in-kernel expert exchange has one set of buffers per layer"
     from ..models.graph import Repeated
 
