@@ -7,7 +7,8 @@ outer branch (``act/rms/gqa.03``, ``act/update_rms/...``, ``act/max_abs/...``,
 ``act/kurtosis/...``), every MoE's routing (``router/max_load/moe.01``, ``router/dead/...``,
 ``router/entropy/...``, ``router/z/...``) and a sample of every attention's logits
 (``attn/logit_max/...``, ``attn/entropy/...``). With `histograms`, log2-magnitude histograms of
-the weights and of the stream after each branch go to ``histograms.jsonl``.
+the weights, of the gradients still held and of the stream after each branch go to
+``histograms.jsonl``.
 Reference: ``train/observe.py``, ``architecture/observe.py``.
 """
 
@@ -29,6 +30,18 @@ def log2_histogram(t: torch.Tensor, lo: int = -24, hi: int = 8) -> list:
     mag = t.detach().float().abs().flatten()
     e = torch.floor(torch.log2(mag.clamp_min(2.0 ** lo))).clamp(lo, hi).long() - lo
     return torch.bincount(e, minlength=hi - lo + 1).tolist()
+
+
+def gradient_stats(trainer, histograms: bool) -> dict:
+    """name -> (RMS, log2-magnitude histogram or None) of every gradient the step still holds
+    (this rank's part of it, under sharding). The trainer calls it on an observed step between
+    the backward and the update."""
+    out = {}
+    for n, p in trainer.model.named_parameters():
+        g = trainer.optimizer.grad_of(p)
+        if g is not None:
+            out[n] = (rms(g), log2_histogram(g) if histograms else None)
+    return out
 
 
 class Observe(Hook):
@@ -75,17 +88,19 @@ class Observe(Hook):
         stats.update({k: float(v) for k, v in tr.observed.items()})
         streams = {k: v.tolist() for k, v in tr.observed_histograms.items()}
         tr.observed, tr.observed_histograms = {}, {}
-        weights = {}
+        weights, grads = {}, {}
+        seen, tr.observed_gradients = tr.observed_gradients, {}
         for n, p in tr.model.named_parameters():
             stats[f"param/{n}"] = rms(p)
-            g = tr.optimizer.grad_of(p)
-            if g is not None:
-                stats[f"grad/{n}"] = rms(g)
+            if n in seen:
+                stats[f"grad/{n}"] = seen[n][0]
+                if seen[n][1] is not None:
+                    grads[n] = seen[n][1]
             if n in self.before:
                 stats[f"update/{n}"] = rms(p.detach().float() - self.before[n])
             if self.c.histograms:
                 weights[n] = log2_histogram(p)
-        self.reports[self.armed_step] = (stats, weights, streams)
+        self.reports[self.armed_step] = (stats, weights, streams, grads)
         self.acts, self.before, self.armed = {}, {}, False
 
     def due(self, step: int, trainer, last: bool = False) -> bool:
@@ -95,12 +110,12 @@ class Observe(Hook):
         if step == getattr(self, "armed_step", None):
             self._collect()   # the run's last step: nothing was launched after it
         if step in self.reports:
-            stats, weights, streams = self.reports.pop(step)
+            stats, weights, streams, grads = self.reports.pop(step)
             for s in sinks or ():
                 s.write(step, stats)
             if self.c.histograms and self.folder is not None:
                 with open(self.folder / "histograms.jsonl", "a") as f:
-                    f.write(json.dumps({"step": step, "histograms": weights, "stream": streams}) + "\n")
+                    f.write(json.dumps({"step": step, "histograms": weights, "stream": streams, "gradients": grads}) + "\n")
 
     def stop(self, trainer, sinks) -> None:
         for h in self.handles:

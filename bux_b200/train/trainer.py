@@ -121,6 +121,7 @@ class Trainer:
         self.pre_step: list = []       # callables of the number of the step that is about to run
         self.observed: dict = {}
         self.observed_histograms: dict = {}
+        self.observed_gradients: dict = {}   # name -> (rms, histogram or None) of an observed step's gradients
         self._prefixes = None
         self._token_bytes = None
         self.stretches = curriculum.stretches(t)
@@ -277,6 +278,10 @@ class Trainer:
                 terms[name] = terms.get(name, 0) + v.float() / n_micro
         if self.parallel is not None:
             self.parallel.finish_grads(self.model)
+        if self.observing is not None:   # an observed step: the gradients' statistics, before the update lets go of them
+            from . import observe
+
+            self.observed_gradients = observe.gradient_stats(self, bool(self.observing.get("histograms")))
         if self.fuse_optimizer:
             # parameters whose gradients had to be summed over ranks first are updated now,
             # with the same (delayed) clip factor as the ones updated during the backward

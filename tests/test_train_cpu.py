@@ -151,6 +151,7 @@ def test_ema_ships_a_blend_and_observe_logs_per_layer_stats(tmp_path):
     lines = [json.loads(x) for x in (folder / "metrics.jsonl").read_text().splitlines()]
     keys = set().union(*(set(x) for x in lines))
     assert any(k.startswith("param/") for k in keys) and any(k.startswith("update/") for k in keys)
+    assert any(k.startswith("grad/") for k in keys)      # taken between the backward and the update
     assert any(k.startswith("act/graph") for k in keys)
     # the forward of an observed step files the stream and the attention under their branches
     for want in ("act/rms/gqa.00", "act/update_rms/gated_mlp.01", "act/max_abs/gqa.01", "act/kurtosis/gated_mlp.00",
@@ -160,6 +161,7 @@ def test_ema_ships_a_blend_and_observe_logs_per_layer_stats(tmp_path):
     assert [x["step"] for x in observed] == [4, 8, 12] and all(x["act/rms/gqa.00"] > 0 for x in observed)
     hist = [json.loads(x) for x in (folder / "histograms.jsonl").read_text().splitlines()]
     assert hist and hist[0]["step"] == 4 and sum(hist[0]["histograms"][name]) == tr.model.get_parameter(name).numel()
+    assert sum(hist[0]["gradients"][name]) == tr.model.get_parameter(name).numel()      # the gradients' too
     assert sum(hist[0]["stream"]["act/hist/gqa.00"]) == 8 * 64 * 64      # batch x seq_len x d_model entries
 
 
