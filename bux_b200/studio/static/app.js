@@ -131,6 +131,18 @@ const ui = {
     editor.select(node.span);
     showInspector($("inspector"), app, node);
   },
+  open(node) {
+    // a layer's inside, drawn by the same code in an overlay; its boxes select nothing in the source
+    const box = clear($("ask"));
+    const picture = document.createElementNS("http://www.w3.org/2000/svg", "svg");
+    picture.id = "inside";
+    const close = () => { box.hidden = true; };
+    box.append(el("div", { style: "max-width:90vw;max-height:90vh;overflow:auto" }, el("h3", {}, `${node.title}${node.name ? " · " + node.name : ""}`),
+      picture, el("div", {}, el("button", { onclick: close }, "close"))));
+    drawModel(picture, node.inside, { pick() {}, repeat() {} });
+    picture.classList.add("diagram");
+    box.hidden = false;
+  },
   repeat(node) {
     const n = prompt("repeat how many times?", node.times);
     if (n && /^\d+$/.test(n.trim()) && node.span) app.edit({ op: "set_repeat", start: node.span[0], end: node.span[1], times: Number(n) });

@@ -40,7 +40,10 @@ function draw(n, cx, bottom, ui) {
   const { w, h } = n._;
   const g = svg("g", { class: "node", "data-id": n.id });
   g.addEventListener("click", ev => { ev.stopPropagation(); ui.pick(n, g); });
-  g.addEventListener("dblclick", ev => { if (n.kind === "repeat") { ev.stopPropagation(); ui.repeat(n); } });
+  g.addEventListener("dblclick", ev => {
+    if (n.kind === "repeat") { ev.stopPropagation(); ui.repeat(n); }
+    else if (n.inside && ui.open) { ev.stopPropagation(); ui.open(n); }     // what the layer is made of
+  });
   const top = bottom - h, left = cx - w / 2;
   if (n.kind === "layer") {
     g.append(svg("rect", { class: "box", x: left, y: top, width: w, height: h, fill: FILL[n.type] || (RECURRENT.has(n.type) ? "var(--rec)" : "white") }));

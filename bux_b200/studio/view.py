@@ -19,6 +19,7 @@ from ..lang import compiler, ir
 from ..lang import syntax as S
 from ..lang.lsp import features
 from ..lang.printer import config_to_source, value_to_source
+from . import internals
 
 TITLES = {
     "embed": "Token embedding", "head": "Output head", "rmsnorm": "RMSNorm", "layernorm": "LayerNorm", "dyt": "Dynamic tanh",
@@ -103,8 +104,8 @@ def chips(c) -> list:
 class Drawing:
     """Turns an architecture's graph into the page's tree, numbering nodes in walk order."""
 
-    def __init__(self, spans: dict, base: int, limit: int):
-        self.spans, self.base, self.limit = spans, base, limit
+    def __init__(self, spans: dict, base: int, limit: int, d_model: int = 0):
+        self.spans, self.base, self.limit, self.d_model = spans, base, limit, d_model
         self.count = 0
 
     def span(self, node) -> Optional[list]:
@@ -122,7 +123,9 @@ class Drawing:
             c = n.config
             out.update(type=c.type, title=TITLES.get(c.type, c.type), chips=chips(c), source=config_to_source(c),
                        ports=[{"name": p.name, "mode": p.mode, "tap": p.tap} for p in n.ports],
-                       opens=c.type in ("mlp", "gated_mlp", "moe", "gqa", "mla", "deltanet", "gdn", "kda", "gdn2", "mamba2"))
+                       opens=c.type in internals.BUILDERS)
+            if out["opens"]:
+                out["inside"] = internals.inside(c, n.width if isinstance(n.width, int) else self.d_model)
             if getattr(n, "share", None):
                 out["shared"] = n.share
         elif isinstance(n, ir.Seq):
@@ -277,7 +280,7 @@ def view(source: str, filename: str = "<buffer>", picks: Optional[dict] = None, 
     chosen = found[run]
     # spans of the chosen run's nodes: evaluate it once more, keeping the evaluator
     ev, arch, train = compiler._evaluate(program, "model", chosen.choices, None, require=False)
-    drawing = Drawing(ev.node_spans, main.start, main.stop)
+    drawing = Drawing(ev.node_spans, main.start, main.stop, arch.d_model)
     out["model"] = drawing.node(arch.graph)
     out["card"] = card(arch)
     out["training"] = training(train) if train is not None else None

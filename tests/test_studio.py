@@ -50,6 +50,11 @@ def test_view_describes_the_run_the_picks_select():
     attn = repeat["body"]["items"][0]["body"]["items"][1]
     assert attn["title"] == "Grouped-query attention" and attn["chips"][:2] == ["4 heads", "2 KV heads"] and "RoPE 10k" in attn["chips"]
     assert SRC[slice(*attn["span"])] == "mixer"            # where the macro writes it
+    inside = attn["inside"]                                 # what the layer opens into
+    assert inside["kind"] == "seq" and inside["items"][0]["kind"] == "prod" and len(inside["items"][0]["factors"]) == 3
+    assert any(i.get("title") == "Softmax attention" for i in inside["items"]) and "64 → 4 × 16" in json.dumps(inside, ensure_ascii=False)
+    ffn = repeat["body"]["items"][1]["body"]["items"][1]
+    assert ffn["inside"]["items"][0]["kind"] == "prod" and ffn["inside"]["items"][-1]["title"] == "Down projection"
     t = v["training"]
     assert t["tokens"] == 50 * 8 * 64 and t["schedule"]["warmup_end"] == 10 and t["schedule"]["decay_start"] == 40
     assert max(t["schedule"]["scale"]) == 1.0 and t["schedule"]["scale"][-1] < 0.05
