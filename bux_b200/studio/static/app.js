@@ -45,6 +45,7 @@ const app = {
       for (const e of v.errors) errors.append(el("div", { onclick: () => { editor.area.focus(); editor.area.setSelectionRange(e.start, e.end); } },
         `line ${text.slice(0, e.start).split("\n").length}: ${e.message}`));
       if (v.errors.length) { $("status").textContent = `${v.errors.length} error${v.errors.length > 1 ? "s" : ""}: the drawing shows the last text that compiled`; return; }
+      if (!v.model) { $("status").textContent = "this file defines no model to draw"; return; }
       this.fresh = true;
       $("diagram-scroll").classList.remove("stale");
       $("status").textContent = "";
