@@ -8,7 +8,8 @@ caller compiles it again before it draws it. Offsets are into the buffer.
   added to the call when it is not, removed when set back to nothing. A name that is a
   definition is changed at its definition; one defined in a module, by an amendment in this
   file (``attn.num_heads = 12``).
-* `set_setting`: a top-level statement (``steps = 200``), replaced or appended.
+* `set_setting`: a top-level statement (``steps = 200``), replaced or appended;
+  `set_setting_field`: one field of a setting written as a call (``schedule = wsd(warmup=20)``).
 * `insert`, `delete`, `wrap`, `unwrap`, `set_repeat`: the graph's shape, at a node's span.
 * `alt_replace`, `alt_add`, `alt_remove`: one alternative of a sweep axis.
 
@@ -166,6 +167,28 @@ def set_setting(source: str, name: str, value: Optional[str]) -> str:
     return source.rstrip("\r\n") + f"{nl}{name} = {value}{nl}"
 
 
+def set_setting_field(source: str, name: str, key: str, value: Optional[str], kind: Optional[str] = None,
+                      path: Optional[str] = None) -> str:
+    """One field of a top-level setting written as a call (``schedule = wsd(warmup=20)``): the
+    field replaced, added or removed inside the call and the rest of it kept. A setting the
+    file does not write is appended as ``name = kind(key=value)``."""
+    ix = features.Index(source, path)
+    st = next((s for s in ix.own if s.name == name and not s.amends and s.body is not None), None)
+    if st is None:
+        if value is None:
+            return source
+        if kind is None:
+            raise EditError(f"the file does not set '{name}': say which type to write")
+        return set_setting(source, name, f"{kind}({key}={value})")
+    body = st.body
+    if isinstance(body, S.Call):
+        return _in_call(source, body, ix.base, tuple(key.split(".")), value)
+    if isinstance(body, S.Name):
+        at = body.span.end - ix.base
+        return source if value is None else splice(source, at, at, f"({key}={value})")
+    raise EditError(f"'{name}' is not written as one call (a sweep's alternatives, say): edit it in the source")
+
+
 # ------------------------------------------------------------------------------ the graph's shape
 def _checked(source: str, start: int, end: int, path) -> None:
     ix = features.Index(source, path)
@@ -263,7 +286,7 @@ def alt_remove(source: str, start: int, end: int) -> str:
     return splice(source, s, end + after.end(), "")
 
 
-OPERATIONS = {"set_field": set_field, "set_setting": set_setting, "insert": insert, "delete": delete, "wrap": wrap,
+OPERATIONS = {"set_field": set_field, "set_setting": set_setting, "set_setting_field": set_setting_field, "insert": insert, "delete": delete, "wrap": wrap,
               "unwrap": unwrap, "set_repeat": set_repeat, "alt_replace": alt_replace, "alt_add": alt_add,
               "alt_remove": alt_remove}
 
@@ -274,6 +297,6 @@ def apply(source: str, edit: dict, path: Optional[str] = None) -> str:
     if op not in OPERATIONS:
         raise EditError(f"no edit called {op!r}")
     args = {k: v for k, v in edit.items() if k != "op"}
-    if op in ("set_field", "insert", "delete", "wrap", "unwrap", "set_repeat"):
+    if op in ("set_field", "set_setting_field", "insert", "delete", "wrap", "unwrap", "set_repeat"):
         args["path"] = path
     return OPERATIONS[op](source, **args)

@@ -85,8 +85,9 @@ function lrChart(t, app) {
       const stepAt = ev => Math.max(0, Math.min(t.steps, Math.round(((ev.clientX - box.left) / box.width * W - L) / (W - L - R) * steps)));
       grip.addEventListener("pointerup", up => {
         const at2 = stepAt(up);
-        const args = what === "warmup" ? `warmup=${at2}` : `warmup=${s.warmup_end}, decay=${((t.steps - at2) / t.steps).toFixed(3)}`;
-        app.edit({ op: "set_setting", name: "schedule", value: `${s.type}(${args})` });
+        // one field of the schedule's call; its other settings (final, shape, ...) stay as written
+        if (what === "warmup") app.edit({ op: "set_setting_field", name: "schedule", key: "warmup", value: String(at2), kind: s.type });
+        else app.edit({ op: "set_setting_field", name: "schedule", key: "decay", value: ((t.steps - at2) / t.steps).toFixed(3), kind: s.type });
       }, { once: true });
     });
     chart.append(grip);

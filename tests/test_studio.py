@@ -133,6 +133,14 @@ def test_edits_are_splices_that_keep_the_rest_of_the_file():
     less = edits.alt_remove(more, *_span(more, "gqa(num_heads=4, num_kv_heads=1)"))
     assert "mqa" not in less and "# full" in less and len(_ok(less)) == 4
     assert edits.apply(SRC, {"op": "set_setting", "name": "batch", "value": "16"}).count("batch = 16") == 1
+    # one field of a setting's call: the rest of the call stays as written
+    shaped = SRC.replace("schedule = wsd(warmup=10)", "schedule = wsd(warmup=10, final=0.1)   # cool down to a tenth")
+    out = edits.apply(shaped, {"op": "set_setting_field", "name": "schedule", "key": "decay", "value": "0.300", "kind": "wsd"}, "s.bux")
+    assert "schedule = wsd(warmup=10, final=0.1, decay=0.300)   # cool down to a tenth" in out and _ok(out)
+    out = edits.apply(out, {"op": "set_setting_field", "name": "schedule", "key": "warmup", "value": "25", "kind": "wsd"}, "s.bux")
+    assert "wsd(warmup=25, final=0.1, decay=0.300)" in out
+    bare = SRC.replace("schedule = wsd(warmup=10)\n", "")
+    assert "schedule = wsd(warmup=5)" in edits.set_setting_field(bare, "schedule", "warmup", "5", "wsd", "s.bux")
 
 
 def test_a_setting_written_in_a_module_is_changed_by_an_amendment(tmp_path):
