@@ -21,6 +21,19 @@ export class Editor {
 
   get text() { return this.area.value; }
 
+  // the width of a character and the height of a line in the editor's own font, measured once
+  get cell() {
+    if (!this._cell) {
+      const probe = el("span", { style: "position:absolute;visibility:hidden;white-space:pre" }, "x".repeat(50));
+      this.marks.append(probe);
+      const box = probe.getBoundingClientRect();
+      const line = parseFloat(getComputedStyle(this.marks).lineHeight) || box.height;
+      this._cell = { w: box.width / 50 || 7.5, h: line || 18.75 };
+      probe.remove();
+    }
+    return this._cell;
+  }
+
   set(text, keepCursor = true) {
     const at = this.area.selectionStart;
     this.area.value = text;
@@ -34,7 +47,7 @@ export class Editor {
     this.selected = span; this.paint();
     if (span) {                                  // bring the text into view without moving the caret
       const line = this.text.slice(0, span[0]).split("\n").length;
-      const y = (line - 3) * 18.75;
+      const y = (line - 3) * this.cell.h;
       if (y < this.area.scrollTop || y > this.area.scrollTop + this.area.clientHeight - 60) this.area.scrollTop = Math.max(0, y);
     }
   }
@@ -71,8 +84,8 @@ export class Editor {
     this.items.forEach((it, i) => this.list.append(el("li", { class: i === 0 ? "on" : "", title: it.doc, onmousedown: ev => { ev.preventDefault(); this.accept(i); } },
       el("span", {}, it.label), el("small", {}, it.detail || it.kind))));
     const lines = before.split("\n");
-    this.list.style.left = Math.min(this.area.clientWidth - 220, 12 + 7.5 * lines[lines.length - 1].length - this.area.scrollLeft) + "px";
-    this.list.style.top = 10 + 18.75 * lines.length - this.area.scrollTop + "px";
+    this.list.style.left = Math.min(this.area.clientWidth - 220, 12 + this.cell.w * lines[lines.length - 1].length - this.area.scrollLeft) + "px";
+    this.list.style.top = 10 + this.cell.h * lines.length - this.area.scrollTop + "px";
     this.list.hidden = false;
   }
 
@@ -104,8 +117,8 @@ export class Editor {
     this.tip.hidden = true;
     this.rest = setTimeout(async () => {
       const box = this.area.getBoundingClientRect();
-      const line = Math.floor((ev.clientY - box.top - 10 + this.area.scrollTop) / 18.75);
-      const col = Math.round((ev.clientX - box.left - 12 + this.area.scrollLeft) / 7.5);
+      const line = Math.floor((ev.clientY - box.top - 10 + this.area.scrollTop) / this.cell.h);
+      const col = Math.round((ev.clientX - box.left - 12 + this.area.scrollLeft) / this.cell.w);
       const lines = this.text.split("\n");
       if (line < 0 || line >= lines.length || col > lines[line].length) return;
       const offset = lines.slice(0, line).reduce((a, l) => a + l.length + 1, 0) + Math.max(0, col);
