@@ -24,8 +24,8 @@ different streams and the device overlaps them. The gradients are the ones a pla
 accumulation gives (each parameter receives the microbatches' terms in the same order).
 
 What it does not combine with, and then runs the microbatches one after another with a
-warning: sharded parameters (a unit gathered for one microbatch's backward would be freed by
-the other's forward), the in-kernel expert exchange (one set of exchange buffers per layer),
+warning: parameters gathered by the peer-memory kernels (one staging buffer per unit; the NCCL
+gathers run under it), the in-kernel expert exchange (one set of exchange buffers per layer),
 block inputs kept in host memory (their prefetch follows one backward at a time), a
 pipeline, and the update fused into the backward. Reference: ``train/interleave.py:1-30,209``.
 """
@@ -108,8 +108,8 @@ def unsupported(trainer) -> Optional[str]:
     if par is not None:
         if getattr(par, "pipeline", None) is not None:
             return "a pipeline has its own schedule"
-        if par.fsdp is not None:
-            return "sharded parameters are gathered for one pass at a time"
+        if par.fsdp is not None and getattr(par.fsdp, "fused_comm", None) is not None:
+            return "the peer-memory all-gather keeps one staging buffer per unit"
         if par.expert_group is not None and getattr(m, "moe", "") in ("fused_ep", "nccl_ep"):
             return "the in-kernel expert exchange has one set of buffers per layer"
     from ..models.graph import Repeated

@@ -552,13 +552,16 @@ def test_a_failed_background_save_is_raised_by_the_next_wait(tmp_path, monkeypat
 
 
 @pytest.mark.parametrize("mesh,extra", [("mesh(data=2)", []),
-                                        ("mesh(expert=2)", ["methods.moe = all_to_all", "methods.capacity = 4.0"])])
+                                        ("mesh(expert=2)", ["methods.moe = all_to_all", "methods.capacity = 4.0"]),
+                                        ("mesh(fsdp=2)", []), ("mesh(fsdp=2)", ["methods.accumulate = unreduced"]),
+                                        ("mesh(fsdp=2)", ["layout = layout(zero=1)"])])
 def test_interleaved_microbatches_over_ranks_match_one_rank(tmp_path, mesh, extra):
     """``methods(interleave=true)`` over two ranks: every rank issues the two halves of a tick in
     the same order, so the collectives of one microbatch's forward and of the other's backward
     (the expert all-to-alls, the early gradient reductions) meet as they would one after another."""
-    over = ["methods.microbatches = 2", "methods.interleave = true", "methods.remat = full"]
-    want_losses, want = _single(MOE, ["methods.microbatches = 2"])
+    n = 4 if "fsdp" in mesh else 2
+    over = [f"methods.microbatches = {n}", "methods.interleave = true", "methods.remat = full"]
+    want_losses, want = _single(MOE, [f"methods.microbatches = {n}"])
     got = _spawn(2, MOE, [f"mesh = {mesh}", *over, *extra], tmp_path)
     assert got["losses"] == pytest.approx(want_losses, abs=2e-5)
     _check_rows(got, want)
