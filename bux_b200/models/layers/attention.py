@@ -71,11 +71,15 @@ class GQA(nn.Module):
         self.dv = c.v_head_dim or self.d
         self.q_rows, self.k_rows = self.hq * self.d, self.g * self.d
         self.v_rows = 0 if c.k_eq_v else self.g * self.dv       # k_eq_v: values are the normalised keys
-        self.qkv = Linear(width, self.q_rows + self.k_rows + self.v_rows, c.bias, b, role="q")
+        from .. import placement
+
         out_bias = c.bias if c.output_bias is None else c.output_bias
-        self.o = Linear(self.h * self.dv, width, out_bias, b, role="o", init_role="out")
-        if c.mimetic_vo is not None:
-            self._mimetic_vo(width, c.mimetic_vo, c.mimetic_noise)
+        # the mimetic initialisation writes V's and O's rows by index: those two are built whole
+        with placement.whole_parameters() if c.mimetic_vo is not None else placement.placing(placement._experts, placement._rows):
+            self.qkv = Linear(width, self.q_rows + self.k_rows + self.v_rows, c.bias, b, role="q")
+            self.o = Linear(self.h * self.dv, width, out_bias, b, role="o", init_role="out")
+            if c.mimetic_vo is not None:
+                self._mimetic_vo(width, c.mimetic_vo, c.mimetic_noise)
         if c.qk_norm is not None:
             per = self.d
             self.q_norm = Norm(c.qk_norm, self.hq * per if c.qk_norm_all_heads else per)

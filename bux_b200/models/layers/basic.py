@@ -18,6 +18,7 @@ from torch import nn
 from ... import ops
 from ...config import layers as L
 from ...ops import reference as ref
+from .. import placement
 from ..registry import BuildContext, Context, register
 
 
@@ -60,6 +61,7 @@ class Linear(nn.Module):
         super().__init__()
         self.weight = nn.Parameter(torch.empty(fan_out, fan_in, dtype=bctx.dtype))
         init_weight(self.weight, bctx.init, init_role)
+        self.weight = placement.place_dense(self.weight)   # under sharded parameters: this rank's rows only
         self.bias = nn.Parameter(torch.zeros(fan_out, dtype=bctx.dtype)) if bias else None
         self.role = role
         self.tp_fused = None  # (kind, group, reorder) when the tensor-parallel collective runs in the GEMM
@@ -130,6 +132,7 @@ class TokenTable(nn.Module):
         super().__init__()
         self.embedding = nn.Parameter(torch.empty(vocab, width, dtype=bctx.dtype))
         init_weight(self.embedding, bctx.init, "embed", fan_in=width, fan_out=width)
+        self.embedding = placement.place_dense(self.embedding)
 
 
 class Embedding(nn.Module):

@@ -107,15 +107,41 @@ class Parallel:
         return idx
 
     # ------------------------------------------------------------------ the model
-    def placement(self):
+    def placement(self, arch=None, dtype=torch.bfloat16):
         """The context a model is built under, so that sharded stacks of experts are created
         as this rank's shard (`bux_b200.models.placement`). Pipeline stages still build the
         whole model first: a stage's share of the blocks is decided on the built graph."""
         from ..models import placement
 
+        experts = rows = None
         if self.expert_group is not None and self.stage_group is None:
-            return placement.placing(experts=(dist.get_rank(self.expert_group), self.shape["expert"]))
-        return placement.placing()
+            experts = (dist.get_rank(self.expert_group), self.shape["expert"])
+        if self.places_dense(arch, dtype):
+            group = self.group(self.shard_axes())
+            rows = (dist.get_rank(group), dist.get_world_size(group))
+        return placement.placing(experts=experts, rows=rows)
+
+    DENSE_PLACEMENT_BYTES = 16 << 30
+
+    def places_dense(self, arch=None, dtype=torch.bfloat16) -> bool:
+        """Whether dense parameters are cut to this rank's rows as they are created. Only where
+        rows are all that cuts them (no tensor parallelism, no pipeline, NCCL gathers) and, by
+        default, where a whole copy would be large (``BUX_PLACE_DENSE=always | never`` overrides)."""
+        how = os.environ.get("BUX_PLACE_DENSE", "auto")
+        options = getattr(getattr(self.train, "compiler", None), "options", "") or ""
+        if (how == "never" or not self.shard_axes() or self.tensor_group is not None or self.stage_group is not None
+                or "--fsdp=fused" in options.split()):
+            return False
+        if how == "always":
+            return True
+        if arch is None:
+            return False
+        from ..models import Model
+
+        with torch.device("meta"):     # shapes only: what a whole copy of the dense parameters would take
+            shapes = Model(arch, dtype=dtype)
+        dense = sum(p.numel() for n, p in shapes.named_parameters() if "experts_gate_up" not in n and "experts_down" not in n)
+        return dense * torch.empty((), dtype=dtype).element_size() >= self.DENSE_PLACEMENT_BYTES
 
     def prepare_model(self, model) -> None:
         """Shard what the mesh shards: experts over ``expert``, then (tensor / fsdp) the

@@ -427,6 +427,11 @@ class FSDP:
                     if block is model and any(owner is m for b in blocks for m in b.modules()):
                         continue
                     taken.add(id(p))
+                    if getattr(p, "placed_whole", None) is not None:
+                        # built as this rank's rows already (`models.placement`): adopted as it is
+                        p._bux_sharded, p._bux_rows = True, p.placed_whole
+                        entries.append((owner, attr, p))
+                        continue
                     if p.dim() == 0 or p.shape[0] % self.world != 0 or p.shape[0] < self.world:
                         continue  # stays whole on every rank (replicated, all-reduced)
                     if fused and (p.dtype != torch.bfloat16 or (p.numel() // self.world * 2) % 16):

@@ -78,7 +78,7 @@ class Trainer:
         cuda = self.device.type == "cuda"
         self.compute = torch.bfloat16 if (t.precision.compute == "bfloat16" and cuda) else torch.float32
         self.param_dtype = self.compute
-        with parallel.placement() if parallel is not None else _null():
+        with parallel.placement(run.arch, self.param_dtype) if parallel is not None else _null():
             self.model = Model(run.arch, dtype=self.param_dtype, seed=t.seed if seed is None else seed,
                                device=self.device)
         if parallel is not None:

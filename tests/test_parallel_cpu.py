@@ -565,3 +565,61 @@ def test_interleaved_microbatches_over_ranks_match_one_rank(tmp_path, mesh, extr
     got = _spawn(2, MOE, [f"mesh = {mesh}", *over, *extra], tmp_path)
     assert got["losses"] == pytest.approx(want_losses, abs=2e-5)
     _check_rows(got, want)
+
+
+def _placed_worker(rank, world, port, overrides, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      BUX_PLACE_DENSE="always")
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from bux_b200.models.layers import basic
+    from bux_b200.parallel.engine import Parallel
+    from bux_b200.train.trainer import Trainer
+
+    torch.set_num_threads(1)
+    # the largest dense parameter this rank ever holds whole: counted where parameters are cut
+    largest = [0]
+    cut = basic.placement.place_dense
+
+    def counting(p):
+        kept = cut(p)
+        if kept is p:
+            largest[0] = max(largest[0], p.numel())
+        return kept
+
+    basic.placement.place_dense = counting
+    run = compile_runs(MOE, filename="p.bux", overrides=overrides)[0]
+    par = Parallel(run.train, torch.device("cpu"))
+    tr = Trainer(run, device="cpu", parallel=par)
+    placed = sum(getattr(p, "placed_whole", None) is not None for p in tr.model.parameters())
+    feed = iter(tr.batches())
+    losses = [tr.train_step(next(feed))["loss"].item() for _ in range(2)]
+    state = {n: p.detach().clone() for n, p in tr.model.named_parameters()}
+    if rank == 0:
+        torch.save({"losses": losses, "state": state, "placed": placed, "whole_kept": largest[0]}, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,mesh,extra", [
+    (2, "mesh(fsdp=2)", ["methods.microbatches = 2", "methods.remat = full"]),
+    (4, "mesh(data=2, fsdp=2)", []),
+    (2, "mesh(expert=2)", ["methods.moe = all_to_all", "methods.capacity = 4.0"]),     # experts and dense rows over one axis
+    (2, "mesh(fsdp=2)", ["a = gqa(num_heads=2, num_kv_heads=1, rope=rope(), mimetic_vo=0.05)"]),
+])
+def test_dense_parameters_are_built_as_the_ranks_shard(tmp_path, world, mesh, extra):
+    """With dense placement every projection and the token table are cut to the rank's rows as
+    they are created (the whole tensor is drawn first, so the values are a one-rank build's): the
+    run matches one rank, and no projection is ever kept whole."""
+    out = str(tmp_path / "r.pt")
+    plain = [e for e in extra if not e.startswith("methods.moe") and not e.startswith("methods.capacity")]
+    want_losses, want = _single(MOE, plain)
+    mp.spawn(_placed_worker, args=(world, _free_port(), [f"mesh = {mesh}", *extra], out), nprocs=world, join=True)
+    got = torch.load(out)
+    assert got["placed"] >= 3, got["placed"]
+    assert got["losses"] == pytest.approx(want_losses, abs=2e-5)
+    _check_rows(got, want)
+    if "mimetic" in " ".join(extra):
+        assert got["whole_kept"] > 0        # V and O of the mimetic layer were built whole on purpose
+    else:
+        assert got["whole_kept"] <= 64      # only parameters whose rows do not divide stay whole (none larger than a bias)
