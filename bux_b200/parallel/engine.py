@@ -138,8 +138,11 @@ class Parallel:
             return False
         from ..models import Model
 
-        with torch.device("meta"):     # shapes only: what a whole copy of the dense parameters would take
-            shapes = Model(arch, dtype=dtype)
+        try:
+            with torch.device("meta"):     # shapes only: what a whole copy of the dense parameters would take
+                shapes = Model(arch, dtype=dtype)
+        except Exception:  # noqa: BLE001 - a layer that cannot be built without memory: keep the old path
+            return False
         dense = sum(p.numel() for n, p in shapes.named_parameters() if "experts_gate_up" not in n and "experts_down" not in n)
         return dense * torch.empty((), dtype=dtype).element_size() >= self.DENSE_PLACEMENT_BYTES
 
