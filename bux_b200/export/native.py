@@ -96,7 +96,8 @@ def detect(arch: ir.Architecture) -> Optional[str]:
         ok = (ffn.router == "softmax" and not ffn.num_shared_experts and ffn.num_groups == 1
               and not ffn.router_bias and ffn.load_balancing not in ("aux_free", "smebu")
               and ffn.routed_scaling_factor == 1.0 and ffn.router_logit_scale == 1.0
-              and x.type == "gated_mlp" and x.activation == "swish" and x.limit is None and not x.up_offset)
+              and x.type == "gated_mlp" and x.activation == "swish" and x.limit is None and not x.up_offset
+              and not x.bias and x.up_softcap is None)
         # what the family's format can say, or what only training uses; anything else off its default is not the family
         allowed = {"type", "num_experts", "top_k", "expert", "normalize_top_k", "aux_loss_coef", "aux_loss_scope",
                    "random_logits", "load_balancing", "bias_update_rate", "bias_softclamp", "bias_momentum"}

@@ -128,6 +128,8 @@ def _dyt(c, b):
 
 # ------------------------------------------------------------------ embedding / head
 class TokenTable(nn.Module):
+    no_muon = True
+
     def __init__(self, vocab: int, width: int, bctx: BuildContext):
         super().__init__()
         self.embedding = nn.Parameter(torch.empty(vocab, width, dtype=bctx.dtype))
@@ -136,6 +138,8 @@ class TokenTable(nn.Module):
 
 
 class Embedding(nn.Module):
+    no_muon = True
+
     def __init__(self, c: L.EmbeddingConfig, b: BuildContext):
         super().__init__()
         self.c = c
@@ -193,6 +197,8 @@ class HeadOutput:
 
 
 class Head(nn.Module):
+    no_muon = True
+
     def __init__(self, c: L.LMHeadConfig, b: BuildContext):
         super().__init__()
         self.c = c

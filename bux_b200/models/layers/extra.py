@@ -129,6 +129,8 @@ def _mla(c, b):
 class ValueEmbedding(nn.Module):
     """A row per token, pushed to the ``ve`` port for an attention layer to add to its
     values; the stream goes on as it is."""
+    no_muon = True
+
 
     def __init__(self, c: L.ValueEmbeddingConfig, b: BuildContext):
         super().__init__()
@@ -229,6 +231,8 @@ class Engram(nn.Module):
     `num_heads` heads into tables of distinct prime sizes; with e the looked-up rows,
     a = <norm(x), norm(W_k e)>/sqrt(d), it adds u = sigmoid(sign(a) sqrt|a|) W_v e and,
     with a conv, silu(conv(norm(u)))."""
+    no_weight_decay = ("table",)
+
 
     def __init__(self, c: L.EngramConfig, b: BuildContext):
         super().__init__()
@@ -379,6 +383,9 @@ class DocCopy(nn.Module):
     """Adds gain·(E[c]·s[b] + e[b]) of each position's candidate c and bucket b to the
     stream (every copy of a widened one). With its ``copy`` port it pushes the vector,
     or reads it instead and adds it by its own gain."""
+    no_weight_decay = ("gain", "scale", "bucket_embed")
+    no_muon = True
+
 
     def __init__(self, c: L.DocCopyConfig, b: BuildContext):
         super().__init__()

@@ -76,6 +76,8 @@ class _ScaleGrad(torch.autograd.Function):
 
 
 class MoE(nn.Module):
+    no_weight_decay = ("up_bias", "down_bias")   # stacks, but of vectors
+
     def __init__(self, c: L.MoEConfig, b: BuildContext):
         super().__init__()
         # plain MLP experts (one projection up, an activation, one down: Nemotron's relu² experts)
@@ -102,6 +104,10 @@ class MoE(nn.Module):
             self.expert_norm = Norm(c.expert_norm, inner)
         self.experts_gate_up = nn.Parameter(torch.empty(e, (2 if self.gated else 1) * f, inner, dtype=b.dtype))
         self.experts_down = nn.Parameter(torch.empty(e, inner, f, dtype=b.dtype))
+        if c.expert.bias:
+            # one bias vector per expert and projection: stacks, but of vectors (no weight decay)
+            self.up_bias = nn.Parameter(torch.zeros(e, (2 if self.gated else 1) * f, dtype=b.dtype))
+            self.down_bias = nn.Parameter(torch.zeros(e, inner, dtype=b.dtype))
         init_weight(self.experts_gate_up, b.init)
         rows = placement.expert_rows(e)   # under expert parallelism: this rank's experts only
         if rows is not None:
@@ -227,16 +233,20 @@ class MoE(nn.Module):
                 raise NotImplementedError("moe: plain MLP experts under expert parallelism")
             if ec.up_softcap is not None:
                 raise NotImplementedError("moe: experts with up_softcap under expert parallelism")
+            if ec.bias:
+                raise NotImplementedError("moe: experts with biases under expert parallelism")
             out = self.ep(self, flat, w_ffn.reshape(bsz * t, -1), idx_ffn.reshape(bsz * t, -1), ctx, fmt)
-        elif c.expert_norm is not None or not self.gated or ec.up_softcap is not None:
+        elif c.expert_norm is not None or not self.gated or ec.up_softcap is not None or ec.bias:
             # each expert's output is normalised before the weighted sum (the rows are needed one
-            # by one), the experts are plain MLPs, or their up branch is soft-capped (the
-            # kernels have no cap): the per-expert statement of the layer
+            # by one), the experts are plain MLPs, their up branch is soft-capped or they have
+            # biases (the kernels have neither): the per-expert statement of the layer
             norm = (lambda rows: self.expert_norm(rows, ctx)) if c.expert_norm is not None else None
             out = ops.moe_reference(flat, self.experts_gate_up, self.experts_down,
                                           w_ffn.reshape(bsz * t, -1), idx_ffn.reshape(bsz * t, -1),
                                           ec.activation, ec.limit, ec.up_offset, row_fn=norm, gated=self.gated,
-                                          up_softcap=ec.up_softcap)
+                                          up_softcap=ec.up_softcap,
+                                          up_bias=getattr(self, "up_bias", None),
+                                          down_bias=getattr(self, "down_bias", None))
         else:
             out = ops.moe_experts(flat, self.experts_gate_up, self.experts_down,
                                   w_ffn.reshape(bsz * t, -1), idx_ffn.reshape(bsz * t, -1),

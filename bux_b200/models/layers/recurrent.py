@@ -408,6 +408,8 @@ class RWKV7(nn.Module):
     """Token shift, r/k/v, low-rank decay w and in-context learning rate a, the
     generalised delta rule S_t = (diag(w) - (a kk) kk^T) S_{t-1} + k v^T, a per-head
     layernorm plus the bonus (r k r_k) v, gate, projection. Port ``v``: value residual."""
+    no_weight_decay = ("shift", "r_k")
+
 
     def __init__(self, c, b: BuildContext):
         super().__init__()
@@ -506,6 +508,8 @@ def mamba_scan(x, dt, A, B, C, starts=None, state=None, last: Optional[list] = N
 
 
 class Mamba(nn.Module):
+    no_weight_decay = ("A_log",)
+
     def __init__(self, c, b: BuildContext):
         super().__init__()
         from ...config import layers as L
@@ -544,6 +548,8 @@ class Mamba(nn.Module):
 
 
 class Mamba2(nn.Module):
+    no_weight_decay = ("A_log",)
+
     def __init__(self, c, b: BuildContext):
         super().__init__()
         from ...config import layers as L

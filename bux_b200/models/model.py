@@ -15,6 +15,22 @@ from .graph import GraphBuilder, Repeated
 from .registry import Context, Precision
 
 
+def mark_exemptions(model: nn.Module) -> None:
+    """Carry what a module's class says about its parameters onto the parameters themselves,
+    where the optimizer reads it: the names in a class's ``no_weight_decay`` are skipped by
+    weight decay whatever their rank (stacks of vectors, decay rates, lookup tables), and every
+    parameter under a ``no_muon`` class is left to AdamW. Reference: ``train/optim.py:345-349,
+    423-428``."""
+    for module in model.modules():
+        for name in getattr(type(module), "no_weight_decay", ()):
+            p = module._parameters.get(name)
+            if p is not None:
+                p.no_weight_decay = True
+        if getattr(type(module), "no_muon", False):
+            for p in module.parameters():
+                p.no_muon = True
+
+
 class Model(nn.Module):
     """``Model(arch)(input_ids)`` runs the graph and returns the forward's `Context`:
     ``ctx.heads`` holds every head's `HeadOutput` (hidden states + output matrix, the
@@ -32,6 +48,7 @@ class Model(nn.Module):
                 self.graph = GraphBuilder(arch, dtype).build(arch.graph)
         finally:
             torch.random.set_rng_state(gen_state)
+        mark_exemptions(self)
 
     def forward(self, input_ids: torch.Tensor, positions: Optional[torch.Tensor] = None,
                 segments: Optional[torch.Tensor] = None, *, training: Optional[bool] = None,

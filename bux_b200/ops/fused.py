@@ -274,11 +274,13 @@ def moe_experts(x, w_gate_up, w_down, weights, experts, *, act: str = "swish",
 
 
 def moe_reference(x, w_gate_up, w_down, weights, experts, act="swish", limit=None, up_offset=0.0, row_fn=None,
-                  gated: bool = True, up_softcap=None):
+                  gated: bool = True, up_softcap=None, up_bias=None, down_bias=None):
     """Differentiable plain-PyTorch experts: sort picks, one matmul pair per expert.
     `row_fn` (optional) maps the experts' output rows before the weighted sum (a norm of
     each expert's output). Without `gated` the experts are plain MLPs: `w_gate_up` is the up
-    projection alone ([E, f, d]) and the activation applies to it."""
+    projection alone ([E, f, d]) and the activation applies to it. `up_bias` ([E, 2f] or
+    [E, f]) is added to an expert's projection before the activation, `down_bias` ([E, d]) to
+    its output before `row_fn` and the weighted sum."""
     t, d = x.shape
     e, f2, _ = w_gate_up.shape
     f = f2 // 2 if gated else f2
@@ -296,6 +298,8 @@ def moe_reference(x, w_gate_up, w_down, weights, experts, act="swish", limit=Non
             continue
         seg = xs[start:start + n]
         h = seg @ w_gate_up[ex].to(seg.dtype).t()
+        if up_bias is not None:
+            h = h + up_bias[ex].to(h.dtype)
         # experts activate as an MLP does: the up branch clipped to +-limit, then soft-capped; a
         # gate capped from above only
         if gated:
@@ -309,7 +313,8 @@ def moe_reference(x, w_gate_up, w_down, weights, experts, act="swish", limit=Non
             if up_softcap is not None:
                 up = up_softcap * torch.tanh(up / up_softcap)
             a = ref.activation(up, act).to(h.dtype)
-        outs.append(a @ w_down[ex].to(seg.dtype).t())
+        y = a @ w_down[ex].to(seg.dtype).t()
+        outs.append(y if down_bias is None else y + down_bias[ex].to(y.dtype))
         start += n
     ys = torch.cat(outs) if outs else xs.new_zeros(0, d)
     if row_fn is not None and ys.shape[0]:

@@ -175,9 +175,10 @@ def weight_decay_mask(name: str, p: torch.Tensor) -> bool:
 
 
 def muon_eligible(name: str, p: torch.Tensor) -> bool:
-    """Hidden 2-D (or stacked expert 3-D) matrices; embeddings and heads use AdamW."""
+    """Hidden 2-D (or stacked expert 3-D) matrices; embeddings and heads use AdamW, and so does
+    what weight decay is told to skip (stacks of vectors, decay rates, tables: no linear maps)."""
     leaf = name.split(".")
-    if p.ndim < 2 or getattr(p, "no_muon", False):
+    if p.ndim < 2 or getattr(p, "no_muon", False) or getattr(p, "no_weight_decay", False):
         return False
     return not ("embedding" in leaf or "proj" in leaf[-2:] and "head" in name or "tokens" in leaf
                 or "router" in leaf or "positions" in leaf)

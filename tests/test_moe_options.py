@@ -184,3 +184,37 @@ def test_shared_experts_scored_by_the_router_and_the_smebu_move():
     layer.step_end_update()
     assert torch.allclose(layer.router_bias[:4], 0.5 * move[:4] if move.numel() > 4 else 0.5 * move, atol=1e-6)
     assert float(layer.router_load.sum()) == 0
+
+
+def test_experts_with_biases_are_the_dense_mlp_and_skip_weight_decay():
+    """``expert=gated_mlp(bias=true)``: one expert with every token routed to it is the dense
+    gated MLP with the same weights and biases; the bias stacks are 2-D but weight decay skips
+    them (reference: ``architecture/experts/moe.py:139,608-622``)."""
+    from bux_b200.lang import compile
+    from bux_b200.models import Model
+    from bux_b200.models.registry import Context, Precision
+    from bux_b200.train import optim
+
+    torch.manual_seed(0)
+    src = ("d_model=16\nvocab_size=8\nf = gated_mlp(intermediate_size=24, activation=swish, bias=true)\n"
+           "e = moe(num_experts=1, top_k=1, expert=f)\nmodel = embed [{0}] head\n")
+    dense = Model(compile(src.format("f"), filename="m.bux"), dtype=torch.float32).graph.items[1].body
+    model = Model(compile(src.format("e"), filename="m.bux"), dtype=torch.float32)
+    sparse = model.graph.items[1].body
+    with torch.no_grad():
+        dense.gate_up.bias.normal_()
+        dense.down.bias.normal_()
+        sparse.experts_gate_up[0].copy_(dense.gate_up.weight)
+        sparse.experts_down[0].copy_(dense.down.weight)
+        sparse.up_bias[0].copy_(dense.gate_up.bias)
+        sparse.down_bias[0].copy_(dense.down.bias)
+    x = torch.randn(2, 5, 16)
+    ctx = Context(torch.zeros(2, 5, dtype=torch.long), None, None, training=False,
+                  precision=Precision(compute=torch.float32))
+    assert torch.allclose(sparse(x, ctx), dense(x, ctx), atol=1e-5)
+    named = dict(model.named_parameters())
+    for name, p in named.items():
+        if name.endswith(("up_bias", "down_bias")):
+            assert p.ndim == 2 and not optim.weight_decay_mask(name, p)
+        if name.endswith("experts_gate_up"):
+            assert optim.weight_decay_mask(name, p) and optim.muon_eligible(name, p)

@@ -512,3 +512,34 @@ def test_checkpointed_blocks_pass_gradients_through_taps_and_ports(model):
     assert got["none"][0] == pytest.approx(got["full"][0], abs=1e-6)
     for name, p in got["none"][1].items():
         assert torch.allclose(p, got["full"][1][name], atol=1e-6), name
+
+
+def test_parameters_their_layers_exempt_skip_weight_decay_and_muon():
+    """The 2-D parameters that are not matrices of a linear map (RWKV-7's shift mixes and bonus
+    keys, Mamba's decay rates, value-embedding and token tables) are marked where the optimizer
+    looks: no weight decay for the first three, AdamW instead of Muon for the tables and the head
+    (reference: ``recurrent/rwkv7.py:76``, ``recurrent/ssm.py:182,267``, ``layers/embedding.py:60,142,197``)."""
+    import torch
+
+    from bux_b200.lang import compile
+    from bux_b200.models import Model
+    from bux_b200.train import optim
+
+    src = ("d_model=32\nvocab_size=64\nn = rmsnorm\nt = rwkv7(num_heads=2, head_dim=16)\n"
+           "s = mamba(state_size=4)\ns2 = mamba2(num_heads=2, head_dim=16, state_size=8)\n"
+           "a = gqa(num_heads=2, num_kv_heads=1, rope=rope(), ve=$ve!)\n"
+           "f = gated_mlp(intermediate_size=48, activation=swish)\n"
+           "model = embed value_embed(features=16, ve=@ve) [n a] [n t] [n s] [n s2] [n f] n head\n")
+    arch = compile(src, filename="m.bux")
+    model = Model(arch, dtype=torch.float32)
+    seen = set()
+    for name, p in model.named_parameters():
+        leaf = name.rsplit(".", 1)[-1]
+        if leaf in ("shift", "r_k", "A_log"):
+            seen.add(leaf)
+            assert not optim.weight_decay_mask(name, p), name
+        if p.ndim >= 2 and (".embed" in "." + name or "head" in name or "tokens" in name or "table" in name):
+            assert not optim.muon_eligible(name, p), name
+    assert seen == {"shift", "r_k", "A_log"}
+    mats = [n for n, p in model.named_parameters() if optim.muon_eligible(n, p)]
+    assert any("gate_up" in n for n in mats) and all(optim.weight_decay_mask(n, dict(model.named_parameters())[n]) for n in mats)
