@@ -139,6 +139,8 @@ def split(module: nn.Module, name: str, dim: int, pieces: list, r: int, n: int, 
         parts.append(old.data.narrow(dim, off + r * per, per))
         off += size
     new = nn.Parameter(torch.cat(parts, dim=dim).contiguous(), requires_grad=old.requires_grad)
+    for k, v in old.__dict__.items():   # what the optimizer reads off a parameter (no_weight_decay, no_muon)
+        setattr(new, k, v)
     module._parameters[name] = new
     layout[id(new)] = (dim, list(pieces))
     return new
